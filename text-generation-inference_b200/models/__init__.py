@@ -1,0 +1,136 @@
+"""Model registry: ``config.json`` -> runner.
+
+Role of the reference's ``models/__init__.py`` (``ModelType`` enum ``:217-417``, ``get_model``
+``:425-1800``, ``get_model_with_lora_adapters`` ``:1802-1916``): resolve dtype / quantisation /
+KV-cache dtype / speculation, pick a runner, load weights shard-wise, attach LoRA adapters.
+"""
+from __future__ import annotations
+
+import json
+import os
+from pathlib import Path
+from typing import Dict, List, Optional
+
+import torch
+
+from ..parallel.dist import initialize_torch_distributed
+from ..utils.quantization import get_loader
+from ..utils.tokenizer import load_tokenizer
+from ..utils.weights import Weights, weight_files
+from .arch import ARCHS, ModelConfig
+
+# model_type -> (display name, multimodal)
+SUPPORTED: Dict[str, str] = {k: k for k in ARCHS}
+
+_DTYPES = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, None: None}
+
+
+def resolve_dtype(dtype: Optional[str], device: torch.device, quantize: Optional[str]) -> torch.dtype:
+    if dtype is not None:
+        return _DTYPES[dtype]
+    if device.type == "cpu":
+        return torch.float32
+    return torch.bfloat16
+
+
+def resolve_kv_dtype(kv_cache_dtype: Optional[str], dtype: torch.dtype) -> torch.dtype:
+    if kv_cache_dtype in (None, "", "auto"):
+        return dtype
+    if kv_cache_dtype in ("fp8_e4m3fn", "fp8", "fp8_e4m3"):
+        return torch.float8_e4m3fn
+    if kv_cache_dtype == "fp8_e5m2":
+        return torch.float8_e5m2
+    raise ValueError(f"unknown kv cache dtype {kv_cache_dtype}")
+
+
+def eos_token_ids(model_path: Path, cfg: ModelConfig):
+    ids = set()
+    g = model_path / "generation_config.json"
+    src = json.loads(g.read_text()) if g.exists() else {}
+    for e in (src.get("eos_token_id"), cfg.get("eos_token_id")):
+        if isinstance(e, int):
+            ids.add(e)
+        elif isinstance(e, (list, tuple)):
+            ids.update(int(x) for x in e)
+    return ids or None
+
+
+def get_model(
+    model_id: str,
+    revision: Optional[str] = None,
+    sharded: bool = False,
+    quantize: Optional[str] = None,
+    speculate: Optional[int] = None,
+    dtype: Optional[str] = None,
+    kv_cache_dtype: Optional[str] = None,
+    trust_remote_code: bool = False,
+    max_input_tokens: Optional[int] = None,
+    device: Optional[torch.device] = None,
+    max_prefill_tokens: Optional[int] = None,
+):
+    """Load the shard of ``model_id`` (a local directory) that belongs to this process."""
+    from .flash_causal_lm import FlashCausalLM
+    from .decoder import CausalDecoder
+
+    process_group, rank, world = initialize_torch_distributed()
+    if device is None:
+        device = torch.device(f"cuda:{torch.cuda.current_device()}") if torch.cuda.is_available() else torch.device("cpu")
+    path = Path(model_id)
+    if not path.is_dir():
+        from ..utils.hub import resolve_model_path
+
+        path = resolve_model_path(model_id, revision)
+    cfg = ModelConfig.from_path(path)
+    model_type = cfg.model_type
+    tdtype = resolve_dtype(dtype, device, quantize)
+    loader = get_loader(quantize, path, cfg.to_dict())
+    speculate = int(speculate or 0)
+    tokenizer = load_tokenizer(str(path), revision, trust_remote_code, vocab_size=cfg.get("vocab_size", 259))
+    if model_type in ("llava_next", "idefics2", "idefics3", "paligemma", "qwen2_vl", "qwen2_5_vl", "mllama"):
+        from .vlm_causal_lm import load_vlm
+
+        return load_vlm(path, cfg, loader, process_group, rank, world, tdtype, device, tokenizer, speculate,
+                        kv_cache_dtype, max_prefill_tokens)
+    if model_type in ("bloom", "mpt", "opt", "t5", "mamba") or model_type not in ARCHS:
+        from .padded import load_padded
+
+        return load_padded(path, cfg, process_group, rank, world, tdtype, device, tokenizer)
+    text_cfg = cfg.text_config()
+    weights = Weights(weight_files(path), device, tdtype, process_group=process_group, loader=loader,
+                      aliases=_aliases(model_type))
+    prefix = ""
+    if model_type in ("gpt2",) and weights.has_tensor("transformer.wte.weight"):
+        prefix = "transformer"
+    model = CausalDecoder(text_cfg, weights, prefix=prefix,
+                          max_positions=_max_positions(text_cfg, max_input_tokens))
+    spec_head = None
+    runner = FlashCausalLM(model, tokenizer, tdtype, device, rank, world, speculate,
+                           resolve_kv_dtype(kv_cache_dtype, tdtype), max_prefill_tokens,
+                           eos_token_ids(path, cfg))
+    weights.close()
+    return runner
+
+
+def _max_positions(cfg: ModelConfig, max_input_tokens: Optional[int]) -> int:
+    mp = int(cfg.get("max_position_embeddings", cfg.get("n_positions", 2048)))
+    cap = int(os.environ.get("TGI_B200_MAX_POSITIONS", "0"))
+    if cap:
+        mp = min(mp, cap) if cap < mp else cap
+    return mp
+
+
+def _aliases(model_type: str):
+    if model_type in ("llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "phi3", "granite"):
+        return {"lm_head.weight": ["model.embed_tokens.weight"]}
+    if model_type == "gpt2":
+        return {"lm_head.weight": ["wte.weight", "transformer.wte.weight"]}
+    return {}
+
+
+def get_model_with_lora_adapters(model_id: str, lora_adapters=None, **kwargs):
+    model = get_model(model_id, **kwargs)
+    if lora_adapters:
+        from ..utils.adapter import load_and_attach_adapters
+
+        load_and_attach_adapters(model, model_id, lora_adapters)
+    return model

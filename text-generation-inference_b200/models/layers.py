@@ -1,0 +1,230 @@
+"""Linear / embedding / head building blocks with tensor parallelism.
+
+Counterparts in the reference: ``layers/linear.py:21-44`` (``FastLinear``),
+``layers/fp8.py:428-579`` (``Fp8Linear``), ``layers/tensor_parallel.py:39-249``
+(column / row linear, vocab-parallel embedding and head), ``layers/speculative.py``.
+
+These are plain callables, not ``nn.Module``s: the forward pass is a flat list of
+kernel launches that gets captured into a CUDA graph, and nothing here needs
+autograd, hooks or state dicts.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+from ..parallel import dist as pdist
+
+FP8 = torch.float8_e4m3fn
+
+
+class FastLinear:
+    """``y = x @ W^T + b`` with ``W[N,K]`` in the serving dtype."""
+
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        self.weight = weight
+        self.bias = bias
+
+    @property
+    def out_features(self):
+        return self.weight.shape[0]
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias)
+
+
+class Fp8Linear:
+    """e4m3 weight with per-tensor, per-channel or 128x128-block scales.
+
+    Block-scaled weights use dynamically 1x128-quantised activations and the block-scaled GEMM; an
+    already quantised activation can be passed as ``(xq, xs)`` so the producer kernel (RMSNorm or
+    SwiGLU) fuses the quantisation.  Per-tensor/per-channel weights are served by re-expressing the
+    scales per block when the shape allows it, otherwise by dequantising once at load.
+    """
+
+    def __init__(self, qweight, scale, bias, dtype, input_scale=None, scale_upper_bound=None,
+                 weight_block_size: Optional[Sequence[int]] = None):
+        self.dtype = dtype
+        self.bias = bias
+        self.input_scale = input_scale
+        self.scale_upper_bound = scale_upper_bound
+        N, K = qweight.shape
+        self.block = None
+        self.dense = None
+        if weight_block_size is not None:
+            assert list(weight_block_size) == [128, 128], "only 128x128 weight blocks are supported"
+            self.qweight, self.scale, self.block = qweight, scale.float().contiguous(), 128
+        elif K % 128 == 0:
+            # Express per-tensor / per-channel scales on the block grid: a per-channel scale cannot
+            # be represented per block, so it is applied in the GEMM epilogue instead.
+            nb, kb = (N + 127) // 128, K // 128
+            if scale.numel() == 1:
+                self.qweight, self.block = qweight, 128
+                self.scale = scale.float().reshape(1, 1).expand(nb, kb).contiguous()
+            else:
+                self.qweight, self.block = qweight, 128
+                self.scale = torch.ones(nb, kb, dtype=torch.float32, device=qweight.device)
+                self.channel_scale = scale.float().reshape(-1).contiguous()
+        else:
+            s = scale.float().reshape(-1, 1) if scale.numel() > 1 else scale.float()
+            self.dense = FastLinear((qweight.float() * s).to(dtype), bias)
+        if not hasattr(self, "channel_scale"):
+            self.channel_scale = None
+
+    @property
+    def out_features(self):
+        return self.dense.out_features if self.dense is not None else self.qweight.shape[0]
+
+    @property
+    def wants_quantized_input(self) -> bool:
+        return self.dense is None
+
+    def __call__(self, x, x_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.dense is not None:
+            return self.dense(x)
+        if x_scale is None:
+            x, x_scale = ops.fp8_quant_act(x)
+        out = ops.gemm_fp8_block(x, x_scale, self.qweight, self.scale, self.dtype,
+                                 self.bias if self.channel_scale is None else None)
+        if self.channel_scale is not None:
+            out = (out.float() * self.channel_scale).to(self.dtype)
+            if self.bias is not None:
+                out = out + self.bias
+        return out
+
+
+def get_linear(weight, bias):
+    """Checkpoint weight object (or raw tensor) -> callable linear."""
+    if isinstance(weight, torch.Tensor):
+        return FastLinear(weight, bias)
+    return weight.get_linear(bias)
+
+
+class TensorParallelColumnLinear:
+    """Output features sharded across ranks; no communication."""
+
+    def __init__(self, linear):
+        self.linear = linear
+
+    @classmethod
+    def load(cls, config, prefix: str, weights, bias: bool):
+        w = weights.get_weights_col(prefix)
+        b = weights.get_sharded(f"{prefix}.bias", dim=0) if bias else None
+        return cls(get_linear(w, b))
+
+    @classmethod
+    def load_multi(cls, config, prefixes: List[str], weights, bias: bool, dim: int = 0):
+        w = weights.get_multi_weights_col(prefixes, dim)
+        b = torch.cat([weights.get_sharded(f"{p}.bias", dim=0) for p in prefixes], dim=dim) if bias else None
+        return cls(get_linear(w, b))
+
+    @classmethod
+    def load_qkv(cls, config, prefix: str, weights, bias: bool, num_heads: int, num_key_value_heads: int):
+        """A checkpoint that stores q, k, v fused in one matrix (Phi-3, GPT-2 style ``c_attn`` ...)."""
+        w = weights.get_weights_col_packed_qkv(prefix, num_heads, num_key_value_heads)
+        b = (weights.get_packed_sharded(f"{prefix}.bias", 0, [num_heads, num_key_value_heads, num_key_value_heads])
+             if bias else None)
+        return cls(get_linear(w, b))
+
+    @classmethod
+    def load_gate_up(cls, config, prefix: str, weights, bias: bool):
+        w = weights.get_weights_col_packed_gate_up(prefix)
+        b = weights.get_packed_sharded(f"{prefix}.bias", 0, 2) if bias else None
+        return cls(get_linear(w, b))
+
+    def __call__(self, x, x_scale=None):
+        if x_scale is not None:
+            return self.linear(x, x_scale)
+        return self.linear(x)
+
+
+class TensorParallelRowLinear:
+    """Input features sharded; partial sums are reduced across ranks (bias lives on rank 0 only)."""
+
+    def __init__(self, linear, process_group, comm=None):
+        self.linear = linear
+        self.process_group = process_group
+        self.comm = comm
+
+    @classmethod
+    def load(cls, config, prefix: str, weights, bias: bool, comm=None):
+        w = weights.get_weights_row(prefix)
+        b = weights.get_tensor(f"{prefix}.bias") if bias and weights.process_group.rank() == 0 else None
+        return cls(get_linear(w, b), weights.process_group, comm)
+
+    def __call__(self, x, x_scale=None, reduce: bool = True):
+        out = self.linear(x, x_scale) if x_scale is not None else self.linear(x)
+        if reduce and self.process_group.size() > 1:
+            if self.comm is not None:
+                return self.comm.all_reduce(out)
+            pdist.all_reduce(out, self.process_group)
+        return out
+
+
+class TensorParallelEmbedding:
+    """Vocab-parallel embedding: each rank owns a ceil-div block of rows; foreign ids hit a zero row."""
+
+    def __init__(self, prefix: str, weights, reduce: bool = True, comm=None):
+        w = weights.get_partial_sharded(f"{prefix}.weight", dim=0)
+        pg = weights.process_group
+        num = weights.get_shape(f"{prefix}.weight")[0]
+        block = (num + pg.size() - 1) // pg.size()
+        self.min_id = pg.rank() * block
+        self.max_id = min(num, (pg.rank() + 1) * block)
+        self.null_idx = w.shape[0]
+        self.process_group = pg
+        self.reduce = reduce
+        self.comm = comm
+        self.weight = torch.cat([w, w.new_zeros(1, w.shape[1])], dim=0) if pg.size() > 1 else w
+
+    def __call__(self, ids: torch.Tensor) -> torch.Tensor:
+        if self.process_group.size() == 1:
+            return ops.embedding(ids, self.weight)
+        local = torch.where((ids < self.min_id) | (ids >= self.max_id), self.null_idx, ids - self.min_id)
+        out = ops.embedding(local, self.weight)
+        if self.reduce:
+            if self.comm is not None:
+                return self.comm.all_reduce(out)
+            pdist.all_reduce(out, self.process_group)
+        return out
+
+
+class TensorParallelHead:
+    """Vocab-parallel lm_head.
+
+    ``__call__`` returns full logits ``[B, V]`` (all-gather of the shards; used when the sampler needs
+    the whole distribution).  ``local_logits`` returns the rank's ``[B, V/tp]`` slice together with the
+    first vocabulary id it covers, for the distributed sampling path that never gathers logits.
+    """
+
+    def __init__(self, linear, process_group, should_gather: bool, vocab_start: int = 0):
+        self.linear = linear
+        self.process_group = process_group
+        self.should_gather = should_gather
+        self.vocab_start = vocab_start
+
+    @classmethod
+    def load(cls, config, prefix: str, weights):
+        pg = weights.process_group
+        total = weights.get_shape(f"{prefix}.weight")[0]
+        if total % pg.size() == 0 and pg.size() > 1:
+            w = weights.get_sharded(f"{prefix}.weight", dim=0)
+            return cls(FastLinear(w), pg, True, pg.rank() * (total // pg.size()))
+        # Vocabulary not divisible: every rank keeps the full head (as the reference does).
+        return cls(FastLinear(weights.get_tensor(f"{prefix}.weight")), pg, False, 0)
+
+    def local_logits(self, x: torch.Tensor):
+        return self.linear(x), self.vocab_start
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        local = self.linear(x)
+        if not self.should_gather:
+            return local
+        world = self.process_group.size()
+        B, Vl = local.shape
+        gathered = local.new_empty(world, B, Vl)
+        pdist.all_gather_into(gathered, local.contiguous(), self.process_group)
+        return gathered.permute(1, 0, 2).reshape(B, world * Vl)

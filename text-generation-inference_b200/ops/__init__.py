@@ -1,0 +1,135 @@
+"""Op front end: routes every hot op to the sm_100a kernels (CUDA tensors) or the PyTorch oracle (CPU).
+
+On a CUDA tensor the native kernel library is *required*: if it has not been
+built, the call raises instead of silently running a PyTorch fallback.  Setting
+``TGI_B200_OPS=torch`` selects the PyTorch implementations on the GPU as well;
+that switch exists for A/B numerics checks and for the library-kernel baseline
+path, never as a default.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from . import reference as ref
+
+_FORCE_TORCH = os.environ.get("TGI_B200_OPS", "") == "torch"
+_backend = None
+
+
+def native():
+    """The CUDA kernel backend module (loads the in-tree shared library on first use)."""
+    global _backend
+    if _backend is None:
+        from . import cuda as _cuda_backend
+
+        _cuda_backend.load()
+        _backend = _cuda_backend
+    return _backend
+
+
+def use_native(t: torch.Tensor) -> bool:
+    return t.is_cuda and not _FORCE_TORCH
+
+
+def set_force_torch(flag: bool) -> None:
+    global _FORCE_TORCH
+    _FORCE_TORCH = flag
+
+
+def rms_norm(x, residual, weight, eps, unit_offset=False):
+    if use_native(x):
+        return native().rms_norm(x, residual, weight, eps, unit_offset)
+    return ref.rms_norm(x, residual, weight, eps, unit_offset)
+
+
+def rms_norm_quant(x, residual, weight, eps, unit_offset=False):
+    """Residual-add + RMSNorm + 1x128 e4m3 quantisation: returns ``(xq, scales, new_residual)``."""
+    if use_native(x):
+        return native().rms_norm_quant(x, residual, weight, eps, unit_offset)
+    y, res = ref.rms_norm(x, residual, weight, eps, unit_offset)
+    q, s = ref.fp8_quant_act(y)
+    return q, s, res
+
+
+def layer_norm(x, residual, weight, bias, eps):
+    if use_native(x):
+        return native().layer_norm(x, residual, weight, bias, eps)
+    return ref.layer_norm(x, residual, weight, bias, eps)
+
+
+def rope_and_cache(qkv, positions, cos_sin, slots, k_cache, v_cache, num_heads, num_kv_heads, head_dim,
+                   rot_dim, neox=True, k_scale=None, v_scale=None):
+    if use_native(qkv):
+        return native().rope_and_cache(qkv, positions, cos_sin, slots, k_cache, v_cache, num_heads,
+                                       num_kv_heads, head_dim, rot_dim, neox, k_scale, v_scale)
+    return ref.rope_and_cache(qkv, positions, cos_sin, slots, k_cache, v_cache, num_heads, num_kv_heads,
+                              head_dim, rot_dim, neox, k_scale, v_scale)
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale, window=-1, softcap=0.0,
+                    k_scale=None, v_scale=None, max_q=None, max_kv=None):
+    if use_native(q):
+        return native().paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale,
+                                        window, softcap, k_scale, v_scale, max_q, max_kv)
+    return ref.paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale, window,
+                               softcap, k_scale, v_scale)
+
+
+def act_and_mul(gate_up, act="silu"):
+    if use_native(gate_up):
+        return native().act_and_mul(gate_up, act)
+    return ref.act_and_mul(gate_up, act)
+
+
+def act_and_mul_quant(gate_up, act="silu"):
+    """``act(gate) * up`` followed by 1x128 e4m3 quantisation: ``(q, scales)``."""
+    if use_native(gate_up):
+        return native().act_and_mul_quant(gate_up, act)
+    return ref.fp8_quant_act(ref.act_and_mul(gate_up, act))
+
+
+def activation(x, act):
+    return ref.activation(x, act)
+
+
+def linear(x, weight, bias=None):
+    if use_native(x) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        return native().gemm_bf16(x, weight, bias)
+    return ref.linear(x, weight, bias)
+
+
+def fp8_quant_act(x, group=128):
+    if use_native(x):
+        return native().fp8_quant_act(x, group)
+    return ref.fp8_quant_act(x, group)
+
+
+def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None):
+    if use_native(xq):
+        return native().gemm_fp8_block(xq, xs, wq, ws, out_dtype, bias)
+    return ref.gemm_fp8_block(xq, xs, wq, ws, out_dtype, bias)
+
+
+def embedding(ids, table):
+    if use_native(table):
+        return native().embedding(ids, table)
+    return ref.embedding(ids, table)
+
+
+def argmax_logprob(logits):
+    if use_native(logits):
+        return native().argmax_logprob(logits)
+    return ref.argmax_logprob(logits)
+
+
+def moe_topk_softmax(router_logits, top_k, renormalize=True):
+    return ref.moe_topk_softmax(router_logits, top_k, renormalize)
+
+
+def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu"):
+    if use_native(x):
+        return native().moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act)
+    return ref.moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act)

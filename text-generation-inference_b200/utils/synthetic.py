@@ -1,0 +1,124 @@
+"""Random-weight checkpoints of a given architecture (tests, smoke run, benchmarks).
+
+``write_llama_checkpoint`` writes an HF-layout directory (``config.json`` + ``model.safetensors``)
+with weights ``N(0, std)`` from a seed and norm weights 1.0 — small models for CPU tests.
+``random_weights_on_device`` fills an *in-memory* checkpoint layer by layer directly on the GPU for
+benchmark-size models that would take too long to write to disk; it returns a ``Weights``-like
+object the decoder loads from (same names, same sharding entry points).
+"""
+from __future__ import annotations
+
+import json
+import os
+from pathlib import Path
+from typing import Dict, Optional
+
+import torch
+
+from .weights import save_safetensors
+
+
+def llama_config(hidden=256, layers=2, heads=4, kv_heads=2, intermediate=688, vocab=32000, eps=1e-5,
+                 theta=10000.0, max_pos=4096, tie=False, model_type="llama", **extra) -> dict:
+    cfg = dict(
+        architectures=["LlamaForCausalLM"], model_type=model_type, hidden_size=hidden, num_hidden_layers=layers,
+        num_attention_heads=heads, num_key_value_heads=kv_heads, intermediate_size=intermediate,
+        vocab_size=vocab, rms_norm_eps=eps, rope_theta=theta, max_position_embeddings=max_pos,
+        hidden_act="silu", tie_word_embeddings=tie, torch_dtype="float32", bos_token_id=1, eos_token_id=2,
+    )
+    cfg.update(extra)
+    return cfg
+
+
+def llama_state_dict(cfg: dict, seed: int = 0, std: float = 0.02, dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    H, L = cfg["hidden_size"], cfg["num_hidden_layers"]
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    D = cfg.get("head_dim") or H // nh
+    I, V = cfg["intermediate_size"], cfg["vocab_size"]
+
+    def rnd(*shape):
+        return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+    sd = {"model.embed_tokens.weight": rnd(V, H), "model.norm.weight": torch.ones(H, dtype=dtype)}
+    if not cfg.get("tie_word_embeddings"):
+        sd["lm_head.weight"] = rnd(V, H)
+    E = cfg.get("num_local_experts", 0)
+    for i in range(L):
+        p = f"model.layers.{i}"
+        sd[f"{p}.input_layernorm.weight"] = torch.ones(H, dtype=dtype)
+        sd[f"{p}.post_attention_layernorm.weight"] = torch.ones(H, dtype=dtype)
+        sd[f"{p}.self_attn.q_proj.weight"] = rnd(nh * D, H)
+        sd[f"{p}.self_attn.k_proj.weight"] = rnd(nkv * D, H)
+        sd[f"{p}.self_attn.v_proj.weight"] = rnd(nkv * D, H)
+        sd[f"{p}.self_attn.o_proj.weight"] = rnd(H, nh * D)
+        if cfg.get("attention_bias") or cfg["model_type"] == "qwen2":
+            sd[f"{p}.self_attn.q_proj.bias"] = rnd(nh * D)
+            sd[f"{p}.self_attn.k_proj.bias"] = rnd(nkv * D)
+            sd[f"{p}.self_attn.v_proj.bias"] = rnd(nkv * D)
+        if E:
+            sd[f"{p}.block_sparse_moe.gate.weight"] = rnd(E, H)
+            for e in range(E):
+                sd[f"{p}.block_sparse_moe.experts.{e}.w1.weight"] = rnd(I, H)
+                sd[f"{p}.block_sparse_moe.experts.{e}.w3.weight"] = rnd(I, H)
+                sd[f"{p}.block_sparse_moe.experts.{e}.w2.weight"] = rnd(H, I)
+        else:
+            sd[f"{p}.mlp.gate_proj.weight"] = rnd(I, H)
+            sd[f"{p}.mlp.up_proj.weight"] = rnd(I, H)
+            sd[f"{p}.mlp.down_proj.weight"] = rnd(H, I)
+    return sd
+
+
+def write_llama_checkpoint(path, cfg: Optional[dict] = None, seed: int = 0, std: float = 0.02,
+                           dtype=torch.float32) -> Path:
+    cfg = cfg or llama_config()
+    p = Path(path)
+    p.mkdir(parents=True, exist_ok=True)
+    (p / "config.json").write_text(json.dumps(cfg, indent=1))
+    save_safetensors(llama_state_dict(cfg, seed, std, dtype), p / "model.safetensors", {"format": "pt"})
+    return p
+
+
+def reference_llama_forward(sd: Dict[str, torch.Tensor], cfg: dict, input_ids: torch.Tensor) -> torch.Tensor:
+    """Plain dense PyTorch Llama forward (no paging, no fusion) over one sequence ``input_ids[T]``.
+
+    Independent oracle for the engine's logits: returns ``[T, vocab]`` in fp32.
+    """
+    H, L = cfg["hidden_size"], cfg["num_hidden_layers"]
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    D = cfg.get("head_dim") or H // nh
+    eps, theta = cfg["rms_norm_eps"], cfg["rope_theta"]
+    T = input_ids.shape[0]
+    x = sd["model.embed_tokens.weight"].float()[input_ids]
+    pos = torch.arange(T, dtype=torch.float32)
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = torch.outer(pos, inv)
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    def norm(v, w):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+
+    def rope(v):
+        a, b = v[..., : D // 2], v[..., D // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+
+    mask = torch.full((T, T), float("-inf")).triu(1)
+    for i in range(L):
+        p = f"model.layers.{i}"
+        h = norm(x, sd[f"{p}.input_layernorm.weight"])
+        q = (h @ sd[f"{p}.self_attn.q_proj.weight"].float().t()).view(T, nh, D)
+        k = (h @ sd[f"{p}.self_attn.k_proj.weight"].float().t()).view(T, nkv, D)
+        v = (h @ sd[f"{p}.self_attn.v_proj.weight"].float().t()).view(T, nkv, D)
+        q, k = rope(q), rope(k)
+        k = k.repeat_interleave(nh // nkv, 1)
+        v = v.repeat_interleave(nh // nkv, 1)
+        att = torch.einsum("thd,shd->hts", q, k) / (D ** 0.5) + mask
+        o = torch.einsum("hts,shd->thd", att.softmax(-1), v).reshape(T, nh * D)
+        x = x + o @ sd[f"{p}.self_attn.o_proj.weight"].float().t()
+        h = norm(x, sd[f"{p}.post_attention_layernorm.weight"])
+        g = h @ sd[f"{p}.mlp.gate_proj.weight"].float().t()
+        u = h @ sd[f"{p}.mlp.up_proj.weight"].float().t()
+        x = x + (torch.nn.functional.silu(g) * u) @ sd[f"{p}.mlp.down_proj.weight"].float().t()
+    x = norm(x, sd["model.norm.weight"])
+    head = sd.get("lm_head.weight", sd["model.embed_tokens.weight"]).float()
+    return x @ head.t()
