@@ -1,0 +1,110 @@
+"""End-to-end engine checks on a GPU: native kernels vs the PyTorch oracle, CUDA-graph decode vs eager."""
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _request(pb, i, n_new, blocks):
+    r = pb.Request(id=i, inputs="")
+    r.parameters.temperature = 1.0
+    r.parameters.top_p = 1.0
+    r.parameters.typical_p = 1.0
+    r.parameters.repetition_penalty = 1.0
+    r.stopping_parameters.max_new_tokens = n_new
+    r.stopping_parameters.ignore_eos_token = True
+    r.blocks.extend(blocks)
+    return r
+
+
+def _build(fp8: bool):
+    from tgi_b200.models.arch import ModelConfig
+    from tgi_b200.models.decoder import CausalDecoder
+    from tgi_b200.models.flash_causal_lm import FlashCausalLM
+    from tgi_b200.utils.quantization import DefaultWeightsLoader, Fp8Loader
+    from tgi_b200.utils.synthetic import SyntheticWeights, llama_config
+    from tgi_b200.utils.tokenizer import ByteTokenizer
+
+    dev = torch.device("cuda", 0)
+    cfg = llama_config(hidden=512, layers=3, heads=8, kv_heads=2, intermediate=1024, vocab=4096, max_pos=1024)
+    w = SyntheticWeights(cfg, dev, torch.bfloat16, fp8_block=fp8, std=0.05)
+    w.weights_loader = Fp8Loader(weight_block_size=[128, 128]) if fp8 else DefaultWeightsLoader()
+    model = CausalDecoder(ModelConfig(cfg), w)
+    runner = FlashCausalLM(model, ByteTokenizer(4096), torch.bfloat16, dev,
+                           kv_cache_dtype=torch.float8_e4m3fn if fp8 else torch.bfloat16)
+    return runner, dev
+
+
+def _generate(runner, dev, prompts, n_new, capture_logits=None):
+    from tgi_b200.models.flash_causal_lm import FlashCausalLMBatch
+    from tgi_b200.proto import generate_v3 as pb
+
+    cursor, reqs = 1, []
+    for i, p in enumerate(prompts):
+        nb = (len(p) + n_new + 15) // 16
+        reqs.append(_request(pb, i, n_new, range(cursor, cursor + nb)))
+        cursor += nb
+    if runner.num_blocks < cursor:
+        runner.init_kv_cache(cursor)
+    batch = FlashCausalLMBatch.from_tokenized(pb.Batch(id=0, requests=reqs, size=len(reqs)), prompts,
+                                              runner.tokenizer, torch.bfloat16, dev)
+    toks = {i: [] for i in range(len(prompts))}
+    while batch is not None:
+        gens, batch, _ = runner.generate_token(batch)
+        for g in gens:
+            toks[g.request_id].extend(g.tokens.token_ids)
+    return toks
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_native_forward_matches_oracle(fp8):
+    from tgi_b200 import ops
+    from tgi_b200.models.decoder import ForwardMeta
+    from tgi_b200.ops import cuda as K
+
+    runner, dev = _build(fp8)
+    runner.init_kv_cache(32)
+    rng = random.Random(0)
+    lens = [45, 100, 17]
+    ids = [rng.randrange(3, 4096) for _ in range(sum(lens))]
+    cu = [0]
+    for l in lens:
+        cu.append(cu[-1] + l)
+    pos, slots, tables, cursor = [], [], [], 1
+    for l in lens:
+        nb = (l + 15) // 16
+        blocks = list(range(cursor, cursor + nb))
+        cursor += nb
+        tables.append(blocks + [0] * (8 - nb))
+        pos.extend(range(l))
+        slots.extend(blocks[j // 16] * 16 + j % 16 for j in range(l))
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    meta = ForwardMeta(t(ids), t(pos), t(slots), t(tables), t(cu), t(lens), max(lens), max(lens),
+                       lm_head_indices=t([c - 1 for c in cu[1:]]))
+    native, _ = runner.model.forward(meta, runner.kv_cache)
+    torch.cuda.synchronize()
+    assert K.check_status(dev) == 0
+    ops.set_force_torch(True)
+    try:
+        runner.init_kv_cache(32)
+        oracle, _ = runner.model.forward(meta, runner.kv_cache)
+    finally:
+        ops.set_force_torch(False)
+    err = (native.float() - oracle.float()).abs().max().item()
+    ref_scale = oracle.float().abs().max().item()
+    assert err <= 0.06 * max(ref_scale, 1.0), f"max |diff| {err} vs logits scale {ref_scale}"
+
+
+def test_cuda_graph_decode_matches_eager():
+    from tgi_b200.models.graphs import DecodeGraphs
+
+    runner, dev = _build(False)
+    rng = random.Random(1)
+    prompts = [[rng.randrange(3, 4096) for _ in range(n)] for n in (20, 33, 64)]
+    eager = _generate(runner, dev, prompts, 8)
+    runner.graphs = DecodeGraphs(runner, 256, buckets=[1, 2, 4])
+    runner.graphs.capture_all()
+    graphed = _generate(runner, dev, prompts, 8)
+    assert graphed == eager

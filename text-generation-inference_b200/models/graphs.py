@@ -1,0 +1,140 @@
+"""CUDA-graph decode: one captured forward per batch-size bucket.
+
+The reference captures the decode forward for batch sizes ``CUDA_GRAPHS`` (default 1,2,4,8,16,32)
+into ``torch.cuda.CUDAGraph`` objects with static input tensors and pads a batch to the next size
+(``models/flash_causal_lm.py:1438-1505`` capture, ``:1792-1888`` replay).  Same idea here with two
+changes: buckets go up to the maximum batch size (256 by default) because a launch-bound decode step
+is where B200 loses most, and all static inputs of a bucket live in ONE int32 buffer that is filled
+by a single host-to-device copy per step.
+
+Padding rows use slot ``-1`` (the RoPE+KV-store kernel skips the write) and a KV length of 0 (the
+attention kernel produces zeros), so they never touch real cache pages.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .decoder import ForwardMeta
+
+DEFAULT_BUCKETS = [1, 2, 4, 8, 16, 32, 64, 96, 128, 192, 256]
+
+
+def configured_buckets() -> List[int]:
+    env = os.environ.get("CUDA_GRAPHS")
+    if env:
+        vals = sorted({int(x) for x in env.split(",") if x.strip() and int(x) > 0})
+        return vals
+    return list(DEFAULT_BUCKETS)
+
+
+class _Bucket:
+    def __init__(self, runner, bs: int, max_blocks: int, pool):
+        dev = runner.device
+        self.bs, self.max_blocks = bs, max_blocks
+        # layout of the static int32 buffer (every segment starts on a 16-byte boundary)
+        seg = lambda n: (n + 3) & ~3
+        self.off_ids = 0
+        self.off_pos = self.off_ids + seg(bs)
+        self.off_slots = self.off_pos + seg(bs)
+        self.off_cu = self.off_slots + seg(bs)
+        self.off_kv = self.off_cu + seg(bs + 1)
+        self.off_bt = self.off_kv + seg(bs)
+        self.total = self.off_bt + seg(bs * max_blocks)
+        self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(self.total, dtype=torch.int32, device=dev)
+        self.host_np[self.off_cu:self.off_cu + bs + 1] = np.arange(bs + 1, dtype=np.int32)
+        self.host_np[self.off_slots:self.off_slots + bs] = -1
+        self.dev.copy_(self.host)
+        d = self.dev
+        self.meta = ForwardMeta(
+            input_ids=d[self.off_ids:self.off_ids + bs],
+            positions=d[self.off_pos:self.off_pos + bs],
+            slots=d[self.off_slots:self.off_slots + bs],
+            cu_seqlens_q=d[self.off_cu:self.off_cu + bs + 1],
+            kv_lens=d[self.off_kv:self.off_kv + bs],
+            block_tables=d[self.off_bt:self.off_bt + bs * max_blocks].view(bs, max_blocks),
+            max_q=1,
+            max_kv=runner_max_kv(runner),
+            lm_head_indices=None,
+        )
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+
+def runner_max_kv(runner) -> int:
+    return int(getattr(runner, "_graph_max_total_tokens", 4096))
+
+
+class DecodeGraphs:
+    def __init__(self, runner, max_total_tokens: int, buckets: Optional[List[int]] = None):
+        self.runner = runner
+        self.max_total_tokens = int(max_total_tokens)
+        runner._graph_max_total_tokens = self.max_total_tokens
+        self.max_blocks = math.ceil(self.max_total_tokens / runner.block_size)
+        self.sizes = buckets or configured_buckets()
+        self.buckets: Dict[int, _Bucket] = {}
+        self.pool = None
+
+    def capture_all(self):
+        for bs in sorted(self.sizes, reverse=True):
+            self.capture(bs)
+
+    def capture(self, bs: int):
+        r = self.runner
+        b = _Bucket(r, bs, self.max_blocks, self.pool)
+        # warm-up run outside capture: lazy kernel attributes and persistent scratch get set up here
+        torch.cuda.synchronize(r.device)
+        r.model.forward(b.meta, r.kv_cache)
+        torch.cuda.synchronize(r.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self.pool):
+            logits, _ = r.model.forward(b.meta, r.kv_cache)
+        if self.pool is None:
+            self.pool = g.pool()
+        torch.cuda.synchronize(r.device)
+        b.graph, b.logits = g, logits
+        self.buckets[bs] = b
+
+    def supports(self, batch) -> bool:
+        n = len(batch)
+        if not self.buckets or n > max(self.buckets):
+            return False
+        for s in batch.seqs:
+            if len(s.blocks) > self.max_blocks or len(s.ids) > self.max_total_tokens:
+                return False
+        return True
+
+    def run(self, batch, counts: List[int]):
+        seqs = batch.seqs
+        n = len(seqs)
+        bs = min(k for k in self.buckets if k >= n)
+        b = self.buckets[bs]
+        h = b.host_np
+        ids = h[b.off_ids:b.off_ids + bs]
+        pos = h[b.off_pos:b.off_pos + bs]
+        slots = h[b.off_slots:b.off_slots + bs]
+        kv = h[b.off_kv:b.off_kv + bs]
+        bt = h[b.off_bt:b.off_bt + bs * b.max_blocks].reshape(bs, b.max_blocks)
+        for i, s in enumerate(seqs):
+            p = len(s.ids) - 1
+            ids[i] = s.ids[-1]
+            pos[i] = p
+            slots[i] = s.slots[p]
+            kv[i] = p + 1
+            nb = len(s.blocks)
+            bt[i, :nb] = s.blocks
+        if n < bs:
+            ids[n:] = 0
+            pos[n:] = 0
+            slots[n:] = -1
+            kv[n:] = 0
+        b.dev.copy_(b.host, non_blocking=True)
+        b.graph.replay()
+        row_owner = [(i, 0) for i in range(n)]
+        return b.logits[:n], row_owner

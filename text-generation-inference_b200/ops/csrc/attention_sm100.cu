@@ -1,0 +1,647 @@
+// Paged causal attention for ragged batches (sm_100a build): prefill / chunked prefill with a cached
+// prefix, and split-KV decode.  KV pages are [num_blocks, block_size, Hkv, D] in bf16 or e4m3 (per
+// KV-head scale folded into the softmax scale and the output).
+//
+// Replaces, in the reference, flashinfer `BatchPrefillWithPagedKVCache` / FA2 `varlen_fwd`
+// (layers/attention/cuda.py:244-296) and flashinfer `BatchDecodeWithPagedKVCache` /
+// `paged_attention_v1/v2` (layers/attention/cuda.py:73-185).
+//
+// Structure: flash-attention style online softmax.  A CTA of 4 warps owns 64 query rows of one
+// head (prefill) or the <=16 query heads that share one KV head (decode, GQA-packed so each KV
+// byte is read once); K/V tiles of 64 tokens are gathered page by page with cp.async into a
+// double-buffered, XOR-swizzled shared-memory tile and multiplied on the tensor cores with
+// m16n8k16 fragments (bf16 inputs for bf16 pages; e4m3 pages are widened to fp16 in shared memory,
+// which is exact).  Decode splits the KV range over CTAs and a second kernel merges the partial
+// (max, sum, output) triples.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int kTile = 64;        // KV tokens per tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;  // src-size 0 => the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+template <bool F16>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if (F16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pack2(float x, float y) {
+  if (F16) {
+    __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// 16-bit tile [rows][D], 16-byte chunks XOR-swizzled by the row index
+template <int D>
+__device__ __forceinline__ int swz(int row, int chunk) {
+  return row * D + ((chunk ^ (row & 7)) << 3);   // element offset
+}
+
+struct Params {
+  const __nv_bfloat16* q;       // [T, Hq, D]
+  const void* k_cache;          // [blocks, bs, Hkv, D]
+  const void* v_cache;
+  const int* block_tables;      // [B, max_blocks]
+  const int* cu_seqlens_q;      // [B+1]
+  const int* kv_lens;           // [B]
+  const float* k_scale;         // [Hkv] or null
+  const float* v_scale;
+  __nv_bfloat16* out;           // [T, Hq, D]
+  float* part_o;                // decode partials [B, Hq, nsplit, D]
+  float* part_ml;               // [B, Hq, nsplit, 2]
+  int max_blocks, block_size, Hq, Hkv, num_blocks;
+  float scale, softcap;
+  int window;
+  int nsplit;
+};
+
+// Gather one 64-token K or V tile (tokens t0..t0+63 of sequence b, KV head kvh) into shared memory.
+// bf16 pages land directly in the swizzled compute tile; e4m3 pages land in a raw staging tile.
+template <int D, bool FP8>
+__device__ __forceinline__ void load_tile(const Params& p, const void* cache, int b, int kvh, int t0, int L,
+                                          void* dst) {
+  constexpr int EB = FP8 ? 1 : 2;
+  constexpr int CPR = D * EB / 16;                 // 16-byte chunks per token row
+  constexpr int TOTAL = kTile * CPR;
+  const char* base = static_cast<const char*>(cache);
+  for (int c = threadIdx.x; c < TOTAL; c += blockDim.x) {
+    const int row = c / CPR, cc = c % CPR;
+    const int t = t0 + row;
+    bool valid = t < L;
+    const char* src = base;
+    if (valid) {
+      const int blk = p.block_tables[static_cast<size_t>(b) * p.max_blocks + t / p.block_size];
+      valid = blk >= 0 && blk < p.num_blocks;     // self-check on the block table
+      const size_t slot = static_cast<size_t>(blk) * p.block_size + t % p.block_size;
+      if (valid) src = base + ((slot * p.Hkv + kvh) * D) * EB + cc * 16;
+    }
+    char* d;
+    if (FP8) d = static_cast<char*>(dst) + row * D + cc * 16;                       // raw, unswizzled
+    else d = reinterpret_cast<char*>(static_cast<uint16_t*>(dst) + swz<D>(row, cc));
+    cp_async16(d, src, valid);
+  }
+}
+
+// widen a raw e4m3 tile [64][D] to the swizzled fp16 compute tile
+template <int D>
+__device__ __forceinline__ void widen_tile(const uint8_t* raw, __half* dst) {
+  constexpr int CPR = D / 16;
+  for (int c = threadIdx.x; c < kTile * CPR; c += blockDim.x) {
+    const int row = c / CPR, cc = c % CPR;
+    const uint4 v = *reinterpret_cast<const uint4*>(raw + row * D + cc * 16);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] & 0xFFFF), __NV_E4M3);
+      __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] >> 16), __NV_E4M3);
+      o[2 * i] = static_cast<uint32_t>(lo.x) | (static_cast<uint32_t>(lo.y) << 16);
+      o[2 * i + 1] = static_cast<uint32_t>(hi.x) | (static_cast<uint32_t>(hi.y) << 16);
+    }
+    *reinterpret_cast<uint4*>(dst + swz<D>(row, 2 * cc)) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(dst + swz<D>(row, 2 * cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+// One warp: S[16 x NT*8] = Q[16 x D] * K[tokens x D]^T for token n-tiles nt0 .. nt0+NT-1 (NT even).
+template <int D, int NT, bool F16>
+__device__ __forceinline__ void qk_warp(const uint32_t (&qf)[D / 16][4], const uint16_t* sK, int nt0,
+                                        float (&s)[NT][4]) {
+  const int lane = threadIdx.x & 31;
+  const int mi = lane >> 3;
+#pragma unroll
+  for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      const int tok = (nt0 + 2 * np) * 8 + (lane & 7) + (mi >> 1) * 8;
+      uint32_t b[4];
+      ldsm_x4(b, sK + swz<D>(tok, ks * 2 + (mi & 1)));
+      mma16816<F16>(s[2 * np], qf[ks], b[0], b[1]);
+      mma16816<F16>(s[2 * np + 1], qf[ks], b[2], b[3]);
+    }
+  }
+}
+
+// One warp: O[16 x D] += P[16 x NT*8] * V[tokens x D]
+template <int D, int NT, bool F16>
+__device__ __forceinline__ void pv_warp(const float (&s)[NT][4], const uint16_t* sV, int nt0, float (&o)[D / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  const int mi = lane >> 3;
+#pragma unroll
+  for (int kt = 0; kt < NT / 2; ++kt) {
+    uint32_t a[4];
+    a[0] = pack2<F16>(s[2 * kt][0], s[2 * kt][1]);
+    a[1] = pack2<F16>(s[2 * kt][2], s[2 * kt][3]);
+    a[2] = pack2<F16>(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+    a[3] = pack2<F16>(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+    const int tok = (nt0 + 2 * kt) * 8 + (lane & 7) + (mi & 1) * 8;
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+      uint32_t b[4];
+      ldsm_x4_t(b, sV + swz<D>(tok, dp * 2 + (mi >> 1)));
+      mma16816<F16>(o[2 * dp], a, b[0], b[1]);
+      mma16816<F16>(o[2 * dp + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Online-softmax update of one warp's 16 rows over NT n-tiles.  pos0/pos1: absolute positions of the
+// thread's two rows (lane/4 and lane/4+8); tbase: first token of n-tile 0.
+template <int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&alpha)[2],
+                                               int tbase, int pos0, int pos1, int L, int window, float scale_log2,
+                                               float softcap, float raw_scale) {
+  const int lane = threadIdx.x & 31;
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int t = tbase + i * 8 + (lane & 3) * 2 + (e & 1);
+      const int pos = (e < 2) ? pos0 : pos1;
+      float v = s[i][e];
+      if (softcap > 0.f) v = softcap * tanhf(v * raw_scale / softcap) * kLog2e;
+      else v = v * scale_log2;
+      const bool ok = t <= pos && t < L && (window <= 0 || t > pos - window);
+      v = ok ? v : -INFINITY;
+      s[i][e] = v;
+      mx[e >> 1] = fmaxf(mx[e >> 1], v);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float mn = fmaxf(m[r], mx[r]);
+    alpha[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - mn);
+    m[r] = mn;
+  }
+  float rs[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float mm = m[e >> 1];
+      const float pv = (mm == -INFINITY) ? 0.f : exp2f(s[i][e] - mm);
+      s[i][e] = pv;
+      rs[e >> 1] += pv;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+    rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+    l[r] = l[r] * alpha[r] + rs[r];
+  }
+}
+
+template <int D, bool FP8>
+struct Smem {
+  static constexpr int kTileElems = kTile * D;                      // 16-bit elements per compute tile
+  static constexpr int kQBytes = kTile * D * 2;
+  // bf16 pages: 2 stages of compute tiles.  e4m3 pages: 2 stages raw + 1 compute tile.
+  static constexpr int kKVBytes = FP8 ? (2 * kTile * D + kTile * D * 2) : (2 * kTile * D * 2);
+  static constexpr int kBytes = kQBytes + 2 * kKVBytes;
+};
+
+// ------------------------------------------------------------------------------------------------
+// prefill: grid (q tiles, Hq, B), block 128
+// ------------------------------------------------------------------------------------------------
+template <int D, bool FP8>
+__global__ void __launch_bounds__(128)
+prefill_kernel(Params p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  using S = Smem<D, FP8>;
+  uint16_t* sQ = reinterpret_cast<uint16_t*>(smem);
+  uint8_t* kv = smem + S::kQBytes;
+  // layout after Q: [K region][V region]; each region = stages (raw for FP8) + compute tile (FP8)
+  uint8_t* kreg = kv;
+  uint8_t* vreg = kv + S::kKVBytes;
+
+  const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+  const int q_begin = p.cu_seqlens_q[b], n = p.cu_seqlens_q[b + 1] - q_begin;
+  if (qt * kTile >= n) return;
+  const int L = p.kv_lens[b];
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_base = qt * kTile;                         // first query row of this CTA inside the chunk
+  const int pos_first = L - n + row_base;
+  const int pos_last = min(L - 1, pos_first + kTile - 1);
+  int t_lo = 0;
+  if (p.window > 0) t_lo = max(0, pos_first - p.window + 1) / kTile * kTile;
+  const int t_hi = pos_last + 1;                           // exclusive
+  const int ntiles = (t_hi - t_lo + kTile - 1) / kTile;
+
+  // ---- Q tile -> shared (bf16, or fp16 for e4m3 pages) ----
+  for (int c = threadIdx.x; c < kTile * (D / 8); c += blockDim.x) {
+    const int row = c / (D / 8), cc = c % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row_base + row < n)
+      v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(q_begin + row_base + row) * p.Hq + h) * D + cc * 8);
+    if (FP8) {
+      const __nv_bfloat162* bv = reinterpret_cast<const __nv_bfloat162*>(&v);
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(bv[i]);
+        o[i] = pack2<true>(f.x, f.y);
+      }
+      v = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    *reinterpret_cast<uint4*>(sQ + swz<D>(row, cc)) = v;
+  }
+  auto stage_ptr = [&](uint8_t* region, int stg) -> void* {
+    return FP8 ? static_cast<void*>(region + stg * kTile * D) : static_cast<void*>(region + stg * kTile * D * 2);
+  };
+  // first tile
+  load_tile<D, FP8>(p, p.k_cache, b, kvh, t_lo, L, stage_ptr(kreg, 0));
+  load_tile<D, FP8>(p, p.v_cache, b, kvh, t_lo, L, stage_ptr(vreg, 0));
+  cp_async_commit();
+  __syncthreads();
+
+  uint32_t qf[D / 16][4];
+  {
+    const int mi = lane >> 3;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+      ldsm_x4(qf[ks], sQ + swz<D>(warp * 16 + (lane & 7) + (mi & 1) * 8, ks * 2 + (mi >> 1)));
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const float ks = p.k_scale ? p.k_scale[kvh] : 1.f;
+  const float vs = p.v_scale ? p.v_scale[kvh] : 1.f;
+  const float raw_scale = p.scale * (FP8 ? ks : 1.f);
+  const float scale_log2 = raw_scale * kLog2e;
+  const int pos0 = pos_first + warp * 16 + (lane >> 2);
+  const int pos1 = pos0 + 8;
+
+  for (int j = 0; j < ntiles; ++j) {
+    const int stg = j & 1;
+    if (j + 1 < ntiles) {
+      load_tile<D, FP8>(p, p.k_cache, b, kvh, t_lo + (j + 1) * kTile, L, stage_ptr(kreg, stg ^ 1));
+      load_tile<D, FP8>(p, p.v_cache, b, kvh, t_lo + (j + 1) * kTile, L, stage_ptr(vreg, stg ^ 1));
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint16_t* cK;
+    const uint16_t* cV;
+    if (FP8) {
+      __half* ck = reinterpret_cast<__half*>(kreg + 2 * kTile * D);
+      __half* cv = reinterpret_cast<__half*>(vreg + 2 * kTile * D);
+      widen_tile<D>(kreg + stg * kTile * D, ck);
+      widen_tile<D>(vreg + stg * kTile * D, cv);
+      __syncthreads();
+      cK = reinterpret_cast<const uint16_t*>(ck);
+      cV = reinterpret_cast<const uint16_t*>(cv);
+    } else {
+      cK = reinterpret_cast<const uint16_t*>(kreg + stg * kTile * D * 2);
+      cV = reinterpret_cast<const uint16_t*>(vreg + stg * kTile * D * 2);
+    }
+    float s[8][4];
+    qk_warp<D, 8, FP8>(qf, cK, 0, s);
+    float alpha[2];
+    softmax_update<8>(s, m, l, alpha, t_lo + j * kTile, pos0, pos1, L, p.window, scale_log2, p.softcap, raw_scale);
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+    pv_warp<D, 8, FP8>(s, cV, 0, o);
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  const float inv0 = l[0] > 0.f ? (FP8 ? vs : 1.f) / l[0] : 0.f;
+  const float inv1 = l[1] > 0.f ? (FP8 ? vs : 1.f) / l[1] : 0.f;
+  const int r0 = row_base + warp * 16 + (lane >> 2), r1 = r0 + 8;
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    const int col = i * 8 + (lane & 3) * 2;
+    if (r0 < n)
+      *reinterpret_cast<__nv_bfloat162*>(p.out + (static_cast<size_t>(q_begin + r0) * p.Hq + h) * D + col) =
+          __floats2bfloat162_rn(o[i][0] * inv0, o[i][1] * inv0);
+    if (r1 < n)
+      *reinterpret_cast<__nv_bfloat162*>(p.out + (static_cast<size_t>(q_begin + r1) * p.Hq + h) * D + col) =
+          __floats2bfloat162_rn(o[i][2] * inv1, o[i][3] * inv1);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode: one query token per sequence.  grid (B, Hkv * gchunks, nsplit), block 128.
+// Rows of the MMA tile are the query heads sharing KV head kvh (up to 16 per CTA).  Warp w owns
+// tokens [16w, 16w+16) of every 64-token tile; the four warps' partial results are merged at the end.
+// ------------------------------------------------------------------------------------------------
+template <int D, bool FP8>
+__global__ void __launch_bounds__(128)
+decode_kernel(Params p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  using S = Smem<D, FP8>;
+  uint16_t* sQ = reinterpret_cast<uint16_t*>(smem);
+  uint8_t* kreg = smem + S::kQBytes;
+  uint8_t* vreg = kreg + S::kKVBytes;
+
+  const int G = p.Hq / p.Hkv;
+  const int gchunks = (G + 15) / 16;
+  const int b = blockIdx.x;
+  const int kvh = blockIdx.y / gchunks, gc = blockIdx.y % gchunks;
+  const int split = blockIdx.z;
+  const int h0 = kvh * G + gc * 16;
+  const int rows = min(16, G - gc * 16);
+  const int L = p.kv_lens[b];
+  const int q_row = p.cu_seqlens_q[b];
+  if (p.cu_seqlens_q[b + 1] == q_row) return;   // sequence contributes no query this step
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = L - 1;
+  int t_lo = 0;
+  if (p.window > 0) t_lo = max(0, pos - p.window + 1) / kTile * kTile;
+  const int tiles_total = (L - t_lo + kTile - 1) / kTile;
+  const int tiles_per = (tiles_total + p.nsplit - 1) / p.nsplit;
+  const int tile_begin = split * tiles_per;
+  const int tile_end = min(tiles_total, tile_begin + tiles_per);
+  const int ntiles = max(0, tile_end - tile_begin);
+
+  for (int c = threadIdx.x; c < 16 * (D / 8); c += blockDim.x) {
+    const int row = c / (D / 8), cc = c % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < rows) v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(q_row) * p.Hq + h0 + row) * D + cc * 8);
+    if (FP8) {
+      const __nv_bfloat162* bv = reinterpret_cast<const __nv_bfloat162*>(&v);
+      uint32_t o4[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(bv[i]);
+        o4[i] = pack2<true>(f.x, f.y);
+      }
+      v = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+    }
+    *reinterpret_cast<uint4*>(sQ + swz<D>(row, cc)) = v;
+  }
+  auto stage_ptr = [&](uint8_t* region, int stg) -> void* {
+    return FP8 ? static_cast<void*>(region + stg * kTile * D) : static_cast<void*>(region + stg * kTile * D * 2);
+  };
+  if (ntiles > 0) {
+    load_tile<D, FP8>(p, p.k_cache, b, kvh, t_lo + tile_begin * kTile, L, stage_ptr(kreg, 0));
+    load_tile<D, FP8>(p, p.v_cache, b, kvh, t_lo + tile_begin * kTile, L, stage_ptr(vreg, 0));
+  }
+  cp_async_commit();
+  __syncthreads();
+
+  uint32_t qf[D / 16][4];
+  {
+    const int mi = lane >> 3;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) ldsm_x4(qf[ks], sQ + swz<D>((lane & 7) + (mi & 1) * 8, ks * 2 + (mi >> 1)));
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const float ksc = p.k_scale ? p.k_scale[kvh] : 1.f;
+  const float vsc = p.v_scale ? p.v_scale[kvh] : 1.f;
+  const float raw_scale = p.scale * (FP8 ? ksc : 1.f);
+  const float scale_log2 = raw_scale * kLog2e;
+
+  for (int j = 0; j < ntiles; ++j) {
+    const int stg = j & 1;
+    if (j + 1 < ntiles) {
+      load_tile<D, FP8>(p, p.k_cache, b, kvh, t_lo + (tile_begin + j + 1) * kTile, L, stage_ptr(kreg, stg ^ 1));
+      load_tile<D, FP8>(p, p.v_cache, b, kvh, t_lo + (tile_begin + j + 1) * kTile, L, stage_ptr(vreg, stg ^ 1));
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint16_t* cK;
+    const uint16_t* cV;
+    if (FP8) {
+      __half* ck = reinterpret_cast<__half*>(kreg + 2 * kTile * D);
+      __half* cv = reinterpret_cast<__half*>(vreg + 2 * kTile * D);
+      widen_tile<D>(kreg + stg * kTile * D, ck);
+      widen_tile<D>(vreg + stg * kTile * D, cv);
+      __syncthreads();
+      cK = reinterpret_cast<const uint16_t*>(ck);
+      cV = reinterpret_cast<const uint16_t*>(cv);
+    } else {
+      cK = reinterpret_cast<const uint16_t*>(kreg + stg * kTile * D * 2);
+      cV = reinterpret_cast<const uint16_t*>(vreg + stg * kTile * D * 2);
+    }
+    float s[2][4];
+    qk_warp<D, 2, FP8>(qf, cK, warp * 2, s);
+    float alpha[2];
+    // every row (= head) sits at the same position `pos`
+    softmax_update<2>(s, m, l, alpha, t_lo + (tile_begin + j) * kTile + warp * 16, pos, pos, L, p.window, scale_log2,
+                      p.softcap, raw_scale);
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+    pv_warp<D, 2, FP8>(s, cV, warp * 2, o);
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps through shared memory (reuse the K region) ----
+  float* mO = reinterpret_cast<float*>(kreg);                // [4][16][D]
+  float* mML = reinterpret_cast<float*>(vreg);               // [4][16][2]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int col = i * 8 + (lane & 3) * 2;
+      mO[(warp * 16 + r0) * D + col] = o[i][0];
+      mO[(warp * 16 + r0) * D + col + 1] = o[i][1];
+      mO[(warp * 16 + r1) * D + col] = o[i][2];
+      mO[(warp * 16 + r1) * D + col + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      mML[(warp * 16 + r0) * 2] = m[0];
+      mML[(warp * 16 + r0) * 2 + 1] = l[0];
+      mML[(warp * 16 + r1) * 2] = m[1];
+      mML[(warp * 16 + r1) * 2 + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
+    const int row = idx / D, col = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, mML[(w * 16 + row) * 2]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mML[(w * 16 + row) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+      acc += mO[(w * 16 + row) * D + col] * f;
+      ll += mML[(w * 16 + row) * 2 + 1] * f;
+    }
+    const int h = h0 + row;
+    if (p.nsplit == 1) {
+      const float inv = ll > 0.f ? (FP8 ? vsc : 1.f) / ll : 0.f;
+      p.out[(static_cast<size_t>(q_row) * p.Hq + h) * D + col] = __float2bfloat16(acc * inv);
+    } else {
+      const size_t pi = (static_cast<size_t>(b) * p.Hq + h) * p.nsplit + split;
+      p.part_o[pi * D + col] = ll > 0.f ? acc * ((FP8 ? vsc : 1.f) / ll) : 0.f;
+      if (col == 0) {
+        p.part_ml[pi * 2] = mm;
+        p.part_ml[pi * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+// merge split partials: grid (B, Hq), block D
+__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const int* __restrict__ cu_seqlens_q, __nv_bfloat16* __restrict__ out, int Hq,
+                                    int D, int nsplit) {
+  const int b = blockIdx.x, h = blockIdx.y;
+  if (cu_seqlens_q[b + 1] == cu_seqlens_q[b]) return;
+  const size_t base = (static_cast<size_t>(b) * Hq + h) * nsplit;
+  float mm = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) {
+    const float l = part_ml[(base + s) * 2 + 1];
+    if (l > 0.f) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+  }
+  for (int col = threadIdx.x; col < D; col += blockDim.x) {
+    float acc = 0.f, wsum = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float l = part_ml[(base + s) * 2 + 1];
+      if (l > 0.f) {
+        const float w = l * exp2f(part_ml[(base + s) * 2] - mm);
+        acc += part_o[(base + s) * D + col] * w;
+        wsum += w;
+      }
+    }
+    out[(static_cast<size_t>(cu_seqlens_q[b]) * Hq + h) * D + col] = __float2bfloat16(wsum > 0.f ? acc / wsum : 0.f);
+  }
+}
+
+template <int D, bool FP8>
+int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
+  using S = Smem<D, FP8>;
+  const int smem = S::kBytes;
+  if (max_q > 1) {
+    auto k = prefill_kernel<D, FP8>;
+    static bool set = false;
+    if (!set) {
+      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+      set = true;
+    }
+    dim3 grid((max_q + kTile - 1) / kTile, p.Hq, B);
+    k<<<grid, 128, smem, stream>>>(p);
+  } else {
+    auto k = decode_kernel<D, FP8>;
+    static bool set = false;
+    if (!set) {
+      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+      set = true;
+    }
+    const int G = p.Hq / p.Hkv;
+    dim3 grid(B, p.Hkv * ((G + 15) / 16), p.nsplit);
+    k<<<grid, 128, smem, stream>>>(p);
+    if (p.nsplit > 1) {
+      dim3 g2(B, p.Hq);
+      decode_merge_kernel<<<g2, D < 128 ? D : 128, 0, stream>>>(p.part_o, p.part_ml, p.cu_seqlens_q, p.out, p.Hq, D,
+                                                                p.nsplit);
+    }
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Split count for a decode launch: enough CTAs for two waves over the SMs, bounded by the tiles a
+// sequence of max_kv tokens has.
+int tgi_attn_decode_splits(int B, int Hkv, int G, int max_kv, int sm_count) {
+  const int ctas = B * Hkv * ((G + 15) / 16);
+  int want = (2 * sm_count + ctas - 1) / ctas;
+  const int tiles = (max_kv + kTile - 1) / kTile;
+  if (want > tiles) want = tiles;
+  if (want > 64) want = 64;
+  return want < 1 ? 1 : want;
+}
+
+int tgi_paged_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                        const int* cu_seqlens_q, const int* kv_lens, const float* k_scale, const float* v_scale,
+                        void* out, float* part_o, float* part_ml, int B, int max_q, int max_blocks, int block_size,
+                        int num_blocks, int Hq, int Hkv, int D, float scale, float softcap, int window, int nsplit,
+                        int fp8_kv, cudaStream_t stream) {
+  if (B <= 0 || max_q <= 0) return 0;
+  if (Hq % Hkv != 0) return -10;
+  Params p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.block_tables = block_tables;
+  p.cu_seqlens_q = cu_seqlens_q;
+  p.kv_lens = kv_lens;
+  p.k_scale = k_scale;
+  p.v_scale = v_scale;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.part_o = part_o;
+  p.part_ml = part_ml;
+  p.max_blocks = max_blocks;
+  p.block_size = block_size;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.num_blocks = num_blocks;
+  p.scale = scale;
+  p.softcap = softcap;
+  p.window = window;
+  p.nsplit = (max_q > 1 || nsplit < 1) ? 1 : nsplit;
+  if (p.nsplit > 1 && (part_o == nullptr || part_ml == nullptr)) return -11;
+  switch (D) {
+    case 64: return fp8_kv ? launch<64, true>(p, B, max_q, stream) : launch<64, false>(p, B, max_q, stream);
+    case 128: return fp8_kv ? launch<128, true>(p, B, max_q, stream) : launch<128, false>(p, B, max_q, stream);
+    case 256: return fp8_kv ? launch<256, true>(p, B, max_q, stream) : launch<256, false>(p, B, max_q, stream);
+    default: return -12;
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,479 @@
+// Bandwidth-bound fused kernels of the decoder layer (sm_100a):
+//   rms_norm / layer_norm with residual add, optional 1x128 e4m3 quantisation of the output
+//   RoPE + paged KV-cache store (bf16 or e4m3 with per-head scale)
+//   act(gate) * up, optional quantisation
+//   dynamic 1x128 e4m3 activation quantisation
+//   embedding gather, greedy argmax + log-probability
+//
+// They replace, in the reference: `dropout_layer_norm.dropout_add_ln_fwd` (layers/layernorm.py:161-187),
+// `rotary.apply_rotary` x2 + `KVCache.store` (layers/rotary.py:54-64, layers/attention/kv_cache.py:184-240),
+// the separate SiLU and multiply torch ops (flash_llama_modeling.py:400-404), `scaled_fp8_quant` /
+// `per_token_group_quant_fp8` (layers/fp8.py:149-159, 508-526), `F.embedding`, and the
+// log_softmax + argmax pair of the greedy sampler (utils/tokens.py).
+//
+// Activation scales are written K-block major, `scale_t[kb * pitch + token]`, the layout the
+// block-scaled GEMM fetches with one TMA box per K block.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr float kFp8Max = 448.f;
+
+struct __align__(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const bf16x8& p, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
+  bf16x8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x + 31) / 32) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+// 8 fp32 -> 8 e4m3 (two 32-bit words)
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float scale) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float q = fminf(fmaxf(f[4 * h + i] / scale, -kFp8Max), kFp8Max);
+      acc |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    }
+    w[h] = acc;
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+// amax over the 16 lanes that share one 128-element group (8 elements per lane)
+__device__ __forceinline__ float group16_max(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// residual add + RMSNorm / LayerNorm (+ quant).  One CTA per token; VPT 16-byte vectors per thread.
+// ------------------------------------------------------------------------------------------------
+template <int VPT, bool LAYER, bool QUANT>
+__global__ void __launch_bounds__(1024)
+norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+            const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ bias,
+            __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ res_out, uint8_t* __restrict__ q_out,
+            float* __restrict__ scale_t, int scale_pitch, int H, float eps, float w_offset) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const size_t base = static_cast<size_t>(row) * H;
+  const int nvec = H / 8;
+  float s[VPT][8];
+  float sum = 0.f, sumsq = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float a[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(x + base + v * 8), a);
+      if (residual != nullptr) {
+        float r[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(residual + base + v * 8), r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = round_bf16(a[j] + r[j]);
+      }
+      if (res_out != nullptr) *reinterpret_cast<bf16x8*>(res_out + base + v * 8) = pack8(a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s[i][j] = a[j];
+        sum += a[j];
+        sumsq += a[j] * a[j];
+      }
+    }
+  }
+  float mean = 0.f;
+  float var;
+  if (LAYER) {
+    mean = block_sum(sum, red) / H;
+    float d = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d += (s[i][j] - mean) * (s[i][j] - mean);
+      }
+    }
+    var = block_sum(d, red) / H;
+  } else {
+    var = block_sum(sumsq, red) / H;
+  }
+  const float rstd = rsqrtf(var + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    const bool active = v < nvec;
+    float y[8];
+    if (active) {
+      float w[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(weight + v * 8), w);
+      float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (LAYER && bias != nullptr) unpack8(*reinterpret_cast<const bf16x8*>(bias + v * 8), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = round_bf16((s[i][j] - mean) * rstd * (w[j] + w_offset) + b[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = 0.f;
+    }
+    if (QUANT) {
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
+      amax = group16_max(amax);
+      const float scale = fmaxf(amax, 1e-12f) / kFp8Max;
+      if (active) {
+        *reinterpret_cast<uint2*>(q_out + base + v * 8) = quant8(y, scale);
+        if ((v & 15) == 0) scale_t[static_cast<size_t>(v >> 4) * scale_pitch + row] = scale;
+      }
+    } else if (active) {
+      *reinterpret_cast<bf16x8*>(out + base + v * 8) = pack8(y);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// act(gate) * up (+ quant): in [T, 2I] -> out [T, I]
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float act_fn(float x, int act) {
+  switch (act) {
+    case 0: return x / (1.f + __expf(-x));                                              // silu
+    case 1: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));                   // gelu (erf)
+    case 2: {                                                                           // gelu (tanh)
+      const float k = 0.7978845608028654f;
+      return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+    }
+    case 3: return fmaxf(x, 0.f);                                                       // relu
+    default: return x / (1.f + __expf(-1.702f * x));                                    // quick gelu
+  }
+}
+
+template <bool QUANT>
+__global__ void __launch_bounds__(256)
+act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ q_out,
+               float* __restrict__ scale_t, int scale_pitch, int I, int act) {
+  const int row = blockIdx.y;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nvec = I / 8;
+  const bool active = v < nvec;
+  float y[8];
+  if (active) {
+    float g[8], u[8];
+    const __nv_bfloat16* p = in + static_cast<size_t>(row) * 2 * I;
+    unpack8(*reinterpret_cast<const bf16x8*>(p + v * 8), g);
+    unpack8(*reinterpret_cast<const bf16x8*>(p + I + v * 8), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = round_bf16(act_fn(g[j], act) * u[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = 0.f;
+  }
+  if (QUANT) {
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
+    amax = group16_max(amax);
+    const float scale = fmaxf(amax, 1e-12f) / kFp8Max;
+    if (active) {
+      *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * I + v * 8) = quant8(y, scale);
+      if ((v & 15) == 0) scale_t[static_cast<size_t>(v >> 4) * scale_pitch + row] = scale;
+    }
+  } else if (active) {
+    *reinterpret_cast<bf16x8*>(out + static_cast<size_t>(row) * I + v * 8) = pack8(y);
+  }
+}
+
+// dynamic 1x128 quantisation of x[T, K]
+__global__ void __launch_bounds__(256)
+quant_act_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q_out, float* __restrict__ scale_t,
+                 int scale_pitch, int K) {
+  const int row = blockIdx.y;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool active = v < K / 8;
+  float y[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (active) unpack8(*reinterpret_cast<const bf16x8*>(x + static_cast<size_t>(row) * K + v * 8), y);
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
+  amax = group16_max(amax);
+  const float scale = fmaxf(amax, 1e-12f) / kFp8Max;
+  if (active) {
+    *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * K + v * 8) = quant8(y, scale);
+    if ((v & 15) == 0) scale_t[static_cast<size_t>(v >> 4) * scale_pitch + row] = scale;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// RoPE + KV store.  grid = tokens, block = 256 threads looping over (head, pair) work items.
+// qkv[T, (Hq + 2 Hkv) * D] -> q_out[T, Hq, D] (rotated), k/v written at `slots` of the paged cache.
+// ------------------------------------------------------------------------------------------------
+template <bool FP8_CACHE>
+__global__ void __launch_bounds__(256)
+rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                  const float* __restrict__ cos_sin, const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
+                  void* __restrict__ k_cache, void* __restrict__ v_cache, const float* __restrict__ k_scale,
+                  const float* __restrict__ v_scale, int Hq, int Hkv, int D, int rot, int neox, long long num_slots) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const long long slot = slots[t];
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * (Hq + 2 * Hkv) * D;
+  const float* cs = cos_sin + static_cast<size_t>(pos) * rot;
+  const int half = D / 2;         // work items per head: D/2 element pairs
+  const int rh = rot / 2;
+  const int total = (Hq + 2 * Hkv) * half;
+  const bool slot_ok = slot >= 0 && slot < num_slots;   // self-check: never write outside the cache
+  for (int w = threadIdx.x; w < total; w += blockDim.x) {
+    const int h = w / half, p = w % half;
+    // element indices of the pair handled by this work item
+    int i0, i1;
+    bool rotate;
+    if (neox) {
+      // pairs (p, p + rot/2) for p < rot/2; the un-rotated tail is handled as plain copies
+      if (p < rh) { i0 = p; i1 = p + rh; rotate = true; }
+      else { i0 = rot + 2 * (p - rh); i1 = i0 + 1; rotate = false; }
+    } else {
+      i0 = 2 * p; i1 = 2 * p + 1; rotate = (i1 < rot);
+    }
+    float x0 = __bfloat162float(src[h * D + i0]);
+    float x1 = __bfloat162float(src[h * D + i1]);
+    if (h < Hq + Hkv && rotate) {
+      const int f = p;   // frequency index
+      const float c = cs[f], s = cs[rh + f];
+      const float r0 = x0 * c - x1 * s;
+      const float r1 = x1 * c + x0 * s;
+      x0 = r0;
+      x1 = r1;
+    }
+    if (h < Hq) {
+      __nv_bfloat16* q = q_out + (static_cast<size_t>(t) * Hq + h) * D;
+      q[i0] = __float2bfloat16(x0);
+      q[i1] = __float2bfloat16(x1);
+    } else if (slot_ok) {
+      const bool is_k = h < Hq + Hkv;
+      const int kvh = is_k ? h - Hq : h - Hq - Hkv;
+      const size_t off = (static_cast<size_t>(slot) * Hkv + kvh) * D;
+      if (FP8_CACHE) {
+        const float* sc = is_k ? k_scale : v_scale;
+        const float scv = sc != nullptr ? sc[kvh] : 1.f;
+        // rotate in bf16 precision first (what a bf16 cache would hold), then quantise
+        x0 = round_bf16(x0);
+        x1 = round_bf16(x1);
+        uint8_t* dst = static_cast<uint8_t*>(is_k ? k_cache : v_cache) + off;
+        dst[i0] = static_cast<uint8_t>(
+            __nv_cvt_float_to_fp8(fminf(fmaxf(x0 / scv, -kFp8Max), kFp8Max), __NV_SATFINITE, __NV_E4M3));
+        dst[i1] = static_cast<uint8_t>(
+            __nv_cvt_float_to_fp8(fminf(fmaxf(x1 / scv, -kFp8Max), kFp8Max), __NV_SATFINITE, __NV_E4M3));
+      } else {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_k ? k_cache : v_cache) + off;
+        dst[i0] = __float2bfloat16(x0);
+        dst[i1] = __float2bfloat16(x1);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
+                 int H, int rows) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= rows) id = rows - 1;  // self-check: clamp instead of reading out of bounds
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) dst[v] = src[v];
+}
+
+// greedy: ids[b] = argmax(logits[b]), logprob[b] = log_softmax(logits[b])[ids[b]]
+template <typename T>
+__global__ void __launch_bounds__(1024)
+argmax_logprob_kernel(const T* __restrict__ logits, long long* __restrict__ ids, float* __restrict__ logprob, int V,
+                      long long row_stride) {
+  __shared__ float s_m[32], s_s[32];
+  __shared__ int s_i[32];
+  const T* row = logits + static_cast<size_t>(blockIdx.x) * row_stride;
+  float m = -INFINITY, s = 0.f;
+  int best = 0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float x = static_cast<float>(row[i]);
+    if (x > m) {
+      s = s * __expf(m - x) + 1.f;
+      m = x;
+      best = i;
+    } else {
+      s += __expf(x - m);
+    }
+  }
+  // merge (m, s, best) across the block; ties resolve to the smallest index like torch.argmax
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const int b2 = __shfl_xor_sync(0xffffffffu, best, o);
+    const float mm = fmaxf(m, m2);
+    const float ns = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+    if (m2 > m || (m2 == m && b2 < best)) best = b2;
+    m = mm;
+    s = ns;
+  }
+  if (lane == 0) { s_m[warp] = m; s_s[warp] = s; s_i[warp] = best; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) / 32;
+    m = lane < nw ? s_m[lane] : -INFINITY;
+    s = lane < nw ? s_s[lane] : 0.f;
+    best = lane < nw ? s_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+      const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      const int b2 = __shfl_xor_sync(0xffffffffu, best, o);
+      const float mm = fmaxf(m, m2);
+      const float ns = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+      if (m2 > m || (m2 == m && b2 < best)) best = b2;
+      m = mm;
+      s = ns;
+    }
+    if (lane == 0) {
+      ids[blockIdx.x] = best;
+      logprob[blockIdx.x] = -logf(s);
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int tgi_norm(const void* x, const void* residual, const void* weight, const void* bias, void* out, void* res_out,
+             void* q_out, float* scale_t, int scale_pitch, int T, int H, float eps, float w_offset, int layer,
+             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || H > 16384) return -10;
+  const bool quant = q_out != nullptr;
+  if (quant && H % 128 != 0) return -11;
+  const int nvec = H / 8;
+  int threads = ((nvec + 31) / 32) * 32;
+  int vpt = 1;
+  if (threads > 1024) { vpt = 2; threads = (((nvec + 1) / 2 + 31) / 32) * 32; }
+  auto x_ = static_cast<const __nv_bfloat16*>(x);
+  auto r_ = static_cast<const __nv_bfloat16*>(residual);
+  auto w_ = static_cast<const __nv_bfloat16*>(weight);
+  auto b_ = static_cast<const __nv_bfloat16*>(bias);
+  auto o_ = static_cast<__nv_bfloat16*>(out);
+  auto ro_ = static_cast<__nv_bfloat16*>(res_out);
+  auto q_ = static_cast<uint8_t*>(q_out);
+#define LAUNCH(VPT, LAYER, QUANT) \
+  norm_kernel<VPT, LAYER, QUANT><<<T, threads, 0, stream>>>(x_, r_, w_, b_, o_, ro_, q_, scale_t, scale_pitch, H, eps, w_offset)
+  if (vpt == 1) {
+    if (layer) { if (quant) LAUNCH(1, true, true); else LAUNCH(1, true, false); }
+    else { if (quant) LAUNCH(1, false, true); else LAUNCH(1, false, false); }
+  } else {
+    if (layer) { if (quant) LAUNCH(2, true, true); else LAUNCH(2, true, false); }
+    else { if (quant) LAUNCH(2, false, true); else LAUNCH(2, false, false); }
+  }
+#undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int tgi_act_mul(const void* in, void* out, void* q_out, float* scale_t, int scale_pitch, int T, int I, int act,
+                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (I % 8 != 0) return -10;
+  const bool quant = q_out != nullptr;
+  if (quant && I % 128 != 0) return -11;
+  dim3 grid((I / 8 + 255) / 256, T);
+  if (quant)
+    act_mul_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), nullptr,
+                                                   static_cast<uint8_t*>(q_out), scale_t, scale_pitch, I, act);
+  else
+    act_mul_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in),
+                                                    static_cast<__nv_bfloat16*>(out), nullptr, nullptr, 0, I, act);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int tgi_quant_act(const void* x, void* q_out, float* scale_t, int scale_pitch, int T, int K, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (K % 128 != 0) return -10;
+  dim3 grid((K / 8 + 255) / 256, T);
+  quant_act_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out),
+                                             scale_t, scale_pitch, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int tgi_rope_cache(const void* qkv, const int* positions, const float* cos_sin, const int* slots, void* q_out,
+                   void* k_cache, void* v_cache, const float* k_scale, const float* v_scale, int T, int Hq, int Hkv,
+                   int D, int rot, int neox, long long num_slots, int fp8_cache, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D % 2 != 0 || rot % 2 != 0 || rot > D) return -10;
+  if (fp8_cache)
+    rope_cache_kernel<true><<<T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
+                                                   static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale,
+                                                   v_scale, Hq, Hkv, D, rot, neox, num_slots);
+  else
+    rope_cache_kernel<false><<<T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
+                                                    static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale,
+                                                    v_scale, Hq, Hkv, D, rot, neox, num_slots);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int tgi_embedding(const int* ids, const void* table, void* out, int T, int H, int rows, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return -10;
+  embedding_kernel<<<T, 256, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table),
+                                          static_cast<__nv_bfloat16*>(out), H, rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int tgi_argmax_logprob(const void* logits, long long* ids, float* logprob, int B, int V, long long row_stride,
+                       int is_fp32, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (is_fp32)
+    argmax_logprob_kernel<float><<<B, 1024, 0, stream>>>(static_cast<const float*>(logits), ids, logprob, V, row_stride);
+  else
+    argmax_logprob_kernel<__nv_bfloat16><<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ids,
+                                                                 logprob, V, row_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // extern "C"

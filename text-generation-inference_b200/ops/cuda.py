@@ -1,0 +1,351 @@
+"""ctypes bindings of the sm_100a kernel library (``libtgi_b200_kernels.so``, built by ``ops/build.py``).
+
+Every wrapper allocates its outputs with torch (so they live in the caching allocator and are graph
+capturable), passes raw pointers plus the current CUDA stream, and raises on a non-zero return code.
+Kernels that wait on barriers report protocol time-outs through a device status word that
+``check_status()`` reads; it is checked by tests and by the engine after each step, never inside a
+captured graph.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+from typing import Optional, Tuple
+
+import torch
+
+_LIB = None
+_LIB_PATH = Path(__file__).resolve().parent / "libtgi_b200_kernels.so"
+FP8 = torch.float8_e4m3fn
+
+_ACT_CODES = {"silu": 0, "swish": 0, "gelu": 1, "gelu_python": 1, "gelu_new": 2, "gelu_fast": 2,
+              "gelu_pytorch_tanh": 2, "gelu_tanh": 2, "relu": 3, "quick_gelu": 4}
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def load():
+    """Load the kernel library; a missing library on a CUDA machine is an error, never a silent fallback."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not _LIB_PATH.exists():
+        if os.environ.get("TGI_B200_AUTOBUILD", "1") == "1":
+            from .build import build
+
+            build()
+        if not _LIB_PATH.exists():
+            raise KernelError(
+                f"{_LIB_PATH} is missing: build it with `python -m tgi_b200.ops.build` "
+                "(the sm_100a kernels are required on CUDA devices)")
+    _LIB = ctypes.CDLL(str(_LIB_PATH))
+    for name in ("tgi_gemm_bf16", "tgi_gemm_fp8_block", "tgi_norm", "tgi_act_mul", "tgi_quant_act",
+                 "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention",
+                 "tgi_gemm_pick_splits", "tgi_attn_decode_splits"):
+        getattr(_LIB, name).restype = c_int
+    _LIB.tgi_gemm_workspace_floats.restype = c_ll
+    return _LIB
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+LAUNCHES = 0  # kernel-launching library calls made so far (benchmarks read and reset it)
+
+
+def _check(rc: int, what: str):
+    global LAUNCHES
+    LAUNCHES += 1
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+# ---- per-device state: split-K workspace, counters, status word --------------------------------
+class _DeviceState:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        self.ws = torch.empty(int(os.environ.get("TGI_B200_SPLITK_WS_MB", "64")) << 18, dtype=torch.float32,
+                              device=device)
+        self.attn_part_o = None
+        self.attn_part_ml = None
+
+
+_STATES = {}
+
+
+def state(device: torch.device) -> _DeviceState:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _STATES.get(idx)
+    if st is None:
+        st = _STATES[idx] = _DeviceState(torch.device("cuda", idx))
+    return st
+
+
+def check_status(device: Optional[torch.device] = None) -> int:
+    """Read (and clear) the kernels' error word; 0 means no kernel gave up on a wait."""
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    st = state(dev)
+    code = int(st.status.item())
+    if code != 0:
+        st.status.zero_()
+    return code
+
+
+# ---- scale tensors -----------------------------------------------------------------------------
+def alloc_act_scales(T: int, groups: int, device) -> torch.Tensor:
+    """Activation scales, logical shape ``[T, groups]`` stored K-block major with a 16-byte aligned pitch."""
+    pitch = (max(T, 1) + 3) & ~3
+    buf = torch.empty(groups, pitch, dtype=torch.float32, device=device)
+    return buf[:, :T].t()
+
+
+def _scale_storage(xs: torch.Tensor) -> Tuple[int, int]:
+    """(data_ptr, pitch) of a ``[T, groups]`` scale view produced by ``alloc_act_scales``."""
+    if xs.dim() != 2 or (xs.shape[0] > 1 and xs.stride(0) != 1):
+        raise KernelError("activation scales must be K-block major (use ops.fp8_quant_act / the fused producers)")
+    pitch = xs.stride(1) if xs.shape[1] > 1 else ((xs.shape[0] + 3) & ~3)
+    return xs.data_ptr(), pitch
+
+
+# ---- GEMMs -------------------------------------------------------------------------------------
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, splits: Optional[int] = None):
+    lib = load()
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M, K = x2.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and w.is_contiguous()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if M == 0:
+        return out.reshape(*lead, N)
+    st = state(x.device)
+    if splits is None:
+        splits = lib.tgi_gemm_pick_splits(M, N, K, 64, st.sm_count)
+    need = lib.tgi_gemm_workspace_floats(M, N, splits)
+    while need > st.ws.numel() and splits > 1:
+        splits -= 1
+        need = lib.tgi_gemm_workspace_floats(M, N, splits)
+    _check(lib.tgi_gemm_bf16(_ptr(x2), _ptr(w), _ptr(out), _ptr(bias), c_int(M), c_int(N), c_int(K), c_int(splits),
+                             _ptr(st.ws), _ptr(st.counters), _ptr(st.status), _stream()), "gemm_bf16")
+    return out.reshape(*lead, N)
+
+
+def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None, splits: Optional[int] = None):
+    lib = load()
+    M, K = xq.shape
+    N = wq.shape[0]
+    assert wq.shape[1] == K and wq.is_contiguous() and xq.is_contiguous()
+    assert out_dtype == torch.bfloat16
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
+    if M == 0:
+        return out
+    st = state(xq.device)
+    sptr, pitch = _scale_storage(xs)
+    if splits is None:
+        splits = lib.tgi_gemm_pick_splits(M, N, K, 128, st.sm_count)
+    need = lib.tgi_gemm_workspace_floats(M, N, splits)
+    while need > st.ws.numel() and splits > 1:
+        splits -= 1
+        need = lib.tgi_gemm_workspace_floats(M, N, splits)
+    if not ws.is_contiguous():
+        ws = ws.contiguous()
+    _check(lib.tgi_gemm_fp8_block(_ptr(xq), c_void_p(sptr), c_int(pitch), _ptr(wq), _ptr(ws), _ptr(out), _ptr(bias),
+                                  c_int(M), c_int(N), c_int(K), c_int(splits), _ptr(st.ws), _ptr(st.counters),
+                                  _ptr(st.status), _stream()), "gemm_fp8_block")
+    return out
+
+
+# ---- norms -------------------------------------------------------------------------------------
+def _norm(x, residual, weight, bias, eps, w_offset, layer, quant):
+    lib = load()
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    T, H = x.shape
+    res_out = torch.empty_like(x) if residual is not None else x
+    out = q = scales = None
+    if quant:
+        q = torch.empty(T, H, dtype=FP8, device=x.device)
+        scales = alloc_act_scales(T, H // 128, x.device)
+        sptr, pitch = _scale_storage(scales)
+    else:
+        out = torch.empty_like(x)
+        sptr, pitch = 0, 0
+    _check(lib.tgi_norm(_ptr(x), _ptr(residual), _ptr(weight), _ptr(bias), _ptr(out),
+                        _ptr(res_out if residual is not None else None), _ptr(q), c_void_p(sptr), c_int(pitch),
+                        c_int(T), c_int(H), c_float(eps), c_float(w_offset), c_int(1 if layer else 0), _stream()),
+           "norm")
+    return out, q, scales, res_out
+
+
+def rms_norm(x, residual, weight, eps, unit_offset=False):
+    out, _, _, res = _norm(x, residual, weight, None, eps, 1.0 if unit_offset else 0.0, False, False)
+    return out, res
+
+
+def rms_norm_quant(x, residual, weight, eps, unit_offset=False):
+    _, q, s, res = _norm(x, residual, weight, None, eps, 1.0 if unit_offset else 0.0, False, True)
+    return q, s, res
+
+
+def layer_norm(x, residual, weight, bias, eps):
+    out, _, _, res = _norm(x, residual, weight, bias, eps, 0.0, True, False)
+    return out, res
+
+
+# ---- activation --------------------------------------------------------------------------------
+def act_and_mul(gate_up, act="silu"):
+    lib = load()
+    T, I2 = gate_up.shape
+    I = I2 // 2
+    out = torch.empty(T, I, dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib.tgi_act_mul(_ptr(gate_up.contiguous()), _ptr(out), c_void_p(0), c_void_p(0), c_int(0), c_int(T),
+                           c_int(I), c_int(_ACT_CODES[act]), _stream()), "act_and_mul")
+    return out
+
+
+def act_and_mul_quant(gate_up, act="silu"):
+    lib = load()
+    T, I2 = gate_up.shape
+    I = I2 // 2
+    q = torch.empty(T, I, dtype=FP8, device=gate_up.device)
+    scales = alloc_act_scales(T, I // 128, gate_up.device)
+    sptr, pitch = _scale_storage(scales)
+    _check(lib.tgi_act_mul(_ptr(gate_up.contiguous()), c_void_p(0), _ptr(q), c_void_p(sptr), c_int(pitch), c_int(T),
+                           c_int(I), c_int(_ACT_CODES[act]), _stream()), "act_and_mul_quant")
+    return q, scales
+
+
+def fp8_quant_act(x, group=128):
+    lib = load()
+    assert group == 128 and x.dtype == torch.bfloat16
+    x = x.contiguous()
+    T, K = x.shape
+    q = torch.empty(T, K, dtype=FP8, device=x.device)
+    scales = alloc_act_scales(T, K // 128, x.device)
+    sptr, pitch = _scale_storage(scales)
+    _check(lib.tgi_quant_act(_ptr(x), _ptr(q), c_void_p(sptr), c_int(pitch), c_int(T), c_int(K), _stream()),
+           "fp8_quant_act")
+    return q, scales
+
+
+# ---- rope + cache ------------------------------------------------------------------------------
+def rope_and_cache(qkv, positions, cos_sin, slots, k_cache, v_cache, num_heads, num_kv_heads, head_dim, rot_dim,
+                   neox=True, k_scale=None, v_scale=None):
+    lib = load()
+    T = qkv.shape[0]
+    qkv = qkv.contiguous()
+    q = torch.empty(T, num_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    fp8 = k_cache.dtype == FP8
+    num_slots = k_cache.shape[0] * k_cache.shape[1]
+    _check(lib.tgi_rope_cache(_ptr(qkv), _ptr(positions), _ptr(cos_sin), _ptr(slots), _ptr(q), _ptr(k_cache),
+                              _ptr(v_cache), _ptr(k_scale if fp8 else None), _ptr(v_scale if fp8 else None),
+                              c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(rot_dim),
+                              c_int(1 if neox else 0), c_ll(num_slots), c_int(1 if fp8 else 0), _stream()),
+           "rope_and_cache")
+    return q
+
+
+# ---- attention ---------------------------------------------------------------------------------
+def paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale, window=-1, softcap=0.0,
+                    k_scale=None, v_scale=None, max_q=None, max_kv=None, nsplit: Optional[int] = None):
+    lib = load()
+    T, Hq, D = q.shape
+    nblk, bs, Hkv, _ = k_cache.shape
+    B = kv_lens.shape[0]
+    out = torch.empty_like(q)
+    if T == 0 or B == 0:
+        return out
+    if max_q is None:
+        max_q = int((cu_seqlens_q[1:] - cu_seqlens_q[:-1]).max().item())
+    if max_kv is None:
+        max_kv = int(kv_lens.max().item())
+    fp8 = k_cache.dtype == FP8
+    st = state(q.device)
+    part_o = part_ml = None
+    if max_q == 1:
+        if nsplit is None:
+            nsplit = lib.tgi_attn_decode_splits(B, Hkv, Hq // Hkv, max_kv, st.sm_count)
+        if nsplit > 1:
+            need = B * Hq * nsplit
+            if st.attn_part_o is None or st.attn_part_o.numel() < need * D:
+                st.attn_part_o = torch.empty(need * D, dtype=torch.float32, device=q.device)
+                st.attn_part_ml = torch.empty(need * 2, dtype=torch.float32, device=q.device)
+            part_o, part_ml = st.attn_part_o, st.attn_part_ml
+    else:
+        nsplit = 1
+    _check(lib.tgi_paged_attention(
+        _ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(cu_seqlens_q), _ptr(kv_lens),
+        _ptr(k_scale if fp8 else None), _ptr(v_scale if fp8 else None), _ptr(out), _ptr(part_o), _ptr(part_ml),
+        c_int(B), c_int(max_q), c_int(block_tables.shape[1]), c_int(bs), c_int(nblk), c_int(Hq), c_int(Hkv), c_int(D),
+        c_float(scale), c_float(softcap), c_int(window if window and window > 0 else -1), c_int(nsplit),
+        c_int(1 if fp8 else 0), _stream()), "paged_attention")
+    return out
+
+
+# ---- misc --------------------------------------------------------------------------------------
+def embedding(ids, table):
+    lib = load()
+    if table.dtype != torch.bfloat16:
+        return torch.nn.functional.embedding(ids.long(), table)
+    T = ids.numel()
+    ids32 = ids if ids.dtype == torch.int32 else ids.to(torch.int32)
+    out = torch.empty(T, table.shape[1], dtype=table.dtype, device=table.device)
+    _check(lib.tgi_embedding(_ptr(ids32.contiguous()), _ptr(table), _ptr(out), c_int(T), c_int(table.shape[1]),
+                             c_int(table.shape[0]), _stream()), "embedding")
+    return out.view(*ids.shape, table.shape[1])
+
+
+def argmax_logprob(logits):
+    lib = load()
+    assert logits.dim() == 2 and logits.stride(1) == 1
+    B, V = logits.shape
+    if logits.dtype not in (torch.bfloat16, torch.float32):
+        logits = logits.float()
+    ids = torch.empty(B, dtype=torch.int64, device=logits.device)
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    _check(lib.tgi_argmax_logprob(_ptr(logits), _ptr(ids), _ptr(lp), c_int(B), c_int(V), c_ll(logits.stride(0)),
+                                  c_int(1 if logits.dtype == torch.float32 else 0), _stream()), "argmax_logprob")
+    return ids, lp
+
+
+def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu"):
+    """Grouped expert MLP: tokens are sorted by expert and each expert's slab runs through the tcgen05 GEMM."""
+    T, H = x.shape
+    E = w_gate_up.shape[0]
+    k = topk_ids.shape[1]
+    flat_e = topk_ids.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)
+    tok = (order // k)
+    counts = torch.bincount(flat_e, minlength=E).tolist()
+    xs = x[tok]
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    wflat = topk_weights.reshape(-1)[order].float()
+    start = 0
+    for e, c in enumerate(counts):
+        if c == 0:
+            continue
+        sl = slice(start, start + c)
+        h = gemm_bf16(xs[sl], w_gate_up[e])
+        a = act_and_mul(h, act)
+        y = gemm_bf16(a, w_down[e])
+        out.index_add_(0, tok[sl], y.float() * wflat[sl].unsqueeze(1))
+        start += c
+    return out.to(x.dtype)

@@ -104,8 +104,9 @@ def rope_and_cache(
     if k_cache.dtype == FP8:
         ks = 1.0 if k_scale is None else k_scale.float().view(1, -1, 1)
         vs = 1.0 if v_scale is None else v_scale.float().view(1, -1, 1)
-        kc[idx] = (k.float() / ks).clamp(-FP8_MAX, FP8_MAX).to(FP8)
-        vc[idx] = (v.float() / vs).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+        # scatter through a byte view: indexed writes are not implemented for fp8 on every backend
+        kc.view(torch.uint8)[idx] = (k.float() / ks).clamp(-FP8_MAX, FP8_MAX).to(FP8).view(torch.uint8)
+        vc.view(torch.uint8)[idx] = (v.float() / vs).clamp(-FP8_MAX, FP8_MAX).to(FP8).view(torch.uint8)
     else:
         kc[idx] = k.to(k_cache.dtype)
         vc[idx] = v.to(v_cache.dtype)
@@ -149,8 +150,12 @@ def paged_attention(
         nb = (L + bs - 1) // bs
         blocks = block_tables[b, :nb].long()
         slot = (blocks.unsqueeze(1) * bs + torch.arange(bs, device=q.device).unsqueeze(0)).reshape(-1)[:L]
-        k = kc[slot].float()
-        v = vc[slot].float()
+        if kc.dtype == FP8:
+            k = kc.view(torch.uint8)[slot].view(FP8).float()
+            v = vc.view(torch.uint8)[slot].view(FP8).float()
+        else:
+            k = kc[slot].float()
+            v = vc[slot].float()
         if k_scale is not None:
             k = k * k_scale.float().view(1, -1, 1)
         if v_scale is not None:
