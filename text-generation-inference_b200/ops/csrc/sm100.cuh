@@ -14,9 +14,11 @@
 
 namespace sm100 {
 
-// Number of mbarrier polls before a wait gives up (each poll may suspend for a short,
-// hardware-defined time, so this is tens of milliseconds to about a second).
-constexpr uint32_t kWaitPolls = 1u << 22;
+// Number of mbarrier polls before a wait gives up.  A poll that does not succeed suspends for a
+// short hardware-defined time (measured here: about 0.7 us), so this is roughly 0.1 s: three orders
+// of magnitude above the longest legitimate wait of these kernels, short enough that a protocol
+// bug costs a fraction of a second instead of hanging the device.
+constexpr uint32_t kWaitPolls = 1u << 17;
 
 // Error codes written to the kernel's status word.
 enum : int {
@@ -27,6 +29,7 @@ enum : int {
   kErrEpilogueWait = 4,   // epilogue waited for a finished accumulator
   kErrPeerWait = 5,       // wait on a flag written by another GPU
   kErrSplitKWait = 6,
+  kErrSmemLayout = 7,     // shared-memory carve-up larger than the launch's dynamic shared memory
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -185,6 +188,17 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Same wait, with the loaded registers as in/out operands: consumers of `r` cannot be scheduled
+// before the wait because they depend on its outputs.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 }
 
 // ---- descriptors ---------------------------------------------------------------------------

@@ -50,7 +50,7 @@ def load():
     _LIB = ctypes.CDLL(str(_LIB_PATH))
     for name in ("tgi_gemm_bf16", "tgi_gemm_fp8_block", "tgi_norm", "tgi_act_mul", "tgi_quant_act",
                  "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention",
-                 "tgi_gemm_pick_splits", "tgi_attn_decode_splits"):
+                 "tgi_gemm_num_tiles", "tgi_attn_decode_splits"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
     return _LIB
@@ -125,7 +125,17 @@ def _scale_storage(xs: torch.Tensor) -> Tuple[int, int]:
 
 
 # ---- GEMMs -------------------------------------------------------------------------------------
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, splits: Optional[int] = None):
+def _gemm_ctas(lib, st, M: int, N: int, max_ctas: Optional[int]) -> int:
+    """Grid size of the persistent stream-K GEMM: one CTA per SM, bounded by the scratch buffers."""
+    ctas = st.sm_count if max_ctas is None else max(1, min(int(max_ctas), st.sm_count))
+    while ctas > 1 and lib.tgi_gemm_workspace_floats(M, ctas) > st.ws.numel():
+        ctas -= 1
+    if lib.tgi_gemm_num_tiles(M, N) > st.counters.numel():
+        raise KernelError("GEMM has more output tiles than tile counters; raise the counter buffer size")
+    return ctas
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, max_ctas: Optional[int] = None):
     lib = load()
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
@@ -138,18 +148,13 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     if M == 0:
         return out.reshape(*lead, N)
     st = state(x.device)
-    if splits is None:
-        splits = lib.tgi_gemm_pick_splits(M, N, K, 64, st.sm_count)
-    need = lib.tgi_gemm_workspace_floats(M, N, splits)
-    while need > st.ws.numel() and splits > 1:
-        splits -= 1
-        need = lib.tgi_gemm_workspace_floats(M, N, splits)
-    _check(lib.tgi_gemm_bf16(_ptr(x2), _ptr(w), _ptr(out), _ptr(bias), c_int(M), c_int(N), c_int(K), c_int(splits),
+    ctas = _gemm_ctas(lib, st, M, N, max_ctas)
+    _check(lib.tgi_gemm_bf16(_ptr(x2), _ptr(w), _ptr(out), _ptr(bias), c_int(M), c_int(N), c_int(K), c_int(ctas),
                              _ptr(st.ws), _ptr(st.counters), _ptr(st.status), _stream()), "gemm_bf16")
     return out.reshape(*lead, N)
 
 
-def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None, splits: Optional[int] = None):
+def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None, max_ctas: Optional[int] = None):
     lib = load()
     M, K = xq.shape
     N = wq.shape[0]
@@ -160,16 +165,11 @@ def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None, splits: 
         return out
     st = state(xq.device)
     sptr, pitch = _scale_storage(xs)
-    if splits is None:
-        splits = lib.tgi_gemm_pick_splits(M, N, K, 128, st.sm_count)
-    need = lib.tgi_gemm_workspace_floats(M, N, splits)
-    while need > st.ws.numel() and splits > 1:
-        splits -= 1
-        need = lib.tgi_gemm_workspace_floats(M, N, splits)
+    ctas = _gemm_ctas(lib, st, M, N, max_ctas)
     if not ws.is_contiguous():
         ws = ws.contiguous()
     _check(lib.tgi_gemm_fp8_block(_ptr(xq), c_void_p(sptr), c_int(pitch), _ptr(wq), _ptr(ws), _ptr(out), _ptr(bias),
-                                  c_int(M), c_int(N), c_int(K), c_int(splits), _ptr(st.ws), _ptr(st.counters),
+                                  c_int(M), c_int(N), c_int(K), c_int(ctas), _ptr(st.ws), _ptr(st.counters),
                                   _ptr(st.status), _stream()), "gemm_fp8_block")
     return out
 
