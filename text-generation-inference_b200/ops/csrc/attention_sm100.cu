@@ -88,7 +88,7 @@ struct Params {
   __nv_bfloat16* out;           // [T, Hq, D]
   float* part_o;                // decode partials [B, Hq, nsplit, D]
   float* part_ml;               // [B, Hq, nsplit, 2]
-  int max_blocks, block_size, Hq, Hkv, num_blocks;
+  int max_blocks, block_size, bs_shift, Hq, Hkv, num_blocks;   // block_size == 1 << bs_shift
   float scale, softcap;
   int window;
   int nsplit;
@@ -109,9 +109,9 @@ __device__ __forceinline__ void load_tile(const Params& p, const void* cache, in
     bool valid = t < L;
     const char* src = base;
     if (valid) {
-      const int blk = p.block_tables[static_cast<size_t>(b) * p.max_blocks + t / p.block_size];
+      const int blk = p.block_tables[static_cast<size_t>(b) * p.max_blocks + (t >> p.bs_shift)];
       valid = blk >= 0 && blk < p.num_blocks;     // self-check on the block table
-      const size_t slot = static_cast<size_t>(blk) * p.block_size + t % p.block_size;
+      const size_t slot = (static_cast<size_t>(blk) << p.bs_shift) + (t & (p.block_size - 1));
       if (valid) src = base + ((slot * p.Hkv + kvh) * D) * EB + cc * 16;
     }
     char* d;
@@ -119,6 +119,13 @@ __device__ __forceinline__ void load_tile(const Params& p, const void* cache, in
     else d = reinterpret_cast<char*>(static_cast<uint16_t*>(dst) + swz<D>(row, cc));
     cp_async16(d, src, valid);
   }
+}
+
+// two e4m3 values -> packed fp16x2 (exact), one instruction
+__device__ __forceinline__ uint32_t cvt_e4m3x2_f16x2(uint16_t v) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+  return r;
 }
 
 // widen a raw e4m3 tile [64][D] to the swizzled fp16 compute tile
@@ -132,10 +139,8 @@ __device__ __forceinline__ void widen_tile(const uint8_t* raw, __half* dst) {
     uint32_t o[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] & 0xFFFF), __NV_E4M3);
-      __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] >> 16), __NV_E4M3);
-      o[2 * i] = static_cast<uint32_t>(lo.x) | (static_cast<uint32_t>(lo.y) << 16);
-      o[2 * i + 1] = static_cast<uint32_t>(hi.x) | (static_cast<uint32_t>(hi.y) << 16);
+      o[2 * i] = cvt_e4m3x2_f16x2(static_cast<uint16_t>(w[i] & 0xFFFF));
+      o[2 * i + 1] = cvt_e4m3x2_f16x2(static_cast<uint16_t>(w[i] >> 16));
     }
     *reinterpret_cast<uint4*>(dst + swz<D>(row, 2 * cc)) = make_uint4(o[0], o[1], o[2], o[3]);
     *reinterpret_cast<uint4*>(dst + swz<D>(row, 2 * cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
@@ -371,18 +376,124 @@ prefill_kernel(Params p) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// decode: one query token per sequence.  grid (B, Hkv * gchunks, nsplit), block 128.
-// Rows of the MMA tile are the query heads sharing KV head kvh (up to 16 per CTA).  Warp w owns
-// tokens [16w, 16w+16) of every 64-token tile; the four warps' partial results are merged at the end.
+// decode, warp-independent pipelines.  grid (B, Hkv * gchunks, nsplit), block 128.
+// The KV range of the split is cut in chunks of CT tokens; warp w takes chunks w, w+4, ...  Every
+// warp runs its own 3-deep cp.async ring and never synchronises with the other warps until the
+// final merge, so the CTA keeps (4 warps x 2 chunks) of KV loads in flight and a warp that waits
+// for memory does not stall the others.
 // ------------------------------------------------------------------------------------------------
 template <int D, bool FP8>
+struct DecodeSmem {
+  static constexpr int CT = (FP8 && D <= 128) ? 32 : 16;        // tokens per warp chunk
+  static constexpr int EB = FP8 ? 1 : 2;
+  static constexpr int kStages = 2;
+  static constexpr int kQBytes = 16 * D * 2;
+  static constexpr int kChunkBytes = CT * D * EB;               // one K or V chunk as stored in the cache
+  static constexpr int kRingBytes = kStages * 2 * kChunkBytes;  // per warp: stages x (K, V)
+  static constexpr int kCompBytes = FP8 ? CT * D * 2 : 0;       // per warp: widened V (e4m3 pages only)
+  static constexpr int kWarpBytes = kRingBytes + kCompBytes;
+  static constexpr int kMergeBytes = 4 * 16 * D * 4 + 4 * 16 * 2 * 4;
+  static constexpr int kBytes = kQBytes + (4 * kWarpBytes > kMergeBytes ? 4 * kWarpBytes : kMergeBytes);
+};
+
+// one warp gathers CT tokens of K or V (sequence b, KV head kvh, tokens t0..) into `dst`
+// RAW_SWZ: e4m3 rows are stored with their 16-byte chunks XOR-ed by the row index, the layout the
+// direct K-fragment loads below read without bank conflicts.
+template <int D, bool FP8, int CT, bool RAW_SWZ>
+__device__ __forceinline__ void warp_load_chunk(const Params& p, const void* cache, int b, int kvh, int t0, int t_end,
+                                                void* dst, int lane) {
+  constexpr int EB = FP8 ? 1 : 2;
+  constexpr int CPR = D * EB / 16;
+  const char* base = static_cast<const char*>(cache);
+#pragma unroll
+  for (int c = lane; c < CT * CPR; c += 32) {
+    const int row = c / CPR, cc = c % CPR;
+    const int t = t0 + row;
+    bool valid = t < t_end;
+    const char* src = base;
+    if (valid) {
+      const int blk = p.block_tables[static_cast<size_t>(b) * p.max_blocks + (t >> p.bs_shift)];
+      valid = blk >= 0 && blk < p.num_blocks;     // self-check on the block table
+      const size_t slot = (static_cast<size_t>(blk) << p.bs_shift) + (t & (p.block_size - 1));
+      if (valid) src = base + ((slot * p.Hkv + kvh) * D) * EB + cc * 16;
+    }
+    char* d;
+    if (FP8) d = static_cast<char*>(dst) + row * D + ((RAW_SWZ ? (cc ^ (row & (CPR < 8 ? CPR - 1 : 7))) : cc) << 4);
+    else d = reinterpret_cast<char*>(static_cast<uint16_t*>(dst) + swz<D>(row, cc));
+    cp_async16(d, src, valid);
+  }
+}
+
+// S[16 x NT*8] = Q * K^T with K read straight from the raw e4m3 chunk: lane (g = lane/4, j = lane%4)
+// loads the 4 consecutive bytes d = 16*ks + 4j .. +3 of token row g and widens them to the two B
+// fragments of the k-step.  The MMA's k index is therefore a permutation of d inside each group of
+// 16; the Q fragments (`load_q_frags_permuted`) use the same permutation, so the dot products are
+// unchanged.
+template <int D, int NT>
+__device__ __forceinline__ void qk_warp_e4m3(const uint32_t (&qf)[D / 16][4], const uint8_t* rawK, float (&s)[NT][4]) {
+  constexpr int CPR = D / 16;
+  constexpr int SW = CPR < 8 ? CPR - 1 : 7;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, j = lane & 3;
+#pragma unroll
+  for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tok = nt * 8 + g;
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(rawK + tok * D + ((ks ^ (tok & SW)) << 4) + j * 4);
+      mma16816<true>(s[nt], qf[ks], cvt_e4m3x2_f16x2(static_cast<uint16_t>(w & 0xFFFF)),
+                     cvt_e4m3x2_f16x2(static_cast<uint16_t>(w >> 16)));
+    }
+  }
+}
+
+// A fragments of the fp16 Q tile [16][D] (plain row-major) under the k permutation of qk_warp_e4m3
+template <int D>
+__device__ __forceinline__ void load_q_frags_permuted(const uint16_t* sQ, uint32_t (&qf)[D / 16][4]) {
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, j = lane & 3;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const uint2 lo = *reinterpret_cast<const uint2*>(sQ + g * D + ks * 16 + 4 * j);         // d = 4j .. 4j+3
+    const uint2 hi = *reinterpret_cast<const uint2*>(sQ + (g + 8) * D + ks * 16 + 4 * j);
+    qf[ks][0] = lo.x;   // row g,   k = 2j, 2j+1   <- d = 4j, 4j+1
+    qf[ks][1] = hi.x;   // row g+8
+    qf[ks][2] = lo.y;   // row g,   k = 2j+8, 2j+9 <- d = 4j+2, 4j+3
+    qf[ks][3] = hi.y;
+  }
+}
+
+template <int D, int CT>
+__device__ __forceinline__ void warp_widen_chunk(const uint8_t* raw, __half* dst, int lane) {
+  constexpr int CPR = D / 16;
+#pragma unroll
+  for (int c = lane; c < CT * CPR; c += 32) {
+    const int row = c / CPR, cc = c % CPR;
+    const uint4 v = *reinterpret_cast<const uint4*>(raw + row * D + cc * 16);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[2 * i] = cvt_e4m3x2_f16x2(static_cast<uint16_t>(w[i] & 0xFFFF));
+      o[2 * i + 1] = cvt_e4m3x2_f16x2(static_cast<uint16_t>(w[i] >> 16));
+    }
+    *reinterpret_cast<uint4*>(dst + swz<D>(row, 2 * cc)) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(dst + swz<D>(row, 2 * cc + 1)) = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+template <int D, bool FP8>
 __global__ void __launch_bounds__(128)
-decode_kernel(Params p) {
+decode_kernel_v2(Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  using S = Smem<D, FP8>;
+  using S = DecodeSmem<D, FP8>;
+  constexpr int CT = S::CT;
+  constexpr int NT = CT / 8;
   uint16_t* sQ = reinterpret_cast<uint16_t*>(smem);
-  uint8_t* kreg = smem + S::kQBytes;
-  uint8_t* vreg = kreg + S::kKVBytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* wbase = smem + S::kQBytes + warp * S::kWarpBytes;
 
   const int G = p.Hq / p.Hkv;
   const int gchunks = (G + 15) / 16;
@@ -394,15 +505,15 @@ decode_kernel(Params p) {
   const int L = p.kv_lens[b];
   const int q_row = p.cu_seqlens_q[b];
   if (p.cu_seqlens_q[b + 1] == q_row) return;   // sequence contributes no query this step
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = L - 1;
   int t_lo = 0;
-  if (p.window > 0) t_lo = max(0, pos - p.window + 1) / kTile * kTile;
-  const int tiles_total = (L - t_lo + kTile - 1) / kTile;
-  const int tiles_per = (tiles_total + p.nsplit - 1) / p.nsplit;
-  const int tile_begin = split * tiles_per;
-  const int tile_end = min(tiles_total, tile_begin + tiles_per);
-  const int ntiles = max(0, tile_end - tile_begin);
+  if (p.window > 0) t_lo = max(0, pos - p.window + 1) / CT * CT;
+  const int chunks_total = (L - t_lo + CT - 1) / CT;
+  const int chunks_per = (chunks_total + p.nsplit - 1) / p.nsplit;
+  const int c0 = split * chunks_per;
+  const int c1 = min(chunks_total, c0 + chunks_per);
+  // chunks of this warp: c0 + warp + 4*i
+  const int my_n = (c1 - c0 - warp + 3) / 4 > 0 ? (c1 - c0 - warp + 3) / 4 : 0;
 
   for (int c = threadIdx.x; c < 16 * (D / 8); c += blockDim.x) {
     const int row = c / (D / 8), cc = c % (D / 8);
@@ -418,20 +529,27 @@ decode_kernel(Params p) {
       }
       v = make_uint4(o4[0], o4[1], o4[2], o4[3]);
     }
-    *reinterpret_cast<uint4*>(sQ + swz<D>(row, cc)) = v;
+    // e4m3 pages: plain row-major fp16 Q (read by load_q_frags_permuted); bf16 pages: swizzled for ldmatrix
+    if (FP8) *reinterpret_cast<uint4*>(sQ + row * D + cc * 8) = v;
+    else *reinterpret_cast<uint4*>(sQ + swz<D>(row, cc)) = v;
   }
-  auto stage_ptr = [&](uint8_t* region, int stg) -> void* {
-    return FP8 ? static_cast<void*>(region + stg * kTile * D) : static_cast<void*>(region + stg * kTile * D * 2);
+  auto kstage = [&](int stg) -> void* { return wbase + stg * 2 * S::kChunkBytes; };
+  auto vstage = [&](int stg) -> void* { return wbase + stg * 2 * S::kChunkBytes + S::kChunkBytes; };
+  auto issue = [&](int i) {
+    if (i < my_n) {
+      const int t0 = t_lo + (c0 + warp + 4 * i) * CT;
+      warp_load_chunk<D, FP8, CT, true>(p, p.k_cache, b, kvh, t0, L, kstage(i % S::kStages), lane);
+      warp_load_chunk<D, FP8, CT, false>(p, p.v_cache, b, kvh, t0, L, vstage(i % S::kStages), lane);
+    }
+    cp_async_commit();
   };
-  if (ntiles > 0) {
-    load_tile<D, FP8>(p, p.k_cache, b, kvh, t_lo + tile_begin * kTile, L, stage_ptr(kreg, 0));
-    load_tile<D, FP8>(p, p.v_cache, b, kvh, t_lo + tile_begin * kTile, L, stage_ptr(vreg, 0));
-  }
-  cp_async_commit();
-  __syncthreads();
+  issue(0);
+  __syncthreads();   // Q tile visible to every warp
 
   uint32_t qf[D / 16][4];
-  {
+  if (FP8) {
+    load_q_frags_permuted<D>(sQ, qf);
+  } else {
     const int mi = lane >> 3;
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) ldsm_x4(qf[ks], sQ + swz<D>((lane & 7) + (mi & 1) * 8, ks * 2 + (mi >> 1)));
@@ -445,49 +563,41 @@ decode_kernel(Params p) {
   const float raw_scale = p.scale * (FP8 ? ksc : 1.f);
   const float scale_log2 = raw_scale * kLog2e;
 
-  for (int j = 0; j < ntiles; ++j) {
-    const int stg = j & 1;
-    if (j + 1 < ntiles) {
-      load_tile<D, FP8>(p, p.k_cache, b, kvh, t_lo + (tile_begin + j + 1) * kTile, L, stage_ptr(kreg, stg ^ 1));
-      load_tile<D, FP8>(p, p.v_cache, b, kvh, t_lo + (tile_begin + j + 1) * kTile, L, stage_ptr(vreg, stg ^ 1));
-    }
-    cp_async_commit();
+  for (int i = 0; i < my_n; ++i) {
+    // the stage that chunk i+1 goes to was last read in iteration i-1 (program order + the
+    // __syncwarp at the end of that iteration make those reads complete before this write)
+    issue(i + 1);
     cp_async_wait<1>();
-    __syncthreads();
-    const uint16_t* cK;
+    __syncwarp();
     const uint16_t* cV;
+    float s[NT][4];
     if (FP8) {
-      __half* ck = reinterpret_cast<__half*>(kreg + 2 * kTile * D);
-      __half* cv = reinterpret_cast<__half*>(vreg + 2 * kTile * D);
-      widen_tile<D>(kreg + stg * kTile * D, ck);
-      widen_tile<D>(vreg + stg * kTile * D, cv);
-      __syncthreads();
-      cK = reinterpret_cast<const uint16_t*>(ck);
+      __half* cv = reinterpret_cast<__half*>(wbase + S::kRingBytes);
+      qk_warp_e4m3<D, NT>(qf, static_cast<const uint8_t*>(kstage(i % S::kStages)), s);
+      warp_widen_chunk<D, CT>(static_cast<const uint8_t*>(vstage(i % S::kStages)), cv, lane);
+      __syncwarp();
       cV = reinterpret_cast<const uint16_t*>(cv);
     } else {
-      cK = reinterpret_cast<const uint16_t*>(kreg + stg * kTile * D * 2);
-      cV = reinterpret_cast<const uint16_t*>(vreg + stg * kTile * D * 2);
+      qk_warp<D, NT, false>(qf, static_cast<const uint16_t*>(kstage(i % S::kStages)), 0, s);
+      cV = static_cast<const uint16_t*>(vstage(i % S::kStages));
     }
-    float s[2][4];
-    qk_warp<D, 2, FP8>(qf, cK, warp * 2, s);
     float alpha[2];
-    // every row (= head) sits at the same position `pos`
-    softmax_update<2>(s, m, l, alpha, t_lo + (tile_begin + j) * kTile + warp * 16, pos, pos, L, p.window, scale_log2,
-                      p.softcap, raw_scale);
+    softmax_update<NT>(s, m, l, alpha, t_lo + (c0 + warp + 4 * i) * CT, pos, pos, L, p.window, scale_log2, p.softcap,
+                       raw_scale);
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    for (int j = 0; j < D / 8; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
     }
-    pv_warp<D, 2, FP8>(s, cV, warp * 2, o);
-    __syncthreads();
+    pv_warp<D, NT, FP8>(s, cV, 0, o);
+    __syncwarp();
   }
   cp_async_wait<0>();
   __syncthreads();
 
-  // ---- merge the four warps through shared memory (reuse the K region) ----
-  float* mO = reinterpret_cast<float*>(kreg);                // [4][16][D]
-  float* mML = reinterpret_cast<float*>(vreg);               // [4][16][2]
+  // ---- merge the four warps through shared memory (the rings are no longer needed) ----
+  float* mO = reinterpret_cast<float*>(smem + S::kQBytes);   // [4][16][D]
+  float* mML = mO + 4 * 16 * D;                              // [4][16][2]
   {
     const int r0 = lane >> 2, r1 = r0 + 8;
 #pragma unroll
@@ -574,15 +684,16 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
     dim3 grid((max_q + kTile - 1) / kTile, p.Hq, B);
     k<<<grid, 128, smem, stream>>>(p);
   } else {
-    auto k = decode_kernel<D, FP8>;
+    auto k = decode_kernel_v2<D, FP8>;
+    constexpr int dsmem = DecodeSmem<D, FP8>::kBytes;
     static bool set = false;
     if (!set) {
-      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, dsmem) != cudaSuccess) return -2;
       set = true;
     }
     const int G = p.Hq / p.Hkv;
     dim3 grid(B, p.Hkv * ((G + 15) / 16), p.nsplit);
-    k<<<grid, 128, smem, stream>>>(p);
+    k<<<grid, 128, dsmem, stream>>>(p);
     if (p.nsplit > 1) {
       dim3 g2(B, p.Hq);
       decode_merge_kernel<<<g2, D < 128 ? D : 128, 0, stream>>>(p.part_o, p.part_ml, p.cu_seqlens_q, p.out, p.Hq, D,
@@ -628,6 +739,9 @@ int tgi_paged_attention(const void* q, const void* k_cache, const void* v_cache,
   p.part_ml = part_ml;
   p.max_blocks = max_blocks;
   p.block_size = block_size;
+  if (block_size <= 0 || (block_size & (block_size - 1)) != 0) return -13;   // pages hold a power-of-two token count
+  p.bs_shift = 0;
+  while ((1 << p.bs_shift) < block_size) ++p.bs_shift;
   p.Hq = Hq;
   p.Hkv = Hkv;
   p.num_blocks = num_blocks;
