@@ -1,0 +1,208 @@
+"""End to end on CPU: a real shard process (tiny Llama, fp32) behind the C++ router binary, driven
+over HTTP — /generate, /generate_stream (SSE), /v1/chat/completions, /tokenize, /info, /health,
+/metrics, validation errors, and the shard's gRPC endpoint."""
+import json
+import os
+import signal
+import socket
+import subprocess
+import sys
+import time
+import urllib.error
+import urllib.request
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _post(port, path, body, timeout=60):
+    req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", data=json.dumps(body).encode(),
+                                 headers={"content-type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=timeout) as r:
+            return r.status, dict(r.headers), r.read().decode()
+    except urllib.error.HTTPError as e:
+        return e.code, dict(e.headers), e.read().decode()
+
+
+def _get(port, path):
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}{path}", timeout=30) as r:
+        return r.status, r.read().decode()
+
+
+@pytest.fixture(scope="module")
+def stack(tmp_path_factory):
+    from tgi_b200.router.build import build
+    from tgi_b200.utils.synthetic import llama_config, write_llama_checkpoint
+
+    router_bin = build()
+    d = tmp_path_factory.mktemp("e2e_model")
+    write_llama_checkpoint(d, llama_config(hidden=64, layers=2, heads=4, kv_heads=2, intermediate=128, vocab=300, max_pos=512))
+    (d / "tokenizer_config.json").write_text(json.dumps({
+        "chat_template": "{% for m in messages %}<|{{ m['role'] }}|>{{ m['content'] }}\n{% endfor %}<|assistant|>"}))
+    uds = str(d / "shard")
+    env = dict(os.environ, PYTHONPATH=ROOT, TGI_B200_CPU_KV_BLOCKS="256", VIRTUAL_ENV=os.environ.get("VIRTUAL_ENV", sys.prefix))
+    shard = subprocess.Popen([sys.executable, "-m", "tgi_b200.server.cli", "serve", str(d), "--uds-path", uds,
+                              "--dtype", "float32"], env=env, cwd=ROOT)
+    port = _free_port()
+    router = subprocess.Popen([str(router_bin), "--master-shard-uds-path", uds, "--tokenizer-name", str(d),
+                               "--port", str(port), "--hostname", "127.0.0.1", "--max-input-tokens", "64",
+                               "--max-total-tokens", "128", "--max-batch-prefill-tokens", "128",
+                               "--repo-root", ROOT], env=env, cwd=ROOT)
+    try:
+        deadline = time.time() + 120
+        while time.time() < deadline:
+            if shard.poll() is not None or router.poll() is not None:
+                raise RuntimeError("a process of the stack exited during start-up")
+            try:
+                if _get(port, "/health")[0] == 200:
+                    break
+            except Exception:
+                time.sleep(0.3)
+        else:
+            raise RuntimeError("router did not come up")
+        yield {"port": port, "uds": uds}
+    finally:
+        for p in (router, shard):
+            p.send_signal(signal.SIGTERM)
+        for p in (router, shard):
+            try:
+                p.wait(timeout=20)
+            except subprocess.TimeoutExpired:
+                p.kill()
+
+
+def test_generate_and_details(stack):
+    st, headers, body = _post(stack["port"], "/generate", {
+        "inputs": "hello world", "parameters": {"max_new_tokens": 5, "details": True, "decoder_input_details": True,
+                                                  "top_n_tokens": 2}})
+    assert st == 200, body
+    out = json.loads(body)
+    d = out["details"]
+    assert d["finish_reason"] == "length" and d["generated_tokens"] == 5 and len(d["tokens"]) == 5
+    assert d["seed"] is None and len(d["prefill"]) == 11 and d["prefill"][0]["logprob"] is None
+    assert all(len(t) >= 2 for t in d["top_tokens"])
+    assert headers.get("x-generated-tokens") == "5" and headers.get("x-prompt-tokens") == "11"
+    # greedy decoding is deterministic, also through the prefix cache on the second call
+    st2, _, body2 = _post(stack["port"], "/generate", {"inputs": "hello world", "parameters": {"max_new_tokens": 5}})
+    assert st2 == 200 and json.loads(body2)["generated_text"] == out["generated_text"]
+
+
+def test_sampling_with_seed_is_reproducible(stack):
+    p = {"max_new_tokens": 6, "do_sample": True, "temperature": 0.8, "top_k": 20, "top_p": 0.9, "seed": 11,
+         "repetition_penalty": 1.1, "details": True}
+    a = json.loads(_post(stack["port"], "/generate", {"inputs": "abc", "parameters": p})[2])
+    b = json.loads(_post(stack["port"], "/generate", {"inputs": "abc", "parameters": p})[2])
+    assert a["details"]["seed"] == 11
+    assert [t["id"] for t in a["details"]["tokens"]] == [t["id"] for t in b["details"]["tokens"]]
+
+
+def test_stream_and_concurrency(stack):
+    import threading
+
+    results = {}
+
+    def run(i):
+        req = urllib.request.Request(f"http://127.0.0.1:{stack['port']}/generate_stream",
+                                     data=json.dumps({"inputs": f"prompt {i}", "parameters": {"max_new_tokens": 4 + i, "details": True}}).encode(),
+                                     headers={"content-type": "application/json"})
+        events = []
+        with urllib.request.urlopen(req, timeout=60) as r:
+            assert r.headers["content-type"] == "text/event-stream"
+            for line in r:
+                line = line.decode().strip()
+                if line.startswith("data:"):
+                    events.append(json.loads(line[5:]))
+        results[i] = events
+
+    ts = [threading.Thread(target=run, args=(i,)) for i in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    for i in range(4):
+        ev = results[i]
+        assert len(ev) == 4 + i and [e["index"] for e in ev] == list(range(4 + i))
+        assert ev[-1]["generated_text"] is not None and ev[-1]["details"]["generated_tokens"] == 4 + i
+        assert all(e["generated_text"] is None for e in ev[:-1])
+
+
+def test_chat_completions(stack):
+    st, _, body = _post(stack["port"], "/v1/chat/completions", {
+        "model": "tgi", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0, "logprobs": True})
+    assert st == 200, body
+    out = json.loads(body)
+    assert out["object"] == "chat.completion" and out["choices"][0]["message"]["role"] == "assistant"
+    assert out["usage"]["completion_tokens"] == 4 and out["choices"][0]["finish_reason"] == "length"
+    assert len(out["choices"][0]["logprobs"]["content"]) == 4
+    st, _, body = _post(stack["port"], "/chat_tokenize", {"messages": [{"role": "user", "content": "hi"}]})
+    assert st == 200 and json.loads(body)["templated_text"] == "<|user|>hi\n<|assistant|>"
+    # streaming
+    req = urllib.request.Request(f"http://127.0.0.1:{stack['port']}/v1/chat/completions",
+                                 data=json.dumps({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3, "stream": True,
+                                                  "stream_options": {"include_usage": True}}).encode(),
+                                 headers={"content-type": "application/json"})
+    lines = []
+    with urllib.request.urlopen(req, timeout=60) as r:
+        for line in r:
+            line = line.decode().strip()
+            if line.startswith("data:"):
+                lines.append(line[5:].strip())
+    assert lines[-1] == "[DONE]"
+    chunks = [json.loads(l) for l in lines[:-1]]
+    assert chunks[0]["object"] == "chat.completion.chunk" and chunks[-1]["usage"]["completion_tokens"] == 3
+    assert chunks[-2]["choices"][0]["finish_reason"] == "length"
+
+
+def test_completions_and_misc_routes(stack):
+    st, _, body = _post(stack["port"], "/v1/completions", {"prompt": ["a", "b"], "max_tokens": 2})
+    out = json.loads(body)
+    assert st == 200 and len(out["choices"]) == 2 and out["usage"]["completion_tokens"] == 4
+    st, _, body = _post(stack["port"], "/tokenize", {"inputs": "hey"})
+    assert st == 200 and [t["id"] for t in json.loads(body)] == [107, 104, 124]
+    st, body = _get(stack["port"], "/info")
+    info = json.loads(body)
+    assert info["max_input_tokens"] == 64 and info["max_total_tokens"] == 128
+    st, body = _get(stack["port"], "/metrics")
+    assert "tgi_request_count" in body and "tgi_batch_inference_count{method=\"decode\"}" in body
+    assert "tgi_request_duration_bucket" in body
+    st, body = _get(stack["port"], "/v1/models")
+    assert json.loads(body)["object"] == "list"
+    st, _, body = _post(stack["port"], "/", {"inputs": "x", "parameters": {"max_new_tokens": 1}})
+    assert st == 200 and isinstance(json.loads(body), list)
+
+
+def test_validation_errors(stack):
+    st, _, body = _post(stack["port"], "/generate", {"inputs": "x", "parameters": {"temperature": 0}})
+    assert st == 422 and json.loads(body)["error_type"] == "validation"
+    st, _, body = _post(stack["port"], "/generate", {"inputs": "x" * 100, "parameters": {}})
+    assert st == 422 and "must have less than 64 tokens" in json.loads(body)["error"]
+    st, _, body = _post(stack["port"], "/generate", {"inputs": "x", "parameters": {"best_of": 2}})
+    assert st == 422
+    st, _, body = _post(stack["port"], "/v1/completions", {"prompt": "a", "suffix": "b"})
+    assert st == 422
+
+
+def test_grammar_constrained_generation(stack):
+    st, _, body = _post(stack["port"], "/generate", {
+        "inputs": "n:", "parameters": {"max_new_tokens": 12, "grammar": {"type": "regex", "value": "(yes|no)"}}})
+    assert st == 200, body
+    assert json.loads(body)["generated_text"] in ("yes", "no")
+
+
+def test_shard_grpc_endpoint(stack):
+    from tgi_b200.proto import generate_v3 as pb
+    from tgi_b200.server.client import ShardedClient
+
+    c = ShardedClient.connect_uds(stack["uds"] + "-0")
+    info = c.info()
+    assert info.block_size == 16 and info.support_chunking and info.use_prefix_caching
+    c.health()
+    c.close()

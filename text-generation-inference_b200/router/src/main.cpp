@@ -1,0 +1,251 @@
+// tgi-b200-router: HTTP front + scheduler process.  Connects to the shard processes, warms them
+// up, derives the serving limits and serves the REST API.
+// (Reference: backends/v3/src/main.rs:9-196 flags and checks, backends/v3/src/lib.rs:48-169
+// connect_backend, router/src/server.rs:1502-1867 run.)
+#include <csignal>
+#include <cstdlib>
+#include <cstring>
+#include <iostream>
+#include <map>
+
+#include "api.hpp"
+#include "http.hpp"
+#include "metrics.hpp"
+#include "pybridge.hpp"
+#include "scheduler.hpp"
+#include "shard_client.hpp"
+
+namespace {
+
+http::Server* g_server = nullptr;
+void on_signal(int) {
+  if (g_server) g_server->stop();
+}
+
+struct Args {
+  std::map<std::string, std::string> kv;
+  // --flag value | --flag=value | env FLAG (upper case, dashes -> underscores)
+  Args(int argc, char** argv) {
+    for (int i = 1; i < argc; ++i) {
+      std::string a = argv[i];
+      if (a.rfind("--", 0) != 0) continue;
+      a = a.substr(2);
+      size_t eq = a.find('=');
+      if (eq != std::string::npos) kv[a.substr(0, eq)] = a.substr(eq + 1);
+      else if (i + 1 < argc && std::strncmp(argv[i + 1], "--", 2) != 0) kv[a] = argv[++i];
+      else kv[a] = "true";
+    }
+  }
+  std::string get(const std::string& name, const std::string& dflt = "") const {
+    auto it = kv.find(name);
+    if (it != kv.end()) return it->second;
+    std::string env = name;
+    for (auto& c : env) c = c == '-' ? '_' : static_cast<char>(toupper(c));
+    const char* e = std::getenv(env.c_str());
+    return e ? e : dflt;
+  }
+  long num(const std::string& name, long dflt) const {
+    std::string v = get(name);
+    return v.empty() ? dflt : std::strtol(v.c_str(), nullptr, 10);
+  }
+  bool flag(const std::string& name) const {
+    std::string v = get(name);
+    return v == "true" || v == "1";
+  }
+  bool has(const std::string& name) const { return !get(name).empty(); }
+};
+
+api::TextServices python_text_services() {
+  api::TextServices t;
+  t.encode = [](const std::string& text, bool add, uint32_t truncate) {
+    json::Value a = json::Value::object();
+    a.set("text", text);
+    a.set("add_special_tokens", add);
+    if (truncate) a.set("truncate", truncate);
+    json::Value r = bridge::call("encode", a);
+    std::vector<uint32_t> ids;
+    for (auto& v : r["ids"].items()) ids.push_back(static_cast<uint32_t>(v.as_int()));
+    return ids;
+  };
+  t.encode_with_offsets = [](const std::string& text, bool add) {
+    json::Value a = json::Value::object();
+    a.set("text", text);
+    a.set("add_special_tokens", add);
+    a.set("offsets", true);
+    return bridge::call("encode", a)["tokens"];
+  };
+  t.chat_template = [](const json::Value& messages, const json::Value& tools, const std::string& tool_prompt) {
+    json::Value a = json::Value::object();
+    a.set("messages", messages);
+    if (!tools.is_null()) a.set("tools", tools);
+    a.set("tool_prompt", tool_prompt);
+    json::Value r = bridge::call("apply_chat_template", a);
+    if (!r["ok"].as_bool()) throw api::ApiError(422, r["error_type"].as_string(), r["error"].as_string());
+    return r["text"].as_string();
+  };
+  t.compile_grammar = [](const std::string& type, const json::Value& value) {
+    json::Value a = json::Value::object();
+    a.set("type", type);
+    a.set("value", value);
+    json::Value r = bridge::call("compile_grammar", a);
+    if (!r["ok"].as_bool()) throw api::validation_error(r["error"].as_string());
+    return std::make_pair(r["grammar"].as_string(), static_cast<uint32_t>(r["grammar_type"].as_int()));
+  };
+  return t;
+}
+
+// Worst-case batch for the memory probe of the shards: full-length prompts up to the prefill
+// budget, all sampling stages on, prompt logprobs and top tokens requested.
+pb::Batch warmup_batch(uint32_t max_input_tokens, uint32_t max_prefill_tokens, uint32_t max_total_tokens,
+                       uint32_t block_size) {
+  pb::Batch b;
+  uint32_t n_tokens = 0;
+  uint64_t id = 0;
+  while (n_tokens < max_prefill_tokens) {
+    const uint32_t len = std::min(max_input_tokens, max_prefill_tokens - n_tokens);
+    pb::Request r;
+    r.id = id++;
+    std::string text;
+    for (uint32_t i = 0; i < len; ++i) text += "_test ";
+    r.inputs = text;
+    pb::InputChunk c;
+    c.text = text;
+    r.input_chunks.push_back(c);
+    r.truncate = len;
+    r.add_special_tokens = true;
+    r.prefill_logprobs = true;
+    r.top_n_tokens = 20;
+    r.parameters.temperature = 0.9f;
+    r.parameters.top_k = 10;
+    r.parameters.top_p = 0.9f;
+    r.parameters.typical_p = 0.9f;
+    r.parameters.do_sample = false;
+    r.parameters.repetition_penalty = 1.2f;
+    r.parameters.frequency_penalty = 0.1f;
+    r.stopping_parameters.max_new_tokens = max_total_tokens > len ? max_total_tokens - len : 1;
+    r.stopping_parameters.ignore_eos_token = true;
+    b.requests.push_back(r);
+    n_tokens += len;
+  }
+  b.id = 0;
+  b.size = static_cast<uint32_t>(b.requests.size());
+  b.max_tokens = max_input_tokens * b.size;
+  b.max_blocks = (max_total_tokens + block_size - 1) / block_size;
+  return b;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  Args args(argc, argv);
+  if (args.flag("help")) {
+    std::cout << "tgi-b200-router --master-shard-uds-path PATH --tokenizer-name DIR [--port 3000] [--hostname 0.0.0.0]\n"
+                 "  [--max-concurrent-requests 128] [--max-best-of 2] [--max-stop-sequences 4] [--max-top-n-tokens 5]\n"
+                 "  [--max-input-tokens N] [--max-total-tokens N] [--max-batch-prefill-tokens N] [--max-batch-total-tokens N]\n"
+                 "  [--waiting-served-ratio 0.3] [--max-waiting-tokens 20] [--max-batch-size N] [--max-client-batch-size 4]\n"
+                 "  [--api-key KEY] [--payload-limit BYTES] [--disable-grammar-support] [--repo-root DIR]\n";
+    return 0;
+  }
+  try {
+    const std::string uds = args.get("master-shard-uds-path", "/tmp/text-generation-server");
+    const std::string tokenizer = args.get("tokenizer-name", args.get("model-id"));
+    std::string repo_root = args.get("repo-root");
+    if (repo_root.empty()) {
+      // the binary lives in <repo>/text-generation-inference_b200/router/
+      std::string self = argv[0];
+      size_t p = self.rfind('/');
+      repo_root = (p == std::string::npos ? std::string(".") : self.substr(0, p)) + "/../..";
+    }
+    bridge::init(repo_root);
+    json::Value la = json::Value::object();
+    la.set("tokenizer_name", tokenizer);
+    json::Value loaded = bridge::call("load", la);
+    if (!loaded["ok"].as_bool()) throw std::runtime_error("tokenizer load failed");
+
+    std::cerr << "[router] connecting to shards at " << uds << std::endl;
+    auto client = sched::ShardedClient::connect(uds, static_cast<int>(args.num("shard-connect-timeout", 1800)));
+    client->clear_cache(std::nullopt);
+    pb::InfoResponse info = client->info();
+
+    uint32_t max_input = static_cast<uint32_t>(args.num("max-input-tokens", 0));
+    uint32_t max_total = static_cast<uint32_t>(args.num("max-total-tokens", 0));
+    uint32_t max_prefill = static_cast<uint32_t>(args.num("max-batch-prefill-tokens", 4096));
+    if (max_input && max_total && max_input >= max_total)
+      throw std::runtime_error("`max_input_tokens` must be < `max_total_tokens`");
+    const uint32_t probe_input = max_input ? max_input : std::min<uint32_t>(max_prefill, 4095);
+    const uint32_t probe_total = max_total ? max_total : probe_input + 1;
+    if (!info.support_chunking && max_prefill < probe_input)
+      throw std::runtime_error("`max_batch_prefill_tokens` must be >= `max_input_tokens`");
+    std::cerr << "[router] warming up shards" << std::endl;
+    pb::WarmupResponse w = client->warmup(warmup_batch(probe_input, max_prefill, probe_total, std::max(1u, info.block_size)),
+                                          max_input ? std::optional<uint32_t>(max_input) : std::nullopt, max_prefill,
+                                          max_total ? std::optional<uint32_t>(max_total) : std::nullopt);
+    if (!max_input) max_input = w.max_input_tokens;
+    if (!max_total) max_total = w.max_total_tokens;
+    uint32_t max_batch_total = static_cast<uint32_t>(args.num("max-batch-total-tokens", 0));
+    if (w.max_supported_total_tokens) {
+      if (max_batch_total && max_batch_total > *w.max_supported_total_tokens)
+        std::cerr << "[router] `--max-batch-total-tokens` is larger than what the shards support; clamping" << std::endl;
+      if (!max_batch_total || max_batch_total > *w.max_supported_total_tokens)
+        max_batch_total = *w.max_supported_total_tokens;
+    } else if (!max_batch_total) {
+      max_batch_total = std::max<uint32_t>(16000, std::max(max_total, max_prefill));
+    }
+    if (max_total > max_batch_total)
+      throw std::runtime_error("`max_total_tokens` must be <= `max_batch_total_tokens`");
+    std::cerr << "[router] max_input_tokens=" << max_input << " max_total_tokens=" << max_total
+              << " max_batch_total_tokens=" << max_batch_total << " block_size=" << info.block_size << std::endl;
+
+    sched::Metrics metrics(max_input, max_total);
+    metrics.gauge_set("tgi_batch_max_total_tokens", max_batch_total);
+    sched::QueueConfig qc;
+    qc.requires_padding = info.requires_padding;
+    qc.block_size = std::max(1u, info.block_size);
+    qc.prefix_caching = info.use_prefix_caching && !args.flag("disable-prefix-caching");
+    qc.window_size = info.window_size;
+    qc.speculate = info.speculate;
+    qc.support_chunking = info.support_chunking;
+    qc.max_batch_total_tokens = max_batch_total;
+    sched::BackendConfig bc;
+    bc.max_batch_prefill_tokens = max_prefill;
+    bc.max_batch_total_tokens = max_batch_total;
+    bc.max_waiting_tokens = static_cast<uint32_t>(args.num("max-waiting-tokens", 20));
+    bc.waiting_served_ratio_x100 = static_cast<uint32_t>(std::atof(args.get("waiting-served-ratio", "0.3").c_str()) * 100);
+    if (args.has("max-batch-size")) bc.max_batch_size = static_cast<size_t>(args.num("max-batch-size", 0));
+    auto backend = std::make_shared<sched::Backend>(client, qc, bc, &metrics);
+    backend->start_thread();
+
+    api::RouterConfig rc;
+    rc.max_concurrent_requests = static_cast<size_t>(args.num("max-concurrent-requests", 128));
+    rc.max_best_of = static_cast<uint32_t>(args.num("max-best-of", 2));
+    rc.max_stop_sequences = static_cast<uint32_t>(args.num("max-stop-sequences", 4));
+    rc.max_top_n_tokens = static_cast<uint32_t>(args.num("max-top-n-tokens", 5));
+    rc.max_input_tokens = max_input;
+    rc.max_total_tokens = max_total;
+    rc.max_client_batch_size = static_cast<uint32_t>(args.num("max-client-batch-size", 4));
+    rc.disable_grammar_support = args.flag("disable-grammar-support");
+    rc.api_key = args.get("api-key");
+    rc.model_id = args.get("model-id", tokenizer);
+    rc.dtype = info.dtype;
+    rc.device_type = info.device_type;
+    rc.max_batch_total_tokens = max_batch_total;
+    api::Router router(backend, python_text_services(), rc, &metrics);
+
+    http::Server server(args.get("hostname", "0.0.0.0"), static_cast<int>(args.num("port", 3000)),
+                        static_cast<size_t>(args.num("payload-limit", 2000000)));
+    router.install(server);
+    g_server = &server;
+    std::signal(SIGINT, on_signal);
+    std::signal(SIGTERM, on_signal);
+    std::signal(SIGPIPE, SIG_IGN);
+    const int port = server.start();
+    std::cerr << "[router] Connected; listening on port " << port << std::endl;
+    server.serve_forever();
+    backend->stop();
+    std::cerr << "[router] shut down" << std::endl;
+    return 0;
+  } catch (const std::exception& e) {
+    std::cerr << "[router] fatal: " << e.what() << std::endl;
+    return 1;
+  }
+}

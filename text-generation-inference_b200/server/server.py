@@ -152,6 +152,48 @@ class TextGenerationService:
         return resp
 
 
+FRAMED_METHODS = ["Info", "ServiceDiscovery", "ClearCache", "FilterBatch", "Warmup", "Prefill", "Decode", "Health"]
+
+
+async def serve_framed(service: TextGenerationService, path: str):
+    """Second transport for the same service: length-prefixed protobuf frames over a unix socket.
+
+    The C++ router has no HTTP/2 stack, so it speaks this framing instead of gRPC; the messages are
+    the same ``generate.v3`` protobufs.  Request frame: ``u8 method index (FRAMED_METHODS), u32 LE
+    length, payload``; response frame: ``u8 status (0 ok / 1 error), u32 LE length, payload`` where
+    the payload of an error is its UTF-8 message.
+    """
+    import struct
+
+    async def handle(reader: asyncio.StreamReader, writer: asyncio.StreamWriter):
+        try:
+            while True:
+                try:
+                    head = await reader.readexactly(5)
+                except asyncio.IncompleteReadError:
+                    break
+                method, length = head[0], struct.unpack("<I", head[1:5])[0]
+                payload = await reader.readexactly(length) if length else b""
+                try:
+                    name = FRAMED_METHODS[method]
+                    req_cls = pb.message_class(pb.METHODS[name][0])
+                    resp = await getattr(service, name)(req_cls.FromString(payload), None)
+                    body, status = resp.SerializeToString(), 0
+                except Exception as err:  # noqa: BLE001
+                    log.exception("framed rpc %s failed", method)
+                    if torch.cuda.is_available():
+                        torch.cuda.empty_cache()
+                    body, status = f"{type(err).__name__}: {err}".encode(), 1
+                writer.write(bytes([status]) + struct.pack("<I", len(body)) + body)
+                await writer.drain()
+        finally:
+            writer.close()
+
+    if os.path.exists(path):
+        os.unlink(path)
+    return await asyncio.start_unix_server(handle, path=path)
+
+
 def generic_handler(service: TextGenerationService) -> grpc.GenericRpcHandler:
     handlers = {}
     for rpc, (req, resp) in pb.METHODS.items():
@@ -195,12 +237,15 @@ def serve(model_id: str, lora_adapters=None, revision: Optional[str] = None, sha
             options=[("grpc.max_receive_message_length", (1 << 31) - 1),
                      ("grpc.max_send_message_length", (1 << 31) - 1)],
         )
-        server.add_generic_rpc_handlers((generic_handler(TextGenerationService(model, Cache(), server_urls)),))
+        service = TextGenerationService(model, Cache(), server_urls)
+        server.add_generic_rpc_handlers((generic_handler(service),))
         server.add_insecure_port(local_url)
         await server.start()
+        framed = await serve_framed(service, local_url[len("unix://"):] + ".raw")
         log.info("Server started at %s", local_url)
         while signal_handler.KEEP_PROCESSING:
             await asyncio.sleep(0.5)
+        framed.close()
         await server.stop(grace=2)
 
     asyncio.run(serve_inner())

@@ -78,7 +78,7 @@ def load_tokenizer(model_path: Optional[str], revision: Optional[str] = None, tr
                    vocab_size: int = 259):
     """Hugging Face tokenizer of a model directory (left truncation/padding), else a ``ByteTokenizer``."""
     if model_path and os.path.isdir(model_path) and any(
-        os.path.exists(os.path.join(model_path, f)) for f in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json", "vocab.json")
+        os.path.exists(os.path.join(model_path, f)) for f in ("tokenizer.json", "tokenizer.model", "vocab.json")
     ):
         from transformers import AutoTokenizer
 
