@@ -306,8 +306,14 @@ def main():
         }
         print(json.dumps(out), flush=True)
     if world > 1:
+        # Leave without tearing the communicator down: destroying a process group whose collectives
+        # were captured into still-alive CUDA graphs can block forever.  All results are printed and
+        # every rank has passed the barrier, so a hard exit loses nothing.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 

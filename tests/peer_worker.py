@@ -1,0 +1,120 @@
+"""Worker of the multi-GPU peer-memory tests: run as N ranks by ``torch.distributed.run``.
+
+Every rank builds its own partial sums from a seed that depends on the rank, so each rank can also
+rebuild what the other ranks hold and compute the expected result locally in fp32.
+Prints ``PEER_WORKER_OK`` on success (rank 0) and exits non-zero on any mismatch.
+"""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from tgi_b200.ops import cuda as K  # noqa: E402
+from tgi_b200.ops import reference as ref  # noqa: E402
+from tgi_b200.parallel import dist as pdist  # noqa: E402
+from tgi_b200.parallel.peer import PeerComm  # noqa: E402
+
+
+def partial_of(rank: int, T: int, H: int, salt: int, device):
+    g = torch.Generator(device="cpu").manual_seed(1000 * salt + rank)
+    return (torch.randn(T, H, generator=g) * 0.5).to(torch.bfloat16).to(device)
+
+
+def main():
+    group, rank, world = pdist.initialize_torch_distributed()
+    device = torch.device("cuda", torch.cuda.current_device())
+    H = int(os.environ.get("PEER_H", "1024"))
+    max_T = 96
+    comm = PeerComm(group, rank, world, device, max_T, H)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    weight = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(device)
+    eps = 1e-5
+    salt = 0
+
+    def expected_sum(T):
+        acc = torch.zeros(T, H, dtype=torch.float32, device=device)
+        for r in range(world):
+            acc += partial_of(r, T, H, salt, device).float()
+        return acc.to(torch.bfloat16)
+
+    # ---- plain all-reduce, several shapes, repeated calls ------------------------------------
+    for T in (1, 5, 16, 96):
+        for _ in range(2):
+            salt += 1
+            t = partial_of(rank, T, H, salt, device).clone()
+            comm.all_reduce(t)
+            torch.cuda.synchronize()
+            assert comm.check() == 0
+            exp = expected_sum(T)
+            assert torch.equal(t, exp), f"all_reduce mismatch T={T} rank={rank}: {(t.float()-exp.float()).abs().max()}"
+
+    # ---- fused reduce + residual + RMSNorm (+ quant), a chain of three calls -----------------
+    for T in (3, 64):
+        rows_per = (T + world - 1) // world
+        row0 = rank * rows_per
+        res_ref = None
+        for step, quant in enumerate((False, True, True)):
+            salt += 1
+            comm.partial(T).copy_(partial_of(rank, T, H, salt, device))
+            out = comm.reduce_norm(T, weight, eps, 0.0, quant=quant, first=(step == 0))
+            torch.cuda.synchronize()
+            assert comm.check() == 0
+            summed = expected_sum(T)
+            normed, res_ref = ref.rms_norm(summed, res_ref, weight, eps, False)
+            mine = slice(row0, min(T, row0 + rows_per))
+            n_mine = max(0, mine.stop - mine.start)
+            if n_mine > 0:
+                assert torch.equal(comm.residual[:n_mine], res_ref[mine]), f"residual mismatch T={T} step={step}"
+            if not quant:
+                err = (out.float() - normed.float()).abs().max().item()
+                assert err <= 2e-2, f"norm mismatch {err}"
+            else:
+                xq, xs = out
+                deq = (xq.float().view(T, H // 128, 128) * xs.float().unsqueeze(-1)).view(T, H)
+                err = (deq - normed.float()).abs().max().item()
+                assert err <= 0.07 * normed.float().abs().max().item() + 1e-3, f"quant norm mismatch {err}"
+                # every rank must hold bit-identical gathered data
+                chk = torch.stack([xq.view(torch.uint8).float().sum(), xs.float().sum()])
+                gathered = [torch.empty_like(chk) for _ in range(world)]
+                torch.distributed.all_gather(gathered, chk, group=group)
+                for o in gathered:
+                    assert torch.equal(o, gathered[0]), "gathered rows differ between ranks"
+
+    # ---- CUDA graph replay: the call counters live in device memory ----------------------------
+    T = 32
+    salt += 1
+    src = partial_of(rank, T, H, salt, device)
+    exp = expected_sum(T)
+    res = torch.empty(T, H, dtype=torch.bfloat16, device=device)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):   # warm-up on the capture stream
+            t = src.clone()
+            comm.all_reduce(t)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    pdist.barrier(group)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        t = src.clone()
+        comm.all_reduce(t)
+        comm.all_reduce(t.zero_().add_(src))
+        res.copy_(t)
+    for _ in range(3):
+        res.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert comm.check() == 0
+        assert torch.equal(res, exp), "graph replay mismatch"
+
+    pdist.barrier(group)
+    comm.close()
+    if rank == 0:
+        print("PEER_WORKER_OK", flush=True)
+
+
+if __name__ == "__main__":
+    main()

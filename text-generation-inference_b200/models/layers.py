@@ -32,8 +32,8 @@ class FastLinear:
     def out_features(self):
         return self.weight.shape[0]
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, self.bias)
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias, out=out)
 
 
 class Fp8Linear:
@@ -82,18 +82,21 @@ class Fp8Linear:
     def wants_quantized_input(self) -> bool:
         return self.dense is None
 
-    def __call__(self, x, x_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, x, x_scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.dense is not None:
-            return self.dense(x)
+            return self.dense(x, out=out)
         if x_scale is None:
             x, x_scale = ops.fp8_quant_act(x)
-        out = ops.gemm_fp8_block(x, x_scale, self.qweight, self.scale, self.dtype,
-                                 self.bias if self.channel_scale is None else None)
-        if self.channel_scale is not None:
-            out = (out.float() * self.channel_scale).to(self.dtype)
-            if self.bias is not None:
-                out = out + self.bias
-        return out
+        if self.channel_scale is None:
+            return ops.gemm_fp8_block(x, x_scale, self.qweight, self.scale, self.dtype, self.bias, out=out)
+        y = ops.gemm_fp8_block(x, x_scale, self.qweight, self.scale, self.dtype, None)
+        y = (y.float() * self.channel_scale).to(self.dtype)
+        if self.bias is not None:
+            y = y + self.bias
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
 
 
 def get_linear(weight, bias):
@@ -155,7 +158,11 @@ class TensorParallelRowLinear:
         b = weights.get_tensor(f"{prefix}.bias") if bias and weights.process_group.rank() == 0 else None
         return cls(get_linear(w, b), weights.process_group, comm)
 
-    def __call__(self, x, x_scale=None, reduce: bool = True):
+    def __call__(self, x, x_scale=None, reduce: bool = True, out: Optional[torch.Tensor] = None):
+        """``out`` receives the (partial) product when given, e.g. a peer-memory buffer that the
+        fused reduction reads; it implies ``reduce=False`` semantics for the caller to finish."""
+        if out is not None:
+            return self.linear(x, x_scale, out=out) if x_scale is not None else self.linear(x, out=out)
         out = self.linear(x, x_scale) if x_scale is not None else self.linear(x)
         if reduce and self.process_group.size() > 1:
             if self.comm is not None:

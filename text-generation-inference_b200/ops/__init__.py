@@ -95,10 +95,18 @@ def activation(x, act):
     return ref.activation(x, act)
 
 
-def linear(x, weight, bias=None):
+def _into(out, y):
+    if out is None:
+        return y
+    out.copy_(y.view_as(out))
+    return out
+
+
+def linear(x, weight, bias=None, out=None):
+    """``x @ weight^T + bias``; ``out`` (bf16, contiguous) receives the result when given."""
     if use_native(x) and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
-        return native().gemm_bf16(x, weight, bias)
-    return ref.linear(x, weight, bias)
+        return native().gemm_bf16(x, weight, bias, out=out)
+    return _into(out, ref.linear(x, weight, bias))
 
 
 def fp8_quant_act(x, group=128):
@@ -107,10 +115,10 @@ def fp8_quant_act(x, group=128):
     return ref.fp8_quant_act(x, group)
 
 
-def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None):
+def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None, out=None):
     if use_native(xq):
-        return native().gemm_fp8_block(xq, xs, wq, ws, out_dtype, bias)
-    return ref.gemm_fp8_block(xq, xs, wq, ws, out_dtype, bias)
+        return native().gemm_fp8_block(xq, xs, wq, ws, out_dtype, bias, out=out)
+    return _into(out, ref.gemm_fp8_block(xq, xs, wq, ws, out_dtype, bias))
 
 
 def embedding(ids, table):

@@ -1,0 +1,363 @@
+// Tensor-parallel collectives over NVLink peer memory (one process per GPU, sm_100a).
+//
+// Every rank owns a "heap" allocated with cudaMalloc and mapped into all other ranks with CUDA IPC;
+// the same byte offset means the same logical buffer on every rank.  The kernels below replace the
+// NCCL all-reduce that follows every row-parallel linear in the reference
+// (layers/tensor_parallel.py:202-209) and the separate residual-add + RMSNorm (+ fp8 quantisation)
+// that follows it (layers/layernorm.py:161-187, layers/fp8.py:149-159):
+//
+//   peer_reduce_kernel: rows of the [T, H] partial sums are split across ranks.  The owner of a row
+//   pulls the eight partial rows with peer loads, adds them in fp32 in rank order, optionally adds
+//   the residual row it keeps locally, applies RMSNorm (+ 1x128 e4m3 quantisation), and pushes the
+//   finished row into the gather buffer of every rank with peer stores.  Norm work is divided by
+//   the number of ranks and every element crosses NVLink once in and once out.
+//
+// Synchronisation is block to block: block b of rank r only depends on block b of the other ranks,
+// through flags in the destination's heap that carry a per-block call counter kept in device
+// memory (so a captured CUDA graph replays correctly).  Every wait is bounded by wall-clock time;
+// a wait that runs out sets the status word and the block returns.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sm100.cuh"
+
+namespace {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxBlocks = 256;           // flag slots per phase
+constexpr float kFp8Max = 448.f;
+constexpr unsigned long long kPeerWaitNs = 2000000000ull;   // 2 s
+
+struct PeerArgs {
+  unsigned char* heap[kMaxRanks];   // heap base of every rank as mapped in this process
+  int rank, world;
+  int T, H;                         // rows and row length (elements) of the reduced matrix
+  long long off_partial;            // [T, H] bf16 partial sums, written by the local producer
+  long long off_gather;             // gathered result: [T, H] bf16, or [T, H] e4m3 when quantising
+  long long off_gscale;             // gathered activation scales, fp32 [H/128][pitch]
+  int gscale_pitch;
+  long long off_flags;              // uint32 [2][kMaxBlocks][kMaxRanks]
+  unsigned int* epoch;              // local, uint32 [kMaxBlocks]: calls made so far by each block
+  const __nv_bfloat16* residual_in; // local [rows_per_rank, H] or nullptr
+  __nv_bfloat16* residual_out;      // local [rows_per_rank, H] or nullptr
+  const __nv_bfloat16* weight;      // norm weight [H]
+  float eps, w_offset;
+  int* status;
+};
+
+struct __align__(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// 16-byte load that bypasses L1 (the data was written by another GPU or is read by one)
+__device__ __forceinline__ uint4 ld_cg16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+
+// Block-level flag exchange with the same block of every other rank.
+struct BlockSync {
+  const PeerArgs& a;
+  unsigned int e;          // value of this call
+  int* failed;             // shared-memory flag
+  __device__ BlockSync(const PeerArgs& args, int* failed_smem) : a(args), failed(failed_smem) {
+    e = a.epoch[blockIdx.x] + 1u;
+  }
+  __device__ unsigned int* flag(int owner, int phase, int src) const {
+    return reinterpret_cast<unsigned int*>(a.heap[owner] + a.off_flags) +
+           (static_cast<size_t>(phase) * kMaxBlocks + blockIdx.x) * kMaxRanks + src;
+  }
+  // all writes of this block made before the call become visible to the peers that see the flag
+  __device__ void signal(int phase) const {
+    __syncthreads();
+    if (threadIdx.x < a.world) {
+      __threadfence_system();
+      st_release_sys(flag(threadIdx.x, phase, a.rank), e);
+    }
+  }
+  // returns false (for the whole block) when a peer did not signal in time
+  __device__ bool wait(int phase) const {
+    if (threadIdx.x < a.world) {
+      const unsigned int* f = flag(a.rank, phase, threadIdx.x);
+      const unsigned long long t0 = global_ns();
+      unsigned int polls = 0;
+      while (static_cast<int>(ld_acquire_sys(f) - e) < 0) {
+        if ((++polls & 63u) == 0 && global_ns() - t0 > kPeerWaitNs) {
+          atomicExch(a.status, sm100::kErrPeerWait);
+          *failed = 1;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    return *failed == 0;
+  }
+  __device__ void finish() const {
+    __syncthreads();
+    if (threadIdx.x == 0) a.epoch[blockIdx.x] = e;
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x + 31) / 32) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+__device__ __forceinline__ uint2 quant8(const float (&f)[8], float scale) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float q = fminf(fmaxf(f[4 * h + i] / scale, -kFp8Max), kFp8Max);
+      acc |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    }
+    w[h] = acc;
+  }
+  return make_uint2(w[0], w[1]);
+}
+__device__ __forceinline__ float group16_max(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum of the `world` partial vectors (8 bf16 each) at element offset `elem` of the partial buffers,
+// in rank order, rounded to bf16 like the all-reduced bf16 tensor it stands for.
+__device__ __forceinline__ void pull_sum8(const PeerArgs& a, size_t elem, float (&acc)[8]) {
+  uint4 raw[kMaxRanks];
+#pragma unroll
+  for (int s = 0; s < kMaxRanks; ++s)
+    if (s < a.world) raw[s] = ld_cg16(a.heap[s] + a.off_partial + elem * 2);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+  for (int s = 0; s < kMaxRanks; ++s)
+    if (s < a.world) {
+      float f[8];
+      unpack8(raw[s], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = round_bf16(acc[j]);
+}
+
+// NORM = false: plain all-reduce (bf16 result in every rank's gather buffer).
+// NORM = true : + residual add, RMSNorm, and with QUANT 1x128 e4m3 quantisation of the result.
+template <bool NORM, bool QUANT, int VPT>
+__global__ void __launch_bounds__(1024)
+peer_reduce_kernel(const PeerArgs a) {
+  __shared__ float red[32];
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  BlockSync sync(a, &failed);
+  const int rows_per = (a.T + a.world - 1) / a.world;
+  const int row0 = a.rank * rows_per;
+  const int my_rows = max(0, min(a.T, row0 + rows_per) - row0);
+  const int nvec = a.H / 8;
+
+  sync.signal(0);                       // my producer kernel has finished: its partial rows may be read
+  bool ok = sync.wait(0);
+  if (ok) {
+    for (int lr = blockIdx.x; lr < my_rows; lr += gridDim.x) {
+      const int row = row0 + lr;
+      const size_t rbase = static_cast<size_t>(row) * a.H;
+      if (!NORM) {
+        for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+          float acc[8];
+          pull_sum8(a, rbase + v * 8, acc);
+          const uint4 packed = pack8(acc);
+#pragma unroll
+          for (int d = 0; d < kMaxRanks; ++d)
+            if (d < a.world) *reinterpret_cast<uint4*>(a.heap[d] + a.off_gather + (rbase + v * 8) * 2) = packed;
+        }
+      } else {
+        float s[VPT][8];
+        float sumsq = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int v = threadIdx.x + i * blockDim.x;
+          if (v < nvec) {
+            pull_sum8(a, rbase + v * 8, s[i]);
+            const size_t lbase = static_cast<size_t>(lr) * a.H + v * 8;
+            if (a.residual_in != nullptr) {
+              float r[8];
+              unpack8(*reinterpret_cast<const uint4*>(a.residual_in + lbase), r);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) s[i][j] = round_bf16(s[i][j] + r[j]);
+            }
+            if (a.residual_out != nullptr) *reinterpret_cast<uint4*>(a.residual_out + lbase) = pack8(s[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sumsq += s[i][j] * s[i][j];
+          }
+        }
+        const float rstd = rsqrtf(block_sum(sumsq, red) / a.H + a.eps);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int v = threadIdx.x + i * blockDim.x;
+          const bool active = v < nvec;
+          float y[8];
+          if (active) {
+            float w[8];
+            unpack8(*reinterpret_cast<const uint4*>(a.weight + v * 8), w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = round_bf16(s[i][j] * rstd * (w[j] + a.w_offset));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = 0.f;
+          }
+          if (QUANT) {
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
+            amax = group16_max(amax);
+            const float scale = fmaxf(amax, 1e-12f) / kFp8Max;
+            if (active) {
+              const uint2 q = quant8(y, scale);
+#pragma unroll
+              for (int d = 0; d < kMaxRanks; ++d)
+                if (d < a.world) {
+                  *reinterpret_cast<uint2*>(a.heap[d] + a.off_gather + rbase + v * 8) = q;
+                  if ((v & 15) == 0)
+                    reinterpret_cast<float*>(a.heap[d] + a.off_gscale)[static_cast<size_t>(v >> 4) * a.gscale_pitch + row] =
+                        scale;
+                }
+            }
+          } else if (active) {
+            const uint4 packed = pack8(y);
+#pragma unroll
+            for (int d = 0; d < kMaxRanks; ++d)
+              if (d < a.world) *reinterpret_cast<uint4*>(a.heap[d] + a.off_gather + (rbase + v * 8) * 2) = packed;
+          }
+        }
+      }
+    }
+    sync.signal(1);                     // my rows are in everybody's gather buffer
+    ok = sync.wait(1);                  // and everybody's rows are in mine
+  }
+  sync.finish();
+}
+
+template <bool NORM, bool QUANT>
+int launch_reduce(const PeerArgs& a, int blocks, cudaStream_t stream) {
+  const int nvec = a.H / 8;
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  if (NORM && nvec > 1024)
+    peer_reduce_kernel<NORM, QUANT, 2><<<blocks, threads, 0, stream>>>(a);
+  else
+    peer_reduce_kernel<NORM, QUANT, 1><<<blocks, threads, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---- heap management (set-up time only) ----------------------------------------------------
+int tgi_peer_alloc(long long bytes, void** ptr) {
+  if (cudaMalloc(ptr, static_cast<size_t>(bytes)) != cudaSuccess) return -1;
+  if (cudaMemset(*ptr, 0, static_cast<size_t>(bytes)) != cudaSuccess) return -2;
+  return cudaDeviceSynchronize() == cudaSuccess ? 0 : -3;
+}
+int tgi_peer_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
+int tgi_peer_export(void* ptr, unsigned char* handle64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) return -1;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+int tgi_peer_import(const unsigned char* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  const cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+int tgi_peer_unmap(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }
+int tgi_peer_max_blocks() { return kMaxBlocks; }
+
+// ---- the collective --------------------------------------------------------------------------
+// mode 0: all-reduce; 1: + residual + RMSNorm -> bf16; 2: + residual + RMSNorm + e4m3 quantisation.
+int tgi_peer_reduce(void* const* heaps, int rank, int world, int T, int H, long long off_partial, long long off_gather,
+                    long long off_gscale, int gscale_pitch, long long off_flags, unsigned int* epoch,
+                    const void* residual_in, void* residual_out, const void* weight, float eps, float w_offset,
+                    int mode, int blocks, int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -10;
+  if (H % 8 != 0 || blocks < 1 || blocks > kMaxBlocks) return -11;
+  if (mode != 0 && H > 16384) return -12;
+  if (mode == 2 && H % 128 != 0) return -13;
+  PeerArgs a;
+  for (int i = 0; i < kMaxRanks; ++i) a.heap[i] = i < world ? static_cast<unsigned char*>(heaps[i]) : nullptr;
+  a.rank = rank;
+  a.world = world;
+  a.T = T;
+  a.H = H;
+  a.off_partial = off_partial;
+  a.off_gather = off_gather;
+  a.off_gscale = off_gscale;
+  a.gscale_pitch = gscale_pitch;
+  a.off_flags = off_flags;
+  a.epoch = epoch;
+  a.residual_in = static_cast<const __nv_bfloat16*>(residual_in);
+  a.residual_out = static_cast<__nv_bfloat16*>(residual_out);
+  a.weight = static_cast<const __nv_bfloat16*>(weight);
+  a.eps = eps;
+  a.w_offset = w_offset;
+  a.status = status;
+  switch (mode) {
+    case 0: return launch_reduce<false, false>(a, blocks, stream);
+    case 1: return launch_reduce<true, false>(a, blocks, stream);
+    case 2: return launch_reduce<true, true>(a, blocks, stream);
+    default: return -14;
+  }
+}
+
+}  // extern "C"

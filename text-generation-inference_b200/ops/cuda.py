@@ -135,7 +135,8 @@ def _gemm_ctas(lib, st, M: int, N: int, max_ctas: Optional[int]) -> int:
     return ctas
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, max_ctas: Optional[int] = None):
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, max_ctas: Optional[int] = None,
+              out: Optional[torch.Tensor] = None):
     lib = load()
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
@@ -144,7 +145,10 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     M, K = x2.shape
     N = w.shape[0]
     assert w.shape[1] == K and w.is_contiguous()
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    else:
+        assert out.numel() == M * N and out.dtype == torch.bfloat16 and out.is_contiguous()
     if M == 0:
         return out.reshape(*lead, N)
     st = state(x.device)
@@ -154,13 +158,16 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     return out.reshape(*lead, N)
 
 
-def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None, max_ctas: Optional[int] = None):
+def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None, max_ctas: Optional[int] = None, out=None):
     lib = load()
     M, K = xq.shape
     N = wq.shape[0]
     assert wq.shape[1] == K and wq.is_contiguous() and xq.is_contiguous()
     assert out_dtype == torch.bfloat16
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
+    else:
+        assert out.shape == (M, N) and out.dtype == torch.bfloat16 and out.is_contiguous()
     if M == 0:
         return out
     st = state(xq.device)

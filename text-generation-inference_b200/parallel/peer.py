@@ -1,0 +1,190 @@
+"""Tensor-parallel communication over NVLink peer memory.
+
+The reference reduces the output of every row-parallel linear with an NCCL all-reduce and then runs
+residual-add + RMSNorm as separate kernels (``layers/tensor_parallel.py:202-209``,
+``layers/layernorm.py:161-187``).  Here each rank owns a *heap* (one ``cudaMalloc`` block) that is
+mapped into every other rank with CUDA IPC, and one kernel (``csrc/peer_comm.cu``) does
+reduce-scatter by peer loads, the residual/norm/quantisation math on the rows a rank owns, and the
+all-gather by peer stores.  ``torch.distributed`` is only used to exchange the IPC handles.
+
+Buffers at fixed offsets of every heap:
+
+    flags    uint32 [2][256][8]          block-to-block signals of the kernel
+    partial  bf16   [max_tokens, width]  written by the local producer (GEMM output, embedding rows)
+    gather   bf16   [max_tokens, width]  result rows pushed by their owners (reused for e4m3 bytes)
+    gscale   fp32   [width/128, pitch]   1x128 activation scales of the e4m3 result, K-block major
+
+The un-normalised residual stream of the rows a rank owns stays in ``self.residual`` on that rank and
+never crosses NVLink.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Tuple
+
+import torch
+
+from ..ops import cuda as K
+from . import dist as pdist
+
+FP8 = torch.float8_e4m3fn
+_ALIGN = 1024
+
+
+class _Span:
+    """Exposes a raw device range through ``__cuda_array_interface__`` so torch can wrap it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
+        }
+
+
+def tensor_from_ptr(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:
+    return torch.as_tensor(_Span(ptr, nbytes), device=device)
+
+
+def _round_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+def exchange_handles(group, rank: int, world: int, handle: bytes) -> List[bytes]:
+    """All-gather of the 64-byte IPC handles (works on NCCL and gloo groups)."""
+    import torch.distributed as dist
+
+    out: List[Optional[bytes]] = [None] * world
+    dist.all_gather_object(out, handle, group=group)
+    return [bytes(h) for h in out]
+
+
+class PeerComm:
+    """Peer-memory collectives of one tensor-parallel group (world <= 8, one node)."""
+
+    def __init__(self, group, rank: int, world: int, device: torch.device, max_tokens: int, width: int):
+        assert 1 <= world <= 8
+        self.group, self.rank, self.world, self.device = group, rank, world, device
+        self.max_tokens, self.width = int(max_tokens), int(width)
+        lib = self.lib = K.load()
+        for name in ("tgi_peer_alloc", "tgi_peer_free", "tgi_peer_export", "tgi_peer_import", "tgi_peer_unmap",
+                     "tgi_peer_max_blocks", "tgi_peer_reduce"):
+            getattr(lib, name).restype = ctypes.c_int
+        self.max_blocks = int(lib.tgi_peer_max_blocks())
+        self.pitch = _round_up(self.max_tokens, 4)
+        nflag = 2 * self.max_blocks * 8 * 4
+        nrows = self.max_tokens * self.width * 2
+        self.off_flags = 0
+        self.off_partial = _round_up(nflag, _ALIGN)
+        self.off_gather = self.off_partial + _round_up(nrows, _ALIGN)
+        self.off_gscale = self.off_gather + _round_up(nrows, _ALIGN)
+        self.heap_bytes = self.off_gscale + _round_up(max(self.width // 128, 1) * self.pitch * 4, _ALIGN)
+
+        torch.cuda.set_device(device)
+        base = ctypes.c_void_p()
+        rc = lib.tgi_peer_alloc(ctypes.c_longlong(self.heap_bytes), ctypes.byref(base))
+        if rc != 0:
+            raise K.KernelError(f"peer heap allocation of {self.heap_bytes} bytes failed ({rc})")
+        self.base = int(base.value)
+        self._mapped: List[int] = []
+        self.heaps = [0] * world
+        self.heaps[rank] = self.base
+        if world > 1:
+            handle = (ctypes.c_ubyte * 64)()
+            if lib.tgi_peer_export(ctypes.c_void_p(self.base), handle) != 0:
+                raise K.KernelError("cudaIpcGetMemHandle failed for the peer heap")
+            handles = exchange_handles(group, rank, world, bytes(handle))
+            for r, h in enumerate(handles):
+                if r == rank:
+                    continue
+                p = ctypes.c_void_p()
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                rc = lib.tgi_peer_import(buf, ctypes.byref(p))
+                if rc != 0:
+                    raise K.KernelError(f"cudaIpcOpenMemHandle failed for the heap of rank {r} (cuda error {-rc})")
+                self.heaps[r] = int(p.value)
+                self._mapped.append(int(p.value))
+        self._heap_arr = (ctypes.c_void_p * 8)(*(self.heaps + [0] * (8 - world)))
+        self._heap_t = tensor_from_ptr(self.base, self.heap_bytes, device)
+        self._partial = self._heap_t[self.off_partial:self.off_partial + nrows].view(torch.bfloat16)
+        self._gather = self._heap_t[self.off_gather:self.off_gather + nrows]
+        self._gscale = self._heap_t[self.off_gscale:self.heap_bytes].view(torch.float32)
+        self.epoch = torch.zeros(self.max_blocks, dtype=torch.int32, device=device)
+        rows_per = (self.max_tokens + world - 1) // world
+        self.residual = torch.zeros(rows_per, self.width, dtype=torch.bfloat16, device=device)
+        self.status = K.state(device).status
+        # every rank must have mapped every heap before anyone's kernel writes into a peer
+        pdist.barrier(group)
+
+    # ---- buffers -------------------------------------------------------------------------------
+    def partial(self, T: int, H: Optional[int] = None) -> torch.Tensor:
+        """``[T, H]`` bf16 view of the partial-sum buffer: the producer of a reduction writes here."""
+        H = H or self.width
+        assert T * H <= self.max_tokens * self.width, "reduction larger than the peer buffers"
+        return self._partial[: T * H].view(T, H)
+
+    def _gather_bf16(self, T: int, H: int) -> torch.Tensor:
+        return self._gather[: T * H * 2].view(torch.bfloat16).view(T, H)
+
+    def _gather_fp8(self, T: int, H: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        q = self._gather[: T * H].view(FP8).view(T, H)
+        s = self._gscale[: (H // 128) * self.pitch].view(H // 128, self.pitch)[:, :T].t()
+        return q, s
+
+    def _blocks(self, T: int) -> int:
+        return max(1, min(128, self.max_blocks, (T + self.world - 1) // self.world))
+
+    def _launch(self, T: int, H: int, mode: int, residual_in, residual_out, weight, eps: float, w_offset: float):
+        rc = self.lib.tgi_peer_reduce(
+            self._heap_arr, ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(T), ctypes.c_int(H),
+            ctypes.c_longlong(self.off_partial), ctypes.c_longlong(self.off_gather), ctypes.c_longlong(self.off_gscale),
+            ctypes.c_int(self.pitch), ctypes.c_longlong(self.off_flags), K._ptr(self.epoch),
+            K._ptr(residual_in), K._ptr(residual_out), K._ptr(weight), ctypes.c_float(eps), ctypes.c_float(w_offset),
+            ctypes.c_int(mode), ctypes.c_int(self._blocks(T)), K._ptr(self.status), K._stream())
+        K._check(rc, "peer_reduce")
+
+    # ---- collectives ---------------------------------------------------------------------------
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """In-place sum over ranks of a bf16 ``[..., H]`` tensor (other dtypes go through the group)."""
+        if self.world == 1:
+            return t
+        H = t.shape[-1] if t.dim() > 0 else 1
+        if t.dtype != torch.bfloat16 or H % 8 != 0 or not t.is_contiguous():
+            return pdist.all_reduce(t, self.group)
+        flat = t.view(-1, H)
+        cap = max(1, (self.max_tokens * self.width) // H)
+        for r0 in range(0, flat.shape[0], cap):
+            rows = flat[r0:r0 + cap]
+            T = rows.shape[0]
+            if rows.data_ptr() != self._partial.data_ptr():
+                self.partial(T, H).copy_(rows)
+            self._launch(T, H, 0, None, None, None, 0.0, 0.0)
+            rows.copy_(self._gather_bf16(T, H))
+        return t
+
+    def reduce_norm(self, T: int, weight: torch.Tensor, eps: float, w_offset: float = 0.0, quant: bool = False,
+                    first: bool = False):
+        """Sum the ranks' ``partial(T)`` rows, add the residual stream, RMSNorm (and quantise).
+
+        Returns the normalised activations of all ``T`` rows: a bf16 ``[T, H]`` tensor, or
+        ``(xq, xs)`` with 1x128 scales when ``quant``.  The tensors are views of the gather buffer and
+        are overwritten by the next collective.  ``first`` starts a new residual stream (the summed
+        rows themselves become the residual), as at the embedding.
+        """
+        H = self.width
+        assert T <= self.max_tokens and weight.shape[0] == H
+        self._launch(T, H, 2 if quant else 1, None if first else self.residual, self.residual, weight, eps, w_offset)
+        if quant:
+            return self._gather_fp8(T, H)
+        return self._gather_bf16(T, H)
+
+    def check(self) -> int:
+        return K.check_status(self.device)
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        pdist.barrier(self.group)
+        for p in self._mapped:
+            self.lib.tgi_peer_unmap(ctypes.c_void_p(p))
+        self._mapped = []
+        if self.base:
+            self.lib.tgi_peer_free(ctypes.c_void_p(self.base))
+            self.base = 0
