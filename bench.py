@@ -159,7 +159,10 @@ def main():
     weights = SyntheticWeights(cfg, dev, torch.bfloat16, process_group=pg, fp8_block=fp8)
     weights.weights_loader = Fp8Loader(weight_block_size=[128, 128]) if fp8 else DefaultWeightsLoader()
     t0 = time.time()
-    model = CausalDecoder(ModelConfig(cfg), weights)
+    from tgi_b200.parallel.peer import make_comm
+
+    comm = make_comm(pg, rank, world, dev, cfg["hidden_size"], max(args.prefill_chunk, args.concurrency))
+    model = CausalDecoder(ModelConfig(cfg), weights, comm=comm)
     torch.cuda.synchronize()
     load_s = time.time() - t0
     C, P, O = args.concurrency, args.prompt_len, args.output_len
@@ -289,7 +292,7 @@ def main():
             "config": {"model": args.model if not args.layers else f"{args.model}-{args.layers}L",
                        "global_batch": C, "seq_len": start_ctx + args.warmup, "prompt_len": start_ctx,
                        "nominal_prompt_len": P, "output_len": O,
-                       "parallelism": f"tp{world}", "block_size": BLOCK_SIZE, "l2": "inputs larger than L2",
+                       "parallelism": f"tp{world}", "collectives": "nccl" if comm is None else "peer-memory kernels", "block_size": BLOCK_SIZE, "l2": "inputs larger than L2",
                        "timed": "CUDA events around K graph replays, max over ranks",
                        "setup": "fast-setup (random KV, development)" if args.fast_setup else "real prefill"},
             "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d_bytes,

@@ -54,3 +54,16 @@ def test_peer_collectives_across_gpus(world):
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), os.path.join(ROOT, "tests", "peer_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "PEER_WORKER_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("world", [2, 8])
+def test_tensor_parallel_engine_on_peer_memory(world, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", TP_WORKER_DIR=str(tmp_path / "ckpt"))
+    env.pop("TGI_B200_COMM", None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29700 + world), os.path.join(ROOT, "tests", "tp_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])

@@ -1,0 +1,124 @@
+"""Worker of the tensor-parallel engine test: run as N ranks by ``torch.distributed.run``.
+
+Loads a small Llama checkpoint through the model registry twice in the same process: once with the
+peer-memory collectives (fused reduce + residual + RMSNorm) and once with the process-group
+collectives (``TGI_B200_COMM=nccl``).  Both must agree with each other and with a dense fp32 CPU
+forward of the unsharded weights; decode through captured CUDA graphs must give the eager tokens.
+Prints ``TP_WORKER_OK`` from rank 0.
+"""
+import os
+import random
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from tgi_b200.models import get_model  # noqa: E402
+from tgi_b200.models.flash_causal_lm import FlashCausalLMBatch  # noqa: E402
+from tgi_b200.models.graphs import DecodeGraphs  # noqa: E402
+from tgi_b200.ops import cuda as K  # noqa: E402
+from tgi_b200.parallel import dist as pdist  # noqa: E402
+from tgi_b200.proto import generate_v3 as pb  # noqa: E402
+from tgi_b200.utils.synthetic import (llama_config, llama_state_dict, reference_llama_forward,  # noqa: E402
+                                      write_llama_checkpoint)
+
+
+def request(i, n_new, blocks):
+    r = pb.Request(id=i, inputs="")
+    r.parameters.temperature = 1.0
+    r.parameters.top_p = 1.0
+    r.parameters.typical_p = 1.0
+    r.parameters.repetition_penalty = 1.0
+    r.stopping_parameters.max_new_tokens = n_new
+    r.stopping_parameters.ignore_eos_token = True
+    r.blocks.extend(blocks)
+    return r
+
+
+def generate(runner, dev, prompts, n_new):
+    cursor, reqs = 1, []
+    for i, p in enumerate(prompts):
+        nb = (len(p) + n_new + 15) // 16
+        reqs.append(request(i, n_new, range(cursor, cursor + nb)))
+        cursor += nb
+    if runner.num_blocks < cursor:
+        runner.init_kv_cache(cursor)
+    batch = FlashCausalLMBatch.from_tokenized(pb.Batch(id=0, requests=reqs, size=len(reqs)), prompts,
+                                              runner.tokenizer, torch.bfloat16, dev)
+    toks = {i: [] for i in range(len(prompts))}
+    first = {}
+    orig = runner.forward
+
+    def spy(meta):
+        out = orig(meta)
+        first.setdefault("logits", out.detach().float().clone())
+        return out
+
+    runner.forward = spy
+    try:
+        while batch is not None:
+            gens, batch, _ = runner.generate_token(batch)
+            for g in gens:
+                toks[g.request_id].extend(g.tokens.token_ids)
+    finally:
+        runner.forward = orig
+    return toks, first["logits"]
+
+
+def main():
+    group, rank, world = pdist.initialize_torch_distributed()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    path = os.environ["TP_WORKER_DIR"]
+    cfg = llama_config(hidden=512, layers=3, heads=8, kv_heads=8 if world > 2 else 2, intermediate=1024, vocab=4096,
+                       max_pos=1024)
+    if rank == 0:
+        write_llama_checkpoint(path, cfg, std=0.05)
+    pdist.barrier(group)
+
+    rng = random.Random(0)
+    prompts = [[rng.randrange(3, 4096) for _ in range(n)] for n in (45, 100, 17, 33)]
+    n_new = 6
+
+    peer = get_model(path, dtype="bfloat16", max_prefill_tokens=512)
+    assert peer.model.comm is not None, "peer-memory communicator was not created"
+    toks_peer, logits_peer = generate(peer, dev, prompts, n_new)
+    assert K.check_status(dev) == 0
+
+    os.environ["TGI_B200_COMM"] = "nccl"
+    base = get_model(path, dtype="bfloat16", max_prefill_tokens=512)
+    assert base.model.comm is None
+    toks_base, logits_base = generate(base, dev, prompts, n_new)
+    os.environ.pop("TGI_B200_COMM")
+
+    scale = logits_base.abs().max().item()
+    diff = (logits_peer - logits_base).abs().max().item()
+    assert diff <= 0.04 * scale, f"peer vs group collectives: {diff} (scale {scale})"
+
+    sd = llama_state_dict(cfg, std=0.05)
+    for i, p in enumerate(prompts):
+        want = reference_llama_forward(sd, cfg, torch.tensor(p))[-1]
+        got = logits_peer[i].cpu()
+        err = (got - want).abs().max().item()
+        assert err <= 0.06 * want.abs().max().item() + 0.02, f"prompt {i}: logits differ from the dense forward by {err}"
+
+    # decode through captured graphs (peer kernels inside the graph) must reproduce the eager tokens
+    peer.graphs = DecodeGraphs(peer, 256, buckets=[4])
+    peer.graphs.capture_all()
+    toks_graph, _ = generate(peer, dev, prompts, n_new)
+    assert K.check_status(dev) == 0
+    agree = sum(toks_graph[i] == toks_peer[i] for i in toks_peer)
+    assert agree == len(prompts), (toks_graph, toks_peer)
+    same = sum(toks_base[i][:2] == toks_peer[i][:2] for i in toks_peer)
+    assert same >= len(prompts) - 1, (toks_base, toks_peer)
+
+    pdist.barrier(group)
+    torch.cuda.synchronize()
+    if rank == 0:
+        print("TP_WORKER_OK", flush=True)
+    sys.stdout.flush()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()

@@ -101,7 +101,11 @@ def get_model(
     prefix = ""
     if model_type in ("gpt2",) and weights.has_tensor("transformer.wte.weight"):
         prefix = "transformer"
-    model = CausalDecoder(text_cfg, weights, prefix=prefix,
+    from ..parallel.peer import make_comm
+
+    hidden = int(text_cfg.get("hidden_size", text_cfg.get("n_embd", text_cfg.get("d_model", 0))) or 0)
+    comm = make_comm(process_group, rank, world, device, hidden, int(max_prefill_tokens or 4096)) if hidden else None
+    model = CausalDecoder(text_cfg, weights, comm=comm, prefix=prefix,
                           max_positions=_max_positions(text_cfg, max_input_tokens))
     spec_head = None
     runner = FlashCausalLM(model, tokenizer, tdtype, device, rank, world, speculate,

@@ -207,7 +207,7 @@ class Attention:
                  * self.k_norm.float()).to(qkv.dtype)
         return torch.cat([q.reshape(T, nq), k.reshape(T, nk), qkv[:, nq + nk:]], dim=-1)
 
-    def __call__(self, x, x_scale, meta: ForwardMeta, rotary: RotaryTable, kv, reduce: bool = True):
+    def __call__(self, x, x_scale, meta: ForwardMeta, rotary: RotaryTable, kv, reduce: bool = True, out=None):
         d = self.dims
         qkv = self.qkv(x, x_scale)
         if meta.adapter_data is not None:
@@ -224,7 +224,7 @@ class Attention:
                                    self.v_scale if v_cache.dtype == torch.float8_e4m3fn else None,
                                    meta.max_q, meta.max_kv)
         attn = attn.reshape(attn.shape[0], d.num_heads * d.head_dim)
-        out = self.o(attn, reduce=reduce)
+        out = self.o(attn, reduce=reduce, out=out)
         if meta.adapter_data is not None:
             out = meta.adapter_data.apply_row(self.layer_idx, "o_proj", attn, out)
         return out
@@ -261,18 +261,18 @@ class DenseMLP:
         lin = self.down.linear
         self.down_quant = isinstance(lin, Fp8Linear) and lin.wants_quantized_input and self.gated
 
-    def __call__(self, x, x_scale=None, reduce: bool = True, meta: Optional[ForwardMeta] = None):
+    def __call__(self, x, x_scale=None, reduce: bool = True, meta: Optional[ForwardMeta] = None, out=None):
         h = self.gate_up(x, x_scale)
         if meta is not None and meta.adapter_data is not None:
             h = meta.adapter_data.apply_gate_up(self.layer_idx, x, h)
         if self.gated:
             if self.down_quant and (meta is None or meta.adapter_data is None):
                 hq, hs = ops.act_and_mul_quant(h, self.act)
-                return self.down(hq, hs, reduce=reduce)
+                return self.down(hq, hs, reduce=reduce, out=out)
             a = ops.act_and_mul(h, self.act)
         else:
             a = ops.activation(h, self.act).to(h.dtype)
-        out = self.down(a, reduce=reduce)
+        out = self.down(a, reduce=reduce, out=out)
         if meta is not None and meta.adapter_data is not None:
             out = meta.adapter_data.apply_row(self.layer_idx, "down_proj", a, out)
         return out
@@ -319,7 +319,10 @@ class SparseMoE:
                 self.shared_gate = FastLinear(weights.get_tensor(f"{prefix}.{arch.moe_shared_gate}.weight"))
         self.expert_parallel = None  # set by parallel.expert.enable()
 
-    def __call__(self, x, x_scale=None, reduce: bool = True, meta=None):
+    def __call__(self, x, x_scale=None, reduce: bool = True, meta=None, out=None):
+        if out is not None:
+            out.copy_(self(x, x_scale, reduce=False, meta=meta))
+            return out
         logits = self.router(x)
         w, idx = ops.moe_topk_softmax(logits, self.top_k, self.renorm)
         if self.expert_parallel is not None:
@@ -410,6 +413,30 @@ class DecoderLayer:
             mlp = mlp * rs
         return mlp, residual
 
+    @property
+    def fusable_tp(self) -> bool:
+        """True when the layer is a plain pre-norm block whose two reductions can each be fused with
+        the residual add and the following RMSNorm."""
+        a = self.arch
+        return (not a.parallel_residual and a.norm == "rms" and self.norm2 is not None and self.post_attn is None
+                and self.post_mlp is None and self.dims.residual_scale == 1.0)
+
+    def fused_tp(self, x, meta: ForwardMeta, rotary, kv, next_norm: Norm, next_quant: bool, comm):
+        """Tensor-parallel layer on peer memory.  ``x`` is this layer's *normalised* input (a tensor or
+        ``(xq, scales)``); returns the normalised input of the next layer in the same form.  Both
+        row-parallel GEMMs write their partial sums into the peer buffer, and one kernel per
+        reduction sums them across ranks, adds the residual stream kept by the row's owner, applies
+        the next RMSNorm (and quantises) and gathers the result on every rank."""
+        T = meta.input_ids.shape[0]
+        xq, xs = x if isinstance(x, tuple) else (x, None)
+        self.attn(xq, xs, meta, rotary, kv, reduce=False, out=comm.partial(T))
+        n2 = self.norm2
+        x2 = comm.reduce_norm(T, n2.weight, n2.eps, 1.0 if n2.unit_offset else 0.0, quant=self.mlp_in_quant)
+        x2q, x2s = x2 if isinstance(x2, tuple) else (x2, None)
+        self.mlp(x2q, x2s, reduce=False, meta=meta, out=comm.partial(T))
+        return comm.reduce_norm(T, next_norm.weight, next_norm.eps, 1.0 if next_norm.unit_offset else 0.0,
+                                quant=next_quant)
+
 
 class CausalDecoder:
     """Weights + forward of one causal LM shard."""
@@ -419,6 +446,8 @@ class CausalDecoder:
         self.arch = arch_for(cfg.model_type)
         pg = weights.process_group
         self.pg = pg
+        self.comm = comm
+        self._fusable: Optional[bool] = None
         self.dims = dims = derive_dims(cfg, self.arch, pg.size())
         self.dtype, self.device = weights.dtype, weights.device
         a = self.arch
@@ -471,7 +500,36 @@ class CausalDecoder:
             h, _ = self.embed_norm(h, None)
         return h
 
+    def _fused_tp_ok(self, meta: ForwardMeta) -> bool:
+        comm = self.comm
+        if comm is None or not hasattr(comm, "reduce_norm") or self.pg.size() == 1:
+            return False
+        if self._fusable is None:
+            d = self.dims
+            self._fusable = (all(l.fusable_tp for l in self.layers) and self.final_norm.kind == "rms"
+                             and d.embed_scale == 1.0 and self.pos_embed is None and self.embed_norm is None
+                             and comm.width == d.hidden and self.dtype == torch.bfloat16)
+        return (self._fusable and meta.adapter_data is None and meta.inputs_embeds is None
+                and meta.input_ids.shape[0] <= comm.max_tokens)
+
+    def _forward_hidden_fused_tp(self, meta: ForwardMeta, kv_cache) -> torch.Tensor:
+        comm = self.comm
+        T = meta.input_ids.shape[0]
+        # vocab-parallel embedding rows (zero for ids of other ranks) are the first partial sums
+        comm.partial(T).copy_(self.embed.local_rows(meta.input_ids))
+        l0 = self.layers[0]
+        x = comm.reduce_norm(T, l0.norm1.weight, l0.norm1.eps, 1.0 if l0.norm1.unit_offset else 0.0,
+                             quant=l0.attn_in_quant, first=True)
+        last = len(self.layers) - 1
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1] if i < last else None
+            x = layer.fused_tp(x, meta, self.rotary, kv_cache[i], nxt.norm1 if nxt else self.final_norm,
+                               nxt.attn_in_quant if nxt else False, comm)
+        return x
+
     def forward_hidden(self, meta: ForwardMeta, kv_cache) -> torch.Tensor:
+        if self._fused_tp_ok(meta):
+            return self._forward_hidden_fused_tp(meta, kv_cache)
         h = meta.inputs_embeds if meta.inputs_embeds is not None else self.embed_tokens(meta.input_ids, meta.positions)
         residual = None
         for i, layer in enumerate(self.layers):

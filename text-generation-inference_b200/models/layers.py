@@ -187,11 +187,17 @@ class TensorParallelEmbedding:
         self.comm = comm
         self.weight = torch.cat([w, w.new_zeros(1, w.shape[1])], dim=0) if pg.size() > 1 else w
 
-    def __call__(self, ids: torch.Tensor) -> torch.Tensor:
+    def local_rows(self, ids: torch.Tensor) -> torch.Tensor:
+        """This rank's contribution to the embedding: the row for ids it owns, zeros for the others."""
         if self.process_group.size() == 1:
             return ops.embedding(ids, self.weight)
         local = torch.where((ids < self.min_id) | (ids >= self.max_id), self.null_idx, ids - self.min_id)
-        out = ops.embedding(local, self.weight)
+        return ops.embedding(local.to(ids.dtype), self.weight)
+
+    def __call__(self, ids: torch.Tensor) -> torch.Tensor:
+        if self.process_group.size() == 1:
+            return ops.embedding(ids, self.weight)
+        out = self.local_rows(ids)
         if self.reduce:
             if self.comm is not None:
                 return self.comm.all_reduce(out)

@@ -188,3 +188,15 @@ class PeerComm:
         if self.base:
             self.lib.tgi_peer_free(ctypes.c_void_p(self.base))
             self.base = 0
+
+
+def make_comm(group, rank: int, world: int, device: torch.device, hidden: int, max_tokens: int):
+    """Peer-memory communicator of a tensor-parallel group, or ``None`` when it does not apply
+    (one rank, CPU run, ``TGI_B200_COMM=nccl`` for the library baseline, or a ``FakeGroup``)."""
+    import os
+
+    if world == 1 or device.type != "cuda" or isinstance(group, pdist.FakeGroup):
+        return None
+    if os.environ.get("TGI_B200_COMM", "peer") == "nccl":
+        return None
+    return PeerComm(group, rank, world, device, max_tokens, hidden)
