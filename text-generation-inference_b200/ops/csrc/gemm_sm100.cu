@@ -23,8 +23,11 @@
 // [c*U/G, (c+1)*U/G), so every SM streams the same number of weight bytes whatever the shape (a
 // tensor-parallel shard with 10 weight slabs keeps all 148 SMs busy).  A tile whose K range is
 // shared by several CTAs is finished through an fp32 workspace: every contributor stores its
-// partial tile, the last one to arrive (atomic counter per tile) sums them in CTA order, so the
-// result does not depend on arrival order.
+// partial tile and counts its arrival; after its own main loop each contributor waits (bounded)
+// for the others and reduces its own slice of the tile's columns, summing the partials in CTA
+// order, so the work of the fix-up is spread over the contributors and the result does not depend
+// on arrival order.  Problems with fewer tiles than SMs use whole tiles or a few aligned K splits
+// instead when that is cheaper (see launch()).
 //
 // Roles inside a CTA (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner
 // (warps 2, 3 idle; the four give their registers away with setmaxnreg), warps 4..11 = promotion /
@@ -51,6 +54,15 @@ struct TileCfg {
   static constexpr int kWBytes = TN * 128;
   static constexpr int kStageBytes = kXBytes + kWBytes;   // 48 KB
 };
+
+constexpr int kMaxGrid = 160;              // upper bound of the grid size (one CTA per SM)
+constexpr int kSplitPolls = 1 << 20;       // polls of a split-tile counter before giving up (about 0.1 s)
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ void report(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
@@ -128,6 +140,16 @@ struct UnitIter {
 // wscale: weight scales [ceil(N/128), K/128] row-major
 // ws: 2 partial-tile slots per CTA; counters: one int per output tile (self-resetting)
 // ------------------------------------------------------------------------------------------------
+#ifdef TGI_GEMM_EXP
+static int g_exp_host = 0;
+__device__ int g_exp = 0;   // 1: no promotion FMAs, 2: no TMEM loads either, 3: no MMAs
+#define EXP_IS(x) ((g_exp & 7) == (x))
+#define EXP_GE(x) ((g_exp & 7) >= (x))
+#else
+#define EXP_IS(x) false
+#define EXP_GE(x) false
+#endif
+
 template <int MH, int TN, int STAGES, bool FP8>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -147,11 +169,12 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   uint64_t* tmem_empty = tmem_full + 2;      // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   int* flag = reinterpret_cast<int*>(tmem_holder + 1);
+  int* cslots = flag + 1;                    // [kMaxGrid] workspace slot of every contributor of a split tile
   {
     // self-check: the carve-up above must fit in the dynamic shared memory of the launch
     uint32_t dyn_bytes;
     asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
-    if (reinterpret_cast<uint8_t*>(flag + 1) - smem_raw > static_cast<ptrdiff_t>(dyn_bytes)) {
+    if (reinterpret_cast<uint8_t*>(cslots + kMaxGrid) - smem_raw > static_cast<ptrdiff_t>(dyn_bytes)) {
       report(status, kErrSmemLayout);
       return;
     }
@@ -211,8 +234,15 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
           for (int h = 0; h < MH; ++h) tma_load_2d_hint(st + h * 16384, &tmX, &full[s], kb * BK, m0 + h * 128, pol_x);
 #pragma unroll
-          for (int h = 0; h < TN / 128; ++h)
+          for (int h = 0; h < TN / 128; ++h) {
+#ifdef TGI_GEMM_EXP
+            if (g_exp & 8) {
+              tma_load_2d_hint(st + Cfg::kXBytes + h * 16384, &tmW, &full[s], 0, ((n0 / 128 + h) * sch.KB + kb) * 128, pol_w);
+              continue;
+            }
+#endif
             tma_load_2d_hint(st + Cfg::kXBytes + h * 16384, &tmW, &full[s], kb * BK, n0 + h * 128, pol_w);
+          }
           if (FP8) tma_load_2d(sc_ring + (it % SC_STAGES) * TM, &tmS, &full[s], m0, kb);
           issued = it + 1;
         }
@@ -250,6 +280,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             for (int k = 0; k < 4; ++k) {   // 4 MMAs of 32 bytes of K each per 128-byte row
               const uint32_t accumulate = FP8 ? (k > 0) : (!seg_start || k > 0);
               const uint32_t d = tmem_base + b * kBufCols + h * TN;
+              if (EXP_IS(3)) continue;
               if (FP8) mma_f8f6f4(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
               else mma_f16(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
             }
@@ -275,6 +306,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     int seg = 0;
     int seg_kb0 = 0;
     bool ok = true;
+    int pend_tile[2];      // tiles this CTA holds only a part of (at most its first and its last)
+    int npend = 0;
     UnitIter ui(u0, sch);
     for (int it = 0; it < nunits && ok; ++it, ui.next(sch)) {
       const int kb = ui.kb;
@@ -293,7 +326,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         ok = mbar_wait(&tmem_full[b], (it >> 1) & 1);
         if (!ok) { report(status, kErrEpilogueWait); break; }
         tc_fence_after();
-        if (warp_active) {
+        if (warp_active && !EXP_GE(2)) {
           const float s = sc_ring[(it % SC_STAGES) * TM + m_local] *
                           __ldg(&wscale[static_cast<size_t>((n0 + n_off) >> 7) * sch.KB + kb]);
           uint32_t v[2][32];
@@ -304,7 +337,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             tmem_ld_wait(cur);
             if (c + 32 < kCols) tmem_ld_32x32b_x32(lane_addr + b * kBufCols + c + 32, v[((c >> 5) + 1) & 1]);
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) acc.fma_pair((c + j) >> 1, cur[j], cur[j + 1], s);
+            for (int j = 0; j < 32; j += 2) {
+              if (EXP_IS(1)) { if (j == 0) acc.fma_pair((c + j) >> 1, cur[j], cur[j + 1], s); continue; }
+              acc.fma_pair((c + j) >> 1, cur[j], cur[j + 1], s);
+            }
           }
         }
         tc_fence_before();
@@ -336,9 +372,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       const int m = m0 + m_local;
       const int nb = n0 + n_off;                              // first output column of this thread
       const bool whole = seg_kb0 == 0 && kb == sch.KB - 1;
-      bool store = whole;
       if (!whole) {
-        // partial tile: store to this CTA's slot (head slot if the tile is the CTA's first, else tail slot)
+        // Partial tile: publish the fp32 partial sums in this CTA's slot (head slot if the tile is the
+        // CTA's first, else tail slot) and count the arrival.  The tile is finished after the main
+        // loop, when every contributor reduces its own slice of the columns (see below).
         const int first_tile = static_cast<int>(u0 / sch.KB);
         const int slot = blockIdx.x * 2 + (tile == first_tile ? 0 : 1);
         float4* wsp = reinterpret_cast<float4*>(ws + static_cast<size_t>(slot) * kTileElems) + et;
@@ -347,35 +384,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           wsp[(j >> 2) * kEpiThreads] = make_float4(acc.get(j), acc.get(j + 1), acc.get(j + 2), acc.get(j + 3));
         __threadfence();
         epi_barrier();
-        const long long t_lo = static_cast<long long>(tile) * sch.KB, t_hi = t_lo + sch.KB - 1;
-        const int c_lo = sch.owner(t_lo), c_hi = sch.owner(t_hi);
-        if (et == 0) {
-          const int old = atomicAdd(&counters[tile], 1);
-          const int last = (old == c_hi - c_lo);
-          if (last) counters[tile] = 0;   // self-cleaning: ready for the next launch / graph replay
-          *flag = last;
-        }
-        epi_barrier();
-        const bool last = *flag != 0;
-        epi_barrier();                    // everyone has read the flag before it can be rewritten
-        if (last) {
-          __threadfence();
-          acc.zero();
-          for (int c = c_lo; c <= c_hi; ++c) {
-            const int c_first_tile = static_cast<int>(sch.begin(c) / sch.KB);
-            const int cslot = c * 2 + (tile == c_first_tile ? 0 : 1);
-            const float4* src = reinterpret_cast<const float4*>(ws + static_cast<size_t>(cslot) * kTileElems) + et;
-#pragma unroll
-            for (int j = 0; j < kCols; j += 4) {
-              const float4 t = __ldcg(src + (j >> 2) * kEpiThreads);
-              acc.set_pair(j >> 1, acc.get(j) + t.x, acc.get(j + 1) + t.y);
-              acc.set_pair((j >> 1) + 1, acc.get(j + 2) + t.z, acc.get(j + 3) + t.w);
-            }
-          }
-          store = true;
-        }
+        if (et == 0) atomicAdd(&counters[tile], 1);
+        pend_tile[npend++] = tile;
+        continue;
       }
-      if (store && m < M && nb < N) {
+      if (m < M && nb < N) {
         __nv_bfloat16* crow = C + static_cast<size_t>(m) * N + nb;
         const bool vec_ok = (N % 8 == 0);
 #pragma unroll
@@ -398,6 +411,73 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
               if (nb + j + e < N) crow[j + e] = __float2bfloat16(f[e]);
           }
         }
+      }
+    }
+
+    // ---- finish the tiles this CTA shares with other CTAs ----
+    // Every contributor of a split tile has published its partial sums by now or will soon: all
+    // CTAs of the grid are resident (one per SM) and none waits before it has published everything.
+    // Contributor i of n reduces float4 columns [32 i / n, 32 (i+1) / n) of all rows, summing the
+    // partials in CTA order (so the result does not depend on timing), and stores them.  The tile
+    // counter counts n arrivals, then n departures; the last departure resets it for the next launch.
+    for (int p = 0; p < npend && ok; ++p) {
+      const int tile = pend_tile[p];
+      const int tn = tile / sch.m_tiles, tm = tile - tn * sch.m_tiles;
+      const int n0 = tn * TN, m0 = tm * TM;
+      const long long t_lo = static_cast<long long>(tile) * sch.KB, t_hi = t_lo + sch.KB - 1;
+      const int c_lo = sch.owner(t_lo), c_hi = sch.owner(t_hi);
+      const int n = c_hi - c_lo + 1;
+      const int mine = blockIdx.x - c_lo;
+      for (int c = c_lo + et; c <= c_hi; c += kEpiThreads)
+        cslots[c - c_lo] = c * 2 + (tile == static_cast<int>(sch.begin(c) / sch.KB) ? 0 : 1);
+      if (et == 0) {
+        int polls = 0;
+        int seen;
+        while ((seen = ld_acquire_gpu(&counters[tile])) < n && ++polls < kSplitPolls) __nanosleep(64);
+        *flag = seen >= n;
+      }
+      epi_barrier();
+      ok = *flag != 0;
+      if (!ok) {
+        report(status, kErrSplitKWait);
+        break;
+      }
+      const int jc0 = mine * (kCols / 4) / n, jc1 = (mine + 1) * (kCols / 4) / n;
+      const int m = m0 + m_local;
+      const int nb = n0 + n_off;
+      const float4* wsb = reinterpret_cast<const float4*>(ws) + et;
+      for (int jc = jc0; jc < jc1; ++jc) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < n; ++i) {
+          const float4 t = __ldcg(wsb + static_cast<size_t>(cslots[i]) * (kTileElems / 4) + jc * kEpiThreads);
+          sum.x += t.x;
+          sum.y += t.y;
+          sum.z += t.z;
+          sum.w += t.w;
+        }
+        const int col = nb + jc * 4;
+        if (m < M && col < N) {
+          float f[4] = {sum.x, sum.y, sum.z, sum.w};
+          if (bias != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col + e < N) f[e] += __bfloat162float(bias[col + e]);
+          }
+          __nv_bfloat16* cp = C + static_cast<size_t>(m) * N + col;
+          if ((N & 3) == 0) {
+            __nv_bfloat162 o[2] = {__floats2bfloat162_rn(f[0], f[1]), __floats2bfloat162_rn(f[2], f[3])};
+            *reinterpret_cast<uint2*>(cp) = *reinterpret_cast<uint2*>(o);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col + e < N) cp[e] = __float2bfloat16(f[e]);
+          }
+        }
+      }
+      epi_barrier();   // all reads of the partials and of cslots are done
+      if (et == 0) {
+        const int old = atomicAdd(&counters[tile], 1);
+        if (old == 2 * n - 1) counters[tile] = 0;
       }
     }
   }
@@ -452,6 +532,11 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
   const uint64_t pitch = static_cast<uint64_t>(K) * (FP8 ? 1 : 2);
   // both operands are fetched in boxes of 128 rows x 128 bytes (one swizzle atom wide)
   int rc = make_map_2d(&tmW, dt, W, N, K, pitch, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+#ifdef TGI_GEMM_EXP
+  if (g_exp_host & 8)   // weights pre-tiled: every 128 x 128-byte box contiguous in memory
+    rc = make_map_2d(&tmW, dt, W, static_cast<uint64_t>(N) * (pitch / 128), 128 / (FP8 ? 1 : 2), 128, 128, BK,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+#endif
   if (rc) return rc;
   rc = make_map_2d(&tmX, dt, X, M, K, pitch, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
@@ -463,7 +548,7 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
     tmS = tmX;
   }
   // stages + (fp8) activation-scale ring [STAGES+2][TM] + alignment slack + barriers
-  const size_t smem = STAGES * Cfg::kStageBytes + (FP8 ? (STAGES + 2) * Cfg::TM * 4 : 0) + 1024 + 256;
+  const size_t smem = STAGES * Cfg::kStageBytes + (FP8 ? (STAGES + 2) * Cfg::TM * 4 : 0) + 1024 + 256 + kMaxGrid * 4;
   auto kern = gemm_streamk_kernel<MH, TN, STAGES, FP8>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -473,9 +558,31 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
   }
   const long long units =
       static_cast<long long>((N + TN - 1) / TN) * ((M + Cfg::TM - 1) / Cfg::TM) * ((K + BK - 1) / BK);
+  // Grid size.  Splitting a tile between CTAs costs a 128 KB fp32 partial per contributor (as much
+  // traffic as 8 K blocks of weights), so small problems prefer whole tiles or a few aligned splits:
+  //   stream-K over all SMs:      ceil(units / max_ctas) K blocks per CTA, plus the fix-up (~2 blocks)
+  //   tiles x s aligned splits:   ceil(KB / s) K blocks per CTA, s = 1 needs no fix-up at all
+  const int KBn = (K + BK - 1) / BK;
+  const int tiles = static_cast<int>(units / KBn);
+  if (max_ctas > kMaxGrid) max_ctas = kMaxGrid;
   int grid = max_ctas;
   if (grid > units) grid = static_cast<int>(units);
   if (grid < 1) grid = 1;
+  if (tiles <= max_ctas) {
+    // Rough costs in microseconds, from timelines measured on B200: a K block takes about 0.4 us per
+    // CTA; every partial tile costs 128 KB written and read through L2 by all CTAs at once (about
+    // 0.05 us each at ~5 TB/s) and a split adds ~3 us of publish / wait / reduce latency.
+    const double kUnit = 0.4, kPartial = 0.05, kSync = 3.0;
+    const double partials_sk = static_cast<double>(grid + tiles < 2 * grid ? grid + tiles : 2 * grid);
+    double best = static_cast<double>((units + grid - 1) / grid) * kUnit + partials_sk * kPartial + kSync;
+    for (int s = 1; s <= max_ctas / tiles && s <= KBn; ++s) {
+      const double c = static_cast<double>((KBn + s - 1) / s) * kUnit + (s > 1 ? tiles * s * kPartial + kSync : 0.0);
+      if (c < best) {
+        best = c;
+        grid = tiles * s;
+      }
+    }
+  }
   kern<<<grid, kThreads, smem, stream>>>(tmW, tmX, tmS, wscale, static_cast<__nv_bfloat16*>(C),
                                          static_cast<const __nv_bfloat16*>(bias), M, N, K, ws, counters, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -493,15 +600,24 @@ long long tgi_gemm_workspace_floats(int M, int ctas) {
 
 // Output tiles of a problem (the counters array needs one int per tile).
 int tgi_gemm_num_tiles(int M, int N) {
-  if (M > 128) return ((N + 127) / 128) * ((M + 255) / 256);
-  return ((N + 255) / 256) * ((M + 127) / 128);
+  const int a = ((N + 127) / 128) * ((M + 255) / 256);
+  const int b = ((N + 255) / 256) * ((M + 127) / 128);
+  return a > b ? a : b;   // upper bound over both tile shapes
 }
+
+#ifdef TGI_GEMM_EXP
+void tgi_gemm_set_exp(int v) { g_exp_host = v; cudaMemcpyToSymbol(g_exp, &v, sizeof(int)); }
+#endif
+
+// Token counts up to this limit use the 128 x 256 tile (weights-wide); larger ones the 256 x 128 tile.
+static int g_wide_m = 128;
+void tgi_gemm_set_wide_m(int m) { g_wide_m = m < 128 ? 128 : m; }
 
 int tgi_gemm_bf16(const void* X, const void* W, void* C, const void* bias, int M, int N, int K, int max_ctas,
                   float* ws, int* counters, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0) return -10;  // TMA row pitch must be a multiple of 16 bytes
-  if (M > 128)
+  if (M > g_wide_m)
     return launch<2, 128, 4, false>(X, nullptr, 0, W, nullptr, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
   return launch<1, 256, 4, false>(X, nullptr, 0, W, nullptr, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
 }
@@ -511,7 +627,7 @@ int tgi_gemm_fp8_block(const void* X, const float* xs_t, int xs_pitch, const voi
                        cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 128 != 0 || xs_pitch % 4 != 0) return -10;
-  if (M > 128)
+  if (M > g_wide_m)
     return launch<2, 128, 4, true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
   return launch<1, 256, 4, true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
 }

@@ -53,6 +53,9 @@ def load():
                  "tgi_gemm_num_tiles", "tgi_attn_decode_splits"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
+    wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
+    if wide:
+        _LIB.tgi_gemm_set_wide_m(c_int(int(wide)))
     return _LIB
 
 
@@ -105,6 +108,7 @@ def check_status(device: Optional[torch.device] = None) -> int:
     code = int(st.status.item())
     if code != 0:
         st.status.zero_()
+        st.counters.zero_()    # a kernel that gave up may have left split-tile counters half-way
     return code
 
 
