@@ -206,3 +206,39 @@ def test_shard_grpc_endpoint(stack):
     assert info.block_size == 16 and info.support_chunking and info.use_prefix_caching
     c.health()
     c.close()
+
+
+def test_python_client_sync_and_async(stack):
+    import asyncio
+
+    from tgi_b200.client import AsyncClient, Client
+    from tgi_b200.client.errors import ValidationError
+
+    base = f"http://127.0.0.1:{stack['port']}"
+    client = Client(base)
+    assert client.health()
+    assert "model_id" in client.info()
+    resp = client.generate("hello world", max_new_tokens=4, decoder_input_details=True)
+    assert resp.details.generated_tokens == 4 and len(resp.details.tokens) == 4 and len(resp.details.prefill) == 11
+    events = list(client.generate_stream("hello world", max_new_tokens=4))
+    assert len(events) == 4 and events[-1].generated_text == resp.generated_text
+    assert events[-1].details.finish_reason.value == "length"
+    chat = client.chat([{"role": "user", "content": "hi"}], max_tokens=3)
+    assert chat.choices[0].message.role == "assistant" and chat.usage.completion_tokens == 3
+    chunks = list(client.chat([{"role": "user", "content": "hi"}], max_tokens=3, stream=True))
+    assert chunks and chunks[0].choices[0].delta.role == "assistant"
+    comp = client.completion("hello", max_tokens=3)
+    assert comp.choices[0].finish_reason == "length"
+    assert len(client.tokenize("hello world")) == 11
+    with pytest.raises(ValidationError):
+        client.generate("hello", max_new_tokens=100000)
+
+    async def run():
+        ac = AsyncClient(base)
+        r = await ac.generate("hello world", max_new_tokens=4)
+        ev = [e async for e in ac.generate_stream("hello world", max_new_tokens=4)]
+        c = await ac.chat([{"role": "user", "content": "hi"}], max_tokens=2)
+        return r, ev, c
+
+    r, ev, c = asyncio.run(run())
+    assert r.generated_text == resp.generated_text and len(ev) == 4 and c.usage.completion_tokens == 2
