@@ -21,6 +21,7 @@ import torch
 from ..proto import generate_v3 as pb
 from .cache import Cache
 from .interceptor import ExceptionInterceptor
+from .tracing import TracingInterceptor, tracer
 
 log = logging.getLogger("tgi_b200.server")
 
@@ -80,7 +81,8 @@ class TextGenerationService:
         batch = self.cache.pop(request.batch_id)
         if batch is None:
             raise ValueError(f"Batch ID {request.batch_id} not found in cache.")
-        filtered = batch.filter(list(request.request_ids))
+        with tracer().span("filter"):
+            filtered = batch.filter(list(request.request_ids))
         self.cache.set(filtered)
         return pb.FilterBatchResponse(batch=filtered.to_pb())
 
@@ -108,9 +110,11 @@ class TextGenerationService:
             if cached is None:
                 raise ValueError(f"Batch ID {request.cached_batch.id} not found in cache.")
             t = time.time_ns()
-            batch = self.model.batch_type.concatenate([cached, batch])
+            with tracer().span("concatenate"):
+                batch = self.model.batch_type.concatenate([cached, batch])
             concat_ns = time.time_ns() - t
-        generations, next_batch, timings = self.model.generate_token(batch)
+        with tracer().span("generate_token", attributes={"batch_size": len(batch)}):
+            generations, next_batch, timings = self.model.generate_token(batch)
         self._check_kernels()
         self.cache.set(next_batch)
         resp = pb.PrefillResponse(generations=[g.to_pb() for g in generations], forward_ns=timings[0],
@@ -136,11 +140,13 @@ class TextGenerationService:
         concat_ns = None
         if len(batches) > 1:
             t = time.time_ns()
-            batch = self.model.batch_type.concatenate(batches)
+            with tracer().span("concatenate"):
+                batch = self.model.batch_type.concatenate(batches)
             concat_ns = time.time_ns() - t
         else:
             batch = batches[0]
-        generations, next_batch, timings = self.model.generate_token(batch)
+        with tracer().span("generate_token", attributes={"batch_size": len(batch)}):
+            generations, next_batch, timings = self.model.generate_token(batch)
         self._check_kernels()
         self.cache.set(next_batch)
         resp = pb.DecodeResponse(generations=[g.to_pb() for g in generations], forward_ns=timings[0],
@@ -233,7 +239,7 @@ def serve(model_id: str, lora_adapters=None, revision: Optional[str] = None, sha
                 dtype=dtype, kv_cache_dtype=kv_cache_dtype, trust_remote_code=trust_remote_code,
                 max_input_tokens=max_input_tokens)
         server = grpc.aio.server(
-            interceptors=[ExceptionInterceptor(lambda: signal_handler.set_keep_processing(False))],
+            interceptors=[ExceptionInterceptor(lambda: signal_handler.set_keep_processing(False)), TracingInterceptor()],
             options=[("grpc.max_receive_message_length", (1 << 31) - 1),
                      ("grpc.max_send_message_length", (1 << 31) - 1)],
         )
