@@ -107,7 +107,14 @@ def get_model(
     comm = make_comm(process_group, rank, world, device, hidden, int(max_prefill_tokens or 4096)) if hidden else None
     model = CausalDecoder(text_cfg, weights, comm=comm, prefix=prefix,
                           max_positions=_max_positions(text_cfg, max_input_tokens))
-    spec_head = None
+    from .speculative import find_speculator, load_speculator
+
+    spec_path = find_speculator(path)
+    if spec_path is not None and (spec_path / "config.json").exists() and (
+            spec_path != path or (path / "medusa_lm_head.safetensors").exists()):
+        head, n_spec = load_speculator(spec_path, device, tdtype, process_group, model.head)
+        model.speculator = head
+        speculate = speculate or n_spec
     runner = FlashCausalLM(model, tokenizer, tdtype, device, rank, world, speculate,
                            resolve_kv_dtype(kv_cache_dtype, tdtype), max_prefill_tokens,
                            eos_token_ids(path, cfg))

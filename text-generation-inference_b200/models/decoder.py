@@ -447,6 +447,7 @@ class CausalDecoder:
         pg = weights.process_group
         self.pg = pg
         self.comm = comm
+        self.speculator = None                   # Medusa / MLP speculator head (models/speculative.py)
         self._fusable: Optional[bool] = None
         self.dims = dims = derive_dims(cfg, self.arch, pg.size())
         self.dtype, self.device = weights.dtype, weights.device
@@ -551,7 +552,9 @@ class CausalDecoder:
         h = self.forward_hidden(meta, kv_cache)
         if meta.lm_head_indices is not None:
             h = h[meta.lm_head_indices.long()]
-        return self.logits(h), None
+        logits = self.logits(h)
+        spec = self.speculator(h, logits) if self.speculator is not None else None
+        return logits, spec
 
 
 def alibi_slopes(n: int) -> torch.Tensor:

@@ -376,7 +376,8 @@ class FlashCausalLM(Model):
         return meta, row_owner
 
     def forward(self, meta: ForwardMeta) -> torch.Tensor:
-        logits, _spec = self.model.forward(meta, self.kv_cache)
+        logits, spec = self.model.forward(meta, self.kv_cache)
+        self.last_speculative_logits = spec     # [rows, n_heads, V] when a speculator head is attached
         return logits
 
     # -- one engine step -------------------------------------------------------------------------
@@ -448,6 +449,7 @@ class FlashCausalLM(Model):
             spec_lens = [0 if seqs[i].prefilling else len(seqs[i].speculative_ids) for i in active]
             Smax = 1 + max(spec_lens)
             if all(l == spec_lens[0] for l in spec_lens):
+                sel_rows = sample_rows
                 sel = logits if len(sample_rows) == logits.shape[0] else logits[
                     torch.tensor(sample_rows, dtype=torch.long, device=logits.device)]
                 speculated = None
@@ -461,6 +463,7 @@ class FlashCausalLM(Model):
                     rows = rows_of[i][-(l + 1):] if not seqs[i].prefilling else [rows_of[i][-1]]
                     idx.extend(rows + [rows[-1]] * (Smax - len(rows)))
                     spec.append((seqs[i].speculative_ids if not seqs[i].prefilling else []) + [-1] * (Smax - 1 - l))
+                sel_rows = idx
                 sel = logits[torch.tensor(idx, dtype=torch.long, device=logits.device)]
                 speculated = torch.tensor(spec, dtype=torch.long, device=logits.device)
             need_history = (chooser.any_rep or chooser.any_freq or bool(chooser.watermarks) or batch.speculate > 0)
@@ -484,8 +487,14 @@ class FlashCausalLM(Model):
                 spec_next = None
                 all_logprobs = None
             else:
+                spec_scores = getattr(self, "last_speculative_logits", None)
+                if spec_scores is not None and not use_graph:
+                    spec_scores = spec_scores[torch.tensor(sel_rows, dtype=torch.long, device=logits.device)]
+                    spec_scores = spec_scores[:, : batch.speculate]
+                else:
+                    spec_scores = None
                 next_ids, next_lp, all_logprobs, accepted, spec_next = chooser(
-                    history, sel, batch.speculate, speculated, None)
+                    history, sel, batch.speculate, speculated, spec_scores)
                 next_ids_l = next_ids.tolist()
                 next_lp_l = next_lp.tolist()
                 accepted_l = accepted.tolist()
