@@ -64,6 +64,15 @@ class Seq:
         return bool(self.request.prefill_logprobs)
 
 
+def _adapter_index(request) -> int:
+    """Index of the LoRA adapter a request asks for (0: base model or unknown adapter)."""
+    if not request.HasField("adapter_id") or not request.adapter_id:
+        return 0
+    from ..utils.adapter import ADAPTER_TO_INDEX
+
+    return ADAPTER_TO_INDEX.get(request.adapter_id, 0)
+
+
 class FlashCausalLMBatch(Batch):
     def __init__(self, batch_id: int, seqs: List[Seq], chooser: NextTokenChooser, device, speculate: int = 0):
         self.batch_id = batch_id
@@ -180,6 +189,7 @@ class FlashCausalLMBatch(Batch):
                 request=r, ids=list(ids), prompt_len=prompt_len, cache_len=cache_len, blocks=blocks, slots=slots,
                 stopping=stopping, top_n=int(r.top_n_tokens), prefix_offset=max(0, prompt_len - 5),
                 read_offset=prompt_len, first_chunk=first_chunk,
+                adapter_index=_adapter_index(r),
             ))
             params.append(r.parameters)
         chooser = NextTokenChooser.from_pb(params, device, tokenizer)
@@ -373,6 +383,11 @@ class FlashCausalLM(Model):
             block_tables=dev[5], max_q=max(counts) if counts else 0, max_kv=int(kv_lens.max()) if B else 0,
             lm_head_indices=dev[6] if len(head_rows) != T else None,
         )
+        lora = getattr(self, "lora", None)
+        if lora is not None and any(s.adapter_index > 0 for s in seqs):
+            token_adapter = np.repeat(np.asarray([s.adapter_index for s in seqs], dtype=np.int64),
+                                      np.asarray(counts, dtype=np.int64))
+            meta.adapter_data = lora.batch_data(token_adapter, self.device)
         return meta, row_owner
 
     def forward(self, meta: ForwardMeta) -> torch.Tensor:
@@ -392,7 +407,8 @@ class FlashCausalLM(Model):
         B = len(seqs)
 
         use_graph = (self.graphs is not None and not batch.prefilling and batch.speculate == 0
-                     and self.graphs.supports(batch))
+                     and self.graphs.supports(batch)
+                     and not (getattr(self, "lora", None) is not None and any(s.adapter_index > 0 for s in seqs)))
         if use_graph:
             logits, row_owner = self.graphs.run(batch, counts)
         else:
