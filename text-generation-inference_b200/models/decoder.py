@@ -471,8 +471,8 @@ class CausalDecoder:
                 self.layers.append(DecoderLayer(a, cfg, dims, px + a.layer.format(i=i), weights, i, comm))
         self.final_norm = Norm.load(a, px + a.final_norm, weights, dims.eps)
         head_name = px + a.lm_head if not a.lm_head.startswith("lm_head") or not prefix else a.lm_head
-        candidates = [head_name, a.lm_head, px + a.embed]
-        if cfg.get("tie_word_embeddings") and not weights.has_tensor(f"{head_name}.weight"):
+        candidates = [head_name, px + a.lm_head, a.lm_head, px + a.embed]
+        if cfg.get("tie_word_embeddings") and not any(weights.has_tensor(f"{c}.weight") for c in candidates[:3]):
             candidates = [px + a.embed]
         with weights.use_loader(DefaultWeightsLoader()):
             for cand in candidates:

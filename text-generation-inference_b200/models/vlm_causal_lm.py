@@ -1,0 +1,286 @@
+"""Vision-language runner: image chunks -> vision tower -> projector -> rows of ``inputs_embeds``.
+
+Reference: ``models/vlm_causal_lm.py:301-1133`` (batch with image inputs, image-token expansion,
+encoder-output scatter), the vision towers ``custom_modeling/{clip,siglip}.py`` and the projectors of
+``llava_next.py`` / ``flash_pali_gemma_modeling.py``.
+
+A request's input is a list of chunks (text or image bytes).  Tokenisation replaces every image by
+``n`` copies of the model's image token, where ``n`` is the number of feature rows the vision side
+produces for one image.  At prefill the images of the chunk being processed are encoded (one ViT
+forward per step for all of them), projected to the text hidden size and written over the
+embeddings of the placeholder rows; the language model then runs on ``inputs_embeds`` unchanged
+(same paged attention, same CUDA-graph decode, since decode steps never contain image rows).
+
+Covered families: LLaVA-style (CLIP tower, 2-layer MLP projector, optional class-token drop; the
+base-resolution view of llava_next) and PaliGemma-style (SigLIP tower, linear projector, embedding
+scale).  Towers are plain pre-norm ViTs evaluated with ``F.scaled_dot_product_attention``: the image
+side is compute-light next to the decoder and runs once per request.
+"""
+from __future__ import annotations
+
+import io
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..utils.weights import Weights, weight_files
+from .decoder import CausalDecoder
+from .flash_causal_lm import FlashCausalLM, FlashCausalLMBatch
+
+CLIP_MEAN, CLIP_STD = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)
+SIGLIP_MEAN, SIGLIP_STD = (0.5, 0.5, 0.5), (0.5, 0.5, 0.5)
+
+
+# ---- vision tower ------------------------------------------------------------------------------
+class _VitLayer:
+    def __init__(self, w: Weights, prefix: str, heads: int, eps: float, act: str):
+        g = w.get_tensor
+        self.ln1 = (g(f"{prefix}.layer_norm1.weight"), g(f"{prefix}.layer_norm1.bias"))
+        self.ln2 = (g(f"{prefix}.layer_norm2.weight"), g(f"{prefix}.layer_norm2.bias"))
+        a = f"{prefix}.self_attn"
+        self.qkv_w = torch.cat([g(f"{a}.q_proj.weight"), g(f"{a}.k_proj.weight"), g(f"{a}.v_proj.weight")], 0)
+        self.qkv_b = torch.cat([g(f"{a}.q_proj.bias"), g(f"{a}.k_proj.bias"), g(f"{a}.v_proj.bias")], 0)
+        self.o = (g(f"{a}.out_proj.weight"), g(f"{a}.out_proj.bias"))
+        self.fc1 = (g(f"{prefix}.mlp.fc1.weight"), g(f"{prefix}.mlp.fc1.bias"))
+        self.fc2 = (g(f"{prefix}.mlp.fc2.weight"), g(f"{prefix}.mlp.fc2.bias"))
+        self.heads, self.eps, self.act = heads, eps, act
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:          # x [B, S, C]
+        B, S, C = x.shape
+        h = F.layer_norm(x, (C,), *self.ln1, self.eps)
+        qkv = F.linear(h, self.qkv_w, self.qkv_b).view(B, S, 3, self.heads, C // self.heads).permute(2, 0, 3, 1, 4)
+        attn = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2]).transpose(1, 2).reshape(B, S, C)
+        x = x + F.linear(attn, *self.o)
+        h = F.layer_norm(x, (C,), *self.ln2, self.eps)
+        h = F.linear(h, *self.fc1)
+        h = F.gelu(h, approximate="tanh") if self.act in ("gelu_pytorch_tanh", "gelu_fast", "gelu_new") else (
+            h * torch.sigmoid(1.702 * h) if self.act == "quick_gelu" else F.gelu(h))
+        return x + F.linear(h, *self.fc2)
+
+
+class VisionTower:
+    """CLIP- or SigLIP-style ViT; returns the hidden states of layer ``feature_layer``."""
+
+    def __init__(self, cfg: dict, w: Weights, prefix: str, kind: str, feature_layer: int = -1):
+        self.kind = kind
+        self.image_size, self.patch = int(cfg["image_size"]), int(cfg["patch_size"])
+        self.hidden, heads = int(cfg["hidden_size"]), int(cfg["num_attention_heads"])
+        eps = float(cfg.get("layer_norm_eps", 1e-5 if kind == "clip" else 1e-6))
+        act = cfg.get("hidden_act", "quick_gelu" if kind == "clip" else "gelu_pytorch_tanh")
+        e = f"{prefix}.embeddings"
+        self.patch_w = w.get_tensor(f"{e}.patch_embedding.weight")
+        self.patch_b = w.get_tensor(f"{e}.patch_embedding.bias") if w.has_tensor(f"{e}.patch_embedding.bias") else None
+        self.pos = w.get_tensor(f"{e}.position_embedding.weight")
+        self.cls = w.get_tensor(f"{e}.class_embedding") if kind == "clip" else None
+        self.pre_ln = None
+        if kind == "clip":
+            name = "pre_layrnorm" if w.has_tensor(f"{prefix}.pre_layrnorm.weight") else "pre_layernorm"
+            self.pre_ln = (w.get_tensor(f"{prefix}.{name}.weight"), w.get_tensor(f"{prefix}.{name}.bias"), eps)
+        n_layers = int(cfg["num_hidden_layers"])
+        use = n_layers + feature_layer + 1 if feature_layer < 0 else feature_layer
+        self.layers = [_VitLayer(w, f"{prefix}.encoder.layers.{i}", heads, eps, act) for i in range(use)]
+        self.post_ln = None
+        if kind == "siglip" and use == n_layers and w.has_tensor(f"{prefix}.post_layernorm.weight"):
+            self.post_ln = (w.get_tensor(f"{prefix}.post_layernorm.weight"), w.get_tensor(f"{prefix}.post_layernorm.bias"), eps)
+
+    @property
+    def num_patches(self) -> int:
+        return (self.image_size // self.patch) ** 2
+
+    def __call__(self, pixels: torch.Tensor) -> torch.Tensor:       # [B, 3, S, S] -> [B, tokens, C]
+        x = F.conv2d(pixels.to(self.patch_w.dtype), self.patch_w, self.patch_b, stride=self.patch)
+        x = x.flatten(2).transpose(1, 2)
+        if self.cls is not None:
+            x = torch.cat([self.cls.view(1, 1, -1).expand(x.shape[0], -1, -1), x], dim=1)
+        x = x + self.pos[: x.shape[1]].unsqueeze(0)
+        if self.pre_ln is not None:
+            x = F.layer_norm(x, (x.shape[-1],), *self.pre_ln)
+        for layer in self.layers:
+            x = layer(x)
+        if self.post_ln is not None:
+            x = F.layer_norm(x, (x.shape[-1],), *self.post_ln)
+        return x
+
+
+# ---- image preprocessing -------------------------------------------------------------------------
+def preprocess_image(data: bytes, size: int, mean, std) -> torch.Tensor:
+    """Decode, convert to RGB, resize to ``size`` x ``size`` (bicubic) and normalise: ``[3, size, size]``."""
+    from PIL import Image
+
+    img = Image.open(io.BytesIO(data)).convert("RGB").resize((size, size), Image.BICUBIC)
+    arr = torch.from_numpy(np.asarray(img, dtype=np.float32) / 255.0).permute(2, 0, 1)
+    m = torch.tensor(mean).view(3, 1, 1)
+    s = torch.tensor(std).view(3, 1, 1)
+    return (arr - m) / s
+
+
+# ---- batch ---------------------------------------------------------------------------------------
+class VlmCausalLMBatch(FlashCausalLMBatch):
+    """Adds, per request, the decoded images and the prompt positions of their placeholder tokens."""
+
+    image_token_id: int = 0
+    tokens_per_image: int = 0
+    image_size: int = 224
+    norm = (CLIP_MEAN, CLIP_STD)
+
+    @classmethod
+    def batch_tokenized_inputs(cls, requests, tokenizer) -> List[List[int]]:
+        out = []
+        cls._pending_images = []
+        for r in requests:
+            ids: List[int] = []
+            images: List[Tuple[int, torch.Tensor]] = []     # (first placeholder position, pixels)
+            chunks = list(r.input_chunks.chunks) if r.HasField("input_chunks") else []
+            if not chunks:
+                ids = list(tokenizer(r.inputs, truncation=False, add_special_tokens=r.add_special_tokens)["input_ids"])
+            first_text = True
+            for c in chunks:
+                if c.WhichOneof("chunk") == "text":
+                    ids.extend(tokenizer(c.text, truncation=False,
+                                         add_special_tokens=r.add_special_tokens and first_text)["input_ids"])
+                    first_text = False
+                else:
+                    pixels = preprocess_image(c.image.data, cls.image_size, *cls.norm)
+                    images.append((len(ids), pixels))
+                    ids.extend([cls.image_token_id] * cls.tokens_per_image)
+            if r.truncate and len(ids) > r.truncate:
+                cut = len(ids) - r.truncate
+                if any(pos < cut for pos, _ in images):
+                    raise ValueError("truncation would cut through an image; raise `truncate` or shorten the prompt")
+                ids = ids[cut:]
+                images = [(pos - cut, px) for pos, px in images]
+            out.append(ids)
+            cls._pending_images.append(images)
+        return out
+
+    @classmethod
+    def from_tokenized(cls, batch_pb, batch_tokenized_inputs, tokenizer, dtype, device, speculate: int = 0):
+        batch = super().from_tokenized(batch_pb, batch_tokenized_inputs, tokenizer, dtype, device, speculate)
+        pending = getattr(cls, "_pending_images", None) or [[] for _ in batch.seqs]
+        for s, images in zip(batch.seqs, pending):
+            s.images = images
+        cls._pending_images = []
+        return batch
+
+
+class VlmCausalLM(FlashCausalLM):
+    def __init__(self, model: CausalDecoder, tower: VisionTower, projector, tokenizer, dtype, device, rank, world,
+                 image_token_id: int, drop_cls: bool, embed_scale: float = 1.0, **kw):
+        super().__init__(model, tokenizer, dtype, device, rank, world, **kw)
+        self.tower, self.projector = tower, projector
+        self.image_token_id, self.drop_cls, self.image_embed_scale = image_token_id, drop_cls, embed_scale
+        self.tokens_per_image = tower.num_patches
+        self.batch_cls = type("BoundVlmBatch", (VlmCausalLMBatch,), dict(
+            image_token_id=image_token_id, tokens_per_image=self.tokens_per_image, image_size=tower.image_size,
+            norm=(CLIP_MEAN, CLIP_STD) if tower.kind == "clip" else (SIGLIP_MEAN, SIGLIP_STD)))
+
+    @property
+    def batch_type(self):
+        return self.batch_cls
+
+    @torch.no_grad()
+    def encode_images(self, pixels: torch.Tensor) -> torch.Tensor:
+        """``[N, 3, S, S]`` -> ``[N, tokens_per_image, hidden_text]``"""
+        feats = self.tower(pixels.to(self.device))
+        if self.drop_cls:
+            feats = feats[:, 1:]
+        out = self.projector(feats.reshape(-1, feats.shape[-1]).to(self.dtype))
+        if self.image_embed_scale != 1.0:
+            out = out * self.image_embed_scale
+        return out.view(feats.shape[0], feats.shape[1], -1)
+
+    def build_meta(self, batch, counts):
+        meta, row_owner = super().build_meta(batch, counts)
+        # rows of this step that are image placeholders: (row in the ragged batch, image, offset)
+        jobs: List[Tuple[int, int, torch.Tensor, int, int]] = []
+        t = 0
+        for s, n in zip(batch.seqs, counts):
+            if s.prefilling and n > 0:
+                lo, hi = s.cache_len, s.cache_len + n
+                for pos, px in getattr(s, "images", []):
+                    a, b = max(pos, lo), min(pos + self.tokens_per_image, hi)
+                    if a < b:
+                        jobs.append((t + a - lo, b - a, px, a - pos, id(px)))
+            t += n
+        if jobs:
+            uniq: Dict[int, int] = {}
+            stack = []
+            for _, _, px, _, key in jobs:
+                if key not in uniq:
+                    uniq[key] = len(stack)
+                    stack.append(px)
+            feats = self.encode_images(torch.stack(stack))
+            embeds = self.model.embed_tokens(meta.input_ids, meta.positions).clone()
+            for row, n, _, off, key in jobs:
+                embeds[row:row + n] = feats[uniq[key], off:off + n].to(embeds.dtype)
+            meta.inputs_embeds = embeds
+        return meta, row_owner
+
+
+class _MlpProjector:
+    def __init__(self, w1, b1, w2, b2, act="gelu"):
+        self.w1, self.b1, self.w2, self.b2, self.act = w1, b1, w2, b2, act
+
+    def __call__(self, x):
+        h = ops.linear(x, self.w1, self.b1)
+        h = F.gelu(h)
+        return ops.linear(h, self.w2, self.b2)
+
+
+class _LinearProjector:
+    def __init__(self, w, b):
+        self.w, self.b = w, b
+
+    def __call__(self, x):
+        return ops.linear(x, self.w, self.b)
+
+
+def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, tokenizer, speculate, kv_cache_dtype,
+             max_prefill_tokens):
+    from . import resolve_kv_dtype
+    from ..parallel.peer import make_comm
+
+    mt = cfg.model_type
+    weights = Weights(weight_files(path), device, dtype, process_group=process_group, loader=loader)
+    text_cfg = cfg.text_config()
+    vis = dict(cfg.get("vision_config") or {})
+    if mt in ("llava_next", "llava"):
+        vis.setdefault("image_size", 336)
+        vis.setdefault("patch_size", 14)
+        tower = VisionTower(vis, weights, "vision_tower.vision_model", "clip",
+                            feature_layer=int(cfg.get("vision_feature_layer", -2)))
+        projector = _MlpProjector(weights.get_tensor("multi_modal_projector.linear_1.weight"),
+                                  weights.get_tensor("multi_modal_projector.linear_1.bias"),
+                                  weights.get_tensor("multi_modal_projector.linear_2.weight"),
+                                  weights.get_tensor("multi_modal_projector.linear_2.bias"))
+        drop_cls = cfg.get("vision_feature_select_strategy", "default") == "default"
+        prefix, scale = "language_model", 1.0
+        image_token = int(cfg.get("image_token_index", cfg.get("image_token_id", 32000)))
+    elif mt == "paligemma":
+        vis.setdefault("image_size", 224)
+        vis.setdefault("patch_size", 14)
+        tower = VisionTower(vis, weights, "vision_tower.vision_model", "siglip", feature_layer=-1)
+        projector = _LinearProjector(weights.get_tensor("multi_modal_projector.linear.weight"),
+                                     weights.get_tensor("multi_modal_projector.linear.bias"))
+        drop_cls = False
+        # Image rows are divided by sqrt(hidden) after the projector and every row of inputs_embeds is
+        # multiplied by sqrt(hidden) at the entry of the Gemma decoder: the two cancel, and the
+        # decoder here scales only the rows it embeds itself.
+        prefix, scale = "language_model", 1.0
+        image_token = int(cfg.get("image_token_index", 257152))
+    else:
+        raise NotImplementedError(f"vision-language model type {mt} has no native runner yet "
+                                  "(llava / llava_next / paligemma are covered)")
+    hidden = int(text_cfg.get("hidden_size"))
+    comm = make_comm(process_group, rank, world, device, hidden, int(max_prefill_tokens or 4096))
+    model = CausalDecoder(text_cfg, weights, comm=comm, prefix=prefix)
+    runner = VlmCausalLM(model, tower, projector, tokenizer, dtype, device, rank, world, image_token, drop_cls,
+                         scale, speculate=speculate,
+                         kv_cache_dtype=resolve_kv_dtype(kv_cache_dtype, dtype), max_prefill_tokens=max_prefill_tokens)
+    weights.close()
+    return runner
