@@ -242,3 +242,20 @@ def test_python_client_sync_and_async(stack):
 
     r, ev, c = asyncio.run(run())
     assert r.generated_text == resp.generated_text and len(ev) == 4 and c.usage.completion_tokens == 2
+
+
+def test_benchmark_tool_against_the_shard(stack):
+    from tgi_b200.router.build import HERE
+
+    exe = HERE / "tgi-b200-benchmark"
+    r = subprocess.run([str(exe), "--master-shard-uds-path", stack["uds"], "--batch-size", "1,3", "--sequence-length", "12",
+                        "--decode-length", "5", "--runs", "2", "--warmups", "1", "--json"],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout)
+    assert out["config"]["sequence_length"] == 12 and [e["batch_size"] for e in out["results"]] == [1, 3]
+    for e in out["results"]:
+        assert e["prefill"]["latency_ms"]["avg"] > 0 and e["decode"]["throughput_tokens_per_s"]["p50"] > 0
+    table = subprocess.run([str(exe), "-m", stack["uds"], "-b", "2", "-s", "8", "-d", "3", "-r", "1"],
+                           capture_output=True, text=True, timeout=120)
+    assert table.returncode == 0 and "Decode throughput (tokens/s)" in table.stdout

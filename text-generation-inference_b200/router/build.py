@@ -1,5 +1,6 @@
 """Builds the native front end in-tree with g++: ``tgi-b200-router`` (HTTP + scheduler, embeds
-CPython for the tokenizer bridge), ``tgi-b200-launcher`` (process supervisor) and ``_router_test.so``
+CPython for the tokenizer bridge), ``tgi-b200-launcher`` (process supervisor), ``tgi-b200-benchmark`` (shard-level prefill/decode
+microbenchmark) and ``_router_test.so``
 (pybind11 bindings of the scheduler core that the unit tests drive)."""
 from __future__ import annotations
 
@@ -43,7 +44,7 @@ def build(tests: bool = True):
     import pybind11
 
     jobs = [(SRC / f, []) for f in CORE] + [(SRC / "pybridge.cpp", py_inc), (SRC / "main.cpp", []),
-                                            (SRC / "launcher.cpp", [])]
+                                            (SRC / "launcher.cpp", []), (SRC / "benchmark.cpp", [])]
     if tests:
         jobs.append((SRC / "bindings.cpp", py_inc + [f"-I{pybind11.get_include()}"]))
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
@@ -58,6 +59,7 @@ def build(tests: bool = True):
 
     link(HERE / "tgi-b200-router", core + [str(objs["pybridge"]), str(objs["main"])], py_ld)
     link(HERE / "tgi-b200-launcher", [str(objs["launcher"])], [])
+    link(HERE / "tgi-b200-benchmark", [str(objs[n]) for n in ("pb", "scheduler", "shard_client", "benchmark")], [])
     if tests:
         link(HERE / "_router_test.so", core + [str(objs["bindings"])], ["-shared"])
     return HERE / "tgi-b200-router"
