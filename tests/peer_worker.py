@@ -82,6 +82,22 @@ def main():
                 for o in gathered:
                     assert torch.equal(o, gathered[0]), "gathered rows differ between ranks"
 
+    # ---- vocabulary-parallel greedy sampling --------------------------------------------------
+    for B, Vl in ((1, 500), (37, 2003), (256, 1024)):
+        salt += 1
+        shards = []
+        for r in range(world):
+            g = torch.Generator(device="cpu").manual_seed(5000 * salt + r)
+            shards.append((torch.randn(B, Vl, generator=g) * 3).to(torch.bfloat16))
+        full = torch.cat(shards, dim=1).to(device).float() * 0.5
+        ids, lps = comm.argmax(shards[rank].to(device), rank * Vl, 0.5)
+        torch.cuda.synchronize()
+        assert comm.check() == 0
+        want_ids = full.argmax(-1)
+        want_lp = torch.log_softmax(full, -1).gather(1, want_ids.view(-1, 1)).view(-1)
+        assert torch.equal(ids, want_ids), f"argmax ids differ B={B}"
+        assert (lps - want_lp).abs().max().item() < 2e-3, f"argmax logprobs differ {(lps - want_lp).abs().max()}"
+
     # ---- CUDA graph replay: the call counters live in device memory ----------------------------
     T = 32
     salt += 1

@@ -547,6 +547,27 @@ class CausalDecoder:
             out = (torch.tanh(out.float() / d.logit_softcap) * d.logit_softcap).to(out.dtype)
         return out
 
+    @property
+    def supports_local_head(self) -> bool:
+        """True when greedy sampling can run on the vocabulary shards without gathering the logits."""
+        return (self.comm is not None and hasattr(self.comm, "argmax") and self.pg.size() > 1
+                and self.head.should_gather and self.dims.logit_softcap == 0 and self.speculator is None
+                and self.dtype == torch.bfloat16)
+
+    def forward_local(self, meta: ForwardMeta, kv_cache) -> Tuple[torch.Tensor, int]:
+        """``(logits of this rank's vocabulary shard [rows, V / tp], first vocabulary id of the shard)``."""
+        h = self.forward_hidden(meta, kv_cache)
+        if meta.lm_head_indices is not None:
+            h = h[meta.lm_head_indices.long()]
+        return self.head.local_logits(h)
+
+    def gather_logits(self, local: torch.Tensor) -> torch.Tensor:
+        """Full ``[rows, V]`` logits from the shards (the path for samplers that need the distribution)."""
+        out = self.head.gather(local)
+        if self.dims.logit_scale != 1.0:
+            out = out * self.dims.logit_scale
+        return out
+
     def forward(self, meta: ForwardMeta, kv_cache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Returns ``(logits[rows, V], speculative_logits or None)``."""
         h = self.forward_hidden(meta, kv_cache)

@@ -460,11 +460,22 @@ class FlashCausalLM(Model):
         next_ids_l: List[int] = []
         if active:
             chooser = batch.next_token_chooser if len(active) == B else batch.next_token_chooser.select(active)
+            greedy_dev = None
+            if logits is None:
+                # the decode graph ended in the vocabulary-parallel argmax: full logits exist only if gathered
+                plain = (chooser.is_greedy_plain and batch.speculate == 0
+                         and not any(seqs[i].top_n > 0 for i in active))
+                if plain:
+                    greedy_dev = self.graphs.greedy()
+                if greedy_dev is None:
+                    logits = self.graphs.gather_last_logits()
             # sequences in the same step may carry different numbers of speculative tokens only when
             # some have none yet (first decode after prefill): pad those with a token that cannot match
             spec_lens = [0 if seqs[i].prefilling else len(seqs[i].speculative_ids) for i in active]
             Smax = 1 + max(spec_lens)
-            if all(l == spec_lens[0] for l in spec_lens):
+            if greedy_dev is not None:
+                sel_rows, sel, speculated = sample_rows, None, None
+            elif all(l == spec_lens[0] for l in spec_lens):
                 sel_rows = sample_rows
                 sel = logits if len(sample_rows) == logits.shape[0] else logits[
                     torch.tensor(sample_rows, dtype=torch.long, device=logits.device)]
@@ -483,7 +494,9 @@ class FlashCausalLM(Model):
                 sel = logits[torch.tensor(idx, dtype=torch.long, device=logits.device)]
                 speculated = torch.tensor(spec, dtype=torch.long, device=logits.device)
             need_history = (chooser.any_rep or chooser.any_freq or bool(chooser.watermarks) or batch.speculate > 0)
-            if need_history:
+            if greedy_dev is not None:
+                history = None
+            elif need_history:
                 L = max(len(seqs[i].ids) for i in active)
                 hist = np.zeros((len(active), L), dtype=np.int64)
                 for r, i in enumerate(active):
@@ -492,10 +505,11 @@ class FlashCausalLM(Model):
             else:
                 history = torch.zeros(len(active), 1, dtype=torch.long, device=logits.device)
             want_top = any(seqs[i].top_n > 0 for i in active)
-            if chooser.is_greedy_plain and batch.speculate == 0 and not want_top and speculated is None:
+            if greedy_dev is not None or (chooser.is_greedy_plain and batch.speculate == 0 and not want_top
+                                          and speculated is None):
                 from .. import ops
 
-                ids_t, lp_t = ops.argmax_logprob(sel)
+                ids_t, lp_t = greedy_dev if greedy_dev is not None else ops.argmax_logprob(sel)
                 packed = torch.stack([ids_t.float(), lp_t.float()]).cpu()
                 next_ids_l = [int(x) for x in packed[0].tolist()]
                 next_lp_l = packed[1].tolist()

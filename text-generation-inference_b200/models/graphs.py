@@ -64,7 +64,10 @@ class _Bucket:
             lm_head_indices=None,
         )
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.logits: Optional[torch.Tensor] = None
+        self.logits: Optional[torch.Tensor] = None          # full logits [bs, V] (gathered-head graphs)
+        self.local_logits: Optional[torch.Tensor] = None    # vocabulary shard [bs, V / tp] (local-head graphs)
+        self.greedy_ids: Optional[torch.Tensor] = None      # filled inside the graph by the peer argmax
+        self.greedy_logprobs: Optional[torch.Tensor] = None
 
 
 def runner_max_kv(runner) -> int:
@@ -93,12 +96,28 @@ class DecodeGraphs:
         r.model.forward(b.meta, r.kv_cache)
         torch.cuda.synchronize(r.device)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, pool=self.pool):
-            logits, _ = r.model.forward(b.meta, r.kv_cache)
+        local_head = bool(getattr(r.model, "supports_local_head", False))
+        if local_head:
+            # Sharded lm_head: the graph ends with the vocabulary-parallel argmax, so a greedy step never
+            # gathers logits; samplers that need the distribution gather the shard after the replay.
+            d = r.model.dims
+            b.greedy_ids = torch.zeros(bs, dtype=torch.int64, device=r.device)
+            b.greedy_logprobs = torch.zeros(bs, dtype=torch.float32, device=r.device)
+            local, v0 = r.model.forward_local(b.meta, r.kv_cache)
+            r.model.comm.argmax(local, v0, d.logit_scale, b.greedy_ids, b.greedy_logprobs)
+            torch.cuda.synchronize(r.device)
+            with torch.cuda.graph(g, pool=self.pool):
+                local, v0 = r.model.forward_local(b.meta, r.kv_cache)
+                r.model.comm.argmax(local, v0, d.logit_scale, b.greedy_ids, b.greedy_logprobs)
+            b.local_logits = local
+        else:
+            with torch.cuda.graph(g, pool=self.pool):
+                logits, _ = r.model.forward(b.meta, r.kv_cache)
+            b.logits = logits
         if self.pool is None:
             self.pool = g.pool()
         torch.cuda.synchronize(r.device)
-        b.graph, b.logits = g, logits
+        b.graph = g
         self.buckets[bs] = b
 
     def supports(self, batch) -> bool:
@@ -137,4 +156,16 @@ class DecodeGraphs:
         b.dev.copy_(b.host, non_blocking=True)
         b.graph.replay()
         row_owner = [(i, 0) for i in range(n)]
-        return b.logits[:n], row_owner
+        self.last = (b, n)
+        return (b.logits[:n] if b.logits is not None else None), row_owner
+
+    def greedy(self):
+        """``(ids, logprobs)`` of the last replay when its graph sampled greedily in-kernel, else ``None``."""
+        b, n = self.last
+        if b.greedy_ids is None:
+            return None
+        return b.greedy_ids[:n], b.greedy_logprobs[:n]
+
+    def gather_last_logits(self) -> torch.Tensor:
+        b, n = self.last
+        return self.runner.model.gather_logits(b.local_logits)[:n]

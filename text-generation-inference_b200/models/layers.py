@@ -236,6 +236,9 @@ class TensorParallelHead:
         local = self.linear(x)
         if not self.should_gather:
             return local
+        return self.gather(local)
+
+    def gather(self, local: torch.Tensor) -> torch.Tensor:
         world = self.process_group.size()
         B, Vl = local.shape
         gathered = local.new_empty(world, B, Vl)

@@ -45,6 +45,7 @@ struct PeerArgs {
   const __nv_bfloat16* weight;      // norm weight [H]
   float eps, w_offset;
   int* status;
+  unsigned long long* trace;     // optional: 8 timestamps (ns) of block 0 for the phase timeline, or nullptr
 };
 
 struct __align__(16) bf16x8 {
@@ -76,6 +77,14 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -97,11 +106,14 @@ struct BlockSync {
            (static_cast<size_t>(phase) * kMaxBlocks + blockIdx.x) * kMaxRanks + src;
   }
   // all writes of this block made before the call become visible to the peers that see the flag
-  __device__ void signal(int phase) const {
+  // `fence`: order this block's earlier writes before the flag.  Phase 0 announces data that the
+  // previous kernel of the stream wrote into this GPU's own memory; the kernel boundary already made
+  // it visible at the L2 that serves the peers' loads, so no fence is needed there (it costs ~3 us).
+  __device__ void signal(int phase, bool fence) const {
     __syncthreads();
     if (threadIdx.x < a.world) {
-      __threadfence_system();
-      st_release_sys(flag(threadIdx.x, phase, a.rank), e);
+      if (fence) __threadfence_system();
+      st_relaxed_sys(flag(threadIdx.x, phase, a.rank), e);
     }
   }
   // returns false (for the whole block) when a peer did not signal in time
@@ -110,13 +122,14 @@ struct BlockSync {
       const unsigned int* f = flag(a.rank, phase, threadIdx.x);
       const unsigned long long t0 = global_ns();
       unsigned int polls = 0;
-      while (static_cast<int>(ld_acquire_sys(f) - e) < 0) {
+      while (static_cast<int>(ld_relaxed_sys(f) - e) < 0) {
         if ((++polls & 63u) == 0 && global_ns() - t0 > kPeerWaitNs) {
           atomicExch(a.status, sm100::kErrPeerWait);
           *failed = 1;
           break;
         }
       }
+      (void)ld_acquire_sys(f);   // one acquire after the flag was seen: later reads observe the peer's data
     }
     __syncthreads();
     return *failed == 0;
@@ -202,8 +215,12 @@ peer_reduce_kernel(const PeerArgs a) {
   const int my_rows = max(0, min(a.T, row0 + rows_per) - row0);
   const int nvec = a.H / 8;
 
-  sync.signal(0);                       // my producer kernel has finished: its partial rows may be read
+  const bool tracing = a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+  if (tracing) a.trace[0] = global_ns();
+  sync.signal(0, false);                       // my producer kernel has finished: its partial rows may be read
+  if (tracing) a.trace[1] = global_ns();
   bool ok = sync.wait(0);
+  if (tracing) a.trace[2] = global_ns();
   if (ok) {
     for (int lr = blockIdx.x; lr < my_rows; lr += gridDim.x) {
       const int row = row0 + lr;
@@ -224,11 +241,13 @@ peer_reduce_kernel(const PeerArgs a) {
         for (int i = 0; i < VPT; ++i) {
           const int v = threadIdx.x + i * blockDim.x;
           if (v < nvec) {
-            pull_sum8(a, rbase + v * 8, s[i]);
             const size_t lbase = static_cast<size_t>(lr) * a.H + v * 8;
+            uint4 res_raw = make_uint4(0, 0, 0, 0);   // issued before the peer loads so the latencies overlap
+            if (a.residual_in != nullptr) res_raw = *reinterpret_cast<const uint4*>(a.residual_in + lbase);
+            pull_sum8(a, rbase + v * 8, s[i]);
             if (a.residual_in != nullptr) {
               float r[8];
-              unpack8(*reinterpret_cast<const uint4*>(a.residual_in + lbase), r);
+              unpack8(res_raw, r);
 #pragma unroll
               for (int j = 0; j < 8; ++j) s[i][j] = round_bf16(s[i][j] + r[j]);
             }
@@ -278,8 +297,128 @@ peer_reduce_kernel(const PeerArgs a) {
         }
       }
     }
-    sync.signal(1);                     // my rows are in everybody's gather buffer
+    if (tracing) a.trace[3] = global_ns();
+    sync.signal(1, true);                     // my rows are in everybody's gather buffer
+    if (tracing) a.trace[4] = global_ns();
     ok = sync.wait(1);                  // and everybody's rows are in mine
+    if (tracing) a.trace[5] = global_ns();
+  }
+  sync.finish();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Vocabulary-parallel greedy sampling.  The reference all-gathers the [B, V] logits of the sharded
+// lm_head (layers/tensor_parallel.py:75-104) and runs log_softmax + argmax on the full matrix.  Here
+// every rank reduces its own [B, V / world] slice to one candidate per row,
+//     (m, i, s) = (max logit, global index of the max, sum of exp(x - m) over the slice),
+// pushes the 16-byte candidate into every rank's heap and merges the `world` candidates of a row:
+//     M = max m_r,  token = i of the rank holding M (lowest rank on ties),
+//     logprob = M - (M + log sum_r s_r exp(m_r - M)).
+// 16 bytes per row and rank cross NVLink instead of V / world logits.
+// ------------------------------------------------------------------------------------------------
+struct __align__(16) Candidate {
+  float m;
+  int idx;
+  float s;
+  int pad;
+};
+
+__global__ void __launch_bounds__(1024)
+peer_argmax_kernel(const PeerArgs a, const __nv_bfloat16* __restrict__ logits, long long row_stride, int vocab_start,
+                   float logit_scale, long long off_cand, long long* __restrict__ ids, float* __restrict__ logprob) {
+  __shared__ float sm_m[32], sm_s[32];
+  __shared__ int sm_i[32];
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  BlockSync sync(a, &failed);
+  const int B = a.T, Vl = a.H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int row = blockIdx.x; row < B; row += gridDim.x) {
+    const __nv_bfloat16* x = logits + static_cast<size_t>(row) * row_stride;
+    float m = -INFINITY, s = 0.f;
+    int idx = 0x7fffffff;
+    for (int v = threadIdx.x; v < Vl; v += blockDim.x) {
+      const float val = __bfloat162float(x[v]) * logit_scale;
+      if (val > m) {
+        s = s * __expf(m - val) + 1.f;
+        m = val;
+        idx = v;
+      } else if (val != -INFINITY) {
+        s += __expf(val - m);
+      }
+    }
+    // merge (m, idx, s) across the warp, then across warps; ties keep the smaller index
+    auto merge = [](float& m1, int& i1, float& s1, float m2, int i2, float s2) {
+      if (m2 == -INFINITY) return;      // the other side saw no finite logit
+      if (m2 > m1 || (m2 == m1 && i2 < i1)) {
+        s1 = s1 * __expf(m1 - m2) + s2;
+        m1 = m2;
+        i1 = i2;
+      } else if (m2 != -INFINITY) {
+        s1 += s2 * __expf(m2 - m1);
+      }
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+      const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+      const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      merge(m, idx, s, m2, i2, s2);
+    }
+    __syncthreads();
+    if (lane == 0) {
+      sm_m[warp] = m;
+      sm_i[warp] = idx;
+      sm_s[warp] = s;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const int nw = blockDim.x >> 5;
+      m = lane < nw ? sm_m[lane] : -INFINITY;
+      idx = lane < nw ? sm_i[lane] : 0x7fffffff;
+      s = lane < nw ? sm_s[lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+        const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        merge(m, idx, s, m2, i2, s2);
+      }
+      if (lane < a.world) {
+        Candidate c;
+        c.m = m;
+        c.idx = idx + vocab_start;
+        c.s = s;
+        c.pad = 0;
+        Candidate* dst = reinterpret_cast<Candidate*>(a.heap[lane] + off_cand) + static_cast<size_t>(row) * kMaxRanks + a.rank;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&c);
+      }
+    }
+  }
+  sync.signal(1, true);
+  const bool ok = sync.wait(1);
+  if (ok) {
+    for (int row = blockIdx.x; row < B; row += gridDim.x) {
+      if (threadIdx.x == 0) {
+        const Candidate* mine = reinterpret_cast<const Candidate*>(a.heap[a.rank] + off_cand) + static_cast<size_t>(row) * kMaxRanks;
+        float M = -INFINITY;
+        int best = 0;
+        Candidate c[kMaxRanks];
+        for (int r = 0; r < a.world; ++r) {
+          const uint4 raw = ld_cg16(mine + r);
+          c[r] = *reinterpret_cast<const Candidate*>(&raw);
+          if (c[r].m > M) {
+            M = c[r].m;
+            best = r;
+          }
+        }
+        float sum = 0.f;
+        for (int r = 0; r < a.world; ++r) sum += c[r].s * __expf(c[r].m - M);
+        ids[row] = c[best].idx;
+        logprob[row] = -__logf(sum);
+      }
+    }
   }
   sync.finish();
 }
@@ -328,7 +467,7 @@ int tgi_peer_max_blocks() { return kMaxBlocks; }
 int tgi_peer_reduce(void* const* heaps, int rank, int world, int T, int H, long long off_partial, long long off_gather,
                     long long off_gscale, int gscale_pitch, long long off_flags, unsigned int* epoch,
                     const void* residual_in, void* residual_out, const void* weight, float eps, float w_offset,
-                    int mode, int blocks, int* status, cudaStream_t stream) {
+                    int mode, int blocks, int* status, unsigned long long* trace, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -10;
   if (H % 8 != 0 || blocks < 1 || blocks > kMaxBlocks) return -11;
@@ -352,12 +491,41 @@ int tgi_peer_reduce(void* const* heaps, int rank, int world, int T, int H, long 
   a.eps = eps;
   a.w_offset = w_offset;
   a.status = status;
+  a.trace = trace;
   switch (mode) {
     case 0: return launch_reduce<false, false>(a, blocks, stream);
     case 1: return launch_reduce<true, false>(a, blocks, stream);
     case 2: return launch_reduce<true, true>(a, blocks, stream);
     default: return -14;
   }
+}
+
+// Greedy token and its log-probability from vocabulary-sharded logits: see peer_argmax_kernel.
+int tgi_peer_argmax(void* const* heaps, int rank, int world, const void* logits, int B, int Vl, long long row_stride,
+                    int vocab_start, float logit_scale, long long off_cand, long long off_flags, unsigned int* epoch,
+                    long long* ids, float* logprob, int blocks, int* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -10;
+  if (blocks < 1 || blocks > kMaxBlocks) return -11;
+  PeerArgs a;
+  for (int i = 0; i < kMaxRanks; ++i) a.heap[i] = i < world ? static_cast<unsigned char*>(heaps[i]) : nullptr;
+  a.rank = rank;
+  a.world = world;
+  a.T = B;
+  a.H = Vl;
+  a.off_partial = a.off_gather = a.off_gscale = 0;
+  a.gscale_pitch = 0;
+  a.off_flags = off_flags;
+  a.epoch = epoch;
+  a.residual_in = nullptr;
+  a.residual_out = nullptr;
+  a.weight = nullptr;
+  a.eps = a.w_offset = 0.f;
+  a.status = status;
+  a.trace = nullptr;
+  peer_argmax_kernel<<<blocks, 1024, 0, stream>>>(a, static_cast<const __nv_bfloat16*>(logits), row_stride, vocab_start,
+                                                  logit_scale, off_cand, ids, logprob);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 }  // extern "C"

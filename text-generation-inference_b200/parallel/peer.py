@@ -76,7 +76,9 @@ class PeerComm:
         self.off_partial = _round_up(nflag, _ALIGN)
         self.off_gather = self.off_partial + _round_up(nrows, _ALIGN)
         self.off_gscale = self.off_gather + _round_up(nrows, _ALIGN)
-        self.heap_bytes = self.off_gscale + _round_up(max(self.width // 128, 1) * self.pitch * 4, _ALIGN)
+        self.off_cand = self.off_gscale + _round_up(max(self.width // 128, 1) * self.pitch * 4, _ALIGN)
+        self.max_argmax_rows = 1024          # greedy candidates: 16 bytes per row and rank
+        self.heap_bytes = self.off_cand + _round_up(self.max_argmax_rows * 8 * 16, _ALIGN)
 
         torch.cuda.set_device(device)
         base = ctypes.c_void_p()
@@ -106,11 +108,12 @@ class PeerComm:
         self._heap_t = tensor_from_ptr(self.base, self.heap_bytes, device)
         self._partial = self._heap_t[self.off_partial:self.off_partial + nrows].view(torch.bfloat16)
         self._gather = self._heap_t[self.off_gather:self.off_gather + nrows]
-        self._gscale = self._heap_t[self.off_gscale:self.heap_bytes].view(torch.float32)
+        self._gscale = self._heap_t[self.off_gscale:self.off_cand].view(torch.float32)
         self.epoch = torch.zeros(self.max_blocks, dtype=torch.int32, device=device)
         rows_per = (self.max_tokens + world - 1) // world
         self.residual = torch.zeros(rows_per, self.width, dtype=torch.bfloat16, device=device)
         self.status = K.state(device).status
+        self.trace: Optional[torch.Tensor] = None   # set to an int64[8] tensor to record block 0's phase timestamps
         # every rank must have mapped every heap before anyone's kernel writes into a peer
         pdist.barrier(group)
 
@@ -138,7 +141,7 @@ class PeerComm:
             ctypes.c_longlong(self.off_partial), ctypes.c_longlong(self.off_gather), ctypes.c_longlong(self.off_gscale),
             ctypes.c_int(self.pitch), ctypes.c_longlong(self.off_flags), K._ptr(self.epoch),
             K._ptr(residual_in), K._ptr(residual_out), K._ptr(weight), ctypes.c_float(eps), ctypes.c_float(w_offset),
-            ctypes.c_int(mode), ctypes.c_int(self._blocks(T)), K._ptr(self.status), K._stream())
+            ctypes.c_int(mode), ctypes.c_int(self._blocks(T)), K._ptr(self.status), K._ptr(self.trace), K._stream())
         K._check(rc, "peer_reduce")
 
     # ---- collectives ---------------------------------------------------------------------------
@@ -175,6 +178,23 @@ class PeerComm:
         if quant:
             return self._gather_fp8(T, H)
         return self._gather_bf16(T, H)
+
+    def argmax(self, local_logits: torch.Tensor, vocab_start: int, logit_scale: float = 1.0,
+               out_ids: Optional[torch.Tensor] = None, out_logprobs: Optional[torch.Tensor] = None):
+        """Greedy token ids (int64) and their log-probabilities from vocabulary-sharded bf16 logits
+        ``[B, V / world]``: only a 16-byte candidate per row and rank crosses NVLink."""
+        B, Vl = local_logits.shape
+        assert local_logits.dtype == torch.bfloat16 and local_logits.stride(1) == 1 and B <= self.max_argmax_rows
+        ids = out_ids if out_ids is not None else torch.empty(B, dtype=torch.int64, device=self.device)
+        lps = out_logprobs if out_logprobs is not None else torch.empty(B, dtype=torch.float32, device=self.device)
+        rc = self.lib.tgi_peer_argmax(
+            self._heap_arr, ctypes.c_int(self.rank), ctypes.c_int(self.world), K._ptr(local_logits), ctypes.c_int(B),
+            ctypes.c_int(Vl), ctypes.c_longlong(local_logits.stride(0)), ctypes.c_int(vocab_start),
+            ctypes.c_float(logit_scale), ctypes.c_longlong(self.off_cand), ctypes.c_longlong(self.off_flags),
+            K._ptr(self.epoch), K._ptr(ids), K._ptr(lps), ctypes.c_int(max(1, min(B, self.max_blocks))),
+            K._ptr(self.status), K._stream())
+        K._check(rc, "peer_argmax")
+        return ids, lps
 
     def check(self) -> int:
         return K.check_status(self.device)
