@@ -82,6 +82,30 @@ def main():
                 for o in gathered:
                     assert torch.equal(o, gathered[0]), "gathered rows differ between ranks"
 
+    # ---- row-parallel GEMM whose epilogue pushes its rows to their owners, then the fused reduction ----
+    from tgi_b200 import ops
+
+    for T, Kd in ((5, 256), (64, 512), (96, 1024)):
+        for rep in range(2):
+            salt += 1
+            xs_all, ws_all = [], []
+            for r in range(world):
+                g = torch.Generator(device="cpu").manual_seed(9000 * salt + r)
+                xs_all.append((torch.randn(T, Kd, generator=g) * 0.5).to(torch.bfloat16).to(device))
+                ws_all.append((torch.randn(H, Kd, generator=g) * 0.05).to(torch.bfloat16).to(device))
+            dst = comm.push_target(T)
+            ops.linear(xs_all[rank], ws_all[rank], None, out=dst)
+            assert dst.used
+            out = comm.reduce_norm(T, weight, eps, 0.0, quant=False, first=True, source=dst)
+            torch.cuda.synchronize()
+            assert comm.check() == 0
+            acc = torch.zeros(T, H, dtype=torch.float32, device=device)
+            for r in range(world):
+                acc += (xs_all[r].float() @ ws_all[r].float().t()).to(torch.bfloat16).float()
+            want, _ = ref.rms_norm(acc.to(torch.bfloat16), None, weight, eps, False)
+            err = (out.float() - want.float()).abs().max().item()
+            assert err <= 3e-2, f"pushed GEMM + reduce mismatch T={T} K={Kd}: {err}"
+
     # ---- vocabulary-parallel greedy sampling --------------------------------------------------
     for B, Vl in ((1, 500), (37, 2003), (256, 1024)):
         salt += 1

@@ -429,13 +429,23 @@ class DecoderLayer:
         the next RMSNorm (and quantises) and gathers the result on every rank."""
         T = meta.input_ids.shape[0]
         xq, xs = x if isinstance(x, tuple) else (x, None)
-        self.attn(xq, xs, meta, rotary, kv, reduce=False, out=comm.partial(T))
+        # o_proj and down_proj store their partial rows straight into the row owners' peer memory
+        # (GEMM epilogue = reduce-scatter transport); producers without such an epilogue use the
+        # plain buffer and the reduction pulls instead.
+        # Measured on B200: below a few hundred rows the scattered peer stores and the system-scope
+        # fences of the pushing epilogue cost more than the pull they replace (decode step 34.5 ms
+        # pulled vs 37.3 ms pushed at TP=2), so small batches pull and prefill-sized ones push.
+        push = hasattr(comm, "push_target") and T >= comm.push_min_tokens
+        dst = comm.push_target(T) if push else None
+        self.attn(xq, xs, meta, rotary, kv, reduce=False, out=dst if dst is not None else comm.partial(T))
         n2 = self.norm2
-        x2 = comm.reduce_norm(T, n2.weight, n2.eps, 1.0 if n2.unit_offset else 0.0, quant=self.mlp_in_quant)
+        x2 = comm.reduce_norm(T, n2.weight, n2.eps, 1.0 if n2.unit_offset else 0.0, quant=self.mlp_in_quant,
+                              source=dst)
         x2q, x2s = x2 if isinstance(x2, tuple) else (x2, None)
-        self.mlp(x2q, x2s, reduce=False, meta=meta, out=comm.partial(T))
+        dst = comm.push_target(T) if push and isinstance(self.mlp, DenseMLP) else None
+        self.mlp(x2q, x2s, reduce=False, meta=meta, out=dst if dst is not None else comm.partial(T))
         return comm.reduce_norm(T, next_norm.weight, next_norm.eps, 1.0 if next_norm.unit_offset else 0.0,
-                                quant=next_quant)
+                                quant=next_quant, source=dst)
 
 
 class CausalDecoder:

@@ -94,7 +94,8 @@ class Fp8Linear:
         if self.bias is not None:
             y = y + self.bias
         if out is not None:
-            out.copy_(y)
+            dst = out.fallback if getattr(out, "is_peer_push", False) else out
+            dst.copy_(y)
             return out
         return y
 

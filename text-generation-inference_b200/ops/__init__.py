@@ -98,6 +98,8 @@ def activation(x, act):
 def _into(out, y):
     if out is None:
         return y
+    if getattr(out, "is_peer_push", False):
+        out = out.fallback      # no pushing kernel on this path: the reduction pulls from the plain buffer
     out.copy_(y.view_as(out))
     return out
 

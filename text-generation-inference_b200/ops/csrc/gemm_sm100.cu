@@ -55,6 +55,21 @@ struct TileCfg {
   static constexpr int kStageBytes = kXBytes + kWBytes;   // 48 KB
 };
 
+// Optional destination of the output rows in peer memory (tensor-parallel row-parallel GEMMs): row m
+// of the partial product belongs to rank m / rows_per and is stored, as bf16, straight into that
+// rank's heap at slot [this rank][m % rows_per], so the reduce-scatter transport happens in the
+// epilogue while other tiles are still being computed.  When the whole grid has stored everything,
+// the last CTA raises this rank's flag in every owner's heap (value: a call counter kept in device
+// memory, so CUDA-graph replays work).  world == 0 means "store to C as usual".
+struct PushArgs {
+  unsigned char* heap[8];
+  long long off_slots;      // byte offset of the slots [world][rows_per][N] bf16 in every heap
+  long long off_flags;      // byte offset of uint32 flags [8] in every heap, indexed by source rank
+  int rank, world, rows_per;
+  int* done_ctas;           // local counter of CTAs that finished their stores (self-resetting)
+  unsigned int* epoch;      // local call counter
+};
+
 constexpr int kMaxGrid = 160;              // upper bound of the grid size (one CTA per SM)
 constexpr int kSplitPolls = 1 << 20;       // polls of a split-tile counter before giving up (about 0.1 s)
 
@@ -155,8 +170,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmS, const float* __restrict__ wscale,
                     __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-                    float* __restrict__ ws, int* __restrict__ counters, int* __restrict__ status) {
+                    float* __restrict__ ws, int* __restrict__ counters, int* __restrict__ status,
+                    const __grid_constant__ PushArgs push) {
   using Cfg = TileCfg<MH, TN>;
+  // first element of output row m: in C, or in the owner's peer-memory slot of this rank
+  auto out_row = [&](int m) -> __nv_bfloat16* {
+    if (push.world == 0) return C + static_cast<size_t>(m) * N;
+    const int owner = m / push.rows_per;
+    const int lr = m - owner * push.rows_per;
+    return reinterpret_cast<__nv_bfloat16*>(push.heap[owner] + push.off_slots) +
+           (static_cast<size_t>(push.rank) * push.rows_per + lr) * N;
+  };
   constexpr int TM = Cfg::TM;
   constexpr int BK = FP8 ? 128 : 64;            // elements per 128-byte row
   constexpr int SC_STAGES = STAGES + 2;
@@ -389,7 +413,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         continue;
       }
       if (m < M && nb < N) {
-        __nv_bfloat16* crow = C + static_cast<size_t>(m) * N + nb;
+        __nv_bfloat16* crow = out_row(m) + nb;
         const bool vec_ok = (N % 8 == 0);
 #pragma unroll
         for (int j = 0; j < kCols; j += 8) {
@@ -463,7 +487,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             for (int e = 0; e < 4; ++e)
               if (col + e < N) f[e] += __bfloat162float(bias[col + e]);
           }
-          __nv_bfloat16* cp = C + static_cast<size_t>(m) * N + col;
+          __nv_bfloat16* cp = out_row(m) + col;
           if ((N & 3) == 0) {
             __nv_bfloat162 o[2] = {__floats2bfloat162_rn(f[0], f[1]), __floats2bfloat162_rn(f[2], f[3])};
             *reinterpret_cast<uint2*>(cp) = *reinterpret_cast<uint2*>(o);
@@ -478,6 +502,25 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       if (et == 0) {
         const int old = atomicAdd(&counters[tile], 1);
         if (old == 2 * n - 1) counters[tile] = 0;
+      }
+    }
+
+    // ---- peer-memory output: tell the row owners that this rank's partial sums have landed ----
+    if (push.world > 0) {
+      epi_barrier();                       // every store of this CTA was issued
+      if (et == 0) {
+        __threadfence_system();            // ... and is ordered before the count below, at system scope
+        const int old = atomicAdd(push.done_ctas, 1);
+        if (old == static_cast<int>(gridDim.x) - 1) {
+          *push.done_ctas = 0;
+          const unsigned int e = *push.epoch + 1u;
+          *push.epoch = e;
+          __threadfence_system();          // the other CTAs' stores (observed through the counter) before the flags
+          for (int r = 0; r < push.world; ++r) {
+            unsigned int* f = reinterpret_cast<unsigned int*>(push.heap[r] + push.off_flags) + push.rank;
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f), "r"(e) : "memory");
+          }
+        }
       }
     }
   }
@@ -524,8 +567,14 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, uint6
 template <int MH, int TN, int STAGES, bool FP8>
 int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C,
            const void* bias, int M, int N, int K, int max_ctas, float* ws, int* counters, int* status,
-           cudaStream_t stream) {
+           cudaStream_t stream, const PushArgs* push_args = nullptr) {
   using Cfg = TileCfg<MH, TN>;
+  PushArgs push;
+  if (push_args != nullptr) {
+    push = *push_args;
+  } else {
+    memset(&push, 0, sizeof(push));
+  }
   constexpr int BK = FP8 ? 128 : 64;
   CUtensorMap tmW, tmX, tmS;
   const CUtensorMapDataType dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -584,8 +633,24 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
     }
   }
   kern<<<grid, kThreads, smem, stream>>>(tmW, tmX, tmS, wscale, static_cast<__nv_bfloat16*>(C),
-                                         static_cast<const __nv_bfloat16*>(bias), M, N, K, ws, counters, status);
+                                         static_cast<const __nv_bfloat16*>(bias), M, N, K, ws, counters, status, push);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int fill_push(PushArgs& p, void* const* heaps, int rank, int world, int rows_per, long long off_slots,
+              long long off_flags, int* done_ctas, unsigned int* epoch, int M) {
+  if (world < 2 || world > 8 || rank < 0 || rank >= world || rows_per < 1) return -20;
+  if (static_cast<long long>(rows_per) * world < M) return -21;
+  memset(&p, 0, sizeof(p));
+  for (int i = 0; i < world; ++i) p.heap[i] = static_cast<unsigned char*>(heaps[i]);
+  p.off_slots = off_slots;
+  p.off_flags = off_flags;
+  p.rank = rank;
+  p.world = world;
+  p.rows_per = rows_per;
+  p.done_ctas = done_ctas;
+  p.epoch = epoch;
+  return 0;
 }
 
 }  // namespace
@@ -630,6 +695,34 @@ int tgi_gemm_fp8_block(const void* X, const float* xs_t, int xs_pitch, const voi
   if (M > g_wide_m)
     return launch<2, 128, 4, true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
   return launch<1, 256, 4, true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
+}
+
+// Row-parallel GEMMs of a tensor-parallel group: same products, but every output row is stored into the
+// peer-memory slot of the rank that owns the row (see PushArgs) and the owners are flagged at the end.
+// `fp8` selects the block-scaled path (xs_t / wscale as in tgi_gemm_fp8_block, ignored otherwise).
+int tgi_gemm_push(int fp8, const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale,
+                  const void* bias, int M, int N, int K, int max_ctas, float* ws, int* counters, int* status,
+                  void* const* heaps, int rank, int world, int rows_per, long long off_slots, long long off_flags,
+                  int* done_ctas, unsigned int* epoch, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (N % 8 != 0) return -22;   // 16-byte row segments in the slots
+  PushArgs p;
+  const int rc = fill_push(p, heaps, rank, world, rows_per, off_slots, off_flags, done_ctas, epoch, M);
+  if (rc) return rc;
+  if (fp8) {
+    if (K % 128 != 0 || xs_pitch % 4 != 0) return -10;
+    if (M > g_wide_m)
+      return launch<2, 128, 4, true>(X, xs_t, xs_pitch, W, wscale, nullptr, bias, M, N, K, max_ctas, ws, counters, status,
+                                     stream, &p);
+    return launch<1, 256, 4, true>(X, xs_t, xs_pitch, W, wscale, nullptr, bias, M, N, K, max_ctas, ws, counters, status,
+                                   stream, &p);
+  }
+  if (K % 8 != 0) return -10;
+  if (M > g_wide_m)
+    return launch<2, 128, 4, false>(X, nullptr, 0, W, nullptr, nullptr, bias, M, N, K, max_ctas, ws, counters, status,
+                                    stream, &p);
+  return launch<1, 256, 4, false>(X, nullptr, 0, W, nullptr, nullptr, bias, M, N, K, max_ctas, ws, counters, status, stream,
+                                  &p);
 }
 
 }  // extern "C"

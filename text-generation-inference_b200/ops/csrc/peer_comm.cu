@@ -46,6 +46,9 @@ struct PeerArgs {
   float eps, w_offset;
   int* status;
   unsigned long long* trace;     // optional: 8 timestamps (ns) of block 0 for the phase timeline, or nullptr
+  int pushed;                       // 1: the partial rows were pushed into this rank's slots by the producers
+  long long off_push_flags;         // uint32 [8] in every heap: call counter of each source's last finished push
+  const unsigned int* push_epoch;   // local: call counter of this rank's own producer (all ranks agree on it)
 };
 
 struct __align__(16) bf16x8 {
@@ -181,11 +184,19 @@ __device__ __forceinline__ float group16_max(float v) {
 
 // Sum of the `world` partial vectors (8 bf16 each) at element offset `elem` of the partial buffers,
 // in rank order, rounded to bf16 like the all-reduced bf16 tensor it stands for.
-__device__ __forceinline__ void pull_sum8(const PeerArgs& a, size_t elem, float (&acc)[8]) {
+// Pull mode: source s holds row `row` of its own [T, H] partial buffer.  Pushed mode: the producers
+// already stored their rows into this rank's slots [source][rows_per][H] (GEMM epilogue, PushArgs of
+// gemm_sm100.cu), so all loads are local.
+__device__ __forceinline__ void pull_sum8(const PeerArgs& a, int row, int lr, int rows_per, int col,
+                                          float (&acc)[8]) {
   uint4 raw[kMaxRanks];
 #pragma unroll
   for (int s = 0; s < kMaxRanks; ++s)
-    if (s < a.world) raw[s] = ld_cg16(a.heap[s] + a.off_partial + elem * 2);
+    if (s < a.world) {
+      const size_t elem = a.pushed ? (static_cast<size_t>(s) * rows_per + lr) * a.H + col
+                                   : static_cast<size_t>(row) * a.H + col;
+      raw[s] = ld_cg16(a.heap[a.pushed ? a.rank : s] + a.off_partial + elem * 2);
+    }
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
@@ -217,9 +228,31 @@ peer_reduce_kernel(const PeerArgs a) {
 
   const bool tracing = a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
   if (tracing) a.trace[0] = global_ns();
-  sync.signal(0, false);                       // my producer kernel has finished: its partial rows may be read
-  if (tracing) a.trace[1] = global_ns();
-  bool ok = sync.wait(0);
+  bool ok;
+  if (a.pushed) {
+    // the producers flagged their pushes themselves: wait until every source's counter reached this call
+    if (threadIdx.x < a.world) {
+      const unsigned int want = *a.push_epoch;
+      const unsigned int* f = reinterpret_cast<const unsigned int*>(a.heap[a.rank] + a.off_push_flags) + threadIdx.x;
+      const unsigned long long t0 = global_ns();
+      unsigned int polls = 0;
+      while (static_cast<int>(ld_relaxed_sys(f) - want) < 0) {
+        if ((++polls & 63u) == 0 && global_ns() - t0 > kPeerWaitNs) {
+          atomicExch(a.status, sm100::kErrPeerWait);
+          failed = 1;
+          break;
+        }
+      }
+      (void)ld_acquire_sys(f);
+    }
+    __syncthreads();
+    ok = failed == 0;
+    if (tracing) a.trace[1] = global_ns();
+  } else {
+    sync.signal(0, false);                     // my producer kernel has finished: its partial rows may be read
+    if (tracing) a.trace[1] = global_ns();
+    ok = sync.wait(0);
+  }
   if (tracing) a.trace[2] = global_ns();
   if (ok) {
     for (int lr = blockIdx.x; lr < my_rows; lr += gridDim.x) {
@@ -228,7 +261,7 @@ peer_reduce_kernel(const PeerArgs a) {
       if (!NORM) {
         for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
           float acc[8];
-          pull_sum8(a, rbase + v * 8, acc);
+          pull_sum8(a, row, lr, rows_per, v * 8, acc);
           const uint4 packed = pack8(acc);
 #pragma unroll
           for (int d = 0; d < kMaxRanks; ++d)
@@ -244,7 +277,7 @@ peer_reduce_kernel(const PeerArgs a) {
             const size_t lbase = static_cast<size_t>(lr) * a.H + v * 8;
             uint4 res_raw = make_uint4(0, 0, 0, 0);   // issued before the peer loads so the latencies overlap
             if (a.residual_in != nullptr) res_raw = *reinterpret_cast<const uint4*>(a.residual_in + lbase);
-            pull_sum8(a, rbase + v * 8, s[i]);
+            pull_sum8(a, row, lr, rows_per, v * 8, s[i]);
             if (a.residual_in != nullptr) {
               float r[8];
               unpack8(res_raw, r);
@@ -467,7 +500,8 @@ int tgi_peer_max_blocks() { return kMaxBlocks; }
 int tgi_peer_reduce(void* const* heaps, int rank, int world, int T, int H, long long off_partial, long long off_gather,
                     long long off_gscale, int gscale_pitch, long long off_flags, unsigned int* epoch,
                     const void* residual_in, void* residual_out, const void* weight, float eps, float w_offset,
-                    int mode, int blocks, int* status, unsigned long long* trace, cudaStream_t stream) {
+                    int mode, int blocks, int* status, unsigned long long* trace, int pushed, long long off_push_flags,
+                    const unsigned int* push_epoch, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -10;
   if (H % 8 != 0 || blocks < 1 || blocks > kMaxBlocks) return -11;
@@ -492,6 +526,10 @@ int tgi_peer_reduce(void* const* heaps, int rank, int world, int T, int H, long 
   a.w_offset = w_offset;
   a.status = status;
   a.trace = trace;
+  a.pushed = pushed;
+  a.off_push_flags = off_push_flags;
+  a.push_epoch = push_epoch;
+  if (pushed && push_epoch == nullptr) return -15;
   switch (mode) {
     case 0: return launch_reduce<false, false>(a, blocks, stream);
     case 1: return launch_reduce<true, false>(a, blocks, stream);
@@ -523,6 +561,9 @@ int tgi_peer_argmax(void* const* heaps, int rank, int world, const void* logits,
   a.eps = a.w_offset = 0.f;
   a.status = status;
   a.trace = nullptr;
+  a.pushed = 0;
+  a.off_push_flags = 0;
+  a.push_epoch = nullptr;
   peer_argmax_kernel<<<blocks, 1024, 0, stream>>>(a, static_cast<const __nv_bfloat16*>(logits), row_stride, vocab_start,
                                                   logit_scale, off_cand, ids, logprob);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;

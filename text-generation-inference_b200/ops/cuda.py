@@ -149,6 +149,17 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     M, K = x2.shape
     N = w.shape[0]
     assert w.shape[1] == K and w.is_contiguous()
+    if getattr(out, "is_peer_push", False):
+        # row-parallel GEMM of a tensor-parallel group: rows go straight to their owners' peer memory
+        if M == 0:
+            return out
+        assert out.T == M and out.N == N
+        st = state(x.device)
+        ctas = _gemm_ctas(lib, st, M, N, max_ctas)
+        _check(lib.tgi_gemm_push(c_int(0), _ptr(x2), c_void_p(0), c_int(0), _ptr(w), c_void_p(0), _ptr(bias), c_int(M),
+                                 c_int(N), c_int(K), c_int(ctas), _ptr(st.ws), _ptr(st.counters), _ptr(st.status),
+                                 *out.gemm_args(), _stream()), "gemm_push")
+        return out
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     else:
@@ -168,6 +179,19 @@ def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, bias=None, max_ctas
     N = wq.shape[0]
     assert wq.shape[1] == K and wq.is_contiguous() and xq.is_contiguous()
     assert out_dtype == torch.bfloat16
+    if getattr(out, "is_peer_push", False):
+        if M == 0:
+            return out
+        assert out.T == M and out.N == N
+        st = state(xq.device)
+        sptr, pitch = _scale_storage(xs)
+        ctas = _gemm_ctas(lib, st, M, N, max_ctas)
+        if not ws.is_contiguous():
+            ws = ws.contiguous()
+        _check(lib.tgi_gemm_push(c_int(1), _ptr(xq), c_void_p(sptr), c_int(pitch), _ptr(wq), _ptr(ws), _ptr(bias),
+                                 c_int(M), c_int(N), c_int(K), c_int(ctas), _ptr(st.ws), _ptr(st.counters),
+                                 _ptr(st.status), *out.gemm_args(), _stream()), "gemm_push")
+        return out
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
     else:

@@ -20,6 +20,7 @@ never crosses NVLink.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -73,8 +74,10 @@ class PeerComm:
         nflag = 2 * self.max_blocks * 8 * 4
         nrows = self.max_tokens * self.width * 2
         self.off_flags = 0
-        self.off_partial = _round_up(nflag, _ALIGN)
-        self.off_gather = self.off_partial + _round_up(nrows, _ALIGN)
+        self.off_push_flags = nflag           # uint32 [8]: call counter of every source's last finished push
+        self.off_partial = _round_up(nflag + 64, _ALIGN)
+        # as push slots [world][ceil(T / world)][width] the region can need up to world - 1 rows more than T
+        self.off_gather = self.off_partial + _round_up(nrows + 8 * self.width * 2, _ALIGN)
         self.off_gscale = self.off_gather + _round_up(nrows, _ALIGN)
         self.off_cand = self.off_gscale + _round_up(max(self.width // 128, 1) * self.pitch * 4, _ALIGN)
         self.max_argmax_rows = 1024          # greedy candidates: 16 bytes per row and rank
@@ -110,6 +113,9 @@ class PeerComm:
         self._gather = self._heap_t[self.off_gather:self.off_gather + nrows]
         self._gscale = self._heap_t[self.off_gscale:self.off_cand].view(torch.float32)
         self.epoch = torch.zeros(self.max_blocks, dtype=torch.int32, device=device)
+        self.push_state = torch.zeros(2, dtype=torch.int32, device=device)   # [finished CTAs, call counter]
+        # row-parallel GEMMs push their rows to the owners from this many tokens on; smaller steps pull
+        self.push_min_tokens = int(os.environ.get("TGI_B200_PUSH_MIN_TOKENS", "512"))
         rows_per = (self.max_tokens + world - 1) // world
         self.residual = torch.zeros(rows_per, self.width, dtype=torch.bfloat16, device=device)
         self.status = K.state(device).status
@@ -135,14 +141,24 @@ class PeerComm:
     def _blocks(self, T: int) -> int:
         return max(1, min(128, self.max_blocks, (T + self.world - 1) // self.world))
 
-    def _launch(self, T: int, H: int, mode: int, residual_in, residual_out, weight, eps: float, w_offset: float):
+    def _launch(self, T: int, H: int, mode: int, residual_in, residual_out, weight, eps: float, w_offset: float,
+                pushed: bool = False):
         rc = self.lib.tgi_peer_reduce(
             self._heap_arr, ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(T), ctypes.c_int(H),
             ctypes.c_longlong(self.off_partial), ctypes.c_longlong(self.off_gather), ctypes.c_longlong(self.off_gscale),
             ctypes.c_int(self.pitch), ctypes.c_longlong(self.off_flags), K._ptr(self.epoch),
             K._ptr(residual_in), K._ptr(residual_out), K._ptr(weight), ctypes.c_float(eps), ctypes.c_float(w_offset),
-            ctypes.c_int(mode), ctypes.c_int(self._blocks(T)), K._ptr(self.status), K._ptr(self.trace), K._stream())
+            ctypes.c_int(mode), ctypes.c_int(self._blocks(T)), K._ptr(self.status), K._ptr(self.trace),
+            ctypes.c_int(1 if pushed else 0), ctypes.c_longlong(self.off_push_flags),
+            ctypes.c_void_p(self.push_state.data_ptr() + 4), K._stream())
         K._check(rc, "peer_reduce")
+
+    def push_target(self, T: int, N: Optional[int] = None) -> "PeerPush":
+        """Destination object for a row-parallel GEMM (pass it as ``out=``): the GEMM's epilogue stores
+        every output row into the peer-memory slot of the rank that owns the row.  If the linear
+        cannot push (no native kernel for its weight format) it writes ``fallback`` instead and the
+        reduction pulls as usual; ``used`` tells which happened."""
+        return PeerPush(self, T, N or self.width)
 
     # ---- collectives ---------------------------------------------------------------------------
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
@@ -164,7 +180,7 @@ class PeerComm:
         return t
 
     def reduce_norm(self, T: int, weight: torch.Tensor, eps: float, w_offset: float = 0.0, quant: bool = False,
-                    first: bool = False):
+                    first: bool = False, source: Optional["PeerPush"] = None):
         """Sum the ranks' ``partial(T)`` rows, add the residual stream, RMSNorm (and quantise).
 
         Returns the normalised activations of all ``T`` rows: a bf16 ``[T, H]`` tensor, or
@@ -174,7 +190,9 @@ class PeerComm:
         """
         H = self.width
         assert T <= self.max_tokens and weight.shape[0] == H
-        self._launch(T, H, 2 if quant else 1, None if first else self.residual, self.residual, weight, eps, w_offset)
+        pushed = source is not None and source.used
+        self._launch(T, H, 2 if quant else 1, None if first else self.residual, self.residual, weight, eps, w_offset,
+                     pushed=pushed)
         if quant:
             return self._gather_fp8(T, H)
         return self._gather_bf16(T, H)
@@ -208,6 +226,33 @@ class PeerComm:
         if self.base:
             self.lib.tgi_peer_free(ctypes.c_void_p(self.base))
             self.base = 0
+
+
+class PeerPush:
+    """``out=`` target that makes a GEMM store its rows into the owners' peer-memory slots.
+
+    ``ops.cuda.gemm_bf16`` / ``gemm_fp8_block`` recognise it by ``is_peer_push`` and call
+    ``launch(...)``; any other producer may write the plain tensor ``fallback`` (the pull buffer)."""
+
+    is_peer_push = True
+
+    def __init__(self, comm: PeerComm, T: int, N: int):
+        self.comm, self.T, self.N = comm, T, N
+        self.rows_per = (T + comm.world - 1) // comm.world
+        self.used = False
+        assert comm.world * self.rows_per * N <= (comm.max_tokens + 8) * comm.width
+
+    @property
+    def fallback(self) -> torch.Tensor:
+        return self.comm.partial(self.T, self.N)
+
+    def gemm_args(self):
+        """Trailing arguments of ``tgi_gemm_push`` that describe the destination."""
+        c = self.comm
+        self.used = True
+        return (c._heap_arr, ctypes.c_int(c.rank), ctypes.c_int(c.world), ctypes.c_int(self.rows_per),
+                ctypes.c_longlong(c.off_partial), ctypes.c_longlong(c.off_push_flags),
+                ctypes.c_void_p(c.push_state.data_ptr()), ctypes.c_void_p(c.push_state.data_ptr() + 4))
 
 
 def make_comm(group, rank: int, world: int, device: torch.device, hidden: int, max_tokens: int):
