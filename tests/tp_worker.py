@@ -72,6 +72,10 @@ def main():
     path = os.environ["TP_WORKER_DIR"]
     cfg = llama_config(hidden=512, layers=3, heads=8, kv_heads=8 if world > 2 else 2, intermediate=1024, vocab=4096,
                        max_pos=1024)
+    if os.environ.get("TP_WORKER_MODEL") == "mixtral":
+        # sparse MoE: experts are placed whole on their owner rank (expert parallel) when the count divides
+        cfg = llama_config(hidden=512, layers=2, heads=8, kv_heads=8 if world > 2 else 2, intermediate=512, vocab=4096,
+                           max_pos=1024, model_type="mixtral", num_local_experts=8, num_experts_per_tok=2)
     if rank == 0:
         write_llama_checkpoint(path, cfg, std=0.05)
     pdist.barrier(group)
@@ -96,7 +100,7 @@ def main():
     assert diff <= 0.04 * scale, f"peer vs group collectives: {diff} (scale {scale})"
 
     sd = llama_state_dict(cfg, std=0.05)
-    for i, p in enumerate(prompts):
+    for i, p in enumerate(prompts if cfg["model_type"] == "llama" else []):   # the dense oracle covers Llama only
         want = reference_llama_forward(sd, cfg, torch.tensor(p))[-1]
         got = logits_peer[i].cpu()
         err = (got - want).abs().max().item()

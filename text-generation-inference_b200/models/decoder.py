@@ -281,7 +281,8 @@ class DenseMLP:
 class SparseMoE:
     """Top-k routed experts.  Tensor-parallel mode slices every expert's intermediate dimension
     (what the reference does, ``layers/moe/unquantized.py:107-163``); expert-parallel mode
-    (``parallel/expert.py``) places whole experts on ranks and exchanges tokens instead."""
+    (``parallel/expert.py``) places whole experts on ranks.  Either way a rank ends up with a partial
+    ``[T, H]`` output that is summed over ranks by the layer's reduction."""
 
     def __init__(self, arch: Arch, cfg, dims: ModelDims, prefix: str, weights, comm):
         pg = weights.process_group
@@ -291,7 +292,21 @@ class SparseMoE:
         self.router = FastLinear(weights.get_tensor(f"{prefix}.{arch.moe_router}.weight"))
         E = dims.num_experts
         gu, dn = [], []
-        if arch.moe_fused:  # dbrx: [E*I, H] stacked
+        from ..parallel.expert import ExpertParallel, local_expert_range, wants_expert_parallel
+
+        self.expert_parallel = None
+        if not arch.moe_fused and wants_expert_parallel(E, pg.size()):
+            # whole experts on their owner rank (no slicing); see parallel/expert.py
+            lo, hi = local_expert_range(E, pg.rank(), pg.size())
+            for e in range(lo, hi):
+                ep = f"{prefix}.{arch.moe_expert.format(e=e)}"
+                gu.append(torch.cat([weights.get_tensor(f"{ep}.{arch.moe_gate}.weight"),
+                                     weights.get_tensor(f"{ep}.{arch.moe_up}.weight")], dim=0))
+                dn.append(weights.get_tensor(f"{ep}.{arch.moe_down}.weight"))
+            self.w_gate_up = torch.stack(gu).contiguous()   # [E / world, 2I, H]
+            self.w_down = torch.stack(dn).contiguous()       # [E / world, H, I]
+            self.expert_parallel = ExpertParallel(self.w_gate_up, self.w_down, lo, self.act)
+        elif arch.moe_fused:  # dbrx: [E*I, H] stacked
             ep = f"{prefix}.{arch.moe_expert}"
             I = dims.intermediate
             w1 = weights.get_tensor(f"{ep}.{arch.moe_gate}").view(E, I, dims.hidden)
@@ -317,7 +332,6 @@ class SparseMoE:
                                    names=("gate_proj", "up_proj", "down_proj"))
             if arch.moe_shared_gate and weights.has_tensor(f"{prefix}.{arch.moe_shared_gate}.weight"):
                 self.shared_gate = FastLinear(weights.get_tensor(f"{prefix}.{arch.moe_shared_gate}.weight"))
-        self.expert_parallel = None  # set by parallel.expert.enable()
 
     def __call__(self, x, x_scale=None, reduce: bool = True, meta=None, out=None):
         if out is not None:
@@ -327,6 +341,11 @@ class SparseMoE:
         w, idx = ops.moe_topk_softmax(logits, self.top_k, self.renorm)
         if self.expert_parallel is not None:
             out = self.expert_parallel(x, w, idx)
+        elif x.is_cuda and (x.shape[0] <= 512 or torch.cuda.is_current_stream_capturing()):
+            # decode-sized step: fixed-shape evaluation of every expert (graph capturable, weight-bound)
+            from ..parallel.expert import dense_experts
+
+            out = dense_experts(x, self.w_gate_up, self.w_down, w, idx, 0, self.act)
         else:
             out = ops.moe_experts(x, self.w_gate_up, self.w_down, w.to(x.dtype), idx, self.act)
         if self.shared is not None:
@@ -334,7 +353,7 @@ class SparseMoE:
             if self.shared_gate is not None:
                 s = s * torch.sigmoid(self.shared_gate(x).float()).to(s.dtype)
             out = out + s
-        if reduce and self.pg.size() > 1 and self.expert_parallel is None:
+        if reduce and self.pg.size() > 1:   # tensor-parallel slices and expert-parallel rows both sum over ranks
             out = self.comm.all_reduce(out) if self.comm is not None else _all_reduce(out, self.pg)
         return out
 

@@ -242,6 +242,7 @@ class TensorParallelHead:
     def gather(self, local: torch.Tensor) -> torch.Tensor:
         world = self.process_group.size()
         B, Vl = local.shape
-        gathered = local.new_empty(world, B, Vl)
+        # concatenated along dim 0 (the one layout every backend accepts), then viewed per rank
+        gathered = local.new_empty(world * B, Vl)
         pdist.all_gather_into(gathered, local.contiguous(), self.process_group)
-        return gathered.permute(1, 0, 2).reshape(B, world * Vl)
+        return gathered.view(world, B, Vl).permute(1, 0, 2).reshape(B, world * Vl)

@@ -1,0 +1,100 @@
+"""Expert parallelism for sparse mixture-of-experts layers.
+
+The reference only tensor-parallelises experts: every rank holds a 1/tp slice of every expert and the
+partial outputs are all-reduced (``layers/moe/unquantized.py:107-163``,
+``flash_mixtral_modeling.py:343-351``).  With expert parallelism each rank holds whole experts
+(expert ``e`` lives on rank ``e // (E / world)``), which gives every expert GEMM its full K and N.
+
+Token exchange.  The attention block of the same layer is tensor parallel, and the fused reduction that
+follows it (``parallel/peer.py``) leaves the normalised activations of *all* tokens on every rank.  So
+the "dispatch" all-to-all degenerates: a rank already holds every token routed to its experts and only
+has to select them.  The "combine" is a sum over ranks of rows that are non-zero on at most ``top_k``
+ranks; it is done by the same peer-memory kernel that reduces dense layers, fused with the residual add
+and the next RMSNorm, so an expert-parallel layer issues exactly one collective.
+
+Two evaluation modes of the local experts:
+
+* ``dense`` (decode-sized steps, CUDA-graph capturable): every local expert runs on all ``T`` tokens and
+  its output is scaled by the token's routing weight (zero when the token was not routed to it).  At
+  decode batch sizes an expert GEMM is bound by streaming its weights, which have to be read as soon as
+  one token uses the expert, so the extra FLOPs are free and there is no data-dependent shape.
+* ``routed`` (prefill-sized steps): tokens are sorted by expert and each expert runs on its own rows.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+
+
+def local_expert_range(num_experts: int, rank: int, world: int):
+    assert num_experts % world == 0, "expert parallelism needs the expert count to be divisible by the ranks"
+    per = num_experts // world
+    return rank * per, (rank + 1) * per
+
+
+class ExpertParallel:
+    """Evaluates the experts owned by this rank; ``__call__`` returns this rank's partial output ``[T, H]``."""
+
+    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, first: int, act: str,
+                 dense_max_tokens: Optional[int] = None):
+        self.w_gate_up, self.w_down, self.first, self.act = w_gate_up, w_down, first, act
+        self.n_local = w_gate_up.shape[0]
+        self.dense_max_tokens = int(os.environ.get("TGI_B200_MOE_DENSE_TOKENS", "512")) \
+            if dense_max_tokens is None else dense_max_tokens
+
+    def __call__(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        T = x.shape[0]
+        if T <= self.dense_max_tokens or torch.cuda.is_current_stream_capturing():
+            return dense_experts(x, self.w_gate_up, self.w_down, topk_weights, topk_ids, self.first, self.act)
+        # routed: keep the (token, slot) pairs that point at a local expert, grouped by expert
+        local = (topk_ids >= self.first) & (topk_ids < self.first + self.n_local)
+        tok, slot = local.nonzero(as_tuple=True)
+        e = topk_ids[tok, slot] - self.first
+        order = torch.argsort(e, stable=True)
+        tok, slot = tok[order], slot[order]
+        w = topk_weights[tok, slot].float()
+        counts = torch.bincount(e, minlength=self.n_local).tolist()
+        out = torch.zeros(T, x.shape[1], dtype=torch.float32, device=x.device)
+        start = 0
+        for j, c in enumerate(counts):
+            if c == 0:
+                continue
+            rows = tok[start:start + c]
+            h = ops.linear(x.index_select(0, rows), self.w_gate_up[j])
+            y = ops.linear(ops.act_and_mul(h, self.act), self.w_down[j])
+            out.index_add_(0, rows, y.float() * w[start:start + c].unsqueeze(1))
+            start += c
+        return out.to(x.dtype)
+
+
+def dense_experts(x, w_gate_up, w_down, topk_weights, topk_ids, first: int, act: str) -> torch.Tensor:
+    """``sum_e route[t, e] * MLP_e(x[t])`` over the experts ``first .. first + E_local`` with fixed shapes."""
+    T, H = x.shape
+    E_local = w_gate_up.shape[0]
+    route = torch.zeros(T, first + E_local + 1, dtype=torch.float32, device=x.device)
+    # ids outside the local range land in columns that are never read (clamped to the last column)
+    cols = torch.where((topk_ids >= first) & (topk_ids < first + E_local), topk_ids,
+                       torch.full_like(topk_ids, first + E_local))
+    route.scatter_add_(1, cols.long(), topk_weights.float())
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    for j in range(E_local):
+        h = ops.linear(x, w_gate_up[j])
+        a = ops.act_and_mul(h, act)
+        y = ops.linear(a, w_down[j])
+        out.addcmul_(y.float(), route[:, first + j:first + j + 1])
+    return out.to(x.dtype)
+
+
+def wants_expert_parallel(num_experts: int, world: int) -> bool:
+    mode = os.environ.get("TGI_B200_MOE_PARALLEL", "auto")
+    if world == 1 or mode == "tp":
+        return False
+    if num_experts % world != 0:
+        if mode == "ep":
+            raise ValueError(f"{num_experts} experts cannot be spread over {world} ranks")
+        return False
+    return mode in ("ep", "auto")
