@@ -259,3 +259,12 @@ def test_benchmark_tool_against_the_shard(stack):
     table = subprocess.run([str(exe), "-m", stack["uds"], "-b", "2", "-s", "8", "-d", "3", "-r", "1"],
                            capture_output=True, text=True, timeout=120)
     assert table.returncode == 0 and "Decode throughput (tokens/s)" in table.stdout
+
+
+def test_load_generator_against_the_stack(stack):
+    from tgi_b200.client import load_test
+
+    res = load_test.main(["--url", f"http://127.0.0.1:{stack['port']}", "--rates", "20", "--requests", "12",
+                          "--prompt-len", "8:40", "--output-len", "5"])
+    assert len(res) == 1 and res[0]["failed"] == 0 and res[0]["output_tok_s"] > 0
+    assert res[0]["ttft_ms"]["p50"] > 0 and res[0]["itl_ms"]["p50"] > 0
