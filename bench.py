@@ -284,7 +284,7 @@ def main():
         e2e_value = C * args.steps / (api_ms / 1e3)
         ttft_sorted = sorted(ttft_ms)
         out = {
-            "metric": METRIC, "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC if args.model == "llama70b-fp8" else f"output tok/s (decode, {args.model}, TP=N)", "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (block-scaled weights+activations, fp8 KV)"
             if fp8 else "bf16", "data": "synthetic: random-token prompts, random-init N(0,0.02) weights",
@@ -292,7 +292,7 @@ def main():
             "config": {"model": args.model if not args.layers else f"{args.model}-{args.layers}L",
                        "global_batch": C, "seq_len": start_ctx + args.warmup, "prompt_len": start_ctx,
                        "nominal_prompt_len": P, "output_len": O,
-                       "parallelism": f"tp{world}", "collectives": "nccl" if comm is None else "peer-memory kernels", "block_size": BLOCK_SIZE, "l2": "inputs larger than L2",
+                       "parallelism": f"tp{world}", "collectives": "none (one GPU)" if world == 1 else ("nccl" if comm is None else "peer-memory kernels"), "block_size": BLOCK_SIZE, "l2": "inputs larger than L2",
                        "timed": "CUDA events around K graph replays, max over ranks",
                        "setup": "fast-setup (random KV, development)" if args.fast_setup else "real prefill"},
             "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d_bytes,
