@@ -1,4 +1,5 @@
 #include "api.hpp"
+#include "images.hpp"
 
 #include <algorithm>
 #include <chrono>
@@ -140,7 +141,41 @@ GenerateParams Router::validate(const std::string& inputs, const Value& p) {
   }
   // tokenise (the scheduler needs the ids for prefix caching and the length for its budgets)
   const bool add_special = bool_or(p, "add_special_tokens", true);
-  v.input_ids = text_.encode(inputs, add_special, truncate);
+  std::vector<images::Piece> pieces;
+  if (images::tokens_per_image(cfg_.model_config, 1, 1) > 0) pieces = images::split_markdown(inputs);
+  bool has_image = false;
+  for (const auto& pc : pieces) has_image = has_image || pc.is_image;
+  if (has_image) {
+    // vision-language request: text pieces are tokenised on their own, every image contributes
+    // placeholder ids (derived from its bytes, so the prefix cache tells images apart)
+    if (truncate) throw validation_error("`truncate` cannot be combined with image inputs");
+    bool first_text = true;
+    for (const auto& pc : pieces) {
+      pb::InputChunk c;
+      if (!pc.is_image) {
+        if (pc.text.empty()) continue;
+        auto ids = text_.encode(pc.text, add_special && first_text, 0);
+        first_text = false;
+        v.input_ids.insert(v.input_ids.end(), ids.begin(), ids.end());
+        c.text = pc.text;
+      } else {
+        images::Fetched img;
+        try {
+          img = images::fetch(pc.text, cfg_.max_image_bytes);
+        } catch (const std::exception& e) {
+          throw validation_error(std::string("invalid image: ") + e.what());
+        }
+        const uint32_t n = images::tokens_per_image(cfg_.model_config, img.width, img.height);
+        for (uint32_t i = 0; i < n; ++i) v.input_ids.push_back(images::placeholder_id(img.data, i));
+        c.is_image = true;
+        c.data = std::move(img.data);
+        c.mimetype = img.mimetype;
+      }
+      v.chunks.push_back(std::move(c));
+    }
+  } else {
+    v.input_ids = text_.encode(inputs, add_special, truncate);
+  }
   v.input_length = static_cast<uint32_t>(v.input_ids.size());
   if (v.input_length == 0) throw validation_error("`inputs` cannot be empty");
   if (v.input_length > cfg_.max_input_tokens)
@@ -161,9 +196,11 @@ GenerateParams Router::validate(const std::string& inputs, const Value& p) {
                            ". Given: " + std::to_string(v.input_length) + " `inputs` tokens and " +
                            std::to_string(max_new) + " `max_new_tokens`");
   v.inputs = inputs;
-  pb::InputChunk chunk;
-  chunk.text = inputs;
-  v.chunks.push_back(chunk);
+  if (!has_image) {
+    pb::InputChunk chunk;
+    chunk.text = inputs;
+    v.chunks.push_back(chunk);
+  }
   v.truncate = truncate;
   v.add_special_tokens = add_special;
   v.top_n_tokens = top_n;

@@ -60,6 +60,10 @@ struct RouterConfig {
   uint32_t max_batch_total_tokens = 0, max_waiting_tokens = 20;
   std::optional<size_t> max_batch_size;
   uint32_t validation_workers = 2;
+  // config.json of the checkpoint (null when unknown): decides whether `inputs` may carry images and
+  // how many placeholder tokens an image costs
+  json::Value model_config;
+  size_t max_image_bytes = 20u << 20;
 };
 
 struct GenerateParams {   // the `parameters` object of /generate, already range-checked

@@ -5,7 +5,9 @@
 #include <csignal>
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <iostream>
+#include <sstream>
 #include <map>
 
 #include "api.hpp"
@@ -229,6 +231,18 @@ int main(int argc, char** argv) {
     rc.dtype = info.dtype;
     rc.device_type = info.device_type;
     rc.max_batch_total_tokens = max_batch_total;
+    {
+      // the checkpoint's config.json tells whether this is a vision-language model
+      std::ifstream cf(tokenizer + "/config.json");
+      if (cf) {
+        std::stringstream ss;
+        ss << cf.rdbuf();
+        try {
+          rc.model_config = json::Value::parse(ss.str());
+        } catch (const std::exception&) {
+        }
+      }
+    }
     api::Router router(backend, python_text_services(), rc, &metrics);
 
     http::Server server(args.get("hostname", "0.0.0.0"), static_cast<int>(args.num("port", 3000)),
