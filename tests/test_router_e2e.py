@@ -268,3 +268,27 @@ def test_load_generator_against_the_stack(stack):
                           "--prompt-len", "8:40", "--output-len", "5"])
     assert len(res) == 1 and res[0]["failed"] == 0 and res[0]["output_tok_s"] > 0
     assert res[0]["ttft_ms"]["p50"] > 0 and res[0]["itl_ms"]["p50"] > 0
+
+
+def test_kserve_routes(stack):
+    port = stack["port"]
+    st, body = _get(port, "/v2")
+    assert st == 200 and json.loads(body)["name"] == "text-generation-inference"
+    assert _get(port, "/v2/health/live")[0] == 200 and json.loads(_get(port, "/v2/health/ready")[1])["live"] is True
+    st, body = _get(port, "/v2/models/tgi/versions/1")
+    meta = json.loads(body)
+    assert st == 200 and meta["inputs"][0]["datatype"] == "BYTES" and meta["versions"] == ["1"]
+    assert json.loads(_get(port, "/v2/models/tgi/versions/1/ready")[1])["ready"] is True
+    st, _, body = _post(port, "/v2/models/tgi/versions/1/infer", {
+        "id": "42", "inputs": [{"name": "text_input", "shape": [2], "datatype": "BYTES", "data": ["hello world", "hi"]}],
+        "parameters": {"max_new_tokens": 4}})
+    assert st == 200, body
+    out = json.loads(body)
+    assert out["id"] == "42" and out["model_name"] == "tgi" and len(out["outputs"]) == 2
+    text = bytes(out["outputs"][0]["data"]).decode("utf-8", "replace")
+    st2, _, plain = _post(port, "/generate", {"inputs": "hello world", "parameters": {"max_new_tokens": 4}})
+    assert st2 == 200 and json.loads(plain)["generated_text"] == text
+    st, _, body = _post(port, "/v2/models/tgi/versions/1/infer", {"inputs": []})
+    assert st == 422
+    with pytest.raises(urllib.error.HTTPError):
+        _get(port, "/v2/nothing/here")

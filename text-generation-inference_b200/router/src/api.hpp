@@ -111,6 +111,7 @@ class Router {
   void h_chat_tokenize(const http::Request&, http::Response&);
   void h_invocations(const http::Request&, http::Response&);
   void h_vertex(const http::Request&, http::Response&);
+  void h_kserve(const http::Request&, http::Response&);   // every /v2/... path (KServe open inference protocol)
   void generate_response(const std::string& inputs, const json::Value& params, http::Response& resp, bool as_array);
   void generate_stream_response(const std::string& inputs, const json::Value& params, http::Response& resp);
   void send_error(http::Response& resp, const ApiError& e);

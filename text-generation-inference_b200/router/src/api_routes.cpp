@@ -332,6 +332,7 @@ void Router::install(http::Server& s) {
   s.route("POST", "/chat_tokenize", std::bind(&Router::h_chat_tokenize, this, _1, _2));
   s.route("POST", "/invocations", std::bind(&Router::h_invocations, this, _1, _2));
   s.route("POST", "/vertex", std::bind(&Router::h_vertex, this, _1, _2));
+  s.set_fallback(std::bind(&Router::h_kserve, this, _1, _2));   // parameterised /v2/models/{name}/versions/{v}/... paths
   auto info = [this](const http::Request&, http::Response& r) { r.send(200, "application/json", info_json().dump()); };
   s.route("GET", "/info", info);
   s.route("GET", "/", [this](const http::Request&, http::Response& r) {
