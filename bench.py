@@ -116,6 +116,8 @@ def model_config(args):
         fp8, kv_fp8 = True, True
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
+    # long-context runs: the rotary table must cover every position that will be generated
+    cfg["max_position_embeddings"] = max(int(cfg["max_position_embeddings"]), args.prompt_len + args.output_len + 8)
     return cfg, fp8, kv_fp8
 
 

@@ -251,9 +251,12 @@ __global__ void __launch_bounds__(256)
 rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
                   const float* __restrict__ cos_sin, const int* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
                   void* __restrict__ k_cache, void* __restrict__ v_cache, const float* __restrict__ k_scale,
-                  const float* __restrict__ v_scale, int Hq, int Hkv, int D, int rot, int neox, long long num_slots) {
+                  const float* __restrict__ v_scale, int Hq, int Hkv, int D, int rot, int neox, long long num_slots,
+                  int max_pos) {
   const int t = blockIdx.x;
-  const int pos = positions[t];
+  // a position beyond the rotary table (operator asked for more tokens than the model supports) reads
+  // the table's last row instead of running off its end
+  const int pos = min(max(positions[t], 0), max_pos - 1);
   const long long slot = slots[t];
   const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * (Hq + 2 * Hkv) * D;
   const float* cs = cos_sin + static_cast<size_t>(pos) * rot;
@@ -443,17 +446,17 @@ int tgi_quant_act(const void* x, void* q_out, float* scale_t, int scale_pitch, i
 
 int tgi_rope_cache(const void* qkv, const int* positions, const float* cos_sin, const int* slots, void* q_out,
                    void* k_cache, void* v_cache, const float* k_scale, const float* v_scale, int T, int Hq, int Hkv,
-                   int D, int rot, int neox, long long num_slots, int fp8_cache, cudaStream_t stream) {
+                   int D, int rot, int neox, long long num_slots, int fp8_cache, int max_pos, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (D % 2 != 0 || rot % 2 != 0 || rot > D) return -10;
+  if (D % 2 != 0 || rot % 2 != 0 || rot > D || max_pos < 1) return -10;
   if (fp8_cache)
     rope_cache_kernel<true><<<T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
                                                    static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale,
-                                                   v_scale, Hq, Hkv, D, rot, neox, num_slots);
+                                                   v_scale, Hq, Hkv, D, rot, neox, num_slots, max_pos);
   else
     rope_cache_kernel<false><<<T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
                                                     static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale,
-                                                    v_scale, Hq, Hkv, D, rot, neox, num_slots);
+                                                    v_scale, Hq, Hkv, D, rot, neox, num_slots, max_pos);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -293,7 +293,8 @@ def rope_and_cache(qkv, positions, cos_sin, slots, k_cache, v_cache, num_heads, 
     _check(lib.tgi_rope_cache(_ptr(qkv), _ptr(positions), _ptr(cos_sin), _ptr(slots), _ptr(q), _ptr(k_cache),
                               _ptr(v_cache), _ptr(k_scale if fp8 else None), _ptr(v_scale if fp8 else None),
                               c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(rot_dim),
-                              c_int(1 if neox else 0), c_ll(num_slots), c_int(1 if fp8 else 0), _stream()),
+                              c_int(1 if neox else 0), c_ll(num_slots), c_int(1 if fp8 else 0),
+                              c_int(cos_sin.shape[0]), _stream()),
            "rope_and_cache")
     return q
 
