@@ -1,0 +1,107 @@
+"""Fused sampler kernel against the sort-based PyTorch warpers: supports of top-k / top-p, argmax rows,
+log-probabilities, distribution of the draws, and reproducibility per (seed, step)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _torch_filtered(scores, temperature, top_k, top_p):
+    from tgi_b200.utils.tokens import top_k_filter, top_p_filter
+
+    x = scores.float() / temperature.view(-1, 1)
+    x = top_k_filter(x, top_k)
+    x = top_p_filter(x, top_p)
+    return x
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_supports_logprobs_and_greedy_rows(dtype):
+    from tgi_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    B, V = 64, 32003
+    scores = (torch.randn(B, V, device=dev, generator=g) * 3).to(dtype)
+    temperature = torch.rand(B, device=dev, generator=g) * 1.5 + 0.3
+    top_k = torch.randint(0, 200, (B,), device=dev, generator=g, dtype=torch.int32)
+    top_k[::5] = 0
+    top_p = torch.rand(B, device=dev, generator=g) * 0.6 + 0.4
+    top_p[::7] = 1.0
+    do_sample = torch.ones(B, dtype=torch.uint8, device=dev)
+    do_sample[::2] = 0
+    seeds = torch.arange(B, device=dev, dtype=torch.int64) * 7919 + 13
+    steps = torch.zeros(B, dtype=torch.int32, device=dev)
+    want = _torch_filtered(scores, temperature, top_k, top_p)
+    want_lp = torch.log_softmax(want, -1)
+    for step in range(4):
+        steps.fill_(step)
+        ids, lps = ops.fused_sample(scores, temperature, top_k, top_p, do_sample, seeds, steps)
+        torch.cuda.synchronize()
+        # support check by value: with repeated values (bf16) the sort-based filter cuts through a group of
+        # equal scores in sort order while the kernel keeps the whole group, so compare against the smallest
+        # kept value instead of the exact index set
+        x = scores.float() / temperature.view(-1, 1)
+        picked = x.gather(1, ids.view(-1, 1)).view(-1)
+        floor = torch.where(torch.isfinite(want), want, torch.full_like(want, float("inf"))).min(-1).values
+        assert (picked >= floor - 1e-6).all(), "a sampled token lies outside the top-k / top-p support"
+        ref_lp = torch.log_softmax(torch.where(x >= floor.view(-1, 1) - 1e-6, x, torch.full_like(x, -float("inf"))), -1)
+        ref_lp = ref_lp.gather(1, ids.view(-1, 1)).view(-1)
+        assert (lps - ref_lp).abs().max().item() < 3e-3
+        greedy = do_sample == 0
+        assert torch.equal(x.gather(1, ids.view(-1, 1)).view(-1)[greedy], x.max(-1).values[greedy])
+    again, _ = ops.fused_sample(scores, temperature, top_k, top_p, do_sample, seeds, steps)
+    assert torch.equal(again, ids), "same seed and step must reproduce the draw"
+    steps.fill_(99)
+    other, _ = ops.fused_sample(scores, temperature, top_k, top_p, do_sample, seeds, steps)
+    assert (other != ids)[do_sample == 1].any()
+
+
+def test_draws_follow_the_distribution():
+    from tgi_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    V, N = 40, 40000
+    g = torch.Generator(device="cuda").manual_seed(1)
+    logits = torch.randn(V, device=dev, generator=g) * 1.5
+    scores = logits.view(1, V).expand(N, V).contiguous()
+    temperature = torch.full((N,), 0.8, device=dev)
+    top_k = torch.full((N,), 12, dtype=torch.int32, device=dev)
+    top_p = torch.full((N,), 0.9, device=dev)
+    do_sample = torch.ones(N, dtype=torch.uint8, device=dev)
+    seeds = torch.full((N,), 1234, dtype=torch.int64, device=dev)
+    steps = torch.arange(N, dtype=torch.int32, device=dev)      # one request, N consecutive steps
+    ids, _ = ops.fused_sample(scores, temperature, top_k, top_p, do_sample, seeds, steps)
+    probs = torch.softmax(_torch_filtered(scores[:1], temperature[:1], top_k[:1], top_p[:1]), -1).view(-1)
+    freq = torch.bincount(ids, minlength=V).float() / N
+    assert (freq[probs == 0] == 0).all()
+    # every kept token within 4 standard errors (plus a small absolute slack) of its probability
+    se = torch.sqrt(probs * (1 - probs) / N)
+    assert ((freq - probs).abs() <= 4 * se + 2e-3).all(), (freq, probs)
+
+
+def test_chooser_uses_the_kernel_and_matches_filters():
+    from tgi_b200.proto import generate_v3 as pb
+    from tgi_b200.utils.tokens import NextTokenChooser
+
+    dev = torch.device("cuda", 0)
+    params = []
+    for i in range(6):
+        p = pb.NextTokenChooserParameters(temperature=(0.7 + 0.1 * i) if i else 1.0, top_k=20 if i % 2 else 0, top_p=0.9 if i % 3 else 1.0,
+                                          typical_p=1.0, do_sample=i != 0, seed=100 + i, repetition_penalty=1.2 if i == 2 else 1.0,
+                                          frequency_penalty=0.0, watermark=False)
+        params.append(p)
+    chooser = NextTokenChooser.from_pb(params, dev, None)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    scores = (torch.randn(6, 5000, device=dev, generator=g) * 2).to(torch.bfloat16)
+    history = torch.randint(0, 5000, (6, 9), device=dev, generator=g)
+    ids, lps, all_lp, accepted, spec = chooser(history, scores, 0, None, None, need_logprobs=False)
+    assert all_lp is None and spec is None and accepted.tolist() == [1] * 6
+    warped = chooser.warp(history, scores.float().clone())
+    assert torch.isfinite(warped.gather(1, ids.view(-1, 1))).all()
+    assert warped[0, ids[0]].item() == warped[0].max().item()      # bf16 scores repeat: compare the value, not the index
+    ref = torch.log_softmax(warped, -1).gather(1, ids.view(-1, 1)).view(-1)
+    assert (lps - ref).abs().max().item() < 8e-2      # equal bf16 scores at the top-p boundary: the kernel keeps the whole group
+    assert chooser.steps == [0, 1, 1, 1, 1, 1]

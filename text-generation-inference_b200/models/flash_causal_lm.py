@@ -524,7 +524,7 @@ class FlashCausalLM(Model):
                 else:
                     spec_scores = None
                 next_ids, next_lp, all_logprobs, accepted, spec_next = chooser(
-                    history, sel, batch.speculate, speculated, spec_scores)
+                    history, sel, batch.speculate, speculated, spec_scores, need_logprobs=want_top)
                 next_ids_l = next_ids.tolist()
                 next_lp_l = next_lp.tolist()
                 accepted_l = accepted.tolist()

@@ -135,6 +135,15 @@ def argmax_logprob(logits):
     return ref.argmax_logprob(logits)
 
 
+def has_fused_sample(scores) -> bool:
+    return use_native(scores)
+
+
+def fused_sample(scores, temperature=None, top_k=None, top_p=None, do_sample=None, seeds=None, steps=None):
+    """One-kernel temperature / top-k / top-p / sampling on CUDA tensors (see ``ops.cuda.fused_sample``)."""
+    return native().fused_sample(scores, temperature, top_k, top_p, do_sample, seeds, steps)
+
+
 def moe_topk_softmax(router_logits, top_k, renormalize=True):
     return ref.moe_topk_softmax(router_logits, top_k, renormalize)
 

@@ -384,6 +384,156 @@ argmax_logprob_kernel(const T* __restrict__ logits, long long* __restrict__ ids,
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Fused sampler: temperature, top-k, top-p, Gumbel-max sampling (or argmax) and the log-probability of
+// the chosen token, one CTA per row.  Replaces the reference's chain of logits warpers and its
+// `probs / Exp(1)` multinomial with a CPU generator per request (utils/tokens.py:346-399,
+// utils/logits_process.py:25-358): no sort, no [B, V] probability matrix, no host round trip.
+//
+//   x_j = logit_j / T
+//   top-k: keep x_j >= (k-th largest x);  top-p: keep x_j unless the mass of strictly larger entries
+//   already reaches p (same sets as the sort-based torch filters).  Both thresholds are found by
+//   bisection on the order-preserving integer image of the float, which is exact and needs no sort.
+//   sample: argmax_j (x_j + g_j) over the kept set, g_j = -log(-log u_j), u_j from Philox4x32-10
+//   keyed by the request's seed with counter (j, step): reproducible for a given seed.
+//   logprob = x_c - logsumexp over the kept set.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t order_bits(float x) {
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ uint4 philox4x32(uint32_t c0, uint32_t c1, uint32_t k0, uint32_t k1) {
+  uint32_t c[4] = {c0, c1, 0u, 0u};
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+    const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
+    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return make_uint4(c[0], c[1], c[2], c[3]);
+}
+
+__device__ __forceinline__ float gumbel_noise(uint32_t j, uint32_t step, uint64_t seed) {
+  const uint4 r = philox4x32(j >> 2, step, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+  const uint32_t w = (j & 3) == 0 ? r.x : (j & 3) == 1 ? r.y : (j & 3) == 2 ? r.z : r.w;
+  const float u = (static_cast<float>(w >> 8) + 0.5f) * (1.0f / 16777216.0f);   // (0, 1)
+  return -__logf(-__logf(u));
+}
+
+// smallest order_bits threshold t such that  sum_{x : bits(x) > t} w(x) < limit   (w = 1 or exp(x - m))
+template <typename T, bool MASS>
+__device__ uint32_t find_threshold(const T* __restrict__ row, int V, float inv_t, float m, float limit, uint32_t floor_bits,
+                                   float* red) {
+  uint32_t lo = floor_bits, hi = order_bits(m);   // predicate false at lo - 1 (or lo is the floor), true at hi
+  // invariant: answer in [lo, hi]
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float x = static_cast<float>(row[i]) * inv_t;
+      const uint32_t b = order_bits(x);
+      if (b > mid && b >= floor_bits) acc += MASS ? __expf(x - m) : 1.f;
+    }
+    const float total = block_sum(acc, red);
+    if (total < limit) hi = mid;
+    else lo = mid + 1;
+  }
+  return lo;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+sample_kernel(const T* __restrict__ scores, long long row_stride, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const unsigned char* __restrict__ do_sample,
+              const long long* __restrict__ seeds, const int* __restrict__ steps, long long* __restrict__ ids,
+              float* __restrict__ logprob, int V) {
+  __shared__ float red[32];
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  const int b = blockIdx.x;
+  const T* row = scores + static_cast<size_t>(b) * row_stride;
+  const float temp = temperature != nullptr ? temperature[b] : 1.f;
+  const float inv_t = 1.f / (temp > 0.f ? temp : 1.f);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // ---- max ----
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, static_cast<float>(row[i]) * inv_t);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __syncthreads();
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  m = red[0];
+  for (int w = 1; w < (blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+  __syncthreads();
+  // ---- thresholds ----
+  uint32_t keep_from = 0u;                      // keep entries whose order_bits >= keep_from
+  const int k = top_k != nullptr ? top_k[b] : 0;
+  if (k > 0 && k < V) keep_from = find_threshold<T, false>(row, V, inv_t, m, static_cast<float>(k), 0u, red);
+  const float p = top_p != nullptr ? top_p[b] : 1.f;
+  if (p < 1.f) {
+    float z = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float x = static_cast<float>(row[i]) * inv_t;
+      if (order_bits(x) >= keep_from) z += __expf(x - m);
+    }
+    z = block_sum(z, red);
+    const uint32_t t = find_threshold<T, true>(row, V, inv_t, m, p * z, keep_from, red);
+    keep_from = max(keep_from, t);
+  }
+  // ---- sample over the kept set ----
+  const bool sample = do_sample != nullptr && do_sample[b] != 0;
+  const uint64_t seed = seeds != nullptr ? static_cast<uint64_t>(seeds[b]) : 0ull;
+  const uint32_t step = steps != nullptr ? static_cast<uint32_t>(steps[b]) : 0u;
+  float z = 0.f, best = -INFINITY, best_x = 0.f;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float x = static_cast<float>(row[i]) * inv_t;
+    if (order_bits(x) < keep_from || x == -INFINITY) continue;
+    z += __expf(x - m);
+    const float key = sample ? x + gumbel_noise(static_cast<uint32_t>(i), step, seed) : x;
+    if (key > best) {
+      best = key;
+      best_i = i;
+      best_x = x;
+    }
+  }
+  z = block_sum(z, red);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float k2 = __shfl_xor_sync(0xffffffffu, best, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, best_i, o);
+    const float x2 = __shfl_xor_sync(0xffffffffu, best_x, o);
+    if (k2 > best || (k2 == best && i2 < best_i)) {
+      best = k2;
+      best_i = i2;
+      best_x = x2;
+    }
+  }
+  __syncthreads();
+  if (lane == 0) {
+    red[warp] = best;
+    s_idx[warp] = best_i;
+    s_val[warp] = best_x;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w)
+      if (red[w] > best || (red[w] == best && s_idx[w] < best_i)) {
+        best = red[w];
+        best_i = s_idx[w];
+        best_x = s_val[w];
+      }
+    ids[b] = best_i == 0x7fffffff ? 0 : best_i;
+    logprob[b] = best_x - m - __logf(z);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -476,6 +626,22 @@ int tgi_argmax_logprob(const void* logits, long long* ids, float* logprob, int B
   else
     argmax_logprob_kernel<__nv_bfloat16><<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ids,
                                                                  logprob, V, row_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Fused temperature / top-k / top-p / sampling; any of temperature, top_k, top_p, do_sample, seeds, steps may be
+// null (stage off).  `is_fp32` selects the element type of `scores`.
+int tgi_sample(const void* scores, long long row_stride, int is_fp32, const float* temperature, const int* top_k,
+               const float* top_p, const unsigned char* do_sample, const long long* seeds, const int* steps,
+               long long* ids, float* logprob, int B, int V, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (V <= 0) return -10;
+  if (is_fp32)
+    sample_kernel<float><<<B, 1024, 0, stream>>>(static_cast<const float*>(scores), row_stride, temperature, top_k, top_p,
+                                                 do_sample, seeds, steps, ids, logprob, V);
+  else
+    sample_kernel<__nv_bfloat16><<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(scores), row_stride, temperature,
+                                                         top_k, top_p, do_sample, seeds, steps, ids, logprob, V);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -362,6 +362,31 @@ def argmax_logprob(logits):
     return ids, lp
 
 
+def fused_sample(scores: torch.Tensor, temperature=None, top_k=None, top_p=None, do_sample=None, seeds=None, steps=None):
+    """Temperature, top-k, top-p and sampling (Gumbel-max with a counter-based generator keyed by the
+    request's seed and step) in one kernel; returns ``(ids int64 [B], logprobs fp32 [B])``.  Any stage
+    whose tensor is ``None`` is off; rows with ``do_sample == 0`` take the argmax of the filtered scores."""
+    lib = load()
+    assert scores.dim() == 2 and scores.stride(1) == 1 and scores.dtype in (torch.float32, torch.bfloat16)
+    B, V = scores.shape
+    dev = scores.device
+    ids = torch.empty(B, dtype=torch.int64, device=dev)
+    lps = torch.empty(B, dtype=torch.float32, device=dev)
+    if B == 0:
+        return ids, lps
+
+    def as_(t, dtype):
+        return None if t is None else t.to(device=dev, dtype=dtype).contiguous()
+
+    temperature, top_p = as_(temperature, torch.float32), as_(top_p, torch.float32)
+    top_k, steps = as_(top_k, torch.int32), as_(steps, torch.int32)
+    do_sample, seeds = as_(do_sample, torch.uint8), as_(seeds, torch.int64)
+    _check(lib.tgi_sample(_ptr(scores), c_ll(scores.stride(0)), c_int(1 if scores.dtype == torch.float32 else 0),
+                          _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(do_sample), _ptr(seeds), _ptr(steps),
+                          _ptr(ids), _ptr(lps), c_int(B), c_int(V), _stream()), "sample")
+    return ids, lps
+
+
 def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu"):
     """Grouped expert MLP: tokens are sorted by expert and each expert's slab runs through the tcgen05 GEMM."""
     T, H = x.shape

@@ -225,14 +225,25 @@ class NextTokenChooser:
         speculate: int = 0,
         speculated_ids: Optional[torch.Tensor] = None,
         speculative_scores: Optional[torch.Tensor] = None,
+        need_logprobs: bool = True,
     ):
         """Returns ``(next_ids, next_logprobs, all_logprobs, accepted_ids, speculative_ids)``.
+
+        ``need_logprobs=False`` tells the chooser that the caller will not read ``all_logprobs`` (no
+        top-n tokens requested); on CUDA tensors the warpers and the sampling then run as one kernel
+        and ``all_logprobs`` is ``None``.
 
         ``scores`` has ``B*(S)`` rows, ``S = 1 + speculated_ids.shape[1]``; ``input_ids[B, L]`` is the
         token history used by the penalties (padding rows with id 0 as the reference does).
         """
         S = 1 if speculated_ids is None else speculated_ids.shape[1] + 1
         B = scores.shape[0] // S
+        if (S == 1 and not need_logprobs and speculate == 0 and speculative_scores is None and not self.any_typical
+                and scores.is_cuda):
+            from .. import ops
+
+            if ops.has_fused_sample(scores):
+                return self._fused(input_ids, scores)
         scores = scores.float().view(B, S, -1)
         next_ids = torch.zeros(B, S, dtype=torch.long, device=scores.device)
         for j in range(S):
@@ -273,6 +284,36 @@ class NextTokenChooser:
             else:
                 speculative_ids = create_n_gram_speculation(input_ids, next_ids, accepted_ids, speculate)
         return next_ids, next_logprobs, all_logprobs, accepted_ids, speculative_ids
+
+    def _fused(self, input_ids: torch.Tensor, scores: torch.Tensor):
+        """CUDA fast path: stages that need the token history or an automaton run in torch on a float
+        copy (only when active), then temperature / top-k / top-p / sampling / log-probability are one
+        kernel launch for the whole batch (``ops.fused_sample``)."""
+        from .. import ops
+
+        if self.watermarks or self.any_rep or self.any_freq or self.grammar is not None:
+            scores = scores.float().clone()
+            for i, wm in self.watermarks.items():
+                scores[i : i + 1] = wm(input_ids[i : i + 1], scores[i : i + 1])
+            if self.any_rep:
+                scores = apply_repetition_penalty(scores, input_ids, self.repetition_penalty)
+            if self.any_freq:
+                scores = apply_frequency_penalty(scores, input_ids, self.frequency_penalty)
+            if self.grammar is not None:
+                scores = self.grammar.mask(scores, self.fsm_grammar_states)
+        elif scores.dtype not in (torch.float32, torch.bfloat16):
+            scores = scores.float()
+        dev = scores.device
+        seeds = steps = do_sample = None
+        if self.any_sample:
+            do_sample = self.do_sample.to(torch.uint8)
+            seeds = torch.tensor([int(s or 0) & 0x7FFFFFFFFFFFFFFF for s in self.seeds], dtype=torch.int64, device=dev)
+            steps = torch.tensor(self.steps, dtype=torch.int32, device=dev)
+            self.steps = [st + (1 if d else 0) for st, d in zip(self.steps, self.do_sample_list)]
+        next_ids, next_logprobs = ops.fused_sample(
+            scores, self.temperature if self.any_temperature else None, self.top_k if self.any_top_k else None,
+            self.top_p if self.any_top_p else None, do_sample, seeds, steps)
+        return next_ids, next_logprobs, None, torch.ones_like(next_ids), None
 
     def advance_grammar(self, next_ids: List[int]):
         if self.grammar is not None:
