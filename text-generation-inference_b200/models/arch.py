@@ -234,6 +234,8 @@ def derive_dims(cfg: ModelConfig, arch: Arch, world: int) -> ModelDims:
     heads = cfg.get("num_attention_heads", cfg.get("n_head", cfg.get("n_heads")))
     head_dim = cfg.get("head_dim", hidden // heads)
     kv = cfg.get("num_key_value_heads")
+    if kv is None and cfg.get("new_decoder_architecture") and cfg.get("num_kv_heads") is not None:
+        kv = cfg.get("num_kv_heads")     # Falcon-40B style: grouped KV heads, `multi_query` is ignored
     if kv is None:
         if cfg.get("multi_query") or (cfg.model_type in ("falcon", "RefinedWebModel", "RefinedWeb")
                                       and cfg.get("multi_query", True) and not cfg.get("new_decoder_architecture")):
@@ -258,7 +260,14 @@ def derive_dims(cfg: ModelConfig, arch: Arch, world: int) -> ModelDims:
     eps = cfg.get("rms_norm_eps", cfg.get("layer_norm_eps", cfg.get("layer_norm_epsilon", cfg.get("norm_epsilon", 1e-5))))
     act = arch.act or cfg.get("hidden_act", cfg.get("hidden_activation", cfg.get("activation_function", "gelu")))
     rope_params = cfg.get("rope_parameters") if isinstance(cfg.get("rope_parameters"), dict) else {}
-    theta = float(cfg.get("rope_theta", rope_params.get("rope_theta", cfg.get("rotary_emb_base", 10000.0))))
+    full = rope_params.get("full_attention") if isinstance(rope_params.get("full_attention"), dict) else {}
+    attn_cfg = cfg.get("attn_config") if isinstance(cfg.get("attn_config"), dict) else {}
+    theta = 10000.0
+    for cand in (cfg.get("rope_theta"), rope_params.get("rope_theta"), full.get("rope_theta"), attn_cfg.get("rope_theta"),
+                 cfg.get("rotary_emb_base")):
+        if cand is not None:
+            theta = float(cand)
+            break
     partial = cfg.get("partial_rotary_factor", cfg.get("rotary_pct", 1.0))
     rot = cfg.get("rotary_dim")
     if rot is None:

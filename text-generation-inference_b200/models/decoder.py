@@ -124,7 +124,8 @@ class Attention:
                 # fewer KV heads than ranks: shard q, replicate the owning KV head
                 self.qkv = self._load_replicated_kv(cfg, names, weights, arch.qkv_bias)
             else:
-                self.qkv = TensorParallelColumnLinear.load_multi(cfg, names, weights, arch.qkv_bias)
+                self.qkv = TensorParallelColumnLinear.load_multi(
+                    cfg, names, weights, arch.qkv_bias and weights.has_tensor(f"{names[0]}.bias"))
         else:
             name = f"{prefix}.{arch.qkv}"
             simple = (arch.qkv_layout == "blocked" and not arch.conv1d_weights
@@ -158,6 +159,8 @@ class Attention:
                 kn = kn.view(dims.total_kv_heads, D)[pg.rank() * dims.num_kv_heads:(pg.rank() + 1) * dims.num_kv_heads]
             self.q_norm, self.k_norm = qn.contiguous(), kn.contiguous()
         self.window = dims.windows[layer_idx]
+        ac = cfg.get("attn_config")
+        self.clip_qkv = float(ac.get("clip_qkv") or 0.0) if isinstance(ac, dict) else float(cfg.get("clip_qkv") or 0.0)
         self.k_scale = self.v_scale = None
         for kname, vname in ((f"{prefix}.self_attn.k_scale", f"{prefix}.self_attn.v_scale"),
                              (f"{prefix}.self_attn.kv_scale", f"{prefix}.self_attn.kv_scale")):
@@ -210,6 +213,8 @@ class Attention:
     def __call__(self, x, x_scale, meta: ForwardMeta, rotary: RotaryTable, kv, reduce: bool = True, out=None):
         d = self.dims
         qkv = self.qkv(x, x_scale)
+        if self.clip_qkv:
+            qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)     # DBRX
         if meta.adapter_data is not None:
             qkv = meta.adapter_data.apply_qkv(self.layer_idx, x, qkv)
         if self.q_norm is not None:
@@ -290,6 +295,7 @@ class SparseMoE:
         self.top_k, self.num_experts, self.act = dims.top_k, dims.num_experts, dims.act
         self.renorm = arch.moe_renormalize if cfg.get("norm_topk_prob") is None else bool(cfg.norm_topk_prob)
         self.router = FastLinear(weights.get_tensor(f"{prefix}.{arch.moe_router}.weight"))
+        self.sparsemixer_eps = float(cfg.get("router_jitter_noise", 0.01)) if cfg.model_type == "phimoe" else None
         E = dims.num_experts
         gu, dn = [], []
         from ..parallel.expert import ExpertParallel, local_expert_range, wants_expert_parallel
@@ -338,7 +344,10 @@ class SparseMoE:
             out.copy_(self(x, x_scale, reduce=False, meta=meta))
             return out
         logits = self.router(x)
-        w, idx = ops.moe_topk_softmax(logits, self.top_k, self.renorm)
+        if self.sparsemixer_eps is not None:
+            w, idx = ops.moe_sparsemixer(logits, self.sparsemixer_eps)       # Phi-3.5-MoE routing
+        else:
+            w, idx = ops.moe_topk_softmax(logits, self.top_k, self.renorm)
         if self.expert_parallel is not None:
             out = self.expert_parallel(x, w, idx)
         elif x.is_cuda and (x.shape[0] <= 512 or torch.cuda.is_current_stream_capturing()):
@@ -367,10 +376,12 @@ def _all_reduce(t, pg):
 class DecoderLayer:
     def __init__(self, arch: Arch, cfg, dims: ModelDims, prefix: str, weights, idx: int, comm):
         self.arch, self.dims = arch, dims
-        self.norm1 = Norm.load(arch, f"{prefix}.{arch.norm1}", weights, dims.eps)
-        self.norm2 = Norm.load(arch, f"{prefix}.{arch.norm2}", weights, dims.eps) if arch.norm2 else None
         if cfg.model_type in ("falcon", "RefinedWeb", "RefinedWebModel"):
+            # the new decoder architecture names its norms ln_attn / ln_mlp and has no input_layernorm
             self.norm1, self.norm2 = self._falcon_norms(arch, cfg, prefix, weights, dims)
+        else:
+            self.norm1 = Norm.load(arch, f"{prefix}.{arch.norm1}", weights, dims.eps)
+            self.norm2 = Norm.load(arch, f"{prefix}.{arch.norm2}", weights, dims.eps) if arch.norm2 else None
         self.post_attn = Norm.load(arch, f"{prefix}.{arch.post_attn_norm}", weights, dims.eps) if arch.post_attn_norm else None
         self.post_mlp = Norm.load(arch, f"{prefix}.{arch.post_mlp_norm}", weights, dims.eps) if arch.post_mlp_norm else None
         self.attn = Attention(arch, cfg, dims, prefix, weights, idx, comm)
@@ -513,6 +524,15 @@ class CausalDecoder:
         self.max_positions = int(max_positions or dims.max_positions)
         self.rotary = RotaryTable.from_config(cfg, dims.rot_dim, dims.rope_theta, self.max_positions,
                                               a.rope_neox).to(self.device)
+        # Gemma-3: sliding-window layers rotate with their own (unscaled) base frequency
+        self.rotary_local = None
+        local_theta = cfg.get("rope_local_base_freq")
+        rp = cfg.get("rope_parameters")
+        if local_theta is None and isinstance(rp, dict) and isinstance(rp.get("sliding_attention"), dict):
+            local_theta = rp["sliding_attention"].get("rope_theta")
+        if local_theta and cfg.model_type in ("gemma3", "gemma3_text"):
+            self.rotary_local = RotaryTable.from_config(None, dims.rot_dim, float(local_theta), self.max_positions,
+                                                        a.rope_neox).to(self.device)
         if a.alibi:
             slopes = alibi_slopes(dims.total_heads)[pg.rank() * dims.num_heads:(pg.rank() + 1) * dims.num_heads]
             for l in self.layers:
@@ -529,6 +549,11 @@ class CausalDecoder:
         if self.embed_norm is not None:
             h, _ = self.embed_norm(h, None)
         return h
+
+    def _rotary_for(self, layer_idx: int) -> RotaryTable:
+        if self.rotary_local is not None and self.dims.windows[layer_idx] > 0:
+            return self.rotary_local
+        return self.rotary
 
     def _fused_tp_ok(self, meta: ForwardMeta) -> bool:
         comm = self.comm
@@ -553,7 +578,7 @@ class CausalDecoder:
         last = len(self.layers) - 1
         for i, layer in enumerate(self.layers):
             nxt = self.layers[i + 1] if i < last else None
-            x = layer.fused_tp(x, meta, self.rotary, kv_cache[i], nxt.norm1 if nxt else self.final_norm,
+            x = layer.fused_tp(x, meta, self._rotary_for(i), kv_cache[i], nxt.norm1 if nxt else self.final_norm,
                                nxt.attn_in_quant if nxt else False, comm)
         return x
 
@@ -563,7 +588,7 @@ class CausalDecoder:
         h = meta.inputs_embeds if meta.inputs_embeds is not None else self.embed_tokens(meta.input_ids, meta.positions)
         residual = None
         for i, layer in enumerate(self.layers):
-            h, residual = layer(h, residual, meta, self.rotary, kv_cache[i])
+            h, residual = layer(h, residual, meta, self._rotary_for(i), kv_cache[i])
         h, _ = self.final_norm(h, residual)
         return h
 

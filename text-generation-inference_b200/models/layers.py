@@ -224,11 +224,14 @@ class TensorParallelHead:
     def load(cls, config, prefix: str, weights):
         pg = weights.process_group
         total = weights.get_shape(f"{prefix}.weight")[0]
+        has_bias = weights.has_tensor(f"{prefix}.bias")      # GPT-J, Phi: the head carries a bias
         if total % pg.size() == 0 and pg.size() > 1:
             w = weights.get_sharded(f"{prefix}.weight", dim=0)
-            return cls(FastLinear(w), pg, True, pg.rank() * (total // pg.size()))
+            b = weights.get_sharded(f"{prefix}.bias", dim=0) if has_bias else None
+            return cls(FastLinear(w, b), pg, True, pg.rank() * (total // pg.size()))
         # Vocabulary not divisible: every rank keeps the full head (as the reference does).
-        return cls(FastLinear(weights.get_tensor(f"{prefix}.weight")), pg, False, 0)
+        b = weights.get_tensor(f"{prefix}.bias") if has_bias else None
+        return cls(FastLinear(weights.get_tensor(f"{prefix}.weight"), b), pg, False, 0)
 
     def local_logits(self, x: torch.Tensor):
         return self.linear(x), self.vocab_start

@@ -148,6 +148,10 @@ def moe_topk_softmax(router_logits, top_k, renormalize=True):
     return ref.moe_topk_softmax(router_logits, top_k, renormalize)
 
 
+def moe_sparsemixer(router_logits, jitter_eps=0.01):
+    return ref.moe_sparsemixer(router_logits, jitter_eps)
+
+
 def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu"):
     if use_native(x):
         return native().moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act)

@@ -284,6 +284,22 @@ def moe_topk_softmax(router_logits: torch.Tensor, top_k: int, renormalize: bool 
     return w, idx
 
 
+def moe_sparsemixer(router_logits: torch.Tensor, jitter_eps: float = 0.01) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Top-2 routing of Phi-3.5-MoE ("sparsemixer", inference form): each of the two picks is the arg-max of
+    the remaining logits, and its weight is the softmax over the logits that lie within a relative
+    band ``2 * jitter_eps`` of that maximum."""
+    s = router_logits.float()
+    neg = float("-inf")
+    m1, i1 = s.max(-1, keepdim=True)
+    mask1 = ((m1 - s) / s.abs().clamp(min=m1)) > 2 * jitter_eps
+    g1 = torch.softmax(s.masked_fill(mask1, neg), -1).gather(-1, i1)
+    s2 = s.scatter(-1, i1, neg)
+    m2, i2 = s2.max(-1, keepdim=True)
+    mask2 = ((m2 - s) / s.abs().clamp(min=m2)) > 2 * jitter_eps
+    g2 = torch.softmax(s2.masked_fill(mask2, neg), -1).gather(-1, i2)
+    return torch.cat([g1, g2], -1), torch.cat([i1, i2], -1)
+
+
 def moe_experts(
     x: torch.Tensor,
     w_gate_up: torch.Tensor,

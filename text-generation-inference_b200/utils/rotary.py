@@ -90,6 +90,8 @@ class RotaryTable:
             return cls(torch.zeros(max_positions, 0), 0, neox)
         inv_freq = _base_inv_freq(base, dim)
         rs = getattr(config, "rope_scaling", None) or getattr(config, "rope_parameters", None)
+        if isinstance(rs, dict) and isinstance(rs.get("full_attention"), dict):
+            rs = rs["full_attention"]      # per-layer-type parameters (Gemma-3): the global layers' entry
         if isinstance(rs, dict) and rs.get("rope_type", rs.get("type")) in (None, "default") and "factor" not in rs:
             rs = None
         env_type = os.environ.get("ROPE_SCALING")
