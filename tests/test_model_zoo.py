@@ -73,12 +73,26 @@ def _cfg(name):
     if name == "falcon_new":
         return T.FalconConfig(vocab_size=320, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_kv_heads=2,
                               new_decoder_architecture=True, parallel_attn=True, bias=False, alibi=False)
+    if name == "deepseek_v3":
+        return T.DeepseekV3Config(vocab_size=320, hidden_size=64, intermediate_size=128, moe_intermediate_size=48,
+                                  num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1,
+                                  n_routed_experts=8, routed_scaling_factor=2.5, kv_lora_rank=32, q_lora_rank=24,
+                                  qk_rope_head_dim=16, v_head_dim=24, qk_nope_head_dim=32, n_group=2, topk_group=1,
+                                  num_experts_per_tok=2, first_k_dense_replace=1, norm_topk_prob=True,
+                                  max_position_embeddings=256)
+    if name == "deepseek_v2":
+        return T.DeepseekV2Config(vocab_size=320, hidden_size=64, intermediate_size=128, moe_intermediate_size=48,
+                                  num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, n_shared_experts=2,
+                                  n_routed_experts=8, routed_scaling_factor=1.0, kv_lora_rank=32, q_lora_rank=None,
+                                  qk_rope_head_dim=16, v_head_dim=24, qk_nope_head_dim=32, n_group=2, topk_group=1,
+                                  num_experts_per_tok=2, first_k_dense_replace=1, norm_topk_prob=False,
+                                  topk_method="greedy", max_position_embeddings=256)   # the grouped V2 path of this transformers version raises
     raise KeyError(name)
 
 
 NAMES = ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "phi3", "phi", "gpt2", "gptj", "gpt_neox", "falcon",
          "starcoder2", "cohere", "granite", "mixtral", "qwen2_moe", "qwen3_moe", "gpt_bigcode", "phimoe", "gemma3_text",
-         "falcon_new"]
+         "falcon_new", "deepseek_v2", "deepseek_v3"]
 # DBRX is left out: the expert matmul of this transformers version multiplies by the untransposed weight
 # (it only runs at all when ffn_hidden_size == d_model), so it is no oracle; the engine follows the layout of the
 # released checkpoints.

@@ -109,6 +109,7 @@ class Arch:
     moe_down: str = "w2"
     moe_fused: bool = False                  # dbrx: experts stored stacked
     moe_shared: Optional[str] = None         # shared expert MLP prefix (qwen2_moe, deepseek)
+    mla: bool = False                        # DeepSeek multi-head latent attention (models/deepseek.py)
     moe_shared_gate: Optional[str] = None
     moe_renormalize: bool = True
 
@@ -189,6 +190,9 @@ ARCHS: Dict[str, Arch] = {
                  moe_gate="w1", moe_up="v1", moe_down="w2"),
 }
 ARCHS["RefinedWeb"] = ARCHS["RefinedWebModel"] = ARCHS["falcon"]
+ARCHS["deepseek_v2"] = ARCHS["deepseek_v3"] = replace(
+    _LLAMA, rope_neox=False, mla=True, moe=True, moe_router="mlp.gate", moe_expert="mlp.experts.{e}",
+    moe_gate="gate_proj", moe_up="up_proj", moe_down="down_proj", moe_shared="mlp.shared_experts")
 ARCHS["gemma3"] = ARCHS["gemma3_text"]
 ARCHS["phi-msft"] = ARCHS["phi"]
 
@@ -234,6 +238,9 @@ def derive_dims(cfg: ModelConfig, arch: Arch, world: int) -> ModelDims:
     heads = cfg.get("num_attention_heads", cfg.get("n_head", cfg.get("n_heads")))
     head_dim = cfg.get("head_dim", hidden // heads)
     kv = cfg.get("num_key_value_heads")
+    if arch.mla:
+        # latent attention is expanded to ordinary heads of a padded dimension (models/deepseek.py)
+        head_dim, kv = 256, heads
     if kv is None and cfg.get("new_decoder_architecture") and cfg.get("num_kv_heads") is not None:
         kv = cfg.get("num_kv_heads")     # Falcon-40B style: grouped KV heads, `multi_query` is ignored
     if kv is None:
@@ -270,6 +277,8 @@ def derive_dims(cfg: ModelConfig, arch: Arch, world: int) -> ModelDims:
             break
     partial = cfg.get("partial_rotary_factor", cfg.get("rotary_pct", 1.0))
     rot = cfg.get("rotary_dim")
+    if arch.mla:
+        rot = int(cfg.qk_rope_head_dim)
     if rot is None:
         rot = int(head_dim * partial)
     rot_dim = rot if arch.rope else 0
@@ -292,7 +301,7 @@ def derive_dims(cfg: ModelConfig, arch: Arch, world: int) -> ModelDims:
             windows = [window if i >= cfg.max_window_layers else -1 for i in range(layers)]
         else:
             windows = [window] * layers
-    ne = cfg.get("num_local_experts", cfg.get("num_experts", 0)) or 0
+    ne = cfg.get("num_local_experts", cfg.get("num_experts", cfg.get("n_routed_experts", 0))) or 0
     tk = cfg.get("num_experts_per_tok", cfg.get("moe_top_k", 0)) or 0
     if isinstance(cfg.get("ffn_config"), dict):
         ne = cfg.ffn_config.get("moe_num_experts", ne)

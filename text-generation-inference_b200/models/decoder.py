@@ -296,6 +296,11 @@ class SparseMoE:
         self.renorm = arch.moe_renormalize if cfg.get("norm_topk_prob") is None else bool(cfg.norm_topk_prob)
         self.router = FastLinear(weights.get_tensor(f"{prefix}.{arch.moe_router}.weight"))
         self.sparsemixer_eps = float(cfg.get("router_jitter_noise", 0.01)) if cfg.model_type == "phimoe" else None
+        self.deepseek_router = None
+        if arch.mla:
+            from .deepseek import DeepseekRouter
+
+            self.deepseek_router = DeepseekRouter(cfg, weights, f"{prefix}.mlp")
         E = dims.num_experts
         gu, dn = [], []
         from ..parallel.expert import ExpertParallel, local_expert_range, wants_expert_parallel
@@ -344,7 +349,9 @@ class SparseMoE:
             out.copy_(self(x, x_scale, reduce=False, meta=meta))
             return out
         logits = self.router(x)
-        if self.sparsemixer_eps is not None:
+        if self.deepseek_router is not None:
+            w, idx = self.deepseek_router(logits)
+        elif self.sparsemixer_eps is not None:
             w, idx = ops.moe_sparsemixer(logits, self.sparsemixer_eps)       # Phi-3.5-MoE routing
         else:
             w, idx = ops.moe_topk_softmax(logits, self.top_k, self.renorm)
@@ -384,14 +391,20 @@ class DecoderLayer:
             self.norm2 = Norm.load(arch, f"{prefix}.{arch.norm2}", weights, dims.eps) if arch.norm2 else None
         self.post_attn = Norm.load(arch, f"{prefix}.{arch.post_attn_norm}", weights, dims.eps) if arch.post_attn_norm else None
         self.post_mlp = Norm.load(arch, f"{prefix}.{arch.post_mlp_norm}", weights, dims.eps) if arch.post_mlp_norm else None
-        self.attn = Attention(arch, cfg, dims, prefix, weights, idx, comm)
-        is_moe = arch.moe
+        if arch.mla:
+            from .deepseek import MLAAttention, is_moe_layer
+
+            self.attn = MLAAttention(arch, cfg, dims, prefix, weights, idx, comm)
+            is_moe = is_moe_layer(cfg, idx)      # the first layers of DeepSeek models are dense
+        else:
+            self.attn = Attention(arch, cfg, dims, prefix, weights, idx, comm)
+            is_moe = arch.moe
         if is_moe and cfg.get("mlp_only_layers") and idx in cfg.mlp_only_layers:
             is_moe = False
         self.mlp = (SparseMoE(arch, cfg, dims, prefix, weights, comm) if is_moe
                     else DenseMLP(arch, cfg, dims, prefix, weights, comm, idx))
         self.pg, self.comm = weights.process_group, comm
-        qlin = self.attn.qkv.linear
+        qlin = getattr(getattr(self.attn, "qkv", None), "linear", None)
         self.attn_in_quant = isinstance(qlin, Fp8Linear) and qlin.wants_quantized_input and self.norm1.can_quant
         glin = getattr(getattr(self.mlp, "gate_up", None), "linear", None)
         self.mlp_in_quant = (isinstance(glin, Fp8Linear) and glin.wants_quantized_input
