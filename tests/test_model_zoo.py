@@ -122,3 +122,36 @@ def test_prefill_logits_match_transformers(tmp_path, name):
     got = model.forward(meta).float()
     err = (got - want).abs().max().item()
     assert err < 2e-3 * max(1.0, want.abs().max().item()), f"{name}: logits differ by {err}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["llama", "gemma2", "qwen3", "gpt2", "falcon", "phi", "mixtral", "deepseek_v3", "starcoder2"])
+def test_prefill_logits_on_gpu_kernels(tmp_path, name):
+    """The same comparison through the sm_100a kernels (bf16 weights): head dims 16..256, softcap, sliding
+    window, partial and interleaved rotary, q/k norms, learned positions, MoE, latent attention."""
+    torch.manual_seed(0)
+    cfg = _cfg(name)
+    hf = transformers.AutoModelForCausalLM.from_config(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.copy_(torch.randn_like(p) * 0.1 + (1.0 if "norm" in n or "ln" in n else 0.0))
+            p.copy_(p.to(torch.bfloat16).float())           # both sides see bf16-representable weights
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    ids = torch.tensor([[5, 17, 100, 42, 7, 9, 250, 31, 64, 3, 77, 12, 200, 150, 99, 21, 8, 44]])
+    with torch.no_grad():
+        want = hf(ids).logits[0].float()
+    dev = torch.device("cuda", 0)
+    model = get_model(str(tmp_path), dtype="bfloat16", device=dev)
+    model.init_kv_cache(4)
+    T = ids.shape[1]
+    i32 = dict(dtype=torch.int32, device=dev)
+    meta = ForwardMeta(input_ids=ids[0].to(**i32), positions=torch.arange(T, **i32), slots=torch.arange(16, 16 + T, **i32),
+                       block_tables=torch.tensor([[1, 2]], **i32), cu_seqlens_q=torch.tensor([0, T], **i32),
+                       kv_lens=torch.tensor([T], **i32), max_q=T, max_kv=T)
+    got = model.forward(meta).float().cpu()
+    from tgi_b200.ops import cuda as K
+
+    assert K.check_status(dev) == 0
+    err = (got - want).abs().max().item()
+    assert err < 0.06 * max(1.0, want.abs().max().item()), f"{name}: logits differ by {err}"

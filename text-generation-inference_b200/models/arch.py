@@ -230,6 +230,7 @@ class ModelDims:
     top_k: int = 0
     total_heads: int = 0
     total_kv_heads: int = 0
+    attn_head_dim: int = 0      # head dimension seen by the attention kernels and the KV cache: head_dim padded to 64/128/256
 
 
 def derive_dims(cfg: ModelConfig, arch: Arch, world: int) -> ModelDims:
@@ -308,7 +309,11 @@ def derive_dims(cfg: ModelConfig, arch: Arch, world: int) -> ModelDims:
         tk = cfg.ffn_config.get("moe_top_k", tk)
     if arch.moe and cfg.get("moe_intermediate_size"):
         inter = cfg.moe_intermediate_size
+    attn_dim = next((d for d in (64, 128, 256) if d >= head_dim), None)
+    if attn_dim is None:
+        raise ValueError(f"head dimension {head_dim} is larger than the attention kernels support (256)")
     return ModelDims(
+        attn_head_dim=attn_dim,
         hidden=hidden, num_layers=layers, num_heads=heads // world, num_kv_heads=kv_local, head_dim=head_dim,
         intermediate=inter, vocab=cfg.get("vocab_size"), eps=float(eps), rope_theta=theta, rot_dim=rot_dim,
         max_positions=max_pos, act=act, softmax_scale=scale, windows=windows,

@@ -220,15 +220,24 @@ class Attention:
         if self.q_norm is not None:
             qkv = self._qk_norm(qkv)
         k_cache, v_cache = kv
+        D = d.head_dim
+        Dp = d.attn_head_dim or D
+        if Dp != D:
+            # head dimensions the attention kernels have no instance for (80, 96, 160, ...) run zero-padded
+            # to the next one; the rotary part stays at the front and the scale is that of the true dimension
+            T_ = qkv.shape[0]
+            qkv = torch.nn.functional.pad(qkv.view(T_, d.num_heads + 2 * d.num_kv_heads, D), (0, Dp - D)).view(T_, -1)
         q = ops.rope_and_cache(qkv, meta.positions, rotary.cos_sin, meta.slots, k_cache, v_cache,
-                               d.num_heads, d.num_kv_heads, d.head_dim, rotary.rot_dim, rotary.neox,
+                               d.num_heads, d.num_kv_heads, Dp, rotary.rot_dim, rotary.neox,
                                self.k_scale, self.v_scale)
         attn = ops.paged_attention(q, k_cache, v_cache, meta.block_tables, meta.cu_seqlens_q, meta.kv_lens,
                                    d.softmax_scale, self.window, d.attn_softcap,
                                    self.k_scale if k_cache.dtype == torch.float8_e4m3fn else None,
                                    self.v_scale if v_cache.dtype == torch.float8_e4m3fn else None,
                                    meta.max_q, meta.max_kv)
-        attn = attn.reshape(attn.shape[0], d.num_heads * d.head_dim)
+        if Dp != D:
+            attn = attn.view(attn.shape[0], d.num_heads, Dp)[:, :, :D]
+        attn = attn.reshape(attn.shape[0], d.num_heads * D)
         out = self.o(attn, reduce=reduce, out=out)
         if meta.adapter_data is not None:
             out = meta.adapter_data.apply_row(self.layer_idx, "o_proj", attn, out)

@@ -286,7 +286,7 @@ class FlashCausalLM(Model):
     def kv_bytes_per_block(self) -> int:
         d = self.dims
         item = torch.empty((), dtype=self.kv_cache_dtype).element_size()
-        return 2 * d.num_layers * BLOCK_SIZE * d.num_kv_heads * d.head_dim * item
+        return 2 * d.num_layers * BLOCK_SIZE * d.num_kv_heads * (d.attn_head_dim or d.head_dim) * item
 
     def init_kv_cache(self, num_blocks: int):
         d = self.dims
@@ -295,8 +295,8 @@ class FlashCausalLM(Model):
             torch.cuda.empty_cache()
         self.num_blocks = int(num_blocks)
         for _ in range(d.num_layers):
-            k = torch.zeros(num_blocks, BLOCK_SIZE, d.num_kv_heads, d.head_dim, dtype=self.kv_cache_dtype,
-                            device=self.device)
+            k = torch.zeros(num_blocks, BLOCK_SIZE, d.num_kv_heads, d.attn_head_dim or d.head_dim,
+                            dtype=self.kv_cache_dtype, device=self.device)
             v = torch.zeros_like(k)
             self.kv_cache.append((k, v))
 
