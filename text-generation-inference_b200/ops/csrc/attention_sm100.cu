@@ -6,13 +6,22 @@
 // (layers/attention/cuda.py:244-296) and flashinfer `BatchDecodeWithPagedKVCache` /
 // `paged_attention_v1/v2` (layers/attention/cuda.py:73-185).
 //
-// Structure: flash-attention style online softmax.  A CTA of 4 warps owns 64 query rows of one
-// head (prefill) or the <=16 query heads that share one KV head (decode, GQA-packed so each KV
-// byte is read once); K/V tiles of 64 tokens are gathered page by page with cp.async into a
-// double-buffered, XOR-swizzled shared-memory tile and multiplied on the tensor cores with
-// m16n8k16 fragments (bf16 inputs for bf16 pages; e4m3 pages are widened to fp16 in shared memory,
-// which is exact).  Decode splits the KV range over CTAs and a second kernel merges the partial
-// (max, sum, output) triples.
+// Structure: flash-attention style online softmax on mma.sync m16n8k16 fragments.
+//
+//   prefill_kernel      a CTA of 4 warps owns 64 query rows of one head; K/V tiles of 64 tokens are gathered
+//                       page by page with cp.async into a double-buffered, XOR-swizzled shared-memory tile
+//                       (e4m3 pages are widened to fp16 in shared memory, which is exact).
+//   decode_kernel_v2    GQA-packed: the query heads that share one KV head form the 16 MMA rows of a warp, so
+//                       each KV byte is read once.  Every warp runs its own 2-stage cp.async ring over chunks
+//                       of 16 or 32 tokens of its slice of the KV range (no CTA-wide barrier in the loop).
+//                       e4m3 K is fed to the MMA directly: the Q fragments are loaded with a k-permutation that
+//                       matches the byte order of a 32-bit K word, and `cvt.rn.f16x2.e4m3x2` widens in
+//                       registers; V is widened to fp16 in shared memory for ldmatrix.trans.
+//   decode_merge_kernel combines the (max, sum, output) partials of the KV splits.
+//
+// The tensor-core path here is the legacy mma.sync one: a tcgen05 / TMEM formulation of both kernels is
+// the open performance item of this file (decode is issue-bound at 0.39 of the HBM roofline, prefill reaches
+// about 100 TFLOP/s).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>

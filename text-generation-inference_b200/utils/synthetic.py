@@ -2,7 +2,7 @@
 
 ``write_llama_checkpoint`` writes an HF-layout directory (``config.json`` + ``model.safetensors``)
 with weights ``N(0, std)`` from a seed and norm weights 1.0 — small models for CPU tests.
-``random_weights_on_device`` fills an *in-memory* checkpoint layer by layer directly on the GPU for
+``SyntheticWeights`` generates an *in-memory* checkpoint tensor by tensor directly on the GPU for
 benchmark-size models that would take too long to write to disk; it returns a ``Weights``-like
 object the decoder loads from (same names, same sharding entry points).
 """
