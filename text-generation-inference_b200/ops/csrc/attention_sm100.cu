@@ -28,6 +28,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch.cuh"
+
 namespace {
 
 constexpr int kTile = 64;        // KV tokens per tile
@@ -265,6 +267,8 @@ struct Smem {
 template <int D, bool FP8>
 __global__ void __launch_bounds__(128)
 prefill_kernel(Params p) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   extern __shared__ __align__(128) uint8_t smem[];
   using S = Smem<D, FP8>;
   uint16_t* sQ = reinterpret_cast<uint16_t*>(smem);
@@ -496,6 +500,8 @@ __device__ __forceinline__ void warp_widen_chunk(const uint8_t* raw, __half* dst
 template <int D, bool FP8>
 __global__ void __launch_bounds__(128)
 decode_kernel_v2(Params p) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   extern __shared__ __align__(128) uint8_t smem[];
   using S = DecodeSmem<D, FP8>;
   constexpr int CT = S::CT;
@@ -657,6 +663,8 @@ decode_kernel_v2(Params p) {
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ cu_seqlens_q, __nv_bfloat16* __restrict__ out, int Hq,
                                     int D, int nsplit) {
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y;
   if (cu_seqlens_q[b + 1] == cu_seqlens_q[b]) return;
   const size_t base = (static_cast<size_t>(b) * Hq + h) * nsplit;
@@ -691,7 +699,7 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
       set = true;
     }
     dim3 grid((max_q + kTile - 1) / kTile, p.Hq, B);
-    k<<<grid, 128, smem, stream>>>(p);
+    tgi::launch(k, dim3(grid), dim3(128), smem, stream, p);
   } else {
     auto k = decode_kernel_v2<D, FP8>;
     constexpr int dsmem = DecodeSmem<D, FP8>::kBytes;
@@ -702,10 +710,10 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
     }
     const int G = p.Hq / p.Hkv;
     dim3 grid(B, p.Hkv * ((G + 15) / 16), p.nsplit);
-    k<<<grid, 128, dsmem, stream>>>(p);
+    tgi::launch(k, dim3(grid), dim3(128), dsmem, stream, p);
     if (p.nsplit > 1) {
       dim3 g2(B, p.Hq);
-      decode_merge_kernel<<<g2, D < 128 ? D : 128, 0, stream>>>(p.part_o, p.part_ml, p.cu_seqlens_q, p.out, p.Hq, D,
+      tgi::launch(decode_merge_kernel, dim3(g2), dim3(D < 128 ? D : 128), 0, stream, p.part_o, p.part_ml, p.cu_seqlens_q, p.out, p.Hq, D,
                                                                 p.nsplit);
     }
   }

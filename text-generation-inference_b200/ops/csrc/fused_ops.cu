@@ -18,6 +18,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch.cuh"
+
 namespace {
 
 constexpr float kFp8Max = 448.f;
@@ -94,6 +96,8 @@ norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
             const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ bias,
             __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ res_out, uint8_t* __restrict__ q_out,
             float* __restrict__ scale_t, int scale_pitch, int H, float eps, float w_offset) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   __shared__ float red[32];
   const int row = blockIdx.x;
   const size_t base = static_cast<size_t>(row) * H;
@@ -191,6 +195,8 @@ template <bool QUANT>
 __global__ void __launch_bounds__(256)
 act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ q_out,
                float* __restrict__ scale_t, int scale_pitch, int I, int act) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   const int row = blockIdx.y;
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
   const int nvec = I / 8;
@@ -226,6 +232,8 @@ act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__
 __global__ void __launch_bounds__(256)
 quant_act_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q_out, float* __restrict__ scale_t,
                  int scale_pitch, int K) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   const int row = blockIdx.y;
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
   const bool active = v < K / 8;
@@ -253,6 +261,8 @@ rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__
                   void* __restrict__ k_cache, void* __restrict__ v_cache, const float* __restrict__ k_scale,
                   const float* __restrict__ v_scale, int Hq, int Hkv, int D, int rot, int neox, long long num_slots,
                   int max_pos) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   const int t = blockIdx.x;
   // a position beyond the rotary table (operator asked for more tokens than the model supports) reads
   // the table's last row instead of running off its end
@@ -318,6 +328,8 @@ rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__
 __global__ void __launch_bounds__(256)
 embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
                  int H, int rows) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= rows) id = rows - 1;  // self-check: clamp instead of reading out of bounds
@@ -331,6 +343,8 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 argmax_logprob_kernel(const T* __restrict__ logits, long long* __restrict__ ids, float* __restrict__ logprob, int V,
                       long long row_stride) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   __shared__ float s_m[32], s_s[32];
   __shared__ int s_i[32];
   const T* row = logits + static_cast<size_t>(blockIdx.x) * row_stride;
@@ -452,6 +466,8 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
               const int* __restrict__ top_k, const float* __restrict__ top_p, const unsigned char* __restrict__ do_sample,
               const long long* __restrict__ seeds, const int* __restrict__ steps, long long* __restrict__ ids,
               float* __restrict__ logprob, int V) {
+  tgi::pdl_wait();      // inputs come from earlier kernels of the stream
+  tgi::pdl_trigger();   // let the next kernel be placed while this one runs
   __shared__ float red[32];
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
@@ -557,7 +573,7 @@ int tgi_norm(const void* x, const void* residual, const void* weight, const void
   auto ro_ = static_cast<__nv_bfloat16*>(res_out);
   auto q_ = static_cast<uint8_t*>(q_out);
 #define LAUNCH(VPT, LAYER, QUANT) \
-  norm_kernel<VPT, LAYER, QUANT><<<T, threads, 0, stream>>>(x_, r_, w_, b_, o_, ro_, q_, scale_t, scale_pitch, H, eps, w_offset)
+  tgi::launch(norm_kernel<VPT, LAYER, QUANT>, dim3(T), dim3(threads), 0, stream, x_, r_, w_, b_, o_, ro_, q_, scale_t, scale_pitch, H, eps, w_offset)
   if (vpt == 1) {
     if (layer) { if (quant) LAUNCH(1, true, true); else LAUNCH(1, true, false); }
     else { if (quant) LAUNCH(1, false, true); else LAUNCH(1, false, false); }
@@ -577,10 +593,10 @@ int tgi_act_mul(const void* in, void* out, void* q_out, float* scale_t, int scal
   if (quant && I % 128 != 0) return -11;
   dim3 grid((I / 8 + 255) / 256, T);
   if (quant)
-    act_mul_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), nullptr,
+    tgi::launch(act_mul_kernel<true>, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), nullptr,
                                                    static_cast<uint8_t*>(q_out), scale_t, scale_pitch, I, act);
   else
-    act_mul_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in),
+    tgi::launch(act_mul_kernel<false>, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in),
                                                     static_cast<__nv_bfloat16*>(out), nullptr, nullptr, 0, I, act);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -589,7 +605,7 @@ int tgi_quant_act(const void* x, void* q_out, float* scale_t, int scale_pitch, i
   if (T <= 0) return 0;
   if (K % 128 != 0) return -10;
   dim3 grid((K / 8 + 255) / 256, T);
-  quant_act_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out),
+  tgi::launch(quant_act_kernel, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q_out),
                                              scale_t, scale_pitch, K);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -600,11 +616,11 @@ int tgi_rope_cache(const void* qkv, const int* positions, const float* cos_sin, 
   if (T <= 0) return 0;
   if (D % 2 != 0 || rot % 2 != 0 || rot > D || max_pos < 1) return -10;
   if (fp8_cache)
-    rope_cache_kernel<true><<<T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
+    tgi::launch(rope_cache_kernel<true>, dim3(T), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
                                                    static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale,
                                                    v_scale, Hq, Hkv, D, rot, neox, num_slots, max_pos);
   else
-    rope_cache_kernel<false><<<T, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
+    tgi::launch(rope_cache_kernel<false>, dim3(T), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
                                                     static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale,
                                                     v_scale, Hq, Hkv, D, rot, neox, num_slots, max_pos);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -613,7 +629,7 @@ int tgi_rope_cache(const void* qkv, const int* positions, const float* cos_sin, 
 int tgi_embedding(const int* ids, const void* table, void* out, int T, int H, int rows, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H % 8 != 0) return -10;
-  embedding_kernel<<<T, 256, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table),
+  tgi::launch(embedding_kernel, dim3(T), dim3(256), 0, stream, ids, static_cast<const __nv_bfloat16*>(table),
                                           static_cast<__nv_bfloat16*>(out), H, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -622,9 +638,9 @@ int tgi_argmax_logprob(const void* logits, long long* ids, float* logprob, int B
                        int is_fp32, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (is_fp32)
-    argmax_logprob_kernel<float><<<B, 1024, 0, stream>>>(static_cast<const float*>(logits), ids, logprob, V, row_stride);
+    tgi::launch(argmax_logprob_kernel<float>, dim3(B), dim3(1024), 0, stream, static_cast<const float*>(logits), ids, logprob, V, row_stride);
   else
-    argmax_logprob_kernel<__nv_bfloat16><<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ids,
+    tgi::launch(argmax_logprob_kernel<__nv_bfloat16>, dim3(B), dim3(1024), 0, stream, static_cast<const __nv_bfloat16*>(logits), ids,
                                                                  logprob, V, row_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -637,10 +653,10 @@ int tgi_sample(const void* scores, long long row_stride, int is_fp32, const floa
   if (B <= 0) return 0;
   if (V <= 0) return -10;
   if (is_fp32)
-    sample_kernel<float><<<B, 1024, 0, stream>>>(static_cast<const float*>(scores), row_stride, temperature, top_k, top_p,
+    tgi::launch(sample_kernel<float>, dim3(B), dim3(1024), 0, stream, static_cast<const float*>(scores), row_stride, temperature, top_k, top_p,
                                                  do_sample, seeds, steps, ids, logprob, V);
   else
-    sample_kernel<__nv_bfloat16><<<B, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(scores), row_stride, temperature,
+    tgi::launch(sample_kernel<__nv_bfloat16>, dim3(B), dim3(1024), 0, stream, static_cast<const __nv_bfloat16*>(scores), row_stride, temperature,
                                                          top_k, top_p, do_sample, seeds, steps, ids, logprob, V);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

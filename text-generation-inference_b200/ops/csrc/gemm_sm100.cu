@@ -33,6 +33,7 @@
 // (warps 2, 3 idle; the four give their registers away with setmaxnreg), warps 4..11 = promotion /
 // epilogue.  All waits are bounded (sm100.cuh): on expiry the kernel records an error code in
 // `status`, drains its outstanding TMA loads, frees TMEM and returns.
+#include "launch.cuh"
 #include "sm100.cuh"
 
 using namespace sm100;
@@ -236,6 +237,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // Barrier set-up, TMEM allocation and descriptor prefetch above touch no tensor data, so they overlap
+  // with the tail of the previous kernel; from here on the operands (and the workspace) are used.
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
 
   if (warp < 4) {
     reg_dec<40>();
@@ -632,9 +637,10 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
       }
     }
   }
-  kern<<<grid, kThreads, smem, stream>>>(tmW, tmX, tmS, wscale, static_cast<__nv_bfloat16*>(C),
-                                         static_cast<const __nv_bfloat16*>(bias), M, N, K, ws, counters, status, push);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  const cudaError_t err = tgi::launch(kern, dim3(grid), dim3(kThreads), smem, stream, tmW, tmX, tmS, wscale,
+                                      static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, K,
+                                      ws, counters, status, push);
+  return err == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 int fill_push(PushArgs& p, void* const* heaps, int rank, int world, int rows_per, long long off_slots,

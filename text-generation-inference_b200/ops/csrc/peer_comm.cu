@@ -21,6 +21,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch.cuh"
 #include "sm100.cuh"
 
 namespace {
@@ -218,6 +219,8 @@ __global__ void __launch_bounds__(1024)
 peer_reduce_kernel(const PeerArgs a) {
   __shared__ float red[32];
   __shared__ int failed;
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
   BlockSync sync(a, &failed);
@@ -362,6 +365,8 @@ peer_argmax_kernel(const PeerArgs a, const __nv_bfloat16* __restrict__ logits, l
   __shared__ float sm_m[32], sm_s[32];
   __shared__ int sm_i[32];
   __shared__ int failed;
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
   BlockSync sync(a, &failed);
@@ -462,9 +467,9 @@ int launch_reduce(const PeerArgs& a, int blocks, cudaStream_t stream) {
   int threads = ((nvec + 31) / 32) * 32;
   if (threads > 1024) threads = 1024;
   if (NORM && nvec > 1024)
-    peer_reduce_kernel<NORM, QUANT, 2><<<blocks, threads, 0, stream>>>(a);
+    tgi::launch(peer_reduce_kernel<NORM, QUANT, 2>, dim3(blocks), dim3(threads), 0, stream, a);
   else
-    peer_reduce_kernel<NORM, QUANT, 1><<<blocks, threads, 0, stream>>>(a);
+    tgi::launch(peer_reduce_kernel<NORM, QUANT, 1>, dim3(blocks), dim3(threads), 0, stream, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -564,8 +569,8 @@ int tgi_peer_argmax(void* const* heaps, int rank, int world, const void* logits,
   a.pushed = 0;
   a.off_push_flags = 0;
   a.push_epoch = nullptr;
-  peer_argmax_kernel<<<blocks, 1024, 0, stream>>>(a, static_cast<const __nv_bfloat16*>(logits), row_stride, vocab_start,
-                                                  logit_scale, off_cand, ids, logprob);
+  tgi::launch(peer_argmax_kernel, dim3(blocks), dim3(1024), 0, stream, a, static_cast<const __nv_bfloat16*>(logits),
+              row_stride, vocab_start, logit_scale, off_cand, ids, logprob);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
