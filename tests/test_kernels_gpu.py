@@ -182,6 +182,8 @@ def test_paged_attention_decode(K, fp8, Hq, Hkv, D):
     _attention_case(K, 3, [1] * 3, [300, 5, 129], Hq, Hkv, D, fp8, nsplit=1)
     _attention_case(K, 3, [1] * 3, [300, 5, 129], Hq, Hkv, D, fp8, nsplit=4)
     _attention_case(K, 2, [1, 1], [500, 90], Hq, Hkv, D, fp8, window=100)
+    _attention_case(K, 3, [1] * 3, [77, 300, 32], Hq, Hkv, D, fp8, softcap=30.0)
+    assert K.check_status() == 0
 
 
 def test_embedding_and_argmax(K):

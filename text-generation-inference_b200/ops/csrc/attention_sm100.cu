@@ -28,7 +28,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
 #include "launch.cuh"
+#include "sm100.cuh"
+#include "tensor_map.cuh"
 
 namespace {
 
@@ -659,6 +666,329 @@ decode_kernel_v2(Params p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// decode over e4m3 pages with D = 128 and at most 8 query heads per KV head: decode_kernel_v3.
+// grid (B, Hkv, nsplit), block 128.  As in v2 every warp walks its own chunks of the KV range, but
+//   * the pages arrive by TMA: one `cp.async.bulk.tensor.2d` per 16 tokens of K or V (box 16 x 128
+//     bytes, 128-byte swizzle) on a per-warp mbarrier ring, so a chunk costs four copy instructions
+//     instead of a block-table lookup and a cp.async per 16 bytes and lane;
+//   * the MMAs are transposed: S^T[tokens x heads] = K Q^T and O^T[d x heads] = V^T P^T, so the 8 query
+//     heads are the N = 8 of m16n8k16 (nothing is padded to 16 rows) and K and V are A operands read
+//     with 16-byte shared-memory loads straight from the raw e4m3 tiles.  Inside an MMA the order of
+//     the contracted index and of the rows is free, so every lane takes the bytes as they lie in its
+//     loads: for Q K^T lane (g, j) owns 16 consecutive head dimensions of token rho(g) and rho(g)+8
+//     (rho = 3-bit reversal, which makes the two rows of a quarter-warp hit different banks under the
+//     TMA swizzle); for P V it owns dimensions 16g..16g+15 of four tokens and pairs the bytes of two
+//     tokens with `prmt` before `cvt.rn.f16x2.e4m3x2`.  No widened copy of V exists in shared memory;
+//   * P goes through a 640-byte per-warp tile (heads x tokens, fp16) to change from accumulator to
+//     B-operand layout; row sums stay per lane until the end.
+// Every mbarrier wait is bounded; a wait that runs out sets `g_attn_status` and the warp stops
+// consuming, waits (bounded) for the copies it still has in flight and takes part in the merge.
+// ------------------------------------------------------------------------------------------------
+__device__ int g_attn_status = 0;
+
+struct DecodeV3 {
+  static constexpr int D = 128;
+  static constexpr int CT = 32;                         // tokens per warp chunk
+  static constexpr int kStages = 2;
+  static constexpr int kStageBytes = 2 * CT * D;        // K then V
+  static constexpr int kWarpRing = kStages * kStageBytes;
+  static constexpr int kRingBytes = 4 * kWarpRing;
+  static constexpr int kQBytes = 8 * D * 2;
+  static constexpr int kPPitch = CT + 8;                // halves per head row of the P tile
+  static constexpr int kPBytes = 8 * kPPitch * 2;
+  static constexpr int kOffQ = kRingBytes;
+  static constexpr int kOffP = kOffQ + kQBytes;
+  static constexpr int kOffBar = kOffP + 4 * kPBytes;
+  static constexpr int kBytes = kOffBar + 4 * kStages * 8;
+  static constexpr int kMergeBytes = 4 * 8 * D * 4 + 4 * 8 * 2 * 4;
+  static_assert(kMergeBytes <= kRingBytes, "merge scratch must fit in the rings");
+};
+
+__device__ __forceinline__ int bitrev3(int x) { return ((x & 1) << 2) | (x & 2) | ((x >> 2) & 1); }
+
+// the two e4m3 pairs of a 32-bit word as fp16x2 (low pair, high pair)
+__device__ __forceinline__ void cvt_e4m3x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 l, h;\n\t"
+      "mov.b32 {l, h}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, l;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(w));
+}
+
+__global__ void __launch_bounds__(128, 3)
+decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
+  using S = DecodeV3;
+  constexpr int D = S::D, CT = S::CT, MT = CT / 16;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, j = lane & 3;
+  uint8_t* ring = smem + warp * S::kWarpRing;
+  uint16_t* sQ = reinterpret_cast<uint16_t*>(smem + S::kOffQ);
+  uint16_t* sP = reinterpret_cast<uint16_t*>(smem + S::kOffP + warp * S::kPBytes);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kOffBar) + warp * S::kStages;
+
+  const int G = p.Hq / p.Hkv;           // <= 8 (checked by the launcher)
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int h0 = kvh * G;
+  const int L = p.kv_lens[b];
+  const int q_row = p.cu_seqlens_q[b];
+  if (p.cu_seqlens_q[b + 1] == q_row) return;   // sequence contributes no query this step
+  const int pos = L - 1;
+  int t_lo = 0;
+  if (p.window > 0) t_lo = max(0, pos - p.window + 1) / CT * CT;
+  const int chunks_total = (L - t_lo + CT - 1) / CT;
+  const int chunks_per = (chunks_total + p.nsplit - 1) / p.nsplit;
+  const int c0 = split * chunks_per;
+  const int c1 = min(chunks_total, c0 + chunks_per);
+  const int my_n = (c1 - c0 - warp + 3) / 4 > 0 ? (c1 - c0 - warp + 3) / 4 : 0;   // chunks c0 + warp + 4 i
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < S::kStages; ++s) sm100::mbar_init(&full[s], 1);
+    sm100::fence_barrier_init();
+  }
+  __syncwarp();
+
+  // lanes 0..2*MT-1 each fetch one 16-token box: lane = 2 * box + (0: K, 1: V)
+  auto issue = [&](int i) {
+    if (i >= my_n) return;
+    const int stg = i % S::kStages;
+    if (lane == 0) {
+      sm100::fence_proxy_async();   // the stage's earlier reads (generic proxy) precede the refill
+      sm100::mbar_arrive_expect_tx(&full[stg], S::kStageBytes);
+    }
+    __syncwarp();
+    if (lane < 2 * MT) {
+      const int isv = lane & 1, box = lane >> 1;
+      int t = t_lo + (c0 + warp + 4 * i) * CT + box * 16;
+      if (t >= L) t = (L - 1) & ~15;   // past the end: fetch the last group again (masked below)
+      const int blk = p.block_tables[static_cast<size_t>(b) * p.max_blocks + (t >> p.bs_shift)];
+      const int row = (blk << p.bs_shift) + (t & (p.block_size - 1));
+      sm100::tma_load_2d(ring + stg * S::kStageBytes + isv * (CT * D) + box * (16 * D), isv ? &tmV : &tmK, &full[stg],
+                         kvh * D, row);
+    }
+  };
+  static_assert(2 * MT <= 32 && 2 * MT * 16 * D == S::kStageBytes, "a stage is MT boxes of K and MT of V");
+#pragma unroll
+  for (int s = 0; s < S::kStages - 1; ++s) issue(s);
+
+  // Q rows of this KV head as fp16, [8][D] row-major (rows past G are zero)
+  for (int c = threadIdx.x; c < 8 * (D / 8); c += blockDim.x) {
+    const int row = c / (D / 8), cc = c % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < G) {
+      v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(q_row) * p.Hq + h0 + row) * D + cc * 8);
+      const __nv_bfloat162* bv = reinterpret_cast<const __nv_bfloat162*>(&v);
+      uint32_t o4[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(bv[i]);
+        o4[i] = pack2<true>(f.x, f.y);
+      }
+      v = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+    }
+    *reinterpret_cast<uint4*>(sQ + row * D + cc * 8) = v;
+  }
+  __syncthreads();
+
+  // B fragments of Q^T: for k-step (q, i) lane (head g, j) holds Q[g][64 q + 16 j + 4 i .. + 3]
+  uint32_t qb[2][4][2];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const uint4 lo = *reinterpret_cast<const uint4*>(sQ + g * D + 64 * q + 16 * j);
+    const uint4 hi = *reinterpret_cast<const uint4*>(sQ + g * D + 64 * q + 16 * j + 8);
+    qb[q][0][0] = lo.x; qb[q][0][1] = lo.y; qb[q][1][0] = lo.z; qb[q][1][1] = lo.w;
+    qb[q][2][0] = hi.x; qb[q][2][1] = hi.y; qb[q][3][0] = hi.z; qb[q][3][1] = hi.w;
+  }
+
+  // o[i]: dimensions 16 g + 2 i (elements 0, 1) and 16 g + 2 i + 1 (elements 2, 3) of heads 2j (0, 2) and 2j+1 (1, 3)
+  float o[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};   // heads 2j, 2j+1; l is this lane's share
+  const float ksc = p.k_scale ? p.k_scale[kvh] : 1.f;
+  const float vsc = p.v_scale ? p.v_scale[kvh] : 1.f;
+  const float raw_scale = p.scale * ksc;
+  const float scale_log2 = raw_scale * kLog2e;
+  const int rg = bitrev3(g);                      // token row (mod 8) of this lane's S^T rows
+  const int rj0 = bitrev3(j), rj1 = bitrev3(j + 4);   // token rows (mod 8) of this lane's V loads
+  bool failed = false;
+  int done = 0;
+
+  for (int i = 0; i < my_n; ++i) {
+    issue(i + S::kStages - 1);
+    if (!__all_sync(0xffffffffu, sm100::mbar_wait(&full[i % S::kStages], (i / S::kStages) & 1))) {
+      failed = true;   // warp-uniform
+      break;
+    }
+    done = i + 1;
+    const uint8_t* sK = ring + (i % S::kStages) * S::kStageBytes;
+    const uint8_t* sV = sK + CT * D;
+    const int tbase = t_lo + (c0 + warp + 4 * i) * CT;
+
+    // ---- S^T = K Q^T ----
+    float s[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+      const uint8_t* ra = sK + (mt * 16 + rg) * D;
+      const uint8_t* rb = ra + 8 * D;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int off = ((4 * q + j) ^ rg) << 4;
+        const uint4 wa = *reinterpret_cast<const uint4*>(ra + off);
+        const uint4 wb = *reinterpret_cast<const uint4*>(rb + off);
+        const uint32_t a4[4] = {wa.x, wa.y, wa.z, wa.w}, b4[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint32_t a[4];
+          cvt_e4m3x4(a4[k], a[0], a[2]);
+          cvt_e4m3x4(b4[k], a[1], a[3]);
+          mma16816<true>(s[mt], a, qb[q][k][0], qb[q][k][1]);
+        }
+      }
+    }
+
+    // ---- online softmax over the tokens of the chunk, per head ----
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int t = tbase + mt * 16 + rg + (e >> 1) * 8;
+        float v = s[mt][e];
+        if (p.softcap > 0.f) v = p.softcap * tanhf(v * raw_scale / p.softcap) * kLog2e;
+        else v = v * scale_log2;
+        const bool ok = t < L && (p.window <= 0 || t > pos - p.window);
+        v = ok ? v : -INFINITY;
+        s[mt][e] = v;
+        mx[e & 1] = fmaxf(mx[e & 1], v);
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
+      const float mn = fmaxf(m[r], mx[r]);
+      alpha[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - mn);
+      m[r] = mn;
+    }
+    float rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float mm = m[e & 1];
+        const float pv = (mm == -INFINITY) ? 0.f : exp2f(s[mt][e] - mm);
+        s[mt][e] = pv;
+        rs[e & 1] += pv;
+      }
+      // contraction index of P V inside the 16 tokens: 2 g (token rho(g)) and 2 g + 1 (token rho(g) + 8)
+      *reinterpret_cast<uint32_t*>(sP + (2 * j) * S::kPPitch + mt * 16 + 2 * g) = pack2<true>(s[mt][0], s[mt][2]);
+      *reinterpret_cast<uint32_t*>(sP + (2 * j + 1) * S::kPPitch + mt * 16 + 2 * g) = pack2<true>(s[mt][1], s[mt][3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l[r] = l[r] * alpha[r] + rs[r];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      o[k][0] *= alpha[0]; o[k][2] *= alpha[0];
+      o[k][1] *= alpha[1]; o[k][3] *= alpha[1];
+    }
+    __syncwarp();
+    uint32_t pb[4];   // B fragments of P^T: (b0, b1) of k-step 0, then of k-step 1
+    ldsm_x4(pb, sP + (lane & 7) * S::kPPitch + (lane >> 3) * 8);
+
+    // ---- O^T += V^T P^T ----
+#pragma unroll
+    for (int ks = 0; ks < MT; ++ks) {
+      const uint8_t* base = sV + ks * 16 * D;
+      const uint4 wa = *reinterpret_cast<const uint4*>(base + rj0 * D + ((g ^ rj0) << 4));         // k = 2j
+      const uint4 wb = *reinterpret_cast<const uint4*>(base + (rj0 + 8) * D + ((g ^ rj0) << 4));   // k = 2j + 1
+      const uint4 wc = *reinterpret_cast<const uint4*>(base + rj1 * D + ((g ^ rj1) << 4));         // k = 2j + 8
+      const uint4 wd = *reinterpret_cast<const uint4*>(base + (rj1 + 8) * D + ((g ^ rj1) << 4));   // k = 2j + 9
+      const uint32_t a4[4] = {wa.x, wa.y, wa.z, wa.w}, b4[4] = {wb.x, wb.y, wb.z, wb.w};
+      const uint32_t c4[4] = {wc.x, wc.y, wc.z, wc.w}, d4[4] = {wd.x, wd.y, wd.z, wd.w};
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        // bytes 4x .. 4x+3 of the lane's 16 dimensions: (0, 1) feed o[2x], (2, 3) feed o[2x+1]
+        uint32_t a[4], a2[4];
+        cvt_e4m3x4(__byte_perm(a4[x], b4[x], 0x5140), a[0], a[1]);
+        cvt_e4m3x4(__byte_perm(c4[x], d4[x], 0x5140), a[2], a[3]);
+        cvt_e4m3x4(__byte_perm(a4[x], b4[x], 0x7362), a2[0], a2[1]);
+        cvt_e4m3x4(__byte_perm(c4[x], d4[x], 0x7362), a2[2], a2[3]);
+        mma16816<true>(o[2 * x], a, pb[2 * ks], pb[2 * ks + 1]);
+        mma16816<true>(o[2 * x + 1], a2, pb[2 * ks], pb[2 * ks + 1]);
+      }
+    }
+    __syncwarp();   // the stage and the P tile are free for the next iteration
+  }
+  if (failed) {
+    if (lane == 0) atomicOr(&g_attn_status, 1);
+    // copies issued but not consumed: chunks done .. min(my_n, done + kStages - 1) - 1 (the refill of
+    // iteration `done` was issued before its wait ran out)
+    for (int i = done; i < my_n && i < done + S::kStages; ++i) sm100::mbar_wait(&full[i % S::kStages], (i / S::kStages) & 1);
+  }
+  __syncthreads();
+
+  // ---- merge the four warps through shared memory (the rings are no longer needed) ----
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 4);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 8);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 16);
+  }
+  float* mO = reinterpret_cast<float*>(smem);   // [4][8][D]
+  float* mML = mO + 4 * 8 * D;                  // [4][8][2]
+  {
+    float* r0 = mO + (warp * 8 + 2 * j) * D + 16 * g;
+    float* r1 = r0 + D;
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      *reinterpret_cast<float4*>(r0 + 4 * x) = make_float4(o[2 * x][0], o[2 * x][2], o[2 * x + 1][0], o[2 * x + 1][2]);
+      *reinterpret_cast<float4*>(r1 + 4 * x) = make_float4(o[2 * x][1], o[2 * x][3], o[2 * x + 1][1], o[2 * x + 1][3]);
+    }
+    if (g == 0) {
+      mML[(warp * 8 + 2 * j) * 2] = m[0];
+      mML[(warp * 8 + 2 * j) * 2 + 1] = l[0];
+      mML[(warp * 8 + 2 * j + 1) * 2] = m[1];
+      mML[(warp * 8 + 2 * j + 1) * 2 + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int row = idx / D, col = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, mML[(w * 8 + row) * 2]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mML[(w * 8 + row) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+      acc += mO[(w * 8 + row) * D + col] * f;
+      ll += mML[(w * 8 + row) * 2 + 1] * f;
+    }
+    const int h = h0 + row;
+    if (p.nsplit == 1) {
+      const float inv = ll > 0.f ? vsc / ll : 0.f;
+      p.out[(static_cast<size_t>(q_row) * p.Hq + h) * D + col] = __float2bfloat16(acc * inv);
+    } else {
+      const size_t pi = (static_cast<size_t>(b) * p.Hq + h) * p.nsplit + split;
+      p.part_o[pi * D + col] = ll > 0.f ? acc * (vsc / ll) : 0.f;
+      if (col == 0) {
+        p.part_ml[pi * 2] = mm;
+        p.part_ml[pi * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
 // merge split partials: grid (B, Hq), block D
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ cu_seqlens_q, __nv_bfloat16* __restrict__ out, int Hq,
@@ -687,6 +1017,53 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
   }
 }
 
+// `TGI_B200_ATTN_V3=0` keeps e4m3 decode on decode_kernel_v2
+bool decode_v3_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("TGI_B200_ATTN_V3");
+    return v == nullptr || std::strcmp(v, "0") != 0;
+  }();
+  return on;
+}
+
+// Tensor map of one e4m3 K or V page pool viewed as [slots, Hkv * 128] bytes, box 16 slots x 128 bytes.
+// Pools live as long as the model, so the maps are cached by (device, pointer, geometry).
+const CUtensorMap* page_map(const void* cache, const Params& p) {
+  struct Key {
+    int dev;
+    const void* ptr;
+    int blocks, bs, hkv;
+    bool operator==(const Key& o) const {
+      return dev == o.dev && ptr == o.ptr && blocks == o.blocks && bs == o.bs && hkv == o.hkv;
+    }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      return std::hash<const void*>()(k.ptr) ^ (static_cast<size_t>(k.blocks) * 1000003u) ^
+             (static_cast<size_t>(k.bs) << 20) ^ (static_cast<size_t>(k.hkv) << 28) ^ static_cast<size_t>(k.dev);
+    }
+  };
+  static std::mutex mu;
+  static std::unordered_map<Key, CUtensorMap*, Hash> maps;
+  Key key{0, cache, p.num_blocks, p.block_size, p.Hkv};
+  if (cudaGetDevice(&key.dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = maps.find(key);
+  if (it != maps.end()) return it->second;
+  void* raw = nullptr;
+  if (posix_memalign(&raw, 64, sizeof(CUtensorMap)) != 0) return nullptr;
+  CUtensorMap* m = static_cast<CUtensorMap*>(raw);
+  const uint64_t pitch = static_cast<uint64_t>(p.Hkv) * 128;
+  const uint64_t slots = static_cast<uint64_t>(p.num_blocks) * p.block_size;
+  if (tgi::make_map_2d(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, cache, slots, pitch, pitch, 16, 128,
+                       CU_TENSOR_MAP_SWIZZLE_128B) != 0) {
+    free(raw);
+    return nullptr;
+  }
+  maps.emplace(key, m);
+  return m;
+}
+
 template <int D, bool FP8>
 int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
   using S = Smem<D, FP8>;
@@ -700,6 +1077,23 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
     }
     dim3 grid((max_q + kTile - 1) / kTile, p.Hq, B);
     tgi::launch(k, dim3(grid), dim3(128), smem, stream, p);
+  } else if (FP8 && D == 128 && p.Hq / p.Hkv <= 8 && p.block_size >= 16 && decode_v3_enabled()) {
+    auto k = decode_kernel_v3;
+    static bool set = false;
+    if (!set) {
+      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeV3::kBytes) != cudaSuccess) return -2;
+      set = true;
+    }
+    const CUtensorMap* tk = page_map(p.k_cache, p);
+    const CUtensorMap* tv = page_map(p.v_cache, p);
+    if (tk == nullptr || tv == nullptr) return -14;
+    dim3 grid(B, p.Hkv, p.nsplit);
+    tgi::launch(k, dim3(grid), dim3(128), DecodeV3::kBytes, stream, p, *tk, *tv);
+    if (p.nsplit > 1) {
+      dim3 g2(B, p.Hq);
+      tgi::launch(decode_merge_kernel, dim3(g2), dim3(128), 0, stream, p.part_o, p.part_ml, p.cu_seqlens_q, p.out, p.Hq, D,
+                  p.nsplit);
+    }
   } else {
     auto k = decode_kernel_v2<D, FP8>;
     constexpr int dsmem = DecodeSmem<D, FP8>::kBytes;
@@ -733,6 +1127,18 @@ int tgi_attn_decode_splits(int B, int Hkv, int G, int max_kv, int sm_count) {
   if (want > tiles) want = tiles;
   if (want > 64) want = 64;
   return want < 1 ? 1 : want;
+}
+
+// Error word of the decode kernels (bit 0: a page copy did not arrive within the wait bound); `reset`
+// clears it after reading.  Synchronises with the device.
+int tgi_attn_status(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int));
+  }
+  return v;
 }
 
 int tgi_paged_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,

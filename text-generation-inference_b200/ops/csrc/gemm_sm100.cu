@@ -34,6 +34,7 @@
 // epilogue.  All waits are bounded (sm100.cuh): on expiry the kernel records an error code in
 // `status`, drains its outstanding TMA loads, frees TMEM and returns.
 #include "launch.cuh"
+#include "tensor_map.cuh"
 #include "sm100.cuh"
 
 using namespace sm100;
@@ -538,36 +539,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// 2-D row-major tensor [rows, cols]; box = [box_rows, box_cols]
-int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, uint64_t rows, uint64_t cols,
-                uint64_t row_pitch_bytes, uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle sw) {
-  EncodeTiledFn enc = get_encode();
-  if (enc == nullptr) return -100;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {row_pitch_bytes};
-  cuuint32_t box[2] = {box_cols, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
-}
+using tgi::make_map_2d;
 
 template <int MH, int TN, int STAGES, bool FP8>
 int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C,

@@ -50,7 +50,7 @@ def load():
     _LIB = ctypes.CDLL(str(_LIB_PATH))
     for name in ("tgi_gemm_bf16", "tgi_gemm_fp8_block", "tgi_norm", "tgi_act_mul", "tgi_quant_act",
                  "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention",
-                 "tgi_gemm_num_tiles", "tgi_attn_decode_splits"):
+                 "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
     wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
@@ -109,6 +109,10 @@ def check_status(device: Optional[torch.device] = None) -> int:
     if code != 0:
         st.status.zero_()
         st.counters.zero_()    # a kernel that gave up may have left split-tile counters half-way
+    with torch.cuda.device(st.device):
+        attn = int(load().tgi_attn_status(c_int(1)))   # decode attention: a page copy did not arrive in time
+    if attn != 0 and code == 0:
+        code = 100 + attn
     return code
 
 
