@@ -100,6 +100,7 @@ def main():
     ap.add_argument("--fp8", type=int, default=1)
     ap.add_argument("--prefill", type=int, default=0, help="also time prefill attention with this many tokens per sequence")
     ap.add_argument("--only", default="")
+    ap.add_argument("--nsplit", type=int, default=0, help="KV splits of the decode attention (0: the library's choice)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--plain", action="store_true", help="time direct launches instead of graph replays")
@@ -195,7 +196,8 @@ def main():
         cu = torch.arange(M + 1, device=dev, dtype=torch.int32)
         kl = torch.full((M,), args.ctx + 1, device=dev, dtype=torch.int32)
         eb = 1 if args.fp8 else 2
-        t = timer(lambda: K.paged_attention(q, kc, vc, bt, cu, kl, D ** -0.5, -1, 0.0, ksc, ksc, 1, args.ctx + 1))
+        t = timer(lambda: K.paged_attention(q, kc, vc, bt, cu, kl, D ** -0.5, -1, 0.0, ksc, ksc, 1, args.ctx + 1,
+                                              nsplit=args.nsplit or None))
         kv_bytes = M * (args.ctx + 1) * hkv * D * 2 * eb
         report(f"attn_decode[{M}x{hq}/{hkv} ctx={args.ctx}]", t, kv_bytes + 4 * M * hq * D,
                4.0 * M * hq * D * (args.ctx + 1))

@@ -59,6 +59,9 @@ __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(smem_u32(p)));
 }
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[4], const void* p) {   // fills r[0], r[1]
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
+}
 __device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -687,10 +690,11 @@ decode_kernel_v2(Params p) {
 // ------------------------------------------------------------------------------------------------
 __device__ int g_attn_status = 0;
 
+template <int CT_, int STAGES_>
 struct DecodeV3 {
   static constexpr int D = 128;
-  static constexpr int CT = 32;                         // tokens per warp chunk
-  static constexpr int kStages = 2;
+  static constexpr int CT = CT_;                        // tokens per warp chunk (16 or 32)
+  static constexpr int kStages = STAGES_;
   static constexpr int kStageBytes = 2 * CT * D;        // K then V
   static constexpr int kWarpRing = kStages * kStageBytes;
   static constexpr int kRingBytes = 4 * kWarpRing;
@@ -702,8 +706,18 @@ struct DecodeV3 {
   static constexpr int kOffBar = kOffP + 4 * kPBytes;
   static constexpr int kBytes = kOffBar + 4 * kStages * 8;
   static constexpr int kMergeBytes = 4 * 8 * D * 4 + 4 * 8 * 2 * 4;
+  static constexpr int kFit = (227 * 1024) / (kBytes + 1024);
+  static constexpr int kCap = CT == 16 ? 4 : 3;            // 32-token chunks need about 146 registers per thread
+  static constexpr int kMinBlocks = kFit > kCap ? kCap : kFit;
   static_assert(kMergeBytes <= kRingBytes, "merge scratch must fit in the rings");
+  static_assert(CT == 16 || CT == 32, "chunks are one or two 16-token boxes");
 };
+
+__device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: 2 ulp, -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ int bitrev3(int x) { return ((x & 1) << 2) | (x & 2) | ((x >> 2) & 1); }
 
@@ -717,11 +731,11 @@ __device__ __forceinline__ void cvt_e4m3x4(uint32_t w, uint32_t& lo, uint32_t& h
       : "r"(w));
 }
 
-__global__ void __launch_bounds__(128, 3)
+template <class S>
+__global__ void __launch_bounds__(128, S::kMinBlocks)
 decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
   tgi::pdl_wait();
   tgi::pdl_trigger();
-  using S = DecodeV3;
   constexpr int D = S::D, CT = S::CT, MT = CT / 16;
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -732,7 +746,9 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kOffBar) + warp * S::kStages;
 
   const int G = p.Hq / p.Hkv;           // <= 8 (checked by the launcher)
-  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  // the KV heads of a sequence are neighbouring CTAs: their 128-byte slices of a token row are then fetched
+  // at about the same time, which keeps the DRAM pages open
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int h0 = kvh * G;
   const int L = p.kv_lens[b];
   const int q_row = p.cu_seqlens_q[b];
@@ -753,7 +769,19 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
   }
   __syncwarp();
 
-  // lanes 0..2*MT-1 each fetch one 16-token box: lane = 2 * box + (0: K, 1: V)
+  // lanes 0..2*MT-1 each fetch one 16-token box: lane = 2 * box + (0: K, 1: V).  The block-table entry of
+  // chunk i+1 is read when chunk i is issued, so that no copy waits for a global load.
+  const int isv = lane & 1, box = lane >> 1;
+  auto first_token = [&](int i) {
+    int t = t_lo + (c0 + warp + 4 * i) * CT + box * 16;
+    if (t >= L) t = (L - 1) & ~15;   // past the end: fetch the last group again (masked below)
+    return t;
+  };
+  auto table_entry = [&](int i) {
+    if (i >= my_n || lane >= 2 * MT) return 0;
+    return p.block_tables[static_cast<size_t>(b) * p.max_blocks + (first_token(i) >> p.bs_shift)];
+  };
+  int blk_next = table_entry(0);
   auto issue = [&](int i) {
     if (i >= my_n) return;
     const int stg = i % S::kStages;
@@ -763,14 +791,11 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
     }
     __syncwarp();
     if (lane < 2 * MT) {
-      const int isv = lane & 1, box = lane >> 1;
-      int t = t_lo + (c0 + warp + 4 * i) * CT + box * 16;
-      if (t >= L) t = (L - 1) & ~15;   // past the end: fetch the last group again (masked below)
-      const int blk = p.block_tables[static_cast<size_t>(b) * p.max_blocks + (t >> p.bs_shift)];
-      const int row = (blk << p.bs_shift) + (t & (p.block_size - 1));
+      const int row = (blk_next << p.bs_shift) + (first_token(i) & (p.block_size - 1));
       sm100::tma_load_2d(ring + stg * S::kStageBytes + isv * (CT * D) + box * (16 * D), isv ? &tmV : &tmK, &full[stg],
                          kvh * D, row);
     }
+    blk_next = table_entry(i + 1);
   };
   static_assert(2 * MT <= 32 && 2 * MT * 16 * D == S::kStageBytes, "a stage is MT boxes of K and MT of V");
 #pragma unroll
@@ -830,15 +855,16 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
     const uint8_t* sV = sK + CT * D;
     const int tbase = t_lo + (c0 + warp + 4 * i) * CT;
 
-    // ---- S^T = K Q^T ----
+    // ---- S^T = K Q^T (two accumulators per 16 tokens keep the dependent MMA chains short) ----
     float s[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-      s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+      float s2[2][4];
       const uint8_t* ra = sK + (mt * 16 + rg) * D;
       const uint8_t* rb = ra + 8 * D;
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
+        s2[q][0] = s2[q][1] = s2[q][2] = s2[q][3] = 0.f;
         const int off = ((4 * q + j) ^ rg) << 4;
         const uint4 wa = *reinterpret_cast<const uint4*>(ra + off);
         const uint4 wb = *reinterpret_cast<const uint4*>(rb + off);
@@ -848,25 +874,39 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
           uint32_t a[4];
           cvt_e4m3x4(a4[k], a[0], a[2]);
           cvt_e4m3x4(b4[k], a[1], a[3]);
-          mma16816<true>(s[mt], a, qb[q][k][0], qb[q][k][1]);
+          mma16816<true>(s2[q], a, qb[q][k][0], qb[q][k][1]);
         }
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[mt][e] = s2[0][e] + s2[1][e];
     }
 
     // ---- online softmax over the tokens of the chunk, per head ----
+    // m[] is kept in the scaled log2 domain; a chunk that needs no masking takes the short path
+    const bool plain = p.softcap <= 0.f && tbase + CT <= L && (p.window <= 0 || tbase > pos - p.window);
     float mx[2] = {-INFINITY, -INFINITY};
+    if (plain) {
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+      for (int mt = 0; mt < MT; ++mt) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[mt][0], s[mt][2]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[mt][1], s[mt][3]));
+      }
+      mx[0] *= scale_log2;   // scale_log2 > 0
+      mx[1] *= scale_log2;
+    } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int t = tbase + mt * 16 + rg + (e >> 1) * 8;
-        float v = s[mt][e];
-        if (p.softcap > 0.f) v = p.softcap * tanhf(v * raw_scale / p.softcap) * kLog2e;
-        else v = v * scale_log2;
-        const bool ok = t < L && (p.window <= 0 || t > pos - p.window);
-        v = ok ? v : -INFINITY;
-        s[mt][e] = v;
-        mx[e & 1] = fmaxf(mx[e & 1], v);
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int t = tbase + mt * 16 + rg + (e >> 1) * 8;
+          float v = s[mt][e];
+          if (p.softcap > 0.f) v = p.softcap * tanhf(v * raw_scale / p.softcap) * kLog2e;
+          else v = v * scale_log2;
+          const bool ok = t < L && (p.window <= 0 || t > pos - p.window);
+          v = ok ? v : -INFINITY;
+          s[mt][e] = v;
+          mx[e & 1] = fmaxf(mx[e & 1], v);
+        }
       }
     }
     float alpha[2];
@@ -876,7 +916,7 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
       const float mn = fmaxf(m[r], mx[r]);
-      alpha[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - mn);
+      alpha[r] = (mn == -INFINITY) ? 0.f : fast_exp2(m[r] - mn);
       m[r] = mn;
     }
     float rs[2] = {0.f, 0.f};
@@ -885,7 +925,9 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float mm = m[e & 1];
-        const float pv = (mm == -INFINITY) ? 0.f : exp2f(s[mt][e] - mm);
+        float pv;
+        if (plain) pv = fast_exp2(fmaf(s[mt][e], scale_log2, -mm));
+        else pv = (mm == -INFINITY) ? 0.f : fast_exp2(s[mt][e] - mm);
         s[mt][e] = pv;
         rs[e & 1] += pv;
       }
@@ -902,7 +944,8 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
     }
     __syncwarp();
     uint32_t pb[4];   // B fragments of P^T: (b0, b1) of k-step 0, then of k-step 1
-    ldsm_x4(pb, sP + (lane & 7) * S::kPPitch + (lane >> 3) * 8);
+    if (MT == 2) ldsm_x4(pb, sP + (lane & 7) * S::kPPitch + (lane >> 3) * 8);
+    else ldsm_x2(pb, sP + (lane & 7) * S::kPPitch + ((lane >> 3) & 1) * 8);
 
     // ---- O^T += V^T P^T ----
 #pragma unroll
@@ -1064,6 +1107,46 @@ const CUtensorMap* page_map(const void* cache, const Params& p) {
   return m;
 }
 
+template <class S>
+int launch_v3_cfg(const Params& p, int B, cudaStream_t stream) {
+  auto k = decode_kernel_v3<S>;
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess) return -2;
+    set = true;
+  }
+  const CUtensorMap* tk = page_map(p.k_cache, p);
+  const CUtensorMap* tv = page_map(p.v_cache, p);
+  if (tk == nullptr || tv == nullptr) return -14;
+  dim3 grid(p.Hkv, B, p.nsplit);
+  tgi::launch(k, dim3(grid), dim3(128), S::kBytes, stream, p, *tk, *tv);
+  if (p.nsplit > 1) {
+    dim3 g2(B, p.Hq);
+    tgi::launch(decode_merge_kernel, dim3(g2), dim3(128), 0, stream, p.part_o, p.part_ml, p.cu_seqlens_q, p.out, p.Hq,
+                128, p.nsplit);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// chunk size and ring depth of decode_kernel_v3; `TGI_B200_ATTN_V3_CFG` = "<tokens>x<stages>" picks another
+// of the compiled shapes
+int launch_v3(const Params& p, int B, cudaStream_t stream) {
+  static const int cfg = [] {
+    const char* v = std::getenv("TGI_B200_ATTN_V3_CFG");
+    if (v == nullptr) return 163;
+    if (std::strcmp(v, "32x2") == 0) return 322;
+    if (std::strcmp(v, "32x3") == 0) return 323;
+    if (std::strcmp(v, "16x4") == 0) return 164;
+    return 163;
+  }();
+  switch (cfg) {
+    case 322: return launch_v3_cfg<DecodeV3<32, 2>>(p, B, stream);
+    case 323: return launch_v3_cfg<DecodeV3<32, 3>>(p, B, stream);
+    case 164: return launch_v3_cfg<DecodeV3<16, 4>>(p, B, stream);
+    default: return launch_v3_cfg<DecodeV3<16, 3>>(p, B, stream);   // 4 CTAs (16 warps) per SM: fastest measured
+  }
+}
+
 template <int D, bool FP8>
 int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
   using S = Smem<D, FP8>;
@@ -1077,23 +1160,8 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
     }
     dim3 grid((max_q + kTile - 1) / kTile, p.Hq, B);
     tgi::launch(k, dim3(grid), dim3(128), smem, stream, p);
-  } else if (FP8 && D == 128 && p.Hq / p.Hkv <= 8 && p.block_size >= 16 && decode_v3_enabled()) {
-    auto k = decode_kernel_v3;
-    static bool set = false;
-    if (!set) {
-      if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeV3::kBytes) != cudaSuccess) return -2;
-      set = true;
-    }
-    const CUtensorMap* tk = page_map(p.k_cache, p);
-    const CUtensorMap* tv = page_map(p.v_cache, p);
-    if (tk == nullptr || tv == nullptr) return -14;
-    dim3 grid(B, p.Hkv, p.nsplit);
-    tgi::launch(k, dim3(grid), dim3(128), DecodeV3::kBytes, stream, p, *tk, *tv);
-    if (p.nsplit > 1) {
-      dim3 g2(B, p.Hq);
-      tgi::launch(decode_merge_kernel, dim3(g2), dim3(128), 0, stream, p.part_o, p.part_ml, p.cu_seqlens_q, p.out, p.Hq, D,
-                  p.nsplit);
-    }
+  } else if (FP8 && D == 128 && p.Hq / p.Hkv <= 8 && p.block_size >= 16 && B <= 65535 && decode_v3_enabled()) {
+    return launch_v3(p, B, stream);
   } else {
     auto k = decode_kernel_v2<D, FP8>;
     constexpr int dsmem = DecodeSmem<D, FP8>::kBytes;
