@@ -522,8 +522,10 @@ decode_kernel_v2(Params p) {
 
   const int G = p.Hq / p.Hkv;
   const int gchunks = (G + 15) / 16;
-  const int b = blockIdx.x;
-  const int kvh = blockIdx.y / gchunks, gc = blockIdx.y % gchunks;
+  // KV heads are the fastest grid dimension: the CTAs that read the neighbouring slices of a token row run
+  // at about the same time, which keeps the DRAM pages open
+  const int b = blockIdx.y;
+  const int kvh = blockIdx.x / gchunks, gc = blockIdx.x % gchunks;
   const int split = blockIdx.z;
   const int h0 = kvh * G + gc * 16;
   const int rows = min(16, G - gc * 16);
@@ -763,6 +765,8 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
   const int my_n = (c1 - c0 - warp + 3) / 4 > 0 ? (c1 - c0 - warp + 3) / 4 : 0;   // chunks c0 + warp + 4 i
 
   if (lane == 0) {
+    sm100::prefetch_tensormap(&tmK);
+    sm100::prefetch_tensormap(&tmV);
 #pragma unroll
     for (int s = 0; s < S::kStages; ++s) sm100::mbar_init(&full[s], 1);
     sm100::fence_barrier_init();
@@ -1160,7 +1164,9 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
     }
     dim3 grid((max_q + kTile - 1) / kTile, p.Hq, B);
     tgi::launch(k, dim3(grid), dim3(128), smem, stream, p);
-  } else if (FP8 && D == 128 && p.Hq / p.Hkv <= 8 && p.block_size >= 16 && B <= 65535 && decode_v3_enabled()) {
+  } else if (B > 65535) {
+    return -15;   // the batch index is grid dimension y
+  } else if (FP8 && D == 128 && p.Hq / p.Hkv <= 8 && p.block_size >= 16 && decode_v3_enabled()) {
     return launch_v3(p, B, stream);
   } else {
     auto k = decode_kernel_v2<D, FP8>;
@@ -1171,7 +1177,7 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
       set = true;
     }
     const int G = p.Hq / p.Hkv;
-    dim3 grid(B, p.Hkv * ((G + 15) / 16), p.nsplit);
+    dim3 grid(p.Hkv * ((G + 15) / 16), B, p.nsplit);
     tgi::launch(k, dim3(grid), dim3(128), dsmem, stream, p);
     if (p.nsplit > 1) {
       dim3 g2(B, p.Hq);
@@ -1186,10 +1192,19 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
 
 extern "C" {
 
-// Split count for a decode launch: enough CTAs for two waves over the SMs, bounded by the tiles a
-// sequence of max_kv tokens has.
+// Split count for a decode launch.  A grid that already has one CTA per SM is not split: measured on B200,
+// the partial results and the merge kernel cost more than the better balance gains (256 sequences x 1 KV
+// head, 1280 tokens: 25 us unsplit, 29 us in two splits, 34 us in four).  Smaller grids are split into
+// enough CTAs for two waves, bounded by the tiles a sequence of max_kv tokens has.
 int tgi_attn_decode_splits(int B, int Hkv, int G, int max_kv, int sm_count) {
   const int ctas = B * Hkv * ((G + 15) / 16);
+  if (ctas >= sm_count) {
+    // long sequences on a grid of fewer than four CTAs per SM: split down to 2048 tokens per CTA
+    if (ctas >= 4 * sm_count || max_kv < 4096) return 1;
+    int want = (4 * sm_count + ctas - 1) / ctas;
+    if (want > max_kv / 2048) want = max_kv / 2048;
+    return want < 1 ? 1 : want;
+  }
   int want = (2 * sm_count + ctas - 1) / ctas;
   const int tiles = (max_kv + kTile - 1) / kTile;
   if (want > tiles) want = tiles;
