@@ -91,6 +91,15 @@ def get_model(
 
         return load_vlm(path, cfg, loader, process_group, rank, world, tdtype, device, tokenizer, speculate,
                         kv_cache_dtype, max_prefill_tokens)
+    if model_type not in ARCHS and world == 1 and os.environ.get("TGI_B200_TRANSFORMERS_BACKEND", "1") == "1":
+        # unknown architecture whose transformers implementation goes through the attention interface: its
+        # own modules run around the paged attention (continuous batching, prefix caching, chunking kept)
+        from . import transformers_backend
+
+        if transformers_backend.supports(cfg.to_dict()):
+            return transformers_backend.load_transformers_flash(
+                path, cfg, process_group, rank, world, tdtype, device, tokenizer, speculate, kv_cache_dtype,
+                max_prefill_tokens)
     if model_type in ("bloom", "mpt", "opt", "t5", "mamba") or model_type not in ARCHS:
         from .padded import load_padded
 
