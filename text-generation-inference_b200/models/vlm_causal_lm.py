@@ -12,8 +12,12 @@ embeddings of the placeholder rows; the language model then runs on ``inputs_emb
 (same paged attention, same CUDA-graph decode, since decode steps never contain image rows).
 
 Covered families: LLaVA-style (CLIP tower, 2-layer MLP projector, optional class-token drop; the
-base-resolution view of llava_next) and PaliGemma-style (SigLIP tower, linear projector, embedding
-scale).  Towers are plain pre-norm ViTs evaluated with ``F.scaled_dot_product_attention``: the image
+base-resolution view of llava_next), PaliGemma-style (SigLIP tower, linear projector, embedding
+scale), Idefics2 (SigLIP-style tower, gated-MLP projection and a perceiver resampler that compresses
+an image to a fixed number of latents; ``custom_modeling/idefics2.py``) and Idefics3 / SmolVLM
+(pixel-shuffle connector; ``custom_modeling/idefics3.py``).  The Idefics families run on the global
+view of an image (the square resize to the tower's resolution); the sub-image tiling their
+processors can add is not produced.  Towers are plain pre-norm ViTs evaluated with ``F.scaled_dot_product_attention``: the image
 side is compute-light next to the decoder and runs once per request.
 """
 from __future__ import annotations
@@ -174,7 +178,7 @@ class VlmCausalLM(FlashCausalLM):
         super().__init__(model, tokenizer, dtype, device, rank, world, **kw)
         self.tower, self.projector = tower, projector
         self.image_token_id, self.drop_cls, self.image_embed_scale = image_token_id, drop_cls, embed_scale
-        self.tokens_per_image = tower.num_patches
+        self.tokens_per_image = projector.out_tokens(tower.num_patches)
         self.batch_cls = type("BoundVlmBatch", (VlmCausalLMBatch,), dict(
             image_token_id=image_token_id, tokens_per_image=self.tokens_per_image, image_size=tower.image_size,
             norm=(CLIP_MEAN, CLIP_STD) if tower.kind == "clip" else (SIGLIP_MEAN, SIGLIP_STD)))
@@ -189,10 +193,10 @@ class VlmCausalLM(FlashCausalLM):
         feats = self.tower(pixels.to(self.device))
         if self.drop_cls:
             feats = feats[:, 1:]
-        out = self.projector(feats.reshape(-1, feats.shape[-1]).to(self.dtype))
+        out = self.projector(feats.to(self.dtype))
         if self.image_embed_scale != 1.0:
             out = out * self.image_embed_scale
-        return out.view(feats.shape[0], feats.shape[1], -1)
+        return out
 
     def build_meta(self, batch, counts):
         meta, row_owner = super().build_meta(batch, counts)
@@ -226,18 +230,98 @@ class _MlpProjector:
     def __init__(self, w1, b1, w2, b2, act="gelu"):
         self.w1, self.b1, self.w2, self.b2, self.act = w1, b1, w2, b2, act
 
-    def __call__(self, x):
-        h = ops.linear(x, self.w1, self.b1)
+    def out_tokens(self, n: int) -> int:
+        return n
+
+    def __call__(self, x):                                   # [N, S, C] -> [N, S, H]
+        N, S, C = x.shape
+        h = ops.linear(x.reshape(N * S, C), self.w1, self.b1)
         h = F.gelu(h)
-        return ops.linear(h, self.w2, self.b2)
+        return ops.linear(h, self.w2, self.b2).view(N, S, -1)
 
 
 class _LinearProjector:
     def __init__(self, w, b):
         self.w, self.b = w, b
 
+    def out_tokens(self, n: int) -> int:
+        return n
+
     def __call__(self, x):
-        return ops.linear(x, self.w, self.b)
+        N, S, C = x.shape
+        return ops.linear(x.reshape(N * S, C), self.w, self.b).view(N, S, -1)
+
+
+class _PixelShuffleProjector:
+    """Idefics3 connector: fold every ``scale x scale`` neighbourhood of patches into the channel dimension
+    (row-major inside the neighbourhood), then one bias-free linear layer."""
+
+    def __init__(self, w, scale: int):
+        self.w, self.scale = w, int(scale)
+
+    def out_tokens(self, n: int) -> int:
+        return n // (self.scale ** 2)
+
+    def __call__(self, x):
+        N, S, C = x.shape
+        side, f = int(round(math.sqrt(S))), self.scale
+        x = x.view(N, side // f, f, side // f, f, C).permute(0, 1, 3, 2, 4, 5)      # [N, h', w', fh, fw, C]
+        x = x.reshape(N * (side // f) ** 2, f * f * C)
+        return ops.linear(x.contiguous(), self.w, None).view(N, (side // f) ** 2, -1)
+
+
+def _rms(x, w, eps):
+    v = x.float()
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+class _PerceiverProjector:
+    """Idefics2 connector: gated MLP to the text width, then ``depth`` blocks in which a fixed set of
+    latents attends (not causally) to the image rows and to itself."""
+
+    def __init__(self, w: Weights, prefix: str, pcfg: dict, eps: float):
+        g = w.get_tensor
+        mp = f"{prefix}.modality_projection"
+        self.mlp = (g(f"{mp}.gate_proj.weight"), g(f"{mp}.up_proj.weight"), g(f"{mp}.down_proj.weight"))
+        rp = f"{prefix}.perceiver_resampler"
+        self.latents = g(f"{rp}.latents")
+        self.heads, self.kv_heads = int(pcfg.get("resampler_n_heads", 16)), int(pcfg.get("num_key_value_heads", 4))
+        self.head_dim = int(pcfg.get("resampler_head_dim", 96))
+        self.eps = eps
+        self.layers = []
+        for i in range(int(pcfg.get("resampler_depth", 3))):
+            lp = f"{rp}.layers.{i}"
+            self.layers.append(dict(
+                ln_lat=g(f"{lp}.input_latents_norm.weight"), ln_ctx=g(f"{lp}.input_context_norm.weight"),
+                q=g(f"{lp}.self_attn.q_proj.weight"), k=g(f"{lp}.self_attn.k_proj.weight"),
+                v=g(f"{lp}.self_attn.v_proj.weight"), o=g(f"{lp}.self_attn.o_proj.weight"),
+                ln_post=g(f"{lp}.post_attention_layernorm.weight"),
+                mlp=(g(f"{lp}.mlp.gate_proj.weight"), g(f"{lp}.mlp.up_proj.weight"), g(f"{lp}.mlp.down_proj.weight"))))
+        self.norm = g(f"{rp}.norm.weight")
+
+    def out_tokens(self, n: int) -> int:
+        return self.latents.shape[0]
+
+    @staticmethod
+    def _gated(x, mlp):
+        return F.linear(F.silu(F.linear(x, mlp[0])) * F.linear(x, mlp[1]), mlp[2])
+
+    def __call__(self, x):                                   # [N, S, C] -> [N, latents, H]
+        ctx = self._gated(x, self.mlp)
+        N = ctx.shape[0]
+        lat = self.latents.to(ctx.dtype).unsqueeze(0).expand(N, -1, -1)
+        L = lat.shape[1]
+        for p in self.layers:
+            hl, hc = _rms(lat, p["ln_lat"], self.eps), _rms(ctx, p["ln_ctx"], self.eps)
+            kv_in = torch.cat([hc, hl], dim=1)
+            q = F.linear(hl, p["q"]).view(N, L, self.heads, self.head_dim).transpose(1, 2)
+            k = F.linear(kv_in, p["k"]).view(N, -1, self.kv_heads, self.head_dim).transpose(1, 2)
+            v = F.linear(kv_in, p["v"]).view(N, -1, self.kv_heads, self.head_dim).transpose(1, 2)
+            rep = self.heads // self.kv_heads
+            a = F.scaled_dot_product_attention(q, k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1))
+            lat = lat + F.linear(a.transpose(1, 2).reshape(N, L, -1), p["o"])
+            lat = lat + self._gated(_rms(lat, p["ln_post"], self.eps), p["mlp"])
+        return _rms(lat, self.norm, self.eps)
 
 
 def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, tokenizer, speculate, kv_cache_dtype,
@@ -246,7 +330,12 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
     from ..parallel.peer import make_comm
 
     mt = cfg.model_type
-    weights = Weights(weight_files(path), device, dtype, process_group=process_group, loader=loader)
+    # the same architectures are published with the language model under `language_model.model.*` or
+    # `model.language_model.*`, and the Idefics text model has no inner `model.` level
+    renames = [("language_model.model.", "model.language_model."), ("language_model.lm_head", "lm_head"),
+               ("vision_tower.", "model.vision_tower."), ("multi_modal_projector.", "model.multi_modal_projector."),
+               ("model.text_model.model.", "model.text_model.")]
+    weights = Weights(weight_files(path), device, dtype, process_group=process_group, loader=loader, renames=renames)
     text_cfg = cfg.text_config()
     vis = dict(cfg.get("vision_config") or {})
     if mt in ("llava_next", "llava"):
@@ -273,9 +362,24 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
         # decoder here scales only the rows it embeds itself.
         prefix, scale = "language_model", 1.0
         image_token = int(cfg.get("image_token_index", 257152))
+    elif mt in ("idefics2", "idefics3"):
+        vis.setdefault("image_size", 364 if mt == "idefics3" else 980)
+        vis.setdefault("patch_size", 14)
+        vis.setdefault("hidden_act", "gelu_pytorch_tanh")
+        tower = VisionTower(vis, weights, "model.vision_model", "siglip", feature_layer=-1)
+        if mt == "idefics3":
+            projector = _PixelShuffleProjector(weights.get_tensor("model.connector.modality_projection.proj.weight"),
+                                               int(cfg.get("scale_factor", 2)))
+        else:
+            pcfg = dict(cfg.get("perceiver_config") or {})
+            projector = _PerceiverProjector(weights, "model.connector", pcfg,
+                                            float(pcfg.get("rms_norm_eps", text_cfg.get("rms_norm_eps", 1e-6))))
+        drop_cls = False
+        prefix, scale = "model.text_model", 1.0
+        image_token = int(cfg.get("image_token_id", 32001 if mt == "idefics2" else 128257))
     else:
         raise NotImplementedError(f"vision-language model type {mt} has no native runner yet "
-                                  "(llava / llava_next / paligemma are covered)")
+                                  "(llava / llava_next / paligemma / idefics2 / idefics3 are covered)")
     hidden = int(text_cfg.get("hidden_size"))
     comm = make_comm(process_group, rank, world, device, hidden, int(max_prefill_tokens or 4096))
     model = CausalDecoder(text_cfg, weights, comm=comm, prefix=prefix)

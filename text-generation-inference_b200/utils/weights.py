@@ -199,6 +199,7 @@ class Weights:
         aliases: Optional[Dict[str, List[str]]] = None,
         prefix: Optional[str] = None,
         loader=None,
+        renames: Optional[List[Tuple[str, str]]] = None,
     ):
         self._handles: List[SafetensorsFile] = []
         self.routing: Dict[str, int] = {}
@@ -214,6 +215,9 @@ class Weights:
                     )
                 self.routing[k] = idx
         self.aliases = aliases or {}
+        # (old prefix, new prefix) pairs: a name that starts with the old prefix is also looked up under the
+        # new one (checkpoints of one architecture published under different module layouts)
+        self.renames = list(renames or [])
         self.device = torch.device(device)
         self.dtype = dtype
         self.process_group = process_group or ProcessGroupView()
@@ -229,6 +233,9 @@ class Weights:
         names = [name]
         if self.prefix:
             names.append(f"{self.prefix}.{name}")
+        for old, new in self.renames:
+            if name.startswith(old):
+                names.append(new + name[len(old):])
         return names
 
     def resolve(self, name: str) -> Tuple[SafetensorsFile, str]:
