@@ -247,6 +247,17 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     const uint32_t side = static_cast<uint32_t>(num("image_size", 336) / num("patch_size", 14));
     return side * side;
   }
+  if (mt == "idefics2") {
+    // perceiver resampler: a fixed number of latents per image
+    const json::Value& pc = config.has("perceiver_config") ? config["perceiver_config"] : vis;
+    return pc.is_object() && pc.has("resampler_n_latents") ? static_cast<uint32_t>(pc["resampler_n_latents"].as_double()) : 64;
+  }
+  if (mt == "idefics3") {
+    // pixel shuffle folds scale x scale patches of the global view into one row
+    const uint32_t side = static_cast<uint32_t>(num("image_size", 364) / num("patch_size", 14));
+    const uint32_t f = config.has("scale_factor") ? static_cast<uint32_t>(config["scale_factor"].as_double()) : 2;
+    return f ? (side / f) * (side / f) : side * side;
+  }
   return 0;
 }
 
