@@ -49,6 +49,8 @@ class ForwardMeta:
     lm_head_indices: Optional[torch.Tensor] = None   # rows of the hidden state that need logits
     inputs_embeds: Optional[torch.Tensor] = None     # overrides the embedding lookup (VLM)
     adapter_data: Optional[object] = None            # LoRA batch metadata
+    rope_cos_sin: Optional[torch.Tensor] = None      # [T, rot_dim] rotary rows of this step (multi-axis positions)
+    rope_rows: Optional[torch.Tensor] = None         # [T] = arange(T): row of `rope_cos_sin` per token
 
 
 class Norm:
@@ -227,7 +229,10 @@ class Attention:
             # to the next one; the rotary part stays at the front and the scale is that of the true dimension
             T_ = qkv.shape[0]
             qkv = torch.nn.functional.pad(qkv.view(T_, d.num_heads + 2 * d.num_kv_heads, D), (0, Dp - D)).view(T_, -1)
-        q = ops.rope_and_cache(qkv, meta.positions, rotary.cos_sin, meta.slots, k_cache, v_cache,
+        rope_pos, rope_tab = meta.positions, rotary.cos_sin
+        if meta.rope_cos_sin is not None and rotary.mrope_section:
+            rope_pos, rope_tab = meta.rope_rows, meta.rope_cos_sin     # rows prepared per token (Qwen2-VL)
+        q = ops.rope_and_cache(qkv, rope_pos, rope_tab, meta.slots, k_cache, v_cache,
                                d.num_heads, d.num_kv_heads, Dp, rotary.rot_dim, rotary.neox,
                                self.k_scale, self.v_scale)
         attn = ops.paged_attention(q, k_cache, v_cache, meta.block_tables, meta.cu_seqlens_q, meta.kv_lens,

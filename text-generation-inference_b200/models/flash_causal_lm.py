@@ -359,7 +359,9 @@ class FlashCausalLM(Model):
                 toks = [s.ids[-1]] + s.speculative_ids
                 start = len(s.ids) - 1
             input_ids[t:t + n] = toks
-            positions[t:t + n] = np.arange(start, start + n, dtype=np.int32)
+            # `pos_delta`: offset between rotary position and token index after a prompt with images (Qwen2-VL)
+            pos0 = start if s.prefilling else start + getattr(s, "pos_delta", 0)
+            positions[t:t + n] = np.arange(pos0, pos0 + n, dtype=np.int32)
             slots[t:t + n] = s.slots[start:start + n]
             cu[i + 1] = t + n
             kv_lens[i] = start + n

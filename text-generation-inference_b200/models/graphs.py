@@ -143,7 +143,7 @@ class DecodeGraphs:
         for i, s in enumerate(seqs):
             p = len(s.ids) - 1
             ids[i] = s.ids[-1]
-            pos[i] = p
+            pos[i] = p + getattr(s, "pos_delta", 0)
             slots[i] = s.slots[p]
             kv[i] = p + 1
             nb = len(s.blocks)

@@ -334,7 +334,10 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
     # `model.language_model.*`, and the Idefics text model has no inner `model.` level
     renames = [("language_model.model.", "model.language_model."), ("language_model.lm_head", "lm_head"),
                ("vision_tower.", "model.vision_tower."), ("multi_modal_projector.", "model.multi_modal_projector."),
-               ("model.text_model.model.", "model.text_model.")]
+               ("model.text_model.model.", "model.text_model."),
+               ("model.language_model.model.", "model.language_model."),
+               # Qwen2-VL as first published: language model at the top level, tower under `visual.`
+               ("model.language_model.model.", "model."), ("model.visual.", "visual.")]
     weights = Weights(weight_files(path), device, dtype, process_group=process_group, loader=loader, renames=renames)
     text_cfg = cfg.text_config()
     vis = dict(cfg.get("vision_config") or {})
@@ -362,6 +365,15 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
         # decoder here scales only the rows it embeds itself.
         prefix, scale = "language_model", 1.0
         image_token = int(cfg.get("image_token_index", 257152))
+    elif mt in ("qwen2_vl",):
+        from .qwen2_vl import load_qwen2_vl
+
+        hidden = int(text_cfg.get("hidden_size"))
+        comm = make_comm(process_group, rank, world, device, hidden, int(max_prefill_tokens or 4096))
+        runner = load_qwen2_vl(path, cfg, weights, comm, rank, world, dtype, device, tokenizer, speculate,
+                               kv_cache_dtype, max_prefill_tokens)
+        weights.close()
+        return runner
     elif mt in ("idefics2", "idefics3"):
         vis.setdefault("image_size", 364 if mt == "idefics3" else 980)
         vis.setdefault("patch_size", 14)

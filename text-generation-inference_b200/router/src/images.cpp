@@ -1,5 +1,7 @@
 #include "images.hpp"
 
+#include <cmath>
+
 #include <arpa/inet.h>
 #include <netdb.h>
 #include <sys/socket.h>
@@ -232,8 +234,6 @@ Fetched fetch(const std::string& url, size_t max_bytes) {
 }
 
 uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t height) {
-  (void)width;
-  (void)height;
   if (!config.is_object() || !config.has("vision_config")) return 0;
   const std::string mt = config.has("model_type") && config["model_type"].is_string() ? config["model_type"].as_string() : "";
   const json::Value& vis = config["vision_config"];
@@ -246,6 +246,29 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     // the runner feeds the base-resolution view: one feature row per patch
     const uint32_t side = static_cast<uint32_t>(num("image_size", 336) / num("patch_size", 14));
     return side * side;
+  }
+  if (mt == "qwen2_vl") {
+    // dynamic resolution: both sides rounded to multiples of patch * merge inside the pixel budget; one row
+    // per merge x merge block of patches, plus the vision-start / vision-end tokens the runner adds
+    const double patch = num("patch_size", 14), merge = num("spatial_merge_size", 2);
+    const double factor = patch * merge;
+    const double min_px = num("min_pixels", 56.0 * 56.0), max_px = num("max_pixels", 14.0 * 14.0 * 4.0 * 1280.0);
+    const double H = height, W = width;
+    double h = std::max(factor, std::nearbyint(H / factor) * factor);
+    double w = std::max(factor, std::nearbyint(W / factor) * factor);
+    if (h * w > max_px) {
+      const double beta = std::sqrt(H * W / max_px);
+      h = std::max(factor, std::floor(H / beta / factor) * factor);
+      w = std::max(factor, std::floor(W / beta / factor) * factor);
+    } else if (h * w < min_px) {
+      const double beta = std::sqrt(min_px / (H * W));
+      h = std::ceil(H * beta / factor) * factor;
+      w = std::ceil(W * beta / factor) * factor;
+    }
+    uint32_t n = static_cast<uint32_t>((h / factor) * (w / factor));
+    if (config.has("vision_start_token_id")) ++n;
+    if (config.has("vision_end_token_id")) ++n;
+    return n;
   }
   if (mt == "idefics2") {
     // perceiver resampler: a fixed number of latents per image

@@ -92,7 +92,8 @@ class RotaryTable:
         rs = getattr(config, "rope_scaling", None) or getattr(config, "rope_parameters", None)
         if isinstance(rs, dict) and isinstance(rs.get("full_attention"), dict):
             rs = rs["full_attention"]      # per-layer-type parameters (Gemma-3): the global layers' entry
-        if isinstance(rs, dict) and rs.get("rope_type", rs.get("type")) in (None, "default") and "factor" not in rs:
+        if (isinstance(rs, dict) and rs.get("rope_type", rs.get("type")) in (None, "default") and "factor" not in rs
+                and "mrope_section" not in rs):
             rs = None
         env_type = os.environ.get("ROPE_SCALING")
         if env_type:
@@ -150,6 +151,15 @@ class RotaryTable:
             else:
                 raise NotImplementedError(f"rope scaling type {kind} is not implemented")
         return cls(cls._table(inv_freq, max_positions, position_scale, mscale), dim, neox, mrope_section)
+
+    def mrope_rows(self, pos3: torch.Tensor) -> torch.Tensor:
+        """Rows ``[T, rot_dim]`` for three position streams ``[3, T]`` (time, height, width): frequency ``d``
+        follows the stream its ``mrope_section`` assigns it to (``layers/rotary.py:563-602`` in the reference)."""
+        h = self.rot_dim // 2
+        owner = torch.repeat_interleave(torch.arange(len(self.mrope_section)), torch.tensor(self.mrope_section))[:h]
+        owner = torch.cat([owner, owner]).to(self.cos_sin.device)                    # cos half, sin half
+        rows = self.cos_sin[pos3.long()]                                              # [3, T, rot_dim]
+        return torch.gather(rows, 0, owner.view(1, 1, -1).expand(1, rows.shape[1], -1))[0].contiguous()
 
     def lookup(self, positions: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         cs = self.cos_sin[positions.long()]
