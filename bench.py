@@ -45,7 +45,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--model", default="llama70b-fp8", choices=["llama70b-fp8", "llama8b-bf16", "tiny"])
+    ap.add_argument("--model", default="llama70b-fp8", choices=["llama70b-fp8", "llama8b-bf16", "mixtral-bf16", "tiny"])
     ap.add_argument("--concurrency", type=int, default=256)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--output-len", type=int, default=512)
@@ -110,6 +110,10 @@ def model_config(args):
         cfg, fp8, kv_fp8 = syn.llama3_70b_config(), True, True
     elif args.model == "llama8b-bf16":
         cfg, fp8, kv_fp8 = syn.llama3_8b_config(), False, False
+    elif args.model == "mixtral-bf16":
+        # Mixtral-8x7B shape; with N > 1 the experts are placed whole on the ranks (expert parallel), attention
+        # stays tensor parallel
+        cfg, fp8, kv_fp8 = syn.mixtral_8x7b_config(), False, False
     else:
         cfg = syn.llama_config(hidden=1024, layers=4, heads=8, kv_heads=2, intermediate=2048, vocab=32000, max_pos=8192)
         cfg["quantization_config"] = {"quant_method": "fp8", "weight_block_size": [128, 128]}

@@ -324,6 +324,80 @@ rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__
   }
 }
 
+// Vector form for the common layout (NeoX halves, rotary over the whole head, D a multiple of 16): a work
+// item is 8 consecutive elements of the first half of a head together with their partners in the
+// second half, so every access is 16 bytes (8 bytes into an e4m3 cache) and the table rows are read
+// as float4.  Same arithmetic, element by element, as the scalar kernel above.
+template <bool FP8_CACHE>
+__global__ void __launch_bounds__(128)
+rope_cache_vec_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                      const float* __restrict__ cos_sin, const int* __restrict__ slots,
+                      __nv_bfloat16* __restrict__ q_out, void* __restrict__ k_cache, void* __restrict__ v_cache,
+                      const float* __restrict__ k_scale, const float* __restrict__ v_scale, int Hq, int Hkv, int D,
+                      long long num_slots, int max_pos) {
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
+  const int t = blockIdx.x;
+  const int pos = min(max(positions[t], 0), max_pos - 1);
+  const long long slot = slots[t];
+  const bool slot_ok = slot >= 0 && slot < num_slots;   // self-check: never write outside the cache
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * (Hq + 2 * Hkv) * D;
+  const float* cs = cos_sin + static_cast<size_t>(pos) * D;
+  const int half = D / 2;
+  const int per_head = D / 16;
+  const int total = (Hq + 2 * Hkv) * per_head;
+  for (int w = threadIdx.x; w < total; w += blockDim.x) {
+    const int h = w / per_head, c = w - h * per_head;
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(src + h * D + 8 * c), a);
+    unpack8(*reinterpret_cast<const bf16x8*>(src + h * D + half + 8 * c), b);
+    if (h < Hq + Hkv) {
+      const float4 c0 = *reinterpret_cast<const float4*>(cs + 8 * c), c1 = *reinterpret_cast<const float4*>(cs + 8 * c + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(cs + half + 8 * c);
+      const float4 s1 = *reinterpret_cast<const float4*>(cs + half + 8 * c + 4);
+      const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float r0 = a[j] * cc[j] - b[j] * ss[j];
+        const float r1 = b[j] * cc[j] + a[j] * ss[j];
+        a[j] = r0;
+        b[j] = r1;
+      }
+    }
+    if (h < Hq) {
+      __nv_bfloat16* q = q_out + (static_cast<size_t>(t) * Hq + h) * D;
+      *reinterpret_cast<bf16x8*>(q + 8 * c) = pack8(a);
+      *reinterpret_cast<bf16x8*>(q + half + 8 * c) = pack8(b);
+    } else if (slot_ok) {
+      const bool is_k = h < Hq + Hkv;
+      const int kvh = is_k ? h - Hq : h - Hq - Hkv;
+      const size_t off = (static_cast<size_t>(slot) * Hkv + kvh) * D;
+      if (FP8_CACHE) {
+        const float* sc = is_k ? k_scale : v_scale;
+        const float scv = sc != nullptr ? sc[kvh] : 1.f;
+        __align__(8) uint8_t qa[8];
+        __align__(8) uint8_t qb[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // rotate in bf16 precision first (what a bf16 cache would hold), then quantise
+          qa[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(
+              fminf(fmaxf(round_bf16(a[j]) / scv, -kFp8Max), kFp8Max), __NV_SATFINITE, __NV_E4M3));
+          qb[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(
+              fminf(fmaxf(round_bf16(b[j]) / scv, -kFp8Max), kFp8Max), __NV_SATFINITE, __NV_E4M3));
+        }
+        uint8_t* dst = static_cast<uint8_t*>(is_k ? k_cache : v_cache) + off;
+        *reinterpret_cast<uint2*>(dst + 8 * c) = *reinterpret_cast<const uint2*>(qa);
+        *reinterpret_cast<uint2*>(dst + half + 8 * c) = *reinterpret_cast<const uint2*>(qb);
+      } else {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_k ? k_cache : v_cache) + off;
+        *reinterpret_cast<bf16x8*>(dst + 8 * c) = pack8(a);
+        *reinterpret_cast<bf16x8*>(dst + half + 8 * c) = pack8(b);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
@@ -615,6 +689,22 @@ int tgi_rope_cache(const void* qkv, const int* positions, const float* cos_sin, 
                    int D, int rot, int neox, long long num_slots, int fp8_cache, int max_pos, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (D % 2 != 0 || rot % 2 != 0 || rot > D || max_pos < 1) return -10;
+  const bool aligned = (reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                        reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                        reinterpret_cast<uintptr_t>(cos_sin)) % 16 == 0;
+  if (neox && rot == D && D % 16 == 0 && aligned) {
+    const int items = (Hq + 2 * Hkv) * (D / 16);
+    const int threads = items >= 128 ? 128 : (items >= 64 ? 64 : 32);
+    if (fp8_cache)
+      tgi::launch(rope_cache_vec_kernel<true>, dim3(T), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(qkv),
+                  positions, cos_sin, slots, static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale, v_scale, Hq,
+                  Hkv, D, num_slots, max_pos);
+    else
+      tgi::launch(rope_cache_vec_kernel<false>, dim3(T), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(qkv),
+                  positions, cos_sin, slots, static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale, v_scale, Hq,
+                  Hkv, D, num_slots, max_pos);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  }
   if (fp8_cache)
     tgi::launch(rope_cache_kernel<true>, dim3(T), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(qkv), positions, cos_sin, slots,
                                                    static_cast<__nv_bfloat16*>(q_out), k_cache, v_cache, k_scale,
