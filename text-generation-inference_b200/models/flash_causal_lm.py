@@ -410,7 +410,10 @@ class FlashCausalLM(Model):
 
         use_graph = (self.graphs is not None and not batch.prefilling and batch.speculate == 0
                      and self.graphs.supports(batch)
-                     and not (getattr(self, "lora", None) is not None and any(s.adapter_index > 0 for s in seqs)))
+                     # adapters ride the graphs through the LoRA kernels on one GPU; with tensor parallelism
+                     # the row-parallel targets need a collective between the two kernels and stay eager
+                     and not (getattr(self, "lora", None) is not None and self.world_size > 1
+                              and any(s.adapter_index > 0 for s in seqs)))
         if use_graph:
             logits, row_owner = self.graphs.run(batch, counts)
         else:

@@ -44,7 +44,8 @@ class _Bucket:
         self.off_cu = self.off_slots + seg(bs)
         self.off_kv = self.off_cu + seg(bs + 1)
         self.off_bt = self.off_kv + seg(bs)
-        self.total = self.off_bt + seg(bs * max_blocks)
+        self.off_ad = self.off_bt + seg(bs * max_blocks)     # LoRA adapter index per row (0 = none)
+        self.total = self.off_ad + seg(bs)
         self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=True)
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=dev)
@@ -63,6 +64,7 @@ class _Bucket:
             max_kv=runner_max_kv(runner),
             lm_head_indices=None,
         )
+        self.token_adapter = d[self.off_ad:self.off_ad + bs]
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None          # full logits [bs, V] (gathered-head graphs)
         self.local_logits: Optional[torch.Tensor] = None    # vocabulary shard [bs, V / tp] (local-head graphs)
@@ -82,15 +84,22 @@ class DecodeGraphs:
         self.max_blocks = math.ceil(self.max_total_tokens / runner.block_size)
         self.sizes = buckets or configured_buckets()
         self.buckets: Dict[int, _Bucket] = {}
+        # graphs whose forward includes the multi-adapter LoRA kernels; captured on first use of a size, so
+        # batches without adapters never pay for the extra launches
+        self.lora_buckets: Dict[int, _Bucket] = {}
         self.pool = None
 
     def capture_all(self):
         for bs in sorted(self.sizes, reverse=True):
             self.capture(bs)
 
-    def capture(self, bs: int):
+    def capture(self, bs: int, lora: bool = False):
         r = self.runner
         b = _Bucket(r, bs, self.max_blocks, self.pool)
+        if lora:
+            from ..utils.adapter import LoraBatchData
+
+            b.meta.adapter_data = LoraBatchData.static(r.lora, b.token_adapter)
         # warm-up run outside capture: lazy kernel attributes and persistent scratch get set up here
         torch.cuda.synchronize(r.device)
         r.model.forward(b.meta, r.kv_cache)
@@ -118,7 +127,7 @@ class DecodeGraphs:
             self.pool = g.pool()
         torch.cuda.synchronize(r.device)
         b.graph = g
-        self.buckets[bs] = b
+        (self.lora_buckets if lora else self.buckets)[bs] = b
 
     def supports(self, batch) -> bool:
         n = len(batch)
@@ -133,7 +142,10 @@ class DecodeGraphs:
         seqs = batch.seqs
         n = len(seqs)
         bs = min(k for k in self.buckets if k >= n)
-        b = self.buckets[bs]
+        lora = getattr(self.runner, "lora", None) is not None and any(s.adapter_index > 0 for s in seqs)
+        if lora and bs not in self.lora_buckets:
+            self.capture(bs, lora=True)
+        b = self.lora_buckets[bs] if lora else self.buckets[bs]
         h = b.host_np
         ids = h[b.off_ids:b.off_ids + bs]
         pos = h[b.off_pos:b.off_pos + bs]
@@ -148,6 +160,10 @@ class DecodeGraphs:
             kv[i] = p + 1
             nb = len(s.blocks)
             bt[i, :nb] = s.blocks
+        if lora:
+            ad = h[b.off_ad:b.off_ad + bs]
+            ad[:n] = [s.adapter_index for s in seqs]
+            ad[n:] = 0
         if n < bs:
             ids[n:] = 0
             pos[n:] = 0

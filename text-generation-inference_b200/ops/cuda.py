@@ -50,7 +50,8 @@ def load():
     _LIB = ctypes.CDLL(str(_LIB_PATH))
     for name in ("tgi_gemm_bf16", "tgi_gemm_fp8_block", "tgi_norm", "tgi_act_mul", "tgi_quant_act",
                  "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention",
-                 "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status"):
+                 "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status", "tgi_lora_shrink",
+                 "tgi_lora_expand"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
     wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
@@ -414,3 +415,25 @@ def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu"):
         out.index_add_(0, tok[sl], y.float() * wflat[sl].unsqueeze(1))
         start += c
     return out.to(x.dtype)
+
+
+# ---- multi-adapter LoRA ------------------------------------------------------------------------
+def lora_shrink(x: torch.Tensor, a_ptrs: torch.Tensor, ranks: torch.Tensor, token_adapter: torch.Tensor,
+                rmax: int) -> torch.Tensor:
+    """``v[t] = A_{adapter(t)} x[t]`` in fp32, ``[T, rmax]`` (zero rows for tokens without adapter)."""
+    T, H = x.shape
+    v = torch.empty(T, rmax, dtype=torch.float32, device=x.device)
+    _check(load().tgi_lora_shrink(_ptr(x.contiguous()), _ptr(a_ptrs), _ptr(ranks), _ptr(token_adapter), _ptr(v),
+                                  c_int(T), c_int(H), c_int(rmax), _stream()), "lora_shrink")
+    return v
+
+
+def lora_expand(v: torch.Tensor, b_ptrs: torch.Tensor, ranks: torch.Tensor, scales: torch.Tensor,
+                token_adapter: torch.Tensor, out: torch.Tensor, col0: int, ncols: int):
+    """``out[t, col0:col0+ncols] += scale * B_{adapter(t)} v[t]`` in place (``out`` bf16, rows contiguous)."""
+    T, rmax = v.shape
+    if out.stride(1) != 1:
+        raise KernelError("lora_expand needs unit stride along the columns of `out`")
+    _check(load().tgi_lora_expand(_ptr(v), _ptr(b_ptrs), _ptr(ranks), _ptr(scales), _ptr(token_adapter), _ptr(out),
+                                  c_ll(out.stride(0)), c_int(col0), c_int(T), c_int(ncols), c_int(rmax), _stream()),
+           "lora_expand")

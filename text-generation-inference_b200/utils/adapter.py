@@ -199,18 +199,44 @@ def merge_adapters(adapters: List[LoraAdapter], weights: List[float], merged_id:
 
 
 class LoraBatchData:
-    """Adapter routing of one forward pass: which rows of the ragged batch use which adapter."""
+    """Adapter routing of one forward pass: which rows of the ragged batch use which adapter.
+
+    On CUDA (bf16) every target projection is two kernel launches for the whole batch
+    (``ops/csrc/lora_sm100.cu``: shrink to ``[T, r]``, expand into the output in place) driven by a
+    per-row adapter index; elsewhere the rows are grouped by adapter and go through plain matmuls."""
 
     def __init__(self, manager: "LoraManager", token_adapter: np.ndarray, device):
         self.manager = manager
         self.groups: List[Tuple[int, torch.Tensor]] = []
+        self.token_adapter = None
+        if torch.device(device).type == "cuda":
+            self.token_adapter = torch.from_numpy(np.ascontiguousarray(token_adapter, dtype=np.int32)).to(device)
         for idx in np.unique(token_adapter):
             if idx <= 0:
                 continue
             rows = np.nonzero(token_adapter == idx)[0]
             self.groups.append((int(idx), torch.from_numpy(rows).to(device=device, dtype=torch.long)))
 
+    @classmethod
+    def static(cls, manager: "LoraManager", token_adapter: torch.Tensor) -> "LoraBatchData":
+        """Routing that reads the adapter index of every row from a fixed device tensor (CUDA-graph decode:
+        the tensor is rewritten before each replay)."""
+        self = cls.__new__(cls)
+        self.manager, self.groups, self.token_adapter = manager, [], token_adapter
+        return self
+
     def _apply(self, layer: int, proj: str, x: torch.Tensor, out: torch.Tensor, col0: int, reduce_group=None):
+        if self.token_adapter is not None and x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
+            tab = self.manager.table(layer, proj, x.device)
+            if tab is None:
+                return
+            from ..ops import cuda as K
+
+            v = K.lora_shrink(x, tab.a_ptrs, tab.ranks, self.token_adapter, tab.rmax)
+            if reduce_group is not None:
+                pdist.all_reduce(v, reduce_group)
+            K.lora_expand(v, tab.b_ptrs, tab.ranks, tab.scales, self.token_adapter, out, col0, tab.ncols)
+            return
         for idx, rows in self.groups:
             lora = self.manager.adapters[idx - 1].layers.get((layer, proj))
             if lora is None:
@@ -242,12 +268,52 @@ class LoraBatchData:
         return out
 
 
+@dataclass
+class LoraTable:
+    """Device-side pointer table of one (layer, projection): entry ``i`` describes adapter index ``i``
+    (entry 0 and adapters without this target are null / rank 0)."""
+
+    a_ptrs: torch.Tensor     # int64 [n + 1]
+    b_ptrs: torch.Tensor     # int64 [n + 1]
+    ranks: torch.Tensor      # int32 [n + 1]
+    scales: torch.Tensor     # fp32 [n + 1]
+    rmax: int
+    ncols: int
+    keep: list               # the contiguous A / B tensors the pointers refer to
+
+
 class LoraManager:
     def __init__(self, dims, process_group):
         self.dims, self.process_group = dims, process_group
         self.adapters: List[LoraAdapter] = []
+        self._tables: Dict[Tuple[int, str], Optional[LoraTable]] = {}
+
+    def table(self, layer: int, proj: str, device) -> Optional[LoraTable]:
+        key = (layer, proj)
+        if key not in self._tables:
+            n = len(self.adapters)
+            a_ptrs, b_ptrs, ranks, scales, keep = [0] * (n + 1), [0] * (n + 1), [0] * (n + 1), [0.0] * (n + 1), []
+            ncols = 0
+            for i, ad in enumerate(self.adapters, start=1):
+                lora = ad.layers.get(key)
+                if lora is None:
+                    continue
+                a, b = lora.a.contiguous(), lora.b.contiguous()
+                keep += [a, b]
+                a_ptrs[i], b_ptrs[i], ranks[i], scales[i] = a.data_ptr(), b.data_ptr(), a.shape[0], float(lora.scale)
+                ncols = max(ncols, b.shape[0])
+            if not keep or max(ranks) > 128:
+                self._tables[key] = None       # no adapter targets this projection (or rank beyond the kernels)
+            else:
+                self._tables[key] = LoraTable(
+                    torch.tensor(a_ptrs, dtype=torch.int64, device=device),
+                    torch.tensor(b_ptrs, dtype=torch.int64, device=device),
+                    torch.tensor(ranks, dtype=torch.int32, device=device),
+                    torch.tensor(scales, dtype=torch.float32, device=device), max(ranks), ncols, keep)
+        return self._tables[key]
 
     def add(self, adapter: LoraAdapter) -> int:
+        self._tables.clear()
         self.adapters.append(adapter)
         ADAPTER_TO_INDEX[adapter.adapter_id] = len(self.adapters)
         return len(self.adapters)
