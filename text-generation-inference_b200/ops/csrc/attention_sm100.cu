@@ -692,12 +692,14 @@ decode_kernel_v2(Params p) {
 // ------------------------------------------------------------------------------------------------
 __device__ int g_attn_status = 0;
 
-template <int CT_, int STAGES_>
+template <int CT_, int STAGES_, bool FP8_ = true>
 struct DecodeV3 {
   static constexpr int D = 128;
+  static constexpr bool FP8 = FP8_;                     // e4m3 pages (1 byte per element) or bf16 pages
+  static constexpr int EB = FP8_ ? 1 : 2;
   static constexpr int CT = CT_;                        // tokens per warp chunk (16 or 32)
   static constexpr int kStages = STAGES_;
-  static constexpr int kStageBytes = 2 * CT * D;        // K then V
+  static constexpr int kStageBytes = 2 * CT * D * EB;   // K then V; a 16-token group is EB boxes of 16 x 128 bytes
   static constexpr int kWarpRing = kStages * kStageBytes;
   static constexpr int kRingBytes = 4 * kWarpRing;
   static constexpr int kQBytes = 8 * D * 2;
@@ -709,7 +711,7 @@ struct DecodeV3 {
   static constexpr int kBytes = kOffBar + 4 * kStages * 8;
   static constexpr int kMergeBytes = 4 * 8 * D * 4 + 4 * 8 * 2 * 4;
   static constexpr int kFit = (227 * 1024) / (kBytes + 1024);
-  static constexpr int kCap = CT == 16 ? 4 : 3;            // 32-token chunks need about 146 registers per thread
+  static constexpr int kCap = (CT == 16 && FP8_) ? 4 : 3;  // 32-token chunks need about 146 registers per thread
   static constexpr int kMinBlocks = kFit > kCap ? kCap : kFit;
   static_assert(kMergeBytes <= kRingBytes, "merge scratch must fit in the rings");
   static_assert(CT == 16 || CT == 32, "chunks are one or two 16-token boxes");
@@ -738,7 +740,8 @@ __global__ void __launch_bounds__(128, S::kMinBlocks)
 decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
   tgi::pdl_wait();
   tgi::pdl_trigger();
-  constexpr int D = S::D, CT = S::CT, MT = CT / 16;
+  constexpr int D = S::D, CT = S::CT, MT = CT / 16, EB = S::EB;
+  constexpr bool FP8 = S::FP8;
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, j = lane & 3;
@@ -773,16 +776,17 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
   }
   __syncwarp();
 
-  // lanes 0..2*MT-1 each fetch one 16-token box: lane = 2 * box + (0: K, 1: V).  The block-table entry of
-  // chunk i+1 is read when chunk i is issued, so that no copy waits for a global load.
+  // lanes 0..2*MT*EB-1 each fetch one box of 16 tokens x 128 bytes: lane = 2 * box + (0: K, 1: V); with bf16
+  // pages a token row is two boxes (head dimensions 0-63 and 64-127).  The block-table entry of chunk i+1 is
+  // read when chunk i is issued, so that no copy waits for a global load.
   const int isv = lane & 1, box = lane >> 1;
   auto first_token = [&](int i) {
-    int t = t_lo + (c0 + warp + 4 * i) * CT + box * 16;
+    int t = t_lo + (c0 + warp + 4 * i) * CT + (box / EB) * 16;
     if (t >= L) t = (L - 1) & ~15;   // past the end: fetch the last group again (masked below)
     return t;
   };
   auto table_entry = [&](int i) {
-    if (i >= my_n || lane >= 2 * MT) return 0;
+    if (i >= my_n || lane >= 2 * MT * EB) return 0;
     return p.block_tables[static_cast<size_t>(b) * p.max_blocks + (first_token(i) >> p.bs_shift)];
   };
   int blk_next = table_entry(0);
@@ -794,14 +798,14 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
       sm100::mbar_arrive_expect_tx(&full[stg], S::kStageBytes);
     }
     __syncwarp();
-    if (lane < 2 * MT) {
+    if (lane < 2 * MT * EB) {
       const int row = (blk_next << p.bs_shift) + (first_token(i) & (p.block_size - 1));
-      sm100::tma_load_2d(ring + stg * S::kStageBytes + isv * (CT * D) + box * (16 * D), isv ? &tmV : &tmK, &full[stg],
-                         kvh * D, row);
+      sm100::tma_load_2d(ring + stg * S::kStageBytes + isv * (CT * D * EB) + box * 2048, isv ? &tmV : &tmK, &full[stg],
+                         kvh * D * EB + (box % EB) * 128, row);
     }
     blk_next = table_entry(i + 1);
   };
-  static_assert(2 * MT <= 32 && 2 * MT * 16 * D == S::kStageBytes, "a stage is MT boxes of K and MT of V");
+  static_assert(2 * MT * EB <= 32 && 2 * MT * EB * 2048 == S::kStageBytes, "a stage is MT*EB boxes of K and of V");
 #pragma unroll
   for (int s = 0; s < S::kStages - 1; ++s) issue(s);
 
@@ -811,27 +815,36 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row < G) {
       v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(q_row) * p.Hq + h0 + row) * D + cc * 8);
-      const __nv_bfloat162* bv = reinterpret_cast<const __nv_bfloat162*>(&v);
-      uint32_t o4[4];
+      if (FP8) {                                   // e4m3 K widens exactly to fp16: Q follows
+        const __nv_bfloat162* bv = reinterpret_cast<const __nv_bfloat162*>(&v);
+        uint32_t o4[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(bv[i]);
-        o4[i] = pack2<true>(f.x, f.y);
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(bv[i]);
+          o4[i] = pack2<true>(f.x, f.y);
+        }
+        v = make_uint4(o4[0], o4[1], o4[2], o4[3]);
       }
-      v = make_uint4(o4[0], o4[1], o4[2], o4[3]);
     }
     *reinterpret_cast<uint4*>(sQ + row * D + cc * 8) = v;
   }
   __syncthreads();
 
-  // B fragments of Q^T: for k-step (q, i) lane (head g, j) holds Q[g][64 q + 16 j + 4 i .. + 3]
-  uint32_t qb[2][4][2];
+  // B fragments of Q^T.  e4m3 pages: for k-step (q, i) lane (head g, j) holds Q[g][64 q + 16 j + 4 i .. + 3].
+  // bf16 pages: a 16-byte load of K is 8 dimensions = 2 k-steps, unit 4 q + j of the row: Q[g][8 (4 q + j) + 4 i .. + 3].
+  constexpr int NQ = FP8 ? 2 : 4, NI = FP8 ? 4 : 2;
+  uint32_t qb[NQ][NI][2];
 #pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    const uint4 lo = *reinterpret_cast<const uint4*>(sQ + g * D + 64 * q + 16 * j);
-    const uint4 hi = *reinterpret_cast<const uint4*>(sQ + g * D + 64 * q + 16 * j + 8);
-    qb[q][0][0] = lo.x; qb[q][0][1] = lo.y; qb[q][1][0] = lo.z; qb[q][1][1] = lo.w;
-    qb[q][2][0] = hi.x; qb[q][2][1] = hi.y; qb[q][3][0] = hi.z; qb[q][3][1] = hi.w;
+  for (int q = 0; q < NQ; ++q) {
+    if (FP8) {
+      const uint4 lo = *reinterpret_cast<const uint4*>(sQ + g * D + 64 * q + 16 * j);
+      const uint4 hi = *reinterpret_cast<const uint4*>(sQ + g * D + 64 * q + 16 * j + 8);
+      qb[q][0][0] = lo.x; qb[q][0][1] = lo.y; qb[q][1][0] = lo.z; qb[q][1][1] = lo.w;
+      qb[q][NI - 2][0] = hi.x; qb[q][NI - 2][1] = hi.y; qb[q][NI - 1][0] = hi.z; qb[q][NI - 1][1] = hi.w;
+    } else {
+      const uint4 lo = *reinterpret_cast<const uint4*>(sQ + g * D + 8 * (4 * q + j));
+      qb[q][0][0] = lo.x; qb[q][0][1] = lo.y; qb[q][1][0] = lo.z; qb[q][1][1] = lo.w;
+    }
   }
 
   // o[i]: dimensions 16 g + 2 i (elements 0, 1) and 16 g + 2 i + 1 (elements 2, 3) of heads 2j (0, 2) and 2j+1 (1, 3)
@@ -841,7 +854,7 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};   // heads 2j, 2j+1; l is this lane's share
   const float ksc = p.k_scale ? p.k_scale[kvh] : 1.f;
   const float vsc = p.v_scale ? p.v_scale[kvh] : 1.f;
-  const float raw_scale = p.scale * ksc;
+  const float raw_scale = p.scale * (FP8 ? ksc : 1.f);
   const float scale_log2 = raw_scale * kLog2e;
   const int rg = bitrev3(g);                      // token row (mod 8) of this lane's S^T rows
   const int rj0 = bitrev3(j), rj1 = bitrev3(j + 4);   // token rows (mod 8) of this lane's V loads
@@ -856,7 +869,7 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
     }
     done = i + 1;
     const uint8_t* sK = ring + (i % S::kStages) * S::kStageBytes;
-    const uint8_t* sV = sK + CT * D;
+    const uint8_t* sV = sK + CT * D * EB;
     const int tbase = t_lo + (c0 + warp + 4 * i) * CT;
 
     // ---- S^T = K Q^T (two accumulators per 16 tokens keep the dependent MMA chains short) ----
@@ -864,21 +877,36 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
       float s2[2][4];
-      const uint8_t* ra = sK + (mt * 16 + rg) * D;
-      const uint8_t* rb = ra + 8 * D;
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        s2[q][0] = s2[q][1] = s2[q][2] = s2[q][3] = 0.f;
-        const int off = ((4 * q + j) ^ rg) << 4;
-        const uint4 wa = *reinterpret_cast<const uint4*>(ra + off);
-        const uint4 wb = *reinterpret_cast<const uint4*>(rb + off);
-        const uint32_t a4[4] = {wa.x, wa.y, wa.z, wa.w}, b4[4] = {wb.x, wb.y, wb.z, wb.w};
+      for (int e = 0; e < 4; ++e) s2[0][e] = s2[1][e] = 0.f;
+      if (FP8) {
+        const uint8_t* ra = sK + (mt * 16 + rg) * D;
+        const uint8_t* rb = ra + 8 * D;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          uint32_t a[4];
-          cvt_e4m3x4(a4[k], a[0], a[2]);
-          cvt_e4m3x4(b4[k], a[1], a[3]);
-          mma16816<true>(s2[q], a, qb[q][k][0], qb[q][k][1]);
+        for (int q = 0; q < 2; ++q) {
+          const int off = ((4 * q + j) ^ rg) << 4;
+          const uint4 wa = *reinterpret_cast<const uint4*>(ra + off);
+          const uint4 wb = *reinterpret_cast<const uint4*>(rb + off);
+          const uint32_t a4[4] = {wa.x, wa.y, wa.z, wa.w}, b4[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint32_t a[4];
+            cvt_e4m3x4(a4[k], a[0], a[2]);
+            cvt_e4m3x4(b4[k], a[1], a[3]);
+            mma16816<true>(s2[q], a, qb[q % NQ][k % NI][0], qb[q % NQ][k % NI][1]);
+          }
+        }
+      } else {
+        // bf16 rows are two boxes of 128 bytes; unit 4 q + j of the row is unit (4 q + j) % 8 of box q / 2
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint8_t* ra = sK + ((mt * 2 + (q >> 1)) * 16 + rg) * 128;
+          const int off = ((4 * (q & 1) + j) ^ rg) << 4;
+          const uint4 wa = *reinterpret_cast<const uint4*>(ra + off);
+          const uint4 wb = *reinterpret_cast<const uint4*>(ra + 8 * 128 + off);
+          const uint32_t a0[4] = {wa.x, wb.x, wa.y, wb.y}, a1[4] = {wa.z, wb.z, wa.w, wb.w};
+          mma16816<false>(s2[q & 1], a0, qb[q % NQ][0][0], qb[q % NQ][0][1]);
+          mma16816<false>(s2[q & 1], a1, qb[q % NQ][1][0], qb[q % NQ][1][1]);
         }
       }
 #pragma unroll
@@ -936,8 +964,8 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
         rs[e & 1] += pv;
       }
       // contraction index of P V inside the 16 tokens: 2 g (token rho(g)) and 2 g + 1 (token rho(g) + 8)
-      *reinterpret_cast<uint32_t*>(sP + (2 * j) * S::kPPitch + mt * 16 + 2 * g) = pack2<true>(s[mt][0], s[mt][2]);
-      *reinterpret_cast<uint32_t*>(sP + (2 * j + 1) * S::kPPitch + mt * 16 + 2 * g) = pack2<true>(s[mt][1], s[mt][3]);
+      *reinterpret_cast<uint32_t*>(sP + (2 * j) * S::kPPitch + mt * 16 + 2 * g) = pack2<FP8>(s[mt][0], s[mt][2]);
+      *reinterpret_cast<uint32_t*>(sP + (2 * j + 1) * S::kPPitch + mt * 16 + 2 * g) = pack2<FP8>(s[mt][1], s[mt][3]);
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) l[r] = l[r] * alpha[r] + rs[r];
@@ -954,23 +982,44 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
     // ---- O^T += V^T P^T ----
 #pragma unroll
     for (int ks = 0; ks < MT; ++ks) {
-      const uint8_t* base = sV + ks * 16 * D;
-      const uint4 wa = *reinterpret_cast<const uint4*>(base + rj0 * D + ((g ^ rj0) << 4));         // k = 2j
-      const uint4 wb = *reinterpret_cast<const uint4*>(base + (rj0 + 8) * D + ((g ^ rj0) << 4));   // k = 2j + 1
-      const uint4 wc = *reinterpret_cast<const uint4*>(base + rj1 * D + ((g ^ rj1) << 4));         // k = 2j + 8
-      const uint4 wd = *reinterpret_cast<const uint4*>(base + (rj1 + 8) * D + ((g ^ rj1) << 4));   // k = 2j + 9
-      const uint32_t a4[4] = {wa.x, wa.y, wa.z, wa.w}, b4[4] = {wb.x, wb.y, wb.z, wb.w};
-      const uint32_t c4[4] = {wc.x, wc.y, wc.z, wc.w}, d4[4] = {wd.x, wd.y, wd.z, wd.w};
+      if (FP8) {
+        const uint8_t* base = sV + ks * 16 * D;
+        const uint4 wa = *reinterpret_cast<const uint4*>(base + rj0 * D + ((g ^ rj0) << 4));         // k = 2j
+        const uint4 wb = *reinterpret_cast<const uint4*>(base + (rj0 + 8) * D + ((g ^ rj0) << 4));   // k = 2j + 1
+        const uint4 wc = *reinterpret_cast<const uint4*>(base + rj1 * D + ((g ^ rj1) << 4));         // k = 2j + 8
+        const uint4 wd = *reinterpret_cast<const uint4*>(base + (rj1 + 8) * D + ((g ^ rj1) << 4));   // k = 2j + 9
+        const uint32_t a4[4] = {wa.x, wa.y, wa.z, wa.w}, b4[4] = {wb.x, wb.y, wb.z, wb.w};
+        const uint32_t c4[4] = {wc.x, wc.y, wc.z, wc.w}, d4[4] = {wd.x, wd.y, wd.z, wd.w};
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        // bytes 4x .. 4x+3 of the lane's 16 dimensions: (0, 1) feed o[2x], (2, 3) feed o[2x+1]
-        uint32_t a[4], a2[4];
-        cvt_e4m3x4(__byte_perm(a4[x], b4[x], 0x5140), a[0], a[1]);
-        cvt_e4m3x4(__byte_perm(c4[x], d4[x], 0x5140), a[2], a[3]);
-        cvt_e4m3x4(__byte_perm(a4[x], b4[x], 0x7362), a2[0], a2[1]);
-        cvt_e4m3x4(__byte_perm(c4[x], d4[x], 0x7362), a2[2], a2[3]);
-        mma16816<true>(o[2 * x], a, pb[2 * ks], pb[2 * ks + 1]);
-        mma16816<true>(o[2 * x + 1], a2, pb[2 * ks], pb[2 * ks + 1]);
+        for (int x = 0; x < 4; ++x) {
+          // bytes 4x .. 4x+3 of the lane's 16 dimensions: (0, 1) feed o[2x], (2, 3) feed o[2x+1]
+          uint32_t a[4], a2[4];
+          cvt_e4m3x4(__byte_perm(a4[x], b4[x], 0x5140), a[0], a[1]);
+          cvt_e4m3x4(__byte_perm(c4[x], d4[x], 0x5140), a[2], a[3]);
+          cvt_e4m3x4(__byte_perm(a4[x], b4[x], 0x7362), a2[0], a2[1]);
+          cvt_e4m3x4(__byte_perm(c4[x], d4[x], 0x7362), a2[2], a2[3]);
+          mma16816<true>(o[2 * x], a, pb[2 * ks], pb[2 * ks + 1]);
+          mma16816<true>(o[2 * x + 1], a2, pb[2 * ks], pb[2 * ks + 1]);
+        }
+      } else {
+        // bf16: the lane owns dimensions 8 g .. 8 g + 7 of each half of the head (unit g of both boxes);
+        // o[4 hf + x] collects dimensions 64 hf + 8 g + 2 x (elements 0, 1) and + 2 x + 1 (elements 2, 3)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const uint8_t* base = sV + (ks * 2 + hf) * 2048;
+          const uint4 wa = *reinterpret_cast<const uint4*>(base + rj0 * 128 + ((g ^ rj0) << 4));
+          const uint4 wb = *reinterpret_cast<const uint4*>(base + (rj0 + 8) * 128 + ((g ^ rj0) << 4));
+          const uint4 wc = *reinterpret_cast<const uint4*>(base + rj1 * 128 + ((g ^ rj1) << 4));
+          const uint4 wd = *reinterpret_cast<const uint4*>(base + (rj1 + 8) * 128 + ((g ^ rj1) << 4));
+          const uint32_t a4[4] = {wa.x, wa.y, wa.z, wa.w}, b4[4] = {wb.x, wb.y, wb.z, wb.w};
+          const uint32_t c4[4] = {wc.x, wc.y, wc.z, wc.w}, d4[4] = {wd.x, wd.y, wd.z, wd.w};
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const uint32_t a[4] = {__byte_perm(a4[x], b4[x], 0x5410), __byte_perm(a4[x], b4[x], 0x7632),
+                                   __byte_perm(c4[x], d4[x], 0x5410), __byte_perm(c4[x], d4[x], 0x7632)};
+            mma16816<false>(o[4 * hf + x], a, pb[2 * ks], pb[2 * ks + 1]);
+          }
+        }
       }
     }
     __syncwarp();   // the stage and the P tile are free for the next iteration
@@ -993,12 +1042,13 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
   float* mO = reinterpret_cast<float*>(smem);   // [4][8][D]
   float* mML = mO + 4 * 8 * D;                  // [4][8][2]
   {
-    float* r0 = mO + (warp * 8 + 2 * j) * D + 16 * g;
-    float* r1 = r0 + D;
+    // e4m3: the lane holds dimensions 16 g .. 16 g + 15; bf16: 8 g .. 8 g + 7 of each half of the head
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
-      *reinterpret_cast<float4*>(r0 + 4 * x) = make_float4(o[2 * x][0], o[2 * x][2], o[2 * x + 1][0], o[2 * x + 1][2]);
-      *reinterpret_cast<float4*>(r1 + 4 * x) = make_float4(o[2 * x][1], o[2 * x][3], o[2 * x + 1][1], o[2 * x + 1][3]);
+      float* r0 = mO + (warp * 8 + 2 * j) * D + (FP8 ? 16 * g + 4 * x : 64 * (x >> 1) + 8 * g + 4 * (x & 1));
+      float* r1 = r0 + D;
+      *reinterpret_cast<float4*>(r0) = make_float4(o[2 * x][0], o[2 * x][2], o[2 * x + 1][0], o[2 * x + 1][2]);
+      *reinterpret_cast<float4*>(r1) = make_float4(o[2 * x][1], o[2 * x][3], o[2 * x + 1][1], o[2 * x + 1][3]);
     }
     if (g == 0) {
       mML[(warp * 8 + 2 * j) * 2] = m[0];
@@ -1023,11 +1073,11 @@ decode_kernel_v3(Params p, const __grid_constant__ CUtensorMap tmK, const __grid
     }
     const int h = h0 + row;
     if (p.nsplit == 1) {
-      const float inv = ll > 0.f ? vsc / ll : 0.f;
+      const float inv = ll > 0.f ? (FP8 ? vsc : 1.f) / ll : 0.f;
       p.out[(static_cast<size_t>(q_row) * p.Hq + h) * D + col] = __float2bfloat16(acc * inv);
     } else {
       const size_t pi = (static_cast<size_t>(b) * p.Hq + h) * p.nsplit + split;
-      p.part_o[pi * D + col] = ll > 0.f ? acc * (vsc / ll) : 0.f;
+      p.part_o[pi * D + col] = ll > 0.f ? acc * ((FP8 ? vsc : 1.f) / ll) : 0.f;
       if (col == 0) {
         p.part_ml[pi * 2] = mm;
         p.part_ml[pi * 2 + 1] = ll;
@@ -1075,13 +1125,13 @@ bool decode_v3_enabled() {
 
 // Tensor map of one e4m3 K or V page pool viewed as [slots, Hkv * 128] bytes, box 16 slots x 128 bytes.
 // Pools live as long as the model, so the maps are cached by (device, pointer, geometry).
-const CUtensorMap* page_map(const void* cache, const Params& p) {
+const CUtensorMap* page_map(const void* cache, const Params& p, int eb) {
   struct Key {
     int dev;
     const void* ptr;
-    int blocks, bs, hkv;
+    int blocks, bs, hkv, eb;
     bool operator==(const Key& o) const {
-      return dev == o.dev && ptr == o.ptr && blocks == o.blocks && bs == o.bs && hkv == o.hkv;
+      return dev == o.dev && ptr == o.ptr && blocks == o.blocks && bs == o.bs && hkv == o.hkv && eb == o.eb;
     }
   };
   struct Hash {
@@ -1092,7 +1142,7 @@ const CUtensorMap* page_map(const void* cache, const Params& p) {
   };
   static std::mutex mu;
   static std::unordered_map<Key, CUtensorMap*, Hash> maps;
-  Key key{0, cache, p.num_blocks, p.block_size, p.Hkv};
+  Key key{0, cache, p.num_blocks, p.block_size, p.Hkv, eb};
   if (cudaGetDevice(&key.dev) != cudaSuccess) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
   auto it = maps.find(key);
@@ -1100,7 +1150,7 @@ const CUtensorMap* page_map(const void* cache, const Params& p) {
   void* raw = nullptr;
   if (posix_memalign(&raw, 64, sizeof(CUtensorMap)) != 0) return nullptr;
   CUtensorMap* m = static_cast<CUtensorMap*>(raw);
-  const uint64_t pitch = static_cast<uint64_t>(p.Hkv) * 128;
+  const uint64_t pitch = static_cast<uint64_t>(p.Hkv) * 128 * eb;   // bytes per slot: Hkv heads of 128 elements
   const uint64_t slots = static_cast<uint64_t>(p.num_blocks) * p.block_size;
   if (tgi::make_map_2d(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, cache, slots, pitch, pitch, 16, 128,
                        CU_TENSOR_MAP_SWIZZLE_128B) != 0) {
@@ -1119,8 +1169,8 @@ int launch_v3_cfg(const Params& p, int B, cudaStream_t stream) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess) return -2;
     set = true;
   }
-  const CUtensorMap* tk = page_map(p.k_cache, p);
-  const CUtensorMap* tv = page_map(p.v_cache, p);
+  const CUtensorMap* tk = page_map(p.k_cache, p, S::EB);
+  const CUtensorMap* tv = page_map(p.v_cache, p, S::EB);
   if (tk == nullptr || tv == nullptr) return -14;
   dim3 grid(p.Hkv, B, p.nsplit);
   tgi::launch(k, dim3(grid), dim3(128), S::kBytes, stream, p, *tk, *tv);
@@ -1134,6 +1184,7 @@ int launch_v3_cfg(const Params& p, int B, cudaStream_t stream) {
 
 // chunk size and ring depth of decode_kernel_v3; `TGI_B200_ATTN_V3_CFG` = "<tokens>x<stages>" picks another
 // of the compiled shapes
+template <bool FP8>
 int launch_v3(const Params& p, int B, cudaStream_t stream) {
   static const int cfg = [] {
     const char* v = std::getenv("TGI_B200_ATTN_V3_CFG");
@@ -1141,8 +1192,14 @@ int launch_v3(const Params& p, int B, cudaStream_t stream) {
     if (std::strcmp(v, "32x2") == 0) return 322;
     if (std::strcmp(v, "32x3") == 0) return 323;
     if (std::strcmp(v, "16x4") == 0) return 164;
+    if (std::strcmp(v, "16x2") == 0) return 162;
     return 163;
   }();
+  if (!FP8) {
+    // bf16 pages: a 16-token chunk is 8 KB, so two stages leave room for 3 CTAs (12 warps) per SM
+    if (cfg == 163) return launch_v3_cfg<DecodeV3<16, 3, false>>(p, B, stream);
+    return launch_v3_cfg<DecodeV3<16, 2, false>>(p, B, stream);
+  }
   if (cfg == 0) {
     // measured: 32-token chunks are 1-3 % faster on grids of many waves (256 sequences x 8 KV heads), 16-token
     // chunks with 16 warps per SM clearly faster on small grids (256 x 1 KV head: 29 us against 36 us)
@@ -1153,7 +1210,7 @@ int launch_v3(const Params& p, int B, cudaStream_t stream) {
     case 322: return launch_v3_cfg<DecodeV3<32, 2>>(p, B, stream);
     case 323: return launch_v3_cfg<DecodeV3<32, 3>>(p, B, stream);
     case 164: return launch_v3_cfg<DecodeV3<16, 4>>(p, B, stream);
-    default: return launch_v3_cfg<DecodeV3<16, 3>>(p, B, stream);   // 4 CTAs (16 warps) per SM: fastest measured
+    default: return launch_v3_cfg<DecodeV3<16, 3>>(p, B, stream);   // 4 CTAs (16 warps) per SM
   }
 }
 
@@ -1172,8 +1229,8 @@ int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
     tgi::launch(k, dim3(grid), dim3(128), smem, stream, p);
   } else if (B > 65535) {
     return -15;   // the batch index is grid dimension y
-  } else if (FP8 && D == 128 && p.Hq / p.Hkv <= 8 && p.block_size >= 16 && decode_v3_enabled()) {
-    return launch_v3(p, B, stream);
+  } else if (D == 128 && p.Hq / p.Hkv <= 8 && p.block_size >= 16 && decode_v3_enabled()) {
+    return launch_v3<FP8>(p, B, stream);
   } else {
     auto k = decode_kernel_v2<D, FP8>;
     constexpr int dsmem = DecodeSmem<D, FP8>::kBytes;
