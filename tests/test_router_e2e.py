@@ -39,6 +39,31 @@ def _get(port, path):
         return r.status, r.read().decode()
 
 
+def _start_collector():
+    """Minimal OTLP/HTTP collector: keeps the JSON bodies posted to /v1/traces."""
+    import http.server
+    import threading
+
+    collected = []
+
+    class Handler(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = self.rfile.read(int(self.headers.get("content-length", "0")))
+            if self.path == "/v1/traces":
+                collected.append(json.loads(body))
+            self.send_response(200)
+            self.send_header("content-length", "2")
+            self.end_headers()
+            self.wfile.write(b"{}")
+
+        def log_message(self, *a):
+            pass
+
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Handler)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    return collected, srv
+
+
 @pytest.fixture(scope="module")
 def stack(tmp_path_factory):
     from tgi_b200.router.build import build
@@ -54,9 +79,12 @@ def stack(tmp_path_factory):
     shard = subprocess.Popen([sys.executable, "-m", "tgi_b200.server.cli", "serve", str(d), "--uds-path", uds,
                               "--dtype", "float32"], env=env, cwd=ROOT)
     port = _free_port()
+    collected, collector = _start_collector()
     router = subprocess.Popen([str(router_bin), "--master-shard-uds-path", uds, "--tokenizer-name", str(d),
                                "--port", str(port), "--hostname", "127.0.0.1", "--max-input-tokens", "64",
                                "--max-total-tokens", "128", "--max-batch-prefill-tokens", "128",
+                               "--otlp-endpoint", f"http://127.0.0.1:{collector.server_address[1]}",
+                               "--otlp-service-name", "tgi-b200-test.router",
                                "--repo-root", ROOT], env=env, cwd=ROOT)
     try:
         deadline = time.time() + 120
@@ -70,7 +98,7 @@ def stack(tmp_path_factory):
                 time.sleep(0.3)
         else:
             raise RuntimeError("router did not come up")
-        yield {"port": port, "uds": uds}
+        yield {"port": port, "uds": uds, "otlp": collected}
     finally:
         for p in (router, shard):
             p.send_signal(signal.SIGTERM)
@@ -292,3 +320,33 @@ def test_kserve_routes(stack):
     assert st == 422
     with pytest.raises(urllib.error.HTTPError):
         _get(port, "/v2/nothing/here")
+
+
+def test_request_spans_reach_the_otlp_collector(stack):
+    import urllib.request
+
+    trace_id, parent = "4bf92f3577b34da6a3ce929d0e0e4736", "00f067aa0ba902b7"
+    req = urllib.request.Request(
+        f"http://127.0.0.1:{stack['port']}/generate",
+        data=json.dumps({"inputs": "traced", "parameters": {"max_new_tokens": 2}}).encode(),
+        headers={"content-type": "application/json", "traceparent": f"00-{trace_id}-{parent}-01"})
+    with urllib.request.urlopen(req, timeout=60) as r:
+        assert r.status == 200
+    deadline = time.time() + 10
+    found = None
+    while time.time() < deadline and found is None:
+        for doc in list(stack["otlp"]):
+            rs = doc["resourceSpans"][0]
+            assert rs["resource"]["attributes"][0]["value"]["stringValue"] == "tgi-b200-test.router"
+            for sp in rs["scopeSpans"][0]["spans"]:
+                if sp["traceId"] == trace_id:
+                    found = sp
+        time.sleep(0.2)
+    assert found is not None, "no span with the caller's trace id was exported"
+    assert found["parentSpanId"] == parent and found["name"] == "POST /generate" and len(found["spanId"]) == 16
+    assert int(found["endTimeUnixNano"]) > int(found["startTimeUnixNano"])
+    attrs = {a["key"]: a["value"] for a in found["attributes"]}
+    assert attrs["http.status_code"]["intValue"] == "200" and found["status"]["code"] == 1
+    # requests without a trace context start a new trace
+    assert any(sp["traceId"] != trace_id and "parentSpanId" not in sp
+               for doc in stack["otlp"] for sp in doc["resourceSpans"][0]["scopeSpans"][0]["spans"])

@@ -1,5 +1,7 @@
 #include "http.hpp"
 
+#include "trace.hpp"
+
 #include <arpa/inet.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
@@ -45,6 +47,7 @@ bool Response::write_all(const char* p, size_t n) {
 }
 
 bool Response::send(int status, const std::string& content_type, const std::string& body) {
+  status_ = status;
   started_ = true;
   std::string head = "HTTP/1.1 " + std::to_string(status) + " " + status_text(status) + "\r\n";
   head += "content-type: " + content_type + "\r\ncontent-length: " + std::to_string(body.size()) + "\r\n";
@@ -54,6 +57,7 @@ bool Response::send(int status, const std::string& content_type, const std::stri
 }
 
 bool Response::begin_stream(int status, const std::string& content_type) {
+  status_ = status;
   started_ = true;
   std::string head = "HTTP/1.1 " + std::to_string(status) + " " + status_text(status) + "\r\n";
   head += "content-type: " + content_type + "\r\ntransfer-encoding: chunked\r\ncache-control: no-cache\r\n";
@@ -227,11 +231,35 @@ void Server::connection(int fd) {
       continue;
     }
     auto it = routes_.find(req.method + " " + req.path);
+    // one server span per request; its parent is the caller's span when a valid `traceparent` came in
+    trace::Span span;
+    const bool traced = trace::exporter() != nullptr && it != routes_.end() && req.path != "/health" &&
+                        req.path != "/metrics";
+    if (traced) {
+      const trace::Context parent = trace::parse_traceparent(req.header("traceparent"));
+      span.trace_id = parent.valid() ? parent.trace_id : trace::random_hex(32);
+      span.parent_span_id = parent.valid() ? parent.span_id : "";
+      span.span_id = trace::random_hex(16);
+      span.name = req.method + " " + req.path;
+      span.start_ns = trace::now_ns();
+    }
+    auto finish_span = [&](bool failed) {
+      if (!traced) return;
+      span.end_ns = trace::now_ns();
+      span.error = failed || resp.status() >= 500;
+      span.str_attrs.emplace_back("http.method", req.method);
+      span.str_attrs.emplace_back("http.route", req.path);
+      span.int_attrs.emplace_back("http.status_code", resp.status());
+      span.int_attrs.emplace_back("http.request_content_length", static_cast<long long>(req.body.size()));
+      trace::exporter()->submit(std::move(span));
+    };
     try {
       if (it != routes_.end()) it->second(req, resp);
       else if (fallback_) fallback_(req, resp);
       else resp.send(404, "application/json", "{\"error\":\"Not Found\",\"error_type\":\"not_found\"}");
+      finish_span(false);
     } catch (const std::exception& e) {
+      finish_span(true);
       if (!resp.started()) {
         std::string msg = e.what();
         for (auto& c : msg) if (c == '"' || c == '\\' || c == '\n') c = ' ';

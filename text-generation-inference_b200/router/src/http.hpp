@@ -31,12 +31,14 @@ class Response {
   bool end_stream();
   bool client_gone();                           // non-blocking probe of the socket
   bool started() const { return started_; }
+  int status() const { return status_; }        // status line sent so far (0: nothing yet)
   bool keep_alive = true;
 
  private:
   bool write_all(const char* p, size_t n);
   int fd_;
   bool started_ = false;
+  int status_ = 0;
   bool alive_ = true;
   std::vector<std::pair<std::string, std::string>> headers_;
 };

@@ -218,6 +218,12 @@ int main(int argc, char** argv) {
     for (const char* f : {"dtype", "kv-cache-dtype", "speculate", "revision", "max-input-tokens"})
       if (args.has(f)) { cmd.push_back(std::string("--") + f); cmd.push_back(args.get(f)); }
     if (args.has("trust-remote-code")) cmd.push_back("--trust-remote-code");
+    if (args.has("otlp-endpoint")) {   // shards and router export to the same collector under their own service names
+      cmd.push_back("--otlp-endpoint");
+      cmd.push_back(args.get("otlp-endpoint"));
+      cmd.push_back("--otlp-service-name");
+      cmd.push_back(args.get("otlp-service-name", "text-generation-inference") + ".server");
+    }
     std::map<std::string, std::string> env = {
         {"RANK", std::to_string(r)}, {"LOCAL_RANK", std::to_string(r)}, {"WORLD_SIZE", std::to_string(num_shard)},
         {"MASTER_ADDR", args.get("master-addr", "127.0.0.1")}, {"MASTER_PORT", args.get("master-port", "29500")},
@@ -267,6 +273,12 @@ int main(int argc, char** argv) {
                         "waiting-served-ratio", "max-waiting-tokens", "max-batch-size", "max-client-batch-size",
                         "api-key", "payload-limit", "disable-grammar-support", "repo-root"})
     if (args.has(f)) { rcmd.push_back(std::string("--") + f); rcmd.push_back(args.get(f)); }
+  if (args.has("otlp-endpoint")) {
+    rcmd.push_back("--otlp-endpoint");
+    rcmd.push_back(args.get("otlp-endpoint"));
+    rcmd.push_back("--otlp-service-name");
+    rcmd.push_back(args.get("otlp-service-name", "text-generation-inference") + ".router");
+  }
   Child router;
   router.name = "router";
   router.pid = spawn(rcmd, {});

@@ -10,6 +10,7 @@
 #include <sstream>
 #include <map>
 
+#include "trace.hpp"
 #include "api.hpp"
 #include "http.hpp"
 #include "metrics.hpp"
@@ -248,6 +249,8 @@ int main(int argc, char** argv) {
     http::Server server(args.get("hostname", "0.0.0.0"), static_cast<int>(args.num("port", 3000)),
                         static_cast<size_t>(args.num("payload-limit", 2000000)));
     router.install(server);
+    // request spans go to an OTLP/HTTP collector when one is configured
+    trace::init(args.get("otlp-endpoint"), args.get("otlp-service-name", "text-generation-inference.router"));
     g_server = &server;
     std::signal(SIGINT, on_signal);
     std::signal(SIGTERM, on_signal);
@@ -256,6 +259,7 @@ int main(int argc, char** argv) {
     std::cerr << "[router] Connected; listening on port " << port << std::endl;
     server.serve_forever();
     backend->stop();
+    trace::shutdown();   // flushes the spans still queued
     std::cerr << "[router] shut down" << std::endl;
     return 0;
   } catch (const std::exception& e) {
