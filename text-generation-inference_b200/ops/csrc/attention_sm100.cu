@@ -214,25 +214,45 @@ __device__ __forceinline__ void pv_warp(const float (&s)[NT][4], const uint16_t*
 
 // Online-softmax update of one warp's 16 rows over NT n-tiles.  pos0/pos1: absolute positions of the
 // thread's two rows (lane/4 and lane/4+8); tbase: first token of n-tile 0.
+__device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: 2 ulp, -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int NT>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&alpha)[2],
                                                int tbase, int pos0, int pos1, int L, int window, float scale_log2,
                                                float softcap, float raw_scale) {
   const int lane = threadIdx.x & 31;
   float mx[2] = {-INFINITY, -INFINITY};
+  // a tile that lies entirely below the diagonal of all 16 rows of the warp, inside the window and inside the
+  // sequence needs no per-element mask (warp-uniform test: the warp's first row is pos0 - lane / 4)
+  const int row_lo = pos0 - (lane >> 2), row_hi = row_lo + 15, t_last = tbase + NT * 8 - 1;
+  const bool plain = softcap <= 0.f && t_last <= row_lo && t_last < L && (window <= 0 || tbase > row_hi - window);
+  if (plain) {
 #pragma unroll
-  for (int i = 0; i < NT; ++i) {
+    for (int i = 0; i < NT; ++i) {
+      mx[0] = fmaxf(mx[0], fmaxf(s[i][0], s[i][1]));
+      mx[1] = fmaxf(mx[1], fmaxf(s[i][2], s[i][3]));
+    }
+    mx[0] *= scale_log2;   // scale_log2 > 0
+    mx[1] *= scale_log2;
+  } else {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int t = tbase + i * 8 + (lane & 3) * 2 + (e & 1);
-      const int pos = (e < 2) ? pos0 : pos1;
-      float v = s[i][e];
-      if (softcap > 0.f) v = softcap * tanhf(v * raw_scale / softcap) * kLog2e;
-      else v = v * scale_log2;
-      const bool ok = t <= pos && t < L && (window <= 0 || t > pos - window);
-      v = ok ? v : -INFINITY;
-      s[i][e] = v;
-      mx[e >> 1] = fmaxf(mx[e >> 1], v);
+    for (int i = 0; i < NT; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int t = tbase + i * 8 + (lane & 3) * 2 + (e & 1);
+        const int pos = (e < 2) ? pos0 : pos1;
+        float v = s[i][e];
+        if (softcap > 0.f) v = softcap * tanhf(v * raw_scale / softcap) * kLog2e;
+        else v = v * scale_log2;
+        const bool ok = t <= pos && t < L && (window <= 0 || t > pos - window);
+        v = ok ? v : -INFINITY;
+        s[i][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
     }
   }
 #pragma unroll
@@ -240,7 +260,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     const float mn = fmaxf(m[r], mx[r]);
-    alpha[r] = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - mn);
+    alpha[r] = (mn == -INFINITY) ? 0.f : fast_exp2(m[r] - mn);
     m[r] = mn;
   }
   float rs[2] = {0.f, 0.f};
@@ -249,7 +269,9 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float mm = m[e >> 1];
-      const float pv = (mm == -INFINITY) ? 0.f : exp2f(s[i][e] - mm);
+      float pv;
+      if (plain) pv = fast_exp2(fmaf(s[i][e], scale_log2, -mm));
+      else pv = (mm == -INFINITY) ? 0.f : fast_exp2(s[i][e] - mm);
       s[i][e] = pv;
       rs[e >> 1] += pv;
     }
@@ -716,12 +738,6 @@ struct DecodeV3 {
   static_assert(kMergeBytes <= kRingBytes, "merge scratch must fit in the rings");
   static_assert(CT == 16 || CT == 32, "chunks are one or two 16-token boxes");
 };
-
-__device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: 2 ulp, -inf -> 0
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 __device__ __forceinline__ int bitrev3(int x) { return ((x & 1) << 2) | (x & 2) | ((x >> 2) & 1); }
 
