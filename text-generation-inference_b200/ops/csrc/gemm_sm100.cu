@@ -191,9 +191,14 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   float* sc_ring = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);   // [SC_STAGES][TM] (fp8 only)
   uint64_t* full = reinterpret_cast<uint64_t*>(sc_ring + (FP8 ? SC_STAGES * TM : 0));
   uint64_t* empty = full + STAGES;
-  uint64_t* tmem_full = empty + STAGES;      // [2]
-  uint64_t* tmem_empty = tmem_full + 2;      // [2]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  // Accumulator hand-over.  Block-scaled fp8 with two token halves (MH == 2) signals every half of a buffer on
+  // its own barrier pair: the promotion of half 0 starts while the MMAs of half 1 are still running and the
+  // MMA warp can refill a half as soon as its four epilogue warps have drained it, which shortens the
+  // MMA -> TMEM load -> release chain that a K block goes through.
+  constexpr int HB = (FP8 && MH == 2) ? 2 : 1;   // barrier pairs per accumulator buffer
+  uint64_t* tmem_full = empty + STAGES;      // [2 * HB]
+  uint64_t* tmem_empty = tmem_full + 4;      // [2 * HB]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 4);
   int* flag = reinterpret_cast<int*>(tmem_holder + 1);
   int* cslots = flag + 1;                    // [kMaxGrid] workspace slot of every contributor of a split tile
   {
@@ -221,9 +226,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < 2 * HB; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], kEpiWarps);
+      mbar_init(&tmem_empty[b], kEpiWarps / HB);
     }
     fence_barrier_init();
     prefetch_tensormap(&tmW);
@@ -294,7 +299,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           const bool seg_end = (it == nunits - 1) || kb == sch.KB - 1;
           const int use = FP8 ? it : seg;
           const int b = use & 1;
-          if ((FP8 || seg_start) && use >= 2 && !mbar_wait(&tmem_empty[b], ((use >> 1) - 1) & 1)) {
+          if (HB == 1 && (FP8 || seg_start) && use >= 2 && !mbar_wait(&tmem_empty[b], ((use >> 1) - 1) & 1)) {
             report(status, kErrMmaWaitAccum);
             break;
           }
@@ -303,8 +308,13 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           tc_fence_after();
           const uint32_t x_addr = smem_u32(smem + s * Cfg::kStageBytes);
           const uint64_t dw = make_desc_sw128(x_addr + Cfg::kXBytes);
+          bool acc_ok = true;
 #pragma unroll
           for (int h = 0; h < MH; ++h) {
+            if (HB == 2) {
+              if (use >= 2 && !mbar_wait(&tmem_empty[b * 2 + h], ((use >> 1) - 1) & 1)) { acc_ok = false; break; }
+              tc_fence_after();
+            }
             const uint64_t dx = make_desc_sw128(x_addr + h * 16384);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {   // 4 MMAs of 32 bytes of K each per 128-byte row
@@ -314,9 +324,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
               if (FP8) mma_f8f6f4(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
               else mma_f16(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
             }
+            if (HB == 2) tc_commit(&tmem_full[b * 2 + h]);
           }
+          if (!acc_ok) { report(status, kErrMmaWaitAccum); break; }
           tc_commit(&empty[s]);
-          if (FP8 || seg_end) tc_commit(&tmem_full[b]);
+          if (HB == 1 && (FP8 || seg_end)) tc_commit(&tmem_full[b]);
           if (seg_end) ++seg;
         }
       }
@@ -353,7 +365,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       }
       if (FP8) {
         const int b = it & 1;
-        ok = mbar_wait(&tmem_full[b], (it >> 1) & 1);
+        const int hb = HB == 2 ? b * 2 + g : b;   // g: token half of this warp when MH == 2
+        ok = mbar_wait(&tmem_full[hb], (it >> 1) & 1);
         if (!ok) { report(status, kErrEpilogueWait); break; }
         tc_fence_after();
         if (warp_active && !EXP_GE(2)) {
@@ -375,7 +388,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[b]);
+        if (lane == 0) mbar_arrive(&tmem_empty[hb]);
       } else if (seg_end) {
         const int b = seg & 1;
         ok = mbar_wait(&tmem_full[b], (seg >> 1) & 1);
