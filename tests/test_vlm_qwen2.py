@@ -28,23 +28,40 @@ def _png(seed, h, w):
     return buf.getvalue()
 
 
-@pytest.fixture(scope="module")
-def qwen(tmp_path_factory):
+def _build(kind, d):
     torch.manual_seed(0)
-    vis = dict(depth=2, embed_dim=32, hidden_size=64, mlp_ratio=2, num_heads=2, patch_size=14, spatial_merge_size=2,
-               temporal_patch_size=2, in_channels=3)
     txt = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                vocab_size=300, max_position_embeddings=512, tie_word_embeddings=False,
                rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]})
-    cfg = transformers.Qwen2VLConfig(vision_config=vis, text_config=txt, image_token_id=IMG, vision_start_token_id=START,
-                                     vision_end_token_id=END, video_token_id=296)
-    hf = transformers.Qwen2VLForConditionalGeneration(cfg).eval()
-    d = tmp_path_factory.mktemp("qwen2vl")
+    ids = dict(image_token_id=IMG, vision_start_token_id=START, vision_end_token_id=END, video_token_id=296)
+    if kind == "qwen2_vl":
+        vis = dict(depth=2, embed_dim=32, hidden_size=64, mlp_ratio=2, num_heads=2, patch_size=14, spatial_merge_size=2,
+                   temporal_patch_size=2, in_channels=3)
+        hf = transformers.Qwen2VLForConditionalGeneration(transformers.Qwen2VLConfig(vision_config=vis, text_config=txt, **ids))
+    else:
+        # windows of 2 x 2 merged patches, full attention only in block 1
+        vis = dict(depth=3, hidden_size=32, out_hidden_size=64, intermediate_size=48, num_heads=2, patch_size=14,
+                   spatial_merge_size=2, temporal_patch_size=2, in_channels=3, window_size=56, fullatt_block_indexes=[1])
+        hf = transformers.Qwen2_5_VLForConditionalGeneration(
+            transformers.Qwen2_5_VLConfig(vision_config=vis, text_config=txt, **ids))
+    hf = hf.eval()
     hf.save_pretrained(str(d), safe_serialization=True)
     c = json.loads((d / "config.json").read_text())
     c["vision_config"]["min_pixels"], c["vision_config"]["max_pixels"] = 28 * 28, 28 * 28 * 16
     (d / "config.json").write_text(json.dumps(c))
-    return hf, d
+    return hf
+
+
+@pytest.fixture(scope="module")
+def qwen(tmp_path_factory):
+    d = tmp_path_factory.mktemp("qwen2vl")
+    return _build("qwen2_vl", d), d
+
+
+@pytest.fixture(scope="module")
+def qwen25(tmp_path_factory):
+    d = tmp_path_factory.mktemp("qwen25vl")
+    return _build("qwen2_5_vl", d), d
 
 
 def test_smart_resize_and_patch_order():
@@ -112,4 +129,35 @@ def test_qwen2_vl_generation_matches_transformers(qwen, chunk):
         with torch.no_grad():
             ref = hf.generate(input_ids=ids, attention_mask=torch.ones_like(ids), max_new_tokens=6, min_new_tokens=6,
                               do_sample=False, **kw)
+        assert got[i][:6] == ref[0, ids.shape[1]:].tolist(), (i, got[i], ref[0, ids.shape[1]:].tolist())
+
+
+def test_qwen2_5_vl_generation_matches_transformers(qwen25):
+    """Windowed vision tower (RMSNorm, gated MLP, window / full attention blocks, window reordering)."""
+    hf, d = qwen25
+    model = get_model(str(d), dtype="float32", device=torch.device("cpu"))
+    assert model.tower.v25 and model.tower.full_blocks == {1}
+    png1, png2 = _png(1, 80, 110), _png(2, 60, 58)          # 84 x 112 (3 x 4 merged patches: ragged windows) and 56 x 56
+    reqs = [
+        _request(0, [("text", "ab"), ("image", png1), ("text", "cde")], 6, range(1, 4)),
+        _request(1, [("image", png2), ("text", "xy"), ("image", png1)], 6, range(4, 8)),
+    ]
+    model.init_kv_cache(12)
+    batch = model.batch_type.from_pb(pb.Batch(id=0, requests=reqs, size=2), model.tokenizer, torch.float32,
+                                     torch.device("cpu"), 0)
+    prompts = [list(s.ids) for s in batch.seqs]
+    assert prompts[0].count(IMG) == 12 and prompts[1].count(IMG) == 4 + 12
+    got = {0: [], 1: []}
+    while batch is not None:
+        gens, batch, _ = model.generate_token(batch)
+        for g in gens:
+            got[g.request_id].extend(g.tokens.token_ids)
+    images = {0: [png1], 1: [png2, png1]}
+    for i in range(2):
+        ids = torch.tensor([prompts[i]])
+        pre = [preprocess_qwen_image(b, 14, 2, 2, 28 * 28, 28 * 28 * 16) for b in images[i]]
+        with torch.no_grad():
+            ref = hf.generate(input_ids=ids, attention_mask=torch.ones_like(ids), max_new_tokens=6, min_new_tokens=6,
+                              do_sample=False, pixel_values=torch.cat([p for p, _ in pre]),
+                              image_grid_thw=torch.tensor([list(g) for _, g in pre]))
         assert got[i][:6] == ref[0, ids.shape[1]:].tolist(), (i, got[i], ref[0, ids.shape[1]:].tolist())

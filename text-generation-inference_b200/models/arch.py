@@ -195,7 +195,7 @@ ARCHS["deepseek_v2"] = ARCHS["deepseek_v3"] = replace(
     moe_gate="gate_proj", moe_up="up_proj", moe_down="down_proj", moe_shared="mlp.shared_experts")
 ARCHS["gemma3"] = ARCHS["gemma3_text"]
 ARCHS["phi-msft"] = ARCHS["phi"]
-ARCHS["qwen2_vl_text"] = ARCHS["qwen2"]      # language model of Qwen2-VL (3-axis rotary handled by the runner)
+ARCHS["qwen2_vl_text"] = ARCHS["qwen2_5_vl_text"] = ARCHS["qwen2"]   # language models of Qwen2-VL / Qwen2.5-VL
 
 
 def arch_for(model_type: str) -> Arch:

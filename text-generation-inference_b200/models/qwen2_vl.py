@@ -1,7 +1,10 @@
-"""Qwen2-VL: dynamic-resolution vision transformer, 2x2 patch merger and 3-axis rotary positions.
+"""Qwen2-VL and Qwen2.5-VL: dynamic-resolution vision transformer, 2x2 patch merger and 3-axis rotary
+positions.
 
-Reference: ``custom_modeling/qwen2_vl.py`` (vision blocks with 2-D rotary embedding, ``PatchMerger``,
-``get_position_ids``) and the Qwen2-VL branch of ``models/vlm_causal_lm.py`` (image-token expansion
+Reference: ``custom_modeling/qwen2_vl.py`` and ``custom_modeling/qwen2_5_vl.py`` (vision blocks with 2-D
+rotary embedding, ``PatchMerger``, ``get_position_ids``; the 2.5 tower uses RMSNorm, a gated SiLU MLP and
+attention restricted to windows of 8 x 8 merged patches in all but a few "full attention" blocks) and the
+Qwen2-VL branch of ``models/vlm_causal_lm.py`` (image-token expansion
 ``<|vision_start|><|image_pad|>*n<|vision_end|>``).
 
 Differences from the fixed-resolution families of ``vlm_causal_lm.py``:
@@ -77,10 +80,19 @@ def preprocess_qwen_image(data: bytes, patch: int, merge: int, temporal: int, mi
 
 
 # ---- vision tower --------------------------------------------------------------------------------
+def _rms_norm(x, weight, eps=1e-6):
+    v = x.float()
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
+
+
 class Qwen2VisionTower:
-    def __init__(self, cfg: dict, w: Weights, prefix: str):
+    def __init__(self, cfg: dict, w: Weights, prefix: str, v25: bool = False):
         g = w.get_tensor
-        self.embed_dim = int(cfg.get("embed_dim", 1280))
+        self.v25 = v25
+        # Qwen2-VL calls the tower width `embed_dim` (and `hidden_size` is the text width); 2.5 calls it `hidden_size`
+        self.embed_dim = int(cfg.get("hidden_size", 1280) if v25 else cfg.get("embed_dim", 1280))
+        self.window = int(cfg.get("window_size", 112))
+        self.full_blocks = set(cfg.get("fullatt_block_indexes", [7, 15, 23, 31])) if v25 else None
         self.heads = int(cfg.get("num_heads", 16))
         self.patch, self.merge = int(cfg.get("patch_size", 14)), int(cfg.get("spatial_merge_size", 2))
         self.temporal = int(cfg.get("temporal_patch_size", 2))
@@ -89,14 +101,21 @@ class Qwen2VisionTower:
         self.blocks = []
         for i in range(int(cfg.get("depth", 32))):
             b = f"{prefix}.blocks.{i}"
-            self.blocks.append(dict(
-                n1=(g(f"{b}.norm1.weight"), g(f"{b}.norm1.bias")), n2=(g(f"{b}.norm2.weight"), g(f"{b}.norm2.bias")),
-                qkv=(g(f"{b}.attn.qkv.weight"), g(f"{b}.attn.qkv.bias")),
-                proj=(g(f"{b}.attn.proj.weight"), g(f"{b}.attn.proj.bias")),
-                fc1=(g(f"{b}.mlp.fc1.weight"), g(f"{b}.mlp.fc1.bias")),
-                fc2=(g(f"{b}.mlp.fc2.weight"), g(f"{b}.mlp.fc2.bias"))))
+            blk = dict(qkv=(g(f"{b}.attn.qkv.weight"), g(f"{b}.attn.qkv.bias")),
+                       proj=(g(f"{b}.attn.proj.weight"), g(f"{b}.attn.proj.bias")))
+            if v25:
+                blk.update(n1=g(f"{b}.norm1.weight"), n2=g(f"{b}.norm2.weight"),
+                           gate=(g(f"{b}.mlp.gate_proj.weight"), g(f"{b}.mlp.gate_proj.bias")),
+                           up=(g(f"{b}.mlp.up_proj.weight"), g(f"{b}.mlp.up_proj.bias")),
+                           down=(g(f"{b}.mlp.down_proj.weight"), g(f"{b}.mlp.down_proj.bias")))
+            else:
+                blk.update(n1=(g(f"{b}.norm1.weight"), g(f"{b}.norm1.bias")),
+                           n2=(g(f"{b}.norm2.weight"), g(f"{b}.norm2.bias")),
+                           fc1=(g(f"{b}.mlp.fc1.weight"), g(f"{b}.mlp.fc1.bias")),
+                           fc2=(g(f"{b}.mlp.fc2.weight"), g(f"{b}.mlp.fc2.bias")))
+            self.blocks.append(blk)
         m = f"{prefix}.merger"
-        self.ln_q = (g(f"{m}.ln_q.weight"), g(f"{m}.ln_q.bias"))
+        self.ln_q = g(f"{m}.ln_q.weight") if v25 else (g(f"{m}.ln_q.weight"), g(f"{m}.ln_q.bias"))
         self.m1 = (g(f"{m}.mlp.0.weight"), g(f"{m}.mlp.0.bias"))
         self.m2 = (g(f"{m}.mlp.2.weight"), g(f"{m}.mlp.2.bias"))
         self.act = cfg.get("hidden_act", "quick_gelu")
@@ -123,28 +142,67 @@ class Qwen2VisionTower:
         rot = torch.cat([-xf[..., h:], xf[..., :h]], dim=-1)
         return (xf * cos[:, None] + rot * sin[:, None]).to(x.dtype)
 
+    def _windows(self, grids: List[Tuple[int, int, int]]) -> Tuple[torch.Tensor, List[int]]:
+        """Qwen2.5-VL: order of the merged patches that makes every attention window contiguous, and the
+        window boundaries in patches (windows are `window / merge / patch` merged patches on a side; border
+        windows are smaller)."""
+        side = self.window // self.merge // self.patch
+        order, bounds, base = [], [0], 0
+        m2 = self.merge ** 2
+        for t, gh, gw in grids:
+            lh, lw = gh // self.merge, gw // self.merge
+            idx = torch.arange(t * lh * lw).view(t, lh, lw)
+            ph, pw = side - lh % side, side - lw % side
+            idx = F.pad(idx, (0, pw, 0, ph), value=-1)
+            nh, nw = (lh + ph) // side, (lw + pw) // side
+            idx = idx.view(t, nh, side, nw, side).permute(0, 1, 3, 2, 4).reshape(t * nh * nw, side * side)
+            for win in idx:
+                keep = win[win >= 0]
+                if keep.numel():
+                    order.append(keep + base)
+                    bounds.append(bounds[-1] + keep.numel() * m2)
+            base += t * lh * lw
+        return torch.cat(order), bounds
+
+    def _attend(self, q, k, v, bounds):
+        out = torch.empty_like(q)
+        for lo, hi in zip(bounds[:-1], bounds[1:]):            # attention never crosses a segment
+            o = F.scaled_dot_product_attention(q[lo:hi].transpose(0, 1)[None], k[lo:hi].transpose(0, 1)[None],
+                                               v[lo:hi].transpose(0, 1)[None])
+            out[lo:hi] = o[0].transpose(0, 1)
+        return out
+
     @torch.no_grad()
     def __call__(self, patches: torch.Tensor, grids: List[Tuple[int, int, int]]) -> torch.Tensor:
         """``[sum(gh*gw), C*T*p*p]`` -> ``[sum(gh*gw) / merge^2, out_hidden]``"""
         x = F.linear(patches.to(self.patch_w.dtype), self.patch_w)
         cos, sin = self._rotary(grids, x.device)
-        bounds = np.cumsum([0] + [t * gh * gw for t, gh, gw in grids]).tolist()
-        C = self.embed_dim
-        for b in self.blocks:
-            h = F.layer_norm(x, (C,), *b["n1"], 1e-6)
+        image_bounds = np.cumsum([0] + [gh * gw for t, gh, gw in grids for _ in range(t)]).tolist()
+        C, m2 = self.embed_dim, self.merge ** 2
+        order = None
+        if self.v25:
+            order, window_bounds = self._windows(grids)
+            order = order.to(x.device)
+            regroup = lambda a: a.view(-1, m2, a.shape[-1])[order].reshape(-1, a.shape[-1])
+            x, cos, sin = regroup(x), regroup(cos), regroup(sin)
+        for li, b in enumerate(self.blocks):
+            h = _rms_norm(x, b["n1"]) if self.v25 else F.layer_norm(x, (C,), *b["n1"], 1e-6)
             qkv = F.linear(h, *b["qkv"]).view(-1, 3, self.heads, self.head_dim)
             q, k, v = self._rot(qkv[:, 0], cos, sin), self._rot(qkv[:, 1], cos, sin), qkv[:, 2]
-            out = torch.empty_like(q)
-            for lo, hi in zip(bounds[:-1], bounds[1:]):        # attention never crosses an image
-                o = F.scaled_dot_product_attention(q[lo:hi].transpose(0, 1)[None], k[lo:hi].transpose(0, 1)[None],
-                                                   v[lo:hi].transpose(0, 1)[None])
-                out[lo:hi] = o[0].transpose(0, 1)
-            x = x + F.linear(out.reshape(-1, C), *b["proj"])
-            h = F.linear(F.layer_norm(x, (C,), *b["n2"], 1e-6), *b["fc1"])
-            h = h * torch.sigmoid(1.702 * h) if self.act == "quick_gelu" else F.gelu(h)
-            x = x + F.linear(h, *b["fc2"])
-        x = F.layer_norm(x, (C,), *self.ln_q, 1e-6).view(-1, C * self.merge ** 2)
-        return F.linear(F.gelu(F.linear(x, *self.m1)), *self.m2)
+            bounds = image_bounds if (not self.v25 or li in self.full_blocks) else window_bounds
+            x = x + F.linear(self._attend(q, k, v, bounds).reshape(-1, C), *b["proj"])
+            if self.v25:
+                h = _rms_norm(x, b["n2"])
+                x = x + F.linear(F.silu(F.linear(h, *b["gate"])) * F.linear(h, *b["up"]), *b["down"])
+            else:
+                h = F.linear(F.layer_norm(x, (C,), *b["n2"], 1e-6), *b["fc1"])
+                h = h * torch.sigmoid(1.702 * h) if self.act == "quick_gelu" else F.gelu(h)
+                x = x + F.linear(h, *b["fc2"])
+        x = _rms_norm(x, self.ln_q) if self.v25 else F.layer_norm(x, (C,), *self.ln_q, 1e-6)
+        out = F.linear(F.gelu(F.linear(x.view(-1, C * m2), *self.m1)), *self.m2)
+        if order is not None:
+            out = out[torch.argsort(order)]                    # back to the order of the image rows
+        return out
 
 
 # ---- batch -----------------------------------------------------------------------------------------
@@ -286,7 +344,7 @@ def load_qwen2_vl(path, cfg, weights: Weights, comm, rank, world, dtype, device,
 
     text_cfg = cfg.text_config()
     vis = dict(cfg.get("vision_config") or {})
-    tower = Qwen2VisionTower(vis, weights, "model.visual")
+    tower = Qwen2VisionTower(vis, weights, "model.visual", v25=cfg.model_type == "qwen2_5_vl")
     model = CausalDecoder(text_cfg, weights, comm=comm, prefix="model.language_model")
     if not model.rotary.mrope_section:
         raise ValueError("qwen2_vl checkpoints need `mrope_section` in their rope parameters")

@@ -365,7 +365,7 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
         # decoder here scales only the rows it embeds itself.
         prefix, scale = "language_model", 1.0
         image_token = int(cfg.get("image_token_index", 257152))
-    elif mt in ("qwen2_vl",):
+    elif mt in ("qwen2_vl", "qwen2_5_vl"):
         from .qwen2_vl import load_qwen2_vl
 
         hidden = int(text_cfg.get("hidden_size"))

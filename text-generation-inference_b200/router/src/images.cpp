@@ -247,7 +247,7 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     const uint32_t side = static_cast<uint32_t>(num("image_size", 336) / num("patch_size", 14));
     return side * side;
   }
-  if (mt == "qwen2_vl") {
+  if (mt == "qwen2_vl" || mt == "qwen2_5_vl") {
     // dynamic resolution: both sides rounded to multiples of patch * merge inside the pixel budget; one row
     // per merge x merge block of patches, plus the vision-start / vision-end tokens the runner adds
     const double patch = num("patch_size", 14), merge = num("spatial_merge_size", 2);
