@@ -271,6 +271,11 @@ class FlashCausalLM(Model):
         self.max_prefill_tokens = max_prefill_tokens
         self.staging = StepStaging(device)
         self.graphs = None
+        # (signature, graphs object, (logits, row_owner)) of a decode replay that was put on the stream at the end
+        # of the previous step, before its text post-processing (see `_prelaunch_next_decode`)
+        self._prelaunched = None
+        self.overlap_hits = 0          # steps that found their replay already on the stream
+        self.overlap_decode = os.environ.get("TGI_B200_OVERLAP_DECODE", "1") == "1"
         self.eos_token_ids = eos_token_ids
         if eos_token_ids is not None and tokenizer is not None:
             try:
@@ -392,6 +397,25 @@ class FlashCausalLM(Model):
             meta.adapter_data = lora.batch_data(token_adapter, self.device)
         return meta, row_owner
 
+    @staticmethod
+    def _decode_signature(seqs) -> tuple:
+        """Identity of a decode step: which sequences, and how long each is."""
+        return tuple(id(s) for s in seqs), tuple(len(s.ids) for s in seqs)
+
+    @staticmethod
+    def _nobody_finishes(seqs, next_ids) -> bool:
+        """True when no sequence can stop on the token it just received: decided without detokenising
+        (length and EOS checks); a sequence with stop strings always counts as "might stop"."""
+        for s, tok in zip(seqs, next_ids):
+            st = s.stopping
+            if st.stop_sequence_criterias or st.current_tokens + 1 >= st.max_new_tokens:
+                return False
+            if not st.ignore_eos_token and tok in st.eos_token_ids:
+                return False
+            if len(s.ids) + 1 >= len(s.slots):      # the next step would need a slot past the allocation
+                return False
+        return True
+
     def forward(self, meta: ForwardMeta) -> torch.Tensor:
         logits, spec = self.model.forward(meta, self.kv_cache)
         self.last_speculative_logits = spec     # [rows, n_heads, V] when a speculator head is attached
@@ -414,8 +438,14 @@ class FlashCausalLM(Model):
                      # the row-parallel targets need a collective between the two kernels and stay eager
                      and not (getattr(self, "lora", None) is not None and self.world_size > 1
                               and any(s.adapter_index > 0 for s in seqs)))
+        pre, self._prelaunched = self._prelaunched, None
         if use_graph:
-            logits, row_owner = self.graphs.run(batch, counts)
+            if (pre is not None and pre[1] is self.graphs and pre[0] == self._decode_signature(seqs)
+                    and all(c == 1 for c in counts)):
+                logits, row_owner = pre[2]          # this step's replay is already on the stream
+                self.overlap_hits += 1
+            else:
+                logits, row_owner = self.graphs.run(batch, counts)
         else:
             meta, row_owner = self.build_meta(batch, counts)
             logits = self.forward(meta) if row_owner or any(counts) else None
@@ -547,6 +577,18 @@ class FlashCausalLM(Model):
                     [seqs[i].top_n for i in active], None, lp_rows,
                     torch.tensor(accepted_l, dtype=torch.long))
 
+            # Overlap: when this was a plain graph decode step and no sequence can finish on it (checked on
+            # token ids alone), the next step's replay goes on the stream now, and the detokenisation /
+            # stop-sequence / response building below runs while the GPU computes it.
+            appended = False
+            if (use_graph and self.overlap_decode and batch.speculate == 0 and len(active) == B
+                    and all(a == 1 for a in accepted_l) and self._nobody_finishes(seqs, next_ids_l)):
+                for s, tok in zip(seqs, next_ids_l):
+                    s.ids.append(tok)
+                appended = True
+                if self.graphs.supports(batch):
+                    out = self.graphs.run(batch, [1] * B)
+                    self._prelaunched = (self._decode_signature(seqs), self.graphs, out)
             cursor = 0
             for r, i in enumerate(active):
                 s = seqs[i]
@@ -562,7 +604,8 @@ class FlashCausalLM(Model):
                 texts, specials, kept_ids, kept_lps = [], [], [], []
                 stop, reason = False, None
                 for tok, lp in zip(new_ids, new_lps):
-                    s.ids.append(tok)
+                    if not appended:
+                        s.ids.append(tok)
                     text, s.prefix_offset, s.read_offset = self.decode_token(s.ids, s.prefix_offset, s.read_offset)
                     kept_ids.append(tok)
                     kept_lps.append(lp)
