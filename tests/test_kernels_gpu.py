@@ -176,7 +176,7 @@ def test_paged_attention_prefill(K, fp8, Hq, Hkv, D):
 
 
 @pytest.mark.parametrize("fp8", [False, True])
-@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64), (32, 1, 128), (64, 8, 128), (4, 2, 256)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 4, 64), (32, 1, 128), (64, 8, 128), (4, 2, 256), (8, 1, 128)])
 def test_paged_attention_decode(K, fp8, Hq, Hkv, D):
     _attention_case(K, 5, [1] * 5, [1, 17, 64, 250, 1000], Hq, Hkv, D, fp8)
     _attention_case(K, 3, [1] * 3, [300, 5, 129], Hq, Hkv, D, fp8, nsplit=1)

@@ -587,7 +587,7 @@ class FlashCausalLM(Model):
                     s.ids.append(tok)
                 appended = True
                 if self.graphs.supports(batch):
-                    out = self.graphs.run(batch, [1] * B)
+                    out = self.graphs.advance(seqs, next_ids_l)     # same bucket as the step that just ran
                     self._prelaunched = (self._decode_signature(seqs), self.graphs, out)
             cursor = 0
             for r, i in enumerate(active):

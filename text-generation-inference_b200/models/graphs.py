@@ -175,6 +175,22 @@ class DecodeGraphs:
         self.last = (b, n)
         return (b.logits[:n] if b.logits is not None else None), row_owner
 
+    def advance(self, seqs, next_ids: List[int]):
+        """Replay the bucket of the last step once more for the same sequences, one token further: ids, positions
+        and KV lengths are updated in place (block tables and adapter indices stay), so the host work between
+        two decode steps is a handful of vector operations.  The caller has appended ``next_ids`` to the sequences."""
+        b, n = self.last
+        h = b.host_np
+        h[b.off_ids:b.off_ids + n] = next_ids
+        h[b.off_pos:b.off_pos + n] += 1
+        h[b.off_kv:b.off_kv + n] += 1
+        slots = h[b.off_slots:b.off_slots + n]
+        for i, s in enumerate(seqs):
+            slots[i] = s.slots[len(s.ids) - 1]
+        b.dev.copy_(b.host, non_blocking=True)
+        b.graph.replay()
+        return (b.logits[:n] if b.logits is not None else None), [(i, 0) for i in range(n)]
+
     def greedy(self):
         """``(ids, logprobs)`` of the last replay when its graph sampled greedily in-kernel, else ``None``."""
         b, n = self.last
