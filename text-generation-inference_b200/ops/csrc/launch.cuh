@@ -19,7 +19,14 @@
 namespace tgi {
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Early trigger: lets the dependent grid be placed while this one still runs.  Measured slower (the early CTAs
+// take SM slots from later waves of the running kernel), so by default the trigger is the implicit one at CTA
+// exit and only the launch latency and the prologue of the next kernel overlap with this kernel's tail.
+__device__ __forceinline__ void pdl_trigger() {
+#ifdef TGI_PDL_EARLY_TRIGGER
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
 
 inline bool pdl_enabled() {
   static const bool on = [] {
