@@ -137,7 +137,7 @@ def test_rope_and_cache(K, fp8_cache, neox, rot):
     torch.testing.assert_close(v1.float(), v2.float(), **tol)
 
 
-def _attention_case(K, B, q_lens, kv_lens, Hq, Hkv, D, fp8, window=-1, softcap=0.0, nsplit=None):
+def _attention_case(K, B, q_lens, kv_lens, Hq, Hkv, D, fp8, window=-1, softcap=0.0, nsplit=None, spans=None):
     torch.manual_seed(B * 7 + Hq)
     bs = 16
     nblocks = sum((l + bs - 1) // bs for l in kv_lens) + 2
@@ -160,9 +160,18 @@ def _attention_case(K, B, q_lens, kv_lens, Hq, Hkv, D, fp8, window=-1, softcap=0
     ks = (torch.rand(Hkv, device=dev()) * 0.2 + 0.15) if fp8 else None
     vs = (torch.rand(Hkv, device=dev()) * 0.2 + 0.15) if fp8 else None
     scale = D ** -0.5
-    want = ref.paged_attention(q, kc, vc, bt, cu, kl, scale, window, softcap, ks, vs)
+    horizon = None
+    if spans is not None:
+        # rows whose position falls in a span [a, b) of their sequence see the whole span
+        hz, t = [], 0
+        for (n, L), sp in zip(zip(q_lens, kv_lens), spans):
+            for i in range(n):
+                pos = L - n + i
+                hz.append(next((b - 1 for a, b in sp if a <= pos < b), pos))
+        horizon = torch.tensor(hz, dtype=torch.int32, device=dev())
+    want = ref.paged_attention(q, kc, vc, bt, cu, kl, scale, window, softcap, ks, vs, horizon=horizon)
     got = K.paged_attention(q, kc, vc, bt, cu, kl, scale, window, softcap, ks, vs, max(q_lens), max(kv_lens),
-                            nsplit=nsplit)
+                            nsplit=nsplit, horizon=horizon)
     torch.cuda.synchronize()
     torch.testing.assert_close(got.float(), want.float(), atol=3e-2, rtol=3e-2)
 
@@ -173,6 +182,16 @@ def test_paged_attention_prefill(K, fp8, Hq, Hkv, D):
     _attention_case(K, 3, [70, 1, 130], [70, 33, 200], Hq, Hkv, D, fp8)
     _attention_case(K, 2, [64, 17], [64, 400], Hq, Hkv, D, fp8, window=48)
     _attention_case(K, 2, [30, 65], [30, 65], Hq, Hkv, D, fp8, softcap=30.0)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 2, 256)])
+def test_paged_attention_prefill_horizon(K, fp8, Hq, Hkv, D):
+    """Image-style spans: rows inside a span attend to the whole span, also across 64-row tiles and with a window."""
+    spans = [[(10, 30), (100, 170)], [(0, 5)], [(60, 130)]]
+    _attention_case(K, 3, [200, 40, 130], [200, 40, 130], Hq, Hkv, D, fp8, spans=spans)
+    _attention_case(K, 3, [200, 40, 130], [200, 40, 130], Hq, Hkv, D, fp8, window=48, spans=spans)
+    _attention_case(K, 2, [100, 70], [150, 70], Hq, Hkv, D, fp8, spans=[[(60, 140)], [(3, 66)]])   # cached prefix
 
 
 @pytest.mark.parametrize("fp8", [False, True])

@@ -51,6 +51,7 @@ class ForwardMeta:
     adapter_data: Optional[object] = None            # LoRA batch metadata
     rope_cos_sin: Optional[torch.Tensor] = None      # [T, rot_dim] rotary rows of this step (multi-axis positions)
     rope_rows: Optional[torch.Tensor] = None         # [T] = arange(T): row of `rope_cos_sin` per token
+    attn_horizon: Optional[torch.Tensor] = None      # [T] last KV position a row may see (image rows: end of their image)
 
 
 class Norm:
@@ -239,7 +240,7 @@ class Attention:
                                    d.softmax_scale, self.window, d.attn_softcap,
                                    self.k_scale if k_cache.dtype == torch.float8_e4m3fn else None,
                                    self.v_scale if v_cache.dtype == torch.float8_e4m3fn else None,
-                                   meta.max_q, meta.max_kv)
+                                   meta.max_q, meta.max_kv, horizon=meta.attn_horizon)
         if Dp != D:
             attn = attn.view(attn.shape[0], d.num_heads, Dp)[:, :, :D]
         attn = attn.reshape(attn.shape[0], d.num_heads * D)

@@ -15,7 +15,10 @@ Covered families: LLaVA-style (CLIP tower, 2-layer MLP projector, optional class
 base-resolution view of llava_next), PaliGemma-style (SigLIP tower, linear projector, embedding
 scale), Idefics2 (SigLIP-style tower, gated-MLP projection and a perceiver resampler that compresses
 an image to a fixed number of latents; ``custom_modeling/idefics2.py``) and Idefics3 / SmolVLM
-(pixel-shuffle connector; ``custom_modeling/idefics3.py``).  The Idefics families run on the global
+(pixel-shuffle connector; ``custom_modeling/idefics3.py``) and Gemma-3 (SigLIP tower, average-pooled
+to ``mm_tokens_per_image`` rows, RMSNorm and a projection matrix; the rows of one image attend to each
+other in both directions, which the attention kernels get as a per-row horizon;
+``custom_modeling/flash_gemma3_modeling.py``).  The Idefics families run on the global
 view of an image (the square resize to the tower's resolution); the sub-image tiling their
 processors can add is not produced.  Towers are plain pre-norm ViTs evaluated with ``F.scaled_dot_product_attention``: the image
 side is compute-light next to the decoder and runs once per request.
@@ -128,6 +131,8 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
     """Adds, per request, the decoded images and the prompt positions of their placeholder tokens."""
 
     image_token_id: int = 0
+    image_start_id: Optional[int] = None      # tokens put around the placeholder rows (Gemma-3: begin / end of image)
+    image_end_id: Optional[int] = None
     tokens_per_image: int = 0
     image_size: int = 224
     norm = (CLIP_MEAN, CLIP_STD)
@@ -150,8 +155,12 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
                     first_text = False
                 else:
                     pixels = preprocess_image(c.image.data, cls.image_size, *cls.norm)
+                    if cls.image_start_id is not None:
+                        ids.append(cls.image_start_id)
                     images.append((len(ids), pixels))
                     ids.extend([cls.image_token_id] * cls.tokens_per_image)
+                    if cls.image_end_id is not None:
+                        ids.append(cls.image_end_id)
             if r.truncate and len(ids) > r.truncate:
                 cut = len(ids) - r.truncate
                 if any(pos < cut for pos, _ in images):
@@ -174,13 +183,20 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
 
 class VlmCausalLM(FlashCausalLM):
     def __init__(self, model: CausalDecoder, tower: VisionTower, projector, tokenizer, dtype, device, rank, world,
-                 image_token_id: int, drop_cls: bool, embed_scale: float = 1.0, **kw):
+                 image_token_id: int, drop_cls: bool, embed_scale: float = 1.0, image_wrap=(None, None),
+                 bidirectional_images: bool = False, **kw):
         super().__init__(model, tokenizer, dtype, device, rank, world, **kw)
+        self.bidirectional_images = bidirectional_images
+        if bidirectional_images:
+            # the rows of an image see each other: an image has to sit inside one prefill step
+            self.support_chunking = False
+            self.max_prefill_tokens = None
         self.tower, self.projector = tower, projector
         self.image_token_id, self.drop_cls, self.image_embed_scale = image_token_id, drop_cls, embed_scale
         self.tokens_per_image = projector.out_tokens(tower.num_patches)
         self.batch_cls = type("BoundVlmBatch", (VlmCausalLMBatch,), dict(
             image_token_id=image_token_id, tokens_per_image=self.tokens_per_image, image_size=tower.image_size,
+            image_start_id=image_wrap[0], image_end_id=image_wrap[1],
             norm=(CLIP_MEAN, CLIP_STD) if tower.kind == "clip" else (SIGLIP_MEAN, SIGLIP_STD)))
 
     @property
@@ -211,6 +227,19 @@ class VlmCausalLM(FlashCausalLM):
                     if a < b:
                         jobs.append((t + a - lo, b - a, px, a - pos, id(px)))
             t += n
+        if jobs and self.bidirectional_images:
+            # horizon of every row of the step: its own position, or the last row of its image
+            hz = meta.positions.clone()
+            t = 0
+            for s, n in zip(batch.seqs, counts):
+                if s.prefilling and n > 0:
+                    lo, hi = s.cache_len, s.cache_len + n
+                    for pos, _ in getattr(s, "images", []):
+                        a, b = max(pos, lo), min(pos + self.tokens_per_image, hi)
+                        if a < b:
+                            hz[t + a - lo:t + b - lo] = pos + self.tokens_per_image - 1
+                t += n
+            meta.attn_horizon = hz
         if jobs:
             uniq: Dict[int, int] = {}
             stack = []
@@ -250,6 +279,25 @@ class _LinearProjector:
     def __call__(self, x):
         N, S, C = x.shape
         return ops.linear(x.reshape(N * S, C), self.w, self.b).view(N, S, -1)
+
+
+class _AvgPoolProjector:
+    """Gemma-3: average-pool the patch grid to ``side x side`` rows, RMSNorm (unit offset), projection matrix."""
+
+    def __init__(self, proj, norm_w, eps: float, side: int):
+        self.proj, self.norm_w, self.eps, self.side = proj, norm_w, eps, int(side)
+
+    def out_tokens(self, n: int) -> int:
+        return self.side ** 2
+
+    def __call__(self, x):                                   # [N, S, C] -> [N, side^2, H]
+        N, S, C = x.shape
+        grid = int(round(math.sqrt(S)))
+        x = F.avg_pool2d(x.transpose(1, 2).reshape(N, C, grid, grid), grid // self.side)
+        x = x.flatten(2).transpose(1, 2)
+        v = x.float()
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps) * (1.0 + self.norm_w.float())
+        return torch.matmul(v.to(x.dtype), self.proj)
 
 
 class _PixelShuffleProjector:
@@ -334,6 +382,7 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
     # `model.language_model.*`, and the Idefics text model has no inner `model.` level
     renames = [("language_model.model.", "model.language_model."), ("language_model.lm_head", "lm_head"),
                ("vision_tower.", "model.vision_tower."), ("multi_modal_projector.", "model.multi_modal_projector."),
+               ("language_model.", "model.language_model."),       # Gemma-3 as saved by recent transformers
                ("model.text_model.model.", "model.text_model."),
                ("model.language_model.model.", "model.language_model."),
                # Qwen2-VL as first published: language model at the top level, tower under `visual.`
@@ -374,6 +423,20 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
                                kv_cache_dtype, max_prefill_tokens)
         weights.close()
         return runner
+    elif mt == "gemma3":
+        vis.setdefault("image_size", 896)
+        vis.setdefault("patch_size", 14)
+        vis.setdefault("hidden_act", "gelu_pytorch_tanh")
+        tower = VisionTower(vis, weights, "vision_tower.vision_model", "siglip", feature_layer=-1)
+        side = int(round(math.sqrt(int(cfg.get("mm_tokens_per_image", 256)))))
+        projector = _AvgPoolProjector(weights.get_tensor("multi_modal_projector.mm_input_projection_weight"),
+                                      weights.get_tensor("multi_modal_projector.mm_soft_emb_norm.weight"),
+                                      float(vis.get("layer_norm_eps", 1e-6)), side)
+        drop_cls = False
+        prefix, scale = "language_model", 1.0
+        image_token = int(cfg.get("image_token_index", cfg.get("image_token_id", 262144)))
+        extra = dict(image_wrap=(cfg.get("boi_token_index", cfg.get("boi_token_id")),
+                                 cfg.get("eoi_token_index", cfg.get("eoi_token_id"))), bidirectional_images=True)
     elif mt in ("idefics2", "idefics3"):
         vis.setdefault("image_size", 364 if mt == "idefics3" else 980)
         vis.setdefault("patch_size", 14)
@@ -396,7 +459,7 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
     comm = make_comm(process_group, rank, world, device, hidden, int(max_prefill_tokens or 4096))
     model = CausalDecoder(text_cfg, weights, comm=comm, prefix=prefix)
     runner = VlmCausalLM(model, tower, projector, tokenizer, dtype, device, rank, world, image_token, drop_cls,
-                         scale, speculate=speculate,
+                         scale, speculate=speculate, **(extra if mt == "gemma3" else {}),
                          kv_cache_dtype=resolve_kv_dtype(kv_cache_dtype, dtype), max_prefill_tokens=max_prefill_tokens)
     weights.close()
     return runner

@@ -70,12 +70,14 @@ def rope_and_cache(qkv, positions, cos_sin, slots, k_cache, v_cache, num_heads, 
 
 
 def paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale, window=-1, softcap=0.0,
-                    k_scale=None, v_scale=None, max_q=None, max_kv=None):
+                    k_scale=None, v_scale=None, max_q=None, max_kv=None, horizon=None):
+    """``horizon`` (optional int32 ``[T]``): last KV position each query row may see when that is past its own
+    position (image rows that attend to their whole image); ``None`` is plain causal attention."""
     if use_native(q):
         return native().paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale,
-                                        window, softcap, k_scale, v_scale, max_q, max_kv)
+                                        window, softcap, k_scale, v_scale, max_q, max_kv, horizon=horizon)
     return ref.paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale, window,
-                               softcap, k_scale, v_scale)
+                               softcap, k_scale, v_scale, horizon=horizon)
 
 
 def act_and_mul(gate_up, act="silu"):

@@ -109,6 +109,8 @@ struct Params {
   __nv_bfloat16* out;           // [T, Hq, D]
   float* part_o;                // decode partials [B, Hq, nsplit, D]
   float* part_ml;               // [B, Hq, nsplit, 2]
+  const int* horizon;           // optional [T]: last KV position query row t may see (>= its own position);
+                                // rows of an image block that attend to each other in both directions (prefill only)
   int max_blocks, block_size, bs_shift, Hq, Hkv, num_blocks;   // block_size == 1 << bs_shift
   float scale, softcap;
   int window;
@@ -223,12 +225,15 @@ __device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: 2 ulp, -i
 template <int NT>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2], float (&alpha)[2],
                                                int tbase, int pos0, int pos1, int L, int window, float scale_log2,
-                                               float softcap, float raw_scale) {
+                                               float softcap, float raw_scale, int hz0 = -1, int hz1 = -1) {
+  // hz0 / hz1: last visible KV position of the two rows (defaults: their own positions, i.e. causal)
+  if (hz0 < 0) hz0 = pos0;
+  if (hz1 < 0) hz1 = pos1;
   const int lane = threadIdx.x & 31;
   float mx[2] = {-INFINITY, -INFINITY};
   // a tile that lies entirely below the diagonal of all 16 rows of the warp, inside the window and inside the
   // sequence needs no per-element mask (warp-uniform test: the warp's first row is pos0 - lane / 4)
-  const int row_lo = pos0 - (lane >> 2), row_hi = row_lo + 15, t_last = tbase + NT * 8 - 1;
+  const int row_lo = hz0 - (lane >> 2), row_hi = pos0 - (lane >> 2) + 15, t_last = tbase + NT * 8 - 1;
   const bool plain = softcap <= 0.f && t_last <= row_lo && t_last < L && (window <= 0 || tbase > row_hi - window);
   if (plain) {
 #pragma unroll
@@ -245,10 +250,11 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
       for (int e = 0; e < 4; ++e) {
         const int t = tbase + i * 8 + (lane & 3) * 2 + (e & 1);
         const int pos = (e < 2) ? pos0 : pos1;
+        const int hz = (e < 2) ? hz0 : hz1;
         float v = s[i][e];
         if (softcap > 0.f) v = softcap * tanhf(v * raw_scale / softcap) * kLog2e;
         else v = v * scale_log2;
-        const bool ok = t <= pos && t < L && (window <= 0 || t > pos - window);
+        const bool ok = t <= hz && t < L && (window <= 0 || t > pos - window);
         v = ok ? v : -INFINITY;
         s[i][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -320,7 +326,7 @@ prefill_kernel(Params p) {
   const int pos_last = min(L - 1, pos_first + kTile - 1);
   int t_lo = 0;
   if (p.window > 0) t_lo = max(0, pos_first - p.window + 1) / kTile * kTile;
-  const int t_hi = pos_last + 1;                           // exclusive
+  const int t_hi = p.horizon != nullptr ? L : pos_last + 1;   // exclusive; with horizons a row may see up to L - 1
   const int ntiles = (t_hi - t_lo + kTile - 1) / kTile;
 
   // ---- Q tile -> shared (bf16, or fp16 for e4m3 pages) ----
@@ -367,6 +373,12 @@ prefill_kernel(Params p) {
   const float scale_log2 = raw_scale * kLog2e;
   const int pos0 = pos_first + warp * 16 + (lane >> 2);
   const int pos1 = pos0 + 8;
+  int hz0 = pos0, hz1 = pos1;
+  if (p.horizon != nullptr) {
+    const int r0 = row_base + warp * 16 + (lane >> 2), r1 = r0 + 8;
+    if (r0 < n) hz0 = max(pos0, min(p.horizon[q_begin + r0], L - 1));
+    if (r1 < n) hz1 = max(pos1, min(p.horizon[q_begin + r1], L - 1));
+  }
 
   for (int j = 0; j < ntiles; ++j) {
     const int stg = j & 1;
@@ -394,7 +406,8 @@ prefill_kernel(Params p) {
     float s[8][4];
     qk_warp<D, 8, FP8>(qf, cK, 0, s);
     float alpha[2];
-    softmax_update<8>(s, m, l, alpha, t_lo + j * kTile, pos0, pos1, L, p.window, scale_log2, p.softcap, raw_scale);
+    softmax_update<8>(s, m, l, alpha, t_lo + j * kTile, pos0, pos1, L, p.window, scale_log2, p.softcap, raw_scale,
+                      hz0, hz1);
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
       o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
@@ -1303,11 +1316,28 @@ int tgi_attn_status(int reset) {
   return v;
 }
 
+// `horizon` (optional, prefill only): per query row the last KV position it may attend to; null = causal
+int tgi_paged_attention_ex(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                           const int* cu_seqlens_q, const int* kv_lens, const float* k_scale, const float* v_scale,
+                           void* out, float* part_o, float* part_ml, int B, int max_q, int max_blocks, int block_size,
+                           int num_blocks, int Hq, int Hkv, int D, float scale, float softcap, int window, int nsplit,
+                           int fp8_kv, const int* horizon, cudaStream_t stream);
+
 int tgi_paged_attention(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
                         const int* cu_seqlens_q, const int* kv_lens, const float* k_scale, const float* v_scale,
                         void* out, float* part_o, float* part_ml, int B, int max_q, int max_blocks, int block_size,
                         int num_blocks, int Hq, int Hkv, int D, float scale, float softcap, int window, int nsplit,
                         int fp8_kv, cudaStream_t stream) {
+  return tgi_paged_attention_ex(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, k_scale, v_scale, out, part_o,
+                                part_ml, B, max_q, max_blocks, block_size, num_blocks, Hq, Hkv, D, scale, softcap, window,
+                                nsplit, fp8_kv, nullptr, stream);
+}
+
+int tgi_paged_attention_ex(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                           const int* cu_seqlens_q, const int* kv_lens, const float* k_scale, const float* v_scale,
+                           void* out, float* part_o, float* part_ml, int B, int max_q, int max_blocks, int block_size,
+                           int num_blocks, int Hq, int Hkv, int D, float scale, float softcap, int window, int nsplit,
+                           int fp8_kv, const int* horizon, cudaStream_t stream) {
   if (B <= 0 || max_q <= 0) return 0;
   if (Hq % Hkv != 0) return -10;
   Params p;
@@ -1322,6 +1352,7 @@ int tgi_paged_attention(const void* q, const void* k_cache, const void* v_cache,
   p.out = static_cast<__nv_bfloat16*>(out);
   p.part_o = part_o;
   p.part_ml = part_ml;
+  p.horizon = max_q > 1 ? horizon : nullptr;
   p.max_blocks = max_blocks;
   p.block_size = block_size;
   if (block_size <= 0 || (block_size & (block_size - 1)) != 0) return -13;   // pages hold a power-of-two token count

@@ -49,7 +49,7 @@ def load():
                 "(the sm_100a kernels are required on CUDA devices)")
     _LIB = ctypes.CDLL(str(_LIB_PATH))
     for name in ("tgi_gemm_bf16", "tgi_gemm_fp8_block", "tgi_norm", "tgi_act_mul", "tgi_quant_act",
-                 "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention",
+                 "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention", "tgi_paged_attention_ex",
                  "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status", "tgi_lora_shrink",
                  "tgi_lora_expand"):
         getattr(_LIB, name).restype = c_int
@@ -306,7 +306,7 @@ def rope_and_cache(qkv, positions, cos_sin, slots, k_cache, v_cache, num_heads, 
 
 # ---- attention ---------------------------------------------------------------------------------
 def paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, scale, window=-1, softcap=0.0,
-                    k_scale=None, v_scale=None, max_q=None, max_kv=None, nsplit: Optional[int] = None):
+                    k_scale=None, v_scale=None, max_q=None, max_kv=None, nsplit: Optional[int] = None, horizon=None):
     lib = load()
     T, Hq, D = q.shape
     nblk, bs, Hkv, _ = k_cache.shape
@@ -332,12 +332,12 @@ def paged_attention(q, k_cache, v_cache, block_tables, cu_seqlens_q, kv_lens, sc
             part_o, part_ml = st.attn_part_o, st.attn_part_ml
     else:
         nsplit = 1
-    _check(lib.tgi_paged_attention(
+    _check(lib.tgi_paged_attention_ex(
         _ptr(q.contiguous()), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(cu_seqlens_q), _ptr(kv_lens),
         _ptr(k_scale if fp8 else None), _ptr(v_scale if fp8 else None), _ptr(out), _ptr(part_o), _ptr(part_ml),
         c_int(B), c_int(max_q), c_int(block_tables.shape[1]), c_int(bs), c_int(nblk), c_int(Hq), c_int(Hkv), c_int(D),
         c_float(scale), c_float(softcap), c_int(window if window and window > 0 else -1), c_int(nsplit),
-        c_int(1 if fp8 else 0), _stream()), "paged_attention")
+        c_int(1 if fp8 else 0), _ptr(horizon), _stream()), "paged_attention")
     return out
 
 

@@ -127,8 +127,10 @@ def paged_attention(
     v_scale: Optional[torch.Tensor] = None,
     max_q: Optional[int] = None,
     max_kv: Optional[int] = None,
+    horizon: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Causal attention of ragged queries over paged KV (covers prefill, chunked prefill and decode).
+    ``horizon[t]`` (optional) replaces the causal limit of query row ``t`` by a later position.
 
     Query ``i`` (0-based inside its sequence's chunk of ``n`` queries) of a sequence with ``L`` KV
     tokens sits at absolute position ``L - n + i`` and attends to KV positions ``<=`` its own
@@ -168,7 +170,8 @@ def paged_attention(
             scores = softcap * torch.tanh(scores / softcap)
         qpos = torch.arange(L - n, L, device=q.device).unsqueeze(1)
         kpos = torch.arange(L, device=q.device).unsqueeze(0)
-        mask = kpos <= qpos
+        limit = qpos if horizon is None else torch.maximum(qpos, horizon[s:e].long().clamp(max=L - 1).unsqueeze(1))
+        mask = kpos <= limit
         if window > 0:
             mask &= kpos > qpos - window
         scores = scores.masked_fill(~mask.unsqueeze(0), float("-inf"))

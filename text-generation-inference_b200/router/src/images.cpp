@@ -270,6 +270,13 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     if (config.has("vision_end_token_id")) ++n;
     return n;
   }
+  if (mt == "gemma3") {
+    // fixed number of pooled rows per image, wrapped in begin-of-image / end-of-image tokens by the runner
+    uint32_t n = config.has("mm_tokens_per_image") ? static_cast<uint32_t>(config["mm_tokens_per_image"].as_double()) : 256;
+    if (config.has("boi_token_index") || config.has("boi_token_id")) ++n;
+    if (config.has("eoi_token_index") || config.has("eoi_token_id")) ++n;
+    return n;
+  }
   if (mt == "idefics2") {
     // perceiver resampler: a fixed number of latents per image
     const json::Value& pc = config.has("perceiver_config") ? config["perceiver_config"] : vis;
