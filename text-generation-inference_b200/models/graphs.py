@@ -65,6 +65,7 @@ class _Bucket:
             lm_head_indices=None,
         )
         self.token_adapter = d[self.off_ad:self.off_ad + bs]
+        self.staged = torch.cuda.Event()        # recorded after every host-to-device copy of the static buffer
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None          # full logits [bs, V] (gathered-head graphs)
         self.local_logits: Optional[torch.Tensor] = None    # vocabulary shard [bs, V / tp] (local-head graphs)
@@ -146,6 +147,7 @@ class DecodeGraphs:
         if lora and bs not in self.lora_buckets:
             self.capture(bs, lora=True)
         b = self.lora_buckets[bs] if lora else self.buckets[bs]
+        b.staged.synchronize()      # the pinned buffer is rewritten below: its previous copy must have left the host
         h = b.host_np
         ids = h[b.off_ids:b.off_ids + bs]
         pos = h[b.off_pos:b.off_pos + bs]
@@ -170,6 +172,7 @@ class DecodeGraphs:
             slots[n:] = -1
             kv[n:] = 0
         b.dev.copy_(b.host, non_blocking=True)
+        b.staged.record()
         b.graph.replay()
         row_owner = [(i, 0) for i in range(n)]
         self.last = (b, n)
@@ -180,6 +183,7 @@ class DecodeGraphs:
         and KV lengths are updated in place (block tables and adapter indices stay), so the host work between
         two decode steps is a handful of vector operations.  The caller has appended ``next_ids`` to the sequences."""
         b, n = self.last
+        b.staged.synchronize()
         h = b.host_np
         h[b.off_ids:b.off_ids + n] = next_ids
         h[b.off_pos:b.off_pos + n] += 1
@@ -188,6 +192,7 @@ class DecodeGraphs:
         for i, s in enumerate(seqs):
             slots[i] = s.slots[len(s.ids) - 1]
         b.dev.copy_(b.host, non_blocking=True)
+        b.staged.record()
         b.graph.replay()
         return (b.logits[:n] if b.logits is not None else None), [(i, 0) for i in range(n)]
 
