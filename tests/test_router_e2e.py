@@ -350,3 +350,16 @@ def test_request_spans_reach_the_otlp_collector(stack):
     # requests without a trace context start a new trace
     assert any(sp["traceId"] != trace_id and "parentSpanId" not in sp
                for doc in stack["otlp"] for sp in doc["resourceSpans"][0]["scopeSpans"][0]["spans"])
+
+
+def test_openapi_document_and_docs_page(stack):
+    status, body = _get(stack["port"], "/api-doc/openapi.json")[:2]
+    assert status == 200
+    doc = json.loads(body)
+    assert doc["openapi"].startswith("3.") and "/generate" in doc["paths"] and "/v1/chat/completions" in doc["paths"]
+    params = doc["components"]["schemas"]["GenerateParameters"]["properties"]
+    assert {"top_p", "grammar", "adapter_id", "top_n_tokens"} <= set(params)
+    ref = doc["paths"]["/generate"]["post"]["requestBody"]["content"]["application/json"]["schema"]["$ref"]
+    assert ref.split("/")[-1] in doc["components"]["schemas"]
+    status, page = _get(stack["port"], "/docs")[:2]
+    assert status == 200 and "openapi.json" in (page if isinstance(page, str) else page.decode())

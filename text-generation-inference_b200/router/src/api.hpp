@@ -130,4 +130,8 @@ class Router {
 json::Value tools_to_grammar_schema(const json::Value& tools, const json::Value& tool_choice);
 std::string finish_reason_str(uint32_t r, bool openai);
 
+// OpenAPI document of the HTTP surface (openapi.cpp) and a self-contained page that renders it
+json::Value openapi_schema(const std::string& version);
+std::string openapi_html();
+
 }  // namespace api

@@ -366,19 +366,9 @@ void Router::install(http::Server& s) {
     r.send(200, "application/json", o.dump());
   });
   s.route("GET", "/api-doc/openapi.json", [this](const http::Request&, http::Response& r) {
-    Value o = Value::object();
-    o.set("openapi", "3.0.3");
-    Value inf = Value::object();
-    inf.set("title", "Text Generation Inference (B200)");
-    inf.set("version", cfg_.version);
-    o.set("info", inf);
-    Value paths = Value::object();
-    for (const char* p : {"/generate", "/generate_stream", "/v1/chat/completions", "/v1/completions", "/tokenize",
-                          "/chat_tokenize", "/info", "/health", "/metrics", "/v1/models", "/invocations"})
-      paths.set(p, Value::object());
-    o.set("paths", paths);
-    r.send(200, "application/json", o.dump());
+    r.send(200, "application/json", openapi_schema(cfg_.version).dump());
   });
+  s.route("GET", "/docs", [](const http::Request&, http::Response& r) { r.send(200, "text/html", openapi_html()); });
 }
 
 }  // namespace api

@@ -141,6 +141,10 @@ pb::Batch warmup_batch(uint32_t max_input_tokens, uint32_t max_prefill_tokens, u
 
 int main(int argc, char** argv) {
   Args args(argc, argv);
+  if (argc > 1 && std::string(argv[1]) == "print-schema") {   // OpenAPI document on stdout, nothing else started
+    std::cout << api::openapi_schema("0").dump() << std::endl;
+    return 0;
+  }
   if (args.flag("help")) {
     std::cout << "tgi-b200-router --master-shard-uds-path PATH --tokenizer-name DIR [--port 3000] [--hostname 0.0.0.0]\n"
                  "  [--max-concurrent-requests 128] [--max-best-of 2] [--max-stop-sequences 4] [--max-top-n-tokens 5]\n"
