@@ -205,6 +205,7 @@ int main(int argc, char** argv) {
 
     sched::Metrics metrics(max_input, max_total);
     metrics.gauge_set("tgi_batch_max_total_tokens", max_batch_total);
+    metrics.gauge_set("tgi_batch_total_tokens", max_batch_total);
     sched::QueueConfig qc;
     qc.requires_padding = info.requires_padding;
     qc.block_size = std::max(1u, info.block_size);

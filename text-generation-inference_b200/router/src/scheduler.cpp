@@ -363,6 +363,7 @@ void Backend::send_generation(Entry& e, pb::Generation& g, bool& finished) {
     e.stream->push(std::move(ev));
   }
   const size_t n = g.tokens.ids.size();
+  if (metrics_ && n > 0) metrics_->histogram_value("tgi_request_skipped_tokens", static_cast<double>(n - 1));   // speculated tokens accepted
   for (size_t i = 0; i < n; ++i) {
     StreamEvent ev;
     ev.token.id = g.tokens.ids[i];
