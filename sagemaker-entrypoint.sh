@@ -1,18 +1,26 @@
 #!/bin/bash
-# SageMaker entry point: the platform passes configuration in environment variables and expects the server on
-# port 8080 with the model under /opt/ml/model (or a hub id in HF_MODEL_ID).
-if [[ -z "${HF_MODEL_ID}" ]]; then
+# SageMaker entry point.  The platform describes the deployment in environment variables, mounts an uploaded
+# model under /opt/ml/model and expects the server on port 8080.  The launcher reads every flag from the
+# environment as well (--num-shard <-> NUM_SHARD), so the platform's names only have to be translated.
+set -u
+declare -A translate=(
+  [HF_MODEL_ID]=MODEL_ID
+  [HF_MODEL_REVISION]=REVISION
+  [HF_MODEL_QUANTIZE]=QUANTIZE
+  [HF_MODEL_TRUST_REMOTE_CODE]=TRUST_REMOTE_CODE
+  [SM_NUM_GPUS]=NUM_SHARD
+)
+for platform_name in "${!translate[@]}"; do
+  value="${!platform_name:-}"
+  [[ -n "$value" ]] && export "${translate[$platform_name]}=$value"
+done
+if [[ -z "${MODEL_ID:-}" ]]; then
   if [[ -d /opt/ml/model ]]; then
-    export HF_MODEL_ID=/opt/ml/model
+    export MODEL_ID=/opt/ml/model
   else
-    echo "HF_MODEL_ID must be set" >&2
-    exit 1
+    echo "sagemaker-entrypoint: set HF_MODEL_ID or mount a model at /opt/ml/model" >&2
+    exit 64
   fi
 fi
-export MODEL_ID="${HF_MODEL_ID}"
-if [[ -n "${HF_MODEL_REVISION}" ]]; then export REVISION="${HF_MODEL_REVISION}"; fi
-if [[ -n "${SM_NUM_GPUS}" ]]; then export NUM_SHARD="${SM_NUM_GPUS}"; fi
-if [[ -n "${HF_MODEL_QUANTIZE}" ]]; then export QUANTIZE="${HF_MODEL_QUANTIZE}"; fi
-if [[ -n "${HF_MODEL_TRUST_REMOTE_CODE}" ]]; then export TRUST_REMOTE_CODE="${HF_MODEL_TRUST_REMOTE_CODE}"; fi
 ldconfig 2>/dev/null || true
 exec tgi-b200-launcher --port 8080 "$@"
