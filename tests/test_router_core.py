@@ -410,3 +410,37 @@ def test_tool_grammar_schema(rt):
     assert set(s["$functions"]) == {"f"}
     with pytest.raises(ValueError):
         rt.tools_to_grammar_schema(json.dumps([tool]), json.dumps({"type": "function", "function": {"name": "g"}}))
+
+
+def test_image_token_counts_match_the_runners(rt):
+    """The router reserves exactly the rows the runners produce for an image (Qwen2-VL: dynamic resolution)."""
+    import json
+
+    from tgi_b200.models.qwen2_vl import smart_resize
+
+    vis = {"patch_size": 14, "spatial_merge_size": 2, "min_pixels": 56 * 56, "max_pixels": 28 * 28 * 1280}
+    cfg = {"model_type": "qwen2_vl", "vision_config": vis, "vision_start_token_id": 1, "vision_end_token_id": 2}
+    for w, h in [(1, 1), (52, 40), (640, 480), (1920, 1080), (4000, 3000), (30, 3000), (999, 1001)]:
+        rh, rw = smart_resize(h, w, 28, vis["min_pixels"], vis["max_pixels"])
+        assert rt.tokens_per_image(json.dumps(cfg), w, h) == (rh // 28) * (rw // 28) + 2, (w, h)
+    cfg25 = dict(cfg, model_type="qwen2_5_vl")
+    assert rt.tokens_per_image(json.dumps(cfg25), 640, 480) == rt.tokens_per_image(json.dumps(cfg), 640, 480)
+    assert rt.tokens_per_image(json.dumps({"model_type": "idefics2", "vision_config": {},
+                                           "perceiver_config": {"resampler_n_latents": 64}}), 10, 10) == 64
+    assert rt.tokens_per_image(json.dumps({"model_type": "idefics3", "scale_factor": 2,
+                                           "vision_config": {"image_size": 364, "patch_size": 14}}), 10, 10) == 169
+    assert rt.tokens_per_image(json.dumps({"model_type": "gemma3", "mm_tokens_per_image": 256, "boi_token_index": 1,
+                                           "eoi_token_index": 2, "vision_config": {}}), 10, 10) == 258
+    assert rt.tokens_per_image(json.dumps({"model_type": "llama"}), 10, 10) == 0
+
+
+def test_traceparent_parsing(rt):
+    ok, tid, sid, sampled = rt.parse_traceparent("00-4bf92f3577b34da6a3ce929d0e0e4736-00f067aa0ba902b7-01")
+    assert ok and tid == "4bf92f3577b34da6a3ce929d0e0e4736" and sid == "00f067aa0ba902b7" and sampled
+    assert rt.parse_traceparent("00-4bf92f3577b34da6a3ce929d0e0e4736-00f067aa0ba902b7-00")[3] is False
+    for bad in ["", "garbage", "ff-4bf92f3577b34da6a3ce929d0e0e4736-00f067aa0ba902b7-01",
+                "00-00000000000000000000000000000000-00f067aa0ba902b7-01",
+                "00-4bf92f3577b34da6a3ce929d0e0e4736-0000000000000000-01",
+                "00-4BF92F3577B34DA6A3CE929D0E0E4736-00f067aa0ba902b7-01",
+                "00-4bf92f3577b34da6a3ce929d0e0e4736-00f067aa0ba902b7-01-extra"]:
+        assert rt.parse_traceparent(bad)[0] is False, bad

@@ -6,6 +6,8 @@
 #include <pybind11/stl.h>
 
 #include "api.hpp"
+#include "images.hpp"
+#include "trace.hpp"
 #include "json.hpp"
 #include "pb.hpp"
 #include "radix.hpp"
@@ -78,6 +80,13 @@ py::dict event_to_dict(const sched::StreamEvent& ev) {
 }  // namespace
 
 PYBIND11_MODULE(_router_test, m) {
+  m.def("tokens_per_image", [](const std::string& config_json, uint32_t width, uint32_t height) {
+    return images::tokens_per_image(json::Value::parse(config_json), width, height);
+  });
+  m.def("parse_traceparent", [](const std::string& h) {
+    const trace::Context c = trace::parse_traceparent(h);
+    return py::make_tuple(c.valid(), c.trace_id, c.span_id, c.sampled);
+  });
   py::class_<sched::BlockAllocation>(m, "BlockAllocation")
       .def_readonly("allocation_id", &sched::BlockAllocation::allocation_id)
       .def_readonly("blocks", &sched::BlockAllocation::blocks)
