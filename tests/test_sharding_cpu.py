@@ -31,3 +31,26 @@ def test_mixtral_experts_tp_and_ep(tmp_path, mode):
                                                   max_pos=256, model_type="mixtral", num_local_experts=4,
                                                   num_experts_per_tok=2))
     _run(tmp_path, 29812 + (mode == "ep"), {"TGI_B200_MOE_PARALLEL": mode})
+
+
+def test_pin_cpu_threads_splits_the_cores():
+    import os
+
+    import torch
+
+    from tgi_b200.parallel.dist import pin_cpu_threads
+
+    before = os.sched_getaffinity(0)
+    threads = torch.get_num_threads()
+    try:
+        cpus = sorted(before)
+        if len(cpus) >= 2:
+            a = pin_cpu_threads(0, 2, cpus)
+            assert os.sched_getaffinity(0) == set(a) and len(a) == len(cpus) // 2
+            b = pin_cpu_threads(1, 2, cpus)
+            assert not set(a) & set(b)
+        # more shards than cores: nothing is pinned
+        assert pin_cpu_threads(0, len(cpus) + 1, cpus) == cpus
+    finally:
+        os.sched_setaffinity(0, before)
+        torch.set_num_threads(threads)

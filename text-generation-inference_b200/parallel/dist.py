@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import os
 from datetime import timedelta
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -78,6 +78,25 @@ def initialize_torch_distributed(timeout_s: Optional[float] = None) -> Tuple[obj
         dist.init_process_group(backend=backend, world_size=world, rank=rank,
                                 timeout=timedelta(seconds=timeout_s), **kwargs)
     return dist.group.WORLD, rank, world
+
+
+def pin_cpu_threads(local_rank: int, local_world: int, cpus: Optional[List[int]] = None) -> List[int]:
+    """Give every shard process its own slice of the host cores (reference: ``init_cpu_threads_env``,
+    ``models/flash_causal_lm.py:91-122``): the tokenizer threads, the Python step loop and the torch
+    intra-op pool of one shard then do not migrate onto the cores of another.  The cores the process may
+    use are split into ``local_world`` contiguous slices (contiguous ids share a socket on the usual
+    enumerations); returns the slice taken.  Opt-in through ``TGI_B200_PIN_CPU=1`` in the shard CLI."""
+    cpus = sorted(cpus if cpus is not None else os.sched_getaffinity(0))
+    per = len(cpus) // max(local_world, 1)
+    if per < 1:
+        return cpus                      # fewer cores than shards: leave the scheduler alone
+    mine = cpus[local_rank * per:(local_rank + 1) * per]
+    try:
+        os.sched_setaffinity(0, mine)
+    except (AttributeError, OSError):
+        return cpus
+    torch.set_num_threads(max(1, min(len(mine), int(os.environ.get("OMP_NUM_THREADS", len(mine))))))
+    return mine
 
 
 def all_reduce(t: torch.Tensor, group) -> torch.Tensor:

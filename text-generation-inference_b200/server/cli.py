@@ -38,6 +38,11 @@ def cmd_serve(a):
             if os.environ.get(var) is None:
                 raise SystemExit(f"{var} must be set when sharded is True")
     lora = _parse_lora(os.environ.get("LORA_ADAPTERS", "")) if os.environ.get("LORA_ADAPTERS") else []
+    if os.environ.get("TGI_B200_PIN_CPU") == "1":
+        from ..parallel.dist import pin_cpu_threads
+
+        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")))
+        pin_cpu_threads(int(os.environ.get("LOCAL_RANK", os.environ.get("RANK", "0"))) % max(local_world, 1), local_world)
     if a.otlp_endpoint:
         from .tracing import setup_tracing
 
