@@ -25,9 +25,11 @@ def test_nobody_finishes_rules():
 
 
 def test_decode_signature_tracks_identity_and_length():
-    sig = FlashCausalLM._decode_signature
+    sig, same = FlashCausalLM._decode_signature, FlashCausalLM._same_step
     a, b = _seq(10, 20, 3), _seq(12, 20, 5)
     s0 = sig([a, b])
-    assert s0 == sig([a, b]) and s0 != sig([b, a]) and s0 != sig([a])
+    assert same(s0, [a, b]) and not same(s0, [b, a]) and not same(s0, [a])
+    # an equal-looking but different sequence object is a different step
+    assert not same(s0, [a, _seq(12, 20, 5)])
     a.ids.append(1)
-    assert sig([a, b]) != s0
+    assert not same(s0, [a, b]) and same(sig([a, b]), [a, b])

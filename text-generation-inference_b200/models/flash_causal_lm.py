@@ -399,8 +399,15 @@ class FlashCausalLM(Model):
 
     @staticmethod
     def _decode_signature(seqs) -> tuple:
-        """Identity of a decode step: which sequences, and how long each is."""
-        return tuple(id(s) for s in seqs), tuple(len(s.ids) for s in seqs)
+        """Identity of a decode step: which sequences (the objects themselves: holding them keeps their identity
+        from being recycled by a later batch), and how long each is."""
+        return tuple(seqs), tuple(len(s.ids) for s in seqs)
+
+    @staticmethod
+    def _same_step(sig: tuple, seqs) -> bool:
+        held, lens = sig
+        return (len(held) == len(seqs) and all(a is b for a, b in zip(held, seqs))
+                and all(n == len(s.ids) for n, s in zip(lens, seqs)))
 
     @staticmethod
     def _nobody_finishes(seqs, next_ids) -> bool:
@@ -440,7 +447,7 @@ class FlashCausalLM(Model):
                               and any(s.adapter_index > 0 for s in seqs)))
         pre, self._prelaunched = self._prelaunched, None
         if use_graph:
-            if (pre is not None and pre[1] is self.graphs and pre[0] == self._decode_signature(seqs)
+            if (pre is not None and pre[1] is self.graphs and self._same_step(pre[0], seqs)
                     and all(c == 1 for c in counts)):
                 logits, row_owner = pre[2]          # this step's replay is already on the stream
                 self.overlap_hits += 1

@@ -65,6 +65,7 @@ class _Bucket:
             lm_head_indices=None,
         )
         self.token_adapter = d[self.off_ad:self.off_ad + bs]
+        self.row_owner: List[Optional[tuple]] = [None] * bs   # (block list, its length) whose table sits in row i
         self.staged = torch.cuda.Event()        # recorded after every host-to-device copy of the static buffer
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None          # full logits [bs, V] (gathered-head graphs)
@@ -161,7 +162,12 @@ class DecodeGraphs:
             slots[i] = s.slots[p]
             kv[i] = p + 1
             nb = len(s.blocks)
-            bt[i, :nb] = s.blocks
+            held = b.row_owner[i]
+            if held is None or held[0] is not s.blocks or held[1] != nb:
+                # the block table row of a sequence is written once per placement; the bucket keeps a reference to
+                # the list, so "same list object" cannot be a recycled identity
+                bt[i, :nb] = s.blocks
+                b.row_owner[i] = (s.blocks, nb)
         if lora:
             ad = h[b.off_ad:b.off_ad + bs]
             ad[:n] = [s.adapter_index for s in seqs]
