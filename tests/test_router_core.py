@@ -444,3 +444,16 @@ def test_traceparent_parsing(rt):
                 "00-4BF92F3577B34DA6A3CE929D0E0E4736-00f067aa0ba902b7-01",
                 "00-4bf92f3577b34da6a3ce929d0e0e4736-00f067aa0ba902b7-01-extra"]:
         assert rt.parse_traceparent(bad)[0] is False, bad
+
+
+def test_llava_next_row_counts_match_the_runner(rt):
+    import json
+
+    from tgi_b200.models.llava_next import anyres_rows
+
+    pins = [[336, 672], [672, 336], [672, 672], [1008, 336], [336, 1008]]
+    cfg = {"model_type": "llava_next", "image_grid_pinpoints": pins, "vision_config": {"image_size": 336, "patch_size": 14}}
+    for w, h in [(640, 480), (480, 640), (1920, 1080), (100, 1000), (1000, 100), (336, 336), (50, 37), (2000, 1999)]:
+        assert rt.tokens_per_image(json.dumps(cfg), w, h) == anyres_rows((h, w), pins, 336, 24), (w, h)
+    plain = {"model_type": "llava_next", "vision_config": {"image_size": 336, "patch_size": 14}}
+    assert rt.tokens_per_image(json.dumps(plain), 640, 480) == 576

@@ -11,8 +11,8 @@ forward per step for all of them), projected to the text hidden size and written
 embeddings of the placeholder rows; the language model then runs on ``inputs_embeds`` unchanged
 (same paged attention, same CUDA-graph decode, since decode steps never contain image rows).
 
-Covered families: LLaVA-style (CLIP tower, 2-layer MLP projector, optional class-token drop; the
-base-resolution view of llava_next), PaliGemma-style (SigLIP tower, linear projector, embedding
+Covered families: LLaVA-style (CLIP tower, 2-layer MLP projector, optional class-token drop; LLaVA-NeXT
+with its any-resolution tiling in ``models/llava_next.py``), PaliGemma-style (SigLIP tower, linear projector, embedding
 scale), Idefics2 (SigLIP-style tower, gated-MLP projection and a perceiver resampler that compresses
 an image to a fixed number of latents; ``custom_modeling/idefics2.py``) and Idefics3 / SmolVLM
 (pixel-shuffle connector; ``custom_modeling/idefics3.py``) and Gemma-3 (SigLIP tower, average-pooled
@@ -138,12 +138,17 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
     norm = (CLIP_MEAN, CLIP_STD)
 
     @classmethod
+    def image_payload(cls, data: bytes):
+        """What the runner needs of one image, and the number of placeholder rows it takes in the prompt."""
+        return preprocess_image(data, cls.image_size, *cls.norm), cls.tokens_per_image
+
+    @classmethod
     def batch_tokenized_inputs(cls, requests, tokenizer) -> List[List[int]]:
         out = []
         cls._pending_images = []
         for r in requests:
             ids: List[int] = []
-            images: List[Tuple[int, torch.Tensor]] = []     # (first placeholder position, pixels)
+            images: List[Tuple[int, object, int]] = []      # (first placeholder position, payload, rows)
             chunks = list(r.input_chunks.chunks) if r.HasField("input_chunks") else []
             if not chunks:
                 ids = list(tokenizer(r.inputs, truncation=False, add_special_tokens=r.add_special_tokens)["input_ids"])
@@ -154,19 +159,19 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
                                          add_special_tokens=r.add_special_tokens and first_text)["input_ids"])
                     first_text = False
                 else:
-                    pixels = preprocess_image(c.image.data, cls.image_size, *cls.norm)
+                    payload, rows = cls.image_payload(c.image.data)
                     if cls.image_start_id is not None:
                         ids.append(cls.image_start_id)
-                    images.append((len(ids), pixels))
-                    ids.extend([cls.image_token_id] * cls.tokens_per_image)
+                    images.append((len(ids), payload, rows))
+                    ids.extend([cls.image_token_id] * rows)
                     if cls.image_end_id is not None:
                         ids.append(cls.image_end_id)
             if r.truncate and len(ids) > r.truncate:
                 cut = len(ids) - r.truncate
-                if any(pos < cut for pos, _ in images):
+                if any(pos < cut for pos, _, _ in images):
                     raise ValueError("truncation would cut through an image; raise `truncate` or shorten the prompt")
                 ids = ids[cut:]
-                images = [(pos - cut, px) for pos, px in images]
+                images = [(pos - cut, px, rows) for pos, px, rows in images]
             out.append(ids)
             cls._pending_images.append(images)
         return out
@@ -214,6 +219,10 @@ class VlmCausalLM(FlashCausalLM):
             out = out * self.image_embed_scale
         return out
 
+    def image_features(self, payloads: list) -> List[torch.Tensor]:
+        """Rows ``[rows_i, hidden_text]`` of every image of a step (one tower forward for all of them)."""
+        return list(self.encode_images(torch.stack(payloads)))
+
     def build_meta(self, batch, counts):
         meta, row_owner = super().build_meta(batch, counts)
         # rows of this step that are image placeholders: (row in the ragged batch, image, offset)
@@ -222,8 +231,8 @@ class VlmCausalLM(FlashCausalLM):
         for s, n in zip(batch.seqs, counts):
             if s.prefilling and n > 0:
                 lo, hi = s.cache_len, s.cache_len + n
-                for pos, px in getattr(s, "images", []):
-                    a, b = max(pos, lo), min(pos + self.tokens_per_image, hi)
+                for pos, px, rows in getattr(s, "images", []):
+                    a, b = max(pos, lo), min(pos + rows, hi)
                     if a < b:
                         jobs.append((t + a - lo, b - a, px, a - pos, id(px)))
             t += n
@@ -234,10 +243,10 @@ class VlmCausalLM(FlashCausalLM):
             for s, n in zip(batch.seqs, counts):
                 if s.prefilling and n > 0:
                     lo, hi = s.cache_len, s.cache_len + n
-                    for pos, _ in getattr(s, "images", []):
-                        a, b = max(pos, lo), min(pos + self.tokens_per_image, hi)
+                    for pos, _, rows in getattr(s, "images", []):
+                        a, b = max(pos, lo), min(pos + rows, hi)
                         if a < b:
-                            hz[t + a - lo:t + b - lo] = pos + self.tokens_per_image - 1
+                            hz[t + a - lo:t + b - lo] = pos + rows - 1
                 t += n
             meta.attn_horizon = hz
         if jobs:
@@ -247,10 +256,10 @@ class VlmCausalLM(FlashCausalLM):
                 if key not in uniq:
                     uniq[key] = len(stack)
                     stack.append(px)
-            feats = self.encode_images(torch.stack(stack))
+            feats = self.image_features(stack)
             embeds = self.model.embed_tokens(meta.input_ids, meta.positions).clone()
             for row, n, _, off, key in jobs:
-                embeds[row:row + n] = feats[uniq[key], off:off + n].to(embeds.dtype)
+                embeds[row:row + n] = feats[uniq[key]][off:off + n].to(embeds.dtype)
             meta.inputs_embeds = embeds
         return meta, row_owner
 
@@ -458,8 +467,15 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
     hidden = int(text_cfg.get("hidden_size"))
     comm = make_comm(process_group, rank, world, device, hidden, int(max_prefill_tokens or 4096))
     model = CausalDecoder(text_cfg, weights, comm=comm, prefix=prefix)
-    runner = VlmCausalLM(model, tower, projector, tokenizer, dtype, device, rank, world, image_token, drop_cls,
-                         scale, speculate=speculate, **(extra if mt == "gemma3" else {}),
+    runner_cls, extra_kw = VlmCausalLM, (extra if mt == "gemma3" else {})
+    newline = next((n for n in ("image_newline", "model.image_newline") if weights.has_tensor(n)), None)
+    if mt == "llava_next" and newline is not None and cfg.get("image_grid_pinpoints"):
+        from .llava_next import LlavaNextCausalLM     # any-resolution tiling; without these weights: base view only
+
+        runner_cls = LlavaNextCausalLM
+        extra_kw = dict(image_newline=weights.get_tensor(newline), pinpoints=cfg.get("image_grid_pinpoints"))
+    runner = runner_cls(model, tower, projector, tokenizer, dtype, device, rank, world, image_token, drop_cls,
+                         scale, speculate=speculate, **extra_kw,
                          kv_cache_dtype=resolve_kv_dtype(kv_cache_dtype, dtype), max_prefill_tokens=max_prefill_tokens)
     weights.close()
     return runner

@@ -1,5 +1,6 @@
 #include "images.hpp"
 
+#include <algorithm>
 #include <cmath>
 
 #include <arpa/inet.h>
@@ -243,9 +244,35 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     return side * side;
   }
   if (mt == "llava" || mt == "llava_next") {
-    // the runner feeds the base-resolution view: one feature row per patch
-    const uint32_t side = static_cast<uint32_t>(num("image_size", 336) / num("patch_size", 14));
-    return side * side;
+    const uint32_t tile = static_cast<uint32_t>(num("image_size", 336));
+    const uint32_t side = static_cast<uint32_t>(tile / num("patch_size", 14));
+    if (mt == "llava" || !config.has("image_grid_pinpoints") || !config["image_grid_pinpoints"].is_array() ||
+        width == 0 || height == 0)
+      return side * side;   // one view: one feature row per patch
+    // any-resolution tiling: base view + the tile map at the best-fitting resolution, without the rows / columns
+    // that only saw padding, plus one newline per remaining row
+    const double W = width, H = height;
+    double best_h = 0, best_w = 0, best_eff = -1, best_waste = 1e300;
+    for (const json::Value& pin : config["image_grid_pinpoints"].items()) {
+      if (!pin.is_array() || pin.items().size() < 2) continue;
+      const double h = pin.items()[0].as_double(), w = pin.items()[1].as_double();
+      const double scale = std::min(w / W, h / H);
+      const double eff = std::min(std::floor(W * scale) * std::floor(H * scale), W * H);
+      const double waste = w * h - eff;
+      if (eff > best_eff || (eff == best_eff && waste < best_waste)) {
+        best_h = h; best_w = w; best_eff = eff; best_waste = waste;
+      }
+    }
+    const long mh = static_cast<long>(best_h / tile) * side, mw = static_cast<long>(best_w / tile) * side;
+    long rows = mh, cols = mw;
+    if (W / H > static_cast<double>(mw) / mh) {
+      const long new_h = static_cast<long>(std::nearbyint(H * (mw / W) * 1e7) / 1e7);
+      rows = mh - 2 * ((mh - new_h) / 2);
+    } else {
+      const long new_w = static_cast<long>(std::nearbyint(W * (mh / H) * 1e7) / 1e7);
+      cols = mw - 2 * ((mw - new_w) / 2);
+    }
+    return side * side + static_cast<uint32_t>(rows * (cols + 1));
   }
   if (mt == "qwen2_vl" || mt == "qwen2_5_vl") {
     // dynamic resolution: both sides rounded to multiples of patch * merge inside the pixel budget; one row
