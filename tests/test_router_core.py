@@ -457,3 +457,18 @@ def test_llava_next_row_counts_match_the_runner(rt):
         assert rt.tokens_per_image(json.dumps(cfg), w, h) == anyres_rows((h, w), pins, 336, 24), (w, h)
     plain = {"model_type": "llava_next", "vision_config": {"image_size": 336, "patch_size": 14}}
     assert rt.tokens_per_image(json.dumps(plain), 640, 480) == 576
+
+
+def test_llava_next_row_counts_random_sizes(rt):
+    import json
+    import random
+
+    from tgi_b200.models.llava_next import anyres_rows
+
+    pins = [[336, 672], [672, 336], [672, 672], [1008, 336], [336, 1008]]
+    cfg = json.dumps({"model_type": "llava_next", "image_grid_pinpoints": pins,
+                      "vision_config": {"image_size": 336, "patch_size": 14}})
+    rng = random.Random(1)
+    for _ in range(500):
+        w, h = rng.randint(8, 3000), rng.randint(8, 3000)
+        assert rt.tokens_per_image(cfg, w, h) == anyres_rows((h, w), pins, 336, 24), (w, h)

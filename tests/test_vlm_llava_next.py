@@ -84,3 +84,25 @@ def test_llava_next_generation_matches_transformers(llava_next):
                               image_sizes=torch.tensor([list(sz) for _, sz in images[i]]), max_new_tokens=5,
                               min_new_tokens=5, do_sample=False)
         assert got[i][:5] == ref[0, ids.shape[1]:].tolist(), (i, got[i], ref[0, ids.shape[1]:].tolist())
+
+
+def test_unpadding_and_fit_match_transformers_on_many_sizes():
+    import random
+
+    from transformers.image_processing_utils import get_patch_output_size
+    from transformers.models.llava_next.modeling_llava_next import unpad_image
+
+    from tgi_b200.models.llava_next import _fit, unpadded_map
+
+    rng = random.Random(0)
+    pins = [[336, 672], [672, 336], [672, 672], [1008, 336], [336, 1008]]
+    for _ in range(200):
+        h, w = rng.randint(8, 2500), rng.randint(8, 2500)
+        bh, bw = select_best_resolution((h, w), pins)
+        img = np.zeros((h, w, 3), dtype=np.uint8)
+        assert _fit((h, w), (bh, bw)) == tuple(get_patch_output_size(img, (bh, bw), "channels_last")), (h, w)
+        mh, mw = bh // 336 * 24, bw // 336 * 24
+        top, bottom, left, right = unpadded_map((h, w), (mh, mw))
+        ref = unpad_image(torch.zeros(1, mh, mw), (h, w))
+        assert (bottom - top, right - left) == tuple(ref.shape[1:]), (h, w)
+        assert anyres_rows((h, w), pins, 336, 24) == 576 + ref.shape[1] * (ref.shape[2] + 1)
