@@ -472,3 +472,20 @@ def test_llava_next_row_counts_random_sizes(rt):
     for _ in range(500):
         w, h = rng.randint(8, 3000), rng.randint(8, 3000)
         assert rt.tokens_per_image(cfg, w, h) == anyres_rows((h, w), pins, 336, 24), (w, h)
+
+
+def test_qwen2_vl_row_counts_random_sizes(rt):
+    import json
+    import random
+
+    from tgi_b200.models.qwen2_vl import smart_resize
+
+    vis = {"patch_size": 14, "spatial_merge_size": 2, "min_pixels": 56 * 56, "max_pixels": 28 * 28 * 1280}
+    cfg = json.dumps({"model_type": "qwen2_vl", "vision_config": vis})
+    rng = random.Random(2)
+    for _ in range(500):
+        w, h = rng.randint(4, 5000), rng.randint(4, 5000)
+        if max(w, h) / min(w, h) > 200:
+            continue
+        rh, rw = smart_resize(h, w, 28, vis["min_pixels"], vis["max_pixels"])
+        assert rt.tokens_per_image(cfg, w, h) == (rh // 28) * (rw // 28), (w, h)

@@ -161,3 +161,17 @@ def test_qwen2_5_vl_generation_matches_transformers(qwen25):
                               do_sample=False, pixel_values=torch.cat([p for p, _ in pre]),
                               image_grid_thw=torch.tensor([list(g) for _, g in pre]))
         assert got[i][:6] == ref[0, ids.shape[1]:].tolist(), (i, got[i], ref[0, ids.shape[1]:].tolist())
+
+
+def test_smart_resize_matches_transformers_on_many_sizes():
+    import random
+
+    from transformers.models.qwen2_vl.image_processing_qwen2_vl import smart_resize as ref
+
+    rng = random.Random(3)
+    for _ in range(500):
+        h, w = rng.randint(4, 5000), rng.randint(4, 5000)
+        if max(h, w) / min(h, w) > 200:
+            continue
+        for lo, hi in [(56 * 56, 28 * 28 * 1280), (28 * 28, 28 * 28 * 16)]:
+            assert smart_resize(h, w, 28, lo, hi) == tuple(ref(h, w, 28, lo, hi)), (h, w, lo, hi)
