@@ -111,6 +111,45 @@ def test_randomized_allocator_invariants(rt):
         a.free(al.blocks, al.allocation_id)
     assert a.check()
     assert a.free_blocks() + a.cached_blocks() == nblocks - 1
+    # nothing is live: no pin may survive, so every block but the reserved one can be had again
+    everything = a.allocate((nblocks - 1) * bs, None)
+    assert everything is not None and len(everything.blocks) == nblocks - 1
+    assert a.cached_blocks() == 0
+    a.free(everything.blocks, everything.allocation_id)
+    assert a.check()
+
+
+def test_split_of_a_pinned_edge_releases_both_halves(rt):
+    a = rt.BlockAllocator(17, 2, True)          # 16 usable blocks
+    x = a.allocate(4, [1, 2, 3, 4])
+    a.free(x.blocks, x.allocation_id)           # edge [1,2,3,4] cached
+    b = a.allocate(4, [1, 2, 3, 4])             # pins that edge
+    assert b.prefix_len == 4
+    c = a.allocate(4, [1, 2, 9, 9])             # shares one block
+    assert c.prefix_len == 2
+    a.free(c.blocks, c.allocation_id)           # inserting [1,2,9,9] splits the pinned edge
+    assert a.check()
+    a.free(b.blocks, b.allocation_id)
+    assert a.check()
+    full = a.allocate(32, None)                 # all 16 blocks must be evictable again
+    assert full is not None and len(full.blocks) == 16
+    a.free(full.blocks, full.allocation_id)
+    assert a.allocate(30, None) is not None
+
+
+def test_free_with_uncomputed_prompt_caches_nothing(rt):
+    a = rt.BlockAllocator(17, 2, True)
+    x = a.allocate(6, [1, 2, 3, 4, 5, 6])
+    a.free(x.blocks, x.allocation_id, 0)        # never ran: its blocks hold no KV
+    assert a.cached_blocks() == 0 and a.free_blocks() == 16
+    y = a.allocate(6, [1, 2, 3, 4, 5, 6])
+    assert y.prefix_len == 0
+    a.free(y.blocks, y.allocation_id, 4)        # partial prefill: two of three blocks computed
+    assert a.cached_blocks() == 2
+    z = a.allocate(6, [1, 2, 3, 4, 5, 6])
+    assert z.prefix_len == 4
+    a.free(z.blocks, z.allocation_id)
+    assert a.check()
 
 
 # ---------------------------------------------------------------------------------------------
@@ -167,6 +206,31 @@ def test_next_batch_prefix_cache_and_full_hit(rt):
     b = q.next_batch()
     assert [r["cache_len"] for r in b["requests"]] == [7, 0]
     assert b["requests"][1]["prefill_logprobs"] is True
+
+
+def test_pushed_back_request_finds_no_cache_entry_of_itself(rt):
+    # over the prefill budget without chunking: the second request goes back to the queue and must come
+    # back with cache_len 0 (its blocks were never written)
+    q = rt.Queue(block_size=4, prefix_caching=True, support_chunking=False, max_batch_total_tokens=400)
+    q.append(16, 4, list(range(100, 116)))
+    q.append(16, 4, list(range(200, 216)))
+    b = q.next_batch(prefill_token_budget=16)
+    assert [(r["id"], r["cache_len"]) for r in b["requests"]] == [(0, 0)]
+    b2 = q.next_batch(prefill_token_budget=16)
+    assert [(r["id"], r["cache_len"]) for r in b2["requests"]] == [(1, 0)]
+    # same with chunking when the earlier prompt fills the budget exactly
+    q = rt.Queue(block_size=4, prefix_caching=True, support_chunking=True, max_batch_total_tokens=400)
+    q.append(16, 4, list(range(100, 116)))
+    q.append(16, 4, list(range(200, 216)))
+    b = q.next_batch(prefill_token_budget=16)
+    assert len(b["requests"]) == 1
+    b2 = q.next_batch(prefill_token_budget=16)
+    assert [(r["id"], r["cache_len"]) for r in b2["requests"]] == [(1, 0)]
+    # a request released after a failed prefill leaves nothing behind either
+    assert q.finish(1, False)
+    q.append(16, 4, list(range(200, 216)))
+    b3 = q.next_batch(prefill_token_budget=16)
+    assert b3["requests"][0]["cache_len"] == 0
 
 
 # ---------------------------------------------------------------------------------------------

@@ -76,10 +76,12 @@ def stack(tmp_path_factory):
         "chat_template": "{% for m in messages %}<|{{ m['role'] }}|>{{ m['content'] }}\n{% endfor %}<|assistant|>"}))
     uds = str(d / "shard")
     env = dict(os.environ, PYTHONPATH=ROOT, TGI_B200_CPU_KV_BLOCKS="256", VIRTUAL_ENV=os.environ.get("VIRTUAL_ENV", sys.prefix))
-    shard = subprocess.Popen([sys.executable, "-m", "tgi_b200.server.cli", "serve", str(d), "--uds-path", uds,
-                              "--dtype", "float32"], env=env, cwd=ROOT)
     port = _free_port()
     collected, collector = _start_collector()
+    shard = subprocess.Popen([sys.executable, "-m", "tgi_b200.server.cli", "serve", str(d), "--uds-path", uds,
+                              "--dtype", "float32",
+                              "--otlp-endpoint", f"http://127.0.0.1:{collector.server_address[1]}",
+                              "--otlp-service-name", "tgi-b200-test.shard"], env=env, cwd=ROOT)
     router = subprocess.Popen([str(router_bin), "--master-shard-uds-path", uds, "--tokenizer-name", str(d),
                                "--port", str(port), "--hostname", "127.0.0.1", "--max-input-tokens", "64",
                                "--max-total-tokens", "128", "--max-batch-prefill-tokens", "128",
@@ -337,9 +339,10 @@ def test_request_spans_reach_the_otlp_collector(stack):
     while time.time() < deadline and found is None:
         for doc in list(stack["otlp"]):
             rs = doc["resourceSpans"][0]
-            assert rs["resource"]["attributes"][0]["value"]["stringValue"] == "tgi-b200-test.router"
+            if rs["resource"]["attributes"][0]["value"]["stringValue"] != "tgi-b200-test.router":
+                continue
             for sp in rs["scopeSpans"][0]["spans"]:
-                if sp["traceId"] == trace_id:
+                if sp["traceId"] == trace_id and sp["name"].startswith("POST"):
                     found = sp
         time.sleep(0.2)
     assert found is not None, "no span with the caller's trace id was exported"
@@ -350,6 +353,28 @@ def test_request_spans_reach_the_otlp_collector(stack):
     # requests without a trace context start a new trace
     assert any(sp["traceId"] != trace_id and "parentSpanId" not in sp
                for doc in stack["otlp"] for sp in doc["resourceSpans"][0]["scopeSpans"][0]["spans"])
+    # the trace continues into the shard: router step span under the request span, shard RPC span under
+    # the step span, the shard's generate_token span under that
+    deadline = time.time() + 15
+    chain = None
+    while time.time() < deadline and chain is None:
+        spans = {}
+        for doc in list(stack["otlp"]):
+            rs = doc["resourceSpans"][0]
+            svc = rs["resource"]["attributes"][0]["value"]["stringValue"]
+            for sp in rs["scopeSpans"][0]["spans"]:
+                if sp["traceId"] == trace_id:
+                    spans[sp["spanId"]] = (svc, sp)
+        for svc, sp in spans.values():
+            if svc == "tgi-b200-test.shard" and sp["name"] == "generate_token":
+                rpc = spans.get(sp.get("parentSpanId"))
+                step = spans.get(rpc[1].get("parentSpanId")) if rpc else None
+                if rpc and step and step[1].get("parentSpanId") == found["spanId"]:
+                    chain = (step, rpc, sp)
+        time.sleep(0.3)
+    assert chain is not None, "shard spans do not descend from the request span"
+    assert chain[0][0] == "tgi-b200-test.router" and chain[0][1]["name"] in ("prefill", "decode")
+    assert chain[1][0] == "tgi-b200-test.shard" and chain[1][1]["name"] in ("Prefill", "Decode")
 
 
 def test_openapi_document_and_docs_page(stack):

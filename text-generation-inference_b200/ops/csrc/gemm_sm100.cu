@@ -33,6 +33,8 @@
 // (warps 2, 3 idle; the four give their registers away with setmaxnreg), warps 4..11 = promotion /
 // epilogue.  All waits are bounded (sm100.cuh): on expiry the kernel records an error code in
 // `status`, drains its outstanding TMA loads, frees TMEM and returns.
+#include <atomic>
+
 #include "launch.cuh"
 #include "tensor_map.cuh"
 #include "sm100.cuh"
@@ -589,11 +591,15 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
   // stages + (fp8) activation-scale ring [STAGES+2][TM] + alignment slack + barriers
   const size_t smem = STAGES * Cfg::kStageBytes + (FP8 ? (STAGES + 2) * Cfg::TM * 4 : 0) + 1024 + 256 + kMaxGrid * 4;
   auto kern = gemm_streamk_kernel<MH, TN, STAGES, FP8>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the shared-memory opt-in is a per-device attribute of the function: one bit per device ordinal
+  static std::atomic<unsigned long long> attr_set{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -2;
+  const unsigned long long dev_bit = 1ull << (dev & 63);
+  if (!(attr_set.load(std::memory_order_acquire) & dev_bit)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return -2;
-    attr_set = true;
+    attr_set.fetch_or(dev_bit, std::memory_order_release);
   }
   const long long units =
       static_cast<long long>((N + TN - 1) / TN) * ((M + Cfg::TM - 1) / Cfg::TM) * ((K + BK - 1) / BK);

@@ -53,7 +53,8 @@ int tgi_gemm_bf16_static(const void* X, const void* W, void* C, const void* bias
                          cudaStream_t stream);
 
 // Copies the kernel status word of the current device to *host_status after synchronising `stream`
-// (0 = no bounded wait ran out).  Returns 0 on success.
+// (0 = no bounded wait ran out).  Returns 0 on success.  Read it before the next tgi_gemm_bf16_static
+// call on the device: that call clears the word, so an error that was never polled is lost.
 int tgi_gemm_static_status(int* host_status, cudaStream_t stream);
 
 // Human-readable text for a code returned by the functions above.

@@ -59,7 +59,7 @@ def build(tests: bool = True):
 
     link(HERE / "tgi-b200-router", core + [str(objs["pybridge"]), str(objs["main"])], py_ld)
     link(HERE / "tgi-b200-launcher", [str(objs["launcher"])], [])
-    link(HERE / "tgi-b200-benchmark", [str(objs[n]) for n in ("pb", "scheduler", "shard_client", "benchmark")], [])
+    link(HERE / "tgi-b200-benchmark", [str(objs[n]) for n in ("pb", "scheduler", "shard_client", "trace", "benchmark")], [])
     if tests:
         link(HERE / "_router_test.so", core + [str(objs["bindings"])], ["-shared"])
     return HERE / "tgi-b200-router"

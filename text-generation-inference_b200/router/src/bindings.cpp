@@ -101,10 +101,11 @@ PYBIND11_MODULE(_router_test, m) {
              return a.allocate(tokens, prompt ? &*prompt : nullptr);
            },
            py::arg("tokens"), py::arg("prompt") = std::nullopt)
-      .def("free", &sched::BlockAllocator::free)
+      .def("free", &sched::BlockAllocator::free, py::arg("blocks"), py::arg("allocation_id"),
+           py::arg("computed_tokens") = UINT32_MAX)
       .def("free_blocks", &sched::BlockAllocator::free_blocks)
       .def("cached_blocks", [](sched::BlockAllocator& a) { return a.trie().cached_blocks(); })
-      .def("check", [](sched::BlockAllocator& a) { return a.trie().check(); });
+      .def("check", [](sched::BlockAllocator& a) { return a.check(); });
 
   py::class_<sched::RadixTrie>(m, "RadixTrie")
       .def(py::init<uint32_t>())
@@ -196,13 +197,15 @@ PYBIND11_MODULE(_router_test, m) {
            py::arg("min_size") = std::nullopt, py::arg("max_size") = std::nullopt, py::arg("prefill_token_budget") = 4096,
            py::arg("token_budget") = 16384)
       .def("finish",
-           [](QueueBox& b, uint64_t id) {
+           [](QueueBox& b, uint64_t id, bool prefill_done) {
              auto it = b.running.find(id);
              if (it == b.running.end()) return false;
+             it->second.prefill_done = prefill_done;
              b.q.release(it->second);
              b.running.erase(it);
              return true;
-           })
+           },
+           py::arg("id"), py::arg("prefill_done") = true)
       .def("free_blocks", [](QueueBox& b) { return b.q.allocator() ? b.q.allocator()->free_blocks() : 0; });
 
   py::class_<sched::Backend, std::shared_ptr<sched::Backend>>(m, "Backend")

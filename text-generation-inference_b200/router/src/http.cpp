@@ -242,9 +242,11 @@ void Server::connection(int fd) {
       span.span_id = trace::random_hex(16);
       span.name = req.method + " " + req.path;
       span.start_ns = trace::now_ns();
+      trace::set_current(trace::Context{span.trace_id, span.span_id, true});
     }
     auto finish_span = [&](bool failed) {
       if (!traced) return;
+      trace::set_current(trace::Context{});
       span.end_ns = trace::now_ns();
       span.error = failed || resp.status() >= 500;
       span.str_attrs.emplace_back("http.method", req.method);

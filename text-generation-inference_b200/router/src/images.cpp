@@ -141,7 +141,11 @@ std::string http_get(const std::string& url, size_t max_bytes, std::string* cont
       if (eol == std::string::npos) break;
       const size_t len = strtoul(body.substr(p, eol - p).c_str(), nullptr, 16);
       if (len == 0) break;
+      // the chunk length comes from the image host: it must fit in what was received, and the decoded
+      // body obeys the same size limit as the raw response
+      if (len > body.size() - (eol + 2)) throw std::runtime_error("malformed chunked image response");
       out.append(body, eol + 2, len);
+      if (out.size() > max_bytes) throw std::runtime_error("image is larger than the size limit");
       p = eol + 2 + len + 2;
     }
     body.swap(out);

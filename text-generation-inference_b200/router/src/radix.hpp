@@ -95,7 +95,7 @@ class RadixTrie {
       }
       touch(child);
       if (shared < nodes_[child].blocks.size()) {
-        split(child, shared);
+        child = split(child, shared);
       }
       pos += shared * bs_;
       node = child;
@@ -137,6 +137,11 @@ class RadixTrie {
     for (const auto& nd : nodes_) n += nd.alive;
     return n;
   }
+  uint32_t ref_count(int node) const { return nodes_[node].ref_count; }
+  int parent(int node) const { return nodes_[node].parent; }
+  size_t arena_size() const { return nodes_.size(); }
+  bool alive(int node) const { return nodes_[node].alive; }
+
   // invariant check used by the tests
   bool check() const {
     for (size_t i = 1; i < nodes_.size(); ++i) {
@@ -208,25 +213,26 @@ class RadixTrie {
     nodes_[parent].children[block_hash(key, pos)] = id;
     leaves_.insert({n.last_accessed, id});
   }
-  // keep the first `nblocks` blocks in `id`, move the rest to a new child that inherits the children
-  void split(int id, size_t nblocks) {
-    int rest = new_node();
+  // Cuts the edge of `id` after `nblocks` blocks.  The node keeps its id and becomes the deeper half (so
+  // holders that pinned `id` release both halves when they walk up from it, as the reference's
+  // split_node does, backends/v3/src/radix.rs:473-506); a new node takes the first `nblocks` blocks
+  // and the place of `id` under its parent.  Returns the new (upper) node.
+  int split(int id, size_t nblocks) {
+    const int head = new_node();   // may grow the arena: take references afterwards
     Node& n = nodes_[id];
-    Node& r = nodes_[rest];
-    const bool was_leaf = n.children.empty() && n.ref_count == 0;
-    if (was_leaf) leaves_.erase({n.last_accessed, id});
-    r.key.assign(n.key.begin() + nblocks * bs_, n.key.end());
-    r.blocks.assign(n.blocks.begin() + nblocks, n.blocks.end());
-    r.children = std::move(n.children);
-    r.parent = id;
-    r.ref_count = n.ref_count;   // every pin of the old edge pins both halves
-    r.last_accessed = n.last_accessed;
-    for (auto& kv : r.children) nodes_[kv.second].parent = rest;
-    n.children.clear();
-    n.key.resize(nblocks * bs_);
-    n.blocks.resize(nblocks);
-    n.children[block_hash(r.key, 0)] = rest;
-    if (r.children.empty() && r.ref_count == 0) leaves_.insert({r.last_accessed, rest});
+    Node& h = nodes_[head];
+    h.key.assign(n.key.begin(), n.key.begin() + nblocks * bs_);
+    h.blocks.assign(n.blocks.begin(), n.blocks.begin() + nblocks);
+    h.parent = n.parent;
+    h.ref_count = n.ref_count;   // every pin of the lower half passes through the upper half
+    h.last_accessed = n.last_accessed;
+    nodes_[n.parent].children[block_hash(h.key, 0)] = head;   // same first block: replaces `id`
+    n.key.erase(n.key.begin(), n.key.begin() + nblocks * bs_);
+    n.blocks.erase(n.blocks.begin(), n.blocks.begin() + nblocks);
+    n.parent = head;
+    h.children[block_hash(n.key, 0)] = id;
+    // `id` keeps its children, pins and position in the leaf set; the upper half has a child and is no leaf
+    return head;
   }
   void remove_node(int id) {
     Node& n = nodes_[id];
@@ -257,6 +263,22 @@ class BlockAllocator {
 
   size_t free_blocks() const { return free_.size(); }
   RadixTrie& trie() { return trie_; }
+  size_t live_allocations() const { return live_.size(); }
+
+  // Structural invariants of the trie plus the pin accounting: every node's reference count equals the
+  // number of live allocations whose pinned path passes through it (so it is 0 everywhere once nothing
+  // is live and every cached block can be evicted again).
+  bool check() const {
+    if (!trie_.check()) return false;
+    std::vector<uint32_t> expect(trie_.arena_size(), 0);
+    for (const auto& kv : live_) {
+      if (!prefix_caching_ || !kv.second.has_prompt) continue;
+      for (int node = kv.second.node; node != 0; node = trie_.parent(node)) ++expect[node];
+    }
+    for (size_t i = 1; i < expect.size(); ++i)
+      if (trie_.alive(static_cast<int>(i)) && trie_.ref_count(static_cast<int>(i)) != expect[i]) return false;
+    return true;
+  }
 
   // Allocate blocks for `tokens` tokens; `prompt` (token ids) enables prefix re-use.
   std::optional<BlockAllocation> allocate(uint32_t tokens, const std::vector<uint32_t>* prompt) {
@@ -299,7 +321,10 @@ class BlockAllocator {
     return a;
   }
 
-  void free(const std::vector<uint32_t>& blocks, uint64_t allocation_id) {
+  // `computed_tokens`: how many prompt tokens have their KV written.  Only those blocks may enter the
+  // prefix cache: a request that was pushed back before it ran, or whose prefill failed or was cut
+  // short, passes what it knows to be computed (0 if nothing) and the rest goes back to the free list.
+  void free(const std::vector<uint32_t>& blocks, uint64_t allocation_id, uint32_t computed_tokens = UINT32_MAX) {
     auto it = live_.find(allocation_id);
     if (it == live_.end()) throw std::runtime_error("allocator: unknown allocation id");
     Live l = std::move(it->second);
@@ -310,7 +335,8 @@ class BlockAllocator {
     }
     trie_.decref(l.node);
     // only whole prompt blocks can be shared; the last prompt token's block may be partial
-    const size_t aligned_blocks = std::min(l.prompt.size() / bs_, blocks.size());
+    const size_t aligned_blocks =
+        std::min(std::min<size_t>(l.prompt.size(), computed_tokens) / bs_, blocks.size());
     size_t already = l.cached_prefix / bs_;
     if (aligned_blocks > 0) {
       std::vector<uint32_t> key(l.prompt.begin(), l.prompt.begin() + aligned_blocks * bs_);

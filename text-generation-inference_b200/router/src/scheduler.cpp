@@ -26,7 +26,9 @@ uint64_t Queue::append(Entry e) {
 
 void Queue::release(Entry& e) {
   if (e.allocation && allocator_) {
-    allocator_->free(e.allocation->blocks, e.allocation->allocation_id);
+    // an entry that never ran, or whose prefill failed or was cut short, has no KV beyond the prefix it
+    // found in the cache: nothing of it may be inserted into the trie
+    allocator_->free(e.allocation->blocks, e.allocation->allocation_id, e.prefill_done ? UINT32_MAX : 0);
     e.allocation.reset();
   }
 }
@@ -173,6 +175,7 @@ std::shared_ptr<ResponseStream> Backend::schedule(ValidRequest req) {
   e.request = std::move(req);
   e.stream = std::make_shared<ResponseStream>();
   e.queue_time = Clock::now();
+  e.trace = trace::current();
   auto stream = e.stream;
   {
     std::lock_guard<std::mutex> g(inbox_m_);
@@ -287,11 +290,40 @@ void Backend::fail_entries(const std::vector<uint64_t>& ids, const std::string& 
   }
 }
 
+trace::Span Backend::begin_step_span(const char* name, const std::vector<uint64_t>& ids) {
+  trace::Span span;
+  for (uint64_t id : ids) {
+    auto it = running_.find(id);
+    if (it == running_.end() || !it->second.trace.valid()) continue;
+    span.name = name;
+    span.trace_id = it->second.trace.trace_id;
+    span.parent_span_id = it->second.trace.span_id;
+    span.span_id = trace::random_hex(16);
+    span.kind = 3;   // SPAN_KIND_CLIENT
+    span.start_ns = trace::now_ns();
+    span.int_attrs.emplace_back("batch.size", static_cast<long long>(ids.size()));
+    break;
+  }
+  client_->set_traceparent(span.name.empty() ? std::string()
+                                             : trace::format_traceparent(trace::Context{span.trace_id, span.span_id, true}));
+  return span;
+}
+
+void Backend::end_step_span(trace::Span& span, bool failed) {
+  client_->set_traceparent("");
+  if (span.name.empty() || trace::exporter() == nullptr) return;
+  span.end_ns = trace::now_ns();
+  span.error = failed;
+  trace::exporter()->submit(std::move(span));
+}
+
 std::optional<pb::CachedBatch> Backend::prefill(NextBatch& nb, const pb::CachedBatch* cached) {
   const auto t0 = Clock::now();
   if (metrics_) metrics_->counter_inc("tgi_batch_inference_count", {{"method", "prefill"}});
+  trace::Span span = begin_step_span("prefill", nb.ids);
   try {
     pb::StepResponse resp = client_->prefill(nb.batch, cached);
+    end_step_span(span, false);
     if (metrics_) {
       metrics_->observe("tgi_batch_forward_duration", resp.forward_ns * 1e-9, {{"method", "prefill"}});
       metrics_->observe("tgi_batch_decode_duration", resp.decode_ns * 1e-9, {{"method", "prefill"}});
@@ -301,6 +333,7 @@ std::optional<pb::CachedBatch> Backend::prefill(NextBatch& nb, const pb::CachedB
     }
     return after_step(resp, "prefill");
   } catch (const std::exception& e) {
+    end_step_span(span, true);
     std::vector<uint64_t> ids = nb.ids;
     if (cached) ids.insert(ids.end(), cached->request_ids.begin(), cached->request_ids.end());
     try {
@@ -317,8 +350,12 @@ std::optional<pb::CachedBatch> Backend::prefill(NextBatch& nb, const pb::CachedB
 std::optional<pb::CachedBatch> Backend::decode(std::vector<pb::CachedBatch>& batches) {
   const auto t0 = Clock::now();
   if (metrics_) metrics_->counter_inc("tgi_batch_inference_count", {{"method", "decode"}});
+  std::vector<uint64_t> step_ids;
+  for (auto& b : batches) step_ids.insert(step_ids.end(), b.request_ids.begin(), b.request_ids.end());
+  trace::Span span = begin_step_span("decode", step_ids);
   try {
     pb::StepResponse resp = client_->decode(batches);
+    end_step_span(span, false);
     if (metrics_) {
       metrics_->observe("tgi_batch_forward_duration", resp.forward_ns * 1e-9, {{"method", "decode"}});
       metrics_->observe("tgi_batch_decode_duration", resp.decode_ns * 1e-9, {{"method", "decode"}});
@@ -329,6 +366,7 @@ std::optional<pb::CachedBatch> Backend::decode(std::vector<pb::CachedBatch>& bat
     }
     return after_step(resp, "decode");
   } catch (const std::exception& e) {
+    end_step_span(span, true);
     std::vector<uint64_t> ids;
     for (auto& b : batches) {
       ids.insert(ids.end(), b.request_ids.begin(), b.request_ids.end());
@@ -363,6 +401,7 @@ void Backend::send_generation(Entry& e, pb::Generation& g, bool& finished) {
     e.stream->push(std::move(ev));
   }
   const size_t n = g.tokens.ids.size();
+  if (n > 0) e.prefill_done = true;
   if (metrics_ && n > 0) metrics_->histogram_value("tgi_request_skipped_tokens", static_cast<double>(n - 1));   // speculated tokens accepted
   for (size_t i = 0; i < n; ++i) {
     StreamEvent ev;

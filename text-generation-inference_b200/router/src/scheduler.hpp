@@ -25,6 +25,7 @@
 
 #include "pb.hpp"
 #include "radix.hpp"
+#include "trace.hpp"
 
 namespace sched {
 
@@ -97,6 +98,10 @@ struct Entry {
   Clock::time_point queue_time;
   std::optional<Clock::time_point> batch_time;
   std::optional<BlockAllocation> allocation;
+  // set once the shards returned the first generated token: from then on the KV of the whole prompt
+  // exists and its blocks may enter the prefix cache when the entry is released
+  bool prefill_done = false;
+  trace::Context trace;   // span of the HTTP request, when it is traced
 };
 
 struct NextBatch {
@@ -151,6 +156,8 @@ class ShardClient {
                                     uint32_t max_prefill_tokens, std::optional<uint32_t> max_total_tokens) = 0;
   virtual pb::StepResponse prefill(const pb::Batch& batch, const pb::CachedBatch* cached) = 0;
   virtual pb::StepResponse decode(const std::vector<pb::CachedBatch>& batches) = 0;
+  // W3C `traceparent` sent along with the following calls of this thread's owner ("" = none)
+  virtual void set_traceparent(const std::string&) {}
 };
 
 struct Metrics;   // metrics.hpp
@@ -185,6 +192,10 @@ class Backend {
   std::optional<pb::CachedBatch> after_step(pb::StepResponse& resp, const char* method);
   void fail_entries(const std::vector<uint64_t>& ids, const std::string& msg);
   void send_generation(Entry& e, pb::Generation& g, bool& finished);
+  // Opens the span of one shard step as a child of the first traced request among `ids`, hands its
+  // `traceparent` to the shard client and returns the span (name empty when nothing is traced).
+  trace::Span begin_step_span(const char* name, const std::vector<uint64_t>& ids);
+  void end_step_span(trace::Span& span, bool failed);
 
   std::shared_ptr<ShardClient> client_;
   QueueConfig qcfg_;

@@ -52,30 +52,33 @@ void FramedConnection::connect_once() {
   }
 }
 
-std::string FramedConnection::call(uint8_t method, const std::string& payload) {
+std::string FramedConnection::call(uint8_t method, const std::string& payload, const std::string& traceparent) {
   std::lock_guard<std::mutex> g(m_);
   if (fd_ < 0) connect_once();
+  const bool with_trace = traceparent.size() == 55;
   char head[5];
-  head[0] = static_cast<char>(method);
+  head[0] = static_cast<char>(with_trace ? (method | 0x80) : method);
   const uint32_t n = static_cast<uint32_t>(payload.size());
   std::memcpy(head + 1, &n, 4);
+  std::string body;
+  char rh[5];
   try {
     write_all(fd_, head, 5);
+    if (with_trace) write_all(fd_, traceparent.data(), 55);
     write_all(fd_, payload.data(), payload.size());
-    char rh[5];
     read_all(fd_, rh, 5);
     uint32_t rn;
     std::memcpy(&rn, rh + 1, 4);
-    std::string body(rn, '\0');
+    body.assign(rn, '\0');
     if (rn) read_all(fd_, body.data(), rn);
-    if (rh[0] != 0) throw std::runtime_error(body);
-    return body;
   } catch (const std::runtime_error&) {
-    if (fd_ >= 0 && errno != 0) {
-      // a transport failure leaves the stream out of sync: reconnect on the next call
-    }
+    // a transport failure leaves the stream out of sync: drop the socket, the next call reconnects
+    ::close(fd_);
+    fd_ = -1;
     throw;
   }
+  if (rh[0] != 0) throw std::runtime_error(body);   // the shard answered with an error message
+  return body;
 }
 
 std::shared_ptr<ShardedClient> ShardedClient::connect(const std::string& uds_path, int timeout_s) {
@@ -110,11 +113,12 @@ ShardedClient::ShardedClient(std::vector<std::string> paths) {
 std::vector<std::string> ShardedClient::all(uint8_t method, const std::string& payload) {
   std::vector<std::string> out(conns_.size());
   if (conns_.size() == 1) {
-    out[0] = conns_[0]->call(method, payload);
+    out[0] = conns_[0]->call(method, payload, traceparent_);
     return out;
   }
+  const std::string tp = traceparent_;
   std::vector<std::future<std::string>> fs;
-  for (auto& c : conns_) fs.push_back(std::async(std::launch::async, [&c, method, &payload] { return c->call(method, payload); }));
+  for (auto& c : conns_) fs.push_back(std::async(std::launch::async, [&c, method, &payload, &tp] { return c->call(method, payload, tp); }));
   std::exception_ptr err;
   for (size_t i = 0; i < fs.size(); ++i) {
     try {

@@ -17,7 +17,8 @@ class FramedConnection {
   explicit FramedConnection(const std::string& path);
   ~FramedConnection();
   // throws std::runtime_error on transport errors and on an error status from the shard
-  std::string call(uint8_t method, const std::string& payload);
+  // A non-empty `traceparent` (55 characters, W3C trace context) travels in the frame header.
+  std::string call(uint8_t method, const std::string& payload, const std::string& traceparent = "");
 
  private:
   void connect_once();
@@ -40,12 +41,14 @@ class ShardedClient : public ShardClient {
                             uint32_t max_prefill_tokens, std::optional<uint32_t> max_total_tokens) override;
   pb::StepResponse prefill(const pb::Batch& batch, const pb::CachedBatch* cached) override;
   pb::StepResponse decode(const std::vector<pb::CachedBatch>& batches) override;
+  void set_traceparent(const std::string& tp) override { traceparent_ = tp; }
   size_t num_shards() const { return conns_.size(); }
 
  private:
   std::vector<std::string> all(uint8_t method, const std::string& payload);
   static pb::StepResponse merge(std::vector<std::string>& raw);
   std::vector<std::unique_ptr<FramedConnection>> conns_;
+  std::string traceparent_;   // written and read by the scheduler thread only
 };
 
 }  // namespace sched

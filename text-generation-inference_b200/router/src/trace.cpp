@@ -41,8 +41,12 @@ std::string json_escape(const std::string& s) {
 }
 
 std::unique_ptr<Exporter> g_exporter;
+thread_local Context t_current;
 
 }  // namespace
+
+void set_current(const Context& c) { t_current = c; }
+const Context& current() { return t_current; }
 
 Context parse_traceparent(const std::string& header) {
   Context c;

@@ -62,6 +62,12 @@ class Exporter {
   std::thread thread_;
 };
 
+// The span of the HTTP request that the calling thread is serving (invalid outside a traced request).
+// The scheduler copies it into the queue entry so that the shard calls made for that request
+// continue its trace (role of backends/grpc-metadata/src/lib.rs:1-41 in the reference).
+void set_current(const Context& c);
+const Context& current();
+
 // process-wide exporter; null until `init` is called with a non-empty endpoint
 void init(const std::string& endpoint, const std::string& service_name);
 Exporter* exporter();

@@ -161,15 +161,24 @@ class TextGenerationService:
 FRAMED_METHODS = ["Info", "ServiceDiscovery", "ClearCache", "FilterBatch", "Warmup", "Prefill", "Decode", "Health"]
 
 
-async def serve_framed(service: TextGenerationService, path: str):
+async def serve_framed(service: TextGenerationService, path: str, shutdown_callback=None):
     """Second transport for the same service: length-prefixed protobuf frames over a unix socket.
 
     The C++ router has no HTTP/2 stack, so it speaks this framing instead of gRPC; the messages are
     the same ``generate.v3`` protobufs.  Request frame: ``u8 method index (FRAMED_METHODS), u32 LE
-    length, payload``; response frame: ``u8 status (0 ok / 1 error), u32 LE length, payload`` where
-    the payload of an error is its UTF-8 message.
+    length, payload``; when bit 7 of the method byte is set, the 55 characters of a W3C ``traceparent``
+    precede the payload (not counted in the length) and the handler runs in a span that continues the
+    caller's trace, as the gRPC transport does from call metadata.  Response frame: ``u8 status (0 ok /
+    1 error), u32 LE length, payload`` where the payload of an error is its UTF-8 message.
+
+    A ``RuntimeError`` of a handler (a CUDA error, a device-side wait that ran out) is fatal for the
+    shard as on the gRPC transport (``server/text_generation_server/interceptor.py:11-40`` in the
+    reference): the error frame is sent, then ``shutdown_callback`` ends the serve loop so that the
+    launcher tears the deployment down instead of letting one rank go on with stale flag epochs.
     """
     import struct
+
+    from .tracing import parse_traceparent
 
     async def handle(reader: asyncio.StreamReader, writer: asyncio.StreamWriter):
         try:
@@ -179,19 +188,32 @@ async def serve_framed(service: TextGenerationService, path: str):
                 except asyncio.IncompleteReadError:
                     break
                 method, length = head[0], struct.unpack("<I", head[1:5])[0]
+                parent = None
+                if method & 0x80:
+                    method &= 0x7F
+                    parent = parse_traceparent((await reader.readexactly(55)).decode("ascii", "replace"))
                 payload = await reader.readexactly(length) if length else b""
+                fatal = False
                 try:
                     name = FRAMED_METHODS[method]
                     req_cls = pb.message_class(pb.METHODS[name][0])
-                    resp = await getattr(service, name)(req_cls.FromString(payload), None)
+                    if parent is not None:
+                        with tracer().span(name, parent=parent, attributes={"rpc.system": "framed", "rpc.method": name}):
+                            resp = await getattr(service, name)(req_cls.FromString(payload), None)
+                    else:
+                        resp = await getattr(service, name)(req_cls.FromString(payload), None)
                     body, status = resp.SerializeToString(), 0
                 except Exception as err:  # noqa: BLE001
                     log.exception("framed rpc %s failed", method)
+                    fatal = isinstance(err, RuntimeError)
                     if torch.cuda.is_available():
                         torch.cuda.empty_cache()
                     body, status = f"{type(err).__name__}: {err}".encode(), 1
                 writer.write(bytes([status]) + struct.pack("<I", len(body)) + body)
                 await writer.drain()
+                if fatal and shutdown_callback is not None:
+                    shutdown_callback()
+                    break
         finally:
             writer.close()
 
@@ -247,7 +269,8 @@ def serve(model_id: str, lora_adapters=None, revision: Optional[str] = None, sha
         server.add_generic_rpc_handlers((generic_handler(service),))
         server.add_insecure_port(local_url)
         await server.start()
-        framed = await serve_framed(service, local_url[len("unix://"):] + ".raw")
+        framed = await serve_framed(service, local_url[len("unix://"):] + ".raw",
+                                    shutdown_callback=lambda: signal_handler.set_keep_processing(False))
         log.info("Server started at %s", local_url)
         while signal_handler.KEEP_PROCESSING:
             await asyncio.sleep(0.5)
