@@ -2,7 +2,7 @@
 """Serving benchmark: decode throughput of a Llama-3-70B-shape model in block-scaled fp8.
 
     python bench.py --gpus N --steps K --warmup W            # this engine
-    python bench.py --impl reference --gpus N ...             # the reference (prints `unavailable`)
+    python bench.py --impl reference --gpus N ...             # the unmodified reference shard (baseline/_ref)
 
 Workload (the headline configuration): Llama-3-70B shape (80 layers, hidden 8192, 64/8 heads,
 intermediate 28672, vocab 128256), weights e4m3 with 128x128 block scales quantised from seeded
@@ -56,13 +56,49 @@ def parse_args():
     return ap.parse_args()
 
 
-def reference_unavailable():
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "text-generation-server cannot be imported offline: its generated protobuf stubs need "
-                       "protoc/grpc_tools and it depends on peft, grpc_interceptor, grpc_reflection and the "
-                       "`kernels` hub binaries, none of which are installable without a network",
-    }))
+def reference_main(args):
+    """Runs the unmodified reference shard (``baseline/_ref``) on the same workload and prints the same JSON
+    line with ``impl: reference``; if any step of that attempt fails, the line says ``unavailable`` with the
+    exception of the attempt."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    try:
+        if args.model not in ("llama70b-fp8", "llama8b-bf16", "tiny"):
+            raise RuntimeError(f"no reference arm for --model {args.model}")
+        from baseline import reference_arm
+
+        rec = reference_arm.run(args, ClockSampler)
+    except BaseException as err:  # noqa: BLE001 - report whatever stopped the attempt
+        if isinstance(err, KeyboardInterrupt):
+            raise
+        import traceback
+
+        traceback.print_exc()
+        msg = f"{type(err).__name__}: {err}".replace("\n", " ")[:600]
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": msg}), flush=True)
+        sys.stdout.flush()
+        os._exit(0)
+    if rank == 0:
+        C = args.concurrency
+        out = {
+            "metric": METRIC if args.model == "llama70b-fp8" else f"output tok/s (decode, {args.model}, TP=N)",
+            "value": round(rec["value"], 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(rec["ms_per_step"], 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8_e4m3 (block-scaled weights+activations, fp8 KV)" if args.model != "llama8b-bf16" else "bf16",
+            "data": "synthetic: random-token prompts, random-init N(0,0.02) weights", "impl": "reference",
+            "config": {"model": args.model if not args.layers else f"{args.model}-{args.layers}L", "global_batch": C,
+                       "seq_len": rec["reference"]["context_at_timed_steps"], "nominal_prompt_len": args.prompt_len,
+                       "output_len": args.output_len, "parallelism": f"tp{world}",
+                       "collectives": "none (one GPU)" if world == 1 else "nccl", "l2": "inputs larger than L2",
+                       "timed": "CUDA events around K calls of generate_token, max over ranks"},
+            "e2e": {k: (round(v, 4) if isinstance(v, float) else v) for k, v in rec["e2e"].items()},
+            "clocks": rec["clocks"], "reference": rec["reference"], "reference_shims": rec["reference_shims"],
+        }
+        print(json.dumps(out), flush=True)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)   # same reason as in main(): no communicator tear-down with live CUDA graphs
 
 
 class ClockSampler(threading.Thread):
@@ -128,8 +164,7 @@ def model_config(args):
 def main():
     args = parse_args()
     if args.impl == "reference":
-        reference_unavailable()
-        return 0
+        return reference_main(args)
 
     import numpy as np
     import torch

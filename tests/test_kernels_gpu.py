@@ -64,6 +64,35 @@ def test_gemm_fp8_block(K, M, N, K_):
         torch.testing.assert_close(got.float(), want, atol=3e-2 * math.sqrt(K_ / 512), rtol=2e-2)
 
 
+@pytest.mark.parametrize("pairs", [True, False])
+@pytest.mark.parametrize("M,N,K_", [(129, 256, 256), (256, 256, 128), (256, 130 * 8, 512), (257, 7168, 8192),
+                                    (512, 28672, 1024), (2048, 1280, 8192)])
+def test_gemm_tile_configurations(K, pairs, M, N, K_):
+    """More than 128 tokens: CTA pairs on 256 x 256 tiles (default) and single CTAs on 256 x 128 tiles must
+    both match the oracle, for whole tiles, aligned K splits and stream-K splits, bf16 and block-scaled fp8."""
+    torch.manual_seed(M + N + K_)
+    x = torch.randn(M, K_, device=dev(), dtype=torch.bfloat16)
+    w = torch.randn(N, K_, device=dev()) * 0.05
+    K.set_gemm_pairs(pairs)
+    try:
+        wb = w.to(torch.bfloat16)
+        want = x.float() @ wb.float().t()
+        for ctas in (None, 2, 37, 74):
+            got = K.gemm_bf16(x, wb, None, max_ctas=ctas)
+            no_kernel_error(K)
+            torch.testing.assert_close(got.float(), want, atol=2e-2 * math.sqrt(K_ / 512), rtol=2e-2)
+        if K_ % 128 == 0 and N % 128 == 0:
+            wq, ws = ref.fp8_quant_block_weight(w)
+            xq, xs = K.fp8_quant_act(x)
+            want8 = ref.gemm_fp8_block(xq, xs.contiguous(), wq, ws, torch.float32)
+            for ctas in (None, 2, 37, 74):
+                got = K.gemm_fp8_block(xq, xs, wq, ws, max_ctas=ctas)
+                no_kernel_error(K)
+                torch.testing.assert_close(got.float(), want8, atol=3e-2 * math.sqrt(K_ / 512), rtol=2e-2)
+    finally:
+        K.set_gemm_pairs(True)
+
+
 @pytest.mark.parametrize("T,H", [(1, 256), (5, 4096), (33, 8192), (4, 5120), (3, 16384)])
 @pytest.mark.parametrize("with_res", [False, True])
 def test_rms_norm(K, T, H, with_res):

@@ -9,9 +9,15 @@
 // Replaces, in the reference, cuBLAS `F.linear` (layers/linear.py:44) and the fp8 paths
 // `w8a8_block_fp8_matmul` / `cutlass_scaled_mm` / `torch._scaled_mm` (layers/fp8.py:507-579).
 //
-// Tile: 256 tokens x 128 weight rows (two 128-lane MMAs sharing the weight tile) when M > 128,
-// 128 tokens x 256 weight rows otherwise.  TMEM lanes run over TOKENS and columns over weight
-// rows.  That orientation is what makes the fp8 promotion cheap: the combined block scale
+// Tile: 128 tokens x 256 weight rows per CTA for M <= 128.  For M > 128 two CTAs of a cluster work
+// as a pair (`cta_group::2`) on 256 tokens x 256 weight rows: each CTA loads its own 128 tokens and
+// one half of the 256 weight rows, the even CTA issues MMAs of 256 x 256 that read the weight
+// halves from both CTAs' shared memory, and each CTA finds the accumulator rows of its tokens in
+// its own TMEM.  Per K block a CTA then moves 32 KB through L2 -> shared memory for 128 x 256
+// outputs where a single CTA needs 48 KB (the activation tile is not fetched once per 128 weight
+// rows any more), and operand traffic into shared memory is what bounds these GEMMs at M >= 256.
+// (A 256 x 128 single-CTA tile is kept for GPUs or launches that cannot form pairs.)
+// TMEM lanes run over TOKENS and columns over weight rows.  That orientation is what makes the fp8 promotion cheap: the combined block scale
 // a_scale[m, kb] * w_scale[slab, kb] is one scalar per thread and K block, kept in a register,
 // instead of a vector that every lane would have to fetch from shared memory (measured: broadcast
 // loads of a per-column scale vector cost 2x the FMAs they feed, because shared memory delivers
@@ -33,6 +39,13 @@
 // (warps 2, 3 idle; the four give their registers away with setmaxnreg), warps 4..11 = promotion /
 // epilogue.  All waits are bounded (sm100.cuh): on expiry the kernel records an error code in
 // `status`, drains its outstanding TMA loads, frees TMEM and returns.
+//
+// Barriers of a pair: `full[s]` lives in the even CTA and counts the bytes of both CTAs' loads
+// (every load names it through its cluster address; only the even CTA's producer posts the
+// expected byte count); `empty[s]` and `tmem_full[b]` exist in both CTAs and are signalled in both
+// by one multicast `tcgen05.commit`; `tmem_empty[b]` lives in the even CTA and collects the
+// arrivals of both CTAs' epilogue warps.  Both CTAs meet at a cluster barrier after barrier
+// initialisation and before TMEM is freed, on every path, error paths included.
 #include <atomic>
 
 #include "launch.cuh"
@@ -50,13 +63,16 @@ constexpr int kCols = 128;                 // accumulator columns per epilogue t
 constexpr int kTileElems = 256 * 128;      // outputs per tile in both configurations
 constexpr int kBufCols = 256;              // TMEM columns per accumulator buffer (two buffers)
 
-template <int MH, int TN>
+template <int MH, int TN, bool PAIR>
 struct TileCfg {
   static_assert(MH * TN == 256, "an accumulator buffer is 256 TMEM columns");
-  static constexpr int TM = MH * 128;                  // tokens per tile
-  static constexpr int kXBytes = TM * 128;             // one 128-byte K row per token
-  static constexpr int kWBytes = TN * 128;
-  static constexpr int kStageBytes = kXBytes + kWBytes;   // 48 KB
+  static_assert(!PAIR || MH == 1, "a pair runs the 128 x 256 per-CTA configuration");
+  static constexpr int CM = MH * 128;                  // tokens per CTA
+  static constexpr int TM = PAIR ? 256 : CM;           // tokens per tile (a pair's tile spans both CTAs)
+  static constexpr int WROWS = PAIR ? TN / 2 : TN;     // weight rows this CTA loads
+  static constexpr int kXBytes = CM * 128;             // one 128-byte K row per token
+  static constexpr int kWBytes = WROWS * 128;
+  static constexpr int kStageBytes = kXBytes + kWBytes;   // 48 KB, 32 KB in a pair
 };
 
 // Optional destination of the output rows in peer memory (tensor-parallel row-parallel GEMMs): row m
@@ -159,24 +175,14 @@ struct UnitIter {
 // wscale: weight scales [ceil(N/128), K/128] row-major
 // ws: 2 partial-tile slots per CTA; counters: one int per output tile (self-resetting)
 // ------------------------------------------------------------------------------------------------
-#ifdef TGI_GEMM_EXP
-static int g_exp_host = 0;
-__device__ int g_exp = 0;   // 1: no promotion FMAs, 2: no TMEM loads either, 3: no MMAs
-#define EXP_IS(x) ((g_exp & 7) == (x))
-#define EXP_GE(x) ((g_exp & 7) >= (x))
-#else
-#define EXP_IS(x) false
-#define EXP_GE(x) false
-#endif
-
-template <int MH, int TN, int STAGES, bool FP8>
+template <int MH, int TN, int STAGES, bool FP8, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmS, const float* __restrict__ wscale,
                     __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
                     float* __restrict__ ws, int* __restrict__ counters, int* __restrict__ status,
                     const __grid_constant__ PushArgs push) {
-  using Cfg = TileCfg<MH, TN>;
+  using Cfg = TileCfg<MH, TN, PAIR>;
   // first element of output row m: in C, or in the owner's peer-memory slot of this rank
   auto out_row = [&](int m) -> __nv_bfloat16* {
     if (push.world == 0) return C + static_cast<size_t>(m) * N;
@@ -186,12 +192,16 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
            (static_cast<size_t>(push.rank) * push.rows_per + lr) * N;
   };
   constexpr int TM = Cfg::TM;
+  constexpr int CM = Cfg::CM;
   constexpr int BK = FP8 ? 128 : 64;            // elements per 128-byte row
+  // position in the pair: the even CTA leads (issues the MMAs, owns `full` and `tmem_empty`)
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   constexpr int SC_STAGES = STAGES + 2;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* sc_ring = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);   // [SC_STAGES][TM] (fp8 only)
-  uint64_t* full = reinterpret_cast<uint64_t*>(sc_ring + (FP8 ? SC_STAGES * TM : 0));
+  float* sc_ring = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);   // [SC_STAGES][CM] (fp8 only)
+  uint64_t* full = reinterpret_cast<uint64_t*>(sc_ring + (FP8 ? SC_STAGES * CM : 0));
   uint64_t* empty = full + STAGES;
   // Accumulator hand-over.  Block-scaled fp8 with two token halves (MH == 2) signals every half of a buffer on
   // its own barrier pair: the promotion of half 0 starts while the MMAs of half 1 are still running and the
@@ -209,6 +219,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
     if (reinterpret_cast<uint8_t*>(cslots + kMaxGrid) - smem_raw > static_cast<ptrdiff_t>(dyn_bytes)) {
       report(status, kErrSmemLayout);
+      if (PAIR) {   // uniform over the cluster (same launch parameters): meet the peer at both cluster barriers
+        cluster_sync();
+        cluster_sync();
+      }
       return;
     }
   }
@@ -217,9 +231,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   sch.n_tiles = (N + TN - 1) / TN;
   sch.m_tiles = (M + TM - 1) / TM;
   sch.KB = (K + BK - 1) / BK;
-  sch.grid = gridDim.x;
+  sch.grid = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   sch.units = static_cast<long long>(sch.n_tiles) * sch.m_tiles * sch.KB;
-  const long long u0 = sch.begin(blockIdx.x), u1 = sch.begin(blockIdx.x + 1);
+  const long long u0 = sch.begin(worker), u1 = sch.begin(worker + 1);
   const int nunits = static_cast<int>(u1 - u0);
   constexpr uint32_t kTmemCols = 2 * kBufCols;
 
@@ -230,7 +244,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     }
     for (int b = 0; b < 2 * HB; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], kEpiWarps / HB);
+      mbar_init(&tmem_empty[b], (PAIR ? 2 : 1) * kEpiWarps / HB);
     }
     fence_barrier_init();
     prefetch_tensormap(&tmW);
@@ -238,13 +252,22 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     if (FP8) prefetch_tensormap(&tmS);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_holder, kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_holder, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_holder, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync();   // the peer's barriers are initialised before anything is signalled on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // cluster addresses of the barriers that live in the leading CTA
+  const uint32_t full0_remote = PAIR ? map_to_cta(smem_u32(&full[0]), 0) : 0u;
+  const uint32_t tmem_empty0_remote = PAIR ? map_to_cta(smem_u32(&tmem_empty[0]), 0) : 0u;
   // Barrier set-up, TMEM allocation and descriptor prefetch above touch no tensor data, so they overlap
   // with the tail of the previous kernel; from here on the operands (and the workspace) are used.
   tgi::pdl_wait();
@@ -267,32 +290,36 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           if (it >= STAGES) ok = mbar_wait(&empty[s], ((it / STAGES) - 1) & 1);
           if (!ok) { report(status, kErrProducerWait); break; }
           uint8_t* st = smem + s * Cfg::kStageBytes;
-          mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes + (FP8 ? TM * 4 : 0));
+          constexpr uint32_t kCtaBytes = Cfg::kStageBytes + (FP8 ? CM * 4 : 0);
+          if (PAIR) {
+            // both CTAs' bytes are counted on the leader's barrier; only the leader posts the expectation
+            const uint32_t bar = full0_remote + s * 8;
+            if (crank == 0) mbar_arrive_expect_tx(&full[s], 2 * kCtaBytes);
+            tma_load_2d_pair_hint(st, &tmX, bar, kb * BK, m0 + static_cast<int>(crank) * CM, pol_x);
+            tma_load_2d_pair_hint(st + Cfg::kXBytes, &tmW, bar, kb * BK, n0 + static_cast<int>(crank) * Cfg::WROWS, pol_w);
+            if (FP8) tma_load_2d_pair(sc_ring + (it % SC_STAGES) * CM, &tmS, bar, m0 + static_cast<int>(crank) * CM, kb);
+          } else {
+            mbar_arrive_expect_tx(&full[s], kCtaBytes);
 #pragma unroll
-          for (int h = 0; h < MH; ++h) tma_load_2d_hint(st + h * 16384, &tmX, &full[s], kb * BK, m0 + h * 128, pol_x);
+            for (int h = 0; h < MH; ++h) tma_load_2d_hint(st + h * 16384, &tmX, &full[s], kb * BK, m0 + h * 128, pol_x);
 #pragma unroll
-          for (int h = 0; h < TN / 128; ++h) {
-#ifdef TGI_GEMM_EXP
-            if (g_exp & 8) {
-              tma_load_2d_hint(st + Cfg::kXBytes + h * 16384, &tmW, &full[s], 0, ((n0 / 128 + h) * sch.KB + kb) * 128, pol_w);
-              continue;
-            }
-#endif
-            tma_load_2d_hint(st + Cfg::kXBytes + h * 16384, &tmW, &full[s], kb * BK, n0 + h * 128, pol_w);
+            for (int h = 0; h < TN / 128; ++h)
+              tma_load_2d_hint(st + Cfg::kXBytes + h * 16384, &tmW, &full[s], kb * BK, n0 + h * 128, pol_w);
+            if (FP8) tma_load_2d(sc_ring + (it % SC_STAGES) * TM, &tmS, &full[s], m0, kb);
           }
-          if (FP8) tma_load_2d(sc_ring + (it % SC_STAGES) * TM, &tmS, &full[s], m0, kb);
           issued = it + 1;
         }
-        if (!ok) {
-          // drain: wait (bounded) for the loads already issued so none lands after the CTA exits
+        if (!ok && (!PAIR || crank == 0)) {
+          // drain: wait (bounded) for the loads already issued so none lands after the CTA exits (in a pair
+          // the cluster barrier at the end additionally keeps both CTAs alive until both producers are done)
           for (int it = max(0, issued - STAGES); it < issued; ++it)
             mbar_wait(&full[it % STAGES], (it / STAGES) & 1, 1u << 12);
         }
       }
     } else if (warp == 1) {
-      // ---------------- MMA issuer ----------------
-      if (elect_one()) {
-        constexpr uint32_t idesc = FP8 ? make_idesc(128, TN, 0, 0) : make_idesc(128, TN, 1, 1);
+      // ---------------- MMA issuer (in a pair: the leading CTA only) ----------------
+      if (crank == 0 && elect_one()) {
+        constexpr uint32_t idesc = FP8 ? make_idesc(PAIR ? 256 : 128, TN, 0, 0) : make_idesc(PAIR ? 256 : 128, TN, 1, 1);
         int seg = 0;        // accumulator uses so far (fp8: one per K block, bf16: one per tile segment)
         UnitIter ui(u0, sch);
         for (int it = 0; it < nunits; ++it, ui.next(sch)) {
@@ -322,15 +349,24 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             for (int k = 0; k < 4; ++k) {   // 4 MMAs of 32 bytes of K each per 128-byte row
               const uint32_t accumulate = FP8 ? (k > 0) : (!seg_start || k > 0);
               const uint32_t d = tmem_base + b * kBufCols + h * TN;
-              if (EXP_IS(3)) continue;
-              if (FP8) mma_f8f6f4(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
-              else mma_f16(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
+              if (PAIR) {
+                if (FP8) mma_f8f6f4_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
+                else mma_f16_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
+              } else {
+                if (FP8) mma_f8f6f4(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
+                else mma_f16(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
+              }
             }
             if (HB == 2) tc_commit(&tmem_full[b * 2 + h]);
           }
           if (!acc_ok) { report(status, kErrMmaWaitAccum); break; }
-          tc_commit(&empty[s]);
-          if (HB == 1 && (FP8 || seg_end)) tc_commit(&tmem_full[b]);
+          if (PAIR) {
+            tc_commit_pair(&empty[s], 3);                                  // frees the stage in both CTAs
+            if (FP8 || seg_end) tc_commit_pair(&tmem_full[b], 3);          // hands the accumulator to both epilogues
+          } else {
+            tc_commit(&empty[s]);
+            if (HB == 1 && (FP8 || seg_end)) tc_commit(&tmem_full[b]);
+          }
           if (seg_end) ++seg;
         }
       }
@@ -342,7 +378,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const int quarter = warp & 3;
     const int g = ew >> 2;                                   // token half (MH == 2) or column half (MH == 1)
     const int col_base = g * kCols;                          // first TMEM column of this thread inside a buffer
-    const int m_local = (MH == 2 ? g * 128 : 0) + quarter * 32 + lane;
+    const int m_cta = (MH == 2 ? g * 128 : 0) + quarter * 32 + lane;      // token row inside this CTA's part
+    const int m_local = m_cta + static_cast<int>(crank) * CM;              // ... inside the tile
     const int n_off = (MH == 2 ? 0 : g * kCols);
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + col_base;
     const int et = threadIdx.x - 128;                        // index among the epilogue threads
@@ -350,6 +387,13 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     int seg = 0;
     int seg_kb0 = 0;
     bool ok = true;
+    // arrival on the accumulator-drained barrier: local, or in the leading CTA of a pair
+    auto release_accum = [&](int hb) {
+      if (PAIR) mbar_arrive_remote(tmem_empty0_remote + hb * 8);
+      else mbar_arrive(&tmem_empty[hb]);
+    };
+    // split tiles are finished per CTA: in a pair every CTA owns the token half it accumulated
+    auto counter_of = [&](int tile) { return PAIR ? tile * 2 + static_cast<int>(crank) : tile; };
     int pend_tile[2];      // tiles this CTA holds only a part of (at most its first and its last)
     int npend = 0;
     UnitIter ui(u0, sch);
@@ -371,8 +415,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         ok = mbar_wait(&tmem_full[hb], (it >> 1) & 1);
         if (!ok) { report(status, kErrEpilogueWait); break; }
         tc_fence_after();
-        if (warp_active && !EXP_GE(2)) {
-          const float s = sc_ring[(it % SC_STAGES) * TM + m_local] *
+        if (warp_active) {
+          const float s = sc_ring[(it % SC_STAGES) * CM + m_cta] *
                           __ldg(&wscale[static_cast<size_t>((n0 + n_off) >> 7) * sch.KB + kb]);
           uint32_t v[2][32];
           tmem_ld_32x32b_x32(lane_addr + b * kBufCols, v[0]);
@@ -382,15 +426,12 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             tmem_ld_wait(cur);
             if (c + 32 < kCols) tmem_ld_32x32b_x32(lane_addr + b * kBufCols + c + 32, v[((c >> 5) + 1) & 1]);
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              if (EXP_IS(1)) { if (j == 0) acc.fma_pair((c + j) >> 1, cur[j], cur[j + 1], s); continue; }
-              acc.fma_pair((c + j) >> 1, cur[j], cur[j + 1], s);
-            }
+            for (int j = 0; j < 32; j += 2) acc.fma_pair((c + j) >> 1, cur[j], cur[j + 1], s);
           }
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[hb]);
+        if (lane == 0) release_accum(hb);
       } else if (seg_end) {
         const int b = seg & 1;
         ok = mbar_wait(&tmem_full[b], (seg >> 1) & 1);
@@ -409,7 +450,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[b]);
+        if (lane == 0) release_accum(b);
       }
       if (!seg_end) continue;
       ++seg;
@@ -429,7 +470,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           wsp[(j >> 2) * kEpiThreads] = make_float4(acc.get(j), acc.get(j + 1), acc.get(j + 2), acc.get(j + 3));
         __threadfence();
         epi_barrier();
-        if (et == 0) atomicAdd(&counters[tile], 1);
+        if (et == 0) atomicAdd(&counters[counter_of(tile)], 1);
         pend_tile[npend++] = tile;
         continue;
       }
@@ -472,13 +513,15 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       const long long t_lo = static_cast<long long>(tile) * sch.KB, t_hi = t_lo + sch.KB - 1;
       const int c_lo = sch.owner(t_lo), c_hi = sch.owner(t_hi);
       const int n = c_hi - c_lo + 1;
-      const int mine = blockIdx.x - c_lo;
+      const int mine = worker - c_lo;
+      // contributor c is a CTA, or in a pair the CTA of worker c that holds the same token half as this one
       for (int c = c_lo + et; c <= c_hi; c += kEpiThreads)
-        cslots[c - c_lo] = c * 2 + (tile == static_cast<int>(sch.begin(c) / sch.KB) ? 0 : 1);
+        cslots[c - c_lo] = (PAIR ? c * 2 + static_cast<int>(crank) : c) * 2 +
+                           (tile == static_cast<int>(sch.begin(c) / sch.KB) ? 0 : 1);
       if (et == 0) {
         int polls = 0;
         int seen;
-        while ((seen = ld_acquire_gpu(&counters[tile])) < n && ++polls < kSplitPolls) __nanosleep(64);
+        while ((seen = ld_acquire_gpu(&counters[counter_of(tile)])) < n && ++polls < kSplitPolls) __nanosleep(64);
         *flag = seen >= n;
       }
       epi_barrier();
@@ -521,8 +564,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       }
       epi_barrier();   // all reads of the partials and of cslots are done
       if (et == 0) {
-        const int old = atomicAdd(&counters[tile], 1);
-        if (old == 2 * n - 1) counters[tile] = 0;
+        const int old = atomicAdd(&counters[counter_of(tile)], 1);
+        if (old == 2 * n - 1) counters[counter_of(tile)] = 0;
       }
     }
 
@@ -548,7 +591,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (PAIR) cluster_sync();   // neither CTA frees TMEM or leaves while the other may still use its memory
+  if (warp == 1) {
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -556,11 +603,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 // ------------------------------------------------------------------------------------------------
 using tgi::make_map_2d;
 
-template <int MH, int TN, int STAGES, bool FP8>
+template <int MH, int TN, int STAGES, bool FP8, bool PAIR>
 int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C,
            const void* bias, int M, int N, int K, int max_ctas, float* ws, int* counters, int* status,
            cudaStream_t stream, const PushArgs* push_args = nullptr) {
-  using Cfg = TileCfg<MH, TN>;
+  using Cfg = TileCfg<MH, TN, PAIR>;
   PushArgs push;
   if (push_args != nullptr) {
     push = *push_args;
@@ -573,54 +620,76 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
   const uint64_t pitch = static_cast<uint64_t>(K) * (FP8 ? 1 : 2);
   // both operands are fetched in boxes of 128 rows x 128 bytes (one swizzle atom wide)
   int rc = make_map_2d(&tmW, dt, W, N, K, pitch, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B);
-#ifdef TGI_GEMM_EXP
-  if (g_exp_host & 8)   // weights pre-tiled: every 128 x 128-byte box contiguous in memory
-    rc = make_map_2d(&tmW, dt, W, static_cast<uint64_t>(N) * (pitch / 128), 128 / (FP8 ? 1 : 2), 128, 128, BK,
-                     CU_TENSOR_MAP_SWIZZLE_128B);
-#endif
   if (rc) return rc;
   rc = make_map_2d(&tmX, dt, X, M, K, pitch, 128, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   if (FP8) {
     rc = make_map_2d(&tmS, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, xs_t, K / 128, M, static_cast<uint64_t>(xs_pitch) * 4, 1,
-                     Cfg::TM, CU_TENSOR_MAP_SWIZZLE_NONE);
+                     Cfg::CM, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
   } else {
     tmS = tmX;
   }
-  // stages + (fp8) activation-scale ring [STAGES+2][TM] + alignment slack + barriers
-  const size_t smem = STAGES * Cfg::kStageBytes + (FP8 ? (STAGES + 2) * Cfg::TM * 4 : 0) + 1024 + 256 + kMaxGrid * 4;
-  auto kern = gemm_streamk_kernel<MH, TN, STAGES, FP8>;
-  // the shared-memory opt-in is a per-device attribute of the function: one bit per device ordinal
+  // stages + (fp8) activation-scale ring [STAGES+2][CM] + alignment slack + barriers
+  const size_t smem = STAGES * Cfg::kStageBytes + (FP8 ? (STAGES + 2) * Cfg::CM * 4 : 0) + 1024 + 256 + kMaxGrid * 4;
+  auto kern = gemm_streamk_kernel<MH, TN, STAGES, FP8, PAIR>;
+  // The shared-memory opt-in is a per-device attribute of the function; the number of CTA pairs that can
+  // be resident at once (a GPC with an odd number of usable SMs cannot pair its last one) is a property of
+  // the device too.  Both are looked up once per device ordinal.
   static std::atomic<unsigned long long> attr_set{0};
+  static std::atomic<int> max_pairs[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -2;
   const unsigned long long dev_bit = 1ull << (dev & 63);
   if (!(attr_set.load(std::memory_order_acquire) & dev_bit)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return -2;
+    if (PAIR) {
+      cudaLaunchConfig_t q{};
+      q.gridDim = dim3(2 * kMaxGrid);
+      q.blockDim = dim3(kThreads);
+      q.dynamicSmemBytes = smem;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, kern, &q) != cudaSuccess || clusters < 1) {
+        cudaGetLastError();
+        return -4;
+      }
+      max_pairs[dev & 63].store(clusters, std::memory_order_relaxed);
+    }
     attr_set.fetch_or(dev_bit, std::memory_order_release);
   }
+  // workers: CTAs, or CTA pairs
+  int max_workers = PAIR ? max_ctas / 2 : max_ctas;
+  if (PAIR && max_workers > max_pairs[dev & 63].load(std::memory_order_relaxed))
+    max_workers = max_pairs[dev & 63].load(std::memory_order_relaxed);
+  if (max_workers > (PAIR ? kMaxGrid / 2 : kMaxGrid)) max_workers = PAIR ? kMaxGrid / 2 : kMaxGrid;
+  if (max_workers < 1) return -4;
   const long long units =
       static_cast<long long>((N + TN - 1) / TN) * ((M + Cfg::TM - 1) / Cfg::TM) * ((K + BK - 1) / BK);
-  // Grid size.  Splitting a tile between CTAs costs a 128 KB fp32 partial per contributor (as much
-  // traffic as 8 K blocks of weights), so small problems prefer whole tiles or a few aligned splits:
-  //   stream-K over all SMs:      ceil(units / max_ctas) K blocks per CTA, plus the fix-up (~2 blocks)
-  //   tiles x s aligned splits:   ceil(KB / s) K blocks per CTA, s = 1 needs no fix-up at all
+  // Number of workers.  Splitting a tile between workers costs a 128 KB fp32 partial per contributing CTA (as
+  // much traffic as 8 K blocks of weights), so small problems prefer whole tiles or a few aligned splits:
+  //   stream-K over all workers:  ceil(units / workers) K blocks each, plus the fix-up (~2 blocks)
+  //   tiles x s aligned splits:   ceil(KB / s) K blocks each, s = 1 needs no fix-up at all
   const int KBn = (K + BK - 1) / BK;
   const int tiles = static_cast<int>(units / KBn);
-  if (max_ctas > kMaxGrid) max_ctas = kMaxGrid;
-  int grid = max_ctas;
+  int grid = max_workers;
   if (grid > units) grid = static_cast<int>(units);
   if (grid < 1) grid = 1;
-  if (tiles <= max_ctas) {
+  if (tiles <= max_workers) {
     // Rough costs in microseconds, from timelines measured on B200: a K block takes about 0.4 us per
     // CTA; every partial tile costs 128 KB written and read through L2 by all CTAs at once (about
     // 0.05 us each at ~5 TB/s) and a split adds ~3 us of publish / wait / reduce latency.
     const double kUnit = 0.4, kPartial = 0.05, kSync = 3.0;
     const double partials_sk = static_cast<double>(grid + tiles < 2 * grid ? grid + tiles : 2 * grid);
     double best = static_cast<double>((units + grid - 1) / grid) * kUnit + partials_sk * kPartial + kSync;
-    for (int s = 1; s <= max_ctas / tiles && s <= KBn; ++s) {
+    for (int s = 1; s <= max_workers / tiles && s <= KBn; ++s) {
       const double c = static_cast<double>((KBn + s - 1) / s) * kUnit + (s > 1 ? tiles * s * kPartial + kSync : 0.0);
       if (c < best) {
         best = c;
@@ -628,9 +697,10 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
       }
     }
   }
-  const cudaError_t err = tgi::launch(kern, dim3(grid), dim3(kThreads), smem, stream, tmW, tmX, tmS, wscale,
-                                      static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, K,
-                                      ws, counters, status, push);
+  const cudaError_t err =
+      tgi::launch_cluster(kern, dim3(PAIR ? 2 * grid : grid), dim3(kThreads), smem, stream, PAIR ? 2 : 1, tmW, tmX, tmS,
+                          wscale, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, K, ws,
+                          counters, status, push);
   return err == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -652,6 +722,27 @@ int fill_push(PushArgs& p, void* const* heaps, int rank, int world, int rows_per
 
 }  // namespace
 
+static int g_wide_m = 128;
+static int g_pairs = 1;
+
+namespace {
+template <bool FP8>
+int dispatch(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C, const void* bias,
+             int M, int N, int K, int max_ctas, float* ws, int* counters, int* status, cudaStream_t stream,
+             const PushArgs* push) {
+  if (M <= g_wide_m)
+    return launch<1, 256, 4, FP8, false>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status,
+                                         stream, push);
+  if (g_pairs && max_ctas >= 2) {
+    const int rc = launch<1, 256, 6, FP8, true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters,
+                                                status, stream, push);
+    if (rc != -4) return rc;   // -4: this device cannot place a pair; fall back to single CTAs
+  }
+  return launch<2, 128, 4, FP8, false>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status,
+                                       stream, push);
+}
+}  // namespace
+
 extern "C" {
 
 // Floats of stream-K workspace a launch with `ctas` CTAs may touch (two partial-tile slots per CTA).
@@ -664,24 +755,20 @@ long long tgi_gemm_workspace_floats(int M, int ctas) {
 int tgi_gemm_num_tiles(int M, int N) {
   const int a = ((N + 127) / 128) * ((M + 255) / 256);
   const int b = ((N + 255) / 256) * ((M + 127) / 128);
-  return a > b ? a : b;   // upper bound over both tile shapes
+  const int c = 2 * ((N + 255) / 256) * ((M + 255) / 256);   // a pair keeps one counter per CTA and tile
+  return a > b ? (a > c ? a : c) : (b > c ? b : c);   // upper bound over all tile shapes
 }
 
-#ifdef TGI_GEMM_EXP
-void tgi_gemm_set_exp(int v) { g_exp_host = v; cudaMemcpyToSymbol(g_exp, &v, sizeof(int)); }
-#endif
-
-// Token counts up to this limit use the 128 x 256 tile (weights-wide); larger ones the 256 x 128 tile.
-static int g_wide_m = 128;
+// Token counts up to this limit use one CTA per 128 x 256 tile (weights-wide); larger ones CTA pairs on
+// 256 x 256 tiles, or single CTAs on 256 x 128 tiles when pairs are switched off.
 void tgi_gemm_set_wide_m(int m) { g_wide_m = m < 128 ? 128 : m; }
+void tgi_gemm_set_pairs(int on) { g_pairs = on != 0; }
 
 int tgi_gemm_bf16(const void* X, const void* W, void* C, const void* bias, int M, int N, int K, int max_ctas,
                   float* ws, int* counters, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0) return -10;  // TMA row pitch must be a multiple of 16 bytes
-  if (M > g_wide_m)
-    return launch<2, 128, 4, false>(X, nullptr, 0, W, nullptr, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
-  return launch<1, 256, 4, false>(X, nullptr, 0, W, nullptr, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
+  return dispatch<false>(X, nullptr, 0, W, nullptr, C, bias, M, N, K, max_ctas, ws, counters, status, stream, nullptr);
 }
 
 int tgi_gemm_fp8_block(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C,
@@ -689,9 +776,7 @@ int tgi_gemm_fp8_block(const void* X, const float* xs_t, int xs_pitch, const voi
                        cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 128 != 0 || xs_pitch % 4 != 0) return -10;
-  if (M > g_wide_m)
-    return launch<2, 128, 4, true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
-  return launch<1, 256, 4, true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status, stream);
+  return dispatch<true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status, stream, nullptr);
 }
 
 // Row-parallel GEMMs of a tensor-parallel group: same products, but every output row is stored into the
@@ -708,18 +793,10 @@ int tgi_gemm_push(int fp8, const void* X, const float* xs_t, int xs_pitch, const
   if (rc) return rc;
   if (fp8) {
     if (K % 128 != 0 || xs_pitch % 4 != 0) return -10;
-    if (M > g_wide_m)
-      return launch<2, 128, 4, true>(X, xs_t, xs_pitch, W, wscale, nullptr, bias, M, N, K, max_ctas, ws, counters, status,
-                                     stream, &p);
-    return launch<1, 256, 4, true>(X, xs_t, xs_pitch, W, wscale, nullptr, bias, M, N, K, max_ctas, ws, counters, status,
-                                   stream, &p);
+    return dispatch<true>(X, xs_t, xs_pitch, W, wscale, nullptr, bias, M, N, K, max_ctas, ws, counters, status, stream, &p);
   }
   if (K % 8 != 0) return -10;
-  if (M > g_wide_m)
-    return launch<2, 128, 4, false>(X, nullptr, 0, W, nullptr, nullptr, bias, M, N, K, max_ctas, ws, counters, status,
-                                    stream, &p);
-  return launch<1, 256, 4, false>(X, nullptr, 0, W, nullptr, nullptr, bias, M, N, K, max_ctas, ws, counters, status, stream,
-                                  &p);
+  return dispatch<false>(X, nullptr, 0, W, nullptr, nullptr, bias, M, N, K, max_ctas, ws, counters, status, stream, &p);
 }
 
 }  // extern "C"

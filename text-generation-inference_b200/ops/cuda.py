@@ -57,7 +57,15 @@ def load():
     wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
     if wide:
         _LIB.tgi_gemm_set_wide_m(c_int(int(wide)))
+    if os.environ.get("TGI_B200_GEMM_PAIRS", "1") == "0":   # single-CTA 256 x 128 tiles instead of CTA pairs
+        _LIB.tgi_gemm_set_pairs(c_int(0))
     return _LIB
+
+
+def set_gemm_pairs(on: bool) -> None:
+    """Use CTA pairs (``cta_group::2``, 256 x 256 tiles) for GEMMs with more than 128 tokens (default), or
+    single CTAs on 256 x 128 tiles."""
+    load().tgi_gemm_set_pairs(c_int(1 if on else 0))
 
 
 def _ptr(t: Optional[torch.Tensor]):
