@@ -372,13 +372,9 @@ class SparseMoE:
             w, idx = ops.moe_topk_softmax(logits, self.top_k, self.renorm)
         if self.expert_parallel is not None:
             out = self.expert_parallel(x, w, idx)
-        elif x.is_cuda and (x.shape[0] <= 512 or torch.cuda.is_current_stream_capturing()):
-            # decode-sized step: fixed-shape evaluation of every expert (graph capturable, weight-bound)
-            from ..parallel.expert import dense_experts
-
-            out = dense_experts(x, self.w_gate_up, self.w_down, w, idx, 0, self.act)
         else:
-            out = ops.moe_experts(x, self.w_gate_up, self.w_down, w.to(x.dtype), idx, self.act)
+            # routed rows only: grouped kernels on CUDA (no host synchronisation, graph capturable), loop on CPU
+            out = ops.moe_experts(x, self.w_gate_up, self.w_down, w, idx, self.act)
         if self.shared is not None:
             s = self.shared(x, reduce=False)
             if self.shared_gate is not None:

@@ -147,6 +147,8 @@ def fused_sample(scores, temperature=None, top_k=None, top_p=None, do_sample=Non
 
 
 def moe_topk_softmax(router_logits, top_k, renormalize=True):
+    if use_native(router_logits) and router_logits.shape[-1] <= 256 and top_k <= 8:
+        return native().moe_topk_softmax(router_logits, top_k, renormalize)
     return ref.moe_topk_softmax(router_logits, top_k, renormalize)
 
 
@@ -154,7 +156,9 @@ def moe_sparsemixer(router_logits, jitter_eps=0.01):
     return ref.moe_sparsemixer(router_logits, jitter_eps)
 
 
-def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu"):
-    if use_native(x):
-        return native().moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act)
-    return ref.moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act)
+def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu", first: int = 0):
+    """Routed experts ``first .. first + E_local - 1`` (``first`` > 0: an expert-parallel rank's share)."""
+    if use_native(x) and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 \
+            and (w_gate_up.shape[1] // 2) % 8 == 0 and w_gate_up.shape[0] <= 256 and topk_ids.shape[1] <= 8:
+        return native().moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act, first)
+    return ref.moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act, first)

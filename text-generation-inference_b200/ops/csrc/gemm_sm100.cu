@@ -15,10 +15,13 @@
 // halves from both CTAs' shared memory, and each CTA finds the accumulator rows of its tokens in
 // its own TMEM.  Per K block a CTA then moves 32 KB through L2 -> shared memory for 128 x 256
 // outputs where a single CTA needs 48 KB (the activation tile is not fetched once per 128 weight
-// rows any more), and operand traffic into shared memory is what bounds these GEMMs at M >= 256.
-// (A 256 x 128 single-CTA tile is kept for GPUs or launches that cannot form pairs.)
-// TMEM lanes run over TOKENS and columns over weight rows.  That orientation is what makes the fp8 promotion cheap: the combined block scale
-// a_scale[m, kb] * w_scale[slab, kb] is one scalar per thread and K block, kept in a register,
+// rows any more).  Measured on B200 against the 256 x 128 single-CTA tile, which is kept for
+// launches that cannot form pairs: bf16 4096 x 8192 x 8192 1050 against 874 TFLOP/s; block-scaled
+// fp8 256 x 57344 x 8192 180 against 187 us (there the hand-over of every K block's products to
+// the promotion warps, not operand traffic, sets the pace).
+//
+// TMEM lanes run over TOKENS and columns over weight rows.  That orientation is what makes the
+// fp8 promotion cheap: the combined block scale a_scale[m, kb] * w_scale[slab, kb] is one scalar per thread and K block, kept in a register,
 // instead of a vector that every lane would have to fetch from shared memory (measured: broadcast
 // loads of a per-column scale vector cost 2x the FMAs they feed, because shared memory delivers
 // 128 B/clk per SM however many lanes read the same word).  It also gives every thread one
@@ -63,7 +66,7 @@ constexpr int kCols = 128;                 // accumulator columns per epilogue t
 constexpr int kTileElems = 256 * 128;      // outputs per tile in both configurations
 constexpr int kBufCols = 256;              // TMEM columns per accumulator buffer (two buffers)
 
-template <int MH, int TN, bool PAIR>
+template <int MH, int TN, bool PAIR, bool FP8 = false>
 struct TileCfg {
   static_assert(MH * TN == 256, "an accumulator buffer is 256 TMEM columns");
   static_assert(!PAIR || MH == 1, "a pair runs the 128 x 256 per-CTA configuration");
@@ -73,6 +76,12 @@ struct TileCfg {
   static constexpr int kXBytes = CM * 128;             // one 128-byte K row per token
   static constexpr int kWBytes = WROWS * 128;
   static constexpr int kStageBytes = kXBytes + kWBytes;   // 48 KB, 32 KB in a pair
+  // Block-scaled fp8 hands every K block's products to the epilogue.  With two token halves (MH == 2) each
+  // half of an accumulator buffer is signalled on its own full / drained barrier pair, so the promotion of
+  // half 0 starts while the MMAs of half 1 still run.  (Splitting the 256 columns of the MH == 1 buffers
+  // into 2 or 4 separately signalled column groups was measured slower: 180 -> 195 -> 222 us on
+  // 256 x 57344 x 8192, the extra commits and waits of the single issuing thread cost more than they hide.)
+  static constexpr int SUB = (FP8 && MH == 2) ? 2 : 1;
 };
 
 // Optional destination of the output rows in peer memory (tensor-parallel row-parallel GEMMs): row m
@@ -91,6 +100,7 @@ struct PushArgs {
 };
 
 constexpr int kMaxGrid = 160;              // upper bound of the grid size (one CTA per SM)
+int g_last_grid = 0;                       // CTAs of the most recent launch (diagnostics)
 constexpr int kSplitPolls = 1 << 20;       // polls of a split-tile counter before giving up (about 0.1 s)
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
@@ -182,7 +192,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
                     float* __restrict__ ws, int* __restrict__ counters, int* __restrict__ status,
                     const __grid_constant__ PushArgs push) {
-  using Cfg = TileCfg<MH, TN, PAIR>;
+  using Cfg = TileCfg<MH, TN, PAIR, FP8>;
   // first element of output row m: in C, or in the owner's peer-memory slot of this rank
   auto out_row = [&](int m) -> __nv_bfloat16* {
     if (push.world == 0) return C + static_cast<size_t>(m) * N;
@@ -203,14 +213,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   float* sc_ring = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes);   // [SC_STAGES][CM] (fp8 only)
   uint64_t* full = reinterpret_cast<uint64_t*>(sc_ring + (FP8 ? SC_STAGES * CM : 0));
   uint64_t* empty = full + STAGES;
-  // Accumulator hand-over.  Block-scaled fp8 with two token halves (MH == 2) signals every half of a buffer on
-  // its own barrier pair: the promotion of half 0 starts while the MMAs of half 1 are still running and the
-  // MMA warp can refill a half as soon as its four epilogue warps have drained it, which shortens the
-  // MMA -> TMEM load -> release chain that a K block goes through.
-  constexpr int HB = (FP8 && MH == 2) ? 2 : 1;   // barrier pairs per accumulator buffer
-  uint64_t* tmem_full = empty + STAGES;      // [2 * HB]
-  uint64_t* tmem_empty = tmem_full + 4;      // [2 * HB]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 4);
+  constexpr int SUB = Cfg::SUB;              // separately signalled parts of an accumulator buffer
+  uint64_t* tmem_full = empty + STAGES;      // [2 * SUB]
+  uint64_t* tmem_empty = tmem_full + 8;      // [2 * SUB]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 8);
   int* flag = reinterpret_cast<int*>(tmem_holder + 1);
   int* cslots = flag + 1;                    // [kMaxGrid] workspace slot of every contributor of a split tile
   {
@@ -227,6 +233,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     }
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // every barrier of a pair is signalled at least in part from the other CTA: short re-evaluation interval
+  auto wait = [](uint64_t* bar, uint32_t parity) { return PAIR ? mbar_wait_fast(bar, parity) : mbar_wait(bar, parity); };
   Sched sch;
   sch.n_tiles = (N + TN - 1) / TN;
   sch.m_tiles = (M + TM - 1) / TM;
@@ -242,9 +250,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int b = 0; b < 2 * HB; ++b) {
+    for (int b = 0; b < 2 * SUB; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], (PAIR ? 2 : 1) * kEpiWarps / HB);
+      // a part is drained by the four warps (one per lane quarter) of one epilogue group, the whole buffer by all eight
+      mbar_init(&tmem_empty[b], (PAIR ? 2 : 1) * (SUB > 1 ? kEpiWarps / 2 : kEpiWarps));
     }
     fence_barrier_init();
     prefetch_tensormap(&tmW);
@@ -287,7 +296,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           const int kb = ui.kb;
           const int n0 = ui.tn * TN, m0 = ui.tm * TM;
           const int s = it % STAGES;
-          if (it >= STAGES) ok = mbar_wait(&empty[s], ((it / STAGES) - 1) & 1);
+          if (it >= STAGES) ok = wait(&empty[s], ((it / STAGES) - 1) & 1);
           if (!ok) { report(status, kErrProducerWait); break; }
           uint8_t* st = smem + s * Cfg::kStageBytes;
           constexpr uint32_t kCtaBytes = Cfg::kStageBytes + (FP8 ? CM * 4 : 0);
@@ -319,7 +328,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     } else if (warp == 1) {
       // ---------------- MMA issuer (in a pair: the leading CTA only) ----------------
       if (crank == 0 && elect_one()) {
-        constexpr uint32_t idesc = FP8 ? make_idesc(PAIR ? 256 : 128, TN, 0, 0) : make_idesc(PAIR ? 256 : 128, TN, 1, 1);
+        constexpr int MMA_M = PAIR ? 256 : 128;
+        constexpr uint32_t idesc = FP8 ? make_idesc(MMA_M, TN, 0, 0) : make_idesc(MMA_M, TN, 1, 1);
         int seg = 0;        // accumulator uses so far (fp8: one per K block, bf16: one per tile segment)
         UnitIter ui(u0, sch);
         for (int it = 0; it < nunits; ++it, ui.next(sch)) {
@@ -328,27 +338,28 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           const bool seg_end = (it == nunits - 1) || kb == sch.KB - 1;
           const int use = FP8 ? it : seg;
           const int b = use & 1;
-          if (HB == 1 && (FP8 || seg_start) && use >= 2 && !mbar_wait(&tmem_empty[b], ((use >> 1) - 1) & 1)) {
+          if (!FP8 && seg_start && use >= 2 && !wait(&tmem_empty[b], ((use >> 1) - 1) & 1)) {
             report(status, kErrMmaWaitAccum);
             break;
           }
           const int s = it % STAGES;
-          if (!mbar_wait(&full[s], (it / STAGES) & 1)) { report(status, kErrMmaWaitFull); break; }
+          if (!wait(&full[s], (it / STAGES) & 1)) { report(status, kErrMmaWaitFull); break; }
           tc_fence_after();
           const uint32_t x_addr = smem_u32(smem + s * Cfg::kStageBytes);
-          const uint64_t dw = make_desc_sw128(x_addr + Cfg::kXBytes);
           bool acc_ok = true;
+          const uint64_t dw = make_desc_sw128(x_addr + Cfg::kXBytes);
 #pragma unroll
-          for (int h = 0; h < MH; ++h) {
-            if (HB == 2) {
-              if (use >= 2 && !mbar_wait(&tmem_empty[b * 2 + h], ((use >> 1) - 1) & 1)) { acc_ok = false; break; }
+          for (int h = 0; h < MH; ++h) {   // token halves
+            if (FP8) {
+              const int p = SUB == 2 ? h : 0;
+              if (use >= 2 && !wait(&tmem_empty[b * SUB + p], ((use >> 1) - 1) & 1)) { acc_ok = false; break; }
               tc_fence_after();
             }
             const uint64_t dx = make_desc_sw128(x_addr + h * 16384);
+            const uint32_t d = tmem_base + b * kBufCols + h * TN;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {   // 4 MMAs of 32 bytes of K each per 128-byte row
               const uint32_t accumulate = FP8 ? (k > 0) : (!seg_start || k > 0);
-              const uint32_t d = tmem_base + b * kBufCols + h * TN;
               if (PAIR) {
                 if (FP8) mma_f8f6f4_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
                 else mma_f16_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
@@ -357,15 +368,19 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 else mma_f16(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
               }
             }
-            if (HB == 2) tc_commit(&tmem_full[b * 2 + h]);
+            if (FP8) {   // hand this part to the epilogue (of both CTAs in a pair)
+              const int p = SUB == 2 ? h : 0;
+              if (PAIR) tc_commit_pair(&tmem_full[b * SUB + p], 3);
+              else tc_commit(&tmem_full[b * SUB + p]);
+            }
           }
           if (!acc_ok) { report(status, kErrMmaWaitAccum); break; }
           if (PAIR) {
             tc_commit_pair(&empty[s], 3);                                  // frees the stage in both CTAs
-            if (FP8 || seg_end) tc_commit_pair(&tmem_full[b], 3);          // hands the accumulator to both epilogues
+            if (!FP8 && seg_end) tc_commit_pair(&tmem_full[b], 3);
           } else {
             tc_commit(&empty[s]);
-            if (HB == 1 && (FP8 || seg_end)) tc_commit(&tmem_full[b]);
+            if (!FP8 && seg_end) tc_commit(&tmem_full[b]);
           }
           if (seg_end) ++seg;
         }
@@ -411,8 +426,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       }
       if (FP8) {
         const int b = it & 1;
-        const int hb = HB == 2 ? b * 2 + g : b;   // g: token half of this warp when MH == 2
-        ok = mbar_wait(&tmem_full[hb], (it >> 1) & 1);
+        const int hb = b * SUB + (SUB == 2 ? g : 0);   // g: token half of this warp when MH == 2
+        ok = wait(&tmem_full[hb], (it >> 1) & 1);
         if (!ok) { report(status, kErrEpilogueWait); break; }
         tc_fence_after();
         if (warp_active) {
@@ -434,7 +449,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (lane == 0) release_accum(hb);
       } else if (seg_end) {
         const int b = seg & 1;
-        ok = mbar_wait(&tmem_full[b], (seg >> 1) & 1);
+        ok = wait(&tmem_full[b], (seg >> 1) & 1);
         if (!ok) { report(status, kErrEpilogueWait); break; }
         tc_fence_after();
         if (warp_active) {
@@ -607,7 +622,7 @@ template <int MH, int TN, int STAGES, bool FP8, bool PAIR>
 int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C,
            const void* bias, int M, int N, int K, int max_ctas, float* ws, int* counters, int* status,
            cudaStream_t stream, const PushArgs* push_args = nullptr) {
-  using Cfg = TileCfg<MH, TN, PAIR>;
+  using Cfg = TileCfg<MH, TN, PAIR, FP8>;
   PushArgs push;
   if (push_args != nullptr) {
     push = *push_args;
@@ -631,7 +646,7 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
     tmS = tmX;
   }
   // stages + (fp8) activation-scale ring [STAGES+2][CM] + alignment slack + barriers
-  const size_t smem = STAGES * Cfg::kStageBytes + (FP8 ? (STAGES + 2) * Cfg::CM * 4 : 0) + 1024 + 256 + kMaxGrid * 4;
+  const size_t smem = STAGES * Cfg::kStageBytes + (FP8 ? (STAGES + 2) * Cfg::CM * 4 : 0) + 1024 + 512 + kMaxGrid * 4;
   auto kern = gemm_streamk_kernel<MH, TN, STAGES, FP8, PAIR>;
   // The shared-memory opt-in is a per-device attribute of the function; the number of CTA pairs that can
   // be resident at once (a GPC with an odd number of usable SMs cannot pair its last one) is a property of
@@ -697,6 +712,7 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
       }
     }
   }
+  g_last_grid = PAIR ? 2 * grid : grid;
   const cudaError_t err =
       tgi::launch_cluster(kern, dim3(PAIR ? 2 * grid : grid), dim3(kThreads), smem, stream, PAIR ? 2 : 1, tmW, tmX, tmS,
                           wscale, static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(bias), M, N, K, ws,
@@ -763,6 +779,8 @@ int tgi_gemm_num_tiles(int M, int N) {
 // 256 x 256 tiles, or single CTAs on 256 x 128 tiles when pairs are switched off.
 void tgi_gemm_set_wide_m(int m) { g_wide_m = m < 128 ? 128 : m; }
 void tgi_gemm_set_pairs(int on) { g_pairs = on != 0; }
+// CTAs of the most recent GEMM launch of this process (diagnostics and benchmarks).
+int tgi_gemm_last_grid(void) { return g_last_grid; }
 
 int tgi_gemm_bf16(const void* X, const void* W, void* C, const void* bias, int M, int N, int K, int max_ctas,
                   float* ws, int* counters, int* status, cudaStream_t stream) {

@@ -85,6 +85,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return false;
 }
 
+// Wait for barriers that are signalled from the other CTA of a pair (remote arrivals, multicast commits,
+// bytes of the peer's TMA loads).  A suspended try_wait is re-evaluated after its suspend time; the default
+// time is long (about 0.7 us measured) and would be paid on every hop of a cross-CTA pipeline, so these
+// waits pass a short suspend-time hint (nanoseconds).  Bounded like mbar_wait: `polls` tries, each of which
+// returns within the hint, about 0.2 s in total.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+constexpr uint32_t kFastWaitPolls = 1u << 23;
+__device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, uint32_t polls = kFastWaitPolls) {
+  for (uint32_t i = 0; i < polls; ++i) {
+    if (mbar_try_wait_hint(bar, parity, 32u)) return true;
+  }
+  return false;
+}
+
 // ---- TMA -----------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -223,8 +247,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on a barrier of another CTA of the cluster.  The plain form (as cutlass::arch::ClusterBarrier uses
+// it): what is handed over through these barriers here is TMEM, ordered by the tcgen05 fences around the
+// arrival, so no cluster-scope release of the thread's earlier memory writes is wanted on this path.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA loads of a CTA pair: data into this CTA's shared memory, bytes counted on a barrier that may
 // live in the other CTA of the pair (`bar_cluster_addr` from map_to_cta).  No multicast.

@@ -51,7 +51,8 @@ def load():
     for name in ("tgi_gemm_bf16", "tgi_gemm_fp8_block", "tgi_norm", "tgi_act_mul", "tgi_quant_act",
                  "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention", "tgi_paged_attention_ex",
                  "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status", "tgi_lora_shrink",
-                 "tgi_lora_expand"):
+                 "tgi_lora_expand", "tgi_moe_topk_softmax", "tgi_moe_sort", "tgi_moe_gather", "tgi_moe_grouped_gemm",
+                 "tgi_moe_combine", "tgi_gemm_last_grid"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
     wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
@@ -400,29 +401,62 @@ def fused_sample(scores: torch.Tensor, temperature=None, top_k=None, top_p=None,
     return ids, lps
 
 
-def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu"):
-    """Grouped expert MLP: tokens are sorted by expert and each expert's slab runs through the tcgen05 GEMM."""
+def moe_topk_softmax(router_logits: torch.Tensor, top_k: int, renormalize: bool = True):
+    """Softmax over the router logits and top-k selection in one kernel: ``(weights fp32 [T, k], ids int32 [T, k])``."""
+    lib = load()
+    T, E = router_logits.shape
+    if router_logits.dtype not in (torch.float32, torch.bfloat16):
+        router_logits = router_logits.float()
+    router_logits = router_logits.contiguous()
+    w = torch.empty(T, top_k, dtype=torch.float32, device=router_logits.device)
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=router_logits.device)
+    _check(lib.tgi_moe_topk_softmax(_ptr(router_logits), c_int(1 if router_logits.dtype == torch.float32 else 0), c_int(T),
+                                    c_int(E), c_int(top_k), c_int(1 if renormalize else 0), _ptr(w), _ptr(ids), _stream()),
+           "moe_topk_softmax")
+    return w, ids
+
+
+def moe_experts(x, w_gate_up, w_down, topk_weights, topk_ids, act="silu", first: int = 0):
+    """Routed expert MLPs of the experts ``first .. first + E_local - 1`` held in ``w_gate_up [E_local, 2I, H]`` /
+    ``w_down [E_local, H, I]``: ``out[t] = sum_slot w[t, slot] * MLP_{id[t, slot]}(x[t])`` over the slots whose
+    expert is local.  Five launches (group, gather, two grouped tcgen05 GEMMs with the activation and the routing
+    weight fused into their epilogues, combine), no host synchronisation, fixed buffer shapes: the whole sequence
+    is CUDA-graph capturable and only routed rows are computed."""
+    lib = load()
+    st = state(x.device)
     T, H = x.shape
-    E = w_gate_up.shape[0]
+    E_local, I2, _ = w_gate_up.shape
+    I = I2 // 2
     k = topk_ids.shape[1]
-    flat_e = topk_ids.reshape(-1)
-    order = torch.argsort(flat_e, stable=True)
-    tok = (order // k)
-    counts = torch.bincount(flat_e, minlength=E).tolist()
-    xs = x[tok]
-    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
-    wflat = topk_weights.reshape(-1)[order].float()
-    start = 0
-    for e, c in enumerate(counts):
-        if c == 0:
-            continue
-        sl = slice(start, start + c)
-        h = gemm_bf16(xs[sl], w_gate_up[e])
-        a = act_and_mul(h, act)
-        y = gemm_bf16(a, w_down[e])
-        out.index_add_(0, tok[sl], y.float() * wflat[sl].unsqueeze(1))
-        start += c
-    return out.to(x.dtype)
+    entries = T * k
+    dev = x.device
+    if T == 0:
+        return torch.zeros(0, H, dtype=x.dtype, device=dev)
+    assert x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+    assert w_gate_up.is_contiguous() and w_down.is_contiguous() and tuple(w_down.shape) == (E_local, H, I)
+    ids = topk_ids.to(torch.int32).contiguous()
+    tw = topk_weights.to(torch.float32).contiguous()
+    pos = torch.empty(entries, dtype=torch.int32, device=dev)
+    order = torch.empty(entries, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E_local + 1, dtype=torch.int32, device=dev)
+    grouped = torch.empty(entries, H, dtype=torch.bfloat16, device=dev)
+    hidden = torch.empty(entries, I, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(entries, H, dtype=torch.bfloat16, device=dev)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    s = _stream()
+    x = x.contiguous()
+    _check(lib.tgi_moe_sort(_ptr(ids), c_int(entries), c_int(first), c_int(E_local), _ptr(pos), _ptr(order), _ptr(offsets),
+                            s), "moe_sort")
+    _check(lib.tgi_moe_gather(_ptr(x), _ptr(order), _ptr(offsets), c_int(E_local), c_int(k), c_int(H), c_int(entries),
+                              _ptr(grouped), s), "moe_gather")
+    _check(lib.tgi_moe_grouped_gemm(c_int(0), _ptr(grouped), c_int(entries), _ptr(w_gate_up), c_int(E_local), c_int(I2),
+                                    c_int(H), _ptr(offsets), c_int(_ACT_CODES[act]), c_void_p(0), c_void_p(0),
+                                    _ptr(hidden), c_int(st.sm_count), _ptr(st.status), s), "moe_grouped_gemm(gate_up)")
+    _check(lib.tgi_moe_grouped_gemm(c_int(1), _ptr(hidden), c_int(entries), _ptr(w_down), c_int(E_local), c_int(H),
+                                    c_int(I), _ptr(offsets), c_int(0), _ptr(tw), _ptr(order), _ptr(y),
+                                    c_int(st.sm_count), _ptr(st.status), s), "moe_grouped_gemm(down)")
+    _check(lib.tgi_moe_combine(_ptr(y), _ptr(pos), c_int(T), c_int(k), c_int(H), _ptr(out), s), "moe_combine")
+    return out
 
 
 # ---- multi-adapter LoRA ------------------------------------------------------------------------

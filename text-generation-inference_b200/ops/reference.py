@@ -310,13 +310,15 @@ def moe_experts(
     topk_weights: torch.Tensor,
     topk_ids: torch.Tensor,
     act: str = "silu",
+    first: int = 0,
 ) -> torch.Tensor:
-    """Dense-loop mixture of experts: ``w_gate_up[E, 2I, H]``, ``w_down[E, H, I]``."""
+    """Dense-loop mixture of experts: ``w_gate_up[E, 2I, H]``, ``w_down[E, H, I]`` hold the experts
+    ``first .. first + E - 1``; slots routed to other experts contribute nothing."""
     T, H = x.shape
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
     E = w_gate_up.shape[0]
     for e in range(E):
-        tok, slot = (topk_ids == e).nonzero(as_tuple=True)
+        tok, slot = (topk_ids == e + first).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue
         h = F.linear(x[tok], w_gate_up[e])

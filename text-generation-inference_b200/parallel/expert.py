@@ -14,11 +14,11 @@ and the next RMSNorm, so an expert-parallel layer issues exactly one collective.
 
 Two evaluation modes of the local experts:
 
-* ``dense`` (decode-sized steps, CUDA-graph capturable): every local expert runs on all ``T`` tokens and
-  its output is scaled by the token's routing weight (zero when the token was not routed to it).  At
-  decode batch sizes an expert GEMM is bound by streaming its weights, which have to be read as soon as
-  one token uses the expert, so the extra FLOPs are free and there is no data-dependent shape.
-* ``routed`` (prefill-sized steps): tokens are sorted by expert and each expert runs on its own rows.
+* ``routed`` (default): the (token, slot) pairs of the local experts are grouped by expert on the device and one
+  grouped GEMM launch per projection walks the per-expert row ranges (``ops/csrc/moe_sm100.cu``): no host
+  synchronisation, fixed buffer shapes, CUDA-graph capturable, only routed rows are computed.
+* ``dense`` (``TGI_B200_MOE_EVAL=dense``, steps of up to ``TGI_B200_MOE_DENSE_TOKENS`` tokens): every local expert
+  runs on all ``T`` tokens and its output is scaled by the token's routing weight; kept as the comparison point.
 """
 from __future__ import annotations
 
@@ -47,28 +47,11 @@ class ExpertParallel:
             if dense_max_tokens is None else dense_max_tokens
 
     def __call__(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
-        T = x.shape[0]
-        if T <= self.dense_max_tokens or torch.cuda.is_current_stream_capturing():
+        mode = os.environ.get("TGI_B200_MOE_EVAL", "routed")
+        if mode == "dense" and x.shape[0] <= self.dense_max_tokens:
             return dense_experts(x, self.w_gate_up, self.w_down, topk_weights, topk_ids, self.first, self.act)
-        # routed: keep the (token, slot) pairs that point at a local expert, grouped by expert
-        local = (topk_ids >= self.first) & (topk_ids < self.first + self.n_local)
-        tok, slot = local.nonzero(as_tuple=True)
-        e = topk_ids[tok, slot] - self.first
-        order = torch.argsort(e, stable=True)
-        tok, slot = tok[order], slot[order]
-        w = topk_weights[tok, slot].float()
-        counts = torch.bincount(e, minlength=self.n_local).tolist()
-        out = torch.zeros(T, x.shape[1], dtype=torch.float32, device=x.device)
-        start = 0
-        for j, c in enumerate(counts):
-            if c == 0:
-                continue
-            rows = tok[start:start + c]
-            h = ops.linear(x.index_select(0, rows), self.w_gate_up[j])
-            y = ops.linear(ops.act_and_mul(h, self.act), self.w_down[j])
-            out.index_add_(0, rows, y.float() * w[start:start + c].unsqueeze(1))
-            start += c
-        return out.to(x.dtype)
+        # routed: the (token, slot) pairs that point at a local expert are grouped by expert on the device
+        return ops.moe_experts(x, self.w_gate_up, self.w_down, topk_weights, topk_ids, self.act, self.first)
 
 
 def dense_experts(x, w_gate_up, w_down, topk_weights, topk_ids, first: int, act: str) -> torch.Tensor:
