@@ -29,7 +29,10 @@ namespace {
 constexpr int kMaxRanks = 8;
 constexpr int kMaxBlocks = 256;           // flag slots per phase
 constexpr float kFp8Max = 448.f;
-constexpr unsigned long long kPeerWaitNs = 2000000000ull;   // 2 s
+// Default limit of a wait on a flag that another rank writes.  The limit travels as a kernel argument so
+// that a test can make it short (tgi_peer_set_wait_ns) and watch a wait run out: a flag that nothing sets
+// ends the kernel with status kErrPeerWait after that time, the context stays usable.
+unsigned long long g_peer_wait_ns = 2000000000ull;   // 2 s
 
 struct PeerArgs {
   unsigned char* heap[kMaxRanks];   // heap base of every rank as mapped in this process
@@ -46,7 +49,7 @@ struct PeerArgs {
   const __nv_bfloat16* weight;      // norm weight [H]
   float eps, w_offset;
   int* status;
-  unsigned long long* trace;     // optional: 8 timestamps (ns) of block 0 for the phase timeline, or nullptr
+  unsigned long long wait_ns;       // limit of every wait on a peer's flag
   int pushed;                       // 1: the partial rows were pushed into this rank's slots by the producers
   long long off_push_flags;         // uint32 [8] in every heap: call counter of each source's last finished push
   const unsigned int* push_epoch;   // local: call counter of this rank's own producer (all ranks agree on it)
@@ -127,7 +130,7 @@ struct BlockSync {
       const unsigned long long t0 = global_ns();
       unsigned int polls = 0;
       while (static_cast<int>(ld_relaxed_sys(f) - e) < 0) {
-        if ((++polls & 63u) == 0 && global_ns() - t0 > kPeerWaitNs) {
+        if ((++polls & 63u) == 0 && global_ns() - t0 > a.wait_ns) {
           atomicExch(a.status, sm100::kErrPeerWait);
           *failed = 1;
           break;
@@ -229,8 +232,6 @@ peer_reduce_kernel(const PeerArgs a) {
   const int my_rows = max(0, min(a.T, row0 + rows_per) - row0);
   const int nvec = a.H / 8;
 
-  const bool tracing = a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
-  if (tracing) a.trace[0] = global_ns();
   bool ok;
   if (a.pushed) {
     // the producers flagged their pushes themselves: wait until every source's counter reached this call
@@ -240,7 +241,7 @@ peer_reduce_kernel(const PeerArgs a) {
       const unsigned long long t0 = global_ns();
       unsigned int polls = 0;
       while (static_cast<int>(ld_relaxed_sys(f) - want) < 0) {
-        if ((++polls & 63u) == 0 && global_ns() - t0 > kPeerWaitNs) {
+        if ((++polls & 63u) == 0 && global_ns() - t0 > a.wait_ns) {
           atomicExch(a.status, sm100::kErrPeerWait);
           failed = 1;
           break;
@@ -250,13 +251,10 @@ peer_reduce_kernel(const PeerArgs a) {
     }
     __syncthreads();
     ok = failed == 0;
-    if (tracing) a.trace[1] = global_ns();
   } else {
     sync.signal(0, false);                     // my producer kernel has finished: its partial rows may be read
-    if (tracing) a.trace[1] = global_ns();
     ok = sync.wait(0);
   }
-  if (tracing) a.trace[2] = global_ns();
   if (ok) {
     for (int lr = blockIdx.x; lr < my_rows; lr += gridDim.x) {
       const int row = row0 + lr;
@@ -333,11 +331,8 @@ peer_reduce_kernel(const PeerArgs a) {
         }
       }
     }
-    if (tracing) a.trace[3] = global_ns();
     sync.signal(1, true);                     // my rows are in everybody's gather buffer
-    if (tracing) a.trace[4] = global_ns();
     ok = sync.wait(1);                  // and everybody's rows are in mine
-    if (tracing) a.trace[5] = global_ns();
   }
   sync.finish();
 }
@@ -499,13 +494,19 @@ int tgi_peer_import(const unsigned char* handle64, void** ptr) {
 }
 int tgi_peer_unmap(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }
 int tgi_peer_max_blocks() { return kMaxBlocks; }
+// Limit (nanoseconds) of the waits on peer flags for kernels launched from now on; returns the previous one.
+unsigned long long tgi_peer_set_wait_ns(unsigned long long ns) {
+  const unsigned long long old = g_peer_wait_ns;
+  if (ns > 0) g_peer_wait_ns = ns;
+  return old;
+}
 
 // ---- the collective --------------------------------------------------------------------------
 // mode 0: all-reduce; 1: + residual + RMSNorm -> bf16; 2: + residual + RMSNorm + e4m3 quantisation.
 int tgi_peer_reduce(void* const* heaps, int rank, int world, int T, int H, long long off_partial, long long off_gather,
                     long long off_gscale, int gscale_pitch, long long off_flags, unsigned int* epoch,
                     const void* residual_in, void* residual_out, const void* weight, float eps, float w_offset,
-                    int mode, int blocks, int* status, unsigned long long* trace, int pushed, long long off_push_flags,
+                    int mode, int blocks, int* status, int pushed, long long off_push_flags,
                     const unsigned int* push_epoch, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -10;
@@ -530,7 +531,7 @@ int tgi_peer_reduce(void* const* heaps, int rank, int world, int T, int H, long 
   a.eps = eps;
   a.w_offset = w_offset;
   a.status = status;
-  a.trace = trace;
+  a.wait_ns = g_peer_wait_ns;
   a.pushed = pushed;
   a.off_push_flags = off_push_flags;
   a.push_epoch = push_epoch;
@@ -565,7 +566,7 @@ int tgi_peer_argmax(void* const* heaps, int rank, int world, const void* logits,
   a.weight = nullptr;
   a.eps = a.w_offset = 0.f;
   a.status = status;
-  a.trace = nullptr;
+  a.wait_ns = g_peer_wait_ns;
   a.pushed = 0;
   a.off_push_flags = 0;
   a.push_epoch = nullptr;

@@ -89,16 +89,6 @@ def main():
         "peer_all_reduce": timed(lambda: comm.all_reduce(x), args.iters, group),
         "peer_reduce_norm": timed(lambda: comm.reduce_norm(T, w, 1e-5, 0.0, quant=True), args.iters, group),
     }
-    # phase timeline of one reduce_norm call (block 0 of this rank), after a barrier so ranks start together
-    comm.trace = torch.zeros(8, dtype=torch.int64, device=dev)
-    dist.barrier(group=group)
-    torch.cuda.synchronize()
-    comm.reduce_norm(T, w, 1e-5, 0.0, quant=True)
-    torch.cuda.synchronize()
-    ts = comm.trace.tolist()
-    comm.trace = None
-    names = ["signal0", "wait0", "reduce+push", "signal1", "wait1"]
-    timeline = {n: round((ts[i + 1] - ts[i]) / 1e3, 2) for i, n in enumerate(names)}
     status = comm.check()
     link_bytes = T * H * 2 * (world - 1) / world
     roof = link_bytes / (NVLINK_GBS * 1e9)
@@ -107,7 +97,6 @@ def main():
             print(json.dumps({"op": name, "world": world, "tokens": T, "hidden": H, "us": round(t * 1e6, 2),
                               "nvlink_roofline_us": round(roof * 1e6, 2),
                               "frac_of_roofline": round(roof / t, 3), "kernel_status": status}), flush=True)
-        print(json.dumps({"op": "peer_reduce_norm phases of one eager call, block 0 (us)", **timeline}), flush=True)
     dist.barrier(group=group)
     torch.cuda.synchronize()
     import os

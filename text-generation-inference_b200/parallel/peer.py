@@ -119,7 +119,6 @@ class PeerComm:
         rows_per = (self.max_tokens + world - 1) // world
         self.residual = torch.zeros(rows_per, self.width, dtype=torch.bfloat16, device=device)
         self.status = K.state(device).status
-        self.trace: Optional[torch.Tensor] = None   # set to an int64[8] tensor to record block 0's phase timestamps
         # every rank must have mapped every heap before anyone's kernel writes into a peer
         pdist.barrier(group)
 
@@ -148,7 +147,7 @@ class PeerComm:
             ctypes.c_longlong(self.off_partial), ctypes.c_longlong(self.off_gather), ctypes.c_longlong(self.off_gscale),
             ctypes.c_int(self.pitch), ctypes.c_longlong(self.off_flags), K._ptr(self.epoch),
             K._ptr(residual_in), K._ptr(residual_out), K._ptr(weight), ctypes.c_float(eps), ctypes.c_float(w_offset),
-            ctypes.c_int(mode), ctypes.c_int(self._blocks(T)), K._ptr(self.status), K._ptr(self.trace),
+            ctypes.c_int(mode), ctypes.c_int(self._blocks(T)), K._ptr(self.status),
             ctypes.c_int(1 if pushed else 0), ctypes.c_longlong(self.off_push_flags),
             ctypes.c_void_p(self.push_state.data_ptr() + 4), K._stream())
         K._check(rc, "peer_reduce")
