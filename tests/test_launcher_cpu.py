@@ -21,7 +21,7 @@ def _free_port():
     return p
 
 
-def _start(tmp_path):
+def _start(tmp_path, extra=()):
     from tgi_b200.router.build import HERE, build
     from tgi_b200.utils.synthetic import llama_config, write_llama_checkpoint
 
@@ -33,7 +33,7 @@ def _start(tmp_path):
     cmd = [str(HERE / "tgi-b200-launcher"), "--model-id", str(d), "--num-shard", "1", "--port", str(port),
            "--hostname", "127.0.0.1", "--shard-uds-path", str(tmp_path / "shard"), "--dtype", "float32",
            "--max-input-tokens", "64", "--max-total-tokens", "128", "--max-batch-prefill-tokens", "128",
-           "--master-port", str(_free_port())]
+           "--master-port", str(_free_port()), *extra]
     log = open(tmp_path / "launcher.log", "w")
     proc = subprocess.Popen(cmd, env=env, cwd=ROOT, stdout=log, stderr=subprocess.STDOUT, start_new_session=True)
     deadline = time.time() + 180
@@ -66,6 +66,43 @@ def test_launcher_serves_and_stops_cleanly(tmp_path):
             assert r.status == 200 and "generated_text" in json.loads(r.read().decode())
         os.kill(proc.pid, signal.SIGTERM)
         assert proc.wait(timeout=60) == 0
+    finally:
+        if proc.poll() is None:
+            os.killpg(proc.pid, signal.SIGKILL)
+        log.close()
+
+
+def test_launcher_downloads_first_reemits_shard_logs_and_serves_metrics_on_its_own_port(tmp_path):
+    prom = _free_port()
+    proc, port, log = _start(tmp_path, extra=("--json-output", "--prometheus-port", str(prom),
+                                              "--cors-allow-origin", "https://a.example", "--usage-stats", "off"))
+    try:
+        with urllib.request.urlopen(f"http://127.0.0.1:{prom}/metrics", timeout=10) as r:
+            assert r.status == 200 and "tgi_queue_size" in r.read().decode()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/info", headers={"origin": "https://a.example"})
+        with urllib.request.urlopen(req, timeout=10) as r:
+            assert r.headers.get("access-control-allow-origin") == "https://a.example"
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/info", headers={"origin": "https://b.example"})
+        with urllib.request.urlopen(req, timeout=10) as r:
+            assert r.headers.get("access-control-allow-origin") is None
+        os.kill(proc.pid, signal.SIGTERM)
+        assert proc.wait(timeout=60) == 0
+        records = []
+        for line in open(tmp_path / "launcher.log").read().splitlines():
+            if line.startswith("{"):
+                records.append(json.loads(line))
+        targets = [r["target"] for r in records]
+        # the weight check ran (and finished) before the shard was started
+        msgs = [r["message"] for r in records if r["target"] == "launcher"]
+        assert any("download" in m.lower() for m in msgs)
+        first_shard = next(i for i, r in enumerate(records) if r["target"] == "launcher" and "Starting shard-0" in r["message"])
+        done = next(i for i, r in enumerate(records) if r["target"] == "launcher" and "Successfully downloaded" in r["message"])
+        assert done < first_shard
+        # the shard's own JSON records come back under its name, at their level
+        shard_records = [r for r in records if r["target"] == "shard-0"]
+        assert shard_records and all(r["level"] in ("DEBUG", "INFO", "WARNING", "ERROR", "CRITICAL") for r in shard_records)
+        assert any("Server started" in r["message"] for r in shard_records)
+        assert "router" in targets
     finally:
         if proc.poll() is None:
             os.killpg(proc.pid, signal.SIGKILL)

@@ -35,6 +35,10 @@ from .types import Batch, GeneratedText, Generation, Tokens
 
 BLOCK_SIZE = int(os.environ.get("TGI_B200_BLOCK_SIZE", "16"))
 WIGGLE_ROOM = float(os.environ.get("TGI_WIGGLE_ROOM", "0.90"))
+# set by the launcher (reference: models/globals.py:8-20): whether the router may re-use cached prompt prefixes
+# and split long prompts into chunks
+PREFIX_CACHING = os.environ.get("PREFIX_CACHING", "1").lower() in ("1", "true")
+PREFILL_CHUNKING = os.environ.get("PREFILL_CHUNKING", "1").lower() in ("1", "true")
 
 
 @dataclass
@@ -262,7 +266,7 @@ class FlashCausalLM(Model):
         windows = [w for w in model.dims.windows if w > 0]
         super().__init__(model, tokenizer, requires_padding=False, dtype=dtype, device=device, rank=rank,
                          world_size=world_size, sliding_window=(windows[0] if windows else None),
-                         speculate=speculate, support_chunking=True, use_prefix_caching=True,
+                         speculate=speculate, support_chunking=PREFILL_CHUNKING, use_prefix_caching=PREFIX_CACHING,
                          block_size=BLOCK_SIZE)
         self.dims = model.dims
         self.kv_cache_dtype = kv_cache_dtype or dtype

@@ -64,6 +64,7 @@ struct RouterConfig {
   // how many placeholder tokens an image costs
   json::Value model_config;
   size_t max_image_bytes = 20u << 20;
+  std::vector<std::string> cors_allow_origin;   // empty: any origin
 };
 
 struct GenerateParams {   // the `parameters` object of /generate, already range-checked

@@ -315,7 +315,14 @@ void Router::h_vertex(const http::Request& req, http::Response& resp) {
 void Router::install(http::Server& s) {
   using namespace std::placeholders;
   s.set_middleware([this](const http::Request& req, http::Response& resp) {
-    resp.set_header("access-control-allow-origin", "*");
+    // CORS: any origin by default, else only the configured ones (reference: --cors-allow-origin)
+    if (cfg_.cors_allow_origin.empty()) {
+      resp.set_header("access-control-allow-origin", "*");
+    } else {
+      const std::string origin = req.header("origin");
+      for (const auto& o : cfg_.cors_allow_origin)
+        if (o == origin || o == "*") resp.set_header("access-control-allow-origin", o == "*" ? "*" : origin);
+    }
     if (cfg_.api_key.empty()) return true;
     const bool open = req.path == "/health" || req.path == "/ping" || req.path == "/" || req.path == "/metrics";
     if (open && req.method == "GET") return true;

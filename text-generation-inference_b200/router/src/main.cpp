@@ -233,6 +233,12 @@ int main(int argc, char** argv) {
     rc.max_client_batch_size = static_cast<uint32_t>(args.num("max-client-batch-size", 4));
     rc.disable_grammar_support = args.flag("disable-grammar-support");
     rc.api_key = args.get("api-key");
+    {
+      std::stringstream origins(args.get("cors-allow-origin"));
+      std::string o;
+      while (std::getline(origins, o, ','))
+        if (!o.empty()) rc.cors_allow_origin.push_back(o);
+    }
     rc.model_id = args.get("model-id", tokenizer);
     rc.dtype = info.dtype;
     rc.device_type = info.device_type;
@@ -262,7 +268,24 @@ int main(int argc, char** argv) {
     std::signal(SIGPIPE, SIG_IGN);
     const int port = server.start();
     std::cerr << "[router] Connected; listening on port " << port << std::endl;
+    // optional second listener that only serves the Prometheus text format (reference: --prometheus-port)
+    std::unique_ptr<http::Server> prom;
+    std::thread prom_thread;
+    if (args.num("prometheus-port", 0) > 0) {
+      prom = std::make_unique<http::Server>(args.get("hostname", "0.0.0.0"), static_cast<int>(args.num("prometheus-port", 0)),
+                                            static_cast<size_t>(1 << 16));
+      prom->route("GET", "/metrics", [&metrics](const http::Request&, http::Response& r) {
+        r.send(200, "text/plain; version=0.0.4", metrics.render());
+      });
+      const int pport = prom->start();
+      std::cerr << "[router] Prometheus metrics on port " << pport << std::endl;
+      prom_thread = std::thread([&prom] { prom->serve_forever(); });
+    }
     server.serve_forever();
+    if (prom) {
+      prom->stop();
+      if (prom_thread.joinable()) prom_thread.join();
+    }
     backend->stop();
     trace::shutdown();   // flushes the spans still queued
     std::cerr << "[router] shut down" << std::endl;

@@ -15,8 +15,11 @@ from pathlib import Path
 
 class _JsonFormatter(logging.Formatter):
     def format(self, record):
+        message = record.getMessage()
+        if record.exc_info:      # keep the traceback with the record: the launcher re-emits one record per line
+            message += "\n" + self.formatException(record.exc_info)
         return json.dumps({"timestamp": self.formatTime(record), "level": record.levelname,
-                           "target": record.name, "message": record.getMessage()})
+                           "target": record.name, "message": message})
 
 
 def _setup_logging(level: str, json_output: bool):
