@@ -122,6 +122,46 @@ def main():
         assert torch.equal(ids, want_ids), f"argmax ids differ B={B}"
         assert (lps - want_lp).abs().max().item() < 2e-3, f"argmax logprobs differ {(lps - want_lp).abs().max()}"
 
+    # ---- vocabulary-parallel sampling: same tokens as the single-GPU fused sampler on the full logits ------
+    from tgi_b200.ops import cuda as K
+
+    for B, Vl, use_pen in ((1, 512, False), (33, 2003, False), (64, 1024, True), (256, 1024, False)):
+        salt += 1
+        g = torch.Generator(device="cpu").manual_seed(9000 + salt)
+        full_bf = (torch.randn(B, Vl * world, generator=g) * 3).to(torch.bfloat16)
+        temperature = torch.rand(B, generator=g) * 1.5 + 0.3
+        top_k = torch.randint(0, 60, (B,), generator=g, dtype=torch.int32)
+        top_k[::3] = 0
+        top_p = torch.rand(B, generator=g) * 0.7 + 0.3
+        top_p[1::4] = 1.0
+        do_sample = (torch.rand(B, generator=g) < 0.8).to(torch.uint8)
+        seeds = torch.randint(0, 2 ** 40, (B,), generator=g, dtype=torch.int64)
+        steps = torch.randint(0, 50, (B,), generator=g, dtype=torch.int32)
+        hist = torch.randint(0, Vl * world, (B, 40), generator=g, dtype=torch.int64)
+        rep = torch.rand(B, generator=g) * 0.5 + 1.0
+        freq = torch.rand(B, generator=g) * 0.4
+        full_dev = full_bf.to(device)
+        local = full_dev[:, rank * Vl:(rank + 1) * Vl].contiguous()
+        if use_pen:
+            ref_scores = K.penalties(full_dev, hist, rep.to(device), freq.to(device), 0, 0.5)
+            want_ids, want_lp = K.fused_sample(ref_scores, temperature, top_k, top_p, do_sample, seeds, steps)
+            loc_scores = K.penalties(local, hist, rep.to(device), freq.to(device), rank * Vl, 0.5)
+            assert torch.equal(loc_scores, ref_scores[:, rank * Vl:(rank + 1) * Vl]), "penalties on a slice differ"
+            ids, lps = comm.sample(loc_scores, rank * Vl, Vl * world, 1.0, temperature, top_k, top_p, do_sample, seeds, steps)
+        else:
+            want_ids, want_lp = K.fused_sample(full_dev.float() * 0.5, temperature, top_k, top_p, do_sample, seeds, steps)
+            ids, lps = comm.sample(local, rank * Vl, Vl * world, 0.5, temperature, top_k, top_p, do_sample, seeds, steps)
+        torch.cuda.synchronize()
+        assert comm.check() == 0
+        same = (ids == want_ids).float().mean().item()
+        assert same >= 0.99, f"sharded sampling differs from the single-GPU sampler: B={B} agree={same}"
+        ok = ids == want_ids
+        assert (lps[ok] - want_lp[ok]).abs().max().item() < 2e-3
+        # every rank must hold the same ids
+        gathered = [torch.empty_like(ids) for _ in range(world)]
+        torch.distributed.all_gather(gathered, ids, group=group)
+        assert all(torch.equal(gathered[0], t) for t in gathered), "ranks disagree on the sampled ids"
+
     # ---- CUDA graph replay: the call counters live in device memory ----------------------------
     T = 32
     salt += 1

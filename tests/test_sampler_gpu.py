@@ -105,3 +105,59 @@ def test_chooser_uses_the_kernel_and_matches_filters():
     ref = torch.log_softmax(warped, -1).gather(1, ids.view(-1, 1)).view(-1)
     assert (lps - ref).abs().max().item() < 8e-2      # equal bf16 scores at the top-p boundary: the kernel keeps the whole group
     assert chooser.steps == [0, 1, 1, 1, 1, 1]
+
+
+def test_penalties_kernel_matches_the_torch_warpers():
+    from tgi_b200.ops import cuda as K
+    from tgi_b200.utils.tokens import apply_frequency_penalty, apply_repetition_penalty
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    B, V, L = 9, 3000, 57
+    logits = (torch.randn(B, V, device=dev) * 4).to(torch.bfloat16)
+    hist = torch.randint(0, V, (B, L), device=dev)
+    hist[:, -7:] = 0                                  # padding zeros count as token 0, as in the reference
+    rep = torch.rand(B, device=dev) * 0.6 + 1.0
+    rep[0] = 1.0
+    freq = torch.rand(B, device=dev) * 0.5
+    freq[1] = 0.0
+    got = K.penalties(logits, hist, rep, freq)
+    want = apply_frequency_penalty(apply_repetition_penalty(logits.float(), hist, rep), hist, freq)
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+    # a vocabulary slice sees only its own ids
+    lo, hi = 1000, 2200
+    part = K.penalties(logits[:, lo:hi].contiguous(), hist, rep, freq, vocab_start=lo)
+    torch.testing.assert_close(part, want[:, lo:hi], atol=1e-5, rtol=1e-5)
+    assert torch.equal(K.penalties(logits, hist, None, None), logits.float())
+
+
+def test_sharded_sampler_with_one_rank_equals_the_fused_sampler():
+    """The vocabulary-parallel sampler run with a single rank (it exchanges its words with itself) must pick
+    the same tokens and log-probabilities as the single-GPU kernel for the same seeds."""
+    from tgi_b200.ops import cuda as K
+    from tgi_b200.parallel.dist import FakeGroup
+    from tgi_b200.parallel.peer import PeerComm
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    comm = PeerComm(FakeGroup(0, 1), 0, 1, dev, 64, 256)
+    g = torch.Generator(device="cpu").manual_seed(17)
+    for B, V in ((1, 300), (40, 5000), (300, 2048)):
+        logits = (torch.randn(B, V, generator=g) * 3).to(torch.bfloat16).to(dev)
+        temperature = torch.rand(B, generator=g) * 1.5 + 0.3
+        top_k = torch.randint(0, 50, (B,), generator=g, dtype=torch.int32)
+        top_k[::2] = 0
+        top_p = torch.rand(B, generator=g) * 0.7 + 0.3
+        top_p[::5] = 1.0
+        do_sample = (torch.rand(B, generator=g) < 0.7).to(torch.uint8)
+        seeds = torch.randint(0, 2 ** 40, (B,), generator=g, dtype=torch.int64)
+        steps = torch.randint(0, 9, (B,), generator=g, dtype=torch.int32)
+        want_ids, want_lp = K.fused_sample(logits, temperature, top_k, top_p, do_sample, seeds, steps)
+        for _ in range(2):       # twice: the exchange counters keep counting across launches
+            ids, lps = comm.sample(logits, 0, V, 1.0, temperature, top_k, top_p, do_sample, seeds, steps)
+            torch.cuda.synchronize()
+            assert comm.check() == 0
+            assert (ids == want_ids).float().mean().item() >= 0.99
+            ok = ids == want_ids
+            assert (lps[ok] - want_lp[ok]).abs().max().item() < 2e-3
+    comm.close()

@@ -297,6 +297,41 @@ class FlashCausalLM(Model):
         item = torch.empty((), dtype=self.kv_cache_dtype).element_size()
         return 2 * d.num_layers * BLOCK_SIZE * d.num_kv_heads * (d.attn_head_dim or d.head_dim) * item
 
+    def _sample_on_shards(self, chooser, seqs, active, sample_rows, batch):
+        """Vocabulary-parallel sampling after a decode graph that left only this rank's logit slice: returns
+        ``(ids, logprobs)`` on the device, or ``None`` when a stage needs the whole distribution on one rank
+        (top-n tokens, typical-p, watermark, grammar, speculation) and the logits have to be gathered."""
+        b, n = self.graphs.last
+        comm = getattr(self.model, "comm", None)
+        if (comm is None or b.local_logits is None or batch.speculate != 0 or chooser.any_typical or chooser.watermarks
+                or chooser.grammar is not None or any(seqs[i].top_n > 0 for i in active)
+                or len(active) != n or sample_rows != list(range(n))):
+            return None
+        from ..ops import cuda as K
+
+        d = self.model.dims
+        local = b.local_logits[:n]
+        v0 = self.model.head.vocab_start
+        scale = float(d.logit_scale)
+        if chooser.any_rep or chooser.any_freq:
+            L = max(len(seqs[i].ids) for i in active)
+            hist = np.zeros((len(active), L), dtype=np.int64)
+            for r, i in enumerate(active):
+                hist[r, :len(seqs[i].ids)] = seqs[i].ids
+            local = K.penalties(local, torch.from_numpy(hist), chooser.repetition_penalty if chooser.any_rep else None,
+                                chooser.frequency_penalty if chooser.any_freq else None, v0, scale)
+            scale = 1.0
+        seeds = steps = do_sample = None
+        if chooser.any_sample:
+            do_sample = chooser.do_sample.to(torch.uint8)
+            seeds = torch.tensor([int(s or 0) & 0x7FFFFFFFFFFFFFFF for s in chooser.seeds], dtype=torch.int64)
+            steps = torch.tensor(chooser.steps, dtype=torch.int32)
+            chooser.steps = [st + (1 if ds else 0) for st, ds in zip(chooser.steps, chooser.do_sample_list)]
+        return comm.sample(local, v0, d.vocab_size, scale,
+                           chooser.temperature if chooser.any_temperature else None,
+                           chooser.top_k if chooser.any_top_k else None, chooser.top_p if chooser.any_top_p else None,
+                           do_sample, seeds, steps)
+
     def init_kv_cache(self, num_blocks: int):
         d = self.dims
         self.kv_cache = []
@@ -513,6 +548,9 @@ class FlashCausalLM(Model):
                          and not any(seqs[i].top_n > 0 for i in active))
                 if plain:
                     greedy_dev = self.graphs.greedy()
+                if greedy_dev is None:
+                    # samplers made of temperature / top-k / top-p / penalties run on the vocabulary shards
+                    greedy_dev = self._sample_on_shards(chooser, seqs, active, sample_rows, batch)
                 if greedy_dev is None:
                     logits = self.graphs.gather_last_logits()
             # sequences in the same step may carry different numbers of speculative tokens only when

@@ -146,6 +146,11 @@ def fused_sample(scores, temperature=None, top_k=None, top_p=None, do_sample=Non
     return native().fused_sample(scores, temperature, top_k, top_p, do_sample, seeds, steps)
 
 
+def penalties(scores, history, repetition_penalty=None, frequency_penalty=None):
+    """fp32 copy of CUDA ``scores[B, V]`` with repetition / frequency penalties of ``history[B, L]`` applied."""
+    return native().penalties(scores, history, repetition_penalty, frequency_penalty)
+
+
 def moe_topk_softmax(router_logits, top_k, renormalize=True):
     if use_native(router_logits) and router_logits.shape[-1] <= 256 and top_k <= 8:
         return native().moe_topk_softmax(router_logits, top_k, renormalize)

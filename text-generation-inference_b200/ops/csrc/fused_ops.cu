@@ -18,6 +18,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "sampling.cuh"
 #include "launch.cuh"
 
 namespace {
@@ -487,31 +488,8 @@ argmax_logprob_kernel(const T* __restrict__ logits, long long* __restrict__ ids,
 //   keyed by the request's seed with counter (j, step): reproducible for a given seed.
 //   logprob = x_c - logsumexp over the kept set.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t order_bits(float x) {
-  const uint32_t u = __float_as_uint(x);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-
-__device__ __forceinline__ uint4 philox4x32(uint32_t c0, uint32_t c1, uint32_t k0, uint32_t k1) {
-  uint32_t c[4] = {c0, c1, 0u, 0u};
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
-    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
-    const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
-    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
-  }
-  return make_uint4(c[0], c[1], c[2], c[3]);
-}
-
-__device__ __forceinline__ float gumbel_noise(uint32_t j, uint32_t step, uint64_t seed) {
-  const uint4 r = philox4x32(j >> 2, step, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
-  const uint32_t w = (j & 3) == 0 ? r.x : (j & 3) == 1 ? r.y : (j & 3) == 2 ? r.z : r.w;
-  const float u = (static_cast<float>(w >> 8) + 0.5f) * (1.0f / 16777216.0f);   // (0, 1)
-  return -__logf(-__logf(u));
-}
+using tgi_sampling::gumbel_noise;
+using tgi_sampling::order_bits;
 
 // smallest order_bits threshold t such that  sum_{x : bits(x) > t} w(x) < limit   (w = 1 or exp(x - m))
 template <typename T, bool MASS>
@@ -624,9 +602,62 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Repetition and frequency penalties on fp32 scores, in place, one CTA per row, from the row's token history
+// (reference: utils/logits_process.py:151-218).  `scores` may be a vocabulary slice [vocab_start,
+// vocab_start + V): ids outside the slice are skipped.  Repetition: every token of the history gets
+// score * p when negative, else score / p, once however often it occurs (the value is computed from the
+// untouched `logits`, so duplicates write the same number).  Frequency: score -= p * occurrences.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+penalties_kernel(const T* __restrict__ logits, long long in_stride, float* __restrict__ scores, long long out_stride,
+                 const long long* __restrict__ history, int L, const float* __restrict__ rep, const float* __restrict__ freq,
+                 int vocab_start, int V, float logit_scale) {
+  tgi::pdl_wait();
+  const int b = blockIdx.x;
+  const T* in = logits + static_cast<size_t>(b) * in_stride;
+  float* out = scores + static_cast<size_t>(b) * out_stride;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) out[i] = static_cast<float>(in[i]) * logit_scale;
+  __syncthreads();
+  const long long* h = history + static_cast<size_t>(b) * L;
+  const float rp = rep != nullptr ? rep[b] : 1.f;
+  if (rp != 1.f) {
+    for (int l = threadIdx.x; l < L; l += blockDim.x) {
+      const long long t = h[l] - vocab_start;
+      if (t < 0 || t >= V) continue;
+      const float x = static_cast<float>(in[t]) * logit_scale;
+      out[t] = x < 0.f ? x * rp : x / rp;
+    }
+    __syncthreads();
+  }
+  const float fp = freq != nullptr ? freq[b] : 0.f;
+  if (fp != 0.f) {
+    for (int l = threadIdx.x; l < L; l += blockDim.x) {
+      const long long t = h[l] - vocab_start;
+      if (t < 0 || t >= V) continue;
+      atomicAdd(&out[t], -fp);
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+// scores[B, V] (fp32) = penalised(logits[B, V] * logit_scale); history int64 [B, L]; rep / freq fp32 [B] or null
+int tgi_penalties(const void* logits, int is_fp32, long long in_stride, float* scores, long long out_stride,
+                  const long long* history, int L, const float* rep, const float* freq, int vocab_start, int B, int V,
+                  float logit_scale, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (is_fp32)
+    tgi::launch(penalties_kernel<float>, dim3(B), dim3(256), 0, stream, static_cast<const float*>(logits), in_stride, scores,
+                out_stride, history, L, rep, freq, vocab_start, V, logit_scale);
+  else
+    tgi::launch(penalties_kernel<__nv_bfloat16>, dim3(B), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(logits),
+                in_stride, scores, out_stride, history, L, rep, freq, vocab_start, V, logit_scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 int tgi_norm(const void* x, const void* residual, const void* weight, const void* bias, void* out, void* res_out,
              void* q_out, float* scale_t, int scale_pitch, int T, int H, float eps, float w_offset, int layer,

@@ -22,6 +22,7 @@
 #include <stdint.h>
 
 #include "launch.cuh"
+#include "sampling.cuh"
 #include "sm100.cuh"
 
 namespace {
@@ -456,6 +457,277 @@ peer_argmax_kernel(const PeerArgs a, const __nv_bfloat16* __restrict__ logits, l
   sync.finish();
 }
 
+// ------------------------------------------------------------------------------------------------
+// Vocabulary-parallel sampling.  The reference gathers the [B, V] logits of the sharded lm_head on every rank
+// and runs its warper chain on the full matrix (layers/tensor_parallel.py:75-104, utils/tokens.py:233-503).
+// Here every rank keeps its [B, V / world] slice and the ranks agree on the result through a few scalars per
+// row: the fused single-GPU sampler (fused_ops.cu `sample_kernel`) only ever needs block-wide reductions of the
+// row (max, counts and probability mass above a threshold, the arg-max of the Gumbel-perturbed scores), so each
+// of them becomes a block reduction over the slice followed by an exchange of one 8-byte word per rank.
+//
+//   x_j = score_j / T;   top-k / top-p thresholds by a 4-way search on the order-preserving integer image of
+//   the float (16 exchange rounds for 32 bits);   sample = argmax_j x_j + g_j with g_j keyed by the GLOBAL
+//   index j, so the draw equals the single-GPU draw for the same seed;   logprob = x_c - logsumexp(kept set).
+//
+// Exchange: a word is (value bits, sequence number) written with one 64-bit store into the slot
+// [block][round parity][word][source rank] of every rank's heap; the reader polls its own slot until the
+// sequence number is the expected one.  No separate flag or fence is needed because value and sequence number
+// travel in the same 8 aligned bytes.  A rank can run at most one round ahead of another (it needs everybody's
+// word of round n before it writes round n + 1), so two parities suffice.  The sequence counter of every block
+// lives in device memory and keeps counting across launches and CUDA-graph replays.  Waits are bounded.
+// ------------------------------------------------------------------------------------------------
+constexpr int kXWords = 4;   // words per exchange round
+
+struct SampleArgs {
+  const float* temperature;          // [B] or null
+  const int* top_k;                  // [B] or null
+  const float* top_p;                // [B] or null
+  const unsigned char* do_sample;    // [B] or null
+  const long long* seeds;            // [B] or null
+  const int* steps;                  // [B] or null
+  long long off_xchg;                // heap offset of uint64 [kMaxBlocks][2][kXWords][kMaxRanks]
+  unsigned int* xseq;                // local uint32 [kMaxBlocks]: exchange rounds made so far by each block
+  int vocab_total;
+};
+
+struct Exchange {
+  const PeerArgs& a;
+  long long off;
+  unsigned int seq;          // rounds done so far by this block (same value on every rank)
+  int* failed;
+  float (*recv)[kMaxRanks];  // shared memory [kXWords][kMaxRanks]
+  __device__ unsigned long long* slot(int owner, unsigned int parity, int word, int src) const {
+    return reinterpret_cast<unsigned long long*>(a.heap[owner] + off) +
+           ((static_cast<size_t>(blockIdx.x) * 2 + parity) * kXWords + word) * kMaxRanks + src;
+  }
+  // Every thread calls with the same (block-uniform) values; afterwards recv[w][r] holds rank r's word w.
+  // Returns false for the whole block when a peer's word did not arrive in time.
+  template <int NW>
+  __device__ bool all_gather(const float (&v)[NW]) {
+    const unsigned int want = seq + 1u;
+    const unsigned int parity = want & 1u;
+    const int t = threadIdx.x;
+    if (t < a.world * NW) {
+      const int peer = t / NW, w = t - peer * NW;
+      const unsigned long long word = (static_cast<unsigned long long>(want) << 32) | __float_as_uint(v[w]);
+      asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot(peer, parity, w, a.rank)), "l"(word) : "memory");
+    }
+    if (t < a.world * NW) {
+      const int src = t / NW, w = t - src * NW;
+      const unsigned long long* p = slot(a.rank, parity, w, src);
+      const unsigned long long t0 = global_ns();
+      unsigned int polls = 0;
+      unsigned long long word;
+      while (true) {
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(p) : "memory");
+        if (static_cast<unsigned int>(word >> 32) == want) break;
+        if ((++polls & 63u) == 0 && global_ns() - t0 > a.wait_ns) {
+          atomicExch(a.status, sm100::kErrPeerWait);
+          *failed = 1;
+          break;
+        }
+      }
+      recv[w][src] = __uint_as_float(static_cast<unsigned int>(word));
+    }
+    __syncthreads();
+    seq = want;
+    return *failed == 0;
+  }
+};
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float m = red[0];
+  for (int w = 1; w < (blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+  __syncthreads();
+  return m;
+}
+
+// three block sums at once (the quartile points of one search round)
+__device__ __forceinline__ void block_sum3(float (&v)[3], float (*red3)[32]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) v[i] = warp_sum(v[i]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < 3; ++i) red3[i][warp] = v[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    float t = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) t += red3[i][w];   // fixed order: same result in every thread
+    v[i] = t;
+  }
+  __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+peer_sample_kernel(const PeerArgs a, const SampleArgs sa, const T* __restrict__ scores, long long row_stride,
+                   int vocab_start, float logit_scale, long long* __restrict__ ids, float* __restrict__ logprob) {
+  using tgi_sampling::gumbel_noise;
+  using tgi_sampling::order_bits;
+  __shared__ float red[32];
+  __shared__ float red3[3][32];
+  __shared__ float recv[kXWords][kMaxRanks];
+  __shared__ float s_key[32], s_x[32];
+  __shared__ int s_idx[32];
+  __shared__ int failed;
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  Exchange xc{a, sa.off_xchg, sa.xseq[blockIdx.x], &failed, recv};
+  const int B = a.T, Vl = a.H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  bool ok = true;
+
+  for (int row = blockIdx.x; row < B && ok; row += gridDim.x) {
+    const T* x_row = scores + static_cast<size_t>(row) * row_stride;
+    const float temp = sa.temperature != nullptr ? sa.temperature[row] : 1.f;
+    const float inv_t = logit_scale / (temp > 0.f ? temp : 1.f);
+    auto val = [&](int i) { return static_cast<float>(x_row[i]) * inv_t; };
+    auto sum_ranks = [&](int w) {
+      float t = 0.f;
+      for (int r = 0; r < a.world; ++r) t += recv[w][r];
+      return t;
+    };
+    // ---- max over the whole vocabulary ----
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < Vl; i += blockDim.x) m = fmaxf(m, val(i));
+    m = block_max(m, red);
+    {
+      const float v1[1] = {m};
+      ok = xc.all_gather<1>(v1);
+      if (!ok) break;
+      for (int r = 0; r < a.world; ++r) m = fmaxf(m, recv[0][r]);
+      __syncthreads();
+    }
+    // ---- thresholds: smallest t with  sum_{bits(x) > t, bits(x) >= floor} w(x) < limit  (w = 1 or exp(x - m)) ----
+    uint32_t keep_from = 0u;
+    auto search = [&](bool mass, float limit, uint32_t floor_bits) -> uint32_t {
+      uint32_t lo = floor_bits, hi = order_bits(m);
+      while (lo < hi && ok) {
+        const uint32_t w = hi - lo;
+        const uint32_t c[3] = {lo + (w >> 2), lo + (w >> 1), lo + (w >> 1) + (w >> 2)};   // lo <= c0 <= c1 <= c2 < hi
+        float acc[3] = {0.f, 0.f, 0.f};
+        for (int i = threadIdx.x; i < Vl; i += blockDim.x) {
+          const float x = val(i);
+          const uint32_t b = order_bits(x);
+          if (b < floor_bits) continue;
+          const float wgt = mass ? __expf(x - m) : 1.f;
+#pragma unroll
+          for (int q = 0; q < 3; ++q)
+            if (b > c[q]) acc[q] += wgt;
+        }
+        block_sum3(acc, red3);
+        ok = xc.all_gather<3>(acc);
+        if (!ok) break;
+        const float t0 = sum_ranks(0), t1 = sum_ranks(1), t2 = sum_ranks(2);
+        __syncthreads();
+        if (t0 < limit) hi = c[0];
+        else if (t1 < limit) { lo = c[0] + 1; hi = c[1]; }
+        else if (t2 < limit) { lo = c[1] + 1; hi = c[2]; }
+        else lo = c[2] + 1;
+      }
+      return lo;
+    };
+    const int k = sa.top_k != nullptr ? sa.top_k[row] : 0;
+    if (k > 0 && k < sa.vocab_total) keep_from = search(false, static_cast<float>(k), 0u);
+    if (!ok) break;
+    const float p = sa.top_p != nullptr ? sa.top_p[row] : 1.f;
+    if (p < 1.f) {
+      float z[1] = {0.f};
+      for (int i = threadIdx.x; i < Vl; i += blockDim.x) {
+        const float x = val(i);
+        if (order_bits(x) >= keep_from) z[0] += __expf(x - m);
+      }
+      z[0] = block_sum(z[0], red);
+      ok = xc.all_gather<1>(z);
+      if (!ok) break;
+      const float ztot = sum_ranks(0);
+      __syncthreads();
+      const uint32_t t = search(true, p * ztot, keep_from);
+      if (!ok) break;
+      keep_from = max(keep_from, t);
+    }
+    // ---- sample over the kept set ----
+    const bool sample = sa.do_sample != nullptr && sa.do_sample[row] != 0;
+    const uint64_t seed = sa.seeds != nullptr ? static_cast<uint64_t>(sa.seeds[row]) : 0ull;
+    const uint32_t step = sa.steps != nullptr ? static_cast<uint32_t>(sa.steps[row]) : 0u;
+    float z = 0.f, best = -INFINITY, best_x = 0.f;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < Vl; i += blockDim.x) {
+      const float x = val(i);
+      if (order_bits(x) < keep_from || x == -INFINITY) continue;
+      z += __expf(x - m);
+      const int gi = i + vocab_start;
+      const float key = sample ? x + gumbel_noise(static_cast<uint32_t>(gi), step, seed) : x;
+      if (key > best || (key == best && gi < best_i)) {
+        best = key;
+        best_i = gi;
+        best_x = x;
+      }
+    }
+    z = block_sum(z, red);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float k2 = __shfl_xor_sync(0xffffffffu, best, o);
+      const int i2 = __shfl_xor_sync(0xffffffffu, best_i, o);
+      const float x2 = __shfl_xor_sync(0xffffffffu, best_x, o);
+      if (k2 > best || (k2 == best && i2 < best_i)) {
+        best = k2;
+        best_i = i2;
+        best_x = x2;
+      }
+    }
+    __syncthreads();
+    if (lane == 0) {
+      s_key[warp] = best;
+      s_idx[warp] = best_i;
+      s_x[warp] = best_x;
+    }
+    __syncthreads();
+    for (int w = 0; w < (blockDim.x >> 5); ++w)   // every thread folds the warps in the same order
+      if (s_key[w] > best || (s_key[w] == best && s_idx[w] < best_i)) {
+        best = s_key[w];
+        best_i = s_idx[w];
+        best_x = s_x[w];
+      }
+    __syncthreads();
+    {
+      const float v4[4] = {z, best, __int_as_float(best_i), best_x};
+      ok = xc.all_gather<4>(v4);
+      if (!ok) break;
+      if (threadIdx.x == 0) {
+        float zt = 0.f, bk = -INFINITY, bx = 0.f;
+        int bi = 0x7fffffff;
+        for (int r = 0; r < a.world; ++r) {
+          zt += recv[0][r];
+          const float kr = recv[1][r];
+          const int ir = __float_as_int(recv[2][r]);
+          if (kr > bk || (kr == bk && ir < bi)) {
+            bk = kr;
+            bi = ir;
+            bx = recv[3][r];
+          }
+        }
+        ids[row] = bi == 0x7fffffff ? 0 : bi;
+        logprob[row] = bx - m - __logf(zt);
+      }
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) sa.xseq[blockIdx.x] = xc.seq;
+}
+
 template <bool NORM, bool QUANT>
 int launch_reduce(const PeerArgs& a, int blocks, cudaStream_t stream) {
   const int nvec = a.H / 8;
@@ -574,5 +846,57 @@ int tgi_peer_argmax(void* const* heaps, int rank, int world, const void* logits,
               row_stride, vocab_start, logit_scale, off_cand, ids, logprob);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// Vocabulary-parallel sampling (temperature, top-k, top-p, seeded Gumbel-max or arg-max, log-probability) on the
+// rank's slice `scores` [B, Vl] (bf16 logits, or fp32 scores that already carry the penalties); see
+// peer_sample_kernel.  Per-row parameter arrays may be null (stage off).  Every rank gets the same ids.
+int tgi_peer_sample(void* const* heaps, int rank, int world, const void* scores, int is_fp32, int B, int Vl,
+                    long long row_stride, int vocab_start, int vocab_total, float logit_scale, const float* temperature,
+                    const int* top_k, const float* top_p, const unsigned char* do_sample, const long long* seeds,
+                    const int* steps, long long off_xchg, unsigned int* xseq, long long* ids, float* logprob, int blocks,
+                    int* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return -10;
+  if (blocks < 1 || blocks > kMaxBlocks) return -11;
+  PeerArgs a;
+  for (int i = 0; i < kMaxRanks; ++i) a.heap[i] = i < world ? static_cast<unsigned char*>(heaps[i]) : nullptr;
+  a.rank = rank;
+  a.world = world;
+  a.T = B;
+  a.H = Vl;
+  a.off_partial = a.off_gather = a.off_gscale = 0;
+  a.gscale_pitch = 0;
+  a.off_flags = 0;
+  a.epoch = nullptr;
+  a.residual_in = nullptr;
+  a.residual_out = nullptr;
+  a.weight = nullptr;
+  a.eps = a.w_offset = 0.f;
+  a.status = status;
+  a.wait_ns = g_peer_wait_ns;
+  a.pushed = 0;
+  a.off_push_flags = 0;
+  a.push_epoch = nullptr;
+  SampleArgs sa;
+  sa.temperature = temperature;
+  sa.top_k = top_k;
+  sa.top_p = top_p;
+  sa.do_sample = do_sample;
+  sa.seeds = seeds;
+  sa.steps = steps;
+  sa.off_xchg = off_xchg;
+  sa.xseq = xseq;
+  sa.vocab_total = vocab_total;
+  if (is_fp32)
+    tgi::launch(peer_sample_kernel<float>, dim3(blocks), dim3(1024), 0, stream, a, sa, static_cast<const float*>(scores),
+                row_stride, vocab_start, logit_scale, ids, logprob);
+  else
+    tgi::launch(peer_sample_kernel<__nv_bfloat16>, dim3(blocks), dim3(1024), 0, stream, a, sa,
+                static_cast<const __nv_bfloat16*>(scores), row_stride, vocab_start, logit_scale, ids, logprob);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// bytes of the exchange region that tgi_peer_sample needs in every heap
+long long tgi_peer_sample_xchg_bytes() { return static_cast<long long>(kMaxBlocks) * 2 * kXWords * kMaxRanks * 8; }
 
 }  // extern "C"

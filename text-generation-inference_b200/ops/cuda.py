@@ -52,7 +52,7 @@ def load():
                  "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention", "tgi_paged_attention_ex",
                  "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status", "tgi_lora_shrink",
                  "tgi_lora_expand", "tgi_moe_topk_softmax", "tgi_moe_sort", "tgi_moe_gather", "tgi_moe_grouped_gemm",
-                 "tgi_moe_combine", "tgi_gemm_last_grid"):
+                 "tgi_moe_combine", "tgi_gemm_last_grid", "tgi_penalties"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
     wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
@@ -399,6 +399,23 @@ def fused_sample(scores: torch.Tensor, temperature=None, top_k=None, top_p=None,
                           _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(do_sample), _ptr(seeds), _ptr(steps),
                           _ptr(ids), _ptr(lps), c_int(B), c_int(V), _stream()), "sample")
     return ids, lps
+
+
+def penalties(logits: torch.Tensor, history: torch.Tensor, repetition_penalty: Optional[torch.Tensor],
+              frequency_penalty: Optional[torch.Tensor], vocab_start: int = 0, logit_scale: float = 1.0) -> torch.Tensor:
+    """fp32 copy of ``logits[B, V]`` (bf16 or fp32; ``V`` may be a vocabulary slice starting at ``vocab_start``) with
+    the repetition and frequency penalties of the rows' token ``history[B, L]`` applied, in one kernel."""
+    lib = load()
+    B, V = logits.shape
+    assert logits.stride(1) == 1 and logits.dtype in (torch.bfloat16, torch.float32)
+    out = torch.empty(B, V, dtype=torch.float32, device=logits.device)
+    history = history.to(device=logits.device, dtype=torch.int64).contiguous()
+    rep = None if repetition_penalty is None else repetition_penalty.to(torch.float32).contiguous()
+    freq = None if frequency_penalty is None else frequency_penalty.to(torch.float32).contiguous()
+    _check(lib.tgi_penalties(_ptr(logits), c_int(1 if logits.dtype == torch.float32 else 0), c_ll(logits.stride(0)),
+                             _ptr(out), c_ll(V), _ptr(history), c_int(history.shape[1]), _ptr(rep), _ptr(freq),
+                             c_int(vocab_start), c_int(B), c_int(V), ctypes.c_float(logit_scale), _stream()), "penalties")
+    return out
 
 
 def moe_topk_softmax(router_logits: torch.Tensor, top_k: int, renormalize: bool = True):

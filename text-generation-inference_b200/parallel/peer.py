@@ -67,8 +67,9 @@ class PeerComm:
         self.max_tokens, self.width = int(max_tokens), int(width)
         lib = self.lib = K.load()
         for name in ("tgi_peer_alloc", "tgi_peer_free", "tgi_peer_export", "tgi_peer_import", "tgi_peer_unmap",
-                     "tgi_peer_max_blocks", "tgi_peer_reduce"):
+                     "tgi_peer_max_blocks", "tgi_peer_reduce", "tgi_peer_argmax", "tgi_peer_sample"):
             getattr(lib, name).restype = ctypes.c_int
+        lib.tgi_peer_sample_xchg_bytes.restype = ctypes.c_longlong
         self.max_blocks = int(lib.tgi_peer_max_blocks())
         self.pitch = _round_up(self.max_tokens, 4)
         nflag = 2 * self.max_blocks * 8 * 4
@@ -81,7 +82,8 @@ class PeerComm:
         self.off_gscale = self.off_gather + _round_up(nrows, _ALIGN)
         self.off_cand = self.off_gscale + _round_up(max(self.width // 128, 1) * self.pitch * 4, _ALIGN)
         self.max_argmax_rows = 1024          # greedy candidates: 16 bytes per row and rank
-        self.heap_bytes = self.off_cand + _round_up(self.max_argmax_rows * 8 * 16, _ALIGN)
+        self.off_xchg = self.off_cand + _round_up(self.max_argmax_rows * 8 * 16, _ALIGN)   # sampler exchange words
+        self.heap_bytes = self.off_xchg + _round_up(int(lib.tgi_peer_sample_xchg_bytes()), _ALIGN)
 
         torch.cuda.set_device(device)
         base = ctypes.c_void_p()
@@ -114,6 +116,7 @@ class PeerComm:
         self._gscale = self._heap_t[self.off_gscale:self.off_cand].view(torch.float32)
         self.epoch = torch.zeros(self.max_blocks, dtype=torch.int32, device=device)
         self.push_state = torch.zeros(2, dtype=torch.int32, device=device)   # [finished CTAs, call counter]
+        self.xseq = torch.zeros(self.max_blocks, dtype=torch.int32, device=device)   # sampler exchange rounds per block
         # row-parallel GEMMs push their rows to the owners from this many tokens on; smaller steps pull
         self.push_min_tokens = int(os.environ.get("TGI_B200_PUSH_MIN_TOKENS", "512"))
         rows_per = (self.max_tokens + world - 1) // world
@@ -211,6 +214,36 @@ class PeerComm:
             K._ptr(self.epoch), K._ptr(ids), K._ptr(lps), ctypes.c_int(max(1, min(B, self.max_blocks))),
             K._ptr(self.status), K._stream())
         K._check(rc, "peer_argmax")
+        return ids, lps
+
+    def sample(self, local_scores: torch.Tensor, vocab_start: int, vocab_total: int, logit_scale: float = 1.0,
+               temperature: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
+               top_p: Optional[torch.Tensor] = None, do_sample: Optional[torch.Tensor] = None,
+               seeds: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None):
+        """Temperature / top-k / top-p / seeded sampling on vocabulary-sharded scores ``[B, V / world]`` (bf16
+        logits, or fp32 scores that already carry the penalties): the ranks exchange a few scalars per row instead
+        of gathering ``[B, V]`` logits, and all of them return the same ``(ids int64, logprobs fp32)``.  The draw
+        for a seed equals the single-GPU fused sampler's (``ops.fused_sample``)."""
+        B, Vl = local_scores.shape
+        assert local_scores.stride(1) == 1 and local_scores.dtype in (torch.bfloat16, torch.float32)
+        dev = self.device
+
+        def as_(t, dtype):
+            return None if t is None else t.to(device=dev, dtype=dtype).contiguous()
+
+        temperature, top_p = as_(temperature, torch.float32), as_(top_p, torch.float32)
+        top_k, steps = as_(top_k, torch.int32), as_(steps, torch.int32)
+        do_sample, seeds = as_(do_sample, torch.uint8), as_(seeds, torch.int64)
+        ids = torch.empty(B, dtype=torch.int64, device=dev)
+        lps = torch.empty(B, dtype=torch.float32, device=dev)
+        rc = self.lib.tgi_peer_sample(
+            self._heap_arr, ctypes.c_int(self.rank), ctypes.c_int(self.world), K._ptr(local_scores),
+            ctypes.c_int(1 if local_scores.dtype == torch.float32 else 0), ctypes.c_int(B), ctypes.c_int(Vl),
+            ctypes.c_longlong(local_scores.stride(0)), ctypes.c_int(vocab_start), ctypes.c_int(vocab_total),
+            ctypes.c_float(logit_scale), K._ptr(temperature), K._ptr(top_k), K._ptr(top_p), K._ptr(do_sample),
+            K._ptr(seeds), K._ptr(steps), ctypes.c_longlong(self.off_xchg), K._ptr(self.xseq), K._ptr(ids), K._ptr(lps),
+            ctypes.c_int(max(1, min(B, self.max_blocks))), K._ptr(self.status), K._stream())
+        K._check(rc, "peer_sample")
         return ids, lps
 
     def check(self) -> int:

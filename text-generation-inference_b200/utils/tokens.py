@@ -291,7 +291,11 @@ class NextTokenChooser:
         kernel launch for the whole batch (``ops.fused_sample``)."""
         from .. import ops
 
-        if self.watermarks or self.any_rep or self.any_freq or self.grammar is not None:
+        if (self.any_rep or self.any_freq) and not self.watermarks and self.grammar is None and hasattr(ops, "penalties"):
+            # penalties from the token history in one kernel (fp32 copy of the scores)
+            scores = ops.penalties(scores, input_ids, self.repetition_penalty if self.any_rep else None,
+                                   self.frequency_penalty if self.any_freq else None)
+        elif self.watermarks or self.any_rep or self.any_freq or self.grammar is not None:
             scores = scores.float().clone()
             for i, wm in self.watermarks.items():
                 scores[i : i + 1] = wm(input_ids[i : i + 1], scores[i : i + 1])
