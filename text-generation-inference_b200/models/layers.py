@@ -36,6 +36,71 @@ class FastLinear:
         return ops.linear(x, self.weight, self.bias, out=out)
 
 
+class PackedQuantLinear:
+    """Weight-only quantised linear whose weights stay packed on the device: 4-bit (GPTQ / AWQ / symmetric, after the
+    one-time repack of ``utils.quantization.pack_gptq_for_kernel``) or int8 with one scale per output channel.
+
+    Steps of up to ``fused_max_tokens`` rows run the fused kernel that dequantises the weight tile on its way into
+    shared memory (``ops/csrc/gemm_wq_sm100.cu``): a decode step streams a quarter (half) of the bf16 bytes.
+    Larger steps are compute bound: the matrix is dequantised into a scratch buffer shared by all layers and the
+    bf16 GEMM runs on it.  Reference: ``layers/marlin/gptq.py:371-440``, ``layers/gptq/exllamav2.py``,
+    ``layers/awq/quantize/cuda.py:19-49``, ``layers/eetq.py:27-47``."""
+
+    fused_max_tokens = int(__import__("os").environ.get("TGI_B200_WQ_FUSED_TOKENS", "512"))
+
+    def __init__(self, wq, scale, zp, group: int, bits: int, perm, in_features: int, bias=None, dtype=torch.bfloat16):
+        self.wq, self.scale, self.zp, self.group, self.bits = wq, scale, zp, int(group), int(bits)
+        self.perm, self.in_features, self.bias, self.dtype = perm, int(in_features), bias, dtype
+
+    @property
+    def out_features(self):
+        return self.wq.shape[0]
+
+    @property
+    def weight(self) -> torch.Tensor:
+        """Dequantised ``[N, K]`` matrix in the original column order (merges, LoRA base lookups, tests)."""
+        w = self.dequantize()
+        if self.perm is not None:
+            inv = torch.empty_like(self.perm)
+            inv[self.perm] = torch.arange(self.perm.numel(), device=self.perm.device)
+            w = w[:, inv]
+        return w
+
+    def dequantize(self) -> torch.Tensor:
+        """bf16 ``[N, K]`` in the kernel's column order: bf16((q - zp) * scale), the GEMM's operand."""
+        if self.wq.is_cuda and ops.use_native(self.wq):
+            return ops.native().wq_dequant(self.wq, self.scale, self.zp, self.group, self.bits, self.in_features)
+        K, N = self.in_features, self.wq.shape[0]
+        if self.bits == 4:
+            q = torch.stack([self.wq & 0xF, self.wq >> 4], dim=2).reshape(N, K).float()
+            z = self.zp.float() if self.zp is not None else torch.full_like(self.scale.float(), 8.0)
+        else:
+            q = self.wq.float()
+            z = torch.zeros_like(self.scale.float())
+        gi = torch.arange(K, device=self.wq.device) // self.group
+        return ((q - z.t()[:, gi]) * self.scale.float().t()[:, gi]).to(torch.bfloat16)
+
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        if self.perm is not None:
+            x2 = x2.index_select(1, self.perm)
+        if x2.is_cuda and ops.use_native(x2) and x2.dtype == torch.bfloat16:
+            if x2.shape[0] <= self.fused_max_tokens:
+                y = ops.native().gemm_wq(x2, self.wq, self.scale, self.zp, self.group, self.bits, self.bias)
+            else:
+                w = ops.native().wq_dequant_scratch(self.wq, self.scale, self.zp, self.group, self.bits, self.in_features)
+                y = ops.linear(x2, w, self.bias)
+        else:
+            y = torch.nn.functional.linear(x2.float(), self.dequantize().float(),
+                                           None if self.bias is None else self.bias.float()).to(x.dtype)
+        y = y.view(*shape[:-1], y.shape[-1])
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+
 class Fp8Linear:
     """e4m3 weight with per-tensor, per-channel or 128x128-block scales.
 

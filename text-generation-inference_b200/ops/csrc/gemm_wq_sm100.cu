@@ -1,0 +1,446 @@
+// Weight-only quantised GEMM for sm_100a:   C[M, N] = X[M, K] (bf16) * dequant(Wq)[N, K]^T (+ bias)
+//
+//   4-bit:  Wq uint8 [N, K / 2], element k of a row in byte k / 2 (even k: low nibble), values 0..15;
+//           w = (q - zp[g, n]) * scale[g, n]  with g = k / group  (zp: the zero point as a bf16 number, 8 when
+//           absent; GPTQ, AWQ and symmetric formats are all served after a one-time repack at load,
+//           utils/quantization.py)
+//   8-bit:  Wq int8 [N, K], w = q * scale[g, n]  (EETQ, LLM.int8 weights, compressed-tensors W8A16)
+//
+// Replaces, in the reference, the Marlin / exllama / AWQ / EETQ weight-only GEMMs (layers/marlin/gptq.py:371-440,
+// server/exllamav2_kernels/.../q_gemm.cu, layers/awq/quantize/cuda.py:19-49, layers/eetq.py:27-47): the packed
+// weights stay packed in device memory (a 4-bit 70B model is 35 GB, not 140 GB) and a decode step streams a
+// quarter of the bytes of the bf16 GEMM.
+//
+// The tensor cores take bf16 operands from shared memory, so the weight tile is dequantised on its way there:
+//   warp 0      TMA producer: token tile [128 x 64 bf16] with the 128-byte swizzle, and the RAW weight tile
+//               [128 rows x 32 or 64 bytes]
+//   warps 4-11  converters, half a weight row per thread: unpack, (q - zp) * scale in fp32, round to bf16 once (the
+//               same number the whole-matrix dequantisation gives) and store the 64 bytes into the operand tile in
+//               the swizzled layout the MMA descriptor expects (16-byte chunk c of row r goes to chunk c ^ (r & 7)),
+//               then `fence.proxy.async` and an arrival on the stage's `wready` barrier
+//   warp 1      one thread issues tcgen05.mma (kind::f16, M 128 x N 128, accumulators in TMEM, two buffers)
+//   warps 12-15 epilogue: TMEM -> registers -> bf16 rows of C (or fp32 partials when K is split)
+// Work units are (output tile, K split); with more than one split the partial tiles go to an fp32 workspace and a
+// second kernel adds them in split order (deterministic).  All waits are bounded (sm100.cuh).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <atomic>
+
+#include "launch.cuh"
+#include "sm100.cuh"
+#include "tensor_map.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kStages = 4;
+constexpr int kTileM = 128, kTileN = 128, kBK = 64;
+
+__device__ __forceinline__ void report(int* status, int code) {
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+template <int BITS>
+struct WqCfg {
+  static constexpr int kRawRowBytes = kBK * BITS / 8;              // 32 (4-bit) or 64 (8-bit)
+  static constexpr int kRawBytes = kTileN * kRawRowBytes;
+  static constexpr int kXBytes = kTileM * 128;
+  static constexpr int kWBytes = kTileN * 128;
+  static constexpr int kStageBytes = kXBytes + kWBytes + kRawBytes;   // 36 KB / 40 KB
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmQ,
+               const __half* __restrict__ scale, const __half* __restrict__ zp, int group,
+               __nv_bfloat16* __restrict__ C, float* __restrict__ partial, const __nv_bfloat16* __restrict__ bias, int M,
+               int N, int K, int splits, int* __restrict__ status) {
+  using Cfg = WqCfg<BITS>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* empty = full + kStages;
+  uint64_t* wready = empty + kStages;
+  uint64_t* tmem_full = wready + kStages;    // [2]
+  uint64_t* tmem_empty = tmem_full + 2;      // [2]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (N + kTileN - 1) / kTileN, m_tiles = (M + kTileM - 1) / kTileM;
+  const int KB = (K + kBK - 1) / kBK;
+  const int kb_per = (KB + splits - 1) / splits;
+  const int units = n_tiles * m_tiles * splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&wready[s], 8);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&tmX);
+    prefetch_tensormap(&tmQ);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
+
+  // unit -> (tile coordinates, K-block range); the weight tile is the slow index so that the CTAs working at
+  // the same time stream different weight rows and share the token tiles in L2
+  auto decode = [&](int unit, int& tm, int& tn, int& kb0, int& kb1) {
+    const int sp = unit % splits;
+    const int tile = unit / splits;
+    tm = tile % m_tiles;
+    tn = tile / m_tiles;
+    kb0 = sp * kb_per;
+    kb1 = min(KB, kb0 + kb_per);
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (elect_one()) {
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      int it = 0, issued = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        int tm, tn, kb0, kb1;
+        decode(unit, tm, tn, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          if (it >= kStages) ok = mbar_wait(&empty[s], ((it / kStages) - 1) & 1);
+          if (!ok) { report(status, kErrProducerWait); break; }
+          uint8_t* st = smem + s * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(&full[s], Cfg::kXBytes + Cfg::kRawBytes);
+          tma_load_2d_hint(st, &tmX, &full[s], kb * kBK, tm * kTileM, pol_x);
+          tma_load_2d_hint(st + Cfg::kXBytes + Cfg::kWBytes, &tmQ, &full[s], kb * Cfg::kRawRowBytes, tn * kTileN, pol_w);
+          issued = it + 1;
+        }
+      }
+      if (!ok)
+        for (int j = max(0, issued - kStages); j < issued; ++j) mbar_wait(&full[j % kStages], (j / kStages) & 1, 1u << 12);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc(kTileM, kTileN, 1, 1);
+      int it = 0, use = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++use) {
+        int tm, tn, kb0, kb1;
+        decode(unit, tm, tn, kb0, kb1);
+        const int b = use & 1;
+        if (use >= 2 && !mbar_wait(&tmem_empty[b], ((use >> 1) - 1) & 1)) {
+          report(status, kErrMmaWaitAccum);
+          break;
+        }
+        tc_fence_after();
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          // token tile landed (TMA), weight tile converted
+          if (!mbar_wait(&full[s], (it / kStages) & 1) || !mbar_wait(&wready[s], (it / kStages) & 1)) {
+            report(status, kErrMmaWaitFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t x_addr = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint64_t dx = make_desc_sw128(x_addr);
+          const uint64_t dw = make_desc_sw128(x_addr + Cfg::kXBytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_f16(tmem_base + b * 128, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(&tmem_full[b]);
+      }
+    }
+  } else if (warp >= 4 && warp < 12) {
+    // ---------------- converters: half a weight row per thread ----------------
+    const int t = (warp - 4) * 32 + lane;       // 0..255
+    const int r = t >> 1, half = t & 1;         // row of the tile, which 32 elements of its 64
+    int it = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+      int tm, tn, kb0, kb1;
+      decode(unit, tm, tn, kb0, kb1);
+      const int n = min(tn * kTileN + r, N - 1);          // rows past N are loaded as zeros and never stored
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % kStages;
+        if (!mbar_wait(&full[s], (it / kStages) & 1)) {
+          report(status, kErrMmaWaitFull);
+          ok = false;
+          break;
+        }
+        const int g = (kb * kBK) / group;
+        const float sc = __half2float(scale[static_cast<size_t>(g) * N + n]);
+        uint8_t* st = smem + s * Cfg::kStageBytes;
+        const uint8_t* raw = st + Cfg::kXBytes + Cfg::kWBytes + r * Cfg::kRawRowBytes + half * (Cfg::kRawRowBytes / 2);
+        uint8_t* dst = st + Cfg::kXBytes + r * 128;
+        if (BITS == 4) {
+          // bf16(128 + q) is 0x4300 | q exactly; widened to fp32 it enters one fused multiply-add:
+          // (128 + q) * s - (128 + zp) * s = (q - zp) * s
+          const float z = zp != nullptr ? __half2float(zp[static_cast<size_t>(g) * N + n]) : 8.f;
+          const float off = -(128.f + z) * sc;
+          const uint4 q = *reinterpret_cast<const uint4*>(raw);
+          const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {         // chunk 4 * half + cc: elements of word cc
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t byte = (words[cc] >> (8 * j)) & 0xFFu;
+              const float lo = __uint_as_float((0x4300u | (byte & 0xFu)) << 16);
+              const float hi = __uint_as_float((0x4300u | (byte >> 4)) << 16);
+              const __nv_bfloat162 v = __floats2bfloat162_rn(fmaf(lo, sc, off), fmaf(hi, sc, off));
+              o[j] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            const int c = half * 4 + cc;
+            *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {         // chunk 4 * half + cc: bytes 8 cc .. 8 cc + 7 of this half
+            const uint2 q = *reinterpret_cast<const uint2*>(raw + cc * 8);
+            const uint32_t w2[2] = {q.x, q.y};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int a = static_cast<int8_t>((w2[j >> 1] >> (16 * (j & 1))) & 0xFF);
+              const int b = static_cast<int8_t>((w2[j >> 1] >> (16 * (j & 1) + 8)) & 0xFF);
+              const __nv_bfloat162 v = __floats2bfloat162_rn(static_cast<float>(a) * sc, static_cast<float>(b) * sc);
+              o[j] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            const int c = half * 4 + cc;
+            *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        fence_proxy_async();        // the generic-proxy stores above become visible to the tensor core's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&wready[s]);
+      }
+    }
+  } else if (warp >= 12) {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;
+    const int r_local = quarter * 32 + lane;
+    int use = 0;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++use) {
+      int tm, tn, kb0, kb1;
+      decode(unit, tm, tn, kb0, kb1);
+      const int b = use & 1;
+      if (!mbar_wait(&tmem_full[b], (use >> 1) & 1)) {
+        report(status, kErrEpilogueWait);
+        break;
+      }
+      tc_fence_after();
+      const int m = tm * kTileM + r_local;
+      const int n0 = tn * kTileN;
+      const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + b * 128;
+      const int sp = unit % splits;
+#pragma unroll
+      for (int c = 0; c < kTileN; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + c, v);
+        tmem_ld_wait();
+        if (m < M) {
+          if (splits == 1) {
+            __nv_bfloat16* dst = C + static_cast<size_t>(m) * N + n0 + c;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (n0 + c + j >= N) break;
+              __nv_bfloat162 o[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float f0 = __uint_as_float(v[j + 2 * q]), f1 = __uint_as_float(v[j + 2 * q + 1]);
+                if (bias != nullptr) {
+                  f0 += __bfloat162float(bias[n0 + c + j + 2 * q]);
+                  f1 += __bfloat162float(bias[n0 + c + j + 2 * q + 1]);
+                }
+                o[q] = __floats2bfloat162_rn(f0, f1);
+              }
+              *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<uint4*>(o);
+            }
+          } else {
+            float* dst = partial + (static_cast<size_t>(sp) * M + m) * N + n0 + c;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (n0 + c + j >= N) break;
+              *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[b]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 256);
+}
+
+// C = sum over splits (in split order) of the fp32 partials (+ bias), 8 outputs per thread
+__global__ void __launch_bounds__(256)
+wq_reduce_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ C,
+                 int M, int N, int splits) {
+  tgi::pdl_wait();
+  const size_t total = static_cast<size_t>(M) * N / 8;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < splits; ++s) {
+      const float4* p = reinterpret_cast<const float4*>(partial + static_cast<size_t>(s) * M * N + i * 8);
+      const float4 a = p[0], b = p[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    const int col = static_cast<int>((i * 8) % N);
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float f0 = acc[2 * q], f1 = acc[2 * q + 1];
+      if (bias != nullptr) {
+        f0 += __bfloat162float(bias[col + 2 * q]);
+        f1 += __bfloat162float(bias[col + 2 * q + 1]);
+      }
+      o[q] = __floats2bfloat162_rn(f0, f1);
+    }
+    reinterpret_cast<uint4*>(C)[i] = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// Whole-matrix dequantisation to bf16 [N, K] (prefill-sized steps run the bf16 GEMM on it)
+template <int BITS>
+__global__ void __launch_bounds__(256)
+wq_dequant_kernel(const uint8_t* __restrict__ wq, const __half* __restrict__ scale, const __half* __restrict__ zp,
+                  int group, __nv_bfloat16* __restrict__ out, int N, int K) {
+  const size_t total = static_cast<size_t>(N) * K / 8;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t e = i * 8;
+    const int n = static_cast<int>(e / K), k = static_cast<int>(e % K);
+    const int g = k / group;
+    const float sc = __half2float(scale[static_cast<size_t>(g) * N + n]);
+    float f[8];
+    if (BITS == 4) {
+      const float z = zp != nullptr ? __half2float(zp[static_cast<size_t>(g) * N + n]) : 8.f;
+      const float off = -(128.f + z) * sc;      // same arithmetic as the GEMM's converters
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(wq + e / 2);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = fmaf(128.f + static_cast<float>((w >> (4 * j)) & 0xF), sc, off);
+    } else {
+      const uint2 w = *reinterpret_cast<const uint2*>(wq + e);
+      const uint32_t ww[2] = {w.x, w.y};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = static_cast<float>(static_cast<int8_t>((ww[j >> 2] >> (8 * (j & 3))) & 0xFF)) * sc;
+    }
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+    reinterpret_cast<uint4*>(out)[i] = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+template <int BITS>
+int launch_wq(const void* X, const void* Wq, const void* scale, const void* zp, int group, void* C, float* partial,
+              long long partial_floats, const void* bias, int M, int N, int K, int ctas, int* status, cudaStream_t stream) {
+  using Cfg = WqCfg<BITS>;
+  CUtensorMap tmX, tmQ;
+  int rc = tgi::make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, X, M, K, static_cast<uint64_t>(K) * 2, 128, kBK,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  const uint64_t row_bytes = static_cast<uint64_t>(K) * BITS / 8;
+  rc = tgi::make_map_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_UINT8, Wq, N, row_bytes, row_bytes, kTileN, Cfg::kRawRowBytes,
+                        CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  const size_t smem = kStages * Cfg::kStageBytes + 1024 + 256;
+  auto kern = gemm_wq_kernel<BITS>;
+  static std::atomic<unsigned long long> attr_set{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -2;
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (!(attr_set.load(std::memory_order_acquire) & bit)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return -2;
+    attr_set.fetch_or(bit, std::memory_order_release);
+  }
+  // K splits: enough units to occupy the GPU, at least 8 K blocks per unit, bounded by the workspace
+  const int tiles = ((N + kTileN - 1) / kTileN) * ((M + kTileM - 1) / kTileM);
+  const int KB = (K + kBK - 1) / kBK;
+  int splits = 1;
+  if (partial != nullptr) {
+    while (tiles * splits < ctas && splits * 2 <= KB / 8 && splits < 16 && KB % (splits * 2) == 0 &&
+           static_cast<long long>(splits * 2) * M * N <= partial_floats)
+      splits *= 2;
+  }
+  if (N % 8 != 0) splits = 1;
+  int grid = tiles * splits < ctas ? tiles * splits : ctas;
+  if (grid < 1) grid = 1;
+  cudaError_t err = tgi::launch(kern, dim3(grid), dim3(kThreads), smem, stream, tmX, tmQ,
+                                static_cast<const __half*>(scale), static_cast<const __half*>(zp), group,
+                                static_cast<__nv_bfloat16*>(C), partial, static_cast<const __nv_bfloat16*>(bias), M, N, K,
+                                splits, status);
+  if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) return -3;
+  if (splits > 1) {
+    const long long vecs = static_cast<long long>(M) * N / 8;
+    const int rgrid = static_cast<int>(vecs / 256 + 1 < 2048 ? vecs / 256 + 1 : 2048);
+    err = tgi::launch(wq_reduce_kernel, dim3(rgrid), dim3(256), 0, stream, static_cast<const float*>(partial),
+                      static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(C), M, N, splits);
+    if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) return -3;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// bits: 4 (Wq uint8 [N, K / 2]) or 8 (Wq int8 [N, K]); scale / zp fp16 [K / group, N] (zp may be null: the 4-bit
+// zero point is then 8, the 8-bit format has none); partial: fp32 workspace of `partial_floats` floats or null.
+int tgi_gemm_wq(int bits, const void* X, const void* Wq, const void* scale, const void* zp, int group, void* C,
+                float* partial, long long partial_floats, const void* bias, int M, int N, int K, int ctas, int* status,
+                cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % kBK != 0 || group < kBK || group % kBK != 0 || N % 8 != 0 || ctas < 1) return -10;
+  if (bits == 4) return launch_wq<4>(X, Wq, scale, zp, group, C, partial, partial_floats, bias, M, N, K, ctas, status, stream);
+  if (bits == 8) return launch_wq<8>(X, Wq, scale, nullptr, group, C, partial, partial_floats, bias, M, N, K, ctas, status, stream);
+  return -11;
+}
+
+// out bf16 [N, K] = dequantised weight (same formats as tgi_gemm_wq)
+int tgi_wq_dequant(int bits, const void* Wq, const void* scale, const void* zp, int group, void* out, int N, int K,
+                   cudaStream_t stream) {
+  if (N <= 0 || K <= 0) return 0;
+  if (K % 8 != 0 || group % 8 != 0) return -10;
+  const long long vecs = static_cast<long long>(N) * K / 8;
+  const int grid = static_cast<int>(vecs / 256 + 1 < 8192 ? vecs / 256 + 1 : 8192);
+  if (bits == 4)
+    tgi::launch(wq_dequant_kernel<4>, dim3(grid), dim3(256), 0, stream, static_cast<const uint8_t*>(Wq),
+                static_cast<const __half*>(scale), static_cast<const __half*>(zp), group,
+                static_cast<__nv_bfloat16*>(out), N, K);
+  else if (bits == 8)
+    tgi::launch(wq_dequant_kernel<8>, dim3(grid), dim3(256), 0, stream, static_cast<const uint8_t*>(Wq),
+                static_cast<const __half*>(scale), static_cast<const __half*>(nullptr), group,
+                static_cast<__nv_bfloat16*>(out), N, K);
+  else
+    return -11;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // extern "C"

@@ -52,7 +52,7 @@ def load():
                  "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention", "tgi_paged_attention_ex",
                  "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status", "tgi_lora_shrink",
                  "tgi_lora_expand", "tgi_moe_topk_softmax", "tgi_moe_sort", "tgi_moe_gather", "tgi_moe_grouped_gemm",
-                 "tgi_moe_combine", "tgi_gemm_last_grid", "tgi_penalties"):
+                 "tgi_moe_combine", "tgi_gemm_last_grid", "tgi_penalties", "tgi_gemm_wq", "tgi_wq_dequant"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
     wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
@@ -399,6 +399,59 @@ def fused_sample(scores: torch.Tensor, temperature=None, top_k=None, top_p=None,
                           _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(do_sample), _ptr(seeds), _ptr(steps),
                           _ptr(ids), _ptr(lps), c_int(B), c_int(V), _stream()), "sample")
     return ids, lps
+
+
+# ---- weight-only quantised GEMM ------------------------------------------------------------------
+_WQ_SCRATCH = {}
+
+
+def _wq_partial(device) -> torch.Tensor:
+    """fp32 workspace of the K-split partial tiles (shared by all layers of a device)."""
+    key = ("partial", device.index)
+    t = _WQ_SCRATCH.get(key)
+    if t is None:
+        t = torch.empty(int(os.environ.get("TGI_B200_WQ_WS_MB", "64")) << 18, dtype=torch.float32, device=device)
+        _WQ_SCRATCH[key] = t
+    return t
+
+
+def gemm_wq(x: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor, zp: Optional[torch.Tensor], group: int, bits: int,
+            bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x[M, K] (bf16) @ dequant(wq)[N, K]^T`` with the weights dequantised on their way into shared memory:
+    ``wq`` uint8 ``[N, K/2]`` (4-bit, low nibble first) or int8 ``[N, K]``; ``scale`` / ``zp`` fp16 ``[K/group, N]``."""
+    lib = load()
+    st = state(x.device)
+    M, K = x.shape
+    N = wq.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    part = _wq_partial(x.device)
+    _check(lib.tgi_gemm_wq(c_int(bits), _ptr(x.contiguous()), _ptr(wq), _ptr(scale), _ptr(zp), c_int(group), _ptr(out),
+                           _ptr(part), c_ll(part.numel()), _ptr(bias), c_int(M), c_int(N), c_int(K), c_int(st.sm_count),
+                           _ptr(st.status), _stream()), "gemm_wq")
+    return out
+
+
+def wq_dequant(wq: torch.Tensor, scale: torch.Tensor, zp: Optional[torch.Tensor], group: int, bits: int, K: int,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 ``[N, K]`` matrix of a packed weight (the numbers the fused GEMM feeds to the tensor cores)."""
+    lib = load()
+    N = wq.shape[0]
+    if out is None:
+        out = torch.empty(N, K, dtype=torch.bfloat16, device=wq.device)
+    _check(lib.tgi_wq_dequant(c_int(bits), _ptr(wq), _ptr(scale), _ptr(zp), c_int(group), _ptr(out), c_int(N), c_int(K),
+                              _stream()), "wq_dequant")
+    return out
+
+
+def wq_dequant_scratch(wq, scale, zp, group, bits, K) -> torch.Tensor:
+    """Dequantise into a per-device scratch matrix that the next call overwrites (prefill-sized GEMMs)."""
+    N = wq.shape[0]
+    key = ("dequant", wq.device.index)
+    t = _WQ_SCRATCH.get(key)
+    if t is None or t.numel() < N * K:
+        t = torch.empty(N * K, dtype=torch.bfloat16, device=wq.device)
+        _WQ_SCRATCH[key] = t
+    return wq_dequant(wq, scale, zp, group, bits, K, out=t[: N * K].view(N, K))
 
 
 def penalties(logits: torch.Tensor, history: torch.Tensor, repetition_penalty: Optional[torch.Tensor],

@@ -105,8 +105,11 @@ class GPTQWeight(Weight):
         return dequantize_gptq(self)
 
     def get_linear(self, bias):
-        from ..models.layers import FastLinear
+        from ..models.layers import FastLinear, PackedQuantLinear
 
+        packed = pack_gptq_for_kernel(self)
+        if packed is not None:     # 4-bit (8-bit) weights stay packed on the device and are dequantised inside the GEMM
+            return PackedQuantLinear(*packed, bias=bias, dtype=self.dtype)
         return FastLinear(self.dequantize().to(self.dtype), bias)
 
 
@@ -142,8 +145,12 @@ class Int8Weight(Weight):
         return (self.qweight.float() * self.scale.float().unsqueeze(1)).to(self.dtype)
 
     def get_linear(self, bias):
-        from ..models.layers import FastLinear
+        from ..models.layers import FastLinear, PackedQuantLinear
 
+        N, K = self.qweight.shape
+        if K % 64 == 0 and N % 8 == 0 and self.dtype == torch.bfloat16 and float(self.scale.abs().max()) < 6e4:
+            scale = self.scale.float().view(1, N).to(torch.float16).contiguous()
+            return PackedQuantLinear(self.qweight.contiguous(), scale, None, K, 8, None, K, bias=bias, dtype=self.dtype)
         return FastLinear(self.dequantize(), bias)
 
 
@@ -210,6 +217,49 @@ def _unpack_int32(packed: torch.Tensor, bits: int, dim: int) -> torch.Tensor:
         return out.reshape(packed.shape[0] * per, packed.shape[1])
     out = (packed.unsqueeze(2) >> shifts.view(1, 1, -1)) & mask
     return out.reshape(packed.shape[0], packed.shape[1] * per)
+
+
+def pack_gptq_for_kernel(w: "GPTQWeight"):
+    """Canonical packed form of a 4-bit GPTQ / AWQ layer for the weight-only GEMM (``ops/csrc/gemm_wq_sm100.cu``), or
+    ``None`` when the layer does not fit it (other bit widths, group sizes that are no multiple of 64, odd shapes).
+
+    Returns ``(wq uint8 [N, K/2], scale fp16 [G, N], zp fp16 [G, N], group, bits, perm, K)``: element ``k`` of output
+    row ``n`` sits in byte ``k // 2`` (even ``k`` in the low nibble) and equals ``(q - zp[k // group, n]) * scale``.
+    With activation ordering (``g_idx`` not sorted) the K axis is reordered once so that groups are contiguous;
+    ``perm`` then tells the linear how to permute the activations' columns (reference: the exllama kernels'
+    ``column_remap``, ``server/exllama_kernels/exllama_kernels/cuda_func/column_remap.cu``).
+    """
+    if w.bits != 4 or w.dtype != torch.bfloat16:
+        return None
+    bits = 4
+    if w.awq:
+        iw = _unpack_int32(w.qweight, bits, dim=1)
+        iz = _unpack_int32(w.qzeros, bits, dim=1)
+        inv = torch.tensor(_AWQ_ORDER, device=iw.device).argsort()
+        iw = iw.view(iw.shape[0], -1, 8)[:, :, inv].reshape(iw.shape[0], -1)
+        zeros = iz.view(iz.shape[0], -1, 8)[:, :, inv].reshape(iz.shape[0], -1)
+    else:
+        iw = _unpack_int32(w.qweight, bits, dim=0)
+        zeros = _unpack_int32(w.qzeros, bits, dim=1) + 1
+    K, N = iw.shape
+    group = w.groupsize if w.groupsize > 0 else K
+    if K % 64 != 0 or group % 64 != 0 or N % 8 != 0 or K % group != 0:
+        return None
+    perm = None
+    if w.g_idx is not None and not w.awq:
+        gi = w.g_idx.long()
+        if not bool((gi[1:] >= gi[:-1]).all()):
+            perm = torch.argsort(gi, stable=True)
+            if not torch.equal(gi[perm], torch.arange(K, device=gi.device) // group):
+                return None      # groups of unequal size: leave it to the dequantised path
+            iw = iw[perm]
+    scales = w.scales.float()
+    if float(scales.abs().max()) >= 6e4:
+        return None
+    wt = iw.t().contiguous().to(torch.uint8)                       # [N, K]
+    wq = (wt[:, 0::2] | (wt[:, 1::2] << 4)).contiguous()
+    zp = zeros[:, :N].to(torch.float16).contiguous()
+    return wq, scales.to(torch.float16).contiguous(), zp, group, bits, perm, K
 
 
 def dequantize_gptq(w: GPTQWeight) -> torch.Tensor:
