@@ -74,6 +74,7 @@ def test_gemm_tile_configurations(K, pairs, M, N, K_):
     x = torch.randn(M, K_, device=dev(), dtype=torch.bfloat16)
     w = torch.randn(N, K_, device=dev()) * 0.05
     K.set_gemm_pairs(pairs)
+    K.load().tgi_gemm_set_pair_min_tiles(1)      # small test shapes too
     try:
         wb = w.to(torch.bfloat16)
         want = x.float() @ wb.float().t()
@@ -91,6 +92,7 @@ def test_gemm_tile_configurations(K, pairs, M, N, K_):
                 torch.testing.assert_close(got.float(), want8, atol=3e-2 * math.sqrt(K_ / 512), rtol=2e-2)
     finally:
         K.set_gemm_pairs(True)
+        K.load().tgi_gemm_set_pair_min_tiles(32)
 
 
 @pytest.mark.parametrize("T,H", [(1, 256), (5, 4096), (33, 8192), (4, 5120), (3, 16384)])
@@ -211,6 +213,18 @@ def test_paged_attention_prefill(K, fp8, Hq, Hkv, D):
     _attention_case(K, 3, [70, 1, 130], [70, 33, 200], Hq, Hkv, D, fp8)
     _attention_case(K, 2, [64, 17], [64, 400], Hq, Hkv, D, fp8, window=48)
     _attention_case(K, 2, [30, 65], [30, 65], Hq, Hkv, D, fp8, softcap=30.0)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (16, 2), (4, 4)])
+def test_paged_attention_prefill_tensor_core_tiles(K, fp8, Hq, Hkv):
+    """Head size 128 with pages of 16 tokens runs the tcgen05 kernel: several 128-row query tiles, several
+    128-token KV tiles, chunked prefill behind a cached prefix, ragged tails, windows and soft-capping."""
+    _attention_case(K, 3, [300, 129, 1000], [300, 500, 1000], Hq, Hkv, 128, fp8)
+    _attention_case(K, 2, [128, 256], [128, 2048], Hq, Hkv, 128, fp8)
+    _attention_case(K, 2, [513, 40], [700, 1100], Hq, Hkv, 128, fp8, window=200)
+    _attention_case(K, 2, [260, 131], [260, 400], Hq, Hkv, 128, fp8, softcap=30.0)
+    assert K.check_status() == 0
 
 
 @pytest.mark.parametrize("fp8", [False, True])

@@ -1243,10 +1243,32 @@ int launch_v3(const Params& p, int B, cudaStream_t stream) {
   }
 }
 
+// tcgen05 / TMEM prefill kernel (attention_prefill_sm100.cu): head size 128, pages of 16 tokens
+extern "C" int tgi_prefill_attention_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                                        const int* cu_seqlens_q, const int* kv_lens, const float* k_scale,
+                                        const float* v_scale, void* out, int B, int max_q, int max_blocks, int num_blocks,
+                                        int Hq, int Hkv, float scale, float softcap, int window, int fp8_kv,
+                                        const int* horizon, int* status, cudaStream_t stream);
+
+bool prefill_tc_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("TGI_B200_PREFILL_TC");
+    return v == nullptr || std::strcmp(v, "0") != 0;
+  }();
+  return on;
+}
+
 template <int D, bool FP8>
 int launch(const Params& p, int B, int max_q, cudaStream_t stream) {
   using S = Smem<D, FP8>;
   const int smem = S::kBytes;
+  if (max_q > 1 && D == 128 && p.block_size == 16 && B <= 65535 && prefill_tc_enabled()) {
+    int* status = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_attn_status) != cudaSuccess) return -2;
+    return tgi_prefill_attention_tc(p.q, p.k_cache, p.v_cache, p.block_tables, p.cu_seqlens_q, p.kv_lens, p.k_scale,
+                                    p.v_scale, p.out, B, max_q, p.max_blocks, p.num_blocks, p.Hq, p.Hkv, p.scale, p.softcap,
+                                    p.window, FP8 ? 1 : 0, p.horizon, status, stream);
+  }
   if (max_q > 1) {
     auto k = prefill_kernel<D, FP8>;
     static bool set = false;

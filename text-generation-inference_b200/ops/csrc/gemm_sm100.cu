@@ -740,6 +740,7 @@ int fill_push(PushArgs& p, void* const* heaps, int rank, int world, int rows_per
 
 static int g_wide_m = 128;
 static int g_pairs = 1;
+static int g_pair_min_tiles = 32;
 
 namespace {
 template <bool FP8>
@@ -749,7 +750,11 @@ int dispatch(const void* X, const float* xs_t, int xs_pitch, const void* W, cons
   if (M <= g_wide_m)
     return launch<1, 256, 4, FP8, false>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status,
                                          stream, push);
-  if (g_pairs && max_ctas >= 2) {
+  // Pairs pay off when there are enough 256 x 256 tiles to go round: with few tiles (tensor-parallel shards, narrow
+  // projections) the 74 pairs split K deeper than 148 single CTAs on 256 x 128 tiles do, and the fix-up of split
+  // tiles costs more than the saved operand traffic (measured: 256 x 7168 x 8192 51 us in pairs, 48 us without).
+  const long long pair_tiles = static_cast<long long>((N + 255) / 256) * ((M + 255) / 256);
+  if (g_pairs && max_ctas >= 2 && pair_tiles >= g_pair_min_tiles) {
     const int rc = launch<1, 256, 6, FP8, true>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters,
                                                 status, stream, push);
     if (rc != -4) return rc;   // -4: this device cannot place a pair; fall back to single CTAs
@@ -779,6 +784,7 @@ int tgi_gemm_num_tiles(int M, int N) {
 // 256 x 256 tiles, or single CTAs on 256 x 128 tiles when pairs are switched off.
 void tgi_gemm_set_wide_m(int m) { g_wide_m = m < 128 ? 128 : m; }
 void tgi_gemm_set_pairs(int on) { g_pairs = on != 0; }
+void tgi_gemm_set_pair_min_tiles(int n) { g_pair_min_tiles = n < 1 ? 1 : n; }
 // CTAs of the most recent GEMM launch of this process (diagnostics and benchmarks).
 int tgi_gemm_last_grid(void) { return g_last_grid; }
 
