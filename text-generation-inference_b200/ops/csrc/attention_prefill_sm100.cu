@@ -16,8 +16,9 @@
 //   O  = O a + PV  eight warps keep the running output in registers (64 columns per thread), rescale it by the
 //                  row's a = exp2(m_old - m_new) and add the tile's product read back from TMEM
 // K and V pages are fetched with TMA boxes of one page (16 tokens x 128 bytes) straight from the page pool, no
-// per-lane address arithmetic.  e4m3 pages are widened to fp16 (exact) by two converter warps on their way into
-// the operand tiles and the MMAs then run in fp16 (Q is converted once); bf16 pages feed bf16 MMAs directly.
+// per-lane address arithmetic.  e4m3 pages are widened to fp16 (exact) on their way into the operand tiles by the
+// eight output warps, which are idle most of a tile (64 bytes per thread), and the MMAs then run in fp16 (Q is
+// converted once); bf16 pages feed bf16 MMAs directly.
 // The S accumulator and the PV accumulator are double-buffered in TMEM (4 x 128 columns), so the tensor core
 // computes S of the next tile while the softmax warps work on the current one.
 // Every wait is bounded; a wait that runs out sets the status word, the CTA drains and frees its TMEM.
@@ -41,7 +42,7 @@ constexpr int kD = 128;            // head size
 constexpr int kRows = 128;         // query rows per CTA
 constexpr int kKeys = 128;         // KV tokens per tile
 constexpr int kPage = 16;          // tokens per page
-constexpr int kThreads = 640;            // 20 warps: producer, MMA, 2 converters, 8 softmax, 8 output
+constexpr int kThreads = 640;            // 20 warps: K producer, MMA, V producer, spare, 8 softmax, 8 output
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kSlab = kRows * 128;             // bytes of one [128 rows x 128 bytes] swizzled slab
 constexpr int kTileBytes = 2 * kSlab;          // a 128 x 128 tile of 16-bit values: two slabs (32 KB)
@@ -205,16 +206,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&k_free[i], FP8 ? 2 : 1);      // e4m3: the two converter warps
-      mbar_init(&v_free[i], FP8 ? 2 : 1);
+      mbar_init(&k_free[i], FP8 ? 8 : 1);      // e4m3: the eight converting warps
+      mbar_init(&v_free[i], FP8 ? 8 : 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_free[i], 8);
       mbar_init(&pv_full[i], 1);
       mbar_init(&pv_free[i], 8);
     }
-    mbar_init(kc_ready, 2);
+    mbar_init(kc_ready, 8);
     mbar_init(kc_free, 1);
-    mbar_init(vc_ready, 2);
+    mbar_init(vc_ready, 8);
     mbar_init(vc_free, 1);
     mbar_init(p_ready, 8);
     mbar_init(p_free, 1);
@@ -259,9 +260,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   // ---------------- TMA producers: one box per page and 64-element half of the head ----------------
   // A thread's TMA copies issue one after the other (about 400 cycles each, measured), so a tile's boxes are
   // spread over lanes: lane l copies page l % 8, half (l / 8) % 2.  Lanes 0..7 read the tile's block ids with one
-  // coalesced load; lane 0 does the waits and posts the expected byte count.  bf16 pages: warp 0 brings K and
-  // warp 2 brings V, each on its own ring of two stages; e4m3 pages (half the bytes, stages released by the
-  // converters right away): warp 0 brings both.
+  // coalesced load; lane 0 does the waits and posts the expected byte count.  Warp 0 brings K and warp 2 brings
+  // V, each on its own ring of two stages.
   auto produce = [&](bool do_k, bool do_v) {
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
@@ -289,11 +289,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       if (!ok) break;
       const int pg = lane & 7;
       if (FP8) {
-        // lanes 0..7: K pages, lanes 8..15: V pages (one 128-byte-wide box covers the whole head)
-        const int kv = lane >> 3;
-        if (lane < 16 && (kv == 0 ? do_k : do_v)) {
-          uint8_t* dst = smem + (kv == 0 ? L::kK : L::kV) + s * L::kRawStage + pg * (kPage * 128);
-          tma_load_2d(dst, kv == 0 ? &tmK : &tmV, kv == 0 ? &k_full[s] : &v_full[s], kvh * kD, blk * kPage);
+        // one 128-byte-wide box covers the whole head
+        if (lane < 8) {
+          if (do_k) tma_load_2d(smem + L::kK + s * L::kRawStage + pg * (kPage * 128), &tmK, &k_full[s], kvh * kD, blk * kPage);
+          if (do_v) tma_load_2d(smem + L::kV + s * L::kRawStage + pg * (kPage * 128), &tmV, &v_full[s], kvh * kD, blk * kPage);
         }
       } else if (lane < 16) {
         const int hf = lane >> 3;
@@ -306,7 +305,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     }
   };
   if (warp == 0) {
-    produce(true, FP8);
+    produce(true, false);
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
@@ -367,52 +366,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         if (ok) ok = issue_pv(j);
       }
     }
-  } else if (warp == 2 || warp == 3) {
-    if (!FP8) {
-      if (warp == 2) produce(false, true);
-    } else {
-      // ---------------- converters (e4m3 pages): raw [128 tokens x 128 bytes] -> fp16 operand tile ----------------
-      const int t = (warp - 2) * 32 + lane;       // 0..63: token rows t and t + 64
-      bool ok = true;
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int s = j & 1;
-        for (int kv = 0; kv < 2 && ok; ++kv) {
-          uint64_t* full = kv == 0 ? &k_full[s] : &v_full[s];
-          uint64_t* raw_free = kv == 0 ? &k_free[s] : &v_free[s];
-          uint64_t* c_ready = kv == 0 ? kc_ready : vc_ready;
-          uint64_t* c_free = kv == 0 ? kc_free : vc_free;
-          if (!mbar_wait(full, (j >> 1) & 1)) { report(p.status, kErrMmaWaitFull); ok = false; break; }
-          if (j >= 1 && !mbar_wait(c_free, (j - 1) & 1)) { report(p.status, kErrMmaWaitAccum); ok = false; break; }
-          const uint8_t* raw = smem + (kv == 0 ? L::kK : L::kV) + s * L::kRawStage;
-          uint8_t* dst = smem + (kv == 0 ? L::kK : L::kV) + 2 * L::kRawStage;
-#pragma unroll
-          for (int rr = 0; rr < 2; ++rr) {
-            const int row = t + rr * 64;
-#pragma unroll
-            for (int c16 = 0; c16 < 8; ++c16) {          // 16 e4m3 bytes -> two 16-byte chunks of fp16
-              const uint4 q = *reinterpret_cast<const uint4*>(raw + row * 128 + c16 * 16);
-              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-              uint32_t o[8];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(o[2 * i]) : "h"(static_cast<unsigned short>(w[i] & 0xFFFFu)));
-                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(o[2 * i + 1]) : "h"(static_cast<unsigned short>(w[i] >> 16)));
-              }
-              const int ch = c16 * 2;                    // chunk index among the row's 16 chunks of 8 elements
-              *reinterpret_cast<uint4*>(dst + (ch >> 3) * kSlab + swz_chunk(row, ch & 7)) = make_uint4(o[0], o[1], o[2], o[3]);
-              *reinterpret_cast<uint4*>(dst + ((ch + 1) >> 3) * kSlab + swz_chunk(row, (ch + 1) & 7)) =
-                  make_uint4(o[4], o[5], o[6], o[7]);
-            }
-          }
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(c_ready);
-            mbar_arrive(raw_free);
-          }
-        }
-      }
-    }
+  } else if (warp == 2) {
+    produce(false, true);
+  } else if (warp == 3) {
+    // spare
   } else if (warp < 12) {
     // ---------------- softmax: two threads per query row, 64 keys each ----------------
     const int quarter = warp & 3;
@@ -515,8 +472,48 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 #pragma unroll
     for (int i = 0; i < 64; ++i) o[i] = 0.f;
     bool ok = true;
+    // e4m3 pages: raw [128 tokens x 128 bytes] stage -> fp16 operand tile (one buffer per K and V), 64 bytes per
+    // thread.  Tile i's K may be written once the S product of tile i - 1 has left the buffer, its V once the PV
+    // product of tile i - 1 has.
+    const int ot = (warp - 12) * 32 + lane;      // 0..255: token row ot / 2, bytes [64 * (ot % 2), +64)
+    auto convert = [&](int kv, int i) {
+      const int st = i & 1;
+      uint64_t* full = kv == 0 ? &k_full[st] : &v_full[st];
+      uint64_t* raw_free = kv == 0 ? &k_free[st] : &v_free[st];
+      if (!mbar_wait(full, (i >> 1) & 1)) { report(p.status, kErrMmaWaitFull); return false; }
+      if (i >= 1 && !mbar_wait(kv == 0 ? kc_free : vc_free, (i - 1) & 1)) { report(p.status, kErrMmaWaitAccum); return false; }
+      const int row = ot >> 1, hb = ot & 1;
+      const uint8_t* raw = smem + (kv == 0 ? L::kK : L::kV) + st * L::kRawStage + row * 128 + hb * 64;
+      uint8_t* dst = smem + (kv == 0 ? L::kK : L::kV) + 2 * L::kRawStage + hb * kSlab;   // 64 bytes -> one 128-byte slab row
+#pragma unroll
+      for (int c16 = 0; c16 < 4; ++c16) {          // 16 e4m3 bytes -> two 16-byte chunks of fp16
+        const uint4 q = *reinterpret_cast<const uint4*>(raw + c16 * 16);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t cv[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(cv[2 * e]) : "h"(static_cast<unsigned short>(w[e] & 0xFFFFu)));
+          asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(cv[2 * e + 1]) : "h"(static_cast<unsigned short>(w[e] >> 16)));
+        }
+        *reinterpret_cast<uint4*>(dst + swz_chunk(row, 2 * c16)) = make_uint4(cv[0], cv[1], cv[2], cv[3]);
+        *reinterpret_cast<uint4*>(dst + swz_chunk(row, 2 * c16 + 1)) = make_uint4(cv[4], cv[5], cv[6], cv[7]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(kv == 0 ? kc_ready : vc_ready);
+        mbar_arrive(raw_free);
+      }
+      return true;
+    };
+    if (FP8) {
+      ok = convert(0, 0);
+      if (ok && ntiles > 1) ok = convert(0, 1);
+      if (ok) ok = convert(1, 0);
+    }
     for (int j = 0; j < ntiles && ok; ++j) {
       const int s = j & 1;
+      if (FP8 && j + 2 < ntiles && !convert(0, j + 2)) { ok = false; break; }
       if (!mbar_wait(&pv_full[s], (j >> 1) & 1)) { report(p.status, kErrEpilogueWait); ok = false; break; }
       tc_fence_after();
       const float alpha = s_alpha[s * 128 + r];
@@ -531,6 +528,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pv_free[s]);
+      if (FP8 && j + 1 < ntiles && !convert(1, j + 1)) { ok = false; break; }
     }
     if (ok && mbar_wait(l_ready, 0)) {
       const float vs = (FP8 && p.v_scale != nullptr) ? p.v_scale[kvh] : 1.f;
