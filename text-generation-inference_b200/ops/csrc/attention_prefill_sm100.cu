@@ -93,6 +93,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
   tmem_ld_wait(r);
 }
 
+// 2^x on the FMA pipe, for x <= 0: the special-function unit does 16 ex2 per cycle and SM and is the busiest
+// unit of a tile (16 K exponentials), so every kPolyEvery-th probability is computed this way instead.  Round x to
+// the nearest integer with the 1.5 * 2^23 trick, evaluate a cubic for 2^f on [-0.5, 0.5] (relative error 1.4e-4,
+// well under the 16-bit rounding of P) and add the integer to the exponent field.
+constexpr int kPolyEvery = 4;
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float r = fmaf(0.05502927f, f, 0.24225698f);
+  r = fmaf(r, f, 0.69325305f);
+  r = fmaf(r, f, 0.99995134f);
+  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
 __device__ __forceinline__ float fast_tanh(float y) {      // 1 - 2 / (1 + e^(2y)); saturates cleanly at +-1
   return 1.f - __fdividef(2.f, 1.f + fast_exp2(y * (2.f * kLog2e)));
 }
@@ -126,7 +140,9 @@ __device__ __forceinline__ float group_prob(const uint32_t (&v)[32], uint32_t (&
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const float x = __uint_as_float(v[i + e]);
-      pr[e] = CAP ? fast_exp2(a.cap_out * fast_tanh(x * a.cap_in) - m) : fast_exp2(fmaf(x, a.scale_log2, -m));
+      if (CAP) pr[e] = fast_exp2(a.cap_out * fast_tanh(x * a.cap_in) - m);
+      else if (kPolyEvery > 0 && (i + e) % kPolyEvery == 1) pr[e] = poly_exp2(fmaf(x, a.scale_log2, -m));
+      else pr[e] = fast_exp2(fmaf(x, a.scale_log2, -m));
       if (MASK) pr[e] = static_cast<unsigned>(i + e - a.lo) <= a.range ? pr[e] : 0.f;
     }
     rs0 += pr[0];
@@ -182,6 +198,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   uint64_t* pv_full = bars + 18;      // [2] PV accumulator written
   uint64_t* pv_free = bars + 20;      // [2] O warps have read it
   uint64_t* l_ready = bars + 22;      // final row sums written
+  uint64_t* q_ready = bars + 23;      // Q tile staged (18 warps)
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 24);
   float* s_alpha = reinterpret_cast<float*>(smem + L::kAlpha);
   float* s_rowsum = reinterpret_cast<float*>(smem + L::kRowSum);
@@ -189,7 +206,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::kAbort);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qt = gridDim.x - 1 - blockIdx.x;       // long tiles (late rows) first: the grid drains on short ones
   const int q_begin = p.cu_seqlens_q[b], n = p.cu_seqlens_q[b + 1] - q_begin;
   if (qt * kRows >= n) return;                       // uniform over the CTA, before anything is allocated
   const int Lkv = p.kv_lens[b];
@@ -220,6 +238,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     mbar_init(p_ready, 8);
     mbar_init(p_free, 1);
     mbar_init(l_ready, 8);
+    mbar_init(q_ready, 18);
     for (int i = 0; i < 8; ++i) s_abort[i] = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmK);
@@ -231,26 +250,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   }
   tgi::pdl_wait();
   tgi::pdl_trigger();
-  // ---- Q tile -> shared, swizzled operand layout (two slabs of 64 head elements); fp16 for e4m3 pages ----
-  for (int c = threadIdx.x; c < kRows * 16; c += blockDim.x) {
-    const int row = c >> 4, ch = c & 15;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row_base + row < n)
-      v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(q_begin + row_base + row) * p.Hq + h) * kD + ch * 8);
-    if (FP8) {
-      const __nv_bfloat162* bv = reinterpret_cast<const __nv_bfloat162*>(&v);
-      uint32_t o[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(bv[i]);
-        const __half2 hh = __floats2half2_rn(f.x, f.y);
-        o[i] = *reinterpret_cast<const uint32_t*>(&hh);
-      }
-      v = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-    *reinterpret_cast<uint4*>(smem + L::kQ + (ch >> 3) * kSlab + swz_chunk(row, ch & 7)) = v;
-  }
-  fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -304,6 +303,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       __syncwarp();
     }
   };
+  if (warp != 0 && warp != 2) {
+    // ---- Q tile -> shared, swizzled operand layout (two slabs of 64 head elements); fp16 for e4m3 pages.  The
+    // two producer warps are already fetching K and V meanwhile; the MMA issuer waits for q_ready. ----
+    const int st = (warp == 1 ? 0 : warp - 2) * 32 + lane;       // 0..575
+    for (int c = st; c < kRows * 16; c += 18 * 32) {
+      const int row = c >> 4, ch = c & 15;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row_base + row < n)
+        v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(q_begin + row_base + row) * p.Hq + h) * kD + ch * 8);
+      if (FP8) {
+        const __nv_bfloat162* bv = reinterpret_cast<const __nv_bfloat162*>(&v);
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(bv[i]);
+          const __half2 hh = __floats2half2_rn(f.x, f.y);
+          o[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        v = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      *reinterpret_cast<uint4*>(smem + L::kQ + (ch >> 3) * kSlab + swz_chunk(row, ch & 7)) = v;
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(q_ready);
+  }
   if (warp == 0) {
     produce(true, false);
   } else if (warp == 1) {
@@ -360,7 +385,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         tc_commit(FP8 ? vc_free : &v_free[s]);
         return true;
       };
-      ok = issue_qk(0);
+      ok = mbar_wait(q_ready, 0);
+      if (!ok) report(p.status, kErrMmaWaitFull);
+      ok = ok && issue_qk(0);
       for (int j = 0; j < ntiles && ok; ++j) {
         if (j + 1 < ntiles) ok = issue_qk(j + 1);      // S of the next tile overlaps the softmax of this one
         if (ok) ok = issue_pv(j);
