@@ -53,6 +53,10 @@ def parse_args():
     ap.add_argument("--fast-setup", action="store_true",
                     help="development only: fill the KV cache with random values instead of running prefill")
     ap.add_argument("--layers", type=int, default=0, help="development only: override the layer count")
+    ap.add_argument("--moe-skew", type=float, default=0.0,
+                    help="MoE models: add this bias to the router logits of experts 0 and 1 (load-imbalance case)")
+    ap.add_argument("--sampling", default="greedy", choices=["greedy", "nucleus"],
+                    help="nucleus = temperature 0.7, top-p 0.9, repetition penalty 1.1 on every request")
     return ap.parse_args()
 
 
@@ -214,6 +218,13 @@ def main():
                            kv_cache_dtype=torch.float8_e4m3fn if kv_fp8 else torch.bfloat16)
     blocks_per_seq = math.ceil(max_total / BLOCK_SIZE)
     runner.init_kv_cache(1 + C * blocks_per_seq)
+    if args.moe_skew:
+        for layer in model.layers:
+            router = getattr(layer.mlp, "router", None)
+            if router is not None:
+                bias = torch.zeros(router.weight.shape[0], dtype=router.weight.dtype, device=dev)
+                bias[:2] = args.moe_skew
+                router.bias = bias
     if kv_fp8:
         for layer in model.layers:
             layer.attn.k_scale = torch.full((model.dims.num_kv_heads,), 0.05, device=dev)
@@ -225,10 +236,14 @@ def main():
 
     def make_request(i):
         r = pb.Request(id=i, inputs="")
-        r.parameters.temperature = 1.0
-        r.parameters.top_p = 1.0
+        nucleus = args.sampling == "nucleus"
+        r.parameters.temperature = 0.7 if nucleus else 1.0
+        r.parameters.top_p = 0.9 if nucleus else 1.0
         r.parameters.typical_p = 1.0
-        r.parameters.repetition_penalty = 1.0
+        r.parameters.repetition_penalty = 1.1 if nucleus else 1.0
+        if nucleus:
+            r.parameters.do_sample = True
+            r.parameters.seed = 1000 + i
         r.stopping_parameters.max_new_tokens = O
         r.stopping_parameters.ignore_eos_token = True
         r.blocks.extend(range(1 + i * blocks_per_seq, 1 + (i + 1) * blocks_per_seq))
@@ -335,7 +350,9 @@ def main():
                        "nominal_prompt_len": P, "output_len": O,
                        "parallelism": f"tp{world}", "collectives": "none (one GPU)" if world == 1 else ("nccl" if comm is None else "peer-memory kernels"), "block_size": BLOCK_SIZE, "l2": "inputs larger than L2",
                        "timed": "CUDA events around K graph replays, max over ranks",
-                       "setup": "fast-setup (random KV, development)" if args.fast_setup else "real prefill"},
+                       "setup": "fast-setup (random KV, development)" if args.fast_setup else "real prefill",
+                       **({"moe_skew": args.moe_skew} if args.moe_skew else {}),
+                       **({"sampling": "T=0.7 top-p=0.9 rep=1.1"} if args.sampling == "nucleus" else {})},
             "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": d2h_bytes, "ms_per_step": round(api_ms / args.steps, 4),
                     "device_ms_per_step": round(api_dev_ms / args.steps, 4),

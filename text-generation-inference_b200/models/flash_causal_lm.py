@@ -85,6 +85,7 @@ class FlashCausalLMBatch(Batch):
         self.device = device
         self.speculate = speculate
         self.max_prefill_tokens: Optional[int] = None
+        self.history = None          # TokenHistory, created by the first step that needs the ids on the device
         self._reindex()
 
     def _reindex(self):
@@ -220,7 +221,20 @@ class FlashCausalLMBatch(Batch):
         out = cls(batches[0].batch_id, seqs, chooser, batches[0].device, batches[0].speculate)
         budgets = [b.max_prefill_tokens for b in batches if b.max_prefill_tokens is not None]
         out.max_prefill_tokens = min(budgets) if budgets else None
+        # rows are keyed by request id: the largest batch's device history stays valid, newcomers are uploaded
+        with_hist = [b for b in batches if b.history is not None]
+        if with_hist:
+            out.history = max(with_hist, key=len).history
         return out
+
+    def device_history(self, active: List[int]) -> torch.Tensor:
+        """``[len(active), L]`` matrix of the ids of the rows ``active`` on the device (zero padded)."""
+        from ..utils.history import TokenHistory
+
+        if self.history is None:
+            self.history = TokenHistory(self.device, rows=max(64, len(self.seqs)))
+        self.history.retain(s.request.id for s in self.seqs)
+        return self.history.sync([self.seqs[i].request.id for i in active], [self.seqs[i].ids for i in active])
 
 
 class StepStaging:
@@ -314,11 +328,7 @@ class FlashCausalLM(Model):
         v0 = self.model.head.vocab_start
         scale = float(d.logit_scale)
         if chooser.any_rep or chooser.any_freq:
-            L = max(len(seqs[i].ids) for i in active)
-            hist = np.zeros((len(active), L), dtype=np.int64)
-            for r, i in enumerate(active):
-                hist[r, :len(seqs[i].ids)] = seqs[i].ids
-            local = K.penalties(local, torch.from_numpy(hist), chooser.repetition_penalty if chooser.any_rep else None,
+            local = K.penalties(local, batch.device_history(active), chooser.repetition_penalty if chooser.any_rep else None,
                                 chooser.frequency_penalty if chooser.any_freq else None, v0, scale)
             scale = 1.0
         seeds = steps = do_sample = None
@@ -581,11 +591,7 @@ class FlashCausalLM(Model):
             if greedy_dev is not None:
                 history = None
             elif need_history:
-                L = max(len(seqs[i].ids) for i in active)
-                hist = np.zeros((len(active), L), dtype=np.int64)
-                for r, i in enumerate(active):
-                    hist[r, :len(seqs[i].ids)] = seqs[i].ids
-                history = torch.from_numpy(hist).to(logits.device)
+                history = batch.device_history(active)
             else:
                 history = torch.zeros(len(active), 1, dtype=torch.long, device=logits.device)
             want_top = any(seqs[i].top_n > 0 for i in active)

@@ -30,15 +30,18 @@ def llama_config(hidden=256, layers=2, heads=4, kv_heads=2, intermediate=688, vo
     return cfg
 
 
-def llama_state_dict(cfg: dict, seed: int = 0, std: float = 0.02, dtype=torch.float32) -> Dict[str, torch.Tensor]:
-    g = torch.Generator().manual_seed(seed)
+def llama_state_dict(cfg: dict, seed: int = 0, std: float = 0.02, dtype=torch.float32,
+                     device: str = "cpu") -> Dict[str, torch.Tensor]:
+    """Random weights of a Llama / Mixtral shape as a CPU state dict; ``device`` is where the random numbers are
+    drawn (a GPU draws a multi-billion-parameter checkpoint in seconds)."""
+    g = torch.Generator(device=device).manual_seed(seed)
     H, L = cfg["hidden_size"], cfg["num_hidden_layers"]
     nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     D = cfg.get("head_dim") or H // nh
     I, V = cfg["intermediate_size"], cfg["vocab_size"]
 
     def rnd(*shape):
-        return (torch.randn(*shape, generator=g) * std).to(dtype)
+        return (torch.randn(*shape, generator=g, device=device) * std).to(dtype).cpu()
 
     sd = {"model.embed_tokens.weight": rnd(V, H), "model.norm.weight": torch.ones(H, dtype=dtype)}
     if not cfg.get("tie_word_embeddings"):
@@ -70,12 +73,12 @@ def llama_state_dict(cfg: dict, seed: int = 0, std: float = 0.02, dtype=torch.fl
 
 
 def write_llama_checkpoint(path, cfg: Optional[dict] = None, seed: int = 0, std: float = 0.02,
-                           dtype=torch.float32) -> Path:
+                           dtype=torch.float32, device: str = "cpu") -> Path:
     cfg = cfg or llama_config()
     p = Path(path)
     p.mkdir(parents=True, exist_ok=True)
     (p / "config.json").write_text(json.dumps(cfg, indent=1))
-    save_safetensors(llama_state_dict(cfg, seed, std, dtype), p / "model.safetensors", {"format": "pt"})
+    save_safetensors(llama_state_dict(cfg, seed, std, dtype, device), p / "model.safetensors", {"format": "pt"})
     return p
 
 
