@@ -495,6 +495,7 @@ def test_image_token_counts_match_the_runners(rt):
                                            "vision_config": {"image_size": 364, "patch_size": 14}}), 10, 10) == 169
     assert rt.tokens_per_image(json.dumps({"model_type": "gemma3", "mm_tokens_per_image": 256, "boi_token_index": 1,
                                            "eoi_token_index": 2, "vision_config": {}}), 10, 10) == 258
+    assert rt.tokens_per_image(json.dumps({"model_type": "mllama", "vision_config": {"image_size": 560}}), 900, 400) == 1
     assert rt.tokens_per_image(json.dumps({"model_type": "llama"}), 10, 10) == 0
 
 

@@ -86,7 +86,12 @@ def get_model(
     loader = get_loader(quantize, path, cfg.to_dict())
     speculate = int(speculate or 0)
     tokenizer = load_tokenizer(str(path), revision, trust_remote_code, vocab_size=cfg.get("vocab_size", 259))
-    if model_type in ("llava_next", "llava", "idefics2", "idefics3", "paligemma", "qwen2_vl", "qwen2_5_vl", "mllama") or (
+    if model_type == "mllama":
+        from .mllama import load_mllama
+
+        return load_mllama(path, cfg, loader, process_group, rank, world, tdtype, device, tokenizer, speculate,
+                           kv_cache_dtype, max_prefill_tokens)
+    if model_type in ("llava_next", "llava", "idefics2", "idefics3", "paligemma", "qwen2_vl", "qwen2_5_vl") or (
             model_type == "gemma3" and cfg.get("vision_config") is not None):
         from .vlm_causal_lm import load_vlm
 

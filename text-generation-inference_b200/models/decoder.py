@@ -52,6 +52,7 @@ class ForwardMeta:
     rope_cos_sin: Optional[torch.Tensor] = None      # [T, rot_dim] rotary rows of this step (multi-axis positions)
     rope_rows: Optional[torch.Tensor] = None         # [T] = arange(T): row of `rope_cos_sin` per token
     attn_horizon: Optional[torch.Tensor] = None      # [T] last KV position a row may see (image rows: end of their image)
+    cross: Optional[object] = None                   # rows and image states for cross-attention layers (models/mllama.py)
 
 
 class Norm:
@@ -524,7 +525,13 @@ class CausalDecoder:
         from ..utils.quantization import DefaultWeightsLoader, Fp8Loader
 
         self.layers: List[DecoderLayer] = []
+        cross_layers = set(cfg.get("cross_attention_layers") or [])
         for i in range(dims.num_layers):
+            if i in cross_layers:
+                from .mllama import CrossAttentionLayer
+
+                self.layers.append(CrossAttentionLayer(a, cfg, dims, px + a.layer.format(i=i), weights, i, comm))
+                continue
             # ``--quantize fp8`` (conversion at load) keeps the first and last layer in the serving
             # dtype, as the reference does (``flash_llama_modeling.py:124-134, 549``).
             loader = weights.weights_loader

@@ -311,6 +311,10 @@ class FlashCausalLM(Model):
         item = torch.empty((), dtype=self.kv_cache_dtype).element_size()
         return 2 * d.num_layers * BLOCK_SIZE * d.num_kv_heads * (d.attn_head_dim or d.head_dim) * item
 
+    def graph_eligible(self, batch) -> bool:
+        """Runners whose step cannot be replayed for some batches (per-sequence side inputs) say so here."""
+        return True
+
     def _sample_on_shards(self, chooser, seqs, active, sample_rows, batch):
         """Vocabulary-parallel sampling after a decode graph that left only this rank's logit slice: returns
         ``(ids, logprobs)`` on the device, or ``None`` when a stage needs the whole distribution on one rank
@@ -489,7 +493,7 @@ class FlashCausalLM(Model):
         B = len(seqs)
 
         use_graph = (self.graphs is not None and not batch.prefilling and batch.speculate == 0
-                     and self.graphs.supports(batch)
+                     and self.graphs.supports(batch) and self.graph_eligible(batch)
                      # adapters ride the graphs through the LoRA kernels on one GPU; with tensor parallelism
                      # the row-parallel targets need a collective between the two kernels and stay eager
                      and not (getattr(self, "lora", None) is not None and self.world_size > 1

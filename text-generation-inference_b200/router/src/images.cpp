@@ -308,6 +308,7 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     if (config.has("eoi_token_index") || config.has("eoi_token_id")) ++n;
     return n;
   }
+  if (mt == "mllama") return 1;   // one <|image|> token; the image itself reaches the text through cross-attention
   if (mt == "idefics2") {
     // perceiver resampler: a fixed number of latents per image
     const json::Value& pc = config.has("perceiver_config") ? config["perceiver_config"] : vis;
