@@ -164,6 +164,75 @@ def test_stream_and_concurrency(stack):
         assert all(e["generated_text"] is None for e in ev[:-1])
 
 
+SNAPSHOT_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "snapshots")
+
+
+def _compare_with_snapshot(name, response, tolerance=0.02):
+    """Golden-file check in the manner of the reference's integration tests (``integration-tests/conftest.py:151-391``):
+    token ids and texts must be equal, log-probabilities within ``tolerance``.  ``TGI_B200_UPDATE_SNAPSHOTS=1``
+    rewrites the file from the current response."""
+    path = os.path.join(SNAPSHOT_DIR, name + ".json")
+    if os.environ.get("TGI_B200_UPDATE_SNAPSHOTS") == "1":
+        os.makedirs(SNAPSHOT_DIR, exist_ok=True)
+        with open(path, "w") as f:
+            json.dump(response, f, indent=1, sort_keys=True)
+    with open(path) as f:
+        want = json.load(f)
+    assert response["generated_text"] == want["generated_text"]
+    got_d, want_d = response["details"], want["details"]
+    assert got_d["finish_reason"] == want_d["finish_reason"] and got_d["generated_tokens"] == want_d["generated_tokens"]
+    for key in ("prefill", "tokens"):
+        assert len(got_d[key]) == len(want_d[key])
+        for g, w in zip(got_d[key], want_d[key]):
+            assert g["id"] == w["id"] and g["text"] == w["text"], (key, g, w)
+            if w["logprob"] is None:
+                assert g["logprob"] is None
+            else:
+                assert abs(g["logprob"] - w["logprob"]) <= tolerance, (key, g, w)
+    for g_row, w_row in zip(got_d.get("top_tokens") or [], want_d.get("top_tokens") or []):
+        assert [t["id"] for t in g_row] == [t["id"] for t in w_row]
+
+
+def test_greedy_response_matches_the_golden_snapshot(stack):
+    st, _, body = _post(stack["port"], "/generate", {
+        "inputs": "What is deep learning?", "parameters": {"max_new_tokens": 10, "details": True,
+                                                           "decoder_input_details": True, "top_n_tokens": 3}})
+    assert st == 200, body
+    _compare_with_snapshot("tiny_llama_greedy", json.loads(body))
+
+
+def test_sampled_response_matches_the_golden_snapshot(stack):
+    st, _, body = _post(stack["port"], "/generate", {
+        "inputs": "What is deep learning?", "parameters": {"max_new_tokens": 10, "details": True, "do_sample": True,
+                                                           "temperature": 0.7, "top_p": 0.9, "top_k": 40, "seed": 7,
+                                                           "repetition_penalty": 1.2}})
+    assert st == 200, body
+    _compare_with_snapshot("tiny_llama_sampled", json.loads(body))
+
+
+def test_identical_concurrent_requests_agree(stack):
+    """The reference's ``*_load`` pattern: the same request sent four times at once is batched with itself (and
+    shares prefix blocks) and every copy must come back identical."""
+    import threading
+
+    body = {"inputs": "The quick brown fox", "parameters": {"max_new_tokens": 12, "details": True}}
+    out = [None] * 4
+
+    def run(i):
+        out[i] = json.loads(_post(stack["port"], "/generate", body)[2])
+
+    ts = [threading.Thread(target=run, args=(i,)) for i in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    first = out[0]
+    assert first["details"]["generated_tokens"] == 12
+    for o in out[1:]:
+        assert o["generated_text"] == first["generated_text"]
+        assert [t["id"] for t in o["details"]["tokens"]] == [t["id"] for t in first["details"]["tokens"]]
+        for a, b in zip(o["details"]["tokens"], first["details"]["tokens"]):
+            assert abs(a["logprob"] - b["logprob"]) <= 1e-3
+
+
 def test_chat_completions(stack):
     st, _, body = _post(stack["port"], "/v1/chat/completions", {
         "model": "tgi", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0, "logprobs": True})
