@@ -299,6 +299,33 @@ class DenseMLP:
         return out
 
 
+def _expert_weight(weights, cfg, name: str, dim: Optional[int] = None) -> torch.Tensor:
+    """One expert projection (``name`` without ``.weight``), whole (``dim=None``) or this rank's slice along ``dim``,
+    in the serving dtype.  Experts of fp8 checkpoints — 128 x 128 ``weight_scale_inv`` blocks, or a per-tensor /
+    per-channel ``weight_scale`` — are dequantised here: the grouped expert GEMM (``ops/csrc/moe_sm100.cu``) runs in
+    bf16, where the reference keeps such experts in fp8 (``layers/moe/fp8.py:20-92``)."""
+    from ..utils.weights import shard_bounds
+
+    fp8 = getattr(torch, "float8_e4m3fn", None)
+    full = weights.get_tensor(f"{name}.weight", to_dtype=False)
+    if fp8 is None or full.dtype != fp8:
+        return weights.get_tensor(f"{name}.weight") if dim is None else weights.get_sharded(f"{name}.weight", dim=dim)
+    N, K = full.shape
+    if weights.has_tensor(f"{name}.weight_scale_inv"):
+        q = cfg.get("quantization_config") or {}
+        blk = list(q.get("weight_block_size") or [128, 128])
+        s = weights.get_tensor(f"{name}.weight_scale_inv", to_dtype=False).float()
+        s = s.repeat_interleave(blk[0], 0)[:N].repeat_interleave(blk[1], 1)[:, :K]
+    else:
+        s = weights.get_tensor(f"{name}.weight_scale", to_dtype=False).float()
+        s = s.reshape(-1, 1) if s.numel() > 1 else s.reshape(1, 1)
+    w = (full.float() * s.to(full.device)).to(weights.dtype)
+    if dim is not None:
+        lo, hi = shard_bounds(w.shape[dim], weights.process_group.rank(), weights.process_group.size())
+        w = w.narrow(dim, lo, hi - lo).contiguous()
+    return w
+
+
 class SparseMoE:
     """Top-k routed experts.  Tensor-parallel mode slices every expert's intermediate dimension
     (what the reference does, ``layers/moe/unquantized.py:107-163``); expert-parallel mode
@@ -327,9 +354,9 @@ class SparseMoE:
             lo, hi = local_expert_range(E, pg.rank(), pg.size())
             for e in range(lo, hi):
                 ep = f"{prefix}.{arch.moe_expert.format(e=e)}"
-                gu.append(torch.cat([weights.get_tensor(f"{ep}.{arch.moe_gate}.weight"),
-                                     weights.get_tensor(f"{ep}.{arch.moe_up}.weight")], dim=0))
-                dn.append(weights.get_tensor(f"{ep}.{arch.moe_down}.weight"))
+                gu.append(torch.cat([_expert_weight(weights, cfg, f"{ep}.{arch.moe_gate}"),
+                                     _expert_weight(weights, cfg, f"{ep}.{arch.moe_up}")], dim=0))
+                dn.append(_expert_weight(weights, cfg, f"{ep}.{arch.moe_down}"))
             self.w_gate_up = torch.stack(gu).contiguous()   # [E / world, 2I, H]
             self.w_down = torch.stack(dn).contiguous()       # [E / world, H, I]
             self.expert_parallel = ExpertParallel(self.w_gate_up, self.w_down, lo, self.act)
@@ -346,10 +373,10 @@ class SparseMoE:
         else:
             for e in range(E):
                 ep = f"{prefix}.{arch.moe_expert.format(e=e)}"
-                g = weights.get_sharded(f"{ep}.{arch.moe_gate}.weight", dim=0)
-                u = weights.get_sharded(f"{ep}.{arch.moe_up}.weight", dim=0)
+                g = _expert_weight(weights, cfg, f"{ep}.{arch.moe_gate}", dim=0)
+                u = _expert_weight(weights, cfg, f"{ep}.{arch.moe_up}", dim=0)
                 gu.append(torch.cat([g, u], dim=0))
-                dn.append(weights.get_sharded(f"{ep}.{arch.moe_down}.weight", dim=1))
+                dn.append(_expert_weight(weights, cfg, f"{ep}.{arch.moe_down}", dim=1))
             self.w_gate_up = torch.stack(gu).contiguous()   # [E, 2I/tp, H]
             self.w_down = torch.stack(dn).contiguous()       # [E, H, I/tp]
         self.shared = None

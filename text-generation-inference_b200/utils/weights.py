@@ -150,7 +150,7 @@ def serialize_safetensors(tensors: Dict[str, torch.Tensor], metadata: Optional[D
     off = 0
     for name in sorted(tensors):
         t = tensors[name].detach().contiguous().cpu()
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _ST_NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         chunks.append(raw)
         off += len(raw)
