@@ -273,3 +273,29 @@ def test_library_is_native():
     assert out.shape == x.shape
     with open("/proc/self/maps") as f:
         assert "libtgi_b200_kernels.so" in f.read()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layer,unit_offset,D", [(False, False, 128), (False, True, 256), (True, False, 128), (False, False, 64)])
+def test_qk_norm_per_head(layer, unit_offset, D):
+    """q / k heads of a fused qkv row normalised in place: RMSNorm with a weight shared by the heads (Qwen3,
+    Gemma-3 with the unit offset) and bias-free LayerNorm with per-head weights (Cohere); v is left alone."""
+    from tgi_b200.ops import cuda as K
+
+    torch.manual_seed(5)
+    T, nh, nkv = 37, 6, 2
+    qkv = (torch.randn(T, (nh + 2 * nkv) * D, device="cuda") * 3).to(torch.bfloat16)
+    qw = (torch.randn(nh, D, device="cuda") if layer else torch.randn(D, device="cuda")).to(torch.bfloat16)
+    kw = (torch.randn(nkv, D, device="cuda") if layer else torch.randn(D, device="cuda")).to(torch.bfloat16)
+    ref = qkv.clone().float().view(T, nh + 2 * nkv, D)
+    for lo, hi, w in ((0, nh, qw), (nh, nh + nkv, kw)):
+        x = ref[:, lo:hi]
+        if layer:
+            y = (x - x.mean(-1, keepdim=True)) * torch.rsqrt(x.var(-1, unbiased=False, keepdim=True) + 1e-6) * w.float()
+        else:
+            y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * (w.float() + (1.0 if unit_offset else 0.0))
+        ref[:, lo:hi] = y
+    out = K.qk_norm(qkv.clone(), nh, nkv, D, qw, kw, 1e-6, unit_offset, layer=layer).float().view(T, nh + 2 * nkv, D)
+    assert torch.equal(out[:, nh + nkv:], qkv.float().view(T, nh + 2 * nkv, D)[:, nh + nkv:])
+    err = (out - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item(), err

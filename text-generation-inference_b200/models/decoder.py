@@ -199,6 +199,12 @@ class Attention:
     def _qk_norm(self, qkv: torch.Tensor) -> torch.Tensor:
         d = self.dims
         T = qkv.shape[0]
+        if qkv.is_cuda and qkv.dtype == torch.bfloat16 and d.head_dim <= 256 and d.head_dim % 2 == 0:
+            from ..ops import cuda as K
+
+            return K.qk_norm(qkv, d.num_heads, d.num_kv_heads, d.head_dim, self.q_norm, self.k_norm, d.eps,
+                             self.arch.qk_norm_kind == "rms" and self.arch.norm_unit_offset,
+                             layer=self.arch.qk_norm_kind != "rms")
         nq, nk = d.num_heads * d.head_dim, d.num_kv_heads * d.head_dim
         q = qkv[:, :nq].reshape(T, d.num_heads, d.head_dim)
         k = qkv[:, nq:nq + nk].reshape(T, d.num_kv_heads, d.head_dim)

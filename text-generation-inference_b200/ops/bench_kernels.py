@@ -168,6 +168,48 @@ def main():
         gu = torch.randn(M, 2 * I, device=dev, dtype=torch.bfloat16)
         t = timer(lambda: K.act_and_mul_quant(gu))
         report(f"act_mul_quant[{M}x{I}]", t, M * I * 5)
+    if want("sample"):
+        V = s["vocab"] // args.tp
+        logits = torch.randn(M, V, device=dev, dtype=torch.bfloat16) * 3
+        temp = torch.full((M,), 0.7, device=dev)
+        top_p = torch.full((M,), 0.9, device=dev)
+        top_k = torch.full((M,), 40, device=dev, dtype=torch.int32)
+        ds = torch.ones(M, device=dev, dtype=torch.uint8)
+        seeds = torch.arange(M, device=dev, dtype=torch.int64)
+        steps = torch.zeros(M, device=dev, dtype=torch.int32)
+        t = timer(lambda: K.fused_sample(logits, temp, top_k, top_p, ds, seeds, steps))
+        report(f"fused_sample[{M}x{V} T,top-k,top-p]", t, 2 * M * V)
+        hist = torch.randint(0, V, (M, args.ctx), device=dev, dtype=torch.int64)
+        rep = torch.full((M,), 1.1, device=dev)
+        t = timer(lambda: K.penalties(logits, hist, rep, None))
+        report(f"penalties[{M}x{V}, history {args.ctx}]", t, M * V * (2 + 4) + M * args.ctx * 8)
+        del logits, hist
+    if want("moe"):
+        # Mixtral-8x7B experts: 8 experts of [2 x 14336, 4096] / [4096, 14336], top-2 routing
+        E, Hm, Im, topk = 8, 4096, 14336 // args.tp, 2
+        x = torch.randn(M, Hm, device=dev, dtype=torch.bfloat16)
+        wgu = torch.randn(E, 2 * Im, Hm, device=dev, dtype=torch.bfloat16) * 0.02
+        wd = torch.randn(E, Hm, Im, device=dev, dtype=torch.bfloat16) * 0.02
+        router = torch.randn(M, E, device=dev, dtype=torch.bfloat16)
+        wts, ids = K.moe_topk_softmax(router, topk)
+        t = timer(lambda: K.moe_experts(x, wgu, wd, wts, ids, "silu"))
+        touched = min(E, M * topk)
+        report(f"moe_experts[{M} tokens, {E} experts top-{topk}, I={Im}]", t, 2 * touched * 3 * Im * Hm, 2.0 * M * topk * 3 * Im * Hm)
+        t = timer(lambda: K.moe_topk_softmax(router, topk))
+        report(f"moe_topk_softmax[{M}x{E}]", t, M * E * 2 + M * topk * 8)
+        del x, wgu, wd
+    if want("wq"):
+        # 4-bit weights, group 128 (GPTQ / AWQ after the canonical repack): the gate_up projection
+        N4, K4, group = 2 * I, H, 128
+        x = torch.randn(M, K4, device=dev, dtype=torch.bfloat16)
+        wq = torch.randint(0, 256, (N4, K4 // 2), device=dev, dtype=torch.uint8)
+        sc = (torch.rand(K4 // group, N4, device=dev) * 0.01 + 0.005).to(torch.float16)
+        zp = torch.full((K4 // group, N4), 8.0, device=dev, dtype=torch.float16)
+        for m in sorted({min(M, 16), M}):
+            xm = x[:m].contiguous()
+            t = timer(lambda: K.gemm_wq(xm, wq, sc, zp, group, 4))
+            report(f"gemm_wq4[{m}x{N4}x{K4}]", t, N4 * K4 // 2 + 4 * (K4 // group) * N4 + 2 * m * (K4 + N4), 2.0 * m * N4 * K4)
+        del x, wq, sc, zp
     bs = 16
     nb_seq = math.ceil((args.ctx + 1) / bs)
     nblocks = M * nb_seq + 1

@@ -641,9 +641,68 @@ penalties_kernel(const T* __restrict__ logits, long long in_stride, float* __res
   }
 }
 
+
+// Per-head normalisation of the q and k heads of a fused qkv row, in place (Qwen3, Gemma-3, OLMoE-style RMSNorm
+// over head_dim; Cohere-style LayerNorm without bias).  One warp per (token, head); the weight is [D] shared by all
+// heads (head_stride 0) or [heads, D].  Replaces, in the reference, the q_norm / k_norm modules applied to the
+// reshaped projections (custom_modeling/flash_qwen3_modeling.py, flash_gemma3_modeling.py, flash_cohere_modeling.py).
+__global__ void __launch_bounds__(256) qk_norm_kernel(__nv_bfloat16* qkv, long long row_stride, int T, int nh, int nkv, int D,
+                                                      const __nv_bfloat16* qw, const __nv_bfloat16* kw, int q_head_stride,
+                                                      int k_head_stride, float eps, float w_offset, int layer) {
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int heads = nh + nkv;
+  if (unit >= static_cast<long long>(T) * heads) return;
+  const int t = static_cast<int>(unit / heads), hd = static_cast<int>(unit % heads);
+  const bool is_q = hd < nh;
+  __nv_bfloat162* row = reinterpret_cast<__nv_bfloat162*>(qkv + t * row_stride + static_cast<long long>(hd) * D);
+  const __nv_bfloat16* w = is_q ? qw + static_cast<long long>(hd) * q_head_stride : kw + static_cast<long long>(hd - nh) * k_head_stride;
+  const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(w);
+  const int pairs = D >> 1;
+  float2 v[4];                      // D <= 256
+  float sum = 0.f, sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p = lane + i * 32;
+    v[i] = p < pairs ? __bfloat1622float2(row[p]) : make_float2(0.f, 0.f);
+    sum += v[i].x + v[i].y;
+    sq += v[i].x * v[i].x + v[i].y * v[i].y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  }
+  const float mean = layer ? sum / D : 0.f;
+  const float var = layer ? fmaxf(sq / D - mean * mean, 0.f) : sq / D;
+  const float inv = rsqrtf(var + eps);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p = lane + i * 32;
+    if (p < pairs) {
+      const float2 g = __bfloat1622float2(w2[p]);
+      row[p] = __floats2bfloat162_rn((v[i].x - mean) * inv * (g.x + w_offset), (v[i].y - mean) * inv * (g.y + w_offset));
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+// qkv bf16 [T, row_stride]: heads 0..nh-1 are q, nh..nh+nkv-1 are k, each D wide; weights bf16
+int tgi_qk_norm(void* qkv, long long row_stride, int T, int nh, int nkv, int D, const void* qw, const void* kw,
+                int q_head_stride, int k_head_stride, float eps, float w_offset, int layer, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D % 2 != 0 || D > 256 || row_stride % 2 != 0) return -10;
+  const long long units = static_cast<long long>(T) * (nh + nkv);
+  tgi::launch(qk_norm_kernel, dim3(static_cast<unsigned>((units + 7) / 8)), dim3(256), 0, stream,
+              static_cast<__nv_bfloat16*>(qkv), row_stride, T, nh, nkv, D, static_cast<const __nv_bfloat16*>(qw),
+              static_cast<const __nv_bfloat16*>(kw), q_head_stride, k_head_stride, eps, w_offset, layer);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 // scores[B, V] (fp32) = penalised(logits[B, V] * logit_scale); history int64 [B, L]; rep / freq fp32 [B] or null
 int tgi_penalties(const void* logits, int is_fp32, long long in_stride, float* scores, long long out_stride,

@@ -52,7 +52,7 @@ def load():
                  "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention", "tgi_paged_attention_ex",
                  "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status", "tgi_lora_shrink",
                  "tgi_lora_expand", "tgi_moe_topk_softmax", "tgi_moe_sort", "tgi_moe_gather", "tgi_moe_grouped_gemm",
-                 "tgi_moe_combine", "tgi_gemm_last_grid", "tgi_penalties", "tgi_gemm_wq", "tgi_wq_dequant"):
+                 "tgi_moe_combine", "tgi_gemm_last_grid", "tgi_penalties", "tgi_gemm_wq", "tgi_wq_dequant", "tgi_qk_norm"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
     wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
@@ -257,6 +257,21 @@ def rms_norm_quant(x, residual, weight, eps, unit_offset=False):
 def layer_norm(x, residual, weight, bias, eps):
     out, _, _, res = _norm(x, residual, weight, bias, eps, 0.0, True, False)
     return out, res
+
+
+def qk_norm(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, q_weight: torch.Tensor,
+            k_weight: torch.Tensor, eps: float, unit_offset: bool = False, layer: bool = False) -> torch.Tensor:
+    """Per-head RMSNorm (or bias-free LayerNorm) of the q and k heads of ``qkv[T, (nh + 2 nkv) D]``, in place.  The
+    weights are ``[D]`` (shared by the heads) or ``[heads, D]``."""
+    lib = load()
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
+    qw = q_weight.to(torch.bfloat16).contiguous()
+    kw = k_weight.to(torch.bfloat16).contiguous()
+    _check(lib.tgi_qk_norm(_ptr(qkv), c_ll(qkv.stride(0)), c_int(qkv.shape[0]), c_int(num_heads), c_int(num_kv_heads),
+                           c_int(head_dim), _ptr(qw), _ptr(kw), c_int(head_dim if qw.dim() > 1 else 0),
+                           c_int(head_dim if kw.dim() > 1 else 0), ctypes.c_float(eps),
+                           ctypes.c_float(1.0 if unit_offset else 0.0), c_int(1 if layer else 0), _stream()), "qk_norm")
+    return qkv
 
 
 # ---- activation --------------------------------------------------------------------------------
