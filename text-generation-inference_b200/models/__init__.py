@@ -86,6 +86,10 @@ def get_model(
     loader = get_loader(quantize, path, cfg.to_dict())
     speculate = int(speculate or 0)
     tokenizer = load_tokenizer(str(path), revision, trust_remote_code, vocab_size=cfg.get("vocab_size", 259))
+    if model_type == "idefics":
+        from .idefics import load_idefics
+
+        return load_idefics(path, cfg, process_group, rank, world, tdtype, device, tokenizer)
     if model_type == "mllama":
         from .mllama import load_mllama
 

@@ -308,6 +308,7 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     if (config.has("eoi_token_index") || config.has("eoi_token_id")) ++n;
     return n;
   }
+  if (mt == "idefics") return 3;  // <fake_token_around_image><image><fake_token_around_image>; cross-attention carries the image
   if (mt == "mllama") return 1;   // one <|image|> token; the image itself reaches the text through cross-attention
   if (mt == "idefics2") {
     // perceiver resampler: a fixed number of latents per image
