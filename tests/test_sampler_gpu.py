@@ -161,3 +161,35 @@ def test_sharded_sampler_with_one_rank_equals_the_fused_sampler():
             ok = ids == want_ids
             assert (lps[ok] - want_lp[ok]).abs().max().item() < 2e-3
     comm.close()
+
+
+def test_typical_p_support_matches_the_torch_filter():
+    """Typical-p after top-k: every draw must lie in the set the sort-based filter keeps, the log-probability is
+    the renormalised one over that set, and greedy rows take the best kept entry."""
+    from tgi_b200 import ops
+    from tgi_b200.utils.tokens import top_k_filter, typical_p_filter
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    B, V = 48, 5003
+    scores = torch.randn(B, V, device=dev, generator=g) * 2.5
+    temperature = torch.rand(B, device=dev, generator=g) + 0.5
+    top_k = torch.randint(0, 400, (B,), device=dev, generator=g, dtype=torch.int32)
+    top_k[::3] = 0
+    typical = torch.rand(B, device=dev, generator=g) * 0.7 + 0.2
+    typical[::6] = 1.0
+    do_sample = torch.ones(B, dtype=torch.uint8, device=dev)
+    do_sample[::4] = 0
+    seeds = torch.arange(B, device=dev, dtype=torch.int64) + 100
+    want = typical_p_filter(top_k_filter(scores / temperature.view(-1, 1), top_k), typical)
+    want_lp = torch.log_softmax(want, -1)
+    kept = torch.isfinite(want)
+    assert (kept.sum(-1) < V).any() and (kept.sum(-1) > 1).any()
+    for step in range(6):
+        steps = torch.full((B,), step, dtype=torch.int32, device=dev)
+        ids, lps = ops.fused_sample(scores, temperature, top_k, None, do_sample, seeds, steps, typical_p=typical)
+        torch.cuda.synchronize()
+        assert kept.gather(1, ids.view(-1, 1)).all(), "a draw lies outside the typical set"
+        assert (lps - want_lp.gather(1, ids.view(-1, 1)).view(-1)).abs().max().item() < 3e-3
+        greedy = do_sample == 0
+        assert torch.equal(ids[greedy], want.argmax(-1)[greedy])

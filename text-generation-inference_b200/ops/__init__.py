@@ -141,9 +141,9 @@ def has_fused_sample(scores) -> bool:
     return use_native(scores)
 
 
-def fused_sample(scores, temperature=None, top_k=None, top_p=None, do_sample=None, seeds=None, steps=None):
-    """One-kernel temperature / top-k / top-p / sampling on CUDA tensors (see ``ops.cuda.fused_sample``)."""
-    return native().fused_sample(scores, temperature, top_k, top_p, do_sample, seeds, steps)
+def fused_sample(scores, temperature=None, top_k=None, top_p=None, do_sample=None, seeds=None, steps=None, typical_p=None):
+    """One-kernel temperature / top-k / top-p / typical-p / sampling on CUDA tensors (see ``ops.cuda.fused_sample``)."""
+    return native().fused_sample(scores, temperature, top_k, top_p, do_sample, seeds, steps, typical_p=typical_p)
 
 
 def penalties(scores, history, repetition_penalty=None, frequency_penalty=None):

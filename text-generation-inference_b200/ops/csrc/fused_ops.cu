@@ -512,10 +512,52 @@ __device__ uint32_t find_threshold(const T* __restrict__ row, int V, float inv_t
   return lo;
 }
 
+// Typical-p (utils/logits_process.py:389-448): over the entries the earlier filters kept, with p_j their
+// renormalised probabilities and H their entropy, keep the entries with the smallest |-log p_j - H| whose mass
+// reaches `mass`.  Returns the largest kept deviation as float bits (deviations are >= 0, so their bit patterns
+// order like the values); found by bisection, no sort.
+template <typename T>
+__device__ uint32_t typical_threshold(const T* __restrict__ row, int V, float inv_t, float m, uint32_t keep_from, float mass,
+                                      float* red, float* log_z_out, float* entropy_out) {
+  float z = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float x = static_cast<float>(row[i]) * inv_t;
+    if (order_bits(x) >= keep_from && x != -INFINITY) z += __expf(x - m);
+  }
+  const float log_z = __logf(block_sum(z, red));
+  float h = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float x = static_cast<float>(row[i]) * inv_t;
+    if (order_bits(x) >= keep_from && x != -INFINITY) {
+      const float lp = x - m - log_z;
+      h -= __expf(lp) * lp;
+    }
+  }
+  const float H = block_sum(h, red);
+  *log_z_out = log_z;
+  *entropy_out = H;
+  uint32_t lo = 0u, hi = 0x7f800000u;       // predicate "mass of deviations <= t reaches `mass`": true at +inf
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1);
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float x = static_cast<float>(row[i]) * inv_t;
+      if (order_bits(x) >= keep_from && x != -INFINITY) {
+        const float lp = x - m - log_z;
+        if (__float_as_uint(fabsf(-lp - H)) <= mid) acc += __expf(lp);
+      }
+    }
+    if (block_sum(acc, red) >= mass) hi = mid;
+    else lo = mid + 1;
+  }
+  return lo;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(1024)
 sample_kernel(const T* __restrict__ scores, long long row_stride, const float* __restrict__ temperature,
-              const int* __restrict__ top_k, const float* __restrict__ top_p, const unsigned char* __restrict__ do_sample,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ typical_p,
+              const unsigned char* __restrict__ do_sample,
               const long long* __restrict__ seeds, const int* __restrict__ steps, long long* __restrict__ ids,
               float* __restrict__ logprob, int V) {
   tgi::pdl_wait();      // inputs come from earlier kernels of the stream
@@ -554,6 +596,10 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
     const uint32_t t = find_threshold<T, true>(row, V, inv_t, m, p * z, keep_from, red);
     keep_from = max(keep_from, t);
   }
+  const float typ = typical_p != nullptr ? typical_p[b] : 1.f;
+  uint32_t typ_bits = 0xffffffffu;
+  float typ_log_z = 0.f, typ_h = 0.f;
+  if (typ < 1.f) typ_bits = typical_threshold<T>(row, V, inv_t, m, keep_from, typ, red, &typ_log_z, &typ_h);
   // ---- sample over the kept set ----
   const bool sample = do_sample != nullptr && do_sample[b] != 0;
   const uint64_t seed = seeds != nullptr ? static_cast<uint64_t>(seeds[b]) : 0ull;
@@ -563,6 +609,7 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     const float x = static_cast<float>(row[i]) * inv_t;
     if (order_bits(x) < keep_from || x == -INFINITY) continue;
+    if (typ < 1.f && __float_as_uint(fabsf(-(x - m - typ_log_z) - typ_h)) > typ_bits) continue;
     z += __expf(x - m);
     const float key = sample ? x + gumbel_noise(static_cast<uint32_t>(i), step, seed) : x;
     if (key > best) {
@@ -828,16 +875,16 @@ int tgi_argmax_logprob(const void* logits, long long* ids, float* logprob, int B
 // Fused temperature / top-k / top-p / sampling; any of temperature, top_k, top_p, do_sample, seeds, steps may be
 // null (stage off).  `is_fp32` selects the element type of `scores`.
 int tgi_sample(const void* scores, long long row_stride, int is_fp32, const float* temperature, const int* top_k,
-               const float* top_p, const unsigned char* do_sample, const long long* seeds, const int* steps,
-               long long* ids, float* logprob, int B, int V, cudaStream_t stream) {
+               const float* top_p, const float* typical_p, const unsigned char* do_sample, const long long* seeds,
+               const int* steps, long long* ids, float* logprob, int B, int V, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (V <= 0) return -10;
   if (is_fp32)
     tgi::launch(sample_kernel<float>, dim3(B), dim3(1024), 0, stream, static_cast<const float*>(scores), row_stride, temperature, top_k, top_p,
-                                                 do_sample, seeds, steps, ids, logprob, V);
+                                                 typical_p, do_sample, seeds, steps, ids, logprob, V);
   else
     tgi::launch(sample_kernel<__nv_bfloat16>, dim3(B), dim3(1024), 0, stream, static_cast<const __nv_bfloat16*>(scores), row_stride, temperature,
-                                                         top_k, top_p, do_sample, seeds, steps, ids, logprob, V);
+                                                         top_k, top_p, typical_p, do_sample, seeds, steps, ids, logprob, V);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -391,7 +391,8 @@ def argmax_logprob(logits):
     return ids, lp
 
 
-def fused_sample(scores: torch.Tensor, temperature=None, top_k=None, top_p=None, do_sample=None, seeds=None, steps=None):
+def fused_sample(scores: torch.Tensor, temperature=None, top_k=None, top_p=None, do_sample=None, seeds=None, steps=None,
+                 typical_p=None):
     """Temperature, top-k, top-p and sampling (Gumbel-max with a counter-based generator keyed by the
     request's seed and step) in one kernel; returns ``(ids int64 [B], logprobs fp32 [B])``.  Any stage
     whose tensor is ``None`` is off; rows with ``do_sample == 0`` take the argmax of the filtered scores."""
@@ -408,11 +409,12 @@ def fused_sample(scores: torch.Tensor, temperature=None, top_k=None, top_p=None,
         return None if t is None else t.to(device=dev, dtype=dtype).contiguous()
 
     temperature, top_p = as_(temperature, torch.float32), as_(top_p, torch.float32)
+    typical_p = as_(typical_p, torch.float32)
     top_k, steps = as_(top_k, torch.int32), as_(steps, torch.int32)
     do_sample, seeds = as_(do_sample, torch.uint8), as_(seeds, torch.int64)
     _check(lib.tgi_sample(_ptr(scores), c_ll(scores.stride(0)), c_int(1 if scores.dtype == torch.float32 else 0),
-                          _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(do_sample), _ptr(seeds), _ptr(steps),
-                          _ptr(ids), _ptr(lps), c_int(B), c_int(V), _stream()), "sample")
+                          _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(typical_p), _ptr(do_sample), _ptr(seeds),
+                          _ptr(steps), _ptr(ids), _ptr(lps), c_int(B), c_int(V), _stream()), "sample")
     return ids, lps
 
 

@@ -238,8 +238,7 @@ class NextTokenChooser:
         """
         S = 1 if speculated_ids is None else speculated_ids.shape[1] + 1
         B = scores.shape[0] // S
-        if (S == 1 and not need_logprobs and speculate == 0 and speculative_scores is None and not self.any_typical
-                and scores.is_cuda):
+        if S == 1 and not need_logprobs and speculate == 0 and speculative_scores is None and scores.is_cuda:
             from .. import ops
 
             if ops.has_fused_sample(scores):
@@ -287,8 +286,8 @@ class NextTokenChooser:
 
     def _fused(self, input_ids: torch.Tensor, scores: torch.Tensor):
         """CUDA fast path: stages that need the token history or an automaton run in torch on a float
-        copy (only when active), then temperature / top-k / top-p / sampling / log-probability are one
-        kernel launch for the whole batch (``ops.fused_sample``)."""
+        copy (only when active), then temperature / top-k / top-p / typical-p / sampling / log-probability are
+        one kernel launch for the whole batch (``ops.fused_sample``)."""
         from .. import ops
 
         if (self.any_rep or self.any_freq) and not self.watermarks and self.grammar is None and hasattr(ops, "penalties"):
@@ -316,7 +315,8 @@ class NextTokenChooser:
             self.steps = [st + (1 if d else 0) for st, d in zip(self.steps, self.do_sample_list)]
         next_ids, next_logprobs = ops.fused_sample(
             scores, self.temperature if self.any_temperature else None, self.top_k if self.any_top_k else None,
-            self.top_p if self.any_top_p else None, do_sample, seeds, steps)
+            self.top_p if self.any_top_p else None, do_sample, seeds, steps,
+            typical_p=self.typical_p if self.any_typical else None)
         return next_ids, next_logprobs, None, torch.ones_like(next_ids), None
 
     def advance_grammar(self, next_ids: List[int]):
