@@ -367,6 +367,9 @@ def test_load_generator_against_the_stack(stack):
                           "--prompt-len", "8:40", "--output-len", "5"])
     assert len(res) == 1 and res[0]["failed"] == 0 and res[0]["output_tok_s"] > 0
     assert res[0]["ttft_ms"]["p50"] > 0 and res[0]["itl_ms"]["p50"] > 0
+    closed = load_test.main(["--url", f"http://127.0.0.1:{stack['port']}", "--concurrency", "1,3", "--requests", "6",
+                             "--prompt-len", "8:40", "--output-len", "4"])
+    assert [r["concurrency"] for r in closed] == [1, 3] and all(r["failed"] == 0 for r in closed)
 
 
 def test_kserve_routes(stack):

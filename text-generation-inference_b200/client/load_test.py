@@ -8,6 +8,7 @@ are recorded.  Prints one JSON document per arrival rate:
 
     python -m tgi_b200.client.load_test --url http://127.0.0.1:3000 --rates 1,4,16 --requests 256 \
         --prompt-len 128:2048 --output-len 256
+    python -m tgi_b200.client.load_test --url http://127.0.0.1:3000 --concurrency 1,8,32 --requests 64   # closed loop
 """
 from __future__ import annotations
 
@@ -94,10 +95,42 @@ async def run_rate(url: str, rate: float, n_requests: int, prompt_chars: Tuple[i
             "e2e_s": {k: round(v, 3) for k, v in summarize(e2e).items()}}
 
 
+async def run_closed_loop(url: str, concurrency: int, n_requests: int, prompt_chars: Tuple[int, int], output_len: int,
+                          seed: int) -> Dict:
+    """``concurrency`` virtual users, each sending its next request as soon as the previous one finished (the
+    constant-VU scenario of the reference's k6 scripts, ``load_tests/common.js``)."""
+    import aiohttp
+
+    rng = random.Random(seed)
+    prompts = [random_prompt(rng, rng.randint(*prompt_chars)) for _ in range(n_requests)]
+    results = []
+    cursor = 0
+
+    async def user(session):
+        nonlocal cursor
+        while cursor < len(prompts):
+            i = cursor
+            cursor += 1
+            results.append(await one_request(session, url, prompts[i], output_len))
+
+    conn = aiohttp.TCPConnector(limit=concurrency + 8)
+    async with aiohttp.ClientSession(connector=conn, timeout=aiohttp.ClientTimeout(total=None)) as session:
+        start = time.perf_counter()
+        await asyncio.gather(*[user(session) for _ in range(concurrency)])
+        wall = time.perf_counter() - start
+    ok = [r for r in results if r[4]]
+    return {"concurrency": concurrency, "requests": n_requests, "failed": len(results) - len(ok),
+            "wall_s": round(wall, 3), "output_tok_s": round(sum(r[3] for r in results) / wall, 2),
+            "ttft_ms": {k: round(v * 1e3, 2) for k, v in summarize([r[0] for r in ok]).items()},
+            "itl_ms": {k: round(v * 1e3, 2) for k, v in summarize([g for r in ok for g in r[1]]).items()},
+            "e2e_s": {k: round(v, 3) for k, v in summarize([r[2] for r in ok]).items()}}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--url", default="http://127.0.0.1:3000")
     ap.add_argument("--rates", default="1,2,4,8,16,32,64", help="arrival rates to sweep, requests per second")
+    ap.add_argument("--concurrency", default="", help="closed loop instead: numbers of concurrent users to sweep, e.g. 1,8,32")
     ap.add_argument("--requests", type=int, default=1024)
     ap.add_argument("--prompt-len", default="128:2048", help="min:max prompt length in characters")
     ap.add_argument("--output-len", type=int, default=256)
@@ -107,6 +140,12 @@ def main(argv=None):
     lo, _, hi = args.prompt_len.partition(":")
     chars = (int(lo), int(hi or lo))
     out = []
+    for users in [int(x) for x in args.concurrency.split(",") if x]:
+        res = asyncio.run(run_closed_loop(args.url.rstrip("/"), users, args.requests, chars, args.output_len, args.seed))
+        print(json.dumps(res), flush=True)
+        out.append(res)
+    if args.concurrency:
+        return out
     for rate in [float(x) for x in args.rates.split(",") if x]:
         res = asyncio.run(run_rate(args.url.rstrip("/"), rate, args.requests, chars, args.output_len, args.seed,
                                    args.max_connections))
