@@ -491,25 +491,78 @@ argmax_logprob_kernel(const T* __restrict__ logits, long long* __restrict__ ids,
 using tgi_sampling::gumbel_noise;
 using tgi_sampling::order_bits;
 
-// smallest order_bits threshold t such that  sum_{x : bits(x) > t} w(x) < limit   (w = 1 or exp(x - m))
+// Calls f(index, score / T) for every entry of a row, the CTA's threads striding over it; 16-byte loads where the
+// row allows it (8 bf16 or 4 fp32 per thread and step).
+template <typename T, typename F>
+__device__ __forceinline__ void scan_row(const T* __restrict__ row, int V, float inv_t, F&& f) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int nvec = (reinterpret_cast<uintptr_t>(row) & 15) == 0 ? V / VEC : 0;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(row)[v];
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) f(v * VEC + j, static_cast<float>(e[j]) * inv_t);
+  }
+  for (int i = nvec * VEC + threadIdx.x; i < V; i += blockDim.x) f(i, static_cast<float>(row[i]) * inv_t);
+}
+
+// smallest order_bits threshold t such that  sum_{x : bits(x) > t} w(x) < limit   (w = 1 or exp(x - m)),
+// not below floor_bits and not above the bits of the row maximum.
+// Radix select over the four bytes of the ordered bits, most significant first: one pass over the row per byte
+// builds a 256-bin histogram of the weights of the entries that match the bytes found so far, and a walk down
+// the bins finds the byte of t (the lowest bin whose entries can still be left out).  Five passes replace the
+// 32 of a bisection.  Weights are accumulated as 2^-40 fixed point in 64-bit integers, so the sums do not depend
+// on the order in which the lanes' atomics land: the same row always yields the same threshold.
+constexpr int kHistCopies = 16;          // one histogram per pair of warps (1024 threads)
+constexpr float kFixedOne = 1099511627776.f;   // 2^40
+
 template <typename T, bool MASS>
 __device__ uint32_t find_threshold(const T* __restrict__ row, int V, float inv_t, float m, float limit, uint32_t floor_bits,
-                                   float* red) {
-  uint32_t lo = floor_bits, hi = order_bits(m);   // predicate false at lo - 1 (or lo is the floor), true at hi
-  // invariant: answer in [lo, hi]
-  while (lo < hi) {
-    const uint32_t mid = lo + ((hi - lo) >> 1);
-    float acc = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float x = static_cast<float>(row[i]) * inv_t;
+                                   unsigned long long* hist, unsigned long long* tot) {
+  const unsigned long long lim = MASS ? static_cast<unsigned long long>(fmaxf(limit, 0.f) * kFixedOne)
+                                      : static_cast<unsigned long long>(fmaxf(limit, 0.f));
+  const int copy = (threadIdx.x >> 5) % kHistCopies;
+  uint32_t prefix = 0u;
+  unsigned long long above = 0ull;         // weight of the entries whose leading bytes exceed the prefix
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < kHistCopies * 256; i += blockDim.x) hist[i] = 0ull;
+    __syncthreads();
+    const uint32_t hi_mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+    unsigned int* hist32 = reinterpret_cast<unsigned int*>(hist);      // counts fit 32 bits: the cheaper atomic
+    scan_row(row, V, inv_t, [&](int, float x) {
       const uint32_t b = order_bits(x);
-      if (b > mid && b >= floor_bits) acc += MASS ? __expf(x - m) : 1.f;
+      if (b >= floor_bits && (b & hi_mask) == prefix) {
+        if (MASS) atomicAdd(&hist[copy * 256 + ((b >> shift) & 255u)], static_cast<unsigned long long>(__expf(x - m) * kFixedOne));
+        else atomicAdd(&hist32[copy * 256 + ((b >> shift) & 255u)], 1u);
+      }
+    });
+    __syncthreads();
+    if (threadIdx.x < 256) {
+      unsigned long long t = 0ull;
+#pragma unroll
+      for (int c = 0; c < kHistCopies; ++c)
+        t += MASS ? hist[c * 256 + threadIdx.x] : static_cast<unsigned long long>(reinterpret_cast<unsigned int*>(hist)[c * 256 + threadIdx.x]);
+      tot[threadIdx.x] = t;
     }
-    const float total = block_sum(acc, red);
-    if (total < limit) hi = mid;
-    else lo = mid + 1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // S(v) = above + sum of the bins over v is the weight left out when t ends in bin v; S(255) < lim holds on
+      // entry, and going one bin down adds that bin: stop before the sum would reach lim
+      unsigned long long run = above;
+      int v = 255;
+      while (v > 0 && run + tot[v] < lim) {
+        run += tot[v];
+        --v;
+      }
+      tot[256] = run;
+      tot[257] = static_cast<unsigned long long>(v);
+    }
+    __syncthreads();
+    above = tot[256];
+    prefix |= static_cast<uint32_t>(tot[257]) << shift;
+    __syncthreads();
   }
-  return lo;
+  return max(min(prefix, order_bits(m)), floor_bits);
 }
 
 // Typical-p (utils/logits_process.py:389-448): over the entries the earlier filters kept, with p_j their
@@ -520,19 +573,17 @@ template <typename T>
 __device__ uint32_t typical_threshold(const T* __restrict__ row, int V, float inv_t, float m, uint32_t keep_from, float mass,
                                       float* red, float* log_z_out, float* entropy_out) {
   float z = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float x = static_cast<float>(row[i]) * inv_t;
+  scan_row(row, V, inv_t, [&](int, float x) {
     if (order_bits(x) >= keep_from && x != -INFINITY) z += __expf(x - m);
-  }
+  });
   const float log_z = __logf(block_sum(z, red));
   float h = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float x = static_cast<float>(row[i]) * inv_t;
+  scan_row(row, V, inv_t, [&](int, float x) {
     if (order_bits(x) >= keep_from && x != -INFINITY) {
       const float lp = x - m - log_z;
       h -= __expf(lp) * lp;
     }
-  }
+  });
   const float H = block_sum(h, red);
   *log_z_out = log_z;
   *entropy_out = H;
@@ -540,13 +591,12 @@ __device__ uint32_t typical_threshold(const T* __restrict__ row, int V, float in
   while (lo < hi) {
     const uint32_t mid = lo + ((hi - lo) >> 1);
     float acc = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float x = static_cast<float>(row[i]) * inv_t;
+    scan_row(row, V, inv_t, [&](int, float x) {
       if (order_bits(x) >= keep_from && x != -INFINITY) {
         const float lp = x - m - log_z;
         if (__float_as_uint(fabsf(-lp - H)) <= mid) acc += __expf(lp);
       }
-    }
+    });
     if (block_sum(acc, red) >= mass) hi = mid;
     else lo = mid + 1;
   }
@@ -565,6 +615,8 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
   __shared__ float red[32];
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
+  __shared__ unsigned long long s_hist[kHistCopies * 256];
+  __shared__ unsigned long long s_tot[258];
   const int b = blockIdx.x;
   const T* row = scores + static_cast<size_t>(b) * row_stride;
   const float temp = temperature != nullptr ? temperature[b] : 1.f;
@@ -572,7 +624,7 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // ---- max ----
   float m = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, static_cast<float>(row[i]) * inv_t);
+  scan_row(row, V, inv_t, [&](int, float x) { m = fmaxf(m, x); });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   __syncthreads();
@@ -584,16 +636,15 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
   // ---- thresholds ----
   uint32_t keep_from = 0u;                      // keep entries whose order_bits >= keep_from
   const int k = top_k != nullptr ? top_k[b] : 0;
-  if (k > 0 && k < V) keep_from = find_threshold<T, false>(row, V, inv_t, m, static_cast<float>(k), 0u, red);
+  if (k > 0 && k < V) keep_from = find_threshold<T, false>(row, V, inv_t, m, static_cast<float>(k), 0u, s_hist, s_tot);
   const float p = top_p != nullptr ? top_p[b] : 1.f;
   if (p < 1.f) {
     float z = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float x = static_cast<float>(row[i]) * inv_t;
+    scan_row(row, V, inv_t, [&](int, float x) {
       if (order_bits(x) >= keep_from) z += __expf(x - m);
-    }
+    });
     z = block_sum(z, red);
-    const uint32_t t = find_threshold<T, true>(row, V, inv_t, m, p * z, keep_from, red);
+    const uint32_t t = find_threshold<T, true>(row, V, inv_t, m, p * z, keep_from, s_hist, s_tot);
     keep_from = max(keep_from, t);
   }
   const float typ = typical_p != nullptr ? typical_p[b] : 1.f;
@@ -606,18 +657,17 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
   const uint32_t step = steps != nullptr ? static_cast<uint32_t>(steps[b]) : 0u;
   float z = 0.f, best = -INFINITY, best_x = 0.f;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float x = static_cast<float>(row[i]) * inv_t;
-    if (order_bits(x) < keep_from || x == -INFINITY) continue;
-    if (typ < 1.f && __float_as_uint(fabsf(-(x - m - typ_log_z) - typ_h)) > typ_bits) continue;
+  scan_row(row, V, inv_t, [&](int i, float x) {
+    if (order_bits(x) < keep_from || x == -INFINITY) return;
+    if (typ < 1.f && __float_as_uint(fabsf(-(x - m - typ_log_z) - typ_h)) > typ_bits) return;
     z += __expf(x - m);
     const float key = sample ? x + gumbel_noise(static_cast<uint32_t>(i), step, seed) : x;
-    if (key > best) {
+    if (key > best || (key == best && i < best_i)) {
       best = key;
       best_i = i;
       best_x = x;
     }
-  }
+  });
   z = block_sum(z, red);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -657,7 +707,7 @@ sample_kernel(const T* __restrict__ scores, long long row_stride, const float* _
 // untouched `logits`, so duplicates write the same number).  Frequency: score -= p * occurrences.
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 penalties_kernel(const T* __restrict__ logits, long long in_stride, float* __restrict__ scores, long long out_stride,
                  const long long* __restrict__ history, int L, const float* __restrict__ rep, const float* __restrict__ freq,
                  int vocab_start, int V, float logit_scale) {
@@ -665,7 +715,23 @@ penalties_kernel(const T* __restrict__ logits, long long in_stride, float* __res
   const int b = blockIdx.x;
   const T* in = logits + static_cast<size_t>(b) * in_stride;
   float* out = scores + static_cast<size_t>(b) * out_stride;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) out[i] = static_cast<float>(in[i]) * logit_scale;
+  {
+    // the copy is the bulk of the kernel: 16-byte loads, 16-byte stores where both rows allow it
+    constexpr int VEC = 16 / sizeof(T);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int nvec = aligned ? V / VEC : 0;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 raw = reinterpret_cast<const uint4*>(in)[v];
+      const T* e = reinterpret_cast<const T*>(&raw);
+      float f[VEC];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) f[j] = static_cast<float>(e[j]) * logit_scale;
+#pragma unroll
+      for (int j = 0; j < VEC; j += 4)
+        reinterpret_cast<float4*>(out + static_cast<size_t>(v) * VEC)[j >> 2] = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+    }
+    for (int i = nvec * VEC + threadIdx.x; i < V; i += blockDim.x) out[i] = static_cast<float>(in[i]) * logit_scale;
+  }
   __syncthreads();
   const long long* h = history + static_cast<size_t>(b) * L;
   const float rp = rep != nullptr ? rep[b] : 1.f;
@@ -757,10 +823,10 @@ int tgi_penalties(const void* logits, int is_fp32, long long in_stride, float* s
                   float logit_scale, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (is_fp32)
-    tgi::launch(penalties_kernel<float>, dim3(B), dim3(256), 0, stream, static_cast<const float*>(logits), in_stride, scores,
+    tgi::launch(penalties_kernel<float>, dim3(B), dim3(1024), 0, stream, static_cast<const float*>(logits), in_stride, scores,
                 out_stride, history, L, rep, freq, vocab_start, V, logit_scale);
   else
-    tgi::launch(penalties_kernel<__nv_bfloat16>, dim3(B), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(logits),
+    tgi::launch(penalties_kernel<__nv_bfloat16>, dim3(B), dim3(1024), 0, stream, static_cast<const __nv_bfloat16*>(logits),
                 in_stride, scores, out_stride, history, L, rep, freq, vocab_start, V, logit_scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
