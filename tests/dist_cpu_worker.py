@@ -77,10 +77,10 @@ def main():
             assert toks[i] == t, (i, toks[i], t)
         else:
             assert toks[i] == []
-    mode = os.environ.get("TGI_B200_MOE_PARALLEL", "auto")
+    mode = os.environ.get("TGI_B200_MOE_PARALLEL", "tp")
     moe = getattr(sharded.model.layers[0], "mlp", None)
     if hasattr(moe, "expert_parallel"):
-        assert (moe.expert_parallel is not None) == (mode != "tp"), "wrong MoE parallel mode"
+        assert (moe.expert_parallel is not None) == (mode == "ep"), "wrong MoE parallel mode"
     pdist.barrier(group)
     if rank == 0:
         print("DIST_WORKER_OK", flush=True)

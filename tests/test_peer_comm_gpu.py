@@ -57,13 +57,15 @@ def test_peer_collectives_across_gpus(world):
 
 
 @pytest.mark.multigpu
-@pytest.mark.parametrize("world,model", [(2, "llama"), (2, "mixtral"), (8, "llama"), (8, "mixtral")])
+@pytest.mark.parametrize("world,model", [(2, "llama"), (2, "mixtral"), (2, "mixtral-ep"), (4, "mixtral"), (8, "llama"),
+                                         (8, "mixtral"), (8, "mixtral-ep")])
 def test_tensor_parallel_engine_on_peer_memory(world, model, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     # prefill steps of 16 tokens or more use the pushing GEMM epilogue, smaller (decode) steps pull
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", TP_WORKER_DIR=str(tmp_path / "ckpt"),
-               TGI_B200_PUSH_MIN_TOKENS="16", TP_WORKER_MODEL=model)
+               TGI_B200_PUSH_MIN_TOKENS="16", TP_WORKER_MODEL=model.split("-")[0],
+               TGI_B200_MOE_PARALLEL="ep" if model.endswith("-ep") else "tp")
     env.pop("TGI_B200_COMM", None)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29700 + world), os.path.join(ROOT, "tests", "tp_worker.py")]

@@ -24,23 +24,27 @@ from tgi_b200.utils.synthetic import (llama_config, llama_state_dict, reference_
                                       write_llama_checkpoint)
 
 
-def request(i, n_new, blocks):
+def request(i, n_new, blocks, sampled=False):
     r = pb.Request(id=i, inputs="")
-    r.parameters.temperature = 1.0
-    r.parameters.top_p = 1.0
+    r.parameters.temperature = 0.7 if sampled else 1.0
+    r.parameters.top_p = 0.9 if sampled else 1.0
+    r.parameters.top_k = 50 if sampled else 0
     r.parameters.typical_p = 1.0
-    r.parameters.repetition_penalty = 1.0
+    r.parameters.repetition_penalty = 1.1 if sampled else 1.0
+    if sampled:
+        r.parameters.do_sample = True
+        r.parameters.seed = 77 + i
     r.stopping_parameters.max_new_tokens = n_new
     r.stopping_parameters.ignore_eos_token = True
     r.blocks.extend(blocks)
     return r
 
 
-def generate(runner, dev, prompts, n_new):
+def generate(runner, dev, prompts, n_new, sampled=False):
     cursor, reqs = 1, []
     for i, p in enumerate(prompts):
         nb = (len(p) + n_new + 15) // 16
-        reqs.append(request(i, n_new, range(cursor, cursor + nb)))
+        reqs.append(request(i, n_new, range(cursor, cursor + nb), sampled))
         cursor += nb
     if runner.num_blocks < cursor:
         runner.init_kv_cache(cursor)
@@ -73,7 +77,7 @@ def main():
     cfg = llama_config(hidden=512, layers=3, heads=8, kv_heads=8 if world > 2 else 2, intermediate=1024, vocab=4096,
                        max_pos=1024)
     if os.environ.get("TP_WORKER_MODEL") == "mixtral":
-        # sparse MoE: experts are placed whole on their owner rank (expert parallel) when the count divides
+        # sparse MoE: experts sliced over the ranks, or whole experts per rank with TGI_B200_MOE_PARALLEL=ep
         cfg = llama_config(hidden=512, layers=2, heads=8, kv_heads=8 if world > 2 else 2, intermediate=512, vocab=4096,
                            max_pos=1024, model_type="mixtral", num_local_experts=8, num_experts_per_tok=2)
     if rank == 0:
@@ -115,6 +119,28 @@ def main():
     assert agree == len(prompts), (toks_graph, toks_peer)
     same = sum(toks_base[i][:2] == toks_peer[i][:2] for i in toks_peer)
     assert same >= len(prompts) - 1, (toks_base, toks_peer)
+
+    # sampled requests (temperature, top-k, top-p, repetition penalty, seed): the decode graph leaves each rank its
+    # slice of the logits and the ranks sample on the slices; the draw is a function of (seed, step) and must repeat
+    taken = []
+    orig_shard_sampler = peer._sample_on_shards
+
+    def shard_sampler_spy(*a, **kw):
+        out = orig_shard_sampler(*a, **kw)
+        taken.append(out is not None)
+        return out
+
+    peer._sample_on_shards = shard_sampler_spy
+    toks_s1, _ = generate(peer, dev, prompts, n_new, sampled=True)
+    toks_s2, _ = generate(peer, dev, prompts, n_new, sampled=True)
+    peer._sample_on_shards = orig_shard_sampler
+    assert K.check_status(dev) == 0
+    assert taken and all(taken), "sampled decode steps did not run on the vocabulary shards"
+    assert toks_s1 == toks_s2, (toks_s1, toks_s2)
+    # a rank reports the generations of the requests it owns (id % world == rank)
+    assert all(len(v) == (n_new if i % world == rank else 0) and all(0 <= t < 4096 for t in v)
+               for i, v in toks_s1.items()), toks_s1
+    assert toks_s1 != toks_graph, "sampling with temperature produced the greedy tokens for every prompt"
 
     pdist.barrier(group)
     torch.cuda.synchronize()

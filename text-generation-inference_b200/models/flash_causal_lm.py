@@ -341,7 +341,7 @@ class FlashCausalLM(Model):
             seeds = torch.tensor([int(s or 0) & 0x7FFFFFFFFFFFFFFF for s in chooser.seeds], dtype=torch.int64)
             steps = torch.tensor(chooser.steps, dtype=torch.int32)
             chooser.steps = [st + (1 if ds else 0) for st, ds in zip(chooser.steps, chooser.do_sample_list)]
-        return comm.sample(local, v0, d.vocab_size, scale,
+        return comm.sample(local, v0, d.vocab, scale,
                            chooser.temperature if chooser.any_temperature else None,
                            chooser.top_k if chooser.any_top_k else None, chooser.top_p if chooser.any_top_p else None,
                            do_sample, seeds, steps)
