@@ -36,7 +36,13 @@ using namespace sm100;
 namespace {
 
 constexpr int kThreads = 512;
-constexpr int kStages = 4;
+// Two rings.  The packed weights are what comes from HBM.  A K block of 64 is only 32 bytes of a 4-bit weight row,
+// and fetching 32-byte slivers of 128 rows that lie 4 KB apart ran the DRAM at a tenth of its bandwidth (measured:
+// 0.6 TB/s), so the weights are fetched in slabs of 128 bytes per row (4 K blocks of 4-bit, 2 of 8-bit weights:
+// whole DRAM bursts) into a ring of kRaw slabs of 16 KB, which also keeps 64 KB per SM in flight.  The token tile
+// (from L2) and the converted weight tile, 16 KB each, use a ring of kStages slots of their own.
+constexpr int kStages = 3;
+constexpr int kRaw = 4;
 constexpr int kTileM = 128, kTileN = 128, kBK = 64;
 
 __device__ __forceinline__ void report(int* status, int code) {
@@ -46,10 +52,13 @@ __device__ __forceinline__ void report(int* status, int code) {
 template <int BITS>
 struct WqCfg {
   static constexpr int kRawRowBytes = kBK * BITS / 8;              // 32 (4-bit) or 64 (8-bit)
-  static constexpr int kRawBytes = kTileN * kRawRowBytes;
+  static constexpr int kSlab = 128 / kRawRowBytes;                    // K blocks per slab: 4 or 2
+  static constexpr int kSlabBytes = kTileN * 128;                     // 16 KB
   static constexpr int kXBytes = kTileM * 128;
   static constexpr int kWBytes = kTileN * 128;
-  static constexpr int kStageBytes = kXBytes + kWBytes + kRawBytes;   // 36 KB / 40 KB
+  static constexpr int kStageBytes = kXBytes + kWBytes;               // token tile + converted weight tile
+  static constexpr int kRawOff = kStages * kStageBytes;               // raw slots follow the stages
+  static constexpr int kBarOff = kRawOff + kRaw * kSlabBytes;
 };
 
 template <int BITS>
@@ -61,10 +70,12 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   using Cfg = WqCfg<BITS>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
-  uint64_t* empty = full + kStages;
-  uint64_t* wready = empty + kStages;
-  uint64_t* tmem_full = wready + kStages;    // [2]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);     // token tile landed
+  uint64_t* empty = full + kStages;          // MMAs done with the stage (token tile and converted weights)
+  uint64_t* wready = empty + kStages;        // converted weight tile written
+  uint64_t* raw_full = wready + kStages;     // [kRaw] packed weights landed
+  uint64_t* raw_empty = raw_full + kRaw;     // [kRaw] converters have read them
+  uint64_t* tmem_full = raw_empty + kRaw;    // [2]
   uint64_t* tmem_empty = tmem_full + 2;      // [2]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -78,6 +89,10 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
       mbar_init(&wready[s], 8);
+    }
+    for (int s = 0; s < kRaw; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], 8);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
@@ -110,9 +125,8 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   };
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer of the token tiles ----------------
     if (elect_one()) {
-      const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
       int it = 0, issued = 0;
       bool ok = true;
@@ -123,20 +137,41 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           const int s = it % kStages;
           if (it >= kStages) ok = mbar_wait(&empty[s], ((it / kStages) - 1) & 1);
           if (!ok) { report(status, kErrProducerWait); break; }
-          uint8_t* st = smem + s * Cfg::kStageBytes;
-          mbar_arrive_expect_tx(&full[s], Cfg::kXBytes + Cfg::kRawBytes);
-          tma_load_2d_hint(st, &tmX, &full[s], kb * kBK, tm * kTileM, pol_x);
-          tma_load_2d_hint(st + Cfg::kXBytes + Cfg::kWBytes, &tmQ, &full[s], kb * Cfg::kRawRowBytes, tn * kTileN, pol_w);
+          mbar_arrive_expect_tx(&full[s], Cfg::kXBytes);
+          tma_load_2d_hint(smem + s * Cfg::kStageBytes, &tmX, &full[s], kb * kBK, tm * kTileM, pol_x);
           issued = it + 1;
         }
       }
       if (!ok)
         for (int j = max(0, issued - kStages); j < issued; ++j) mbar_wait(&full[j % kStages], (j / kStages) & 1, 1u << 12);
     }
+  } else if (warp == 2) {
+    // ---------------- TMA producer of the packed weights (runs kRaw slabs ahead) ----------------
+    if (elect_one()) {
+      const uint64_t pol_w = policy_evict_first();
+      int it = 0, issued = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        int tm, tn, kb0, kb1;
+        decode(unit, tm, tn, kb0, kb1);
+        // a unit whose K range starts or ends inside a slab fetches the whole slab; bytes past the end of a row
+        // are filled with zeros by the copy and meet zero token columns
+        for (int sl = kb0 / Cfg::kSlab; sl <= (kb1 - 1) / Cfg::kSlab; ++sl, ++it) {
+          const int s = it % kRaw;
+          if (it >= kRaw) ok = mbar_wait(&raw_empty[s], ((it / kRaw) - 1) & 1);
+          if (!ok) { report(status, kErrProducerWait); break; }
+          mbar_arrive_expect_tx(&raw_full[s], Cfg::kSlabBytes);
+          tma_load_2d_hint(smem + Cfg::kRawOff + s * Cfg::kSlabBytes, &tmQ, &raw_full[s], sl * 128, tn * kTileN, pol_w);
+          issued = it + 1;
+        }
+      }
+      if (!ok)
+        for (int j = max(0, issued - kRaw); j < issued; ++j) mbar_wait(&raw_full[j % kRaw], (j / kRaw) & 1, 1u << 12);
+    }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc(kTileM, kTileN, 1, 1);
+      constexpr uint32_t idesc = make_idesc(kTileM, kTileN, 1, 0);     // tokens bf16, converted weights fp16
       int it = 0, use = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++use) {
@@ -172,46 +207,96 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     // ---------------- converters: half a weight row per thread ----------------
     const int t = (warp - 4) * 32 + lane;       // 0..255
     const int r = t >> 1, half = t & 1;         // row of the tile, which 32 elements of its 64
-    int it = 0;
+    int it = 0, rit = -1;
     bool ok = true;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
       int tm, tn, kb0, kb1;
       decode(unit, tm, tn, kb0, kb1);
+      int cur_slab = -1;
       const int n = min(tn * kTileN + r, N - 1);          // rows past N are loaded as zeros and never stored
+      // scale and zero point of a group come from global memory: the next group's pair is requested one K block
+      // early so that its latency passes under the wait and the conversion of the current block
+      int g_cur = -1, g_next = -1;
+      __half sc = __float2half(0.f), zq = __float2half(8.f), sc_next = sc, zq_next = zq;
+      auto fetch = [&](int g, __half& s_out, __half& z_out) {
+        s_out = scale[static_cast<size_t>(g) * N + n];
+        z_out = (BITS == 4 && zp != nullptr) ? zp[static_cast<size_t>(g) * N + n] : __float2half(8.f);
+      };
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % kStages;
-        if (!mbar_wait(&full[s], (it / kStages) & 1)) {
+        const int g = (kb * kBK) / group;
+        if (g != g_cur) {
+          if (g == g_next) {
+            sc = sc_next;
+            zq = zq_next;
+          } else {
+            fetch(g, sc, zq);
+          }
+          g_cur = g;
+        }
+        const int g_after = ((kb + 1) * kBK) / group;
+        if (kb + 1 < kb1 && g_after != g_cur && g_after != g_next) {
+          fetch(g_after, sc_next, zq_next);
+          g_next = g_after;
+        }
+        // the slab with this K block's packed weights landed; the converted tile of the stage is free once the MMAs
+        // that read its previous contents are done
+        if (kb / Cfg::kSlab != cur_slab) {
+          cur_slab = kb / Cfg::kSlab;
+          ++rit;
+          if (!mbar_wait(&raw_full[rit % kRaw], (rit / kRaw) & 1)) {
+            report(status, kErrMmaWaitFull);
+            ok = false;
+            break;
+          }
+        }
+        const int rs = rit % kRaw;
+        if (it >= kStages && !mbar_wait(&empty[s], ((it / kStages) - 1) & 1)) {
           report(status, kErrMmaWaitFull);
           ok = false;
           break;
         }
-        const int g = (kb * kBK) / group;
-        const float sc = __half2float(scale[static_cast<size_t>(g) * N + n]);
         uint8_t* st = smem + s * Cfg::kStageBytes;
-        const uint8_t* raw = st + Cfg::kXBytes + Cfg::kWBytes + r * Cfg::kRawRowBytes + half * (Cfg::kRawRowBytes / 2);
+        const uint8_t* raw = smem + Cfg::kRawOff + rs * Cfg::kSlabBytes + r * 128 + (kb % Cfg::kSlab) * Cfg::kRawRowBytes +
+                             half * (Cfg::kRawRowBytes / 2);
         uint8_t* dst = st + Cfg::kXBytes + r * 128;
         if (BITS == 4) {
-          // bf16(128 + q) is 0x4300 | q exactly; widened to fp32 it enters one fused multiply-add:
-          // (128 + q) * s - (128 + zp) * s = (q - zp) * s
-          const float z = zp != nullptr ? __half2float(zp[static_cast<size_t>(g) * N + n]) : 8.f;
-          const float off = -(128.f + z) * sc;
+          // Eight nibbles of a word become four fp16 pairs with one LOP3 each: (w & 0x000f000f) | 0x64006400 is the
+          // pair (1024 + n0, 1024 + n4), the mask 0x00f000f0 gives (1024 + 16 n1, 1024 + 16 n5).  Subtracting
+          // 1024 + zp (or multiplying by 1/16 and adding -(64 + zp)) is exact in fp16 for integer zero points, one
+          // multiplication by the group's scale follows: about two instructions per weight instead of six.  The
+          // converted tile is fp16 (11 significant bits); the MMA takes bf16 tokens and fp16 weights.
+          const __half2 s2 = __half2half2(sc);
+          const __half2 z_lo = __half2half2(__hadd(__float2half(1024.f), zq));           // 1024 + zp
+          const __half2 z_hi = __half2half2(__hneg(__hadd(__float2half(64.f), zq)));     // -(64 + zp)
+          const __half2 sixteenth = __float2half2_rn(0.0625f);
           const uint4 q = *reinterpret_cast<const uint4*>(raw);
           const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {         // chunk 4 * half + cc: elements of word cc
-            uint32_t o[4];
+          for (int cc = 0; cc < 4; ++cc) {         // chunk 4 * half + cc: the eight elements of word cc
+            uint32_t w = words[cc];
+            uint32_t p[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t byte = (words[cc] >> (8 * j)) & 0xFFu;
-              const float lo = __uint_as_float((0x4300u | (byte & 0xFu)) << 16);
-              const float hi = __uint_as_float((0x4300u | (byte >> 4)) << 16);
-              const __nv_bfloat162 v = __floats2bfloat162_rn(fmaf(lo, sc, off), fmaf(hi, sc, off));
-              o[j] = *reinterpret_cast<const uint32_t*>(&v);
+            for (int j = 0; j < 2; ++j) {
+              uint32_t lo, hi;
+              asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xEA;" : "=r"(lo) : "r"(w));
+              asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xEA;" : "=r"(hi) : "r"(w));
+              const __half2 a = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&lo), z_lo), s2);
+              const __half2 b2 = __hmul2(__hfma2(*reinterpret_cast<const __half2*>(&hi), sixteenth, z_hi), s2);
+              p[2 * j] = *reinterpret_cast<const uint32_t*>(&a);        // elements (2j, 2j + 4)
+              p[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&b2);   // elements (2j + 1, 2j + 5)
+              w >>= 8;
             }
+            uint32_t o[4];
+            asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o[0]) : "r"(p[0]), "r"(p[1]));     // e0, e1
+            asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o[1]) : "r"(p[2]), "r"(p[3]));     // e2, e3
+            asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o[2]) : "r"(p[0]), "r"(p[1]));     // e4, e5
+            asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o[3]) : "r"(p[2]), "r"(p[3]));     // e6, e7
             const int c = half * 4 + cc;
             *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         } else {
+          const float scf = __half2float(sc);
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) {         // chunk 4 * half + cc: bytes 8 cc .. 8 cc + 7 of this half
             const uint2 q = *reinterpret_cast<const uint2*>(raw + cc * 8);
@@ -221,7 +306,7 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             for (int j = 0; j < 4; ++j) {
               const int a = static_cast<int8_t>((w2[j >> 1] >> (16 * (j & 1))) & 0xFF);
               const int b = static_cast<int8_t>((w2[j >> 1] >> (16 * (j & 1) + 8)) & 0xFF);
-              const __nv_bfloat162 v = __floats2bfloat162_rn(static_cast<float>(a) * sc, static_cast<float>(b) * sc);
+              const __half2 v = __floats2half2_rn(static_cast<float>(a) * scf, static_cast<float>(b) * scf);
               o[j] = *reinterpret_cast<const uint32_t*>(&v);
             }
             const int c = half * 4 + cc;
@@ -230,7 +315,10 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         }
         fence_proxy_async();        // the generic-proxy stores above become visible to the tensor core's reads
         __syncwarp();
-        if (lane == 0) mbar_arrive(&wready[s]);
+        if (lane == 0) {
+          mbar_arrive(&wready[s]);
+          if (kb % Cfg::kSlab == Cfg::kSlab - 1 || kb == kb1 - 1) mbar_arrive(&raw_empty[rs]);     // done with the slab
+        }
       }
     }
   } else if (warp >= 12) {
@@ -366,10 +454,10 @@ int launch_wq(const void* X, const void* Wq, const void* scale, const void* zp, 
                             CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   const uint64_t row_bytes = static_cast<uint64_t>(K) * BITS / 8;
-  rc = tgi::make_map_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_UINT8, Wq, N, row_bytes, row_bytes, kTileN, Cfg::kRawRowBytes,
+  rc = tgi::make_map_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_UINT8, Wq, N, row_bytes, row_bytes, kTileN, 128,
                         CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
-  const size_t smem = kStages * Cfg::kStageBytes + 1024 + 256;
+  const size_t smem = Cfg::kBarOff + 1024 + 512;
   auto kern = gemm_wq_kernel<BITS>;
   static std::atomic<unsigned long long> attr_set{0};
   int dev = 0;
@@ -380,6 +468,9 @@ int launch_wq(const void* X, const void* Wq, const void* scale, const void* zp, 
       return -2;
     attr_set.fetch_or(bit, std::memory_order_release);
   }
+  int per_sm = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+  ctas *= per_sm > 2 ? 2 : per_sm;
   // K splits: enough units to occupy the GPU, at least 8 K blocks per unit, bounded by the workspace
   const int tiles = ((N + kTileN - 1) / kTileN) * ((M + kTileM - 1) / kTileM);
   const int KB = (K + kBK - 1) / kBK;
