@@ -62,8 +62,10 @@ def test_w4a16_matches_the_dequantised_product(M, N, K, group, act_order, awq):
     got = lin(x)
     torch.cuda.synchronize()
     assert Kc.check_status(dev()) == 0, "a kernel wait timed out"
-    want = x.float() @ w.to(torch.bfloat16).float().to(dev()).t()
-    torch.testing.assert_close(got.float(), want, atol=2e-2 * math.sqrt(K / 512), rtol=2e-2)
+    # the op itself: tokens times the exact dequantised weights in fp32; the fused kernel rounds the weights to fp16
+    # and the output to bf16, the large-step path rounds the weights to bf16
+    want = x.float() @ w.float().to(dev()).t()
+    torch.testing.assert_close(got.float(), want, atol=3e-2 * math.sqrt(K / 512), rtol=2e-2)
 
 
 def test_int8_per_channel_and_bias_and_large_step():

@@ -171,7 +171,7 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc(kTileM, kTileN, 1, 0);     // tokens bf16, converted weights fp16
+      constexpr uint32_t idesc = make_idesc(kTileM, kTileN, 0, 0);     // fp16 x fp16 (tokens are cast once per call)
       int it = 0, use = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++use) {
@@ -265,7 +265,9 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           // pair (1024 + n0, 1024 + n4), the mask 0x00f000f0 gives (1024 + 16 n1, 1024 + 16 n5).  Subtracting
           // 1024 + zp (or multiplying by 1/16 and adding -(64 + zp)) is exact in fp16 for integer zero points, one
           // multiplication by the group's scale follows: about two instructions per weight instead of six.  The
-          // converted tile is fp16 (11 significant bits); the MMA takes bf16 tokens and fp16 weights.
+          // converted tile is fp16 (11 significant bits) and the MMA runs fp16 x fp16 on an fp16 copy of the tokens
+          // (mixing bf16 tokens with fp16 weights in one kind::f16 instruction is not done: both operands use
+          // the same format here).
           const __half2 s2 = __half2half2(sc);
           const __half2 z_lo = __half2half2(__hadd(__float2half(1024.f), zq));           // 1024 + zp
           const __half2 z_hi = __half2half2(__hneg(__hadd(__float2half(64.f), zq)));     // -(64 + zp)
@@ -383,6 +385,29 @@ gemm_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   if (warp == 1) tmem_dealloc(tmem_base, 256);
 }
 
+// tokens bf16 -> fp16, clamped to the fp16 range (weight-only kernels of the reference run in fp16 too:
+// layers/marlin/gptq.py, layers/gptq/exllamav2.py), 8 values per thread
+__global__ void __launch_bounds__(256)
+wq_cast_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ y, long long vecs) {
+  tgi::pdl_wait();
+  tgi::pdl_trigger();
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(x)[v];
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(b[i]);
+      f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
+      f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
+      const __half2 h = __floats2half2_rn(f.x, f.y);
+      o[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    reinterpret_cast<uint4*>(y)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // C = sum over splits (in split order) of the fp32 partials (+ bias), 8 outputs per thread
 __global__ void __launch_bounds__(256)
 wq_reduce_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ C,
@@ -446,11 +471,18 @@ wq_dequant_kernel(const uint8_t* __restrict__ wq, const __half* __restrict__ sca
 }
 
 template <int BITS>
-int launch_wq(const void* X, const void* Wq, const void* scale, const void* zp, int group, void* C, float* partial,
+int launch_wq(const void* X, void* Xh, const void* Wq, const void* scale, const void* zp, int group, void* C, float* partial,
               long long partial_floats, const void* bias, int M, int N, int K, int ctas, int* status, cudaStream_t stream) {
   using Cfg = WqCfg<BITS>;
   CUtensorMap tmX, tmQ;
-  int rc = tgi::make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, X, M, K, static_cast<uint64_t>(K) * 2, 128, kBK,
+  {
+    const long long vecs = static_cast<long long>(M) * K / 8;
+    const int cgrid = static_cast<int>(vecs / 256 + 1 < 1184 ? vecs / 256 + 1 : 1184);
+    if (tgi::launch(wq_cast_kernel, dim3(cgrid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(X),
+                    static_cast<__half*>(Xh), vecs) != cudaSuccess)
+      return -3;
+  }
+  int rc = tgi::make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, Xh, M, K, static_cast<uint64_t>(K) * 2, 128, kBK,
                             CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   const uint64_t row_bytes = static_cast<uint64_t>(K) * BITS / 8;
@@ -474,11 +506,21 @@ int launch_wq(const void* X, const void* Wq, const void* scale, const void* zp, 
   // K splits: enough units to occupy the GPU, at least 8 K blocks per unit, bounded by the workspace
   const int tiles = ((N + kTileN - 1) / kTileN) * ((M + kTileM - 1) / kTileM);
   const int KB = (K + kBK - 1) / kBK;
+  // K splits: the kernel's time is (rounds of units per CTA) x (K blocks per unit); 448 tiles on 148 CTAs are 4
+  // rounds of whole tiles but 13 rounds of quarter tiles (416 instead of 512 K blocks on the busiest CTA).  Each split
+  // adds a partial tile and work for the reduce kernel, charged here as 8 K blocks per split.
   int splits = 1;
   if (partial != nullptr) {
-    while (tiles * splits < ctas && splits * 2 <= KB / 8 && splits < 16 && KB % (splits * 2) == 0 &&
-           static_cast<long long>(splits * 2) * M * N <= partial_floats)
-      splits *= 2;
+    long long best = -1;
+    for (int sp = 1; sp <= 16; sp *= 2) {
+      if (KB % sp != 0 || KB / sp < 8 || static_cast<long long>(sp) * M * N > partial_floats) break;
+      const long long rounds = (static_cast<long long>(tiles) * sp + ctas - 1) / ctas;
+      const long long cost = rounds * (KB / sp) + (sp > 1 ? 8LL * sp : 0);
+      if (best < 0 || cost < best) {
+        best = cost;
+        splits = sp;
+      }
+    }
   }
   if (N % 8 != 0) splits = 1;
   int grid = tiles * splits < ctas ? tiles * splits : ctas;
@@ -504,13 +546,13 @@ extern "C" {
 
 // bits: 4 (Wq uint8 [N, K / 2]) or 8 (Wq int8 [N, K]); scale / zp fp16 [K / group, N] (zp may be null: the 4-bit
 // zero point is then 8, the 8-bit format has none); partial: fp32 workspace of `partial_floats` floats or null.
-int tgi_gemm_wq(int bits, const void* X, const void* Wq, const void* scale, const void* zp, int group, void* C,
+int tgi_gemm_wq(int bits, const void* X, void* Xh, const void* Wq, const void* scale, const void* zp, int group, void* C,
                 float* partial, long long partial_floats, const void* bias, int M, int N, int K, int ctas, int* status,
                 cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % kBK != 0 || group < kBK || group % kBK != 0 || N % 8 != 0 || ctas < 1) return -10;
-  if (bits == 4) return launch_wq<4>(X, Wq, scale, zp, group, C, partial, partial_floats, bias, M, N, K, ctas, status, stream);
-  if (bits == 8) return launch_wq<8>(X, Wq, scale, nullptr, group, C, partial, partial_floats, bias, M, N, K, ctas, status, stream);
+  if (bits == 4) return launch_wq<4>(X, Xh, Wq, scale, zp, group, C, partial, partial_floats, bias, M, N, K, ctas, status, stream);
+  if (bits == 8) return launch_wq<8>(X, Xh, Wq, scale, nullptr, group, C, partial, partial_floats, bias, M, N, K, ctas, status, stream);
   return -11;
 }
 

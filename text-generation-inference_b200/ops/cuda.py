@@ -442,7 +442,9 @@ def gemm_wq(x: torch.Tensor, wq: torch.Tensor, scale: torch.Tensor, zp: Optional
     N = wq.shape[0]
     out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     part = _wq_partial(x.device)
-    _check(lib.tgi_gemm_wq(c_int(bits), _ptr(x.contiguous()), _ptr(wq), _ptr(scale), _ptr(zp), c_int(group), _ptr(out),
+    x = x.contiguous()
+    xh = torch.empty(M, K, dtype=torch.float16, device=x.device)       # fp16 copy of the tokens, written by the call
+    _check(lib.tgi_gemm_wq(c_int(bits), _ptr(x), _ptr(xh), _ptr(wq), _ptr(scale), _ptr(zp), c_int(group), _ptr(out),
                            _ptr(part), c_ll(part.numel()), _ptr(bias), c_int(M), c_int(N), c_int(K), c_int(st.sm_count),
                            _ptr(st.status), _stream()), "gemm_wq")
     return out
