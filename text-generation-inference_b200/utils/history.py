@@ -79,9 +79,7 @@ class TokenHistory:
                 self.len_of[rid] = len(seq)
         if rows_l:
             packed = np.stack([np.concatenate(rows_l), np.concatenate(pos_l), np.concatenate(tok_l)])
-            t = torch.from_numpy(packed)
-            if self.device.type == "cuda":
-                t = t.pin_memory().to(self.device, non_blocking=True)
+            t = torch.from_numpy(packed).to(self.device)       # a few hundred bytes per step
             self.buf.index_put_((t[0], t[1]), t[2])
         order = [self.row_of[rid] for rid in request_ids]
         if n and order == list(range(order[0], order[0] + n)):     # neighbouring rows: a view, no gather
