@@ -166,12 +166,16 @@ struct Layout {
   static constexpr int kKBytes = 2 * kTileBytes;                  // 64 KB in both modes
   static constexpr int kV = kK + kKBytes;
   static constexpr int kP = kV + kKBytes;
-  static constexpr int kBars = kP + kTileBytes;                   // 192 KB
+  // two P tiles: the softmax of tile j + 1 writes one while the PV product of tile j still reads the other.  The
+  // final partial row sums (float [2][128]) are written into the P tile that the last product does not read.
+  static constexpr int kBars = kP + 2 * kTileBytes;               // 224 KB
   static constexpr int kAlpha = kBars + 256;                      // float [2][128]
-  static constexpr int kRowSum = kAlpha + 2 * 128 * 4;            // float [2][128]: partial row sums of the two halves
-  static constexpr int kRowMax = kRowSum + 2 * 128 * 4;           // float [2][128]: row maxima of the two halves
+  static constexpr int kRowMax = kAlpha + 2 * 128 * 4;            // float [2][128]: row maxima of the two halves
   static constexpr int kAbort = kRowMax + 2 * 128 * 4;            // int [4][2]: a softmax thread of the lane quarter gave up
-  static constexpr int kTotal = kAbort + 64 + 1024;               // + alignment slack
+  // no slack for aligning the base: the kernel checks that the dynamic shared memory starts on a 1024-byte
+  // boundary (it does when the kernel has no static shared memory) and reports an error otherwise
+  static constexpr int kTotal = kAbort + 64;
+  static_assert(kTotal <= 227 * 1024, "shared memory of a CTA");
   // e4m3: raw stage s at kK + s * 16 K, converted tile at kK + 32 K
   static constexpr int kRawStage = kKeys * 128;
 };
@@ -181,7 +185,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const PrefillParams p) {
   using L = Layout<FP8>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0u) {       // uniform over the CTA, before anything is allocated
+    if (threadIdx.x == 0) report(p.status, kErrProducerWait);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
   uint64_t* k_full = bars;            // [2] TMA landed (bf16: operand tile, e4m3: raw tile)
   uint64_t* k_free = bars + 2;        // [2] bf16: MMA done with the stage; e4m3: converters done with the raw stage
@@ -193,15 +201,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   uint64_t* vc_free = bars + 11;
   uint64_t* s_full = bars + 12;       // [2] S accumulator written
   uint64_t* s_free = bars + 14;       // [2] softmax warps have read it
-  uint64_t* p_ready = bars + 16;      // P tile written
-  uint64_t* p_free = bars + 17;       // PV MMA done with the P tile
+  uint64_t* p_ready = bars + 24;      // [2] P tile written
+  uint64_t* p_free = bars + 26;       // [2] PV MMA done with the P tile
   uint64_t* pv_full = bars + 18;      // [2] PV accumulator written
   uint64_t* pv_free = bars + 20;      // [2] O warps have read it
   uint64_t* l_ready = bars + 22;      // final row sums written
   uint64_t* q_ready = bars + 23;      // Q tile staged (18 warps)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 24);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 28);
   float* s_alpha = reinterpret_cast<float*>(smem + L::kAlpha);
-  float* s_rowsum = reinterpret_cast<float*>(smem + L::kRowSum);
   float* s_rowmax = reinterpret_cast<float*>(smem + L::kRowMax);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::kAbort);
 
@@ -235,8 +242,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     mbar_init(kc_free, 1);
     mbar_init(vc_ready, 8);
     mbar_init(vc_free, 1);
-    mbar_init(p_ready, 8);
-    mbar_init(p_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&p_ready[i], 8);
+      mbar_init(&p_free[i], 1);
+    }
     mbar_init(l_ready, 8);
     mbar_init(q_ready, 18);
     for (int i = 0; i < 8; ++i) s_abort[i] = 0;
@@ -337,7 +346,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       constexpr uint32_t id_qk = idesc16(FP8 ? 0u : 1u, false);
       constexpr uint32_t id_pv = idesc16(FP8 ? 0u : 1u, true);
       const uint32_t q_addr = smem_u32(smem + L::kQ);
-      const uint32_t p_addr = smem_u32(smem + L::kP);
+      const uint32_t p_base = smem_u32(smem + L::kP);
       bool ok = true;
       auto issue_qk = [&](int j) {
         const int s = j & 1;
@@ -372,7 +381,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
           if (!mbar_wait(&v_full[s], (j >> 1) & 1)) { report(p.status, kErrMmaWaitFull); return false; }
           v_addr = smem_u32(smem + L::kV + s * kTileBytes);
         }
-        if (!mbar_wait(p_ready, j & 1)) { report(p.status, kErrMmaWaitFull); return false; }
+        if (!mbar_wait(&p_ready[s], (j >> 1) & 1)) { report(p.status, kErrMmaWaitFull); return false; }
+        const uint32_t p_addr = p_base + s * kTileBytes;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {      // 16 keys per MMA: 32 bytes along a P row, two 8-row groups of V
@@ -381,7 +391,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
           mma_f16(tPV + s * 128, da, db, id_pv, k > 0 ? 1u : 0u);
         }
         tc_commit(&pv_full[s]);
-        tc_commit(p_free);
+        tc_commit(&p_free[s]);
         tc_commit(FP8 ? vc_free : &v_free[s]);
         return true;
       };
@@ -453,7 +463,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       const float m_new = fmaxf(m, fmaxf(mx, s_rowmax[(hf ^ 1) * 128 + r]));
       const float alpha = m_new == -INFINITY ? 0.f : fast_exp2(m - m_new);
       // the P tile and this parity's alpha slot are free once the PV product two tiles back was consumed
-      if (j >= 1 && !mbar_wait(p_free, (j - 1) & 1)) { report(p.status, kErrEpilogueWait); fail = true; }
+      if (j >= 2 && !mbar_wait(&p_free[s], ((j >> 1) - 1) & 1)) { report(p.status, kErrEpilogueWait); fail = true; }
       if (!fail && j >= 2 && !mbar_wait(&pv_free[s], ((j >> 1) - 1) & 1)) { report(p.status, kErrEpilogueWait); fail = true; }
       if (fail) continue;
       // pass 2: probabilities as 16-bit values into the P operand tile, partial row sum.  A row without a visible
@@ -471,7 +481,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {      // four 16-byte chunks (8 keys each) of this 32-key group
           const int ch = hf * 8 + (c >> 3) + q4;   // chunk index among the row's 16
-          *reinterpret_cast<uint4*>(smem + L::kP + (ch >> 3) * kSlab + swz_chunk(r, ch & 7)) =
+          *reinterpret_cast<uint4*>(smem + L::kP + s * kTileBytes + (ch >> 3) * kSlab + swz_chunk(r, ch & 7)) =
               make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
         }
       }
@@ -483,12 +493,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&s_free[s]);
-        mbar_arrive(p_ready);
+        mbar_arrive(&p_ready[s]);
       }
     }
-    s_rowsum[hf * 128 + r] = l;
-    __syncwarp();
-    if (lane == 0) mbar_arrive(l_ready);
+    // partial row sums into the P tile the last product does not read; that tile was last read by the product of
+    // the tile before the last one
+    if (!fail && ntiles >= 2 && !mbar_wait(&p_free[ntiles & 1], ((ntiles - 2) >> 1) & 1)) {
+      report(p.status, kErrEpilogueWait);
+      fail = true;
+    }
+    if (!fail) {
+      reinterpret_cast<float*>(smem + L::kP + (ntiles & 1) * kTileBytes)[hf * 128 + r] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(l_ready);
+    }
   } else {
     // ---------------- running output: 64 columns per thread ----------------
     const int quarter = warp & 3;
@@ -559,6 +577,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     }
     if (ok && mbar_wait(l_ready, 0)) {
       const float vs = (FP8 && p.v_scale != nullptr) ? p.v_scale[kvh] : 1.f;
+      const float* s_rowsum = reinterpret_cast<const float*>(smem + L::kP + (ntiles & 1) * kTileBytes);
       const float l = s_rowsum[r] + s_rowsum[128 + r];
       const float inv = l > 0.f ? vs / l : 0.f;
       if (row_base + r < n) {
