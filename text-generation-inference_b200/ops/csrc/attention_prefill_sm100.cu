@@ -444,10 +444,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       sa.range = t_max >= t_min ? static_cast<unsigned>(t_max - t_min) : 0u;
       // pass 1: maximum of the (masked) scores of this half
       float mx = -INFINITY;
+      uint32_t v[32];            // after pass 1 it still holds the second 32-key group: pass 2 starts with that one
       if (!fail) {
 #pragma unroll 1
         for (int c = 0; c < 64; c += 32) {
-          uint32_t v[32];
           tmem_ld32(lane_addr + s * 128 + c, v);
           sa.lo = t_max >= t_min ? t_min - (t0 + c) : (1 << 30);
           if (plain) mx = group_max<false, false>(v, mx, sa);
@@ -470,9 +470,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       // key so far has m_new = -inf: every key of it is masked, so the value never reaches P.
       float rs = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(lane_addr + s * 128 + c, v);
+      for (int c = 32; c >= 0; c -= 32) {
+        if (c == 0) tmem_ld32(lane_addr + s * 128, v);
         uint32_t packed[16];
         sa.lo = t_max >= t_min ? t_min - (t0 + c) : (1 << 30);
         if (plain) rs += group_prob<false, false, FP8>(v, packed, m_new, sa);
