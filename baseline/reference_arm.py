@@ -165,11 +165,12 @@ def checkpoint_bytes(m) -> int:
     return body + 2 * m["vocab"] * m["hidden"] * 2
 
 
-def write_checkpoint(path: str, m: dict, max_pos: int, device):
+def write_checkpoint(path: str, m: dict, max_pos: int, device, all_block: bool = False):
     """config.json, tokenizer files and one safetensors file per layer.  Weights are N(0, 0.02) in bf16;
     with ``fp8`` the linear layers are stored as e4m3, the MLPs with one fp32 ``weight_scale_inv`` per 128x128
     block (the DeepSeek-style format the reference reads in ``layers/fp8.py:187-396``), the tensors the
-    reference's Llama cannot read in that format with per-channel scales (see below)."""
+    reference's Llama cannot read in that format with per-channel scales (see below); ``all_block`` stores every
+    linear layer in the block format (a checkpoint for engines that read it everywhere)."""
     import torch
     from safetensors.torch import save_file
 
@@ -224,11 +225,11 @@ def write_checkpoint(path: str, m: dict, max_pos: int, device):
         # layer, inside its `no_fp8` scope, whose loader has no block size (`flash_llama_modeling.py:124-134,
         # 411, 514, 549`): those tensors can only be read as fp8 with a per-output-channel `weight_scale`.
         # All weights stay e4m3 either way, so the bytes a decode step streams are those of the block format.
-        mlp_block = 0 < layer < L - 1
-        linear(t, p + ".self_attn.q_proj", nh * D, H, False)
-        linear(t, p + ".self_attn.k_proj", nkv * D, H, False)
-        linear(t, p + ".self_attn.v_proj", nkv * D, H, False)
-        linear(t, p + ".self_attn.o_proj", H, nh * D, False)
+        mlp_block = all_block or 0 < layer < L - 1
+        linear(t, p + ".self_attn.q_proj", nh * D, H, all_block)
+        linear(t, p + ".self_attn.k_proj", nkv * D, H, all_block)
+        linear(t, p + ".self_attn.v_proj", nkv * D, H, all_block)
+        linear(t, p + ".self_attn.o_proj", H, nh * D, all_block)
         linear(t, p + ".mlp.gate_proj", I, H, mlp_block)
         linear(t, p + ".mlp.up_proj", I, H, mlp_block)
         linear(t, p + ".mlp.down_proj", H, I, mlp_block)
