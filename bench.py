@@ -352,6 +352,8 @@ def main():
                        "parallelism": f"tp{world}", "collectives": "none (one GPU)" if world == 1 else ("nccl" if comm is None else "peer-memory kernels"), "block_size": BLOCK_SIZE, "l2": "inputs larger than L2",
                        "timed": "CUDA events around K graph replays, max over ranks",
                        "setup": "fast-setup (random KV, development)" if args.fast_setup else "real prefill",
+                       **({"fp8_gemm": "tcgen05 block-scaled MMA, power-of-two block scales (weights requantised at load)"
+                           if K.fp8_mx() else "per-K-block promotion, checkpoint scales"} if fp8 else {}),
                        **({"moe_skew": args.moe_skew} if args.moe_skew else {}),
                        **({"sampling": "T=0.7 top-p=0.9 rep=1.1"} if args.sampling == "nucleus" else {})},
             "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d_bytes,

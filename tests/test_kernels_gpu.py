@@ -19,6 +19,16 @@ def K():
     return K
 
 
+@pytest.fixture(autouse=True)
+def promote_path_by_default(K):
+    """The kernel tests hand arbitrary (not power-of-two) block scales to the fp8 GEMM: they exercise the promotion
+    path; the scale-factor MMA has its own test, which switches it on."""
+    was = K.fp8_mx()
+    K.set_fp8_mx(False)
+    yield
+    K.set_fp8_mx(was)
+
+
 def dev():
     return torch.device("cuda", 0)
 
@@ -62,6 +72,35 @@ def test_gemm_fp8_block(K, M, N, K_):
         got = K.gemm_fp8_block(xq, xs, wq, ws, max_ctas=ctas)
         no_kernel_error(K)
         torch.testing.assert_close(got.float(), want, atol=3e-2 * math.sqrt(K_ / 512), rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 256, 512), (16, 384, 1024), (100, 512, 2048), (128, 4096, 4096), (256, 1024, 3584),
+                                    (256, 2048, 8192), (513, 768, 1024), (256, 10240, 8192), (64, 8192, 28672),
+                                    (2048, 1280, 8192)])
+def test_gemm_fp8_block_scaled_mma(K, M, N, K_):
+    """Block-scaled fp8 on the scale-factor MMA: activation scales come out of the quantiser as powers of two,
+    weights are requantised to power-of-two block scales, and the product must match the fp32 product of the
+    dequantised operands (whole tiles, K splits and stream-K splits)."""
+    torch.manual_seed(M * 13 + N)
+    x = torch.randn(M, K_, device=dev(), dtype=torch.bfloat16)
+    w = torch.randn(N, K_, device=dev()) * 0.05
+    wq0, ws0 = ref.fp8_quant_block_weight(w)
+    K.set_fp8_mx(True)
+    try:
+        wq, ws = K.requant_block_pow2(wq0, ws0)
+        assert (torch.frexp(ws)[0] == 0.5).all()
+        xq, xs = K.fp8_quant_act(x)
+        assert (torch.frexp(xs)[0] == 0.5).all(), "activation scales are not powers of two"
+        # the power-of-two scale is at most twice the tight one: the row still uses at least half of the e4m3 range
+        deq = xq.float().view(M, K_ // 128, 128) * xs.float().unsqueeze(-1)
+        assert (deq.view(M, K_) - x.float()).abs().max().item() <= 0.07 * x.float().abs().max().item()
+        want = ref.gemm_fp8_block(xq, xs.contiguous(), wq, ws, torch.float32)
+        for ctas in (None, 1, 37):
+            got = K.gemm_fp8_block(xq, xs, wq, ws, max_ctas=ctas)
+            no_kernel_error(K)
+            torch.testing.assert_close(got.float(), want, atol=3e-2 * math.sqrt(K_ / 512), rtol=2e-2)
+    finally:
+        K.set_fp8_mx(False)
 
 
 @pytest.mark.parametrize("pairs", [True, False])

@@ -138,6 +138,11 @@ class Fp8Linear:
             self.dense = FastLinear((qweight.float() * s).to(dtype), bias)
         if not hasattr(self, "channel_scale"):
             self.channel_scale = None
+        if self.block is not None and qweight.is_cuda:
+            from ..ops import cuda as K
+
+            if K.fp8_mx():       # the scale-factor MMA takes power-of-two scales: requantise once
+                self.qweight, self.scale = K.requant_block_pow2(self.qweight, self.scale, self.block)
 
     @property
     def out_features(self):

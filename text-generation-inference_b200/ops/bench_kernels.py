@@ -104,9 +104,12 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--plain", action="store_true", help="time direct launches instead of graph replays")
+    ap.add_argument("--promote", action="store_true",
+                    help="fp8 GEMMs with per-K-block promotion instead of the block-scaled MMA (TGI_B200_FP8_MX=0)")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     K.load()
+    K.set_fp8_mx(not args.promote)
     s = SHAPES[args.model]
     H, D = s["hidden"], s["head_dim"]
     hq, hkv, I = s["heads"] // args.tp, max(1, s["kv_heads"] // args.tp), s["inter"] // args.tp
@@ -139,6 +142,8 @@ def main():
         if args.fp8:
             wq = w.to(FP8)
             ws = torch.rand((N + 127) // 128, Kd // 128, device=dev) + 0.5
+            if K.fp8_mx():
+                wq, ws = K.requant_block_pow2(wq, ws)
             xq, xs = K.fp8_quant_act(x)
             t = timer(lambda: K.gemm_fp8_block(xq, xs, wq, ws))
             report(f"gemm_fp8_{name}[{M}x{N}x{Kd}]", t, N * Kd + M * Kd + 2 * M * N, 2.0 * M * N * Kd)

@@ -24,6 +24,15 @@
 namespace {
 
 constexpr float kFp8Max = 448.f;
+// Scale of a 128-wide activation block.  With g_quant_pow2 set (the block-scaled MMA takes power-of-two scale
+// factors) it is rounded up to the next power of two: the quantised values then use at least half of the e4m3
+// range, which costs no relative precision.
+__device__ int g_quant_pow2 = 0;
+__device__ __forceinline__ float block_scale(float amax) {
+  float s = fmaxf(amax, 1e-12f) / kFp8Max;
+  if (g_quant_pow2) s = __uint_as_float((__float_as_uint(s) + 0x007FFFFFu) & 0xFF800000u);
+  return s;
+}
 
 struct __align__(16) bf16x8 {
   __nv_bfloat162 v[4];
@@ -165,7 +174,7 @@ norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 #pragma unroll
       for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
       amax = group16_max(amax);
-      const float scale = fmaxf(amax, 1e-12f) / kFp8Max;
+      const float scale = block_scale(amax);
       if (active) {
         *reinterpret_cast<uint2*>(q_out + base + v * 8) = quant8(y, scale);
         if ((v & 15) == 0) scale_t[static_cast<size_t>(v >> 4) * scale_pitch + row] = scale;
@@ -219,7 +228,7 @@ act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__
 #pragma unroll
     for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
     amax = group16_max(amax);
-    const float scale = fmaxf(amax, 1e-12f) / kFp8Max;
+    const float scale = block_scale(amax);
     if (active) {
       *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * I + v * 8) = quant8(y, scale);
       if ((v & 15) == 0) scale_t[static_cast<size_t>(v >> 4) * scale_pitch + row] = scale;
@@ -244,7 +253,7 @@ quant_act_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q_ou
 #pragma unroll
   for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
   amax = group16_max(amax);
-  const float scale = fmaxf(amax, 1e-12f) / kFp8Max;
+  const float scale = block_scale(amax);
   if (active) {
     *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * K + v * 8) = quant8(y, scale);
     if ((v & 15) == 0) scale_t[static_cast<size_t>(v >> 4) * scale_pitch + row] = scale;
@@ -955,3 +964,8 @@ int tgi_sample(const void* scores, long long row_stride, int is_fp32, const floa
 }
 
 }  // extern "C"
+
+extern "C" int tgi_quant_set_pow2(int on) {
+  const int v = on != 0;
+  return cudaMemcpyToSymbol(g_quant_pow2, &v, sizeof(v)) == cudaSuccess ? 0 : -3;
+}

@@ -66,7 +66,7 @@ constexpr int kCols = 128;                 // accumulator columns per epilogue t
 constexpr int kTileElems = 256 * 128;      // outputs per tile in both configurations
 constexpr int kBufCols = 256;              // TMEM columns per accumulator buffer (two buffers)
 
-template <int MH, int TN, bool PAIR, bool FP8 = false>
+template <int MH, int TN, bool PAIR, bool FP8 = false, bool MX = false>
 struct TileCfg {
   static_assert(MH * TN == 256, "an accumulator buffer is 256 TMEM columns");
   static_assert(!PAIR || MH == 1, "a pair runs the 128 x 256 per-CTA configuration");
@@ -81,7 +81,7 @@ struct TileCfg {
   // half 0 starts while the MMAs of half 1 still run.  (Splitting the 256 columns of the MH == 1 buffers
   // into 2 or 4 separately signalled column groups was measured slower: 180 -> 195 -> 222 us on
   // 256 x 57344 x 8192, the extra commits and waits of the single issuing thread cost more than they hide.)
-  static constexpr int SUB = (FP8 && MH == 2) ? 2 : 1;
+  static constexpr int SUB = (FP8 && !MX && MH == 2) ? 2 : 1;
 };
 
 // Optional destination of the output rows in peer memory (tensor-parallel row-parallel GEMMs): row m
@@ -185,14 +185,22 @@ struct UnitIter {
 // wscale: weight scales [ceil(N/128), K/128] row-major
 // ws: 2 partial-tile slots per CTA; counters: one int per output tile (self-resetting)
 // ------------------------------------------------------------------------------------------------
-template <int MH, int TN, int STAGES, bool FP8, bool PAIR>
+// MX: block-scaled fp8 on `tcgen05.mma.kind::mxf8f6f4.block_scale`.  Operands, scales and scheduling are those of the
+// fp8 mode, but the two block scales of a K block (powers of two, a precondition of this mode) are handed to the
+// tensor core as E8M0 scale factors in TMEM, so a tile accumulates over all of its K blocks in TMEM like a bf16
+// tile and the per-K-block promotion disappears.  TMEM: one accumulator buffer (columns 0..255) and a ring of
+// scale-factor columns (16 per stage, from column 256): A's rows use 4 columns per 128 tokens, B's 4 per 128
+// weight rows.  Four epilogue warps (one per lane quarter) write a stage's scale factors when its copy has landed.
+template <int MH, int TN, int STAGES, bool FP8, bool PAIR, bool MX = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                     const __grid_constant__ CUtensorMap tmS, const float* __restrict__ wscale,
                     __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
                     float* __restrict__ ws, int* __restrict__ counters, int* __restrict__ status,
                     const __grid_constant__ PushArgs push) {
-  using Cfg = TileCfg<MH, TN, PAIR, FP8>;
+  using Cfg = TileCfg<MH, TN, PAIR, FP8, MX>;
+  static_assert(!MX || (FP8 && !PAIR), "the block-scaled mode is built for fp8 operands and single CTAs");
+  constexpr bool PROMOTE = FP8 && !MX;          // per-K-block promotion in the epilogue warps
   // first element of output row m: in C, or in the owner's peer-memory slot of this rank
   auto out_row = [&](int m) -> __nv_bfloat16* {
     if (push.world == 0) return C + static_cast<size_t>(m) * N;
@@ -216,7 +224,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   constexpr int SUB = Cfg::SUB;              // separately signalled parts of an accumulator buffer
   uint64_t* tmem_full = empty + STAGES;      // [2 * SUB]
   uint64_t* tmem_empty = tmem_full + 8;      // [2 * SUB]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 8);
+  uint64_t* sf_ready = tmem_empty + 8;       // [STAGES] scale factors of the stage written to TMEM (MX)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_ready + 8);
   int* flag = reinterpret_cast<int*>(tmem_holder + 1);
   int* cslots = flag + 1;                    // [kMaxGrid] workspace slot of every contributor of a split tile
   {
@@ -249,6 +258,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+      if (MX) mbar_init(&sf_ready[s], 4);
     }
     for (int b = 0; b < 2 * SUB; ++b) {
       mbar_init(&tmem_full[b], 1);
@@ -330,27 +340,31 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       if (crank == 0 && elect_one()) {
         constexpr int MMA_M = PAIR ? 256 : 128;
         constexpr uint32_t idesc = FP8 ? make_idesc(MMA_M, TN, 0, 0) : make_idesc(MMA_M, TN, 1, 1);
+        constexpr uint32_t kSfCol0 = kBufCols;       // first scale-factor column (MX)
         int seg = 0;        // accumulator uses so far (fp8: one per K block, bf16: one per tile segment)
         UnitIter ui(u0, sch);
         for (int it = 0; it < nunits; ++it, ui.next(sch)) {
           const int kb = ui.kb;
           const bool seg_start = (it == 0) || kb == 0;
           const bool seg_end = (it == nunits - 1) || kb == sch.KB - 1;
-          const int use = FP8 ? it : seg;
-          const int b = use & 1;
-          if (!FP8 && seg_start && use >= 2 && !wait(&tmem_empty[b], ((use >> 1) - 1) & 1)) {
+          const int use = PROMOTE ? it : seg;
+          const int b = MX ? 0 : use & 1;            // MX: a single accumulator buffer
+          if (!PROMOTE && seg_start &&
+              (MX ? (use >= 1 && !wait(&tmem_empty[0], (use - 1) & 1))
+                  : (use >= 2 && !wait(&tmem_empty[b], ((use >> 1) - 1) & 1)))) {
             report(status, kErrMmaWaitAccum);
             break;
           }
           const int s = it % STAGES;
           if (!wait(&full[s], (it / STAGES) & 1)) { report(status, kErrMmaWaitFull); break; }
+          if (MX && !wait(&sf_ready[s], (it / STAGES) & 1)) { report(status, kErrMmaWaitFull); break; }
           tc_fence_after();
           const uint32_t x_addr = smem_u32(smem + s * Cfg::kStageBytes);
           bool acc_ok = true;
           const uint64_t dw = make_desc_sw128(x_addr + Cfg::kXBytes);
 #pragma unroll
           for (int h = 0; h < MH; ++h) {   // token halves
-            if (FP8) {
+            if (PROMOTE) {
               const int p = SUB == 2 ? h : 0;
               if (use >= 2 && !wait(&tmem_empty[b * SUB + p], ((use >> 1) - 1) & 1)) { acc_ok = false; break; }
               tc_fence_after();
@@ -359,8 +373,13 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             const uint32_t d = tmem_base + b * kBufCols + h * TN;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {   // 4 MMAs of 32 bytes of K each per 128-byte row
-              const uint32_t accumulate = FP8 ? (k > 0) : (!seg_start || k > 0);
-              if (PAIR) {
+              const uint32_t accumulate = PROMOTE ? (k > 0) : (!seg_start || k > 0);
+              if (MX) {
+                // scale-factor byte k of the stage's columns: the k-th 32-deep slice of the K block
+                const uint32_t tsf = tmem_base + kSfCol0 + s * 16;
+                mma_mxf8f6f4(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), make_idesc_mx(MMA_M, TN, k, k), tsf + h * 4, tsf + 8,
+                             accumulate);
+              } else if (PAIR) {
                 if (FP8) mma_f8f6f4_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
                 else mma_f16_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
               } else {
@@ -368,7 +387,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 else mma_f16(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
               }
             }
-            if (FP8) {   // hand this part to the epilogue (of both CTAs in a pair)
+            if (PROMOTE) {   // hand this part to the epilogue (of both CTAs in a pair)
               const int p = SUB == 2 ? h : 0;
               if (PAIR) tc_commit_pair(&tmem_full[b * SUB + p], 3);
               else tc_commit(&tmem_full[b * SUB + p]);
@@ -377,10 +396,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           if (!acc_ok) { report(status, kErrMmaWaitAccum); break; }
           if (PAIR) {
             tc_commit_pair(&empty[s], 3);                                  // frees the stage in both CTAs
-            if (!FP8 && seg_end) tc_commit_pair(&tmem_full[b], 3);
+            if (!PROMOTE && seg_end) tc_commit_pair(&tmem_full[b], 3);
           } else {
             tc_commit(&empty[s]);
-            if (!FP8 && seg_end) tc_commit(&tmem_full[b]);
+            if (!PROMOTE && seg_end) tc_commit(&tmem_full[b]);
           }
           if (seg_end) ++seg;
         }
@@ -424,7 +443,35 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         seg_kb0 = kb;
         acc.zero();
       }
-      if (FP8) {
+      if (MX && ew < 4) {
+        // scale factors of this K block into the stage's TMEM columns: rows 32 * blk + lane of an operand go to
+        // column blk of this warp's lane quarter, the block scale's exponent in all four bytes
+        const int s = it % STAGES;
+        ok = wait(&full[s], (it / STAGES) & 1);
+        if (!ok) { report(status, kErrEpilogueWait); break; }
+        const uint32_t tsf = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kBufCols + s * 16;
+        const float* sc = sc_ring + (it % SC_STAGES) * CM;
+#pragma unroll
+        for (int h = 0; h < MH; ++h) {
+          uint32_t w[4];
+#pragma unroll
+          for (int blk = 0; blk < 4; ++blk)
+            w[blk] = ((__float_as_uint(sc[h * 128 + blk * 32 + lane]) >> 23) & 0xFFu) * 0x01010101u;
+          tmem_st_32x32b_x4(tsf + h * 4, w);
+        }
+#pragma unroll
+        for (int j = 0; j < TN / 128; ++j) {
+          const float sw = __ldg(&wscale[static_cast<size_t>((n0 >> 7) + j) * sch.KB + kb]);
+          const uint32_t e = ((__float_as_uint(sw) >> 23) & 0xFFu) * 0x01010101u;
+          const uint32_t w[4] = {e, e, e, e};
+          tmem_st_32x32b_x4(tsf + 8 + j * 4, w);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sf_ready[s]);
+      }
+      if (PROMOTE) {
         const int b = it & 1;
         const int hb = b * SUB + (SUB == 2 ? g : 0);   // g: token half of this warp when MH == 2
         ok = wait(&tmem_full[hb], (it >> 1) & 1);
@@ -448,8 +495,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         __syncwarp();
         if (lane == 0) release_accum(hb);
       } else if (seg_end) {
-        const int b = seg & 1;
-        ok = wait(&tmem_full[b], (seg >> 1) & 1);
+        const int b = MX ? 0 : seg & 1;
+        ok = wait(&tmem_full[b], MX ? (seg & 1) : ((seg >> 1) & 1));
         if (!ok) { report(status, kErrEpilogueWait); break; }
         tc_fence_after();
         if (warp_active) {
@@ -618,11 +665,11 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 // ------------------------------------------------------------------------------------------------
 using tgi::make_map_2d;
 
-template <int MH, int TN, int STAGES, bool FP8, bool PAIR>
+template <int MH, int TN, int STAGES, bool FP8, bool PAIR, bool MX = false>
 int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C,
            const void* bias, int M, int N, int K, int max_ctas, float* ws, int* counters, int* status,
            cudaStream_t stream, const PushArgs* push_args = nullptr) {
-  using Cfg = TileCfg<MH, TN, PAIR, FP8>;
+  using Cfg = TileCfg<MH, TN, PAIR, FP8, MX>;
   PushArgs push;
   if (push_args != nullptr) {
     push = *push_args;
@@ -647,7 +694,7 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
   }
   // stages + (fp8) activation-scale ring [STAGES+2][CM] + alignment slack + barriers
   const size_t smem = STAGES * Cfg::kStageBytes + (FP8 ? (STAGES + 2) * Cfg::CM * 4 : 0) + 1024 + 512 + kMaxGrid * 4;
-  auto kern = gemm_streamk_kernel<MH, TN, STAGES, FP8, PAIR>;
+  auto kern = gemm_streamk_kernel<MH, TN, STAGES, FP8, PAIR, MX>;
   // The shared-memory opt-in is a per-device attribute of the function; the number of CTA pairs that can
   // be resident at once (a GPC with an odd number of usable SMs cannot pair its last one) is a property of
   // the device too.  Both are looked up once per device ordinal.
@@ -741,12 +788,20 @@ int fill_push(PushArgs& p, void* const* heaps, int rank, int world, int rows_per
 static int g_wide_m = 128;
 static int g_pairs = 1;
 static int g_pair_min_tiles = 32;
+static int g_fp8_mx = 0;          // block-scaled MMA for fp8 (scales must be powers of two)
 
 namespace {
 template <bool FP8>
 int dispatch(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C, const void* bias,
              int M, int N, int K, int max_ctas, float* ws, int* counters, int* status, cudaStream_t stream,
              const PushArgs* push) {
+  if (FP8 && g_fp8_mx) {
+    if (M <= g_wide_m)
+      return launch<1, 256, 4, FP8, false, FP8>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters,
+                                                 status, stream, push);
+    return launch<2, 128, 4, FP8, false, FP8>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status,
+                                               stream, push);
+  }
   if (M <= g_wide_m)
     return launch<1, 256, 4, FP8, false>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status,
                                          stream, push);
@@ -784,6 +839,9 @@ int tgi_gemm_num_tiles(int M, int N) {
 // 256 x 256 tiles, or single CTAs on 256 x 128 tiles when pairs are switched off.
 void tgi_gemm_set_wide_m(int m) { g_wide_m = m < 128 ? 128 : m; }
 void tgi_gemm_set_pairs(int on) { g_pairs = on != 0; }
+// fp8 GEMMs on the block-scaled MMA: every activation and weight scale handed to tgi_gemm_fp8_block must then be a
+// power of two (their exponents become the E8M0 scale factors; mantissa bits are ignored)
+void tgi_gemm_set_fp8_mx(int on) { g_fp8_mx = on != 0; }
 void tgi_gemm_set_pair_min_tiles(int n) { g_pair_min_tiles = n < 1 ? 1 : n; }
 // CTAs of the most recent GEMM launch of this process (diagnostics and benchmarks).
 int tgi_gemm_last_grid(void) { return g_last_grid; }

@@ -30,6 +30,15 @@ namespace {
 constexpr int kMaxRanks = 8;
 constexpr int kMaxBlocks = 256;           // flag slots per phase
 constexpr float kFp8Max = 448.f;
+// Scale of a 128-wide activation block.  With g_quant_pow2 set (the block-scaled MMA takes power-of-two scale
+// factors) it is rounded up to the next power of two: the quantised values then use at least half of the e4m3
+// range, which costs no relative precision.
+__device__ int g_quant_pow2 = 0;
+__device__ __forceinline__ float block_scale(float amax) {
+  float s = fmaxf(amax, 1e-12f) / kFp8Max;
+  if (g_quant_pow2) s = __uint_as_float((__float_as_uint(s) + 0x007FFFFFu) & 0xFF800000u);
+  return s;
+}
 // Default limit of a wait on a flag that another rank writes.  The limit travels as a kernel argument so
 // that a test can make it short (tgi_peer_set_wait_ns) and watch a wait run out: a flag that nothing sets
 // ends the kernel with status kErrPeerWait after that time, the context stays usable.
@@ -311,7 +320,7 @@ peer_reduce_kernel(const PeerArgs a) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
             amax = group16_max(amax);
-            const float scale = fmaxf(amax, 1e-12f) / kFp8Max;
+            const float scale = block_scale(amax);
             if (active) {
               const uint2 q = quant8(y, scale);
 #pragma unroll
@@ -900,3 +909,8 @@ int tgi_peer_sample(void* const* heaps, int rank, int world, const void* scores,
 long long tgi_peer_sample_xchg_bytes() { return static_cast<long long>(kMaxBlocks) * 2 * kXWords * kMaxRanks * 8; }
 
 }  // extern "C"
+
+extern "C" int tgi_peer_set_quant_pow2(int on) {
+  const int v = on != 0;
+  return cudaMemcpyToSymbol(g_quant_pow2, &v, sizeof(v)) == cudaSuccess ? 0 : -3;
+}

@@ -188,6 +188,42 @@ __device__ __forceinline__ void mma_f8f6f4(uint32_t tmem_d, uint64_t desc_a, uin
       : "memory");
 }
 
+// Block-scaled fp8 MMA (`kind::mxf8f6f4`): every 32 K elements of a row of A and of B carry one E8M0 scale factor
+// (a power of two) that the tensor core applies, so products of differently scaled K blocks accumulate in TMEM.
+// The scale factors live in TMEM: rows 32*blk + i of an operand sit in lane i (replicated in the four lane
+// quarters) of column `tsf + blk`, one byte per 32-deep K slice, selected by the descriptor's scale-factor ids
+// (layout: cute/atom/mma_traits_sm100.hpp `tmem_sf_frg`; instruction form: cute/arch/mma_sm100_umma.hpp
+// `SM100_MMA_MXF8F6F4_SS`; descriptor: cute/arch/mma_sm100_desc.hpp `InstrDescriptorBlockScaled`).
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t m, uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return (b_sf_id << 4)         // scale-factor byte of B
+         | (0u << 7)            // a_format = E4M3
+         | (0u << 10)           // b_format = E4M3
+         | (0u << 15)           // a_major = K
+         | (0u << 16)           // b_major = K
+         | ((n >> 3) << 17)     // n_dim
+         | (1u << 23)           // scale format = E8M0
+         | ((m >> 4) << 24)     // m_dim
+         | (a_sf_id << 29);     // scale-factor byte of A
+}
+__device__ __forceinline__ void mma_mxf8f6f4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+// registers -> TMEM: each thread of the warp writes 4 (8) consecutive 32-bit columns of its own lane
+__device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // TMEM -> registers: each thread of the warp reads 32 consecutive fp32 columns of its own lane.
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(

@@ -52,7 +52,8 @@ def load():
                  "tgi_rope_cache", "tgi_embedding", "tgi_argmax_logprob", "tgi_paged_attention", "tgi_paged_attention_ex",
                  "tgi_gemm_num_tiles", "tgi_attn_decode_splits", "tgi_attn_status", "tgi_lora_shrink",
                  "tgi_lora_expand", "tgi_moe_topk_softmax", "tgi_moe_sort", "tgi_moe_gather", "tgi_moe_grouped_gemm",
-                 "tgi_moe_combine", "tgi_gemm_last_grid", "tgi_penalties", "tgi_gemm_wq", "tgi_wq_dequant", "tgi_qk_norm"):
+                 "tgi_moe_combine", "tgi_gemm_last_grid", "tgi_penalties", "tgi_gemm_wq", "tgi_wq_dequant", "tgi_qk_norm",
+                 "tgi_quant_set_pow2", "tgi_peer_set_quant_pow2"):
         getattr(_LIB, name).restype = c_int
     _LIB.tgi_gemm_workspace_floats.restype = c_ll
     wide = os.environ.get("TGI_B200_GEMM_WIDE_M")
@@ -60,7 +61,53 @@ def load():
         _LIB.tgi_gemm_set_wide_m(c_int(int(wide)))
     if os.environ.get("TGI_B200_GEMM_PAIRS", "1") == "0":   # single-CTA 256 x 128 tiles instead of CTA pairs
         _LIB.tgi_gemm_set_pairs(c_int(0))
+    # fp8 GEMMs run on the block-scaled MMA unless TGI_B200_FP8_MX=0 (then: per-K-block promotion, arbitrary scales)
+    if os.environ.get("TGI_B200_FP8_MX", "1") == "1" and torch.cuda.is_available():
+        set_fp8_mx(True)
     return _LIB
+
+
+_FP8_MX = False
+
+
+def set_fp8_mx(on: bool) -> None:
+    """Block-scaled fp8 GEMMs on ``tcgen05.mma.kind::mxf8f6f4``: the tensor core applies the block scales, so they
+    must be powers of two.  Switching it on makes every activation-quantising kernel round its scales up to a power
+    of two; block-scaled weights have to be brought to power-of-two scales once (``requant_block_pow2``, done by
+    ``Fp8Linear`` at load)."""
+    global _FP8_MX
+    lib = _LIB if _LIB is not None else load()
+    v = c_int(1 if on else 0)
+    lib.tgi_gemm_set_fp8_mx(v)
+    _check(lib.tgi_quant_set_pow2(v), "quant_set_pow2")
+    _check(lib.tgi_peer_set_quant_pow2(v), "peer_set_quant_pow2")
+    _FP8_MX = bool(on)
+    from . import reference
+
+    reference.POW2_ACT_SCALES = bool(on)     # the PyTorch oracle quantises the same way
+
+
+def fp8_mx() -> bool:
+    return _FP8_MX
+
+
+def requant_block_pow2(wq: torch.Tensor, scale: torch.Tensor, block: int = 128):
+    """e4m3 weights ``[N, K]`` with one scale per ``block x block`` tile -> the same matrix with every scale rounded
+    up to a power of two and the values re-rounded to e4m3 (``w * s = w' * s'`` up to that rounding).  Engines that
+    feed block-scaled checkpoints to Blackwell's scale-factor MMA do the same (it takes E8M0 scale factors)."""
+    scale = scale.float()
+    mant, expo = torch.frexp(scale)                      # scale = mant * 2^expo, mant in [0.5, 1)
+    s2 = torch.where(mant == 0.5, scale, torch.ldexp(torch.ones_like(scale), expo))
+    ratio = scale / s2                                   # in (0.5, 1]
+    N, K = wq.shape
+    out = torch.empty_like(wq)
+    rows = max(block, (1 << 26) // max(K, 1) // block * block)     # chunks of about 64 M elements
+    for r0 in range(0, N, rows):
+        r1 = min(N, r0 + rows)
+        rr = ratio[r0 // block:(r1 + block - 1) // block].repeat_interleave(block, 0)[:r1 - r0]
+        rr = rr.repeat_interleave(block, 1)[:, :K]
+        out[r0:r1] = (wq[r0:r1].float() * rr).to(wq.dtype)
+    return out, s2.contiguous()
 
 
 def set_gemm_pairs(on: bool) -> None:

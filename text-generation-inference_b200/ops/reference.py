@@ -224,6 +224,9 @@ def fp8_quant_block_weight(w: torch.Tensor, block: int = 128) -> Tuple[torch.Ten
     return q.to(FP8).contiguous(), scale.contiguous()
 
 
+POW2_ACT_SCALES = False      # activation block scales rounded up to powers of two
+
+
 def fp8_quant_act(x: torch.Tensor, group: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
     """Dynamic per-token, per-``group``-columns quantisation: ``x[T,K] ~= xq * scale[T, K/group]``."""
     T, K = x.shape
@@ -231,6 +234,9 @@ def fp8_quant_act(x: torch.Tensor, group: int = 128) -> Tuple[torch.Tensor, torc
     xg = x.float().view(T, K // group, group)
     amax = xg.abs().amax(dim=-1).clamp_min(1e-12)
     scale = amax / FP8_MAX
+    if POW2_ACT_SCALES:      # what the kernels do while the block-scaled MMA is in use (ops.cuda.set_fp8_mx)
+        mant, expo = torch.frexp(scale)
+        scale = torch.where(mant == 0.5, scale, torch.ldexp(torch.ones_like(scale), expo))
     q = (xg / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).view(T, K)
     return q.to(FP8), scale.contiguous()
 
