@@ -224,8 +224,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   constexpr int SUB = Cfg::SUB;              // separately signalled parts of an accumulator buffer
   uint64_t* tmem_full = empty + STAGES;      // [2 * SUB]
   uint64_t* tmem_empty = tmem_full + 8;      // [2 * SUB]
-  uint64_t* sf_ready = tmem_empty + 8;       // [STAGES] scale factors of the stage written to TMEM (MX)
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_ready + 8);
+  uint64_t* sf_ready = tmem_empty + 8;       // [2 * STAGES] scale factors of a K block written to TMEM (MX)
+  uint64_t* sc_full = sf_ready + 16;         // [SC_STAGES] activation scales of a K block landed (MX)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sc_full + 8);
   int* flag = reinterpret_cast<int*>(tmem_holder + 1);
   int* cslots = flag + 1;                    // [kMaxGrid] workspace slot of every contributor of a split tile
   {
@@ -258,8 +259,13 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      if (MX) mbar_init(&sf_ready[s], 4);
+      if (MX) {
+        mbar_init(&sf_ready[s], 4);
+        mbar_init(&sf_ready[STAGES + s], 4);
+      }
     }
+    if (MX)
+      for (int s = 0; s < SC_STAGES; ++s) mbar_init(&sc_full[s], 1);
     for (int b = 0; b < 2 * SUB; ++b) {
       mbar_init(&tmem_full[b], 1);
       // a part is drained by the four warps (one per lane quarter) of one epilogue group, the whole buffer by all eight
@@ -309,14 +315,17 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           if (it >= STAGES) ok = wait(&empty[s], ((it / STAGES) - 1) & 1);
           if (!ok) { report(status, kErrProducerWait); break; }
           uint8_t* st = smem + s * Cfg::kStageBytes;
-          constexpr uint32_t kCtaBytes = Cfg::kStageBytes + (FP8 ? CM * 4 : 0);
+          // MX: with a stage go the activation scales of the K block AFTER its own (with the first stage also its
+          // own), on barriers of their own, so that a K block's scale factors are in TMEM before its operands land
+          const bool sc_next = MX && it + 1 < nunits;
+          constexpr uint32_t kCtaBytes = Cfg::kStageBytes + (PROMOTE ? CM * 4 : 0);
           if (PAIR) {
             // both CTAs' bytes are counted on the leader's barrier; only the leader posts the expectation
             const uint32_t bar = full0_remote + s * 8;
             if (crank == 0) mbar_arrive_expect_tx(&full[s], 2 * kCtaBytes);
             tma_load_2d_pair_hint(st, &tmX, bar, kb * BK, m0 + static_cast<int>(crank) * CM, pol_x);
             tma_load_2d_pair_hint(st + Cfg::kXBytes, &tmW, bar, kb * BK, n0 + static_cast<int>(crank) * Cfg::WROWS, pol_w);
-            if (FP8) tma_load_2d_pair(sc_ring + (it % SC_STAGES) * CM, &tmS, bar, m0 + static_cast<int>(crank) * CM, kb);
+            if (PROMOTE) tma_load_2d_pair(sc_ring + (it % SC_STAGES) * CM, &tmS, bar, m0 + static_cast<int>(crank) * CM, kb);
           } else {
             mbar_arrive_expect_tx(&full[s], kCtaBytes);
 #pragma unroll
@@ -324,7 +333,22 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
             for (int h = 0; h < TN / 128; ++h)
               tma_load_2d_hint(st + Cfg::kXBytes + h * 16384, &tmW, &full[s], kb * BK, n0 + h * 128, pol_w);
-            if (FP8) tma_load_2d(sc_ring + (it % SC_STAGES) * TM, &tmS, &full[s], m0, kb);
+            if (PROMOTE) tma_load_2d(sc_ring + (it % SC_STAGES) * TM, &tmS, &full[s], m0, kb);
+            if (MX) {
+              if (it == 0) {
+                mbar_arrive_expect_tx(&sc_full[0], CM * 4);
+                tma_load_2d(sc_ring, &tmS, &sc_full[0], m0, kb);
+              }
+              if (sc_next) {
+                // the slot's previous scales (K block it - STAGES - 1) were turned into scale factors before the MMAs
+                // of K block it - STAGES could run, and those are complete (this stage was free)
+                UnitIter nxt = ui;
+                nxt.next(sch);
+                const int slot = (it + 1) % SC_STAGES;
+                mbar_arrive_expect_tx(&sc_full[slot], CM * 4);
+                tma_load_2d(sc_ring + slot * TM, &tmS, &sc_full[slot], nxt.tm * TM, nxt.kb);
+              }
+            }
           }
           issued = it + 1;
         }
@@ -333,6 +357,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           // the cluster barrier at the end additionally keeps both CTAs alive until both producers are done)
           for (int it = max(0, issued - STAGES); it < issued; ++it)
             mbar_wait(&full[it % STAGES], (it / STAGES) & 1, 1u << 12);
+          if (MX)      // the scale copies that went out with the last stages
+            for (int j = max(0, issued - 1); j <= issued; ++j) mbar_wait(&sc_full[j % SC_STAGES], (j / SC_STAGES) & 1, 1u << 12);
         }
       }
     } else if (warp == 1) {
@@ -357,7 +383,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           }
           const int s = it % STAGES;
           if (!wait(&full[s], (it / STAGES) & 1)) { report(status, kErrMmaWaitFull); break; }
-          if (MX && !wait(&sf_ready[s], (it / STAGES) & 1)) { report(status, kErrMmaWaitFull); break; }
+          const int sfs = it % (2 * STAGES);      // scale-factor slot: a ring twice as long as the stages
+          if (MX && !wait(&sf_ready[sfs], (it / (2 * STAGES)) & 1)) { report(status, kErrMmaWaitFull); break; }
           tc_fence_after();
           const uint32_t x_addr = smem_u32(smem + s * Cfg::kStageBytes);
           bool acc_ok = true;
@@ -376,7 +403,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
               const uint32_t accumulate = PROMOTE ? (k > 0) : (!seg_start || k > 0);
               if (MX) {
                 // scale-factor byte k of the stage's columns: the k-th 32-deep slice of the K block
-                const uint32_t tsf = tmem_base + kSfCol0 + s * 16;
+                const uint32_t tsf = tmem_base + kSfCol0 + sfs * 16;
                 mma_mxf8f6f4(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), make_idesc_mx(MMA_M, TN, k, k), tsf + h * 4, tsf + 8,
                              accumulate);
               } else if (PAIR) {
@@ -446,10 +473,14 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       if (MX && ew < 4) {
         // scale factors of this K block into the stage's TMEM columns: rows 32 * blk + lane of an operand go to
         // column blk of this warp's lane quarter, the block scale's exponent in all four bytes
-        const int s = it % STAGES;
-        ok = wait(&full[s], (it / STAGES) & 1);
+        // The scales of K block `it` were requested together with the copies of K block `it - 1` (the first with its
+        // own), so this write is done before the block's operands land.  The scale-factor ring is 2 * STAGES long:
+        // the scales of block `it` are requested when the MMAs of block `it - 1 - STAGES` are complete, which
+        // covers the slot's previous user `it - 2 * STAGES`.
+        ok = wait(&sc_full[it % SC_STAGES], (it / SC_STAGES) & 1);
         if (!ok) { report(status, kErrEpilogueWait); break; }
-        const uint32_t tsf = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kBufCols + s * 16;
+        const int sfs = it % (2 * STAGES);
+        const uint32_t tsf = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kBufCols + sfs * 16;
         const float* sc = sc_ring + (it % SC_STAGES) * CM;
 #pragma unroll
         for (int h = 0; h < MH; ++h) {
@@ -469,7 +500,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sf_ready[s]);
+        if (lane == 0) mbar_arrive(&sf_ready[sfs]);
       }
       if (PROMOTE) {
         const int b = it & 1;
