@@ -103,6 +103,33 @@ def test_gemm_fp8_block_scaled_mma(K, M, N, K_):
         K.set_fp8_mx(False)
 
 
+@pytest.mark.parametrize("M,N,K_", [(129, 256, 256), (256, 256, 128), (256, 130 * 8, 512), (257, 7168, 8192),
+                                    (512, 28672, 1024), (2048, 1280, 8192)])
+def test_gemm_fp8_block_scaled_mma_on_cta_pairs(K, M, N, K_):
+    """The scale-factor MMA on 256 x 256 pair tiles: each CTA writes the scale factors of its own tokens and of all
+    256 weight rows into its TMEM."""
+    torch.manual_seed(M + 3 * N + K_)
+    x = torch.randn(M, K_, device=dev(), dtype=torch.bfloat16)
+    w = torch.randn(N, K_, device=dev()) * 0.05
+    wq0, ws0 = ref.fp8_quant_block_weight(w)
+    lib = K.load()
+    K.set_fp8_mx(True)
+    lib.tgi_gemm_set_mx_pairs(1)
+    lib.tgi_gemm_set_pair_min_tiles(1)
+    try:
+        wq, ws = K.requant_block_pow2(wq0, ws0)
+        xq, xs = K.fp8_quant_act(x)
+        want = ref.gemm_fp8_block(xq, xs.contiguous(), wq, ws, torch.float32)
+        for ctas in (None, 2, 38):
+            got = K.gemm_fp8_block(xq, xs, wq, ws, max_ctas=ctas)
+            no_kernel_error(K)
+            assert lib.tgi_gemm_last_grid() % 2 == 0, "the launch did not use CTA pairs"
+            torch.testing.assert_close(got.float(), want, atol=3e-2 * math.sqrt(K_ / 512), rtol=2e-2)
+    finally:
+        lib.tgi_gemm_set_pair_min_tiles(32)
+        K.set_fp8_mx(False)
+
+
 @pytest.mark.parametrize("pairs", [True, False])
 @pytest.mark.parametrize("M,N,K_", [(129, 256, 256), (256, 256, 128), (256, 130 * 8, 512), (257, 7168, 8192),
                                     (512, 28672, 1024), (2048, 1280, 8192)])

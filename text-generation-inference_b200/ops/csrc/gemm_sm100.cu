@@ -199,7 +199,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     float* __restrict__ ws, int* __restrict__ counters, int* __restrict__ status,
                     const __grid_constant__ PushArgs push) {
   using Cfg = TileCfg<MH, TN, PAIR, FP8, MX>;
-  static_assert(!MX || (FP8 && !PAIR), "the block-scaled mode is built for fp8 operands and single CTAs");
+  static_assert(!MX || FP8, "the block-scaled mode is built for fp8 operands");
   constexpr bool PROMOTE = FP8 && !MX;          // per-K-block promotion in the epilogue warps
   // first element of output row m: in C, or in the owner's peer-memory slot of this rank
   auto out_row = [&](int m) -> __nv_bfloat16* {
@@ -260,8 +260,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
       if (MX) {
-        mbar_init(&sf_ready[s], 4);
-        mbar_init(&sf_ready[STAGES + s], 4);
+        mbar_init(&sf_ready[s], PAIR ? 8 : 4);            // four writer warps per CTA
+        mbar_init(&sf_ready[STAGES + s], PAIR ? 8 : 4);
       }
     }
     if (MX)
@@ -293,6 +293,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   // cluster addresses of the barriers that live in the leading CTA
   const uint32_t full0_remote = PAIR ? map_to_cta(smem_u32(&full[0]), 0) : 0u;
   const uint32_t tmem_empty0_remote = PAIR ? map_to_cta(smem_u32(&tmem_empty[0]), 0) : 0u;
+  const uint32_t sf_ready0_remote = (PAIR && MX) ? map_to_cta(smem_u32(&sf_ready[0]), 0) : 0u;
   // Barrier set-up, TMEM allocation and descriptor prefetch above touch no tensor data, so they overlap
   // with the tail of the previous kernel; from here on the operands (and the workspace) are used.
   tgi::pdl_wait();
@@ -326,6 +327,19 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             tma_load_2d_pair_hint(st, &tmX, bar, kb * BK, m0 + static_cast<int>(crank) * CM, pol_x);
             tma_load_2d_pair_hint(st + Cfg::kXBytes, &tmW, bar, kb * BK, n0 + static_cast<int>(crank) * Cfg::WROWS, pol_w);
             if (PROMOTE) tma_load_2d_pair(sc_ring + (it % SC_STAGES) * CM, &tmS, bar, m0 + static_cast<int>(crank) * CM, kb);
+            if (MX) {      // every CTA fetches the scales of its own token rows, on its own barriers
+              if (it == 0) {
+                mbar_arrive_expect_tx(&sc_full[0], CM * 4);
+                tma_load_2d(sc_ring, &tmS, &sc_full[0], m0 + static_cast<int>(crank) * CM, kb);
+              }
+              if (sc_next) {
+                UnitIter nxt = ui;
+                nxt.next(sch);
+                const int slot = (it + 1) % SC_STAGES;
+                mbar_arrive_expect_tx(&sc_full[slot], CM * 4);
+                tma_load_2d(sc_ring + slot * CM, &tmS, &sc_full[slot], nxt.tm * TM + static_cast<int>(crank) * CM, nxt.kb);
+              }
+            }
           } else {
             mbar_arrive_expect_tx(&full[s], kCtaBytes);
 #pragma unroll
@@ -404,8 +418,12 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
               if (MX) {
                 // scale-factor byte k of the stage's columns: the k-th 32-deep slice of the K block
                 const uint32_t tsf = tmem_base + kSfCol0 + sfs * 16;
-                mma_mxf8f6f4(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), make_idesc_mx(MMA_M, TN, k, k), tsf + h * 4, tsf + 8,
-                             accumulate);
+                if (PAIR)
+                  mma_mxf8f6f4_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), make_idesc_mx(MMA_M, TN, k, k), tsf + h * 4,
+                                    tsf + 8, accumulate);
+                else
+                  mma_mxf8f6f4(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), make_idesc_mx(MMA_M, TN, k, k), tsf + h * 4, tsf + 8,
+                               accumulate);
               } else if (PAIR) {
                 if (FP8) mma_f8f6f4_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
                 else mma_f16_pair(d, dx + (k * 32 >> 4), dw + (k * 32 >> 4), idesc, accumulate);
@@ -500,7 +518,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sf_ready[sfs]);
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_remote(sf_ready0_remote + sfs * 8);      // the leading CTA issues the MMAs
+          else mbar_arrive(&sf_ready[sfs]);
+        }
       }
       if (PROMOTE) {
         const int b = it & 1;
@@ -696,6 +717,8 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 // ------------------------------------------------------------------------------------------------
 using tgi::make_map_2d;
 
+int g_streamk_small = 0;   // 1: problems with fewer tiles than workers may also be spread by stream-K
+
 template <int MH, int TN, int STAGES, bool FP8, bool PAIR, bool MX = false>
 int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const float* wscale, void* C,
            const void* bias, int M, int N, int K, int max_ctas, float* ws, int* counters, int* status,
@@ -782,6 +805,10 @@ int launch(const void* X, const float* xs_t, int xs_pitch, const void* W, const 
     const double kUnit = 0.4, kPartial = 0.05, kSync = 3.0;
     const double partials_sk = static_cast<double>(grid + tiles < 2 * grid ? grid + tiles : 2 * grid);
     double best = static_cast<double>((units + grid - 1) / grid) * kUnit + partials_sk * kPartial + kSync;
+    // Measured on B200, aligned splits win wherever both apply: 256 x 10240 x 8192 bf16 51.1 us against 64.4 with
+    // stream-K, 256 x 8192 x 8192 46.5 against 54.4, 32 x 8192 x 28672 fp8 53.0 against 63.9, fp8 pairs 256 x 10240 x
+    // 8192 36.1 against 54.3.  So stream-K is left to problems with more tiles than workers unless it is asked for.
+    if (!g_streamk_small) best = 1e30;
     for (int s = 1; s <= max_workers / tiles && s <= KBn; ++s) {
       const double c = static_cast<double>((KBn + s - 1) / s) * kUnit + (s > 1 ? tiles * s * kPartial + kSync : 0.0);
       if (c < best) {
@@ -820,6 +847,7 @@ static int g_wide_m = 128;
 static int g_pairs = 1;
 static int g_pair_min_tiles = 32;
 static int g_fp8_mx = 0;          // block-scaled MMA for fp8 (scales must be powers of two)
+static int g_mx_pairs = 1;        // CTA pairs in the block-scaled mode
 
 namespace {
 template <bool FP8>
@@ -830,6 +858,16 @@ int dispatch(const void* X, const float* xs_t, int xs_pitch, const void* W, cons
     if (M <= g_wide_m)
       return launch<1, 256, 4, FP8, false, FP8>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters,
                                                  status, stream, push);
+    const long long mx_pair_tiles = static_cast<long long>((N + 255) / 256) * ((M + 255) / 256);
+    // pairs need enough work to repay their fixed cost: 256 x 8192 x 4096 (32 tiles of 32 K blocks) takes 30.7 us in
+    // pairs and 25.6 us on single CTAs, 256 x 8192 x 8192 37.1 against 38.3, 256 x 8192 x 14336 47.5 against 51.2
+    const long long mx_pair_units = mx_pair_tiles * ((K + 127) / 128);
+    if (g_pairs && g_mx_pairs && max_ctas >= 2 && mx_pair_tiles >= g_pair_min_tiles &&
+        (mx_pair_units >= 2048 || g_pair_min_tiles < 32)) {
+      const int rc = launch<1, 256, 6, FP8, FP8, FP8>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters,
+                                                       status, stream, push);
+      if (rc != -4) return rc;
+    }
     return launch<2, 128, 4, FP8, false, FP8>(X, xs_t, xs_pitch, W, wscale, C, bias, M, N, K, max_ctas, ws, counters, status,
                                                stream, push);
   }
@@ -873,6 +911,8 @@ void tgi_gemm_set_pairs(int on) { g_pairs = on != 0; }
 // fp8 GEMMs on the block-scaled MMA: every activation and weight scale handed to tgi_gemm_fp8_block must then be a
 // power of two (their exponents become the E8M0 scale factors; mantissa bits are ignored)
 void tgi_gemm_set_fp8_mx(int on) { g_fp8_mx = on != 0; }
+void tgi_gemm_set_mx_pairs(int on) { g_mx_pairs = on != 0; }
+void tgi_gemm_set_streamk_small(int on) { g_streamk_small = on != 0; }
 void tgi_gemm_set_pair_min_tiles(int n) { g_pair_min_tiles = n < 1 ? 1 : n; }
 // CTAs of the most recent GEMM launch of this process (diagnostics and benchmarks).
 int tgi_gemm_last_grid(void) { return g_last_grid; }

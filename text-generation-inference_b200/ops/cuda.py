@@ -61,6 +61,10 @@ def load():
         _LIB.tgi_gemm_set_wide_m(c_int(int(wide)))
     if os.environ.get("TGI_B200_GEMM_PAIRS", "1") == "0":   # single-CTA 256 x 128 tiles instead of CTA pairs
         _LIB.tgi_gemm_set_pairs(c_int(0))
+    if os.environ.get("TGI_B200_MX_PAIRS", "1") == "0":       # block-scaled mode on single CTAs only
+        _LIB.tgi_gemm_set_mx_pairs(c_int(0))
+    if os.environ.get("TGI_B200_GEMM_STREAMK_SMALL", "0") == "1":   # stream-K also below one tile per worker
+        _LIB.tgi_gemm_set_streamk_small(c_int(1))
     # fp8 GEMMs run on the block-scaled MMA unless TGI_B200_FP8_MX=0 (then: per-K-block promotion, arbitrary scales)
     if os.environ.get("TGI_B200_FP8_MX", "1") == "1" and torch.cuda.is_available():
         set_fp8_mx(True)
