@@ -76,3 +76,28 @@ def test_fallback_runner_matches_transformers_generate(tmp_path, arch):
             ref = hf.generate(ids, max_new_tokens=n_new, min_new_tokens=n_new, do_sample=False)
         want = ref[0, (1 if arch == "t5" else ids.shape[1]):].tolist()
         assert got[i] == want[:n_new], (arch, i, got[i], want)
+
+
+@pytest.mark.parametrize("arch", ["bloom", "opt"])
+def test_fallback_runner_tensor_parallel(tmp_path, arch):
+    """Two gloo ranks: column-parallel q / k / v and first MLP layer, row-parallel output projections, Bloom's ALiBi
+    bias cut to the rank's heads; greedy tokens equal those of the unsharded transformers model."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    torch.manual_seed(0)
+    V = 300
+    if arch == "bloom":
+        hf = transformers.BloomForCausalLM(transformers.BloomConfig(vocab_size=V, hidden_size=32, n_layer=2, n_head=4))
+    else:
+        hf = transformers.OPTForCausalLM(transformers.OPTConfig(
+            vocab_size=V, hidden_size=32, ffn_dim=64, num_hidden_layers=2, num_attention_heads=4, word_embed_proj_dim=32,
+            max_position_embeddings=64, pad_token_id=0, eos_token_id=1, bos_token_id=2))
+    _save(hf.eval(), tmp_path, V)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", DIST_WORKER_DIR=str(tmp_path), PYTHONPATH=root)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(29851 + (arch == "opt")), os.path.join(root, "tests", "dist_padded_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "DIST_WORKER_OK" in r.stdout, (r.stdout[-1500:], r.stderr[-3000:])

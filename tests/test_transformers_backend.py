@@ -57,6 +57,25 @@ def test_transformers_backend_matches_generate(tmp_path, arch):
         assert got[i] == ref[0, ids.shape[1]:].tolist()[:n_new], (arch, i)
 
 
+@pytest.mark.parametrize("arch", ["olmo2", "glm", "helium"])
+def test_transformers_backend_tensor_parallel(tmp_path, arch):
+    """Two gloo ranks: helium shards the heads (column-parallel q / k / v), olmo2 gathers q / k / v for its norms over
+    all heads, glm gathers its fused gate_up; all three must match the unsharded transformers model."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    torch.manual_seed(0)
+    _tiny(arch).eval().save_pretrained(str(tmp_path), safe_serialization=True)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", DIST_WORKER_DIR=str(tmp_path), PYTHONPATH=root)
+    port = 29831 + ["olmo2", "glm", "helium"].index(arch)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(root, "tests", "dist_tfb_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "DIST_WORKER_OK" in r.stdout, (r.stdout[-1500:], r.stderr[-3000:])
+
+
 def test_unsupported_models_still_fall_back():
     assert not supports({"model_type": "stablelm"})
     assert not supports({"model_type": "no_such_model"})

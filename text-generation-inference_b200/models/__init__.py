@@ -101,7 +101,7 @@ def get_model(
 
         return load_vlm(path, cfg, loader, process_group, rank, world, tdtype, device, tokenizer, speculate,
                         kv_cache_dtype, max_prefill_tokens)
-    if model_type not in ARCHS and world == 1 and os.environ.get("TGI_B200_TRANSFORMERS_BACKEND", "1") == "1":
+    if model_type not in ARCHS and os.environ.get("TGI_B200_TRANSFORMERS_BACKEND", "1") == "1":
         # unknown architecture whose transformers implementation goes through the attention interface: its
         # own modules run around the paged attention (continuous batching, prefix caching, chunking kept)
         from . import transformers_backend

@@ -233,16 +233,70 @@ class PaddedSeq2SeqLM(PaddedCausalLM):
         return out.logits[0, -1], out.logits[0] if len(s.ids) == 1 else None
 
 
+# Tensor-parallel plans for model types whose transformers config carries none (module names inside the base model).
+# The reference shards these families in its own modelling files (``custom_modeling/opt_modeling.py``,
+# ``bloom_modeling.py``): column-parallel q / k / v and first MLP layer, row-parallel output projections.
+PADDED_TP = {
+    "opt": dict(plan={"decoder.layers.*.self_attn.q_proj": "colwise", "decoder.layers.*.self_attn.k_proj": "colwise",
+                      "decoder.layers.*.self_attn.v_proj": "colwise", "decoder.layers.*.self_attn.out_proj": "rowwise",
+                      "decoder.layers.*.fc1": "colwise", "decoder.layers.*.fc2": "rowwise"},
+                alibi=False),
+    # the fused query_key_value is laid out [head, (q, k, v), head_dim]: a contiguous slice of rows is a slice of heads
+    "bloom": dict(plan={"h.*.self_attention.query_key_value": "colwise", "h.*.self_attention.dense": "rowwise",
+                        "h.*.mlp.dense_h_to_4h": "colwise", "h.*.mlp.dense_4h_to_h": "rowwise"},
+                  alibi=True),
+}
+
+
+def _slice_alibi(module, rank: int, world: int):
+    """Bloom builds the ALiBi bias for all heads ``[batch * heads, 1, kv]`` outside the attention module; a sharded
+    attention module keeps the rows of its own heads."""
+
+    def cut(alibi, batch):
+        total = alibi.shape[0] // batch
+        per = total // world
+        return alibi.view(batch, total, *alibi.shape[1:])[:, rank * per:(rank + 1) * per].reshape(
+            batch * per, *alibi.shape[1:])
+
+    def hook(mod, args, kwargs):
+        batch = (args[0] if args else kwargs["hidden_states"]).shape[0]
+        if "alibi" in kwargs:
+            kwargs["alibi"] = cut(kwargs["alibi"], batch)
+        elif len(args) > 2:
+            args = args[:2] + (cut(args[2], batch),) + args[3:]
+        return args, kwargs
+
+    module.register_forward_pre_hook(hook, with_kwargs=True)
+
+
+def shard_padded(model, model_type: str, rank: int, world: int, group) -> None:
+    from .transformers_backend import ShardedLinear, shard_model
+
+    spec = PADDED_TP.get(model_type)
+    cfg = model.config
+    if spec is None and not getattr(cfg, "base_model_tp_plan", None):
+        raise NotImplementedError(f"the fallback runner has no tensor-parallel plan for model type {model_type!r}: "
+                                  "run it on one GPU")
+    shard_model(model, rank, world, group, plan=spec["plan"] if spec else None, head_attrs=("num_heads",))
+    if spec and spec["alibi"]:
+        for m in model.modules():
+            if isinstance(getattr(m, "query_key_value", None), ShardedLinear):
+                _slice_alibi(m, rank, world)
+
+
 def load_padded(path, cfg, process_group, rank: int, world: int, dtype, device, tokenizer):
     """Instantiate the ``transformers`` implementation of ``path`` and wrap it in a fallback runner."""
-    if world > 1:
-        raise NotImplementedError("the transformers fallback runners are not sharded: run them on one GPU")
     import transformers
 
     hf_cfg = transformers.AutoConfig.from_pretrained(str(path))
     seq2seq = bool(getattr(hf_cfg, "is_encoder_decoder", False))
     cls = transformers.AutoModelForSeq2SeqLM if seq2seq else transformers.AutoModelForCausalLM
-    model = cls.from_pretrained(str(path), torch_dtype=dtype).to(device)
+    model = cls.from_pretrained(str(path), torch_dtype=dtype)
+    if world > 1:
+        if seq2seq:
+            raise NotImplementedError("the encoder-decoder fallback runner is not sharded: run it on one GPU")
+        shard_padded(model, str(hf_cfg.model_type), rank, world, process_group)
+    model = model.to(device)
     if not hasattr(tokenizer, "decode"):
         tokenizer = transformers.AutoTokenizer.from_pretrained(str(path))
     eos = getattr(hf_cfg, "eos_token_id", None)

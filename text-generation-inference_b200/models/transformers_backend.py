@@ -80,6 +80,105 @@ def register():
     _registered = True
 
 
+class ShardedLinear(torch.nn.Module):
+    """One rank's part of a ``torch.nn.Linear`` under tensor parallelism.
+
+    The styles are those of the ``base_model_tp_plan`` a ``transformers`` config carries
+    (``integrations/tensor_parallel.py`` in that library): ``colwise`` keeps a contiguous slice of the output
+    features (for q / k / v that is a contiguous range of heads) and returns it; ``colwise_gather_output`` returns the
+    full output (models that normalise q or k over all heads, or split a fused gate_up themselves); ``rowwise``
+    multiplies the rank's slice of the input features and sums the partial outputs over the ranks;
+    ``rowwise_split_input`` receives the full input and cuts its own slice first.  The bias of a row-parallel layer is
+    added once, after the sum.
+    """
+
+    STYLES = ("colwise", "colwise_gather_output", "rowwise", "rowwise_split_input")
+
+    def __init__(self, linear: torch.nn.Linear, style: str, rank: int, world: int, group):
+        super().__init__()
+        if style not in self.STYLES:
+            raise NotImplementedError(f"tensor-parallel style {style!r}")
+        out_f, in_f = linear.weight.shape
+        self.style, self.rank, self.world, self.group = style, rank, world, group
+        if style.startswith("colwise"):
+            if out_f % world:
+                raise ValueError(f"{out_f} output features cannot be split over {world} ranks")
+            per = out_f // world
+            w = linear.weight.detach()[rank * per:(rank + 1) * per]
+            b = None if linear.bias is None else linear.bias.detach()[rank * per:(rank + 1) * per]
+        else:
+            if in_f % world:
+                raise ValueError(f"{in_f} input features cannot be split over {world} ranks")
+            per = in_f // world
+            w = linear.weight.detach()[:, rank * per:(rank + 1) * per]
+            b = None if linear.bias is None else linear.bias.detach()
+        self.per = per
+        self.weight = torch.nn.Parameter(w.clone().contiguous(), requires_grad=False)
+        self.bias = None if b is None else torch.nn.Parameter(b.clone().contiguous(), requires_grad=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from ..parallel import dist as pdist
+
+        if self.style == "colwise":
+            return torch.nn.functional.linear(x, self.weight, self.bias)
+        if self.style == "colwise_gather_output":
+            y = torch.nn.functional.linear(x, self.weight, self.bias)
+            rows = y.reshape(-1, y.shape[-1]).contiguous()
+            parts = torch.empty(self.world * rows.shape[0], rows.shape[1], dtype=y.dtype, device=y.device)
+            pdist.all_gather_into(parts, rows, self.group)      # rank-major blocks of rows
+            full = parts.view(self.world, rows.shape[0], rows.shape[1]).transpose(0, 1)
+            return full.reshape(*y.shape[:-1], self.world * y.shape[-1])
+        if self.style == "rowwise_split_input":
+            x = x[..., self.rank * self.per:(self.rank + 1) * self.per]
+        y = torch.nn.functional.linear(x, self.weight)
+        y = pdist.all_reduce(y.contiguous(), self.group)
+        return y if self.bias is None else y + self.bias
+
+
+def shard_model(hf_model, rank: int, world: int, group, plan: Optional[dict] = None, head_attrs=()) -> dict:
+    """Replace the linear layers named by the config's ``base_model_tp_plan`` with this rank's part.  Returns
+    ``{"heads_sharded": bool, "kv_sharded": bool}``: whether the attention of a layer sees a slice of the heads (q / k
+    column-parallel without a gather) or all of them.  Reference: ``models/transformers_flash_causal_lm.py:137-150``
+    loads with ``tp_plan="auto"``, which applies the same plan through DTensor hooks.  ``plan`` overrides the config's
+    (model types whose config carries none); ``head_attrs`` names integer attributes of an attention module (its head
+    count) that are divided by the number of ranks when its q projection is column parallel, for modelling code that
+    reshapes with a stored head count instead of ``-1``."""
+    import re
+
+    cfg = hf_model.config.get_text_config() if hasattr(hf_model.config, "get_text_config") else hf_model.config
+    plan = dict(plan or getattr(cfg, "base_model_tp_plan", None) or {})
+    if not plan:
+        raise NotImplementedError(f"model type {cfg.model_type!r} carries no tensor-parallel plan")
+    body = getattr(hf_model, hf_model.base_model_prefix, None) or hf_model.model
+    rules = [(re.compile("^" + re.escape(k).replace(r"\*", r"\d+") + "$"), v) for k, v in plan.items()]
+    info = {"heads_sharded": False, "kv_sharded": False}
+    todo = []
+    for name, mod in body.named_modules():
+        for rx, style in rules:
+            if rx.match(name):
+                if not isinstance(mod, torch.nn.Linear):
+                    raise NotImplementedError(f"tensor-parallel plan names {name} ({type(mod).__name__}), not a Linear")
+                todo.append((name, mod, style))
+                break
+    if not todo:
+        raise NotImplementedError("the tensor-parallel plan matches no module")
+    for name, mod, style in todo:
+        parent_name, _, leaf = name.rpartition(".")
+        parent = body.get_submodule(parent_name) if parent_name else body
+        setattr(parent, leaf, ShardedLinear(mod, style, rank, world, group))
+        if style == "colwise" and leaf in ("q_proj", "qkv_proj", "query_key_value"):
+            info["heads_sharded"] = True
+            for attr in head_attrs:
+                n = getattr(parent, attr, None)
+                if isinstance(n, int):
+                    if n % world:
+                        raise ValueError(f"{n} heads cannot be split over {world} ranks")
+                    setattr(parent, attr, n // world)
+        if style == "colwise" and leaf in ("k_proj", "qkv_proj", "query_key_value"):
+            info["kv_sharded"] = True
+    return info
+
+
 class TransformersDecoder:
     """Adapter with the interface ``FlashCausalLM`` expects from a decoder (``dims``, ``forward``)."""
 
@@ -87,12 +186,17 @@ class TransformersDecoder:
     speculator = None
     supports_local_head = False
 
-    def __init__(self, hf_model, device, dtype):
+    def __init__(self, hf_model, device, dtype, world: int = 1, heads_sharded: bool = False, kv_sharded: bool = False):
         self.hf = hf_model.eval()
         cfg = hf_model.config.get_text_config() if hasattr(hf_model.config, "get_text_config") else hf_model.config
-        heads = int(cfg.num_attention_heads)
-        head_dim = int(getattr(cfg, "head_dim", None) or cfg.hidden_size // heads)
-        kv = int(getattr(cfg, "num_key_value_heads", None) or heads)
+        total_heads = int(cfg.num_attention_heads)
+        head_dim = int(getattr(cfg, "head_dim", None) or cfg.hidden_size // total_heads)
+        total_kv = int(getattr(cfg, "num_key_value_heads", None) or total_heads)
+        if (heads_sharded and total_heads % world) or (kv_sharded and total_kv % world):
+            raise ValueError(f"{total_heads} / {total_kv} heads cannot be split over {world} ranks")
+        # the heads this rank's attention sees: a slice when q / k are column parallel, else all of them
+        heads = total_heads // world if heads_sharded else total_heads
+        kv = total_kv // world if kv_sharded else total_kv
         layers = int(cfg.num_hidden_layers)
         window = getattr(cfg, "sliding_window", None)
         layer_types = getattr(cfg, "layer_types", None)
@@ -110,7 +214,7 @@ class TransformersDecoder:
             rot_dim=head_dim, max_positions=int(getattr(cfg, "max_position_embeddings", 2048)),
             act=str(getattr(cfg, "hidden_act", "silu")), softmax_scale=head_dim ** -0.5, windows=windows,
             attn_softcap=0.0, logit_softcap=0.0, logit_scale=1.0, embed_scale=1.0, residual_scale=1.0,
-            total_heads=heads, total_kv_heads=kv, attn_head_dim=head_dim)
+            total_heads=total_heads, total_kv_heads=total_kv, attn_head_dim=head_dim)
         self.device, self.dtype = device, dtype
 
     @torch.no_grad()
@@ -156,13 +260,15 @@ def load_transformers_flash(path, cfg, process_group, rank, world, dtype, device
     from . import resolve_kv_dtype
     from .flash_causal_lm import FlashCausalLM
 
-    if world > 1:
-        raise NotImplementedError("the transformers backend runs unsharded; use a natively supported architecture "
-                                  "for tensor parallelism")
     register()
     hf = AutoModelForCausalLM.from_pretrained(str(path), torch_dtype=dtype, attn_implementation=ATTN_NAME)
+    info = {}
+    if world > 1:
+        # every rank reads the checkpoint on the host, keeps its slices of the planned layers and moves those to the
+        # device; embeddings, norms and the output head stay replicated (every rank computes the same logits)
+        info = shard_model(hf, rank, world, process_group)
     hf.to(device)
-    model = TransformersDecoder(hf, device, dtype)
+    model = TransformersDecoder(hf, device, dtype, world, info.get("heads_sharded", False), info.get("kv_sharded", False))
     kv_dtype = resolve_kv_dtype(kv_cache_dtype, dtype)
     if kv_dtype != dtype:
         raise NotImplementedError("the transformers backend keeps the KV cache in the model dtype")
