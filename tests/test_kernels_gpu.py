@@ -207,6 +207,13 @@ def test_act_and_mul(K, act):
     torch.testing.assert_close(deq, want.float(), atol=0.1, rtol=0.08)
 
 
+def test_act_and_mul_width_not_a_multiple_of_16(K):
+    """An intermediate size of 8 (mod 16) takes the kernel instance with one 16-byte vector per thread."""
+    torch.manual_seed(4)
+    gu = torch.randn(5, 2 * 1800, device=dev(), dtype=torch.bfloat16)
+    torch.testing.assert_close(K.act_and_mul(gu, "silu").float(), ref.act_and_mul(gu, "silu").float(), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("fp8_cache", [False, True])
 @pytest.mark.parametrize("neox,rot", [(True, 128), (False, 128), (True, 64)])
 def test_rope_and_cache(K, fp8_cache, neox, rot):

@@ -190,7 +190,7 @@ norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float act_fn(float x, int act) {
   switch (act) {
-    case 0: return x / (1.f + __expf(-x));                                              // silu
+    case 0: return __fdividef(x, 1.f + __expf(-x));                                     // silu (fast division)
     case 1: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));                   // gelu (erf)
     case 2: {                                                                           // gelu (tanh)
       const float k = 0.7978845608028654f;
@@ -201,40 +201,65 @@ __device__ __forceinline__ float act_fn(float x, int act) {
   }
 }
 
-template <bool QUANT>
+// NV 16-byte vectors (8 elements each) of gate and of up per thread; a 128-element quantisation group is spread
+// over 16 / NV lanes.  NV = 2 halves the per-element index / shuffle overhead (the kernel is instruction bound).
+template <bool QUANT, int NV>
 __global__ void __launch_bounds__(256)
 act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ q_out,
                float* __restrict__ scale_t, int scale_pitch, int I, int act) {
   tgi::pdl_wait();      // inputs come from earlier kernels of the stream
   tgi::pdl_trigger();   // let the next kernel be placed while this one runs
+  constexpr int E = 8 * NV;            // elements per thread
+  constexpr int LANES = 128 / E;       // lanes per quantisation group
   const int row = blockIdx.y;
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
-  const int nvec = I / 8;
-  const bool active = v < nvec;
-  float y[8];
+  const bool active = v < I / E;
+  float y[NV][8];
   if (active) {
-    float g[8], u[8];
-    const __nv_bfloat16* p = in + static_cast<size_t>(row) * 2 * I;
-    unpack8(*reinterpret_cast<const bf16x8*>(p + v * 8), g);
-    unpack8(*reinterpret_cast<const bf16x8*>(p + I + v * 8), u);
+    const __nv_bfloat16* p = in + static_cast<size_t>(row) * 2 * I + static_cast<size_t>(v) * E;
+    bf16x8 gv[NV], uv[NV];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) y[j] = round_bf16(act_fn(g[j], act) * u[j]);
+    for (int k = 0; k < NV; ++k) {
+      gv[k] = *reinterpret_cast<const bf16x8*>(p + k * 8);
+      uv[k] = *reinterpret_cast<const bf16x8*>(p + I + k * 8);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float g[8], u[8];
+      unpack8(gv[k], g);
+      unpack8(uv[k], u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[k][j] = round_bf16(act_fn(g[j], act) * u[j]);
+    }
   } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) y[j] = 0.f;
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[k][j] = 0.f;
   }
   if (QUANT) {
     float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
-    amax = group16_max(amax);
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[k][j]));
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     const float scale = block_scale(amax);
     if (active) {
-      *reinterpret_cast<uint2*>(q_out + static_cast<size_t>(row) * I + v * 8) = quant8(y, scale);
-      if ((v & 15) == 0) scale_t[static_cast<size_t>(v >> 4) * scale_pitch + row] = scale;
+      uint8_t* q = q_out + static_cast<size_t>(row) * I + static_cast<size_t>(v) * E;
+      if (NV == 2) {
+        const uint2 lo = quant8(y[0], scale), hi = quant8(y[NV - 1], scale);
+        *reinterpret_cast<uint4*>(q) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+      } else {
+        *reinterpret_cast<uint2*>(q) = quant8(y[0], scale);
+      }
+      if ((v & (LANES - 1)) == 0) scale_t[static_cast<size_t>(v / LANES) * scale_pitch + row] = scale;
     }
   } else if (active) {
-    *reinterpret_cast<bf16x8*>(out + static_cast<size_t>(row) * I + v * 8) = pack8(y);
+    __nv_bfloat16* o = out + static_cast<size_t>(row) * I + static_cast<size_t>(v) * E;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) *reinterpret_cast<bf16x8*>(o + k * 8) = pack8(y[k]);
   }
 }
 
@@ -877,13 +902,19 @@ int tgi_act_mul(const void* in, void* out, void* q_out, float* scale_t, int scal
   if (I % 8 != 0) return -10;
   const bool quant = q_out != nullptr;
   if (quant && I % 128 != 0) return -11;
-  dim3 grid((I / 8 + 255) / 256, T);
-  if (quant)
-    tgi::launch(act_mul_kernel<true>, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), nullptr,
-                                                   static_cast<uint8_t*>(q_out), scale_t, scale_pitch, I, act);
-  else
-    tgi::launch(act_mul_kernel<false>, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in),
-                                                    static_cast<__nv_bfloat16*>(out), nullptr, nullptr, 0, I, act);
+  if (quant) {   // I % 128 == 0: 16 elements per thread
+    dim3 grid((I / 16 + 255) / 256, T);
+    tgi::launch(act_mul_kernel<true, 2>, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), nullptr,
+                static_cast<uint8_t*>(q_out), scale_t, scale_pitch, I, act);
+  } else if (I % 16 == 0) {
+    dim3 grid((I / 16 + 255) / 256, T);
+    tgi::launch(act_mul_kernel<false, 2>, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in),
+                static_cast<__nv_bfloat16*>(out), nullptr, nullptr, 0, I, act);
+  } else {
+    dim3 grid((I / 8 + 255) / 256, T);
+    tgi::launch(act_mul_kernel<false, 1>, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in),
+                static_cast<__nv_bfloat16*>(out), nullptr, nullptr, 0, I, act);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
