@@ -510,7 +510,9 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
 #pragma unroll
         for (int j = 0; j < TN / 128; ++j) {
-          const float sw = __ldg(&wscale[static_cast<size_t>((n0 >> 7) + j) * sch.KB + kb]);
+          // a tile that hangs over the last weight rows reads the last block's scale for the rows that do not exist
+          const int wb = min((n0 >> 7) + j, (N - 1) >> 7);
+          const float sw = __ldg(&wscale[static_cast<size_t>(wb) * sch.KB + kb]);
           const uint32_t e = ((__float_as_uint(sw) >> 23) & 0xFFu) * 0x01010101u;
           const uint32_t w[4] = {e, e, e, e};
           tmem_st_32x32b_x4(tsf + 8 + j * 4, w);
@@ -861,6 +863,7 @@ int dispatch(const void* X, const float* xs_t, int xs_pitch, const void* W, cons
     const long long mx_pair_tiles = static_cast<long long>((N + 255) / 256) * ((M + 255) / 256);
     // pairs need enough work to repay their fixed cost: 256 x 8192 x 4096 (32 tiles of 32 K blocks) takes 30.7 us in
     // pairs and 25.6 us on single CTAs, 256 x 8192 x 8192 37.1 against 38.3, 256 x 8192 x 14336 47.5 against 51.2
+    // (a caller that lowers the tile threshold, as the tests do to reach pairs with small problems, lifts this one too)
     const long long mx_pair_units = mx_pair_tiles * ((K + 127) / 128);
     if (g_pairs && g_mx_pairs && max_ctas >= 2 && mx_pair_tiles >= g_pair_min_tiles &&
         (mx_pair_units >= 2048 || g_pair_min_tiles < 32)) {
