@@ -160,14 +160,13 @@ class Fp8Linear:
         if self.channel_scale is None:
             return ops.gemm_fp8_block(x, x_scale, self.qweight, self.scale, self.dtype, self.bias, out=out)
         y = ops.gemm_fp8_block(x, x_scale, self.qweight, self.scale, self.dtype, None)
-        y = (y.float() * self.channel_scale).to(self.dtype)
+        # one elementwise kernel: the product is formed in fp32 (type promotion) and stored in the output dtype,
+        # in place or straight into the caller's buffer
+        dst = y if out is None else (out.fallback if getattr(out, "is_peer_push", False) else out)
+        torch.mul(y, self.channel_scale, out=dst)
         if self.bias is not None:
-            y = y + self.bias
-        if out is not None:
-            dst = out.fallback if getattr(out, "is_peer_push", False) else out
-            dst.copy_(y)
-            return out
-        return y
+            dst.add_(self.bias)
+        return dst if out is None else out
 
 
 def get_linear(weight, bias):
