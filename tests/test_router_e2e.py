@@ -44,13 +44,19 @@ def _start_collector():
     import http.server
     import threading
 
-    collected = []
+    class _Docs(list):
+        pass
+
+    collected = _Docs()
+    collected.usage = []       # usage-statistics events posted to /api/telemetry/tgi
 
     class Handler(http.server.BaseHTTPRequestHandler):
         def do_POST(self):
             body = self.rfile.read(int(self.headers.get("content-length", "0")))
             if self.path == "/v1/traces":
                 collected.append(json.loads(body))
+            elif self.path == "/api/telemetry/tgi":
+                collected.usage.append(json.loads(body))
             self.send_response(200)
             self.send_header("content-length", "2")
             self.end_headers()
@@ -87,6 +93,9 @@ def stack(tmp_path_factory):
                                "--max-total-tokens", "128", "--max-batch-prefill-tokens", "128",
                                "--otlp-endpoint", f"http://127.0.0.1:{collector.server_address[1]}",
                                "--otlp-service-name", "tgi-b200-test.router",
+                               "--usage-stats", "no-stack", "--usage-stats-ping-seconds", "1",
+                               "--usage-stats-endpoint", f"http://127.0.0.1:{collector.server_address[1]}/api/telemetry/tgi",
+                               "--usage-stats-file", str(d / "usage.jsonl"),
                                "--repo-root", ROOT], env=env, cwd=ROOT)
     try:
         deadline = time.time() + 120
@@ -100,7 +109,7 @@ def stack(tmp_path_factory):
                 time.sleep(0.3)
         else:
             raise RuntimeError("router did not come up")
-        yield {"port": port, "uds": uds, "otlp": collected}
+        yield {"port": port, "uds": uds, "otlp": collected, "usage": collected.usage, "usage_file": d / "usage.jsonl"}
     finally:
         for p in (router, shard):
             p.send_signal(signal.SIGTERM)
@@ -447,6 +456,25 @@ def test_request_spans_reach_the_otlp_collector(stack):
     assert chain is not None, "shard spans do not descend from the request span"
     assert chain[0][0] == "tgi-b200-test.router" and chain[0][1]["name"] in ("prefill", "decode")
     assert chain[1][0] == "tgi-b200-test.shard" and chain[1][1]["name"] in ("Prefill", "Decode")
+
+
+def test_usage_statistics_events_reach_the_named_sinks(stack):
+    """Start and Ping events arrive at the collector and in the file, with the run's id, the reduced arguments and
+    the host description; nothing is sent when no sink is named (the default)."""
+    deadline = time.time() + 10
+    while time.time() < deadline and not any(e["event_type"] == "Ping" for e in stack["usage"]):
+        time.sleep(0.2)
+    kinds = [e["event_type"] for e in stack["usage"]]
+    assert kinds[0] == "Start" and "Ping" in kinds
+    ev = stack["usage"][0]
+    ua = ev["user_agent"]
+    assert len(ua["uid"]) == 36 and ua["uid"][14] == "4"
+    assert ua["args"]["max_input_tokens"] == 64 and ua["args"]["max_total_tokens"] == 128
+    assert ua["args"]["usage_stats_level"] == "no-stack" and ua["args"]["model_config"] == "llama"
+    assert ua["env"]["cpu_count"] >= 1 and ua["env"]["total_memory"] > 0 and "architecture" in ua["env"]
+    assert all(e["user_agent"]["uid"] == ua["uid"] for e in stack["usage"])
+    lines = [json.loads(l) for l in stack["usage_file"].read_text().splitlines()]
+    assert lines[0]["event_type"] == "Start" and lines[0]["user_agent"]["uid"] == ua["uid"]
 
 
 def test_openapi_document_and_docs_page(stack):

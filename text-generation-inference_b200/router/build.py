@@ -16,7 +16,7 @@ SRC = HERE / "src"
 OBJ = HERE / "_build"
 CXX = os.environ.get("CXX", "g++")
 FLAGS = ["-std=c++17", "-O2", "-g", "-fPIC", "-Wall", "-pthread"]
-CORE = ["pb.cpp", "scheduler.cpp", "shard_client.cpp", "trace.cpp", "http.cpp", "images.cpp", "api.cpp", "api_routes.cpp", "api_openai.cpp", "api_kserve.cpp", "openapi.cpp"]
+CORE = ["pb.cpp", "scheduler.cpp", "shard_client.cpp", "trace.cpp", "usage.cpp", "http.cpp", "images.cpp", "api.cpp", "api_routes.cpp", "api_openai.cpp", "api_kserve.cpp", "openapi.cpp"]
 
 
 def _py_flags():

@@ -324,7 +324,7 @@ int main(int argc, char** argv) {
         "             --max-client-batch-size 4 --payload-limit 2000000 --validation-workers 2\n"
         "  serving:   --hostname 0.0.0.0 --port 3000 --prometheus-port 9000 --api-key KEY --cors-allow-origin a,b\n"
         "             --disable-grammar-support --enable-prefill-logprobs --watermark-gamma G --watermark-delta D\n"
-        "  operation: --json-output --otlp-endpoint URL --otlp-service-name NAME --usage-stats on|off|no-stack (no-op)\n"
+        "  operation: --json-output --otlp-endpoint URL --otlp-service-name NAME --usage-stats on|off|no-stack --usage-stats-endpoint URL --usage-stats-file PATH\n"
         "             --graceful-termination-timeout 90 --env --python python\n";
     return args.has("help") ? 0 : 2;
   }
@@ -357,7 +357,9 @@ int main(int argc, char** argv) {
   if (args.has("env")) {
     if (system("nvidia-smi") != 0) log_line("WARNING", "launcher", "nvidia-smi is not available");
   }
-  if (args.has("usage-stats")) log_line("INFO", "launcher", "usage statistics are never sent by this launcher");
+  if (args.has("usage-stats") && args.get("usage-stats") != "off" && !args.has("usage-stats-endpoint") &&
+      !args.has("usage-stats-file"))
+    log_line("INFO", "launcher", "usage statistics have no sink: name one with --usage-stats-endpoint or --usage-stats-file");
 
   // environment shared by the weight download and the shards
   std::map<std::string, std::string> base_env;
@@ -513,6 +515,8 @@ int main(int argc, char** argv) {
     rcmd.push_back("--otlp-service-name");
     rcmd.push_back(args.get("otlp-service-name", "text-generation-inference") + ".router");
   }
+  for (const char* f : {"usage-stats", "usage-stats-endpoint", "usage-stats-file", "usage-stats-ping-seconds"})
+    if (args.has(f)) { rcmd.push_back(std::string("--") + f); rcmd.push_back(args.get(f)); }
   Child router;
   router.name = "router";
   {

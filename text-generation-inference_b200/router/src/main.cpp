@@ -11,6 +11,7 @@
 #include <map>
 
 #include "trace.hpp"
+#include "usage.hpp"
 #include "api.hpp"
 #include "http.hpp"
 #include "metrics.hpp"
@@ -153,6 +154,7 @@ int main(int argc, char** argv) {
                  "  [--api-key KEY] [--payload-limit BYTES] [--disable-grammar-support] [--repo-root DIR]\n";
     return 0;
   }
+  std::unique_ptr<usage::Reporter> usage_reporter;   // outlives the try block: fatal errors are reported too
   try {
     const std::string uds = args.get("master-shard-uds-path", "/tmp/text-generation-server");
     const std::string tokenizer = args.get("tokenizer-name", args.get("model-id"));
@@ -262,12 +264,32 @@ int main(int argc, char** argv) {
     router.install(server);
     // request spans go to an OTLP/HTTP collector when one is configured
     trace::init(args.get("otlp-endpoint"), args.get("otlp-service-name", "text-generation-inference.router"));
+    // usage statistics (off unless asked for; events go to the operator's collector or file, nowhere else)
+    json::Value uargs = json::Value::object();
+    uargs.set("model_config", rc.model_config.is_object() && rc.model_config.has("model_type")
+                                  ? json::Value(rc.model_config["model_type"].as_string()) : json::Value());
+    uargs.set("tokenizer_class", json::Value());
+    uargs.set("validation_workers", args.num("validation-workers", 2));
+    uargs.set("max_concurrent_requests", static_cast<long>(rc.max_concurrent_requests));
+    uargs.set("max_best_of", static_cast<long>(rc.max_best_of));
+    uargs.set("max_stop_sequences", static_cast<long>(rc.max_stop_sequences));
+    uargs.set("max_top_n_tokens", static_cast<long>(rc.max_top_n_tokens));
+    uargs.set("max_input_tokens", static_cast<long>(rc.max_input_tokens));
+    uargs.set("max_total_tokens", static_cast<long>(rc.max_total_tokens));
+    uargs.set("max_batch_total_tokens", static_cast<long>(rc.max_batch_total_tokens));
+    uargs.set("max_client_batch_size", static_cast<long>(rc.max_client_batch_size));
+    uargs.set("disable_grammar_support", rc.disable_grammar_support);
+    uargs.set("usage_stats_level", args.get("usage-stats", "off"));
+    usage_reporter = std::make_unique<usage::Reporter>(args.get("usage-stats", "off"), args.get("usage-stats-endpoint"),
+                                                       args.get("usage-stats-file"), uargs);
     g_server = &server;
     std::signal(SIGINT, on_signal);
     std::signal(SIGTERM, on_signal);
     std::signal(SIGPIPE, SIG_IGN);
     const int port = server.start();
     std::cerr << "[router] Connected; listening on port " << port << std::endl;
+    usage_reporter->send("Start");
+    usage_reporter->start_pings(static_cast<int>(args.num("usage-stats-ping-seconds", 900)));
     // optional second listener that only serves the Prometheus text format (reference: --prometheus-port)
     std::unique_ptr<http::Server> prom;
     std::thread prom_thread;
@@ -287,11 +309,13 @@ int main(int argc, char** argv) {
       if (prom_thread.joinable()) prom_thread.join();
     }
     backend->stop();
+    usage_reporter->send("Stop");
     trace::shutdown();   // flushes the spans still queued
     std::cerr << "[router] shut down" << std::endl;
     return 0;
   } catch (const std::exception& e) {
     std::cerr << "[router] fatal: " << e.what() << std::endl;
+    if (usage_reporter) usage_reporter->send("Error", e.what());
     return 1;
   }
 }

@@ -175,7 +175,9 @@ void Exporter::loop() {
   }
 }
 
-bool Exporter::post(const std::string& body) {
+bool Exporter::post(const std::string& body) { return http_post_json(host_, port_, path_, body); }
+
+bool http_post_json(const std::string& host_, int port_, const std::string& path_, const std::string& body) {
   addrinfo hints{}, *res = nullptr;
   hints.ai_family = AF_UNSPEC;
   hints.ai_socktype = SOCK_STREAM;

@@ -37,6 +37,9 @@ struct Span {
   std::vector<std::pair<std::string, long long>> int_attrs;
 };
 
+// POST `body` as application/json over plain HTTP (2 s socket timeouts); true on a 2xx answer.
+bool http_post_json(const std::string& host, int port, const std::string& path, const std::string& body);
+
 // One OTLP ExportTraceServiceRequest (JSON) for a batch of spans.
 std::string encode_otlp(const std::vector<Span>& spans, const std::string& service_name);
 
