@@ -101,3 +101,30 @@ def test_fallback_runner_tensor_parallel(tmp_path, arch):
            "--master-port", str(29851 + (arch == "opt")), os.path.join(root, "tests", "dist_padded_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "DIST_WORKER_OK" in r.stdout, (r.stdout[-1500:], r.stderr[-3000:])
+
+
+def test_galactica_sequences_are_marked_character_by_character():
+    from tgi_b200.models.padded import GALACTICA_SPLIT_MARKER as M, galactica_mark_sequences
+
+    assert galactica_mark_sequences("plain text") == "plain text"
+    got = galactica_mark_sequences("x [START_DNA]ACG[END_DNA] y [START_SMILES]C=O[END_SMILES]")
+    assert got == f"x [START_DNA]{M}A{M}C{M}G{M}[END_DNA] y [START_SMILES]{M}C{M}={M}O{M}[END_SMILES]"
+    # an unmatched or mismatched pair is left alone
+    assert galactica_mark_sequences("[START_DNA]AC[END_AMINO]") == "[START_DNA]AC[END_AMINO]"
+
+
+def test_galactica_checkpoints_get_their_batch_type(tmp_path):
+    from tgi_b200.models.padded import GalacticaBatch
+
+    torch.manual_seed(0)
+    V = 300
+    hf = transformers.OPTForCausalLM(transformers.OPTConfig(
+        vocab_size=V, hidden_size=32, ffn_dim=64, num_hidden_layers=1, num_attention_heads=4, word_embed_proj_dim=32,
+        max_position_embeddings=64, pad_token_id=0, eos_token_id=1, bos_token_id=2))
+    d = tmp_path / "galactica-tiny"
+    d.mkdir()
+    _save(hf.eval(), d, V)
+    model = get_model(str(d), dtype="float32", device=torch.device("cpu"))
+    assert model.batch_type is GalacticaBatch
+    got = _run(model, [[10, 20, 30]], 3)
+    assert len(got[0]) == 3

@@ -35,10 +35,15 @@ def _tiny(arch):
         return transformers.Olmo2ForCausalLM(transformers.Olmo2Config(**common))
     if arch == "glm":
         return transformers.GlmForCausalLM(transformers.GlmConfig(head_dim=64, partial_rotary_factor=0.5, **common))
+    if arch == "llama4_text":      # the text decoder of Llama-4: interleaved MoE layers, q/k norm, rotary in pairs
+        return transformers.Llama4ForCausalLM(transformers.Llama4TextConfig(
+            vocab_size=V, hidden_size=64, intermediate_size=64, intermediate_size_mlp=128, num_hidden_layers=2,
+            num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_local_experts=2, num_experts_per_tok=1,
+            max_position_embeddings=128, pad_token_id=0, eos_token_id=1, bos_token_id=2, attention_chunk_size=64))
     return transformers.HeliumForCausalLM(transformers.HeliumConfig(head_dim=64, **common))
 
 
-@pytest.mark.parametrize("arch", ["olmo2", "glm", "helium"])
+@pytest.mark.parametrize("arch", ["olmo2", "glm", "helium", "llama4_text"])
 def test_transformers_backend_matches_generate(tmp_path, arch):
     assert arch not in ARCHS and supports({"model_type": arch})
     torch.manual_seed(0)
@@ -51,10 +56,12 @@ def test_transformers_backend_matches_generate(tmp_path, arch):
     n_new = 6
     got = _run(model, prompts, n_new)
     for i, p in enumerate(prompts):
-        ids = torch.tensor([model.tokenizer("".join(chr(3 + t) for t in p))["input_ids"]])
-        with torch.no_grad():
-            ref = hf.generate(ids, max_new_tokens=n_new, min_new_tokens=n_new, do_sample=False)
-        assert got[i] == ref[0, ids.shape[1]:].tolist()[:n_new], (arch, i)
+        seq = list(model.tokenizer("".join(chr(3 + t) for t in p))["input_ids"])
+        n0 = len(seq)
+        with torch.no_grad():      # plain greedy decoding (``generate`` would mask the end-of-sequence token)
+            for _ in range(n_new):
+                seq.append(int(hf(torch.tensor([seq])).logits[0, -1].argmax()))
+        assert got[i] == seq[n0:], (arch, i)
 
 
 @pytest.mark.parametrize("arch", ["olmo2", "glm", "helium"])

@@ -98,6 +98,46 @@ class PaddedSeq2SeqBatch(PaddedBatch):
     seq2seq = True
 
 
+# Galactica (an OPT checkpoint) tokenises the body of [START_DNA] / [START_SMILES] / [START_I_SMILES] / [START_AMINO]
+# spans one character at a time: its tokenizer splits on a marker string that the serving side has to put in front of
+# every character of the span and in front of the closing tag (reference: ``models/galactica.py:18-58``).
+GALACTICA_SPLIT_MARKER = "SPL" + "1T-TH" + "1S-Pl3A5E"
+_GALACTICA_SPAN = None
+
+
+def galactica_mark_sequences(text: str) -> str:
+    global _GALACTICA_SPAN
+    if _GALACTICA_SPAN is None:
+        import re
+
+        _GALACTICA_SPAN = re.compile(r"\[START_(DNA|SMILES|I_SMILES|AMINO)\](.*?)\[END_\1\]", re.DOTALL)
+
+    def mark(m):
+        kind, body = m.group(1), m.group(2)
+        spaced = "".join(GALACTICA_SPLIT_MARKER + ch for ch in body)
+        return f"[START_{kind}]{spaced}{GALACTICA_SPLIT_MARKER}[END_{kind}]"
+
+    return _GALACTICA_SPAN.sub(mark, text)
+
+
+class GalacticaBatch(PaddedBatch):
+    @classmethod
+    def from_pb(cls, batch_pb, tokenizer, dtype, device, speculate: int = 0) -> "GalacticaBatch":
+        seqs, params = [], []
+        for r in batch_pb.requests:
+            text = r.inputs
+            if r.HasField("input_chunks") and len(r.input_chunks.chunks) > 0:
+                text = "".join(c.text for c in r.input_chunks.chunks if c.WhichOneof("chunk") == "text")
+            ids = list(tokenizer(galactica_mark_sequences(text), truncation=False,
+                                 add_special_tokens=r.add_special_tokens)["input_ids"])
+            if r.truncate and len(ids) > r.truncate:
+                ids = ids[-r.truncate:]
+            stopping = StoppingCriteria.from_pb(r.stopping_parameters, tokenizer)
+            seqs.append(PaddedSeq(r, ids, len(ids), stopping, int(r.top_n_tokens), max(0, len(ids) - 5), len(ids)))
+            params.append(r.parameters)
+        return cls(batch_pb.id, seqs, NextTokenChooser.from_pb(params, device, tokenizer), device)
+
+
 class PaddedCausalLM(Model):
     """``AutoModelForCausalLM``-style runner (also state-space models: the cache object is opaque)."""
 
@@ -114,12 +154,14 @@ class PaddedCausalLM(Model):
         self.kv_cache: list = []
         self.num_blocks = 0
 
+    galactica = False        # set by the loader for facebook/galactica checkpoints
+
     @property
     def batch_type(self) -> Type[PaddedBatch]:
         if self.seq2seq:
             PaddedSeq2SeqBatch.decoder_start = self.decoder_start
             return PaddedSeq2SeqBatch
-        return PaddedBatch
+        return GalacticaBatch if self.galactica else PaddedBatch
 
     def init_kv_cache(self, num_blocks: int):      # interface parity with the paged runner
         self.num_blocks = num_blocks
@@ -302,4 +344,10 @@ def load_padded(path, cfg, process_group, rank: int, world: int, dtype, device, 
     eos = getattr(hf_cfg, "eos_token_id", None)
     eos_ids = set(eos) if isinstance(eos, (list, tuple)) else ({eos} if eos is not None else None)
     runner_cls = PaddedSeq2SeqLM if seq2seq else PaddedCausalLM
-    return runner_cls(model, tokenizer, dtype, device, rank, world, eos_ids)
+    runner = runner_cls(model, tokenizer, dtype, device, rank, world, eos_ids)
+    # the reference recognises Galactica by its repository name (``models/__init__.py:742-760``); a local directory
+    # is recognised by its name or by the `_name_or_path` the checkpoint's config recorded
+    names = (str(path) + " " + str(getattr(hf_cfg, "_name_or_path", ""))).lower()
+    if not seq2seq and hf_cfg.model_type == "opt" and "galactica" in names:
+        runner.galactica = True
+    return runner
