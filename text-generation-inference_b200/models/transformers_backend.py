@@ -216,9 +216,18 @@ class TransformersDecoder:
             attn_softcap=0.0, logit_softcap=0.0, logit_scale=1.0, embed_scale=1.0, residual_scale=1.0,
             total_heads=total_heads, total_kv_heads=total_kv, attn_head_dim=head_dim)
         self.device, self.dtype = device, dtype
+        # Llama-4 style chunked attention (a token sees only the keys of its own chunk) has no counterpart in the
+        # paged kernels: contexts that stay inside one chunk are exact, longer ones are refused instead of being
+        # silently attended in full
+        chunked = layer_types and any(t == "chunked_attention" for t in layer_types)
+        self.attention_chunk = int(getattr(cfg, "attention_chunk_size", 0) or 0) if chunked else 0
 
     @torch.no_grad()
     def forward(self, meta: ForwardMeta, kv_cache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        if self.attention_chunk and int(meta.max_kv) > self.attention_chunk:
+            raise ValueError(      # fails the batch; the shard keeps serving
+                f"a context of {int(meta.max_kv)} tokens crosses the model's attention chunk of {self.attention_chunk} "
+                "tokens; chunked attention is not implemented in the paged kernels")
         token = _STEP.set((meta, kv_cache))
         try:
             kw = dict(position_ids=meta.positions.long().unsqueeze(0), use_cache=False, return_dict=True)
