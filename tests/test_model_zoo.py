@@ -124,6 +124,58 @@ def test_prefill_logits_match_transformers(tmp_path, name):
     assert err < 2e-3 * max(1.0, want.abs().max().item()), f"{name}: logits differ by {err}"
 
 
+def test_legacy_santacoder_layout(tmp_path):
+    """The first SantaCoder checkpoints: a ``gpt2`` config with ``attention_head_type: multiquery``, q and the shared
+    k/v projection stored separately, every linear weight in GPT-2's transposed layout.  Built here from a tiny
+    multi-query GPTBigCode model (the same network in its later layout), which is also the oracle."""
+    import json
+
+    from safetensors.torch import save_file
+
+    torch.manual_seed(0)
+    cfg = transformers.GPTBigCodeConfig(vocab_size=320, n_embd=64, n_layer=2, n_head=4, n_positions=256, multi_query=True,
+                                        activation_function="gelu_pytorch_tanh")
+    hf = transformers.GPTBigCodeForCausalLM(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.copy_(torch.randn_like(p) * 0.1 + (1.0 if "ln" in n else 0.0))
+    H, D = 64, 16
+    legacy = {}
+    for name, t in hf.state_dict().items():
+        if name == "lm_head.weight":
+            continue                                  # tied to the embedding
+        if ".attn.c_attn." in name:
+            q, kv = t[:H], t[H:H + 2 * D]
+            if name.endswith("weight"):
+                q, kv = q.t(), kv.t()
+            legacy[name.replace("c_attn", "q_attn")] = q.contiguous()
+            legacy[name.replace("c_attn", "kv_attn")] = kv.contiguous()
+        elif name.endswith("weight") and any(k in name for k in (".attn.c_proj.", ".mlp.c_fc.", ".mlp.c_proj.")):
+            legacy[name] = t.t().contiguous()
+        else:
+            legacy[name] = t.contiguous()
+    save_file(legacy, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(dict(
+        model_type="gpt2", architectures=["GPT2LMHeadCustomModel"], attention_head_type="multiquery", vocab_size=320,
+        n_embd=64, n_layer=2, n_head=4, n_positions=256, activation_function="gelu_pytorch_tanh",
+        layer_norm_epsilon=cfg.layer_norm_epsilon)))
+    ids = torch.tensor([[5, 17, 100, 42, 7, 9, 250, 31, 64, 3, 77, 12]])
+    with torch.no_grad():
+        want = hf(ids).logits[0].float()
+    model = get_model(str(tmp_path), dtype="float32", device=torch.device("cpu"))
+    assert model.model.dims.total_kv_heads == 1
+    model.init_kv_cache(4)
+    T = ids.shape[1]
+    meta = ForwardMeta(input_ids=ids[0].to(torch.int32), positions=torch.arange(T, dtype=torch.int32),
+                       slots=torch.arange(16, 16 + T, dtype=torch.int32), block_tables=torch.tensor([[1, 2]], dtype=torch.int32),
+                       cu_seqlens_q=torch.tensor([0, T], dtype=torch.int32), kv_lens=torch.tensor([T], dtype=torch.int32),
+                       max_q=T, max_kv=T)
+    got = model.forward(meta).float()
+    err = (got - want).abs().max().item()
+    assert err < 2e-3 * max(1.0, want.abs().max().item()), f"logits differ by {err}"
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", ["llama", "gemma2", "qwen3", "gpt2", "falcon", "phi", "mixtral", "deepseek_v3", "starcoder2"])
 def test_prefill_logits_on_gpu_kernels(tmp_path, name):

@@ -120,6 +120,8 @@ def get_model(
     prefix = ""
     if model_type in ("gpt2",) and weights.has_tensor("transformer.wte.weight"):
         prefix = "transformer"
+    if model_type == "gpt2" and text_cfg.get("attention_head_type") == "multiquery":
+        weights.derive = _santacoder_fused_qkv
     from ..parallel.peer import make_comm
 
     hidden = int(text_cfg.get("hidden_size", text_cfg.get("n_embd", text_cfg.get("d_model", 0))) or 0)
@@ -147,6 +149,25 @@ def _max_positions(cfg: ModelConfig, max_input_tokens: Optional[int]) -> int:
     if cap:
         mp = min(mp, cap) if cap < mp else cap
     return mp
+
+
+def _santacoder_fused_qkv(weights, name: str, probe: bool):
+    """The first SantaCoder checkpoints (a ``gpt2`` config with ``attention_head_type: multiquery`` and custom
+    modelling code) store the query projection and the shared key/value projection separately
+    (``attn.q_attn`` [H, H], ``attn.kv_attn`` [H, 2 D], both in the transposed GPT-2 layout); the decoder wants one
+    ``attn.c_attn``.  Reference: ``custom_modeling/flash_santacoder_modeling.py:60-130`` builds the same fused
+    matrix at load."""
+    for kind in ("weight", "bias"):
+        tail = f"attn.c_attn.{kind}"
+        if name.endswith(tail):
+            stem = name[:-len(tail)]
+            q, kv = f"{stem}attn.q_attn.{kind}", f"{stem}attn.kv_attn.{kind}"
+            if not (weights.has_tensor(q) and weights.has_tensor(kv)):
+                return None
+            if probe:
+                return True
+            return torch.cat([weights.get_tensor(q, to_device=False), weights.get_tensor(kv, to_device=False)], dim=-1)
+    return None
 
 
 def _aliases(model_type: str):

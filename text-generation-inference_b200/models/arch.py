@@ -246,7 +246,9 @@ def derive_dims(cfg: ModelConfig, arch: Arch, world: int) -> ModelDims:
     if kv is None and cfg.get("new_decoder_architecture") and cfg.get("num_kv_heads") is not None:
         kv = cfg.get("num_kv_heads")     # Falcon-40B style: grouped KV heads, `multi_query` is ignored
     if kv is None:
-        if cfg.get("multi_query") or (cfg.model_type in ("falcon", "RefinedWebModel", "RefinedWeb")
+        if cfg.get("attention_head_type") == "multiquery":        # the first SantaCoder checkpoints
+            kv = 1
+        elif cfg.get("multi_query") or (cfg.model_type in ("falcon", "RefinedWebModel", "RefinedWeb")
                                       and cfg.get("multi_query", True) and not cfg.get("new_decoder_architecture")):
             kv = 1
         elif cfg.get("n_head_kv") is not None or cfg.get("num_kv_heads") is not None:

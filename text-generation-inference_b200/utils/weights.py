@@ -227,6 +227,9 @@ class Weights:
 
             loader = DefaultWeightsLoader()
         self.weights_loader = loader
+        # optional hook ``derive(weights, name) -> tensor or None`` for tensors a checkpoint stores in another form
+        # (consulted by has_tensor / get_tensor when the name itself is absent)
+        self.derive = None
 
     # -- lookup ---------------------------------------------------------------------
     def _candidates(self, name: str) -> List[str]:
@@ -253,7 +256,7 @@ class Weights:
             self.resolve(name)
             return True
         except KeyError:
-            return False
+            return self.derive is not None and self.derive(self, name, probe=True) is not None
 
     def _slice(self, name: str) -> TensorSlice:
         h, real = self.resolve(name)
@@ -277,6 +280,13 @@ class Weights:
         return t.contiguous()
 
     def get_tensor(self, name: str, to_device: bool = True, to_dtype: bool = True) -> torch.Tensor:
+        if self.derive is not None:
+            try:
+                self.resolve(name)
+            except KeyError:
+                t = self.derive(self, name, probe=False)
+                if t is not None:
+                    return self._finish(t, to_device, to_dtype)
         return self._finish(self._slice(name).tensor(), to_device, to_dtype)
 
     # -- sharding -------------------------------------------------------------------
