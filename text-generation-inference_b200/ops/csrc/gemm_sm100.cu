@@ -550,7 +550,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (lane == 0) release_accum(hb);
       } else if (seg_end) {
         const int b = MX ? 0 : seg & 1;
-        ok = wait(&tmem_full[b], MX ? (seg & 1) : ((seg >> 1) & 1));
+        ok = mbar_wait_relaxed(&tmem_full[b], MX ? (seg & 1) : ((seg >> 1) & 1));
         if (!ok) { report(status, kErrEpilogueWait); break; }
         tc_fence_after();
         if (warp_active) {

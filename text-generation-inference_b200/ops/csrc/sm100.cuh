@@ -109,6 +109,15 @@ __device__ __forceinline__ bool mbar_wait_fast(uint64_t* bar, uint32_t parity, u
   return false;
 }
 
+// Wait for an event that is tens of microseconds away (a whole tile's accumulation): a long suspend time keeps the
+// waiting warps off the issue ports; the latency it can add is one suspend time per tile.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t polls = 1u << 19) {
+  for (uint32_t i = 0; i < polls; ++i) {
+    if (mbar_try_wait_hint(bar, parity, 400u)) return true;
+  }
+  return false;
+}
+
 // ---- TMA -----------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
