@@ -493,6 +493,20 @@ def test_image_token_counts_match_the_runners(rt):
                                            "perceiver_config": {"resampler_n_latents": 64}}), 10, 10) == 64
     assert rt.tokens_per_image(json.dumps({"model_type": "idefics3", "scale_factor": 2,
                                            "vision_config": {"image_size": 364, "patch_size": 14}}), 10, 10) == 169
+    # Idefics3 image splitting: the router's count equals the shard's layout for every image size
+    from tgi_b200.models.idefics3 import expansion_length, tile_grid
+
+    for tile, longest, nl, nlnl in [(364, 1456, 1, 1), (384, 1536, 1, 2), (28, 112, 1, 2), (364, 364, 1, 1)]:
+        seq = (tile // 14 // 2) ** 2 if tile >= 28 else 1
+        cfg3 = {"model_type": "idefics3", "scale_factor": 2, "vision_config": {"image_size": tile, "patch_size": 14},
+                "_idefics3": {"tile": tile, "longest_edge": longest, "split": True, "nl": nl, "nlnl": nlnl}}
+        for w, h in [(1, 1), (52, 40), (40, 52), (640, 480), (480, 640), (1920, 1080), (4000, 3000), (30, 3000), (999, 1001),
+                     (1456, 1456), (333, 777), (5000, 17), (364, 365)]:
+            _, _, rows, cols = tile_grid(h, w, longest, tile)
+            assert rt.tokens_per_image(json.dumps(cfg3), w, h) == expansion_length(rows, cols, seq, nl, nlnl), (tile, w, h)
+    unsplit = {"model_type": "idefics3", "scale_factor": 2, "vision_config": {"image_size": 364, "patch_size": 14},
+               "_idefics3": {"tile": 364, "longest_edge": 1456, "split": False, "nl": 1, "nlnl": 1}}
+    assert rt.tokens_per_image(json.dumps(unsplit), 2000, 1000) == 169 + 3
     assert rt.tokens_per_image(json.dumps({"model_type": "gemma3", "mm_tokens_per_image": 256, "boi_token_index": 1,
                                            "eoi_token_index": 2, "vision_config": {}}), 10, 10) == 258
     assert rt.tokens_per_image(json.dumps({"model_type": "mllama", "vision_config": {"image_size": 560}}), 900, 400) == 1

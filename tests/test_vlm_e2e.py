@@ -123,3 +123,62 @@ def test_image_request_end_to_end(vlm_stack):
     assert st == 422 and "image" in bad
     st, _, bad2 = _post(port, "/generate", {"inputs": "x![](https://example.com/a.png)y", "parameters": {"max_new_tokens": 3}})
     assert st == 422 and "https" in bad2
+
+
+def test_idefics3_split_image_end_to_end(tmp_path):
+    """Router and shard agree on the prompt length of a split image: the router counts the tiles, the marker tokens
+    and the newlines from the image's size, the shard builds that layout (x-prompt-tokens is the router's count; the
+    shard would run out of the blocks the router allotted if it needed more)."""
+    from tests.test_vlm_idefics import TXT, VIS, _marker_tokenizer
+    from tgi_b200.models.idefics3 import expansion_length, tile_grid
+    from tgi_b200.router.build import build
+
+    torch.manual_seed(0)
+    ids_of = _marker_tokenizer(tmp_path)
+    cfg = transformers.Idefics3Config(vision_config=VIS, text_config=dict(TXT, model_type="llama"),
+                                      image_token_id=ids_of["<image>"], scale_factor=2)
+    transformers.Idefics3ForConditionalGeneration(cfg).eval().save_pretrained(str(tmp_path), safe_serialization=True)
+    c = json.loads((tmp_path / "config.json").read_text())
+    c["vision_config"] = dict(c["vision_config"], **VIS)
+    (tmp_path / "config.json").write_text(json.dumps(c))
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps(
+        {"size": {"longest_edge": 84}, "max_image_size": {"longest_edge": 28}, "do_image_splitting": True}))
+    router_bin = build()
+    uds = str(tmp_path / "shard")
+    env = dict(os.environ, PYTHONPATH=ROOT, TGI_B200_CPU_KV_BLOCKS="256")
+    shard = subprocess.Popen([sys.executable, "-m", "tgi_b200.server.cli", "serve", str(tmp_path), "--uds-path", uds,
+                              "--dtype", "float32"], env=env, cwd=ROOT)
+    port = _free_port()
+    router = subprocess.Popen([str(router_bin), "--master-shard-uds-path", uds, "--tokenizer-name", str(tmp_path),
+                               "--port", str(port), "--hostname", "127.0.0.1", "--max-input-tokens", "200",
+                               "--max-total-tokens", "256", "--max-batch-prefill-tokens", "256", "--repo-root", ROOT],
+                              env=env, cwd=ROOT)
+    try:
+        deadline = time.time() + 180
+        while time.time() < deadline:
+            assert shard.poll() is None and router.poll() is None, "a process of the stack exited during start-up"
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=5) as r:
+                    if r.status == 200:
+                        break
+            except Exception:
+                time.sleep(0.3)
+        else:
+            raise RuntimeError("router did not come up")
+        for size in [(40, 52), (30, 90), (28, 28)]:                      # (height, width)
+            uri = "data:image/png;base64," + base64.b64encode(_png(3, size)).decode()
+            st, headers, out = _post(port, "/generate", {"inputs": f"ab![]({uri})cde",
+                                                         "parameters": {"max_new_tokens": 4, "details": True}})
+            assert st == 200, out
+            _, _, rows, cols = tile_grid(size[0], size[1], 84, 28)
+            want = 5 + expansion_length(rows, cols, 4, 1, 2)             # character tokenizer: "\n" 1 token, "\n\n" 2
+            assert int(headers["x-prompt-tokens"]) == want, (size, rows, cols, headers["x-prompt-tokens"], want)
+            assert json.loads(out)["details"]["generated_tokens"] == 4
+    finally:
+        for p in (router, shard):
+            p.send_signal(signal.SIGTERM)
+        for p in (router, shard):
+            try:
+                p.wait(timeout=20)
+            except subprocess.TimeoutExpired:
+                p.kill()

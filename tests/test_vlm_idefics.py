@@ -69,3 +69,114 @@ def test_idefics_generation_matches_transformers(tmp_path, kind, tokens):
                               pixel_attention_mask=torch.ones(1, px.shape[1], 28, 28, dtype=torch.long),
                               max_new_tokens=6, min_new_tokens=6, do_sample=False)
         assert got[i][:6] == ref[0, ids.shape[1]:].tolist(), (kind, i, got[i], ref[0, ids.shape[1]:].tolist())
+
+
+def _image(w, h, seed=0):
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    rng = np.random.default_rng(seed)
+    # smooth content: resampling filters of different libraries agree on it far better than on noise
+    base = rng.integers(0, 255, size=(4, 4, 3), dtype=np.uint8)
+    img = Image.fromarray(base).resize((w, h), Image.BICUBIC)
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    return buf.getvalue(), img
+
+
+@pytest.mark.parametrize("w,h", [(52, 40), (40, 52), (200, 90), (90, 200), (28, 28), (640, 480), (17, 300)])
+def test_idefics3_tile_grid_matches_the_transformers_processor(w, h):
+    """Resized size, grid and number of views against the image processor of transformers (tile 28, longest edge 112)."""
+    from tgi_b200.models.idefics3 import split_views, tile_grid
+
+    data, img = _image(w, h)
+    proc = transformers.Idefics3ImageProcessor(size={"longest_edge": 112}, max_image_size={"longest_edge": 28},
+                                               do_image_splitting=True)
+    out = proc(images=[img], return_tensors="pt", return_row_col_info=True)
+    rows, cols = int(out["rows"][0][0]), int(out["cols"][0][0])
+    _, _, r, c = tile_grid(h, w, 112, 28)
+    assert (r, c) == (rows, cols)
+    sp = split_views(data, 112, 28)
+    px = out["pixel_values"][0]
+    assert tuple(sp.views.shape) == tuple(px.shape) == (rows * cols + 1 if rows else 1, 3, 28, 28)
+    # same content up to the resampling filter's implementation
+    assert (sp.views - px).abs().mean().item() < 0.08
+
+
+def _marker_tokenizer(path, image_token="<image>"):
+    """A character-level tokenizer with the Idefics3 marker tokens, saved as tokenizer.json."""
+    from tokenizers import Regex, Tokenizer, models, pre_tokenizers
+
+    chars = ["<unk>"] + [chr(c) for c in range(32, 127)] + ["\n"]
+    tok = Tokenizer(models.WordLevel({c: i for i, c in enumerate(chars)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Split(Regex("."), "isolated")
+    # "." does not match a newline: split those as well
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(r"\n"), "isolated"),
+                                                 pre_tokenizers.Split(Regex("."), "isolated")])
+    specials = ["<fake_token_around_image>", "<global-img>", image_token] + [
+        f"<row_{r}_col_{c}>" for r in range(1, 5) for c in range(1, 5)]
+    tok.add_special_tokens(specials)
+    tok.save(str(path / "tokenizer.json"))
+    (path / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "PreTrainedTokenizerFast",
+                                                            "unk_token": "<unk>"}))
+    return {s: tok.token_to_id(s) for s in specials}
+
+
+def test_idefics3_split_image_generation_matches_transformers(tmp_path):
+    """A 52 x 40 image with 28-pixel tiles and a longest edge of 56: a 2 x 2 grid plus the global view.  The prompt
+    rows hold marker embeddings and tile features in the processor's order; greedy tokens equal those of
+    transformers on the equivalent input ids and pixel values."""
+    from tgi_b200.models.idefics3 import Idefics3CausalLM, expansion_length, split_views
+
+    torch.manual_seed(0)
+    ids_of = _marker_tokenizer(tmp_path)
+    image_id = ids_of["<image>"]
+    cfg = transformers.Idefics3Config(vision_config=VIS, text_config=dict(TXT, model_type="llama"),
+                                      image_token_id=image_id, scale_factor=2)
+    hf = transformers.Idefics3ForConditionalGeneration(cfg).eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    c = json.loads((tmp_path / "config.json").read_text())
+    c["vision_config"] = dict(c["vision_config"], **VIS)
+    (tmp_path / "config.json").write_text(json.dumps(c))
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps(
+        {"size": {"longest_edge": 56}, "max_image_size": {"longest_edge": 28}, "do_image_splitting": True}))
+    model = get_model(str(tmp_path), dtype="float32", device=torch.device("cpu"))
+    assert isinstance(model, Idefics3CausalLM) and model.markers is not None
+    seq = model.tokens_per_image
+    png = _png(1)
+    sp = split_views(png, 56, 28)
+    assert (sp.rows, sp.cols) == (2, 2) and sp.views.shape[0] == 5
+    nl = model.tokenizer("\n", add_special_tokens=False)["input_ids"]
+    nlnl = model.tokenizer("\n\n", add_special_tokens=False)["input_ids"]
+    R = expansion_length(2, 2, seq, len(nl), len(nlnl))
+    reqs = [_request(0, [("text", "ab"), ("image", png), ("text", "cde")], 6, range(1, 8))]
+    model.init_kv_cache(12)
+    batch = model.batch_type.from_pb(pb.Batch(id=0, requests=reqs, size=1), model.tokenizer, torch.float32,
+                                     torch.device("cpu"), 0)
+    prompt = list(batch.seqs[0].ids)
+    assert prompt.count(image_id) == R and len(prompt) == 2 + R + 3
+    got = []
+    while batch is not None:
+        gens, batch, _ = model.generate_token(batch)
+        for g in gens:
+            got.extend(g.tokens.token_ids)
+    # the same prompt for transformers: real marker ids around runs of the image token
+    fake, glob = ids_of["<fake_token_around_image>"], ids_of["<global-img>"]
+    run = []
+    for r in range(2):
+        for col in range(2):
+            run += [fake, ids_of[f"<row_{r + 1}_col_{col + 1}>"]] + [image_id] * seq
+        run += nl if r == 0 else nlnl
+    run += [fake, glob] + [image_id] * seq + [fake]
+    assert len(run) == R
+    text_a = model.tokenizer("ab", add_special_tokens=False)["input_ids"]
+    text_b = model.tokenizer("cde", add_special_tokens=False)["input_ids"]
+    ids = torch.tensor([text_a + run + text_b])
+    px = sp.views.unsqueeze(0)
+    with torch.no_grad():
+        ref = hf.generate(input_ids=ids, attention_mask=torch.ones_like(ids), pixel_values=px,
+                          pixel_attention_mask=torch.ones(1, px.shape[1], 28, 28, dtype=torch.long),
+                          max_new_tokens=6, min_new_tokens=6, do_sample=False)
+    assert got[:6] == ref[0, ids.shape[1]:].tolist(), (got, ref[0, ids.shape[1]:].tolist())

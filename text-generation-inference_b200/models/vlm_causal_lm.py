@@ -474,6 +474,11 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
 
         runner_cls = LlavaNextCausalLM
         extra_kw = dict(image_newline=weights.get_tensor(newline), pinpoints=cfg.get("image_grid_pinpoints"))
+    if mt == "idefics3":
+        from .idefics3 import Idefics3CausalLM, processor_settings      # image splitting into tiles + global view
+
+        longest, split = processor_settings(path, int(vis["image_size"]))
+        runner_cls, extra_kw = Idefics3CausalLM, dict(longest_edge=longest, do_split=split)
     runner = runner_cls(model, tower, projector, tokenizer, dtype, device, rank, world, image_token, drop_cls,
                          scale, speculate=speculate, **extra_kw,
                          kv_cache_dtype=resolve_kv_dtype(kv_cache_dtype, dtype), max_prefill_tokens=max_prefill_tokens)

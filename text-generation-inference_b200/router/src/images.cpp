@@ -316,10 +316,54 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     return pc.is_object() && pc.has("resampler_n_latents") ? static_cast<uint32_t>(pc["resampler_n_latents"].as_double()) : 64;
   }
   if (mt == "idefics3") {
-    // pixel shuffle folds scale x scale patches of the global view into one row
+    // pixel shuffle folds scale x scale patches of a view into one row
     const uint32_t side = static_cast<uint32_t>(num("image_size", 364) / num("patch_size", 14));
     const uint32_t f = config.has("scale_factor") ? static_cast<uint32_t>(config["scale_factor"].as_double()) : 2;
-    return f ? (side / f) * (side / f) : side * side;
+    const uint32_t seq = f ? (side / f) * (side / f) : side * side;
+    // Image splitting (the shard's models/idefics3.py does the same arithmetic): `_idefics3` is added to the config by
+    // the router's start-up when the tokenizer has the marker tokens: {longest_edge, tile, split, nl, nlnl}
+    if (!config.has("_idefics3") || width == 0 || height == 0) return seq;
+    const json::Value& sp = config["_idefics3"];
+    if (!sp.has("split") || !sp["split"].as_bool()) return seq + 3;
+    const long tile = static_cast<long>(sp["tile"].as_double());
+    const long longest = static_cast<long>(sp["longest_edge"].as_double());
+    const uint32_t nl = static_cast<uint32_t>(sp["nl"].as_double()), nlnl = static_cast<uint32_t>(sp["nlnl"].as_double());
+    long w, h;
+    const double aspect = static_cast<double>(width) / static_cast<double>(height);
+    if (width >= height) {
+      w = longest;
+      h = static_cast<long>(static_cast<double>(w) / aspect);
+      h += h % 2;
+    } else {
+      h = longest;
+      w = static_cast<long>(static_cast<double>(h) * aspect);
+      w += w % 2;
+    }
+    h = std::max(h, 1L);
+    w = std::max(w, 1L);
+    const long upper = 4096;
+    const double aspect2 = static_cast<double>(w) / static_cast<double>(h);
+    if (w >= h && w > upper) {
+      w = upper;
+      h = static_cast<long>(static_cast<double>(w) / aspect2);
+    } else if (h > w && h > upper) {
+      h = upper;
+      w = static_cast<long>(static_cast<double>(h) * aspect2);
+    }
+    h = std::max(h, 1L);
+    w = std::max(w, 1L);
+    const double aspect3 = static_cast<double>(w) / static_cast<double>(h);
+    auto up = [tile](long v) { return (v + tile - 1) / tile * tile; };
+    if (w >= h) {
+      w = up(w);
+      h = up(static_cast<long>(static_cast<double>(w) / aspect3));
+    } else {
+      h = up(h);
+      w = up(static_cast<long>(static_cast<double>(h) * aspect3));
+    }
+    if (h <= tile && w <= tile) return seq + 3;      // one view between the markers
+    const uint32_t rows = static_cast<uint32_t>(h / tile), cols = static_cast<uint32_t>(w / tile);
+    return rows * cols * (seq + 2) + (rows - 1) * nl + nlnl + seq + 3;
   }
   return 0;
 }

@@ -257,7 +257,46 @@ int main(int argc, char** argv) {
         }
       }
     }
-    api::Router router(backend, python_text_services(), rc, &metrics);
+    api::TextServices text_services = python_text_services();
+    if (rc.model_config.is_object() && rc.model_config.has("model_type") &&
+        rc.model_config["model_type"].as_string() == "idefics3") {
+      // Image splitting of Idefics3 / SmolVLM: the prompt of a split image contains marker tokens.  When the tokenizer
+      // has them, the token count of an image follows the shard's layout (models/idefics3.py); the settings come
+      // from the checkpoint's preprocessor_config.json.
+      try {
+        const auto fake = text_services.encode("<fake_token_around_image>", false, 0);
+        const auto glob = text_services.encode("<global-img>", false, 0);
+        const auto rc11 = text_services.encode("<row_1_col_1>", false, 0);
+        if (fake.size() == 1 && glob.size() == 1 && rc11.size() == 1) {
+          const json::Value& vis = rc.model_config["vision_config"];
+          const double tile = vis.is_object() && vis.has("image_size") ? vis["image_size"].as_double() : 364;
+          double longest = 4 * tile;
+          bool split = true;
+          std::ifstream pf(tokenizer + "/preprocessor_config.json");
+          if (pf) {
+            std::stringstream ss;
+            ss << pf.rdbuf();
+            try {
+              json::Value pc = json::Value::parse(ss.str());
+              if (pc.has("size") && pc["size"].is_object() && pc["size"].has("longest_edge"))
+                longest = pc["size"]["longest_edge"].as_double();
+              if (pc.has("do_image_splitting")) split = pc["do_image_splitting"].as_bool();
+            } catch (const std::exception&) {
+            }
+          }
+          json::Value sp = json::Value::object();
+          sp.set("tile", tile);
+          sp.set("longest_edge", longest);
+          sp.set("split", split);
+          sp.set("nl", static_cast<long>(text_services.encode("\n", false, 0).size()));
+          sp.set("nlnl", static_cast<long>(text_services.encode("\n\n", false, 0).size()));
+          rc.model_config.set("_idefics3", sp);
+        }
+      } catch (const std::exception& e) {
+        std::cerr << "[router] idefics3 marker probe failed: " << e.what() << std::endl;
+      }
+    }
+    api::Router router(backend, text_services, rc, &metrics);
 
     http::Server server(args.get("hostname", "0.0.0.0"), static_cast<int>(args.num("port", 3000)),
                         static_cast<size_t>(args.num("payload-limit", 2000000)));
