@@ -583,6 +583,11 @@ class CompressedTensorsLoader(WeightsLoader):
     """
 
     def __init__(self, config: dict):
+        # 2:4-sparse checkpoints ("marlin-24") are stored in the permuted layout of one particular CUDA kernel
+        # (reference: ``layers/compressed_tensors/wna16_int_24.py``); that layout is not decoded here
+        if str(config.get("format", "")).lower() in ("marlin-24", "marlin_24"):
+            raise NotImplementedError("compressed-tensors checkpoints in the 2:4-sparse `marlin-24` format are not "
+                                      "supported; use the dense pack-quantized or fp8 variant of the model")
         self.ignore = config.get("ignore", []) or []
         self.groups = []
         for g in (config.get("config_groups") or {}).values():
