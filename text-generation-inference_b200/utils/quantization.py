@@ -219,6 +219,21 @@ def _unpack_int32(packed: torch.Tensor, bits: int, dim: int) -> torch.Tensor:
     return out.reshape(packed.shape[0], packed.shape[1] * per)
 
 
+def _pack_int32(vals: torch.Tensor, bits: int, dim: int) -> torch.Tensor:
+    """Inverse of ``_unpack_int32``: ``32/bits`` little-endian fields per int32 along ``dim`` (0 or 1)."""
+    per = 32 // bits
+    v = vals.to(torch.int64) & ((1 << bits) - 1)
+    shifts = torch.arange(0, 32, bits, device=vals.device, dtype=torch.int64)[:per]
+    if dim == 0:
+        v = v.view(vals.shape[0] // per, per, vals.shape[1])
+        word = (v << shifts.view(1, -1, 1)).sum(1)
+    else:
+        v = v.view(vals.shape[0], vals.shape[1] // per, per)
+        word = (v << shifts.view(1, 1, -1)).sum(2)
+    word = torch.where(word >= (1 << 31), word - (1 << 32), word)        # two's complement of the top field
+    return word.to(torch.int32)
+
+
 def pack_gptq_for_kernel(w: "GPTQWeight"):
     """Canonical packed form of a 4-bit GPTQ / AWQ layer for the weight-only GEMM (``ops/csrc/gemm_wq_sm100.cu``), or
     ``None`` when the layer does not fit it (other bit widths, group sizes that are no multiple of 64, odd shapes).
@@ -605,13 +620,28 @@ class CompressedTensorsLoader(WeightsLoader):
 
     def _int_weight(self, weights, prefix, getter) -> Weight:
         if weights.has_tensor(f"{prefix}.weight_packed"):
+            # pack-quantized int4: `weight_packed` int32 [N, K/8] (fields along K, offset binary), `weight_scale`
+            # [N, G], optionally `weight_zero_point` int32 [N/8, G] (fields along N).  Re-expressed in the GPTQ layout
+            # so that the layer is served by the weight-only GEMM (packed on the device) like any other 4-bit layer.
             packed = getter(f"{prefix}.weight_packed", False)
             scale = getter(f"{prefix}.weight_scale", True).float()
             bits = 4
-            vals = _unpack_int32(packed, bits, dim=1).float() - 8
-            K = vals.shape[1]
-            gs = K // scale.shape[1] if scale.dim() == 2 and scale.shape[1] > 0 else K
-            w = vals * scale.repeat_interleave(gs, dim=1)[:, :K]
+            iw = _unpack_int32(packed, bits, dim=1)                                  # [N, K], 0..15
+            N, K = iw.shape
+            scale = scale.reshape(N, -1)
+            G = scale.shape[1]
+            gs = K // G
+            if weights.has_tensor(f"{prefix}.weight_zero_point"):
+                zp = _unpack_int32(getter(f"{prefix}.weight_zero_point", False), bits, dim=0)[:N].reshape(N, G)
+            else:
+                zp = torch.full((N, G), 8, dtype=iw.dtype, device=iw.device)
+            if N % 8 == 0 and K % 8 == 0 and K % G == 0:
+                return GPTQWeight(qweight=_pack_int32(iw.t().contiguous(), bits, dim=0),
+                                  qzeros=_pack_int32((zp.t() - 1).contiguous(), bits, dim=1),
+                                  scales=scale.t().contiguous().to(weights.dtype), g_idx=None, bits=bits, groupsize=gs,
+                                  awq=False, sym=not weights.has_tensor(f"{prefix}.weight_zero_point"),
+                                  dtype=weights.dtype)
+            w = (iw.float() - zp.float().repeat_interleave(gs, dim=1)[:, :K]) * scale.repeat_interleave(gs, dim=1)[:, :K]
             return UnquantizedWeight(w.to(weights.dtype))
         q = getter(f"{prefix}.weight", False)
         scale = getter(f"{prefix}.weight_scale", True).float().reshape(-1)
@@ -647,6 +677,10 @@ class CompressedTensorsLoader(WeightsLoader):
         if all(isinstance(p, Int8Weight) for p in parts):
             return Int8Weight(torch.cat([p.qweight for p in parts], 0), torch.cat([p.scale for p in parts], 0),
                               weights.dtype)
+        if all(isinstance(p, GPTQWeight) for p in parts) and len({(p.bits, p.groupsize) for p in parts}) == 1:
+            return GPTQWeight(torch.cat([p.qweight for p in parts], 1), torch.cat([p.qzeros for p in parts], 1),
+                              torch.cat([p.scales for p in parts], 1), None, parts[0].bits, parts[0].groupsize, False,
+                              all(p.sym for p in parts), parts[0].dtype)
         return UnquantizedWeight(torch.cat([p.weight if isinstance(p, UnquantizedWeight) else p.dequantize()
                                             for p in parts], 0))
 
