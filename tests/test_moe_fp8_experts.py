@@ -69,3 +69,25 @@ def test_fp8_experts_are_dequantised_with_their_scales(tmp_path, scheme):
     ids = [5, 17, 250, 33, 90, 12, 7]
     a, b = _logits(qdir, ids), _logits(ddir, ids)
     assert torch.allclose(a, b, atol=2e-4, rtol=1e-4), (a - b).abs().max()
+
+
+def test_packed_integer_experts_are_dequantised_through_the_loader(tmp_path):
+    """A GPTQ-packed expert projection (`qweight` / `qzeros` / `scales` / `g_idx`) loads as the dense matrix it
+    encodes, whole or as a rank's slice."""
+    from tgi_b200.models.decoder import _expert_weight
+    from tgi_b200.utils.quantization import GPTQLoader, _pack_int32
+    from tgi_b200.utils.weights import Weights, save_safetensors
+
+    torch.manual_seed(0)
+    N, K, G = 32, 128, 64
+    q = torch.randint(0, 16, (K, N))
+    zeros = torch.randint(1, 16, (K // G, N))
+    scales = (torch.rand(K // G, N) * 0.02 + 0.001).to(torch.bfloat16)
+    gi = torch.arange(K) // G
+    dense = ((q.float() - zeros.float()[gi]) * scales.float()[gi]).t().contiguous()
+    save_safetensors({"e.qweight": _pack_int32(q, 4, dim=0), "e.qzeros": _pack_int32(zeros - 1, 4, dim=1),
+                      "e.scales": scales, "e.g_idx": gi.to(torch.int32)}, tmp_path / "model.safetensors", {"format": "pt"})
+    w = Weights([tmp_path / "model.safetensors"], "cpu", torch.bfloat16, loader=GPTQLoader(4, G, False, "gptq"))
+    got = _expert_weight(w, {}, "e")
+    torch.testing.assert_close(got.float(), dense.to(torch.bfloat16).float(), atol=0, rtol=0)
+    w.close()

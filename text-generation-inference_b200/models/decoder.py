@@ -313,6 +313,16 @@ def _expert_weight(weights, cfg, name: str, dim: Optional[int] = None) -> torch.
     from ..utils.weights import shard_bounds
 
     fp8 = getattr(torch, "float8_e4m3fn", None)
+    if not weights.has_tensor(f"{name}.weight"):
+        # packed integer experts (GPTQ / AWQ `qweight`, compressed-tensors `weight_packed`): dequantised through the
+        # checkpoint's loader, like the fp8 ones (the reference serves them with a Marlin MoE kernel,
+        # ``layers/moe/gptq_marlin.py``)
+        qw = weights.weights_loader.get_weights(weights, name)
+        w = qw.dequantize().to(weights.dtype) if hasattr(qw, "dequantize") else qw.weight.to(weights.dtype)
+        if dim is not None:
+            lo, hi = shard_bounds(w.shape[dim], weights.process_group.rank(), weights.process_group.size())
+            w = w.narrow(dim, lo, hi - lo).contiguous()
+        return w
     full = weights.get_tensor(f"{name}.weight", to_dtype=False)
     if fp8 is None or full.dtype != fp8:
         return weights.get_tensor(f"{name}.weight") if dim is None else weights.get_sharded(f"{name}.weight", dim=dim)
