@@ -72,10 +72,21 @@ def test_list_content_is_flattened_with_image_placeholders():
 def test_tools_go_to_templates_that_know_them_and_into_the_last_turn_otherwise():
     tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object"}}}]
     aware = "{% if tools %}T:{{ tools | length }};{% endif %}{% for m in messages %}{{ m['content'] }}{% endfor %}"
-    assert render(aware, CHAT[:1], tools=tools, tool_prompt="Use: ")["text"] == "T:1;Hello, how are you?"
+    assert render(aware, CHAT[:1], tools=tools, tool_prompt="Use: ")["text"] == "T:1;Hello, how are you?\n---\nUse: "
     plain = "{% for m in messages %}{{ m['content'] }}{% endfor %}"
-    text = render(plain, CHAT[:1], tools=tools, tool_prompt="Use: ")["text"]
-    assert text.startswith("Hello, how are you?\n---\nUse: ") and "get_weather" in text
+    text = render(plain, CHAT[:1], tools=tools, tool_prompt="Use them.")["text"]
+    assert text.startswith('Hello, how are you?\n---\n[{"type":"function"') and text.endswith("]\nUse them.")
+
+
+def test_a_trailing_assistant_message_is_continued():
+    """The rendered prompt ends right after the assistant's partial answer: no end-of-turn marker, no new
+    generation prompt (the reference's continue_final_message behaviour)."""
+    tpl = ("{% for m in messages %}<|{{ m['role'] }}|>{{ m['content'] }}</s>\n{% endfor %}"
+           "{% if add_generation_prompt %}<|assistant|>{% endif %}")
+    msgs = [{"role": "user", "content": "Which is bigger?"}, {"role": "assistant", "content": "the elephant, but "}]
+    assert render(tpl, msgs, True)["text"] == "<|user|>Which is bigger?</s>\n<|assistant|>the elephant, but"
+    # a conversation that ends with the user is rendered as before
+    assert render(tpl, msgs[:1], True)["text"] == "<|user|>Which is bigger?</s>\n<|assistant|>"
 
 
 def test_missing_template_is_an_error():

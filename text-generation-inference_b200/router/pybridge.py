@@ -142,11 +142,15 @@ def apply_chat_template(arg: str) -> str:
             m["content"] = "".join(parts)
         norm.append(m)
     uses_tools = "tools" in template
-    if tools and not uses_tools and norm:
-        # describe the tools in the last user turn for templates that have no tools section
-        text = json.dumps(tools, ensure_ascii=False)
+    if tools and norm:
+        # the last message carries the tool prompt; templates without a tools section also get the tool list there
+        # (chat_template.rs:83-105: "\n---\n" + tools + "\n" + prompt, or "\n---\n" + prompt)
+        if uses_tools:
+            text = f"\n---\n{tool_prompt}"
+        else:
+            text = f"\n---\n{json.dumps(tools, ensure_ascii=False, separators=(',', ':'))}\n{tool_prompt}"
         norm[-1] = dict(norm[-1])
-        norm[-1]["content"] = f"{norm[-1].get('content') or ''}\n---\n{tool_prompt}{text}"
+        norm[-1]["content"] = f"{norm[-1].get('content') or ''}{text}"
     try:
         tpl = _jinja_env().from_string(template)
         rendered = tpl.render(messages=norm, bos_token=_STATE.get("bos_token") or "",
@@ -156,7 +160,14 @@ def apply_chat_template(arg: str) -> str:
                               guideline=a.get("guideline"))
     except Exception as err:  # noqa: BLE001
         return _err(f"Template error: {err}", "template_error")
-    # assistant prefill: a trailing assistant message is continued, not closed
+    # assistant prefill: a trailing assistant message is continued, not closed.  The rendered text is cut right after
+    # the last occurrence of that message's content (chat_template.rs:120-136, after the text-generation pipeline of
+    # transformers), which drops the end-of-turn marker and the generation prompt the template added behind it.
+    if norm and norm[-1].get("role") == "assistant" and isinstance(norm[-1].get("content"), str) and norm[-1]["content"]:
+        content = norm[-1]["content"]
+        at = rendered.rfind(content)
+        if at >= 0:
+            rendered = rendered[:at + len(content)].rstrip()
     return _ok(text=rendered)
 
 
