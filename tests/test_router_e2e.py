@@ -273,6 +273,16 @@ def test_completions_and_misc_routes(stack):
     st, _, body = _post(stack["port"], "/v1/completions", {"prompt": ["a", "b"], "max_tokens": 2})
     out = json.loads(body)
     assert st == 200 and len(out["choices"]) == 2 and out["usage"]["completion_tokens"] == 4
+    # four prompts of one request run side by side; every choice keeps the index of its prompt
+    prompts = ["one", "two", "three", "four"]
+    st, _, body = _post(stack["port"], "/v1/completions", {"prompt": prompts, "max_tokens": 3, "temperature": 0})
+    many = json.loads(body)
+    assert st == 200 and [c["index"] for c in many["choices"]] == [0, 1, 2, 3]
+    for i, pr in enumerate(prompts):
+        st, _, body = _post(stack["port"], "/v1/completions", {"prompt": pr, "max_tokens": 3, "temperature": 0})
+        assert json.loads(body)["choices"][0]["text"] == many["choices"][i]["text"]
+    st, _, body = _post(stack["port"], "/v1/completions", {"prompt": ["a"] * 5, "max_tokens": 1})
+    assert st == 422          # more prompts than --max-client-batch-size (4)
     st, _, body = _post(stack["port"], "/tokenize", {"inputs": "hey"})
     assert st == 200 and [t["id"] for t in json.loads(body)] == [107, 104, 124]
     st, body = _get(stack["port"], "/info")

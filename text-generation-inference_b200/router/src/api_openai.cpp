@@ -8,6 +8,9 @@
 
 #include "api.hpp"
 
+#include <exception>
+#include <thread>
+
 namespace api {
 
 using json::Value;
@@ -436,10 +439,34 @@ void Router::h_completions(const http::Request& req, http::Response& resp) {
     if (!stream) {
       Value choices = Value::array();
       uint32_t prompt_tokens = 0, completion_tokens = 0;
+      // the prompts of one request run side by side, so the scheduler batches them (server.rs joins their futures)
+      std::vector<GenerateParams> ps;
+      for (const auto& pr : prompts) ps.push_back(validate(pr, params));
+      std::vector<Collected> done(prompts.size());
+      std::vector<std::exception_ptr> failed(prompts.size());
+      {
+        std::vector<std::thread> workers;
+        for (size_t i = 1; i < prompts.size(); ++i)
+          workers.emplace_back([&, i] {
+            try {
+              auto permit = acquire();
+              done[i] = generate(ps[i]);
+            } catch (...) {
+              failed[i] = std::current_exception();
+            }
+          });
+        try {
+          auto permit = acquire();
+          done[0] = generate(ps[0]);
+        } catch (...) {
+          failed[0] = std::current_exception();
+        }
+        for (auto& w : workers) w.join();
+      }
+      for (auto& f : failed)
+        if (f) std::rethrow_exception(f);
       for (size_t i = 0; i < prompts.size(); ++i) {
-        auto permit = acquire();
-        GenerateParams p = validate(prompts[i], params);
-        Collected c = generate(p);
+        Collected& c = done[i];
         Value choice = Value::object();
         choice.set("index", static_cast<unsigned>(i));
         choice.set("text", c.output_text);
