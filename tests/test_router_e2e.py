@@ -283,6 +283,19 @@ def test_completions_and_misc_routes(stack):
         assert json.loads(body)["choices"][0]["text"] == many["choices"][i]["text"]
     st, _, body = _post(stack["port"], "/v1/completions", {"prompt": ["a"] * 5, "max_tokens": 1})
     assert st == 422          # more prompts than --max-client-batch-size (4)
+    # streamed: the chunks of the four prompts share the response, each tagged with its prompt's index
+    st, _, body = _post(stack["port"], "/v1/completions", {"prompt": prompts, "max_tokens": 3, "temperature": 0,
+                                                           "stream": True})
+    assert st == 200 and body.rstrip().endswith("data: [DONE]")
+    chunks = [0, 0, 0, 0]
+    finished = set()
+    for line in body.splitlines():
+        if line.startswith("data:{"):
+            ch = json.loads(line[5:])["choices"][0]
+            chunks[ch["index"]] += 1
+            if ch["finish_reason"]:
+                finished.add(ch["index"])
+    assert finished == {0, 1, 2, 3} and chunks == [3, 3, 3, 3]
     st, _, body = _post(stack["port"], "/tokenize", {"inputs": "hey"})
     assert st == 200 and [t["id"] for t in json.loads(body)] == [107, 104, 124]
     st, body = _get(stack["port"], "/info")

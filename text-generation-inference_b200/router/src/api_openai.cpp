@@ -9,6 +9,7 @@
 #include "api.hpp"
 
 #include <exception>
+#include <mutex>
 #include <thread>
 
 namespace api {
@@ -493,10 +494,15 @@ void Router::h_completions(const http::Request& req, http::Response& resp) {
     }
     resp.set_header("x-accel-buffering", "no");
     resp.begin_stream(200, "text/event-stream");
-    for (size_t i = 0; i < prompts.size(); ++i) {
+    // all prompts are validated before the first byte goes out; their token streams are interleaved on the one
+    // response, every chunk tagged with the index of its prompt
+    std::vector<GenerateParams> ps;
+    for (const auto& pr : prompts) ps.push_back(validate(pr, params));
+    std::mutex write_mu;
+    std::vector<std::exception_ptr> failed(prompts.size());
+    auto run_one = [&](size_t i) {
       auto permit = acquire();
-      GenerateParams p = validate(prompts[i], params);
-      stream_tokens(p, [&](const sched::StreamEvent& ev, const std::string&) {
+      stream_tokens(ps[i], [&, i](const sched::StreamEvent& ev, const std::string&) {
         if (ev.kind == sched::StreamEvent::Prefill) return true;
         Value choice = Value::object();
         choice.set("index", static_cast<unsigned>(i));
@@ -513,9 +519,29 @@ void Router::h_completions(const http::Request& req, http::Response& resp) {
         o.set("model", model);
         o.set("system_fingerprint", fingerprint);
         o.set("choices", choices);
+        std::lock_guard<std::mutex> g(write_mu);
         return resp.write_chunk("data:" + o.dump() + "\n\n") && !resp.client_gone();
       });
+    };
+    {
+      std::vector<std::thread> workers;
+      for (size_t i = 1; i < prompts.size(); ++i)
+        workers.emplace_back([&, i] {
+          try {
+            run_one(i);
+          } catch (...) {
+            failed[i] = std::current_exception();
+          }
+        });
+      try {
+        run_one(0);
+      } catch (...) {
+        failed[0] = std::current_exception();
+      }
+      for (auto& w : workers) w.join();
     }
+    for (auto& f : failed)
+      if (f) std::rethrow_exception(f);
     resp.write_chunk("data: [DONE]\n\n");
     resp.end_stream();
   } catch (const ApiError& e) {
