@@ -324,7 +324,7 @@ int main(int argc, char** argv) {
         "             --max-client-batch-size 4 --payload-limit 2000000 --validation-workers 2\n"
         "  serving:   --hostname 0.0.0.0 --port 3000 --prometheus-port 9000 --api-key KEY --cors-allow-origin a,b\n"
         "             --disable-grammar-support --enable-prefill-logprobs --watermark-gamma G --watermark-delta D\n"
-        "  operation: --json-output --otlp-endpoint URL --otlp-service-name NAME --usage-stats on|off|no-stack --usage-stats-endpoint URL --usage-stats-file PATH\n"
+        "  operation: --json-output --otlp-endpoint URL --otlp-service-name NAME --usage-stats on|off|no-stack --usage-stats-endpoint URL --usage-stats-file PATH --max-image-fetch-size BYTES\n"
         "             --graceful-termination-timeout 90 --env --python python\n";
     return args.has("help") ? 0 : 2;
   }
@@ -502,7 +502,7 @@ int main(int argc, char** argv) {
   for (const char* f : {"port", "hostname", "max-concurrent-requests", "max-best-of", "max-stop-sequences",
                         "max-top-n-tokens", "max-total-tokens", "max-batch-total-tokens",
                         "waiting-served-ratio", "max-waiting-tokens", "max-batch-size", "max-client-batch-size",
-                        "api-key", "payload-limit", "repo-root", "prometheus-port", "cors-allow-origin",
+                        "api-key", "payload-limit", "max-image-fetch-size", "repo-root", "prometheus-port", "cors-allow-origin",
                         "tokenizer-config-path", "validation-workers", "revision"})
     if (args.has(f)) { rcmd.push_back(std::string("--") + f); rcmd.push_back(args.get(f)); }
   if (max_input) { rcmd.push_back("--max-input-tokens"); rcmd.push_back(std::to_string(max_input)); }

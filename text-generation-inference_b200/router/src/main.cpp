@@ -234,6 +234,8 @@ int main(int argc, char** argv) {
     rc.max_total_tokens = max_total;
     rc.max_client_batch_size = static_cast<uint32_t>(args.num("max-client-batch-size", 4));
     rc.disable_grammar_support = args.flag("disable-grammar-support");
+    // largest image a request may carry or point at (reference: --max-image-fetch-size, 1 GiB by default)
+    rc.max_image_bytes = static_cast<size_t>(args.num("max-image-fetch-size", 1073741824L));
     rc.api_key = args.get("api-key");
     {
       std::stringstream origins(args.get("cors-allow-origin"));
