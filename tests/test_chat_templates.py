@@ -93,3 +93,22 @@ def test_missing_template_is_an_error():
     pybridge._STATE.update(chat_template=None)
     out = json.loads(pybridge.apply_chat_template(json.dumps(dict(messages=CHAT))))
     assert not out.get("ok") and "no chat template" in out["error"]
+
+
+def test_template_files_beside_the_tokenizer_config(tmp_path):
+    """chat_template.json overrides tokenizer_config.json; processor_config.json and chat_template.jinja are read when
+    nothing else defines a template."""
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"chat_template": "from-tokenizer-config"}))
+    out = json.loads(pybridge.load(json.dumps({"tokenizer_name": str(tmp_path)})))
+    assert out["has_chat_template"] and pybridge._STATE["chat_template"] == "from-tokenizer-config"
+    (tmp_path / "processor_config.json").write_text(json.dumps({"chat_template": "from-processor", "image_seq_len": 169}))
+    pybridge.load(json.dumps({"tokenizer_name": str(tmp_path)}))
+    assert pybridge._STATE["chat_template"] == "from-processor"
+    (tmp_path / "chat_template.json").write_text(json.dumps({"chat_template": "stand-alone"}))
+    pybridge.load(json.dumps({"tokenizer_name": str(tmp_path)}))
+    assert pybridge._STATE["chat_template"] == "stand-alone"
+    other = tmp_path / "jinja"
+    other.mkdir()
+    (other / "chat_template.jinja").write_text("{{ messages[0]['content'] }}!")
+    pybridge.load(json.dumps({"tokenizer_name": str(other)}))
+    assert json.loads(pybridge.apply_chat_template(json.dumps(dict(messages=CHAT))))["text"] == CHAT[0]["content"] + "!"

@@ -40,7 +40,24 @@ def load(arg: str) -> str:
                 cfg[name] = json.load(fh)
     _STATE["config"] = cfg
     tc = cfg.get("tokenizer_config.json", {})
-    template = a.get("chat_template") or getattr(tok, "chat_template", None) or tc.get("chat_template")
+    # A stand-alone chat_template.json overrides the tokenizer's template (server.rs:1662-1689); vision-language
+    # checkpoints also keep theirs in processor_config.json, newer ones in chat_template.jinja.
+    standalone = None
+    if path:
+        for name in ("chat_template.json", "processor_config.json"):
+            f = os.path.join(path, name)
+            if standalone is None and os.path.exists(f):
+                try:
+                    with open(f) as fh:
+                        standalone = json.load(fh).get("chat_template")
+                except (OSError, ValueError):
+                    standalone = None
+        f = os.path.join(path, "chat_template.jinja")
+        if standalone is None and os.path.exists(f):
+            with open(f) as fh:
+                standalone = fh.read()
+    template = (a.get("chat_template") or standalone or getattr(tok, "chat_template", None)
+                or tc.get("chat_template"))
     if isinstance(template, list):  # named templates: take "default"
         template = next((t["template"] for t in template if t.get("name") == "default"), template[0]["template"])
     _STATE["chat_template"] = template
