@@ -285,6 +285,10 @@ def test_completions_and_misc_routes(stack):
     st, _, body = _post(stack["port"], "/v1/completions", {"prompt": prompts, "max_tokens": 3, "temperature": 0,
                                                            "stream": True})
     assert st == 200 and body.rstrip().endswith("data: [DONE]")
+    st, _, body = _post(stack["port"], "/v1/completions", {"prompt": ["ok", "x" * 100], "max_tokens": 3, "stream": True})
+    assert st == 422 and "inputs" in body        # the over-long second prompt is refused before the stream starts
+    st, _, body = _post(stack["port"], "/v1/completions", {"prompt": prompts, "max_tokens": 3, "temperature": 0,
+                                                           "stream": True})
     chunks = [0, 0, 0, 0]
     finished = set()
     for line in body.splitlines():

@@ -492,12 +492,12 @@ void Router::h_completions(const http::Request& req, http::Response& resp) {
       resp.send(200, "application/json", out.dump());
       return;
     }
-    resp.set_header("x-accel-buffering", "no");
-    resp.begin_stream(200, "text/event-stream");
-    // all prompts are validated before the first byte goes out; their token streams are interleaved on the one
-    // response, every chunk tagged with the index of its prompt
+    // all prompts are validated before the first byte goes out (a bad one is a plain 422); their token streams are
+    // interleaved on the one response, every chunk tagged with the index of its prompt
     std::vector<GenerateParams> ps;
     for (const auto& pr : prompts) ps.push_back(validate(pr, params));
+    resp.set_header("x-accel-buffering", "no");
+    resp.begin_stream(200, "text/event-stream");
     std::mutex write_mu;
     std::vector<std::exception_ptr> failed(prompts.size());
     auto run_one = [&](size_t i) {
