@@ -180,3 +180,64 @@ def test_idefics3_split_image_generation_matches_transformers(tmp_path):
                           pixel_attention_mask=torch.ones(1, px.shape[1], 28, 28, dtype=torch.long),
                           max_new_tokens=6, min_new_tokens=6, do_sample=False)
     assert got[:6] == ref[0, ids.shape[1]:].tolist(), (got, ref[0, ids.shape[1]:].tolist())
+
+
+@pytest.mark.parametrize("split", [False, True])
+def test_idefics2_marker_layout_matches_transformers(tmp_path, split):
+    """Marker tokens around the image rows and, with image splitting, the four quadrants before the whole image:
+    greedy tokens equal those of transformers on the equivalent ids and pixel values; the router counts the same
+    number of prompt rows."""
+    from tgi_b200.models.idefics2 import Idefics2CausalLM, expansion_length, quadrants_and_whole
+
+    torch.manual_seed(0)
+    ids_of = _marker_tokenizer(tmp_path)
+    image_id, fake = ids_of["<image>"], ids_of["<fake_token_around_image>"]
+    cfg = transformers.Idefics2Config(
+        vision_config=VIS, text_config=dict(TXT, model_type="mistral", sliding_window=None), image_token_id=image_id,
+        perceiver_config=dict(resampler_n_latents=4, resampler_depth=2, resampler_n_heads=2, resampler_head_dim=16,
+                              num_key_value_heads=1, hidden_act="silu", hidden_size=64, rms_norm_eps=1e-6))
+    hf = transformers.Idefics2ForConditionalGeneration(cfg).eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    c = json.loads((tmp_path / "config.json").read_text())
+    c["vision_config"] = dict(c["vision_config"], **VIS)
+    (tmp_path / "config.json").write_text(json.dumps(c))
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps({"do_image_splitting": split}))
+    model = get_model(str(tmp_path), dtype="float32", device=torch.device("cpu"))
+    assert isinstance(model, Idefics2CausalLM) and model.fake_id == fake
+    L = model.tokens_per_image
+    views = 5 if split else 1
+    R = expansion_length(views, L)
+    png = _png(1)
+    reqs = [_request(0, [("text", "ab"), ("image", png), ("text", "cde")], 6, range(1, 6))]
+    model.init_kv_cache(8)
+    batch = model.batch_type.from_pb(pb.Batch(id=0, requests=reqs, size=1), model.tokenizer, torch.float32,
+                                     torch.device("cpu"), 0)
+    prompt = list(batch.seqs[0].ids)
+    assert prompt.count(image_id) == R and len(prompt) == 5 + R
+    got = []
+    while batch is not None:
+        gens, batch, _ = model.generate_token(batch)
+        for g in gens:
+            got.extend(g.tokens.token_ids)
+    run = [fake]
+    for _ in range(views):
+        run += [image_id] * L + [fake]
+    text_a = model.tokenizer("ab", add_special_tokens=False)["input_ids"]
+    text_b = model.tokenizer("cde", add_special_tokens=False)["input_ids"]
+    ids = torch.tensor([text_a + run + text_b])
+    parts = quadrants_and_whole(png) if split else [png]
+    px = torch.stack([preprocess_image(p, 28, SIGLIP_MEAN, SIGLIP_STD) for p in parts]).unsqueeze(0)
+    with torch.no_grad():
+        ref = hf.generate(input_ids=ids, attention_mask=torch.ones_like(ids), pixel_values=px,
+                          pixel_attention_mask=torch.ones(1, px.shape[1], 28, 28, dtype=torch.long),
+                          max_new_tokens=6, min_new_tokens=6, do_sample=False)
+    assert got[:6] == ref[0, ids.shape[1]:].tolist(), (got, ref[0, ids.shape[1]:].tolist())
+    # the router's count for the same image
+    from tgi_b200.router.build import build
+
+    build()
+    from tgi_b200.router import _router_test as rt
+
+    rcfg = dict(c, _idefics2={"split": split})
+    assert rt.tokens_per_image(json.dumps(rcfg), 52, 40) == R
+    assert rt.tokens_per_image(json.dumps(c), 52, 40) == L

@@ -479,6 +479,10 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
 
         longest, split = processor_settings(path, int(vis["image_size"]))
         runner_cls, extra_kw = Idefics3CausalLM, dict(longest_edge=longest, do_split=split)
+    if mt == "idefics2":
+        from .idefics2 import Idefics2CausalLM, processor_split_setting    # markers around images, optional 5-way split
+
+        runner_cls, extra_kw = Idefics2CausalLM, dict(do_split=processor_split_setting(path))
     runner = runner_cls(model, tower, projector, tokenizer, dtype, device, rank, world, image_token, drop_cls,
                          scale, speculate=speculate, **extra_kw,
                          kv_cache_dtype=resolve_kv_dtype(kv_cache_dtype, dtype), max_prefill_tokens=max_prefill_tokens)

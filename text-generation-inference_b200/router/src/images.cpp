@@ -313,7 +313,14 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
   if (mt == "idefics2") {
     // perceiver resampler: a fixed number of latents per image
     const json::Value& pc = config.has("perceiver_config") ? config["perceiver_config"] : vis;
-    return pc.is_object() && pc.has("resampler_n_latents") ? static_cast<uint32_t>(pc["resampler_n_latents"].as_double()) : 64;
+    const uint32_t seq =
+        pc.is_object() && pc.has("resampler_n_latents") ? static_cast<uint32_t>(pc["resampler_n_latents"].as_double()) : 64;
+    // `_idefics2` is added at start-up when the tokenizer has the marker token: the image's rows sit between markers,
+    // and with image splitting the four quadrants come before the whole image (the shard's models/idefics2.py)
+    if (!config.has("_idefics2")) return seq;
+    const bool split = config["_idefics2"].has("split") && config["_idefics2"]["split"].as_bool() && width >= 2 && height >= 2;
+    const uint32_t views = split ? 5 : 1;
+    return views * (seq + 1) + 1;
   }
   if (mt == "idefics3") {
     // pixel shuffle folds scale x scale patches of a view into one row

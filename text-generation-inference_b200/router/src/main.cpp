@@ -298,6 +298,29 @@ int main(int argc, char** argv) {
         std::cerr << "[router] idefics3 marker probe failed: " << e.what() << std::endl;
       }
     }
+    if (rc.model_config.is_object() && rc.model_config.has("model_type") &&
+        rc.model_config["model_type"].as_string() == "idefics2") {
+      try {
+        if (text_services.encode("<fake_token_around_image>", false, 0).size() == 1) {
+          bool split = false;
+          std::ifstream pf(tokenizer + "/preprocessor_config.json");
+          if (pf) {
+            std::stringstream ss;
+            ss << pf.rdbuf();
+            try {
+              json::Value pc = json::Value::parse(ss.str());
+              if (pc.has("do_image_splitting")) split = pc["do_image_splitting"].as_bool();
+            } catch (const std::exception&) {
+            }
+          }
+          json::Value sp = json::Value::object();
+          sp.set("split", split);
+          rc.model_config.set("_idefics2", sp);
+        }
+      } catch (const std::exception& e) {
+        std::cerr << "[router] idefics2 marker probe failed: " << e.what() << std::endl;
+      }
+    }
     api::Router router(backend, text_services, rc, &metrics);
 
     http::Server server(args.get("hostname", "0.0.0.0"), static_cast<int>(args.num("port", 3000)),
