@@ -136,6 +136,9 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
     tokens_per_image: int = 0
     image_size: int = 224
     norm = (CLIP_MEAN, CLIP_STD)
+    # PaliGemma: every text piece is "<bos>" + text + "\n" and is tokenised without further special tokens
+    # (``models/vlm_causal_lm.py:194-197, 433-437`` of the reference); the newline separates prompt and answer
+    text_wrap: Optional[Tuple[str, str]] = None
 
     @classmethod
     def image_payload(cls, data: bytes):
@@ -155,8 +158,12 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
             first_text = True
             for c in chunks:
                 if c.WhichOneof("chunk") == "text":
-                    ids.extend(tokenizer(c.text, truncation=False,
-                                         add_special_tokens=r.add_special_tokens and first_text)["input_ids"])
+                    if cls.text_wrap is not None:
+                        ids.extend(tokenizer(cls.text_wrap[0] + c.text + cls.text_wrap[1], truncation=False,
+                                             add_special_tokens=False)["input_ids"])
+                    else:
+                        ids.extend(tokenizer(c.text, truncation=False,
+                                             add_special_tokens=r.add_special_tokens and first_text)["input_ids"])
                     first_text = False
                 else:
                     payload, rows = cls.image_payload(c.image.data)
@@ -189,7 +196,7 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
 class VlmCausalLM(FlashCausalLM):
     def __init__(self, model: CausalDecoder, tower: VisionTower, projector, tokenizer, dtype, device, rank, world,
                  image_token_id: int, drop_cls: bool, embed_scale: float = 1.0, image_wrap=(None, None),
-                 bidirectional_images: bool = False, **kw):
+                 bidirectional_images: bool = False, text_wrap=None, **kw):
         super().__init__(model, tokenizer, dtype, device, rank, world, **kw)
         self.bidirectional_images = bidirectional_images
         if bidirectional_images:
@@ -201,7 +208,7 @@ class VlmCausalLM(FlashCausalLM):
         self.tokens_per_image = projector.out_tokens(tower.num_patches)
         self.batch_cls = type("BoundVlmBatch", (VlmCausalLMBatch,), dict(
             image_token_id=image_token_id, tokens_per_image=self.tokens_per_image, image_size=tower.image_size,
-            image_start_id=image_wrap[0], image_end_id=image_wrap[1],
+            image_start_id=image_wrap[0], image_end_id=image_wrap[1], text_wrap=text_wrap,
             norm=(CLIP_MEAN, CLIP_STD) if tower.kind == "clip" else (SIGLIP_MEAN, SIGLIP_STD)))
 
     @property
@@ -479,6 +486,10 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
 
         longest, split = processor_settings(path, int(vis["image_size"]))
         runner_cls, extra_kw = Idefics3CausalLM, dict(longest_edge=longest, do_split=split)
+    if mt == "paligemma":
+        bos = getattr(tokenizer, "bos_token", None)
+        if isinstance(bos, str) and bos:
+            extra_kw = dict(extra_kw, text_wrap=(bos, "\n"))
     if mt == "idefics2":
         from .idefics2 import Idefics2CausalLM, processor_split_setting    # markers around images, optional 5-way split
 

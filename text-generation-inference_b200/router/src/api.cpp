@@ -154,7 +154,10 @@ GenerateParams Router::validate(const std::string& inputs, const Value& p) {
       pb::InputChunk c;
       if (!pc.is_image) {
         if (pc.text.empty()) continue;
-        auto ids = text_.encode(pc.text, add_special && first_text, 0);
+        const bool wrap = cfg_.model_config.is_object() && cfg_.model_config.has("_text_wrap");
+        auto ids = wrap ? text_.encode(cfg_.model_config["_text_wrap"]["prefix"].as_string() + pc.text +
+                                           cfg_.model_config["_text_wrap"]["suffix"].as_string(), false, 0)
+                        : text_.encode(pc.text, add_special && first_text, 0);
         first_text = false;
         v.input_ids.insert(v.input_ids.end(), ids.begin(), ids.end());
         c.text = pc.text;

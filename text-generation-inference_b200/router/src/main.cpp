@@ -299,6 +299,15 @@ int main(int argc, char** argv) {
       }
     }
     if (rc.model_config.is_object() && rc.model_config.has("model_type") &&
+        rc.model_config["model_type"].as_string() == "paligemma" && loaded.has("bos_token") &&
+        loaded["bos_token"].is_string() && !loaded["bos_token"].as_string().empty()) {
+      // PaliGemma: every text piece is bos + text + "\n", tokenised as it stands (the shard does the same)
+      json::Value w = json::Value::object();
+      w.set("prefix", loaded["bos_token"].as_string());
+      w.set("suffix", "\n");
+      rc.model_config.set("_text_wrap", w);
+    }
+    if (rc.model_config.is_object() && rc.model_config.has("model_type") &&
         rc.model_config["model_type"].as_string() == "idefics2") {
       try {
         if (text_services.encode("<fake_token_around_image>", false, 0).size() == 1) {
