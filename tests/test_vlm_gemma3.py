@@ -81,3 +81,38 @@ def test_horizon_changes_the_result(gemma):
         assert (meta.attn_horizon is not None) == bidir
         outs.append(model.forward(meta).float())
     assert not torch.allclose(outs[0], outs[1], atol=1e-5)
+
+
+def test_gemma3_image_runs_get_blank_lines_with_a_real_tokenizer(gemma, tmp_path):
+    """With a Hugging Face tokenizer an image is "\\n\\n" + begin token + rows + end token + "\\n\\n", as the processor
+    writes it; the router counts those tokens too."""
+    import shutil
+
+    from tokenizers import Regex, Tokenizer, models, pre_tokenizers
+
+    _, d = gemma
+    for f in d.iterdir():
+        shutil.copy(f, tmp_path / f.name)
+    chars = ["<unk>"] + [chr(c) for c in range(32, 127)] + ["\n"]
+    tok = Tokenizer(models.WordLevel({c: i for i, c in enumerate(chars)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(r"\n"), "isolated"),
+                                                 pre_tokenizers.Split(Regex("."), "isolated")])
+    tok.save(str(tmp_path / "tokenizer.json"))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "PreTrainedTokenizerFast",
+                                                                "unk_token": "<unk>"}))
+    model = get_model(str(tmp_path), dtype="float32", device=torch.device("cpu"))
+    reqs = [_request(0, [("text", "ab"), ("image", _png(1)), ("text", "c")], 2, range(1, 4))]
+    model.init_kv_cache(6)
+    batch = model.batch_type.from_pb(pb.Batch(id=0, requests=reqs, size=1), model.tokenizer, torch.float32,
+                                     torch.device("cpu"), 0)
+    nl = tok.token_to_id("\n")
+    a, b, c = (tok.token_to_id(x) for x in "abc")
+    assert list(batch.seqs[0].ids) == [a, b, nl, nl, BOI] + [IMG] * 4 + [EOI, nl, nl, c]
+    from tgi_b200.router.build import build
+
+    build()
+    from tgi_b200.router import _router_test as rt
+
+    cfg = json.loads((tmp_path / "config.json").read_text())
+    assert rt.tokens_per_image(json.dumps(dict(cfg, _gemma3={"pad": 2})), 52, 40) == 4 + 2 + 4
+    assert rt.tokens_per_image(json.dumps(cfg), 52, 40) == 4 + 2

@@ -133,6 +133,7 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
     image_token_id: int = 0
     image_start_id: Optional[int] = None      # tokens put around the placeholder rows (Gemma-3: begin / end of image)
     image_end_id: Optional[int] = None
+    image_pad_ids: Tuple[int, ...] = ()       # tokens before the start and after the end token (Gemma-3: "\n\n")
     tokens_per_image: int = 0
     image_size: int = 224
     norm = (CLIP_MEAN, CLIP_STD)
@@ -168,11 +169,13 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
                 else:
                     payload, rows = cls.image_payload(c.image.data)
                     if cls.image_start_id is not None:
+                        ids.extend(cls.image_pad_ids)
                         ids.append(cls.image_start_id)
                     images.append((len(ids), payload, rows))
                     ids.extend([cls.image_token_id] * rows)
                     if cls.image_end_id is not None:
                         ids.append(cls.image_end_id)
+                        ids.extend(cls.image_pad_ids)
             if r.truncate and len(ids) > r.truncate:
                 cut = len(ids) - r.truncate
                 if any(pos < cut for pos, _, _ in images):
@@ -196,7 +199,7 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
 class VlmCausalLM(FlashCausalLM):
     def __init__(self, model: CausalDecoder, tower: VisionTower, projector, tokenizer, dtype, device, rank, world,
                  image_token_id: int, drop_cls: bool, embed_scale: float = 1.0, image_wrap=(None, None),
-                 bidirectional_images: bool = False, text_wrap=None, **kw):
+                 bidirectional_images: bool = False, text_wrap=None, image_pad_ids=(), **kw):
         super().__init__(model, tokenizer, dtype, device, rank, world, **kw)
         self.bidirectional_images = bidirectional_images
         if bidirectional_images:
@@ -209,6 +212,7 @@ class VlmCausalLM(FlashCausalLM):
         self.batch_cls = type("BoundVlmBatch", (VlmCausalLMBatch,), dict(
             image_token_id=image_token_id, tokens_per_image=self.tokens_per_image, image_size=tower.image_size,
             image_start_id=image_wrap[0], image_end_id=image_wrap[1], text_wrap=text_wrap,
+            image_pad_ids=tuple(image_pad_ids),
             norm=(CLIP_MEAN, CLIP_STD) if tower.kind == "clip" else (SIGLIP_MEAN, SIGLIP_STD)))
 
     @property
@@ -486,6 +490,11 @@ def load_vlm(path, cfg, loader, process_group, rank, world, dtype, device, token
 
         longest, split = processor_settings(path, int(vis["image_size"]))
         runner_cls, extra_kw = Idefics3CausalLM, dict(longest_edge=longest, do_split=split)
+    if mt == "gemma3" and hasattr(tokenizer, "convert_tokens_to_ids"):
+        # the processor writes "\n\n<start_of_image>" ... "<end_of_image>\n\n" (reference: vlm_causal_lm.py:160-165)
+        pad = list(tokenizer("\n\n", add_special_tokens=False)["input_ids"])
+        if 0 < len(pad) <= 2:
+            extra_kw = dict(extra_kw, image_pad_ids=pad)
     if mt == "paligemma":
         bos = getattr(tokenizer, "bos_token", None)
         if isinstance(bos, str) and bos:

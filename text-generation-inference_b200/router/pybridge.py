@@ -66,6 +66,7 @@ def load(arg: str) -> str:
     model_cfg = cfg.get("config.json", {})
     return _ok(model_type=model_cfg.get("model_type"), has_chat_template=template is not None,
                bos_token=_STATE["bos_token"] if isinstance(_STATE["bos_token"], str) else None,
+               is_hf_tokenizer=hasattr(tok, "convert_tokens_to_ids"),
                max_position_embeddings=model_cfg.get("max_position_embeddings"),
                vocab_size=model_cfg.get("vocab_size"))
 

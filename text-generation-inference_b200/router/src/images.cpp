@@ -306,6 +306,8 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     uint32_t n = config.has("mm_tokens_per_image") ? static_cast<uint32_t>(config["mm_tokens_per_image"].as_double()) : 256;
     if (config.has("boi_token_index") || config.has("boi_token_id")) ++n;
     if (config.has("eoi_token_index") || config.has("eoi_token_id")) ++n;
+    // "\n\n" before the begin and after the end token when the tokenizer is a real one (`_gemma3.pad` tokens each side)
+    if (config.has("_gemma3")) n += 2 * static_cast<uint32_t>(config["_gemma3"]["pad"].as_double());
     return n;
   }
   if (mt == "idefics") return 3;  // <fake_token_around_image><image><fake_token_around_image>; cross-attention carries the image

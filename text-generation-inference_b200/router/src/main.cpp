@@ -308,6 +308,16 @@ int main(int argc, char** argv) {
       rc.model_config.set("_text_wrap", w);
     }
     if (rc.model_config.is_object() && rc.model_config.has("model_type") &&
+        rc.model_config["model_type"].as_string() == "gemma3" && rc.model_config.has("vision_config") &&
+        loaded.has("is_hf_tokenizer") && loaded["is_hf_tokenizer"].as_bool()) {
+      const size_t pad = text_services.encode("\n\n", false, 0).size();
+      if (pad > 0 && pad <= 2) {
+        json::Value g = json::Value::object();
+        g.set("pad", static_cast<long>(pad));
+        rc.model_config.set("_gemma3", g);
+      }
+    }
+    if (rc.model_config.is_object() && rc.model_config.has("model_type") &&
         rc.model_config["model_type"].as_string() == "idefics2") {
       try {
         if (text_services.encode("<fake_token_around_image>", false, 0).size() == 1) {
