@@ -487,6 +487,9 @@ def test_image_token_counts_match_the_runners(rt):
     for w, h in [(1, 1), (52, 40), (640, 480), (1920, 1080), (4000, 3000), (30, 3000), (999, 1001)]:
         rh, rw = smart_resize(h, w, 28, vis["min_pixels"], vis["max_pixels"])
         assert rt.tokens_per_image(json.dumps(cfg), w, h) == (rh // 28) * (rw // 28) + 2, (w, h)
+    # images at most 20 pixels wide are doubled before the resize (shard and router alike)
+    rh, rw = smart_resize(800, 40, 28, vis["min_pixels"], vis["max_pixels"])
+    assert rt.tokens_per_image(json.dumps(cfg), 20, 400) == (rh // 28) * (rw // 28) + 2
     cfg25 = dict(cfg, model_type="qwen2_5_vl")
     assert rt.tokens_per_image(json.dumps(cfg25), 640, 480) == rt.tokens_per_image(json.dumps(cfg), 640, 480)
     assert rt.tokens_per_image(json.dumps({"model_type": "idefics2", "vision_config": {},
@@ -566,5 +569,6 @@ def test_qwen2_vl_row_counts_random_sizes(rt):
         w, h = rng.randint(4, 5000), rng.randint(4, 5000)
         if max(w, h) / min(w, h) > 200:
             continue
-        rh, rw = smart_resize(h, w, 28, vis["min_pixels"], vis["max_pixels"])
+        k = 2 if w <= 20 else 1           # narrow images are doubled before the resize (shard and router)
+        rh, rw = smart_resize(k * h, k * w, 28, vis["min_pixels"], vis["max_pixels"])
         assert rt.tokens_per_image(cfg, w, h) == (rh // 28) * (rw // 28), (w, h)

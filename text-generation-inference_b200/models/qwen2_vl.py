@@ -72,6 +72,8 @@ def preprocess_qwen_image(data: bytes, patch: int, merge: int, temporal: int, mi
     from PIL import Image
 
     img = Image.open(io.BytesIO(data)).convert("RGB")
+    if img.width <= 20:      # very narrow images are doubled first (reference: vlm_causal_lm.py:203-204)
+        img = img.resize((img.width * 2, img.height * 2))
     h, w = smart_resize(img.height, img.width, patch * merge, min_pixels, max_pixels)
     img = img.resize((w, h), Image.BICUBIC)
     arr = torch.from_numpy(np.asarray(img, dtype=np.float32) / 255.0).permute(2, 0, 1)

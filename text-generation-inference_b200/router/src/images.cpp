@@ -284,7 +284,8 @@ uint32_t tokens_per_image(const json::Value& config, uint32_t width, uint32_t he
     const double patch = num("patch_size", 14), merge = num("spatial_merge_size", 2);
     const double factor = patch * merge;
     const double min_px = num("min_pixels", 56.0 * 56.0), max_px = num("max_pixels", 14.0 * 14.0 * 4.0 * 1280.0);
-    const double H = height, W = width;
+    // images at most 20 pixels wide are doubled before the resize, as the shard does
+    const double H = width <= 20 ? 2.0 * height : height, W = width <= 20 ? 2.0 * width : width;
     double h = std::max(factor, std::nearbyint(H / factor) * factor);
     double w = std::max(factor, std::nearbyint(W / factor) * factor);
     if (h * w > max_px) {
