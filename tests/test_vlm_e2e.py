@@ -125,34 +125,24 @@ def test_image_request_end_to_end(vlm_stack):
     assert st == 422 and "https" in bad2
 
 
-def test_idefics3_split_image_end_to_end(tmp_path):
-    """Router and shard agree on the prompt length of a split image: the router counts the tiles, the marker tokens
-    and the newlines from the image's size, the shard builds that layout (x-prompt-tokens is the router's count; the
-    shard would run out of the blocks the router allotted if it needed more)."""
-    from tests.test_vlm_idefics import TXT, VIS, _marker_tokenizer
-    from tgi_b200.models.idefics3 import expansion_length, tile_grid
+import contextlib
+
+
+@contextlib.contextmanager
+def _serve(model_dir, max_input=200):
+    """Shard + router for the model in ``model_dir``; yields the router's port."""
     from tgi_b200.router.build import build
 
-    torch.manual_seed(0)
-    ids_of = _marker_tokenizer(tmp_path)
-    cfg = transformers.Idefics3Config(vision_config=VIS, text_config=dict(TXT, model_type="llama"),
-                                      image_token_id=ids_of["<image>"], scale_factor=2)
-    transformers.Idefics3ForConditionalGeneration(cfg).eval().save_pretrained(str(tmp_path), safe_serialization=True)
-    c = json.loads((tmp_path / "config.json").read_text())
-    c["vision_config"] = dict(c["vision_config"], **VIS)
-    (tmp_path / "config.json").write_text(json.dumps(c))
-    (tmp_path / "preprocessor_config.json").write_text(json.dumps(
-        {"size": {"longest_edge": 84}, "max_image_size": {"longest_edge": 28}, "do_image_splitting": True}))
     router_bin = build()
-    uds = str(tmp_path / "shard")
+    uds = str(model_dir / "shard")
     env = dict(os.environ, PYTHONPATH=ROOT, TGI_B200_CPU_KV_BLOCKS="256")
-    shard = subprocess.Popen([sys.executable, "-m", "tgi_b200.server.cli", "serve", str(tmp_path), "--uds-path", uds,
+    shard = subprocess.Popen([sys.executable, "-m", "tgi_b200.server.cli", "serve", str(model_dir), "--uds-path", uds,
                               "--dtype", "float32"], env=env, cwd=ROOT)
     port = _free_port()
-    router = subprocess.Popen([str(router_bin), "--master-shard-uds-path", uds, "--tokenizer-name", str(tmp_path),
-                               "--port", str(port), "--hostname", "127.0.0.1", "--max-input-tokens", "200",
-                               "--max-total-tokens", "256", "--max-batch-prefill-tokens", "256", "--repo-root", ROOT],
-                              env=env, cwd=ROOT)
+    router = subprocess.Popen([str(router_bin), "--master-shard-uds-path", uds, "--tokenizer-name", str(model_dir),
+                               "--port", str(port), "--hostname", "127.0.0.1", "--max-input-tokens", str(max_input),
+                               "--max-total-tokens", str(max_input + 56), "--max-batch-prefill-tokens", str(max_input + 56),
+                               "--repo-root", ROOT], env=env, cwd=ROOT)
     try:
         deadline = time.time() + 180
         while time.time() < deadline:
@@ -165,6 +155,35 @@ def test_idefics3_split_image_end_to_end(tmp_path):
                 time.sleep(0.3)
         else:
             raise RuntimeError("router did not come up")
+        yield port
+    finally:
+        for p in (router, shard):
+            p.send_signal(signal.SIGTERM)
+        for p in (router, shard):
+            try:
+                p.wait(timeout=20)
+            except subprocess.TimeoutExpired:
+                p.kill()
+
+
+def test_idefics3_split_image_end_to_end(tmp_path):
+    """Router and shard agree on the prompt length of a split image: the router counts the tiles, the marker tokens
+    and the newlines from the image's size, the shard builds that layout (x-prompt-tokens is the router's count; the
+    shard would run out of the blocks the router allotted if it needed more)."""
+    from tests.test_vlm_idefics import TXT, VIS, _marker_tokenizer
+    from tgi_b200.models.idefics3 import expansion_length, tile_grid
+
+    torch.manual_seed(0)
+    ids_of = _marker_tokenizer(tmp_path)
+    cfg = transformers.Idefics3Config(vision_config=VIS, text_config=dict(TXT, model_type="llama"),
+                                      image_token_id=ids_of["<image>"], scale_factor=2)
+    transformers.Idefics3ForConditionalGeneration(cfg).eval().save_pretrained(str(tmp_path), safe_serialization=True)
+    c = json.loads((tmp_path / "config.json").read_text())
+    c["vision_config"] = dict(c["vision_config"], **VIS)
+    (tmp_path / "config.json").write_text(json.dumps(c))
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps(
+        {"size": {"longest_edge": 84}, "max_image_size": {"longest_edge": 28}, "do_image_splitting": True}))
+    with _serve(tmp_path) as port:
         for size in [(40, 52), (30, 90), (28, 28)]:                      # (height, width)
             uri = "data:image/png;base64," + base64.b64encode(_png(3, size)).decode()
             st, headers, out = _post(port, "/generate", {"inputs": f"ab![]({uri})cde",
@@ -174,11 +193,31 @@ def test_idefics3_split_image_end_to_end(tmp_path):
             want = 5 + expansion_length(rows, cols, 4, 1, 2)             # character tokenizer: "\n" 1 token, "\n\n" 2
             assert int(headers["x-prompt-tokens"]) == want, (size, rows, cols, headers["x-prompt-tokens"], want)
             assert json.loads(out)["details"]["generated_tokens"] == 4
-    finally:
-        for p in (router, shard):
-            p.send_signal(signal.SIGTERM)
-        for p in (router, shard):
-            try:
-                p.wait(timeout=20)
-            except subprocess.TimeoutExpired:
-                p.kill()
+
+
+def test_idefics2_markers_and_adjacent_images_end_to_end(tmp_path):
+    """Idefics2 with image splitting: five views per image between markers, and two images in a row share one marker;
+    the router's prompt length is the shard's."""
+    from tests.test_vlm_idefics import TXT, VIS, _marker_tokenizer
+
+    torch.manual_seed(0)
+    ids_of = _marker_tokenizer(tmp_path)
+    cfg = transformers.Idefics2Config(
+        vision_config=VIS, text_config=dict(TXT, model_type="mistral", sliding_window=None),
+        image_token_id=ids_of["<image>"],
+        perceiver_config=dict(resampler_n_latents=4, resampler_depth=2, resampler_n_heads=2, resampler_head_dim=16,
+                              num_key_value_heads=1, hidden_act="silu", hidden_size=64, rms_norm_eps=1e-6))
+    transformers.Idefics2ForConditionalGeneration(cfg).eval().save_pretrained(str(tmp_path), safe_serialization=True)
+    c = json.loads((tmp_path / "config.json").read_text())
+    c["vision_config"] = dict(c["vision_config"], **VIS)
+    (tmp_path / "config.json").write_text(json.dumps(c))
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps({"do_image_splitting": True}))
+    with _serve(tmp_path) as port:
+        uri1 = "data:image/png;base64," + base64.b64encode(_png(1)).decode()
+        uri2 = "data:image/png;base64," + base64.b64encode(_png(2)).decode()
+        one = 5 * (4 + 1) + 1
+        st, headers, out = _post(port, "/generate", {"inputs": f"ab![]({uri1})c", "parameters": {"max_new_tokens": 3}})
+        assert st == 200 and int(headers["x-prompt-tokens"]) == 3 + one, (out, dict(headers))
+        st, headers, out = _post(port, "/generate", {"inputs": f"ab![]({uri1})![]({uri2})c",
+                                                     "parameters": {"max_new_tokens": 3}})
+        assert st == 200 and int(headers["x-prompt-tokens"]) == 3 + 2 * one - 1, (out, dict(headers))

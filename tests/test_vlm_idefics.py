@@ -241,3 +241,46 @@ def test_idefics2_marker_layout_matches_transformers(tmp_path, split):
     rcfg = dict(c, _idefics2={"split": split})
     assert rt.tokens_per_image(json.dumps(rcfg), 52, 40) == R
     assert rt.tokens_per_image(json.dumps(c), 52, 40) == L
+
+
+def test_idefics2_adjacent_images_share_a_marker(tmp_path):
+    """Two images without text between them: marker, rows, marker, rows, marker (the processor collapses the doubled
+    marker); generation equals transformers on that prompt."""
+    from tgi_b200.models.idefics2 import expansion_length
+
+    torch.manual_seed(0)
+    ids_of = _marker_tokenizer(tmp_path)
+    image_id, fake = ids_of["<image>"], ids_of["<fake_token_around_image>"]
+    cfg = transformers.Idefics2Config(
+        vision_config=VIS, text_config=dict(TXT, model_type="mistral", sliding_window=None), image_token_id=image_id,
+        perceiver_config=dict(resampler_n_latents=4, resampler_depth=2, resampler_n_heads=2, resampler_head_dim=16,
+                              num_key_value_heads=1, hidden_act="silu", hidden_size=64, rms_norm_eps=1e-6))
+    hf = transformers.Idefics2ForConditionalGeneration(cfg).eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    c = json.loads((tmp_path / "config.json").read_text())
+    c["vision_config"] = dict(c["vision_config"], **VIS)
+    (tmp_path / "config.json").write_text(json.dumps(c))
+    model = get_model(str(tmp_path), dtype="float32", device=torch.device("cpu"))
+    L = model.tokens_per_image
+    png1, png2 = _png(1), _png(2)
+    reqs = [_request(0, [("text", "ab"), ("image", png1), ("image", png2), ("text", "c")], 5, range(1, 6))]
+    model.init_kv_cache(8)
+    batch = model.batch_type.from_pb(pb.Batch(id=0, requests=reqs, size=1), model.tokenizer, torch.float32,
+                                     torch.device("cpu"), 0)
+    prompt = list(batch.seqs[0].ids)
+    R = expansion_length(1, L)
+    assert prompt.count(image_id) == 2 * R - 1
+    got = []
+    while batch is not None:
+        gens, batch, _ = model.generate_token(batch)
+        for g in gens:
+            got.extend(g.tokens.token_ids)
+    run = [fake] + [image_id] * L + [fake] + [image_id] * L + [fake]
+    ids = torch.tensor([model.tokenizer("ab", add_special_tokens=False)["input_ids"] + run +
+                        model.tokenizer("c", add_special_tokens=False)["input_ids"]])
+    px = torch.stack([preprocess_image(p, 28, SIGLIP_MEAN, SIGLIP_STD) for p in (png1, png2)]).unsqueeze(0)
+    with torch.no_grad():
+        ref = hf.generate(input_ids=ids, attention_mask=torch.ones_like(ids), pixel_values=px,
+                          pixel_attention_mask=torch.ones(1, 2, 28, 28, dtype=torch.long),
+                          max_new_tokens=5, min_new_tokens=5, do_sample=False)
+    assert got[:5] == ref[0, ids.shape[1]:].tolist(), (got, ref[0, ids.shape[1]:].tolist())

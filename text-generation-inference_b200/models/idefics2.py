@@ -62,6 +62,20 @@ class Idefics2Batch(VlmCausalLMBatch):
         views = torch.stack([preprocess_image(p, cls.image_size, *cls.norm) for p in parts])
         return views, expansion_length(len(parts), cls.tokens_per_image)
 
+    @classmethod
+    def join_adjacent(cls, payload, rows: int):
+        if cls.fake_id is None:
+            return payload, rows
+        return _Joined(payload), rows - 1
+
+
+class _Joined:
+    """Views of an image that directly follows another image: its opening marker is the previous image's closing one
+    (the processor collapses doubled markers)."""
+
+    def __init__(self, views: torch.Tensor):
+        self.views = views
+
 
 def _size(data: bytes) -> Tuple[int, int]:
     from PIL import Image
@@ -81,15 +95,16 @@ class Idefics2CausalLM(VlmCausalLM):
     def image_features(self, payloads: list) -> List[torch.Tensor]:
         if self.fake_id is None:
             return super().image_features(payloads)
-        feats = self.encode_images(torch.cat(payloads))                   # [sum of views, L, H]
+        views = [p.views if isinstance(p, _Joined) else p for p in payloads]
+        feats = self.encode_images(torch.cat(views))                      # [sum of views, L, H]
         t = torch.tensor([self.fake_id], dtype=torch.int32, device=self.device)
         fake = self.model.embed_tokens(t, torch.zeros_like(t)).to(feats.dtype)
         out, cursor = [], 0
-        for p in payloads:
-            parts = [fake]
-            for v in range(p.shape[0]):
+        for p, vw in zip(payloads, views):
+            parts = [] if isinstance(p, _Joined) else [fake]
+            for v in range(vw.shape[0]):
                 parts += [feats[cursor + v], fake]
-            cursor += p.shape[0]
+            cursor += vw.shape[0]
             out.append(torch.cat(parts, dim=0))
         return out
 

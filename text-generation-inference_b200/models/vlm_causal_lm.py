@@ -147,6 +147,11 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
         return preprocess_image(data, cls.image_size, *cls.norm), cls.tokens_per_image
 
     @classmethod
+    def join_adjacent(cls, payload, rows: int):
+        """Hook for layouts in which an image that directly follows another one shares a marker with it."""
+        return payload, rows
+
+    @classmethod
     def batch_tokenized_inputs(cls, requests, tokenizer) -> List[List[int]]:
         out = []
         cls._pending_images = []
@@ -157,8 +162,10 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
             if not chunks:
                 ids = list(tokenizer(r.inputs, truncation=False, add_special_tokens=r.add_special_tokens)["input_ids"])
             first_text = True
+            after_image = False        # the previous chunk was an image (no text in between)
             for c in chunks:
                 if c.WhichOneof("chunk") == "text":
+                    after_image = after_image and not c.text
                     if cls.text_wrap is not None:
                         ids.extend(tokenizer(cls.text_wrap[0] + c.text + cls.text_wrap[1], truncation=False,
                                              add_special_tokens=False)["input_ids"])
@@ -168,6 +175,9 @@ class VlmCausalLMBatch(FlashCausalLMBatch):
                     first_text = False
                 else:
                     payload, rows = cls.image_payload(c.image.data)
+                    if after_image:
+                        payload, rows = cls.join_adjacent(payload, rows)
+                    after_image = True
                     if cls.image_start_id is not None:
                         ids.extend(cls.image_pad_ids)
                         ids.append(cls.image_start_id)

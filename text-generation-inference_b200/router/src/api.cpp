@@ -150,10 +150,12 @@ GenerateParams Router::validate(const std::string& inputs, const Value& p) {
     // placeholder ids (derived from its bytes, so the prefix cache tells images apart)
     if (truncate) throw validation_error("`truncate` cannot be combined with image inputs");
     bool first_text = true;
+    bool after_image = false;     // the previous piece was an image: Idefics2 lets adjacent images share a marker
     for (const auto& pc : pieces) {
       pb::InputChunk c;
       if (!pc.is_image) {
         if (pc.text.empty()) continue;
+        after_image = false;
         const bool wrap = cfg_.model_config.is_object() && cfg_.model_config.has("_text_wrap");
         auto ids = wrap ? text_.encode(cfg_.model_config["_text_wrap"]["prefix"].as_string() + pc.text +
                                            cfg_.model_config["_text_wrap"]["suffix"].as_string(), false, 0)
@@ -168,7 +170,9 @@ GenerateParams Router::validate(const std::string& inputs, const Value& p) {
         } catch (const std::exception& e) {
           throw validation_error(std::string("invalid image: ") + e.what());
         }
-        const uint32_t n = images::tokens_per_image(cfg_.model_config, img.width, img.height);
+        uint32_t n = images::tokens_per_image(cfg_.model_config, img.width, img.height);
+        if (after_image && cfg_.model_config.has("_idefics2") && n > 0) --n;
+        after_image = true;
         for (uint32_t i = 0; i < n; ++i) v.input_ids.push_back(images::placeholder_id(img.data, i));
         c.is_image = true;
         c.data = std::move(img.data);
